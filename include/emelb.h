@@ -1,0 +1,215 @@
+/*
+ * emelb.h — C-ABI of the B200 (sm_100a) CUDA backend for EMEL's quantized
+ * matrix-product path.
+ *
+ * EMEL has no C plugin ABI of its own (include/emel/emel.h:1-18 only declares
+ * emel_error_type); the seam this library sits behind is the C++ kernel-event
+ * surface `bool emel::kernel::any::process_event(const event::op_X&)`
+ * (src/emel/kernel/any.hpp:76-80).  Every entry point below names the
+ * reference interface it replaces.  A `kernel::cuda::sm` actor forwards its
+ * op events to these calls one-to-one (see emel.cpp_b200/cuda_sm.hpp).
+ *
+ * Conventions
+ *  - Every call returns the reference's kernel error bitmask
+ *    (src/emel/kernel/errors.hpp:7-13).  Nothing throws or aborts.
+ *  - Views are borrowed for the duration of the call.
+ *  - A view's `data` pointer may be: a device pointer; a host pointer inside
+ *    a span registered with emelb_residency_upload (weights: the device copy
+ *    is used, no transfer); or any other host pointer (activations/results:
+ *    staged through the context's pinned buffers, the call returns after the
+ *    result is back in host memory).  The pointer kind is looked up (residency
+ *    table, then the CUDA driver's pointer attributes), never guessed.
+ *  - One context per caller thread/lane; a context is not re-entrant
+ *    (same rule as one kernel actor per lane,
+ *    src/emel/kernel/matmul/context.hpp:16-24).
+ *  - With device-resident operands a call only enqueues work on the context's
+ *    stream; emelb_sync waits for it.
+ */
+#ifndef EMELB_H
+#define EMELB_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* src/emel/kernel/errors.hpp:7-13 */
+enum {
+  EMELB_OK = 0u,
+  EMELB_INVALID_REQUEST = 1u << 0,
+  EMELB_UNSUPPORTED_OP = 1u << 1,
+  EMELB_INTERNAL_ERROR = 1u << 2,
+  EMELB_UNTRACKED = 1u << 3
+};
+
+/* dtype codes: src/emel/kernel/events.hpp:78-123 (ggml's numbering). */
+enum {
+  EMELB_F32 = 0,
+  EMELB_F16 = 1,
+  EMELB_Q4_0 = 2,
+  EMELB_Q8_0 = 8,
+  EMELB_Q4_K = 12,
+  EMELB_Q6_K = 14,
+  EMELB_Q8_K = 15,
+  EMELB_I32 = 26,
+  EMELB_UNKNOWN = 255
+};
+
+/* tensor_view / tensor_view_mut: src/emel/kernel/events.hpp:125-137.
+ * ne[0] is the fastest dimension, nb[i] the byte stride of dimension i. */
+typedef struct emelb_view {
+  const void* data;
+  uint8_t type;
+  uint64_t ne[4];
+  uint64_t nb[4];
+} emelb_view;
+
+/* EMEL_KERNEL_GENERIC_OP_FIELDS + op_mul_mat_argmax::index_out:
+ * src/emel/kernel/events.hpp:178-189, 220-223. `dst.data` is written. */
+typedef struct emelb_op {
+  emelb_view src0;
+  emelb_view src1;
+  emelb_view src2;
+  emelb_view dst;
+  uint8_t op_params[64];
+  uint32_t op_params_size;
+  int32_t* index_out;
+} emelb_op;
+
+/* op codes for emelb_can_run */
+enum {
+  EMELB_OP_MUL_MAT = 1,
+  EMELB_OP_MUL_MAT_ARGMAX = 2,
+  EMELB_OP_FLASH_ATTN_EXT = 3
+};
+
+/* lifecycle: src/emel/model/tensor/events.hpp:18-24 */
+enum {
+  EMELB_LIFECYCLE_UNBOUND = 0,
+  EMELB_LIFECYCLE_RESIDENT = 1,
+  EMELB_LIFECYCLE_EVICTED = 2,
+  EMELB_LIFECYCLE_INTERNAL_ERROR = 3,
+  EMELB_LIFECYCLE_MMAP_RESIDENT = 4
+};
+
+/* tensor_state: src/emel/model/tensor/events.hpp:26-34; `buffer` is the
+ * device address of the uploaded bytes, `host` the span it mirrors. */
+typedef struct emelb_tensor_state {
+  uint8_t lifecycle_state;
+  const void* buffer;
+  uint64_t buffer_bytes;
+  const void* host;
+  int32_t tensor_type;
+} emelb_tensor_state;
+
+/* Dispatch counters; names follow event::diagnostics
+ * (src/emel/kernel/events.hpp:39-62). */
+typedef struct emelb_diag {
+  uint64_t optimized_flash_dispatch_calls;
+  uint64_t shared_flash_dispatch_calls;
+  uint64_t optimized_q4_dispatch_calls;
+  uint64_t optimized_q4_vector_dispatch_calls;
+  uint64_t optimized_q6_dispatch_calls;
+  uint64_t optimized_q6_vector_dispatch_calls;
+  uint64_t optimized_q6_vector_argmax_dispatch_calls;
+  uint64_t optimized_q8_0_dispatch_calls;
+  uint64_t optimized_q4_0_dispatch_calls;
+  uint64_t rejected_dispatch_calls;
+  uint64_t kernel_launches;      /* CUDA kernels launched by this context */
+  uint64_t h2d_bytes;            /* staged host->device bytes */
+  uint64_t d2h_bytes;            /* staged device->host bytes */
+} emelb_diag;
+
+typedef struct emelb_ctx emelb_ctx;
+
+/* ---- context: replaces constructing one kernel actor
+ * (src/emel/kernel/x86_64/context.hpp:214-243). Allocates the persistent
+ * workspace (activation scratch, attention partials, pinned staging); no
+ * allocation happens in any dispatch call afterwards. ---- */
+uint32_t emelb_create(int device, emelb_ctx** out);
+uint32_t emelb_destroy(emelb_ctx* ctx);
+/* waits for the context's stream; EMELB_INTERNAL_ERROR on a CUDA error */
+uint32_t emelb_sync(emelb_ctx* ctx);
+/* the cudaStream_t all work of this context is enqueued on */
+uint32_t emelb_get_stream(emelb_ctx* ctx, void** stream_out);
+/* event::capture_diagnostics: src/emel/kernel/any.hpp:38-74 */
+uint32_t emelb_diagnostics(const emelb_ctx* ctx, emelb_diag* out);
+/* attention numerics: 0 = split-KV f32 accumulators (fast, default);
+ * 1 = reference order: sequential over tokens with an f16-rounded accumulator
+ * (src/emel/kernel/detail.hpp:5238-5291). */
+uint32_t emelb_set_attention_mode(emelb_ctx* ctx, int mode);
+
+/* ---- residency: replaces io::loader strategy `external_buffer`
+ * (src/emel/io/loader/events.hpp:25-31, rejected as unsupported at
+ * src/emel/io/loader/sm.hpp:78-81) and model::tensor lifecycle/state
+ * (src/emel/model/tensor/events.hpp:18-34, 85-89). Bytes are uploaded
+ * unchanged; `host` stays the key a later view may carry. ---- */
+uint32_t emelb_residency_upload(emelb_ctx* ctx, int32_t tensor_id,
+                                const void* host, uint64_t bytes,
+                                int32_t tensor_type, const void** dev_out);
+uint32_t emelb_residency_evict(emelb_ctx* ctx, int32_t tensor_id);
+uint32_t emelb_residency_state(const emelb_ctx* ctx, int32_t tensor_id,
+                               emelb_tensor_state* out);
+
+/* plain device buffers for activations / KV cache owned by the caller */
+uint32_t emelb_device_alloc(emelb_ctx* ctx, uint64_t bytes, void** dev_out);
+uint32_t emelb_device_free(emelb_ctx* ctx, void* dev);
+uint32_t emelb_copy_to_device(emelb_ctx* ctx, void* dev, const void* host,
+                              uint64_t bytes);
+uint32_t emelb_copy_to_host(emelb_ctx* ctx, void* host, const void* dev,
+                            uint64_t bytes);
+
+/* ---- guards: replaces can_run_mul_mat / can_run_mul_mat_argmax /
+ * can_run_flash_attn_ext + validate_dispatch_request
+ * (src/emel/kernel/detail.hpp:3843-3872, 3573-3606, 4346-4390, 1919-1927).
+ * Pure: returns EMELB_OK or EMELB_INVALID_REQUEST, launches nothing. ---- */
+uint32_t emelb_can_run(const emelb_ctx* ctx, uint32_t op_code,
+                       const emelb_op* op);
+
+/* ---- op_mul_mat: replaces x86_64::sm.process_event(op_mul_mat)
+ * (src/emel/kernel/x86_64/sm.hpp:355-423) i.e. run_mul_mat
+ * (src/emel/kernel/detail.hpp:3356-3571) and the AVX2 drivers
+ * (src/emel/kernel/x86_64/actions.hpp:1186-1326).
+ * src0 = {K, M} Q4_K|Q6_K|Q8_0|Q4_0 rows; src1 = {N, K} f32 (token fastest),
+ * or the pre-quantized vector form {1, K} of type Q8_K / Q8_0
+ * (src/emel/kernel/aarch64/actions.hpp:1471-1503); dst = {N, M} f32. ---- */
+uint32_t emelb_mul_mat(emelb_ctx* ctx, const emelb_op* op);
+
+/* ---- op_mul_mat_argmax: replaces run_mul_mat_argmax
+ * (src/emel/kernel/detail.hpp:3608-3731): dst[0] = best value,
+ * *index_out = lowest row attaining it. ---- */
+uint32_t emelb_mul_mat_argmax(emelb_ctx* ctx, const emelb_op* op);
+
+/* ---- op_flash_attn_ext: replaces
+ * run_flash_attn_ext_active_kv_with_workspace
+ * (src/emel/kernel/detail.hpp:5238-5300) and the AVX2 one-chunk route
+ * (src/emel/kernel/x86_64/actions.hpp:1575-1641). ---- */
+uint32_t emelb_flash_attn_ext(emelb_ctx* ctx, const emelb_op* op);
+
+/* ---- activation quantizers: replace quantize_row_q8_k_strided /
+ * quantize_row_q8_0_strided (src/emel/kernel/detail.hpp:826-867, 804-824).
+ * src = f32 {N, K} (token fastest, as op_mul_mat's src1); dst type selects
+ * Q8_K or Q8_0; dst holds N rows of K/256 (K/32) reference-layout blocks,
+ * row j = column j of src.  Bit-exact. ---- */
+uint32_t emelb_quantize(emelb_ctx* ctx, const emelb_view* src_f32,
+                        const emelb_view* dst);
+
+/* ---- block dequantizers: replace dequantize_row_q4_k / q6_k / q8_0 / q4_0
+ * (src/emel/kernel/detail.hpp:523-552, 592-629, 679-690, 487-502).
+ * src = {K, M} quantized rows, dst = {K, M} f32.  Bit-exact. ---- */
+uint32_t emelb_dequantize(emelb_ctx* ctx, const emelb_view* src,
+                          const emelb_view* dst_f32);
+
+/* ---- row-slice helper: replaces compute_sliced_mul_mat_event +
+ * compute_fixed_row_slice (src/emel/kernel/matmul/detail.hpp:36-54,
+ * src/emel/kernel/matmul/actions.hpp:48-67). Pure host arithmetic:
+ * writes lane `lane` of `lane_count`'s slice of `op` to `out`. ---- */
+uint32_t emelb_row_slice(const emelb_op* op, uint32_t lane,
+                         uint32_t lane_count, emelb_op* out,
+                         uint64_t* row_begin, uint64_t* row_count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMELB_H */

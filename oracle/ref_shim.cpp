@@ -1,0 +1,262 @@
+// TEST INFRASTRUCTURE ONLY — never linked into or called by the product path.
+//
+// Thin extern "C" exports over the reference's own kernel headers, included in
+// place from the reference checkout (-I<reference>/src -I<reference>/include;
+// nothing is copied).  Built into oracle/_ref/libemel_ref.so by
+// oracle/Makefile with `g++ -O2 -std=c++20 -ffp-contract=off` and no global
+// -mavx2/-mfma: the AVX2 functions carry their own target attributes
+// (src/emel/kernel/x86_64/actions.hpp:22-37), and contraction is off so that
+// "bit-exact against the reference" names one well-defined build.
+//
+// Uses: validating oracle/emel_oracle.c, generating tests/golden fixtures,
+// being the checker in the GPU parity tests, and the timed CPU baseline.
+
+#include <cstdint>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include "emel/kernel/x86_64/actions.hpp"
+
+#include "../include/emelb.h"
+
+namespace kd = ::emel::kernel::detail;
+namespace kq = ::emel::kernel::detail::quant;
+namespace kx = ::emel::kernel::x86_64::detail;
+namespace ev = ::emel::kernel::event;
+
+namespace {
+
+ev::tensor_view to_view(const emelb_view& v) {
+  ev::tensor_view out{};
+  out.data = v.data;
+  out.type = static_cast<ev::dtype>(v.type);
+  for (int i = 0; i < 4; ++i) {
+    out.ne[i] = v.ne[i];
+    out.nb[i] = v.nb[i];
+  }
+  return out;
+}
+
+ev::tensor_view_mut to_view_mut(const emelb_view& v) {
+  ev::tensor_view_mut out{};
+  out.data = const_cast<void*>(v.data);
+  out.type = static_cast<ev::dtype>(v.type);
+  for (int i = 0; i < 4; ++i) {
+    out.ne[i] = v.ne[i];
+    out.nb[i] = v.nb[i];
+  }
+  return out;
+}
+
+template <class op_type>
+op_type to_op(const emelb_op& op) {
+  op_type out{};
+  out.src0 = to_view(op.src0);
+  out.src1 = to_view(op.src1);
+  out.src2 = to_view(op.src2);
+  out.dst = to_view_mut(op.dst);
+  std::memcpy(out.op_params.data(), op.op_params, 64);
+  out.op_params_size = op.op_params_size;
+  return out;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---- fp16 <-> fp32 (src/emel/kernel/detail.hpp:350-392)
+float ref_fp16_to_fp32(uint16_t h) { return kq::fp16_to_fp32(h); }
+uint16_t ref_fp32_to_fp16(float f) { return kq::fp32_to_fp16(f); }
+
+// ---- activation quantizers (src/emel/kernel/detail.hpp:804-867)
+void ref_quantize_q8_k(const float* x, uint64_t stride, void* y, int64_t k) {
+  kq::quantize_row_q8_k_strided(x, stride, static_cast<kq::block_q8_k*>(y), k);
+}
+void ref_quantize_q8_0(const float* x, uint64_t stride, void* y, int64_t k) {
+  kq::quantize_row_q8_0_strided(x, stride, static_cast<kq::block_q8_0*>(y), k);
+}
+// weight quantizer the reference owns (src/emel/kernel/detail.hpp:699-…)
+void ref_quantize_q4_0(const float* x, void* y, int64_t k) {
+  kq::quantize_row_q4_0_ref(x, static_cast<kq::block_q4_0*>(y), k);
+}
+
+// ---- dequantizers (src/emel/kernel/detail.hpp:487-690)
+int ref_dequantize_row(int type, const void* x, float* y, int64_t k) {
+  switch (type) {
+    case EMELB_Q4_0:
+      kq::dequantize_row_q4_0(static_cast<const kq::block_q4_0*>(x), y, k);
+      return 1;
+    case EMELB_Q8_0:
+      kq::dequantize_row_q8_0(static_cast<const kq::block_q8_0*>(x), y, k);
+      return 1;
+    case EMELB_Q4_K:
+      kq::dequantize_row_q4_k(static_cast<const kq::block_q4_k*>(x), y, k);
+      return 1;
+    case EMELB_Q6_K:
+      kq::dequantize_row_q6_k(static_cast<const kq::block_q6_k*>(x), y, k);
+      return 1;
+    default:
+      return 0;
+  }
+}
+
+// ---- guards (src/emel/kernel/detail.hpp:1919-1927, 3843-3872, 3573-3606,
+//      4346-4390): validate_dispatch_request && can_run_*
+int ref_can_run(uint32_t op_code, const emelb_op* op) {
+  if (op_code == EMELB_OP_MUL_MAT) {
+    const auto r = to_op<ev::op_mul_mat>(*op);
+    return kd::validate_dispatch_request(r) && kd::can_run_mul_mat(r);
+  }
+  if (op_code == EMELB_OP_MUL_MAT_ARGMAX) {
+    auto r = to_op<ev::op_mul_mat_argmax>(*op);
+    r.index_out = op->index_out;
+    return kd::validate_dispatch_request(r) && kd::can_run_mul_mat_argmax(r);
+  }
+  if (op_code == EMELB_OP_FLASH_ATTN_EXT) {
+    const auto r = to_op<ev::op_flash_attn_ext>(*op);
+    return kd::validate_dispatch_request(r) && kd::can_run_flash_attn_ext(r);
+  }
+  return 0;
+}
+
+// ---- op_mul_mat, scalar shared route (src/emel/kernel/detail.hpp:3356-3571)
+int ref_mul_mat_scalar(const emelb_op* op) {
+  const auto r = to_op<ev::op_mul_mat>(*op);
+  if (!(kd::validate_dispatch_request(r) && kd::can_run_mul_mat(r))) return 0;
+  return kd::run_mul_mat(r) ? 1 : 0;
+}
+
+// ---- op_mul_mat, AVX2/FMA route
+//      (src/emel/kernel/x86_64/actions.hpp:1186-1326)
+int ref_mul_mat_avx2(const emelb_op* op) {
+  const auto r = to_op<ev::op_mul_mat>(*op);
+  if (!(kd::validate_dispatch_request(r) && kd::can_run_mul_mat(r))) return 0;
+  switch (op->src0.type) {
+    case EMELB_Q4_K:
+      kx::execute_avx2_fma_mul_mat_q4_k_q8_k_unchecked(r);
+      return 1;
+    case EMELB_Q6_K:
+      kx::execute_avx2_fma_mul_mat_q6_k_q8_k_unchecked(r);
+      return 1;
+    case EMELB_Q8_0:
+      kx::execute_avx2_fma_mul_mat_q8_0_q8_0_unchecked(r);
+      return 1;
+    case EMELB_Q4_0:
+      kx::execute_avx2_fma_mul_mat_q4_0_q8_0_unchecked(r);
+      return 1;
+    default:
+      return 0;
+  }
+}
+
+// Row-sliced fork/join of the AVX2 route over std::thread: the reference's
+// execute_parallel (src/emel/kernel/matmul/actions.hpp:48-67, 107-136;
+// src/emel/kernel/matmul/detail.hpp:36-54) needs its un-vendored scheduler,
+// so the slicing arithmetic is restated here and each lane runs the
+// reference's own AVX2 driver on its slice.
+int ref_mul_mat_avx2_lanes(const emelb_op* op, uint32_t lanes) {
+  if (lanes <= 1) return ref_mul_mat_avx2(op);
+  const uint64_t rows = op->src0.ne[1];
+  std::vector<emelb_op> sliced;
+  for (uint32_t lane = 0; lane < lanes; ++lane) {
+    const uint64_t per = rows / lanes, extra = rows % lanes;
+    const uint64_t begin = lane * per + (lane < extra ? lane : extra);
+    const uint64_t count = per + (lane < extra ? 1u : 0u);
+    if (count == 0) continue;
+    emelb_op s = *op;
+    s.src0.data = static_cast<const uint8_t*>(op->src0.data) + begin * op->src0.nb[1];
+    s.src0.ne[1] = count;
+    s.src0.nb[2] = op->src0.nb[1] * count;
+    s.src0.nb[3] = s.src0.nb[2];
+    s.dst.data = static_cast<const uint8_t*>(op->dst.data) + begin * op->dst.nb[1];
+    s.dst.ne[1] = count;
+    s.dst.nb[2] = op->dst.nb[1] * count;
+    s.dst.nb[3] = s.dst.nb[2];
+    sliced.push_back(s);
+  }
+  std::vector<int> ok(sliced.size(), 1);
+  std::vector<std::thread> workers;
+  for (size_t lane = 1; lane < sliced.size(); ++lane) {
+    workers.emplace_back([&, lane] { ok[lane] = ref_mul_mat_avx2(&sliced[lane]); });
+  }
+  ok[0] = ref_mul_mat_avx2(&sliced[0]);
+  for (auto& w : workers) w.join();
+  for (int v : ok) {
+    if (!v) return 0;
+  }
+  return 1;
+}
+
+// ---- op_mul_mat_argmax (src/emel/kernel/detail.hpp:3608-3731)
+int ref_mul_mat_argmax(const emelb_op* op) {
+  auto r = to_op<ev::op_mul_mat_argmax>(*op);
+  r.index_out = op->index_out;
+  if (!kd::validate_dispatch_request(r)) return 0;
+  return kd::run_mul_mat_argmax(r) ? 1 : 0;
+}
+
+// ---- op_flash_attn_ext, scalar (src/emel/kernel/detail.hpp:5238-5300)
+int ref_flash_attn_scalar(const emelb_op* op) {
+  const auto r = to_op<ev::op_flash_attn_ext>(*op);
+  if (!kd::validate_dispatch_request(r)) return 0;
+  static thread_local kd::flash_attn_workspace ws{};
+  return kd::run_flash_attn_ext_active_kv_with_workspace(r, ws) ? 1 : 0;
+}
+
+// ---- op_flash_attn_ext, AVX2/FMA/F16C one-chunk route
+//      (src/emel/kernel/x86_64/actions.hpp:1575-1641)
+int ref_flash_attn_avx2(const emelb_op* op) {
+  const auto r = to_op<ev::op_flash_attn_ext>(*op);
+  if (!kd::validate_dispatch_request(r)) return 0;
+  static thread_local kd::flash_attn_workspace ws{};
+  if (!kd::can_run_flash_attn_ext_with_workspace(r, ws)) return 0;
+  kx::run_flash_attn_ext_f16kv_one_chunk_avx2_fma_f16c_unchecked(r, ws);
+  return 1;
+}
+
+// ---- single-row dots, for SIMD==scalar checks
+//      (tests/kernel/x86_64_tests.cpp:330-354, 536-654, 896-920)
+float ref_row_dot_scalar(int type, const void* lhs, const void* rhs, uint64_t blocks) {
+  switch (type) {
+    case EMELB_Q4_K:
+      return kd::dot_q4_k_q8_k_row_scalar(static_cast<const kq::block_q4_k*>(lhs),
+                                          static_cast<const kq::block_q8_k*>(rhs), blocks);
+    case EMELB_Q6_K:
+      return kd::dot_q6_k_q8_k_row_scalar(static_cast<const kq::block_q6_k*>(lhs),
+                                          static_cast<const kq::block_q8_k*>(rhs), blocks);
+    case EMELB_Q8_0:
+      return kd::dot_q8_0_q8_0_row_scalar(static_cast<const kq::block_q8_0*>(lhs),
+                                          static_cast<const kq::block_q8_0*>(rhs), blocks);
+    case EMELB_Q4_0:
+      return kd::dot_q4_0_q8_0_row_scalar(static_cast<const kq::block_q4_0*>(lhs),
+                                          static_cast<const kq::block_q8_0*>(rhs), blocks);
+    default:
+      return 0.0f;
+  }
+}
+
+float ref_row_dot_avx2(int type, const void* lhs, const void* rhs, uint64_t blocks) {
+  switch (type) {
+    case EMELB_Q4_K:
+      return kx::dot_q4_k_q8_k_row_avx2_fma(static_cast<const kq::block_q4_k*>(lhs),
+                                            static_cast<const kq::block_q8_k*>(rhs), blocks);
+    case EMELB_Q6_K:
+      return kx::dot_q6_k_q8_k_row_avx2_fma(static_cast<const kq::block_q6_k*>(lhs),
+                                            static_cast<const kq::block_q8_k*>(rhs), blocks);
+    case EMELB_Q8_0:
+      return kx::dot_q8_0_q8_0_row_avx2_fma(static_cast<const kq::block_q8_0*>(lhs),
+                                            static_cast<const kq::block_q8_0*>(rhs), blocks);
+    case EMELB_Q4_0:
+      return kx::dot_q4_0_q8_0_row_avx2_fma(static_cast<const kq::block_q4_0*>(lhs),
+                                            static_cast<const kq::block_q8_0*>(rhs), blocks);
+    default:
+      return 0.0f;
+  }
+}
+
+int ref_host_has_avx2_fma_f16c(void) {
+  return kx::detect_avx2() && kx::detect_fma() ? 1 : 0;
+}
+
+}  // extern "C"
