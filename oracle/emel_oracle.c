@@ -465,6 +465,10 @@ int orc_mul_mat_argmax(const o_op* r) {
                 dense(&r->src1) && dense(&r->dst) && r->src0.nb[0] == 1 && r->src0.nb[1] == orc_row_bytes(t, k) &&
                 r->src0.nb[2] == r->src0.nb[1] * m && r->src0.nb[3] == r->src0.nb[2];
   if (k == 0 || m == 0 || n != 1 || !r->index_out || !shape || !q) return 0;
+  /* run_mul_mat_argmax has branches for f32, Q5_0, Q8_0 and the K-quants only
+   * (src/emel/kernel/detail.hpp:3621-3731): a Q4_0 request falls through to
+   * `return false` although the guard accepts it */
+  if (t == T_Q4_0) return 0;
   const float* b = (const float*)r->src1.data;
   const uint8_t* a = (const uint8_t*)r->src0.data;
   const uint64_t rb = r->src0.nb[1];

@@ -261,7 +261,11 @@ def test_mul_mat_port_equals_ref(port, ref, t, k, m, n):
 
 def test_mul_mat_argmax_port_equals_ref(port, ref):
     k, m = 1024, 257
-    for t in (ob.Q4_K, ob.Q6_K, ob.Q8_0, ob.Q4_0):
+    w4 = synth.encoded_weights(port, ob.Q4_0, 61, m, k)
+    for lib in (port, ref):   # no Q4_0 branch in run_mul_mat_argmax (src/emel/kernel/detail.hpp:3621-3731)
+        assert not lib.mul_mat_argmax(ob.mul_mat_op(w4, ob.Q4_0, k, m, synth.activations_f32(62, k), 1,
+                                                    np.zeros(1, np.float32), np.zeros(1, np.int32)))
+    for t in (ob.Q4_K, ob.Q6_K, ob.Q8_0):
         w = synth.encoded_weights(port, t, 61, m, k)
         w = w.reshape(m, -1)
         w[200] = w[7]                                  # duplicate row: lowest index must win a tie
