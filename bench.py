@@ -1,0 +1,336 @@
+"""Benchmark of the quantized matrix-product hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One JSON line on stdout (rank 0).  Workloads (synthetic data, seeded):
+  gemv_q4_k   configuration 1: Q4_K 4096x4096 mat-vec, x ~ N(0,1) quantized to Q8_K.
+              One step = one mat-vec over each of COPIES distinct weight copies
+              (COPIES x 9.4 MB > the 126 MB L2, so every step streams from HBM).
+  gemv_q8_0   configuration 2: Q8_0 14336x4096, token batch --ncols in {1, 8, 64}.
+`value` is measured with operands resident in HBM; `e2e` through the same C-ABI
+calls with host (pinned) activation and result buffers, copies inside the timed
+region.  `--impl reference` times the reference's own AVX2 kernels
+(oracle/_ref, compiled from the reference's headers) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC_GEMV = "Q4_K GEMV HBM GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def ncu_traffic(kernel_key):
+    """DRAM bytes per launch from the committed ncu summary, when one exists."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f).get(kernel_key)
+    return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl" if os.environ.get("EMELB_BENCH_BACKEND", "nccl") == "nccl" else "gloo")
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def max_over_ranks(x, world, device):
+    if world == 1:
+        return x
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ------------------------------------------------------------------ GEMV workloads
+def gemv_spec(args):
+    import emel_cpp_b200 as eb
+    if args.workload == "gemv_q4_k":
+        t, k, m, n = eb.Q4_K, 4096, 4096, 1
+        name = "cfg1: Q4_K 4096x4096 mat-vec, x~N(0,1) -> Q8_K"
+    else:
+        t, k, m, n = eb.Q8_0, 4096, 14336, args.ncols
+        name = f"cfg2: Q8_0 14336x4096, token batch {n}"
+    wbytes = m * eb.row_bytes(t, k)
+    copies = max(4, int(np.ceil(640e6 / wbytes)))     # > 5x the 126 MB L2
+    return dict(type=t, k=k, m=m, n=n, name=name, wbytes=wbytes, copies=copies,
+                alg_bytes=wbytes + 4 * k * n + 4 * m * n)
+
+
+def run_gemv(args):
+    import torch
+    import emel_cpp_b200 as eb
+
+    rank, world, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    sp = gemv_spec(args)
+    t, k, m, n, copies = sp["type"], sp["k"], sp["m"], sp["n"], sp["copies"]
+    be = eb.Backend(local)
+    stream = torch.cuda.ExternalStream(be.stream(), device=dev)
+
+    # weights: `copies` distinct matrices, N(0, 0.02) encoded on the device (each rank its own)
+    wdev = be.alloc(copies * sp["wbytes"])
+    for c in range(copies):
+        assert be.synth_fill(wdev + c * sp["wbytes"], t, m * k, 1000 + rank * 100 + c, 0.02, 0)
+    xdev, ydev = be.alloc(4 * k * n), be.alloc(4 * m * n)
+    assert be.synth_fill(xdev, eb.F32, k * n, 7 + rank, 1.0, 0) and be.sync()
+    x_host = torch.empty(k * n, dtype=torch.float32).pin_memory()
+    y_host = torch.empty(m * n, dtype=torch.float32).pin_memory()
+    assert be.to_host(x_host.numpy(), xdev)
+
+    ops_dev = [eb.mul_mat_op(wdev + c * sp["wbytes"], t, k, m, xdev, n, ydev) for c in range(copies)]
+    ops_host = [eb.mul_mat_op(wdev + c * sp["wbytes"], t, k, m, x_host, n, y_host) for c in range(copies)]
+    src1_view = eb.dense_view(xdev, eb.F32, [n, k])
+
+    def step_dev():
+        for op in ops_dev:
+            assert be.mul_mat(op)
+
+    def step_host():
+        for op in ops_host:
+            assert be.mul_mat(op)
+
+    def step_kernel_only():
+        for op in ops_dev:
+            assert be.mul_mat_prepared(op)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        be.sync()
+        barrier(world)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0 = be.diagnostics()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        be.sync()
+        torch.cuda.synchronize()
+        barrier(world)
+        d1 = be.diagnostics()
+        ms = max_over_ranks(e0.elapsed_time(e1), world, dev)
+        return ms, {k_: d1[k_] - d0[k_] for k_ in d1}
+
+    with ClockSampler(local) as clk:
+        ms, dd = timed(step_dev, args.steps, args.warmup)
+        assert be.prepare_rhs(src1_view, t)
+        ms_k, dk = timed(step_kernel_only, args.steps, args.warmup)
+        ms_e, de = timed(step_host, args.steps, args.warmup)
+    clocks = clk.summary()
+
+    total_bytes = sp["alg_bytes"] * copies * args.steps * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+    e2e = total_bytes / (ms_e * 1e-3) / 1e9
+    launches = copies * args.steps
+    kernel_gbs = sp["alg_bytes"] / (ms_k * 1e-3 / launches) / 1e9
+    peaks, peak_kind = measured_peaks()
+    kname = {eb.Q4_K: "gemv_stream_q4_k", eb.Q8_0: "gemv_stream_q8_0"}[t] + f"_n{n}"
+    line = {
+        "metric": METRIC_GEMV if args.workload == "gemv_q4_k" else "Q8_0 GEMV HBM GB/s",
+        "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 6), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 dot (dp4a) + f32 scales", "data": "synthetic",
+        "config": {"workload": sp["name"], "rows": m, "cols": k, "tokens": n, "weight_copies_per_step": copies,
+                   "l2_policy": f"inputs larger than L2: {copies} distinct weight copies = {copies * sp['wbytes'] / 1e6:.0f} MB per step",
+                   "parallelism": f"{world} independent row-shard replicas, no collective"},
+        "pct_of_8tbs_nominal": round(100 * kernel_gbs / NOMINAL_HBM_GBS, 2),
+        "e2e": {"value": round(e2e, 2), "unit": "GB/s", "h2d_bytes_per_step": de["h2d_bytes"] // args.steps,
+                "d2h_bytes_per_step": de["d2h_bytes"] // args.steps},
+        "gpu_launches": int(dd["kernel_launches"]),
+        "roofline": {"bound": "hbm", "kernel": kname, "achieved": round(kernel_gbs, 2), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(kernel_gbs / peaks["hbm_gbs"], 4), "peak_source": f"of {peak_kind}",
+                     "us_per_launch": round(ms_k * 1e3 / launches, 3), "algorithmic_bytes_per_launch": sp["alg_bytes"],
+                     "traffic": ncu_traffic(kname)},
+        "clocks": clocks,
+    }
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline_gemv(be, sp, wdev, x_host.numpy().copy(), budget_s=args.cpu_budget)
+        print(json.dumps(line), flush=True)
+    be.close()
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def cpu_baseline_gemv(be, sp, wdev, x, budget_s=8.0, lanes=None):
+    """The reference's AVX2 op_mul_mat (oracle/_ref; the C port where that was never built) on the
+    same weight bytes and activations, timed on this host for a bounded sample."""
+    from oracle import bindings as ob
+    lib = ob.ref()
+    kind = "reference" if lib is not None else "port"
+    lib = lib or ob.port()
+    t, k, m, n = sp["type"], sp["k"], sp["m"], sp["n"]
+    w = np.zeros(sp["wbytes"], np.uint8)
+    assert be.to_host(w, wdev)
+    y = np.zeros((m, n), np.float32)
+    op = ob.mul_mat_op(w, t, k, m, x, n, y)
+    cores = lanes or min(8, os.cpu_count() or 1)
+    kw = {"route": "avx2", "lanes": cores} if kind == "reference" else {}
+    if kind == "port":
+        cores = 1
+    assert lib.mul_mat(op, **kw)            # warm-up
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        assert lib.mul_mat(op, **kw)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or reps >= 2000:
+            break
+    gbs = sp["alg_bytes"] * reps / dt / 1e9
+    return {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": f"{reps} x {sp['name']} in {dt:.1f} s, AVX2/FMA route, row-sliced over {cores} threads",
+            "us_per_op": round(dt / reps * 1e6, 1)}
+
+
+def run_reference_gemv(args):
+    """--impl reference: the reference's own CPU kernels for the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import emel_cpp_b200 as eb
+    from oracle import bindings as ob
+    sp = gemv_spec(args)
+    t, k, m, n = sp["type"], sp["k"], sp["m"], sp["n"]
+    lib = ob.ref()
+    kind = "reference" if lib is not None else "port"
+    lib = lib or ob.port()
+    rng = np.random.Generator(np.random.PCG64(1000))
+    # weights: random block bytes with sane scales (the CPU arm's time does not depend on the values)
+    w = rng.integers(0, 256, size=sp["wbytes"], dtype=np.uint8)
+    bb = eb.BLOCK_BYTES[t]
+    blocks = w.reshape(-1, bb)
+    for off in ({eb.Q4_K: (0, 2), eb.Q6_K: (208,), eb.Q8_0: (0,), eb.Q4_0: (0,)}[t]):
+        blocks[:, off] = rng.integers(0, 256, size=blocks.shape[0])
+        blocks[:, off + 1] = rng.integers(0x18, 0x30, size=blocks.shape[0])
+    x = rng.standard_normal((k, n), dtype=np.float32)
+    y = np.zeros((m, n), np.float32)
+    op = ob.mul_mat_op(w, t, k, m, x, n, y)
+    cores = os.cpu_count() or 1
+    lanes = min(cores, 64)
+    kw = {"route": "avx2", "lanes": lanes} if kind == "reference" else {}
+    per_step = max(1, min(sp["copies"], 8))           # bounded sample of the step's mat-vecs
+    for _ in range(args.warmup):
+        assert lib.mul_mat(op, **kw)
+    t0 = time.perf_counter()
+    for _ in range(args.steps * per_step):
+        assert lib.mul_mat(op, **kw)
+    dt = time.perf_counter() - t0
+    gbs = sp["alg_bytes"] * args.steps * per_step / dt / 1e9
+    line = {"impl": "reference", "metric": METRIC_GEMV if args.workload == "gemv_q4_k" else "Q8_0 GEMV HBM GB/s",
+            "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dt / args.steps * 1e3 * sp["copies"] / per_step, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot (AVX2 maddubs) + f32 scales", "data": "synthetic",
+            "config": {"workload": sp["name"], "rows": m, "cols": k, "tokens": n},
+            "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": lanes if kind == "reference" else 1, "kind": kind,
+                             "sample": f"{per_step} of the step's {sp['copies']} mat-vecs per step, scaled"},
+            "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemv_q4_k", choices=["gemv_q4_k", "gemv_q8_0"])
+    ap.add_argument("--ncols", type=int, default=1)
+    ap.add_argument("--cpu-budget", type=float, default=8.0)
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        run_reference_gemv(args)
+    else:
+        run_gemv(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,302 @@
+"""emel.cpp_b200 — Python host side over the C-ABI library (libemelb.so).
+
+The library is the product: hand-written sm_100a kernels behind the entry
+points of include/emelb.h.  This module only loads it and mirrors, for tests
+and the benchmark, the calling convention of the reference's kernel actor:
+`process_event(op) -> bool` with the reason kept in `last_error`
+(src/emel/kernel/any.hpp:76-80, src/emel/kernel/x86_64/sm.hpp:1198-1211,
+1327-1331).  There is no CPU fallback: without the built library every entry
+point raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libemelb.so")
+
+# dtype codes (src/emel/kernel/events.hpp:78-123)
+F32, F16, Q4_0, Q8_0, Q4_K, Q6_K, Q8_K, I32 = 0, 1, 2, 8, 12, 14, 15, 26
+BLOCK_ELEMS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, Q8_K: 256}
+BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, Q8_K: 292}
+# error bitmask (src/emel/kernel/errors.hpp:7-13)
+OK, INVALID_REQUEST, UNSUPPORTED_OP, INTERNAL_ERROR, UNTRACKED = 0, 1, 2, 4, 8
+OP_MUL_MAT, OP_MUL_MAT_ARGMAX, OP_FLASH_ATTN_EXT = 1, 2, 3
+LIFECYCLE = {0: "unbound", 1: "resident", 2: "evicted", 3: "internal_error", 4: "mmap_resident"}
+
+
+class View(C.Structure):
+    """tensor_view (src/emel/kernel/events.hpp:125-137)."""
+    _fields_ = [("data", C.c_void_p), ("type", C.c_uint8), ("ne", C.c_uint64 * 4), ("nb", C.c_uint64 * 4)]
+
+
+class Op(C.Structure):
+    """Generic op fields + index_out (src/emel/kernel/events.hpp:178-189, 220-223)."""
+    _fields_ = [("src0", View), ("src1", View), ("src2", View), ("dst", View),
+                ("op_params", C.c_uint8 * 64), ("op_params_size", C.c_uint32),
+                ("index_out", C.POINTER(C.c_int32))]
+
+
+class TensorState(C.Structure):
+    _fields_ = [("lifecycle_state", C.c_uint8), ("buffer", C.c_void_p), ("buffer_bytes", C.c_uint64),
+                ("host", C.c_void_p), ("tensor_type", C.c_int32)]
+
+
+class Diag(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "optimized_flash_dispatch_calls", "shared_flash_dispatch_calls", "optimized_q4_dispatch_calls",
+        "optimized_q4_vector_dispatch_calls", "optimized_q6_dispatch_calls", "optimized_q6_vector_dispatch_calls",
+        "optimized_q6_vector_argmax_dispatch_calls", "optimized_q8_0_dispatch_calls", "optimized_q4_0_dispatch_calls",
+        "rejected_dispatch_calls", "kernel_launches", "h2d_bytes", "d2h_bytes")]
+
+    def as_dict(self):
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
+class BackendError(RuntimeError):
+    pass
+
+
+_lib = None
+
+# every symbol include/emelb.h declares: (name, argtypes)
+_P = C.c_void_p
+_SIGNATURES = {
+    "emelb_create": [C.c_int, C.POINTER(_P)],
+    "emelb_destroy": [_P],
+    "emelb_sync": [_P],
+    "emelb_get_stream": [_P, C.POINTER(_P)],
+    "emelb_diagnostics": [_P, C.POINTER(Diag)],
+    "emelb_set_attention_mode": [_P, C.c_int],
+    "emelb_residency_upload": [_P, C.c_int32, _P, C.c_uint64, C.c_int32, C.POINTER(_P)],
+    "emelb_residency_evict": [_P, C.c_int32],
+    "emelb_residency_state": [_P, C.c_int32, C.POINTER(TensorState)],
+    "emelb_device_alloc": [_P, C.c_uint64, C.POINTER(_P)],
+    "emelb_device_free": [_P, _P],
+    "emelb_copy_to_device": [_P, _P, _P, C.c_uint64],
+    "emelb_copy_to_host": [_P, _P, _P, C.c_uint64],
+    "emelb_can_run": [_P, C.c_uint32, C.POINTER(Op)],
+    "emelb_mul_mat": [_P, C.POINTER(Op)],
+    "emelb_mul_mat_argmax": [_P, C.POINTER(Op)],
+    "emelb_prepare_rhs": [_P, C.POINTER(View), C.c_int32],
+    "emelb_mul_mat_prepared": [_P, C.POINTER(Op)],
+    "emelb_flash_attn_ext": [_P, C.POINTER(Op)],
+    "emelb_quantize": [_P, C.POINTER(View), C.POINTER(View)],
+    "emelb_dequantize": [_P, C.POINTER(View), C.POINTER(View)],
+    "emelb_synth_fill": [_P, _P, C.c_int32, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64],
+    "emelb_row_slice": [C.POINTER(Op), C.c_uint32, C.c_uint32, C.POINTER(Op), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
+}
+
+
+def declared_symbols():
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    """The loaded C-ABI library; raises when it has not been built (no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise BackendError(f"{LIB_PATH} is missing: build it with `python emel.cpp_b200/build.py` "
+                               "(this backend has no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        for name, args in _SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.restype = C.c_uint32
+            fn.argtypes = args
+        from . import llama as _llama  # noqa: F401  (registers the decoder's signatures when present)
+    return _lib
+
+
+def row_bytes(t: int, k: int) -> int:
+    return k // BLOCK_ELEMS[t] * BLOCK_BYTES[t]
+
+
+def ptr(a) -> int:
+    """Address of a numpy array, a torch tensor, or a raw integer address."""
+    if hasattr(a, "ctypes"):
+        return a.ctypes.data
+    if hasattr(a, "data_ptr"):
+        return a.data_ptr()
+    return int(a) if a is not None else 0
+
+
+def dense_view(data, t: int, ne) -> View:
+    ne = list(ne) + [1] * (4 - len(ne))
+    v = View()
+    v.data = ptr(data)
+    v.type = t
+    stride = {F32: 4, F16: 2, I32: 4}[t]
+    for i in range(4):
+        v.ne[i] = ne[i]
+        v.nb[i] = stride
+        stride *= ne[i]
+    return v
+
+
+def quant_view(data, t: int, k: int, m: int) -> View:
+    """{k, m} rows of native blocks, the layout the reference's guards require."""
+    v = View()
+    v.data = ptr(data)
+    v.type = t
+    rb = row_bytes(t, k)
+    v.ne[0], v.ne[1], v.ne[2], v.ne[3] = k, m, 1, 1
+    v.nb[0], v.nb[1], v.nb[2], v.nb[3] = 1, rb, rb * m, rb * m
+    return v
+
+
+def mul_mat_op(w, t, k, m, x, n, y, index_out=None, src1_type=F32) -> Op:
+    op = Op()
+    op.src0 = quant_view(w, t, k, m)
+    if src1_type == F32:
+        op.src1 = dense_view(x, F32, [n, k])
+    else:  # pre-quantized vector form
+        rb = row_bytes(src1_type, k)
+        v = View()
+        v.data, v.type = ptr(x), src1_type
+        v.ne[0], v.ne[1], v.ne[2], v.ne[3] = 1, k, 1, 1
+        v.nb[0], v.nb[1], v.nb[2], v.nb[3] = 1, rb, rb, rb
+        op.src1 = v
+    op.dst = dense_view(y, F32, [n, m] if index_out is None else [1, 1])
+    if index_out is not None:
+        op.index_out = C.cast(ptr(index_out), C.POINTER(C.c_int32))
+    return op
+
+
+def flash_op(q, kc, vc, dst, head_dim, heads, kv_heads, tokens, capacity, scale=None, masked_total=None) -> Op:
+    """Request of make_flash_attn_request (src/emel/text/generator/detail.hpp:3232-3279)."""
+    import struct
+    op = Op()
+    op.src0 = dense_view(q, F32, [head_dim, 1, heads])
+    for name, buf in (("src1", kc), ("src2", vc)):
+        v = View()
+        v.data, v.type = ptr(buf), F16
+        v.ne[0], v.ne[1], v.ne[2], v.ne[3] = head_dim, tokens, kv_heads, 1
+        v.nb[0], v.nb[1] = 2, 2 * head_dim
+        v.nb[2] = 2 * capacity * head_dim
+        v.nb[3] = v.nb[2] * kv_heads
+        setattr(op, name, v)
+    op.dst = dense_view(dst, F32, [head_dim, 1, heads])
+    if scale is not None:
+        raw = struct.pack("<f", scale) + (struct.pack("<I", masked_total) if masked_total is not None else b"")
+        for i, b in enumerate(raw):
+            op.op_params[i] = b
+        op.op_params_size = len(raw)
+    return op
+
+
+class Backend:
+    """One backend context = one kernel actor lane."""
+
+    def __init__(self, device: int = 0):
+        self._h = _P()
+        err = lib().emelb_create(device, C.byref(self._h))
+        if err != OK:
+            raise BackendError(f"emelb_create failed with error mask {err}")
+        self.device = device
+        self.last_error = OK
+
+    # -- lifetime
+    def close(self):
+        if self._h:
+            lib().emelb_destroy(self._h)
+            self._h = _P()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def _ret(self, err: int) -> bool:
+        self.last_error = err
+        return err == OK
+
+    def sync(self) -> bool:
+        return self._ret(lib().emelb_sync(self._h))
+
+    def stream(self) -> int:
+        s = _P()
+        lib().emelb_get_stream(self._h, C.byref(s))
+        return s.value or 0
+
+    def diagnostics(self) -> dict:
+        d = Diag()
+        lib().emelb_diagnostics(self._h, C.byref(d))
+        return d.as_dict()
+
+    def set_attention_mode(self, mode: int) -> bool:
+        return self._ret(lib().emelb_set_attention_mode(self._h, mode))
+
+    # -- residency
+    def upload(self, tensor_id: int, host, nbytes: int | None = None, tensor_type: int = 0) -> int:
+        nbytes = int(host.nbytes) if nbytes is None else nbytes
+        dev = _P()
+        if not self._ret(lib().emelb_residency_upload(self._h, tensor_id, ptr(host), nbytes, tensor_type, C.byref(dev))):
+            raise BackendError(f"residency upload failed with error mask {self.last_error}")
+        return dev.value
+
+    def evict(self, tensor_id: int) -> bool:
+        return self._ret(lib().emelb_residency_evict(self._h, tensor_id))
+
+    def state(self, tensor_id: int) -> TensorState:
+        s = TensorState()
+        lib().emelb_residency_state(self._h, tensor_id, C.byref(s))
+        return s
+
+    def alloc(self, nbytes: int) -> int:
+        dev = _P()
+        if not self._ret(lib().emelb_device_alloc(self._h, nbytes, C.byref(dev))):
+            raise BackendError(f"device alloc of {nbytes} bytes failed with error mask {self.last_error}")
+        return dev.value
+
+    def free(self, dev: int) -> bool:
+        return self._ret(lib().emelb_device_free(self._h, dev))
+
+    def to_device(self, dev: int, host, nbytes: int | None = None) -> bool:
+        return self._ret(lib().emelb_copy_to_device(self._h, dev, ptr(host), int(host.nbytes) if nbytes is None else nbytes))
+
+    def to_host(self, host, dev: int, nbytes: int | None = None) -> bool:
+        return self._ret(lib().emelb_copy_to_host(self._h, ptr(host), dev, int(host.nbytes) if nbytes is None else nbytes))
+
+    # -- ops: `bool accepted`, reason in last_error
+    def can_run(self, code: int, op: Op) -> bool:
+        return lib().emelb_can_run(self._h, code, C.byref(op)) == OK
+
+    def mul_mat(self, op: Op) -> bool:
+        return self._ret(lib().emelb_mul_mat(self._h, C.byref(op)))
+
+    def mul_mat_argmax(self, op: Op) -> bool:
+        return self._ret(lib().emelb_mul_mat_argmax(self._h, C.byref(op)))
+
+    def prepare_rhs(self, src1: View, weight_type: int) -> bool:
+        return self._ret(lib().emelb_prepare_rhs(self._h, C.byref(src1), weight_type))
+
+    def mul_mat_prepared(self, op: Op) -> bool:
+        return self._ret(lib().emelb_mul_mat_prepared(self._h, C.byref(op)))
+
+    def flash_attn_ext(self, op: Op) -> bool:
+        return self._ret(lib().emelb_flash_attn_ext(self._h, C.byref(op)))
+
+    def quantize(self, src: View, dst: View) -> bool:
+        return self._ret(lib().emelb_quantize(self._h, C.byref(src), C.byref(dst)))
+
+    def dequantize(self, src: View, dst: View) -> bool:
+        return self._ret(lib().emelb_dequantize(self._h, C.byref(src), C.byref(dst)))
+
+    def synth_fill(self, dev: int, t: int, elems: int, seed: int, sigma: float, offset: int = 0) -> bool:
+        """N(0, sigma) synthetic data, f32 or block-encoded on the device."""
+        return self._ret(lib().emelb_synth_fill(self._h, dev, t, elems, seed, sigma, offset))
+
+
+def row_slice(op: Op, lane: int, lanes: int):
+    out, b, c = Op(), C.c_uint64(), C.c_uint64()
+    err = lib().emelb_row_slice(C.byref(op), lane, lanes, C.byref(out), C.byref(b), C.byref(c))
+    if err != OK:
+        raise BackendError(f"row_slice rejected: {err}")
+    return out, b.value, c.value

@@ -1,0 +1,357 @@
+// Decode attention over the f16 KV cache (one query token per head).
+// Replaces run_flash_attn_ext_active_kv_with_workspace_unchecked
+// (src/emel/kernel/detail.hpp:5238-5291) and the AVX2 one-chunk route
+// (src/emel/kernel/x86_64/actions.hpp:1575-1641).
+//
+// Two kernels families:
+//  * split-KV (default): the KV sequence of each KV head is cut into `splits`
+//    ranges, one CTA per (range, kv head, group of <=4 query heads sharing that
+//    KV head, so K/V are read once per group).  Inside a CTA: scores for the
+//    range (8 lanes per token row, 128-bit loads), exact range maximum,
+//    probabilities, then the V accumulation with 128-bit loads; f32 throughout.
+//    A small second kernel merges the ranges.  HBM-bound: K and V are each read
+//    once.
+//  * reference order: scores as f64 sums of exact f16 products, then the
+//    reference's sequential online softmax with an f16 accumulator rounded after
+//    every token — the same roundings in the same order as the scalar route, for
+//    parity runs and for shapes the split kernel does not take.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace emelb {
+
+namespace {
+
+constexpr int LMAX = 1024;  // tokens per split the shared score buffer holds
+
+__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+template <int NREP>
+__device__ __forceinline__ void block_reduce(float (&v)[NREP], float* scratch /*[4][NREP]*/, bool is_max) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int r = 0; r < NREP; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float t = __shfl_xor_sync(0xffffffffu, v[r], o);
+      v[r] = is_max ? fmaxf(v[r], t) : v[r] + t;
+    }
+    if (lane == 0) scratch[warp * NREP + r] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < NREP; ++r) {
+    float t = scratch[r];
+    for (int w = 1; w < 4; ++w) t = is_max ? fmaxf(t, scratch[w * NREP + r]) : t + scratch[w * NREP + r];
+    v[r] = t;
+  }
+  __syncthreads();
+}
+
+template <int D, int NREP>
+__global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
+  constexpr int DPL = D / 8;   // dims per lane while scoring (8 lanes per token row)
+  constexpr int TPR = D / 8;   // threads per token row while accumulating V (8 halves each)
+  constexpr int SLOTS = 128 / TPR;
+  static_assert(SLOTS * NREP * D <= NREP * LMAX, "V reduction reuses the score buffer");
+  __shared__ __align__(16) float s_p[NREP * LMAX];
+  __shared__ float s_red[4 * NREP];
+
+  const int tid = threadIdx.x;
+  const int split = blockIdx.x, kh = blockIdx.y;
+  const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
+  const int n_rep = a.heads / a.kv_heads;
+  const int head0 = kh * n_rep + blockIdx.z * NREP;
+  int L = (T + a.splits - 1) / a.splits;
+  L = L > LMAX ? LMAX : L;  // host sizes `splits` so this never clips
+  const int t0 = split * L;
+  const int t1 = min(T, t0 + L);
+  const int n = t1 > t0 ? t1 - t0 : 0;
+
+  if (n == 0) {
+    for (int idx = tid; idx < NREP * D; idx += 128)
+      a.part_acc[((size_t)(head0 + idx / D) * a.splits + split) * D + idx % D] = 0.0f;
+    if (tid < NREP) {
+      float* ml = a.part_ml + ((size_t)(head0 + tid) * a.splits + split) * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.0f;
+    }
+    return;
+  }
+
+  // ---- scores: q is rounded to f16 first, as the reference does (detail.hpp:5255)
+  const int l8 = tid & 7, slot = tid >> 3;
+  float q[NREP][DPL];
+#pragma unroll
+  for (int r = 0; r < NREP; ++r)
+#pragma unroll
+    for (int i = 0; i < DPL; ++i)
+      q[r][i] = __half2float(__float2half_rn(a.q[(size_t)(head0 + r) * D + l8 * DPL + i]));
+
+  float mx[NREP];
+#pragma unroll
+  for (int r = 0; r < NREP; ++r) mx[r] = -INFINITY;
+  const char* kbase = reinterpret_cast<const char*>(a.k) + (size_t)kh * a.k_nb2 + (size_t)l8 * DPL * 2;
+  constexpr int U = 4;
+  for (int t = slot; t < n; t += 16 * U) {
+    uint4 kv[U][DPL / 8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int tt = min(t + 16 * u, n - 1);
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)(t0 + tt) * a.k_nb1);
+#pragma unroll
+      for (int c = 0; c < DPL / 8; ++c) kv[u][c] = __ldg(kp + c);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float s[NREP];
+#pragma unroll
+      for (int r = 0; r < NREP; ++r) s[r] = 0.0f;
+#pragma unroll
+      for (int c = 0; c < DPL / 8; ++c) {
+        float kf[8];
+        unpack8(kv[u][c], kf);
+#pragma unroll
+        for (int r = 0; r < NREP; ++r)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s[r] = fmaf(q[r][8 * c + i], kf[i], s[r]);
+      }
+      const int tt = t + 16 * u;
+#pragma unroll
+      for (int r = 0; r < NREP; ++r) {
+        float v = s[r];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v *= a.scale;
+        if (tt < n) {
+          mx[r] = fmaxf(mx[r], v);
+          if (l8 == 0) s_p[r * LMAX + tt] = v;
+        }
+      }
+    }
+  }
+  block_reduce<NREP>(mx, s_red, true);  // also orders the score writes before the reads below
+
+  // ---- probabilities relative to the range maximum
+  float lsum[NREP];
+#pragma unroll
+  for (int r = 0; r < NREP; ++r) lsum[r] = 0.0f;
+  for (int idx = tid; idx < n; idx += 128) {
+#pragma unroll
+    for (int r = 0; r < NREP; ++r) {
+      const float pr = expf(s_p[r * LMAX + idx] - mx[r]);
+      s_p[r * LMAX + idx] = pr;
+      lsum[r] += pr;
+    }
+  }
+  block_reduce<NREP>(lsum, s_red, false);
+
+  // ---- V accumulation: TPR threads cover one token row with 128-bit loads
+  const int c = tid % TPR, vs = tid / TPR;
+  float acc[NREP][8];
+#pragma unroll
+  for (int r = 0; r < NREP; ++r)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
+  const char* vbase = reinterpret_cast<const char*>(a.v) + (size_t)kh * a.v_nb2 + (size_t)c * 16;
+  for (int t = vs; t < n; t += SLOTS * U) {
+    uint4 vv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int tt = min(t + SLOTS * u, n - 1);
+      vv[u] = __ldg(reinterpret_cast<const uint4*>(vbase + (size_t)(t0 + tt) * a.v_nb1));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int tt = t + SLOTS * u;
+      if (tt < n) {
+        float vf[8];
+        unpack8(vv[u], vf);
+#pragma unroll
+        for (int r = 0; r < NREP; ++r) {
+          const float pr = s_p[r * LMAX + tt];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[r][i] = fmaf(pr, vf[i], acc[r][i]);
+        }
+      }
+    }
+  }
+  __syncthreads();  // all probability reads done; the buffer becomes the slot reduction area
+#pragma unroll
+  for (int r = 0; r < NREP; ++r)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_p[(vs * NREP + r) * D + c * 8 + i] = acc[r][i];
+  __syncthreads();
+  for (int idx = tid; idx < NREP * D; idx += 128) {
+    const int r = idx / D, d = idx % D;
+    float sum = 0.0f;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) sum += s_p[(s * NREP + r) * D + d];
+    a.part_acc[((size_t)(head0 + r) * a.splits + split) * D + d] = sum;
+  }
+  if (tid < NREP) {
+    float* ml = a.part_ml + ((size_t)(head0 + tid) * a.splits + split) * 2;
+    ml[0] = mx[tid];
+    ml[1] = lsum[tid];
+  }
+}
+
+// merge the ranges: out = sum_s e^{m_s-M} acc_s / sum_s e^{m_s-M} l_s
+__global__ void flash_merge_kernel(const FlashArgs a) {
+  const int h = blockIdx.x, D = a.head_dim;
+  const float* ml = a.part_ml + (size_t)h * a.splits * 2;
+  float M = -INFINITY;
+  for (int s = 0; s < a.splits; ++s) M = fmaxf(M, ml[2 * s]);
+  float den = 0.0f;
+  for (int s = 0; s < a.splits; ++s) den += (ml[2 * s] == -INFINITY ? 0.0f : expf(ml[2 * s] - M)) * ml[2 * s + 1];
+  const float inv = den == 0.0f ? 0.0f : 1.0f / den;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.0f;
+    for (int s = 0; s < a.splits; ++s) {
+      const float w = ml[2 * s] == -INFINITY ? 0.0f : expf(ml[2 * s] - M);
+      o = fmaf(w, a.part_acc[((size_t)h * a.splits + s) * D + d], o);
+    }
+    a.dst[(size_t)h * D + d] = o * inv;
+  }
+}
+
+// ---------------------------------------------------------------- reference order
+// scores[h][t] = (float)(sum_i (double)q16[i] * (double)k[t][i]) * scale
+// (dot_product_f16_f16_scores, src/emel/kernel/detail.hpp:2203-2208); one warp per
+// (token, head), f64 partial sums combined across lanes.
+__global__ void __launch_bounds__(128) flash_ref_scores_kernel(const FlashArgs a, float* scores, int t_stride) {
+  const int lane = threadIdx.x & 31;
+  const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
+  const int h = blockIdx.y;
+  const int kh = h / (a.heads / a.kv_heads);
+  for (int t = blockIdx.x * 4 + (threadIdx.x >> 5); t < T; t += gridDim.x * 4) {
+    const __half* kr = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(a.k) + (size_t)t * a.k_nb1 + (size_t)kh * a.k_nb2);
+    double s = 0.0;
+    for (int i = lane; i < a.head_dim; i += 32) {
+      const float qv = __half2float(__float2half_rn(a.q[(size_t)h * a.head_dim + i]));
+      s += (double)qv * (double)__half2float(kr[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) scores[(size_t)h * t_stride + t] = __fmul_rn((float)s, a.scale);
+  }
+}
+
+__device__ __forceinline__ float round16(float v) { return __half2float(__float2half_rn(v)); }
+// std::exp(float) of the host libm is correctly rounded in all but vanishingly
+// rare cases; the f64 exp rounded once to f32 reproduces that
+__device__ __forceinline__ float exp_cr(float x) { return (float)exp((double)x); }
+
+// One CTA per head; thread d owns accumulator dims d, d+blockDim, ...; every
+// thread replays the scalar recurrences (max, scales, sum) so no barrier sits
+// inside the token loop.  Mirrors detail.hpp:5261-5290 with
+// scale_f16_buffer_scalar (:4312-4320) and axpy_f16_buffer_scalar (:4322-4332).
+template <int DPT>
+__global__ void flash_ref_sequential_kernel(const FlashArgs a, const float* scores, int t_stride) {
+  __shared__ float s_sc[256];
+  const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
+  const int h = blockIdx.x, D = a.head_dim;
+  const int kh = h / (a.heads / a.kv_heads);
+  float acc[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) acc[i] = 0.0f;
+  float sum = 0.0f, mx = -INFINITY;
+  const char* vbase = reinterpret_cast<const char*>(a.v) + (size_t)kh * a.v_nb2;
+  for (int tb = 0; tb < T; tb += 256) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256 && tb + i < T; i += blockDim.x) s_sc[i] = scores[(size_t)h * t_stride + tb + i];
+    __syncthreads();
+    const int tn = min(256, T - tb);
+    for (int tt = 0; tt < tn; ++tt) {
+      const float score = s_sc[tt];
+      const float old = mx;
+      float ms = 1.0f, vsc = 1.0f;
+      const bool bump = score > mx;
+      if (bump) { mx = score; ms = exp_cr(old - mx); } else { vsc = exp_cr(score - mx); }
+      const float rs = round16(ms), ra = round16(vsc);
+      const __half* vr = reinterpret_cast<const __half*>(vbase + (size_t)(tb + tt) * a.v_nb1);
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+        if (d < D) {
+          float x = acc[i];
+          if (bump) x = round16(__fmul_rn(x, rs));
+          acc[i] = round16(__fadd_rn(x, __fmul_rn(__half2float(vr[d]), ra)));
+        }
+      }
+      sum = __fadd_rn(__fmul_rn(sum, ms), vsc);
+    }
+  }
+  const float inv = sum == 0.0f ? 0.0f : __fdiv_rn(1.0f, sum);
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    if (d < D) a.dst[(size_t)h * D + d] = sum == 0.0f ? 0.0f : __fmul_rn(acc[i], inv);
+  }
+}
+
+template <int D>
+cudaError_t launch_split(const FlashArgs& a, int n_rep, cudaStream_t st) {
+  if (n_rep % 4 == 0) {
+    flash_split_kernel<D, 4><<<dim3(a.splits, a.kv_heads, n_rep / 4), 128, 0, st>>>(a);
+  } else if (n_rep % 2 == 0) {
+    flash_split_kernel<D, 2><<<dim3(a.splits, a.kv_heads, n_rep / 2), 128, 0, st>>>(a);
+  } else {
+    flash_split_kernel<D, 1><<<dim3(a.splits, a.kv_heads, n_rep), 128, 0, st>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int flash_pick_splits(int tokens, int kv_heads, int sm_count, int max_splits) {
+  int need = (tokens + LMAX - 1) / LMAX;          // score buffer bound
+  int want = (2 * sm_count + kv_heads - 1) / kv_heads;  // ~2 CTAs per SM
+  const int by_len = tokens / 32 > 0 ? tokens / 32 : 1; // at least 32 tokens per range
+  if (want > by_len) want = by_len;
+  if (want < need) want = need;
+  if (want > max_splits) want = max_splits;
+  return want < 1 ? 1 : want;
+}
+
+bool flash_split_supported(const FlashArgs& a) {
+  const bool d_ok = a.head_dim == 64 || a.head_dim == 128;
+  const bool al = (reinterpret_cast<uintptr_t>(a.k) % 16 == 0) && (reinterpret_cast<uintptr_t>(a.v) % 16 == 0) &&
+                  a.k_nb1 % 16 == 0 && a.k_nb2 % 16 == 0 && a.v_nb1 % 16 == 0 && a.v_nb2 % 16 == 0;
+  return d_ok && al && (int64_t)a.splits * LMAX >= a.tokens;
+}
+
+cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches) {
+  (void)sm_count;
+  const int n_rep = a.heads / a.kv_heads;
+  cudaError_t e = a.head_dim == 64 ? launch_split<64>(a, n_rep, st) : launch_split<128>(a, n_rep, st);
+  if (e != cudaSuccess) return e;
+  flash_merge_kernel<<<a.heads, 128, 0, st>>>(a);
+  *launches += 2;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, cudaStream_t st, int* launches) {
+  int gx = (a.tokens + 3) / 4;
+  if (gx > 1024) gx = 1024;
+  flash_ref_scores_kernel<<<dim3(gx, a.heads), 128, 0, st>>>(a, score_ws, t_stride);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int D = a.head_dim;
+  if (D <= 256) flash_ref_sequential_kernel<1><<<a.heads, D < 32 ? 32 : ((D + 31) / 32) * 32, 0, st>>>(a, score_ws, t_stride);
+  else if (D <= 1024) flash_ref_sequential_kernel<4><<<a.heads, 256, 0, st>>>(a, score_ws, t_stride);
+  else flash_ref_sequential_kernel<16><<<a.heads, 256, 0, st>>>(a, score_ws, t_stride);
+  *launches += 2;
+  return cudaGetLastError();
+}
+
+}  // namespace emelb

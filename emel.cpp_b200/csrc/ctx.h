@@ -1,0 +1,66 @@
+// The backend context behind include/emelb.h's opaque emelb_ctx: stream,
+// persistent workspace, residency table and dispatch counters.  Its role is the
+// one of a kernel actor's context in the reference
+// (src/emel/kernel/x86_64/context.hpp:214-243): everything a dispatch needs is
+// allocated once, up front.
+#pragma once
+
+#include <map>
+#include <set>
+
+#include "../../include/emelb.h"
+#include "kernels.h"
+
+namespace emelb {
+
+constexpr uint64_t kFlashPartFloats = 4u << 20;   // split-KV partial accumulators
+constexpr uint64_t kFlashScoreFloats = 8u << 20;  // reference-order score rows
+
+struct Resident {
+  int state = EMELB_LIFECYCLE_UNBOUND;
+  void* dev = nullptr;
+  uint64_t bytes = 0;
+  const void* host = nullptr;
+  int32_t type = 0;
+};
+
+ActPlanes planes_view(const ActPlanesMut& m, int type, int K);
+cudaError_t quantize_into_planes(int wtype, const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st);
+
+}  // namespace emelb
+
+struct emelb_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  int attention_mode = 0;
+  int last_cuda_error = 0;
+  // device staging for host-resident activations / results
+  void* stage_in = nullptr;
+  uint64_t stage_in_bytes = 0;
+  void* stage_out = nullptr;
+  uint64_t stage_out_bytes = 0;
+  // quantized activation planes (scratch of op_mul_mat)
+  int8_t* act_qs = nullptr;
+  float* act_d = nullptr;
+  int16_t* act_bsums = nullptr;
+  uint64_t act_capacity = 0;  // elements
+  // shape of the activations emelb_prepare_rhs left in the planes (0 = none)
+  uint64_t prepared_n = 0;
+  uint64_t prepared_k = 0;
+  bool prepared_k_family = false;
+  // argmax candidates and result cells
+  float* part_val = nullptr;
+  int* part_idx = nullptr;
+  float* best_val = nullptr;
+  int* best_idx = nullptr;
+  // attention workspace
+  float* fa_part_acc = nullptr;
+  float* fa_part_ml = nullptr;
+  float* fa_scores = nullptr;
+  // residency: tensor id -> device copy; host span start -> tensor id
+  std::map<int32_t, emelb::Resident> residents;
+  std::map<uintptr_t, int32_t> by_host;
+  std::set<void*> owned;
+  emelb_diag diag = {};
+};

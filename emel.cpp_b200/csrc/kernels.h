@@ -1,0 +1,80 @@
+// Host-side launch interface of the sm_100a kernels (internal to the library;
+// the public surface is include/emelb.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace emelb {
+
+constexpr int kMaxArgmaxParts = 2048;
+
+struct GemvArgs {
+  const uint8_t* W;      // {K, M} native block rows
+  int64_t row_bytes;
+  int M;
+  int K;
+  ActPlanes act;         // quantized activations, column planes
+  int col0;              // first activation column this launch covers
+  float* y;              // y[row*ldy + col]
+  int64_t ldy;
+  const float* residual; // optional: y = residual + W x  (same indexing as y)
+  float* part_val;       // argmax: per-block candidates (kMaxArgmaxParts)
+  int* part_idx;
+  float* best_val;       // argmax result
+  int* best_idx;
+};
+
+// gemv.cu
+bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K);
+cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
+                        int* launches);
+
+// quantize.cu — built with -fmad=false: every float op rounds as written
+struct ActPlanesMut {
+  int8_t* qs;
+  float* d;
+  int16_t* bsums;
+};
+// x: f32 {n, K} token-fastest (x[p*n + j]); quantizes columns [0, ncols) into planes 0..ncols-1
+cudaError_t launch_quantize_q8_k_planes(const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st);
+cudaError_t launch_quantize_q8_0_planes(const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st);
+// reference array-of-blocks output: row j of `out` (row_bytes apart) = column j
+cudaError_t launch_quantize_q8_k_blocks(const float* x, int n, int K, uint8_t* out, int64_t row_bytes, cudaStream_t st);
+cudaError_t launch_quantize_q8_0_blocks(const float* x, int n, int K, uint8_t* out, int64_t row_bytes, cudaStream_t st);
+// reference blocks (one vector of K) -> planes
+cudaError_t launch_blocks_to_planes(int type, const uint8_t* blocks, int K, ActPlanesMut out, cudaStream_t st);
+// src rows of native blocks -> f32 rows
+cudaError_t launch_dequantize(int type, const uint8_t* src, int64_t src_row_bytes, float* dst, int64_t dst_row_elems,
+                              int K, int M, cudaStream_t st);
+
+// synth.cu — synthetic N(0, sigma) data generated and block-encoded on the device
+cudaError_t launch_fill_normal(float* out, uint64_t n, uint64_t seed, float sigma, uint64_t offset, cudaStream_t st);
+cudaError_t launch_encode_normal(int type, uint8_t* out, uint64_t elems, uint64_t seed, float sigma, uint64_t offset,
+                                 cudaStream_t st);
+
+// attention.cu
+struct FlashArgs {
+  const float* q;        // {d, 1, H} dense
+  const __half* k;       // {d, T, Hkv}, byte strides nb1 / nb2
+  const __half* v;
+  float* dst;            // {d, 1, H} dense
+  int64_t k_nb1, k_nb2, v_nb1, v_nb2;
+  int head_dim, heads, kv_heads;
+  int tokens;            // used when tokens_dev == nullptr
+  const int* tokens_dev; // optional: token count read on the device (graph replay)
+  float scale;
+  int splits;            // KV splits per kv head
+  float* part_acc;       // [H][splits][d]
+  float* part_ml;        // [H][splits][2]  (running max, running sum)
+};
+cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches);
+// score_ws: [heads][t_stride] f32 scratch
+cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, cudaStream_t st, int* launches);
+// true when the split-KV kernel takes this request (head_dim 64/128, 16-byte aligned rows)
+bool flash_split_supported(const FlashArgs& a);
+int flash_pick_splits(int tokens, int kv_heads, int sm_count, int max_splits);
+
+}  // namespace emelb

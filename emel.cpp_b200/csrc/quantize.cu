@@ -1,0 +1,242 @@
+// Activation quantizers and block dequantizers — the bit-exact kernels.
+// This file is compiled with -fmad=false and uses the IEEE round-to-nearest
+// intrinsics for every division, so each float operation rounds exactly as the
+// reference's C++ does when built without contraction:
+//   quantize_row_q8_k_strided   src/emel/kernel/detail.hpp:826-867
+//   quantize_row_q8_0_strided   src/emel/kernel/detail.hpp:804-824
+//   dequantize_row_q4_k/q6_k/q8_0/q4_0   :523-552, 592-629, 679-690, 487-502
+#include "common.cuh"
+#include "kernels.h"
+
+namespace emelb {
+
+namespace {
+
+// nearest_int, src/emel/kernel/detail.hpp:692-697 (1.5*2^23 magic add)
+__device__ __forceinline__ int nearest_int(float v) {
+  const float biased = __fadd_rn(v, 12582912.0f);
+  return (__float_as_int(biased) & 0x007fffff) - 0x00400000;
+}
+
+// One warp per (256-block, column).  Lane l owns elements 8l..8l+7 so that two
+// neighbouring lanes form one 16-wide bsum group.
+template <bool BLOCKS>
+__global__ void __launch_bounds__(128)
+quantize_q8_k_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut planes, uint8_t* blocks, int64_t row_bytes) {
+  const int lane = threadIdx.x & 31;
+  const int blk = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int col = blockIdx.y;
+  if (blk >= K / QK_K) return;
+  const float* src = x + ((int64_t)blk * QK_K + 8 * lane) * n + col;
+  float v[8];
+  float amax = 0.0f, mx = 0.0f;
+  int idx = 8 * lane;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[i] = src[(int64_t)i * n];
+    const float a = fabsf(v[i]);
+    if (a > amax) { amax = a; mx = v[i]; idx = 8 * lane + i; }
+  }
+  // first element attaining the largest |x| wins (strict > scan in the reference)
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+    const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
+  }
+  int q[8];
+  float d = 0.0f;
+  if (amax == 0.0f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = 0;
+  } else {
+    const float iscale = __fdiv_rn(-127.0f, mx);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = nearest_int(__fmul_rn(iscale, v[i]));
+      q[i] = (int)(int8_t)(t < 127 ? t : 127);
+    }
+    d = __fdiv_rn(1.0f, iscale);
+  }
+  int s = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += q[i];
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    lo |= (uint32_t)(q[i] & 0xff) << (8 * i);
+    hi |= (uint32_t)(q[4 + i] & 0xff) << (8 * i);
+  }
+  if constexpr (BLOCKS) {
+    // reference layout: f32 d, i8 qs[256], i16 bsums[16]; 4-byte aligned only
+    uint8_t* b = blocks + (int64_t)col * row_bytes + (int64_t)blk * Q8_K_BYTES;
+    uint32_t* qw = reinterpret_cast<uint32_t*>(b + 4 + 8 * lane);
+    qw[0] = lo; qw[1] = hi;
+    if ((lane & 1) == 0) *reinterpret_cast<int16_t*>(b + 260 + 2 * (lane >> 1)) = (int16_t)s;
+    if (lane == 0) *reinterpret_cast<float*>(b) = d;
+  } else {
+    const int64_t e0 = (int64_t)blk * QK_K + 8 * lane;
+    *reinterpret_cast<uint2*>(planes.qs + (int64_t)col * K + e0) = make_uint2(lo, hi);
+    if ((lane & 1) == 0) planes.bsums[(int64_t)col * (K / 16) + blk * 16 + (lane >> 1)] = (int16_t)s;
+    if (lane == 0) planes.d[(int64_t)col * (K / QK_K) + blk] = d;
+  }
+}
+
+// Eight lanes per 32-block, four elements per lane; std::round = roundf
+template <bool BLOCKS>
+__global__ void __launch_bounds__(128)
+quantize_q8_0_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut planes, uint8_t* blocks, int64_t row_bytes) {
+  const int sub = threadIdx.x & 7;
+  const int blk = blockIdx.x * 16 + (threadIdx.x >> 3);
+  const int col = blockIdx.y;
+  const bool live = blk < K / QK32;
+  const int cb = live ? blk : 0;
+  const float* src = x + ((int64_t)cb * QK32 + 4 * sub) * n + col;
+  float v[4];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[i] = src[(int64_t)i * n];
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = __fdiv_rn(amax, 127.0f);
+  const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+  uint32_t w = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int t = (int)roundf(__fmul_rn(v[i], id));
+    t = t < -127 ? -127 : (t > 127 ? 127 : t);
+    w |= (uint32_t)(t & 0xff) << (8 * i);
+  }
+  if (!live) return;
+  const __half dh = __float2half_rn(d);  // fp32_to_fp16, src/emel/kernel/detail.hpp:372-392 (RNE)
+  if constexpr (BLOCKS) {
+    uint8_t* b = blocks + (int64_t)col * row_bytes + (int64_t)blk * Q8_0_BYTES;
+    uint16_t* qh = reinterpret_cast<uint16_t*>(b + 2 + 4 * sub);  // 2-byte aligned payload
+    qh[0] = (uint16_t)(w & 0xffffu);
+    qh[1] = (uint16_t)(w >> 16);
+    if (sub == 0) *reinterpret_cast<uint16_t*>(b) = __half_as_ushort(dh);
+  } else {
+    *reinterpret_cast<uint32_t*>(planes.qs + (int64_t)col * K + (int64_t)blk * QK32 + 4 * sub) = w;
+    if (sub == 0) planes.d[(int64_t)col * (K / QK32) + blk] = __half2float(dh);
+  }
+}
+
+__global__ void blocks_to_planes_q8_k_kernel(const uint8_t* __restrict__ blocks, int nblk, ActPlanesMut out) {
+  const int blk = blockIdx.x;
+  const uint8_t* b = blocks + (int64_t)blk * Q8_K_BYTES;
+  const int t = threadIdx.x;  // 64 threads
+  if (blk >= nblk) return;
+  reinterpret_cast<uint32_t*>(out.qs + (int64_t)blk * QK_K)[t] = *reinterpret_cast<const uint32_t*>(b + 4 + 4 * t);
+  if (t < 16) out.bsums[blk * 16 + t] = *reinterpret_cast<const int16_t*>(b + 260 + 2 * t);
+  if (t == 0) out.d[blk] = *reinterpret_cast<const float*>(b);
+}
+
+__global__ void blocks_to_planes_q8_0_kernel(const uint8_t* __restrict__ blocks, int nblk, ActPlanesMut out) {
+  const int blk = blockIdx.x * 8 + (threadIdx.x >> 4);
+  const int t = threadIdx.x & 15;  // 16 threads per block, 2 bytes each
+  if (blk >= nblk) return;
+  const uint8_t* b = blocks + (int64_t)blk * Q8_0_BYTES;
+  reinterpret_cast<uint16_t*>(out.qs + (int64_t)blk * QK32)[t] = *reinterpret_cast<const uint16_t*>(b + 2 + 2 * t);
+  if (t == 0) out.d[blk] = h2f(*reinterpret_cast<const uint16_t*>(b));
+}
+
+// ---- dequantizers: one thread per output element, scalar loads (rows of
+// embedding tables and parity checks; not a bandwidth path)
+__device__ __forceinline__ uint16_t ld16u(const uint8_t* p) { return (uint16_t)p[0] | ((uint16_t)p[1] << 8); }
+
+template <int T>
+__global__ void dequantize_kernel(const uint8_t* __restrict__ src, int64_t src_row_bytes, float* __restrict__ dst,
+                                  int64_t dst_row_elems, int K, int M) {
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int row = blockIdx.y;
+  if (e >= K || row >= M) return;
+  const uint8_t* r = src + (int64_t)row * src_row_bytes;
+  float out;
+  if constexpr (T == T_Q4_K) {
+    const uint8_t* b = r + (e / QK_K) * Q4_K_BYTES;
+    const int p = (int)(e % QK_K), j = p / 32, l = p % 32;
+    const float d = h2f(ld16u(b)), mn = h2f(ld16u(b + 2));
+    const uint8_t* s = b + 4;
+    int sc, m;
+    if (j < 4) { sc = s[j] & 63; m = s[j + 4] & 63; }
+    else { sc = (s[j + 4] & 0x0f) | ((s[j - 4] >> 6) << 4); m = (s[j + 4] >> 4) | ((s[j] >> 6) << 4); }
+    const uint8_t qb = b[16 + 32 * (j >> 1) + l];
+    const int q = (j & 1) ? (qb >> 4) : (qb & 0x0f);
+    const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(mn, (float)m);
+    out = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+  } else if constexpr (T == T_Q6_K) {
+    const uint8_t* b = r + (e / QK_K) * Q6_K_BYTES;
+    const int p = (int)(e % QK_K), n = p / 128, pp = p % 128, g = pp / 32, l = pp % 32;
+    const uint8_t qlb = b[64 * n + l + 32 * (g & 1)];
+    const uint8_t qhb = b[128 + 32 * n + l];
+    const int lo = (g & 2) ? (qlb >> 4) : (qlb & 0x0f);
+    const int q = (int)(int8_t)(lo | (((qhb >> (2 * g)) & 3) << 4)) - 32;
+    const int sc = (int)(int8_t)b[192 + 8 * n + l / 16 + 2 * g];
+    const float d = h2f(ld16u(b + 208));
+    out = __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+  } else if constexpr (T == T_Q8_0) {
+    const uint8_t* b = r + (e / QK32) * Q8_0_BYTES;
+    out = __fmul_rn(h2f(ld16u(b)), (float)(int8_t)b[2 + e % QK32]);
+  } else {
+    const uint8_t* b = r + (e / QK32) * Q4_0_BYTES;
+    const int p = (int)(e % QK32);
+    const uint8_t qb = b[2 + (p & 15)];
+    const int q = (p < 16 ? (qb & 0x0f) : (qb >> 4)) - 8;
+    out = __fmul_rn((float)q, h2f(ld16u(b)));
+  }
+  dst[(int64_t)row * dst_row_elems + e] = out;
+}
+
+}  // namespace
+
+cudaError_t launch_quantize_q8_k_planes(const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st) {
+  const dim3 grid((K / QK_K + 3) / 4, ncols);
+  quantize_q8_k_kernel<false><<<grid, 128, 0, st>>>(x, n, K, out, nullptr, 0);
+  return cudaGetLastError();
+}
+cudaError_t launch_quantize_q8_0_planes(const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st) {
+  const dim3 grid((K / QK32 + 15) / 16, ncols);
+  quantize_q8_0_kernel<false><<<grid, 128, 0, st>>>(x, n, K, out, nullptr, 0);
+  return cudaGetLastError();
+}
+cudaError_t launch_quantize_q8_k_blocks(const float* x, int n, int K, uint8_t* out, int64_t row_bytes, cudaStream_t st) {
+  const dim3 grid((K / QK_K + 3) / 4, n);
+  quantize_q8_k_kernel<true><<<grid, 128, 0, st>>>(x, n, K, ActPlanesMut{}, out, row_bytes);
+  return cudaGetLastError();
+}
+cudaError_t launch_quantize_q8_0_blocks(const float* x, int n, int K, uint8_t* out, int64_t row_bytes, cudaStream_t st) {
+  const dim3 grid((K / QK32 + 15) / 16, n);
+  quantize_q8_0_kernel<true><<<grid, 128, 0, st>>>(x, n, K, ActPlanesMut{}, out, row_bytes);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_blocks_to_planes(int type, const uint8_t* blocks, int K, ActPlanesMut out, cudaStream_t st) {
+  if (type == T_Q8_K) {
+    blocks_to_planes_q8_k_kernel<<<K / QK_K, 64, 0, st>>>(blocks, K / QK_K, out);
+  } else if (type == T_Q8_0) {
+    blocks_to_planes_q8_0_kernel<<<(K / QK32 + 7) / 8, 128, 0, st>>>(blocks, K / QK32, out);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize(int type, const uint8_t* src, int64_t src_row_bytes, float* dst, int64_t dst_row_elems,
+                              int K, int M, cudaStream_t st) {
+  const dim3 grid((K + 255) / 256, M);
+  switch (type) {
+    case T_Q4_K: dequantize_kernel<T_Q4_K><<<grid, 256, 0, st>>>(src, src_row_bytes, dst, dst_row_elems, K, M); break;
+    case T_Q6_K: dequantize_kernel<T_Q6_K><<<grid, 256, 0, st>>>(src, src_row_bytes, dst, dst_row_elems, K, M); break;
+    case T_Q8_0: dequantize_kernel<T_Q8_0><<<grid, 256, 0, st>>>(src, src_row_bytes, dst, dst_row_elems, K, M); break;
+    case T_Q4_0: dequantize_kernel<T_Q4_0><<<grid, 256, 0, st>>>(src, src_row_bytes, dst, dst_row_elems, K, M); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace emelb

@@ -16,8 +16,8 @@
  *  - A view's `data` pointer may be: a device pointer; a host pointer inside
  *    a span registered with emelb_residency_upload (weights: the device copy
  *    is used, no transfer); or any other host pointer (activations/results:
- *    staged through the context's pinned buffers, the call returns after the
- *    result is back in host memory).  The pointer kind is looked up (residency
+ *    copied through the context's device staging area inside the call, which
+ *    returns after the result is back in host memory).  The pointer kind is looked up (residency
  *    table, then the CUDA driver's pointer attributes), never guessed.
  *  - One context per caller thread/lane; a context is not re-entrant
  *    (same rule as one kernel actor per lane,
@@ -29,6 +29,12 @@
 #define EMELB_H
 
 #include <stdint.h>
+
+#if defined(__GNUC__)
+#define EMELB_API __attribute__((visibility("default")))
+#else
+#define EMELB_API
+#endif
 
 #ifdef __cplusplus
 extern "C" {
@@ -125,46 +131,46 @@ typedef struct emelb_ctx emelb_ctx;
 
 /* ---- context: replaces constructing one kernel actor
  * (src/emel/kernel/x86_64/context.hpp:214-243). Allocates the persistent
- * workspace (activation scratch, attention partials, pinned staging); no
+ * workspace (activation scratch, attention partials, device staging); no
  * allocation happens in any dispatch call afterwards. ---- */
-uint32_t emelb_create(int device, emelb_ctx** out);
-uint32_t emelb_destroy(emelb_ctx* ctx);
+EMELB_API uint32_t emelb_create(int device, emelb_ctx** out);
+EMELB_API uint32_t emelb_destroy(emelb_ctx* ctx);
 /* waits for the context's stream; EMELB_INTERNAL_ERROR on a CUDA error */
-uint32_t emelb_sync(emelb_ctx* ctx);
+EMELB_API uint32_t emelb_sync(emelb_ctx* ctx);
 /* the cudaStream_t all work of this context is enqueued on */
-uint32_t emelb_get_stream(emelb_ctx* ctx, void** stream_out);
+EMELB_API uint32_t emelb_get_stream(emelb_ctx* ctx, void** stream_out);
 /* event::capture_diagnostics: src/emel/kernel/any.hpp:38-74 */
-uint32_t emelb_diagnostics(const emelb_ctx* ctx, emelb_diag* out);
+EMELB_API uint32_t emelb_diagnostics(const emelb_ctx* ctx, emelb_diag* out);
 /* attention numerics: 0 = split-KV f32 accumulators (fast, default);
  * 1 = reference order: sequential over tokens with an f16-rounded accumulator
  * (src/emel/kernel/detail.hpp:5238-5291). */
-uint32_t emelb_set_attention_mode(emelb_ctx* ctx, int mode);
+EMELB_API uint32_t emelb_set_attention_mode(emelb_ctx* ctx, int mode);
 
 /* ---- residency: replaces io::loader strategy `external_buffer`
  * (src/emel/io/loader/events.hpp:25-31, rejected as unsupported at
  * src/emel/io/loader/sm.hpp:78-81) and model::tensor lifecycle/state
  * (src/emel/model/tensor/events.hpp:18-34, 85-89). Bytes are uploaded
  * unchanged; `host` stays the key a later view may carry. ---- */
-uint32_t emelb_residency_upload(emelb_ctx* ctx, int32_t tensor_id,
+EMELB_API uint32_t emelb_residency_upload(emelb_ctx* ctx, int32_t tensor_id,
                                 const void* host, uint64_t bytes,
                                 int32_t tensor_type, const void** dev_out);
-uint32_t emelb_residency_evict(emelb_ctx* ctx, int32_t tensor_id);
-uint32_t emelb_residency_state(const emelb_ctx* ctx, int32_t tensor_id,
+EMELB_API uint32_t emelb_residency_evict(emelb_ctx* ctx, int32_t tensor_id);
+EMELB_API uint32_t emelb_residency_state(const emelb_ctx* ctx, int32_t tensor_id,
                                emelb_tensor_state* out);
 
 /* plain device buffers for activations / KV cache owned by the caller */
-uint32_t emelb_device_alloc(emelb_ctx* ctx, uint64_t bytes, void** dev_out);
-uint32_t emelb_device_free(emelb_ctx* ctx, void* dev);
-uint32_t emelb_copy_to_device(emelb_ctx* ctx, void* dev, const void* host,
+EMELB_API uint32_t emelb_device_alloc(emelb_ctx* ctx, uint64_t bytes, void** dev_out);
+EMELB_API uint32_t emelb_device_free(emelb_ctx* ctx, void* dev);
+EMELB_API uint32_t emelb_copy_to_device(emelb_ctx* ctx, void* dev, const void* host,
                               uint64_t bytes);
-uint32_t emelb_copy_to_host(emelb_ctx* ctx, void* host, const void* dev,
+EMELB_API uint32_t emelb_copy_to_host(emelb_ctx* ctx, void* host, const void* dev,
                             uint64_t bytes);
 
 /* ---- guards: replaces can_run_mul_mat / can_run_mul_mat_argmax /
  * can_run_flash_attn_ext + validate_dispatch_request
  * (src/emel/kernel/detail.hpp:3843-3872, 3573-3606, 4346-4390, 1919-1927).
  * Pure: returns EMELB_OK or EMELB_INVALID_REQUEST, launches nothing. ---- */
-uint32_t emelb_can_run(const emelb_ctx* ctx, uint32_t op_code,
+EMELB_API uint32_t emelb_can_run(const emelb_ctx* ctx, uint32_t op_code,
                        const emelb_op* op);
 
 /* ---- op_mul_mat: replaces x86_64::sm.process_event(op_mul_mat)
@@ -174,40 +180,64 @@ uint32_t emelb_can_run(const emelb_ctx* ctx, uint32_t op_code,
  * src0 = {K, M} Q4_K|Q6_K|Q8_0|Q4_0 rows; src1 = {N, K} f32 (token fastest),
  * or the pre-quantized vector form {1, K} of type Q8_K / Q8_0
  * (src/emel/kernel/aarch64/actions.hpp:1471-1503); dst = {N, M} f32. ---- */
-uint32_t emelb_mul_mat(emelb_ctx* ctx, const emelb_op* op);
+EMELB_API uint32_t emelb_mul_mat(emelb_ctx* ctx, const emelb_op* op);
+
+/* ---- quantize once, multiply many: replaces the q8 route of the reference's
+ * callers, quantize_vector_q8_k + matmul_vector_q8_input (one quantized input
+ * feeds Q, K and V, or gate and up:
+ * src/emel/text/generator/detail.hpp:3780-3793, 3885-3899).
+ * emelb_prepare_rhs quantizes src1 (f32 {N, K}) for a weight type's family
+ * (Q8_K for K-quants, Q8_0 for 32-blocks) into the context's activation
+ * planes; emelb_mul_mat_prepared then runs op_mul_mat against those planes,
+ * launching only the matrix kernel.  op->src1 must describe the same {N, K}
+ * f32 tensor (its data pointer is not read).  Any other dispatch on the context
+ * invalidates the prepared planes. ---- */
+EMELB_API uint32_t emelb_prepare_rhs(emelb_ctx* ctx, const emelb_view* src1_f32,
+                                     int32_t weight_type);
+EMELB_API uint32_t emelb_mul_mat_prepared(emelb_ctx* ctx, const emelb_op* op);
 
 /* ---- op_mul_mat_argmax: replaces run_mul_mat_argmax
  * (src/emel/kernel/detail.hpp:3608-3731): dst[0] = best value,
  * *index_out = lowest row attaining it. ---- */
-uint32_t emelb_mul_mat_argmax(emelb_ctx* ctx, const emelb_op* op);
+EMELB_API uint32_t emelb_mul_mat_argmax(emelb_ctx* ctx, const emelb_op* op);
 
 /* ---- op_flash_attn_ext: replaces
  * run_flash_attn_ext_active_kv_with_workspace
  * (src/emel/kernel/detail.hpp:5238-5300) and the AVX2 one-chunk route
  * (src/emel/kernel/x86_64/actions.hpp:1575-1641). ---- */
-uint32_t emelb_flash_attn_ext(emelb_ctx* ctx, const emelb_op* op);
+EMELB_API uint32_t emelb_flash_attn_ext(emelb_ctx* ctx, const emelb_op* op);
 
 /* ---- activation quantizers: replace quantize_row_q8_k_strided /
  * quantize_row_q8_0_strided (src/emel/kernel/detail.hpp:826-867, 804-824).
  * src = f32 {N, K} (token fastest, as op_mul_mat's src1); dst type selects
  * Q8_K or Q8_0; dst holds N rows of K/256 (K/32) reference-layout blocks,
  * row j = column j of src.  Bit-exact. ---- */
-uint32_t emelb_quantize(emelb_ctx* ctx, const emelb_view* src_f32,
+EMELB_API uint32_t emelb_quantize(emelb_ctx* ctx, const emelb_view* src_f32,
                         const emelb_view* dst);
 
 /* ---- block dequantizers: replace dequantize_row_q4_k / q6_k / q8_0 / q4_0
  * (src/emel/kernel/detail.hpp:523-552, 592-629, 679-690, 487-502).
  * src = {K, M} quantized rows, dst = {K, M} f32.  Bit-exact. ---- */
-uint32_t emelb_dequantize(emelb_ctx* ctx, const emelb_view* src,
+EMELB_API uint32_t emelb_dequantize(emelb_ctx* ctx, const emelb_view* src,
                           const emelb_view* dst_f32);
 
 /* ---- row-slice helper: replaces compute_sliced_mul_mat_event +
  * compute_fixed_row_slice (src/emel/kernel/matmul/detail.hpp:36-54,
  * src/emel/kernel/matmul/actions.hpp:48-67). Pure host arithmetic:
  * writes lane `lane` of `lane_count`'s slice of `op` to `out`. ---- */
-uint32_t emelb_row_slice(const emelb_op* op, uint32_t lane,
+EMELB_API uint32_t emelb_row_slice(const emelb_op* op, uint32_t lane,
                          uint32_t lane_count, emelb_op* out,
                          uint64_t* row_begin, uint64_t* row_count);
+
+/* ---- synthetic data (no reference counterpart; the reference's benches fill
+ * buffers with closed-form patterns on the host,
+ * tools/bench/text/generator/parallel_matmul_bench.cpp:177-238).  Fills `dev`
+ * with `elems` values drawn N(0, sigma) from (seed, offset): as f32, or encoded
+ * on the device into Q4_K / Q6_K / Q8_0 / Q4_0 blocks by this project's own
+ * encoders.  Benchmark-sized models (tens of GB) are built this way. ---- */
+EMELB_API uint32_t emelb_synth_fill(emelb_ctx* ctx, void* dev, int32_t type,
+                                    uint64_t elems, uint64_t seed, float sigma,
+                                    uint64_t offset);
 
 #ifdef __cplusplus
 }
