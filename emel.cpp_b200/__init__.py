@@ -84,13 +84,18 @@ _SIGNATURES = {
     "emelb_flash_attn_ext": [_P, C.POINTER(Op)],
     "emelb_quantize": [_P, C.POINTER(View), C.POINTER(View)],
     "emelb_dequantize": [_P, C.POINTER(View), C.POINTER(View)],
+    "emelb_graph_begin": [_P],
+    "emelb_graph_end": [_P, C.POINTER(_P)],
+    "emelb_graph_launch": [_P, _P],
+    "emelb_graph_destroy": [_P, _P],
     "emelb_synth_fill": [_P, _P, C.c_int32, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64],
     "emelb_row_slice": [C.POINTER(Op), C.c_uint32, C.c_uint32, C.POINTER(Op), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
 }
 
 
 def declared_symbols():
-    return sorted(_SIGNATURES)
+    from . import llama as _llama
+    return sorted(list(_SIGNATURES) + list(_llama.SIGNATURES))
 
 
 def lib():
@@ -105,7 +110,8 @@ def lib():
             fn = getattr(_lib, name)
             fn.restype = C.c_uint32
             fn.argtypes = args
-        from . import llama as _llama  # noqa: F401  (registers the decoder's signatures when present)
+        from . import llama as _llama
+        _llama.register(_lib)
     return _lib
 
 
@@ -288,6 +294,22 @@ class Backend:
 
     def dequantize(self, src: View, dst: View) -> bool:
         return self._ret(lib().emelb_dequantize(self._h, C.byref(src), C.byref(dst)))
+
+    # -- stream capture of device-resident call sequences
+    def graph_begin(self) -> bool:
+        return self._ret(lib().emelb_graph_begin(self._h))
+
+    def graph_end(self) -> int:
+        g = _P()
+        if not self._ret(lib().emelb_graph_end(self._h, C.byref(g))):
+            raise BackendError(f"graph capture failed with error mask {self.last_error}")
+        return g.value
+
+    def graph_launch(self, graph: int) -> bool:
+        return self._ret(lib().emelb_graph_launch(self._h, graph))
+
+    def graph_destroy(self, graph: int) -> bool:
+        return self._ret(lib().emelb_graph_destroy(self._h, graph))
 
     def synth_fill(self, dev: int, t: int, elems: int, seed: int, sigma: float, offset: int = 0) -> bool:
         """N(0, sigma) synthetic data, f32 or block-encoded on the device."""

@@ -145,7 +145,17 @@ bool can_run_flash(const emelb_op& r) {
 // ------------------------------------------------------------------ pointers
 enum class Where { device, host, unknown };
 
-Where classify(const void* p) {
+// device ranges this context allocated itself are known without a driver query
+bool known_device(const emelb_ctx* c, const void* p) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  auto it = c->dev_ranges.upper_bound(a);
+  if (it == c->dev_ranges.begin()) return false;
+  --it;
+  return a < it->first + it->second;
+}
+
+Where classify(const emelb_ctx* c, const void* p) {
+  if (known_device(c, p)) return Where::device;
   cudaPointerAttributes at{};
   if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
     cudaGetLastError();
@@ -176,14 +186,14 @@ bool cuda_ok(emelb_ctx* c, cudaError_t e) {
 // weights: device pointer, or a host pointer inside a resident span
 const void* resolve_weights(emelb_ctx* c, const void* p) {
   if (const void* d = resident_lookup(c, p)) return d;
-  return classify(p) == Where::device ? p : nullptr;
+  return classify(c, p) == Where::device ? p : nullptr;
 }
 
 // activation input: device pointer used as is; host memory copied into the
 // device staging area (counted as h2d traffic)
 const void* stage_in(emelb_ctx* c, const void* p, uint64_t bytes, uint64_t slot_offset) {
   if (const void* d = resident_lookup(c, p)) return d;
-  if (classify(p) == Where::device) return p;
+  if (classify(c, p) == Where::device) return p;
   if (slot_offset + bytes > c->stage_in_bytes) return nullptr;
   void* d = static_cast<uint8_t*>(c->stage_in) + slot_offset;
   if (!cuda_ok(c, cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, c->stream))) return nullptr;
@@ -199,7 +209,7 @@ struct OutBinding {
 
 bool bind_out(emelb_ctx* c, const void* p, uint64_t bytes, uint64_t slot_offset, OutBinding* o) {
   o->bytes = bytes;
-  if (classify(p) == Where::device) { o->dev = const_cast<void*>(p); return true; }
+  if (classify(c, p) == Where::device) { o->dev = const_cast<void*>(p); return true; }
   if (slot_offset + bytes > c->stage_out_bytes) return false;
   o->dev = static_cast<uint8_t*>(c->stage_out) + slot_offset;
   o->host = const_cast<void*>(p);
@@ -253,6 +263,9 @@ ActPlanes planes_view(const ActPlanesMut& m, int type, int K) {
   return a;
 }
 
+const void* ctx_resolve_weights(emelb_ctx* c, const void* p) { return resolve_weights(c, p); }
+bool ctx_cuda_ok(emelb_ctx* c, cudaError_t e) { return cuda_ok(c, e); }
+
 cudaError_t quantize_into_planes(int wtype, const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st) {
   return is_k_type(wtype) ? launch_quantize_q8_k_planes(x, n, ncols, K, out, st)
                           : launch_quantize_q8_0_planes(x, n, ncols, K, out, st);
@@ -298,6 +311,8 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
     emelb_destroy(c);
     return EMELB_INTERNAL_ERROR;
   }
+  c->dev_ranges[reinterpret_cast<uintptr_t>(c->stage_in)] = c->stage_in_bytes;
+  c->dev_ranges[reinterpret_cast<uintptr_t>(c->stage_out)] = c->stage_out_bytes;
   *out = c;
   return EMELB_OK;
 }
@@ -337,7 +352,7 @@ uint32_t emelb_diagnostics(const emelb_ctx* c, emelb_diag* out) {
 }
 
 uint32_t emelb_set_attention_mode(emelb_ctx* c, int mode) {
-  if (!c || (mode != 0 && mode != 1)) return EMELB_INVALID_REQUEST;
+  if (!c || mode < 0 || mode > 2) return EMELB_INVALID_REQUEST;
   c->attention_mode = mode;
   return EMELB_OK;
 }
@@ -365,6 +380,7 @@ uint32_t emelb_residency_upload(emelb_ctx* c, int32_t tensor_id, const void* hos
   if (r.host) c->by_host.erase(reinterpret_cast<uintptr_t>(r.host));
   r = Resident{EMELB_LIFECYCLE_RESIDENT, dev, bytes, host, tensor_type};
   c->by_host[reinterpret_cast<uintptr_t>(host)] = tensor_id;
+  c->dev_ranges[reinterpret_cast<uintptr_t>(dev)] = bytes;
   if (dev_out) *dev_out = dev;
   return EMELB_OK;
 }
@@ -375,6 +391,7 @@ uint32_t emelb_residency_evict(emelb_ctx* c, int32_t tensor_id) {
   if (it == c->residents.end() || it->second.state != EMELB_LIFECYCLE_RESIDENT) return EMELB_INVALID_REQUEST;
   cudaStreamSynchronize(c->stream);
   cudaFree(it->second.dev);
+  c->dev_ranges.erase(reinterpret_cast<uintptr_t>(it->second.dev));
   c->by_host.erase(reinterpret_cast<uintptr_t>(it->second.host));
   it->second.dev = nullptr;
   it->second.state = EMELB_LIFECYCLE_EVICTED;
@@ -399,6 +416,7 @@ uint32_t emelb_device_alloc(emelb_ctx* c, uint64_t bytes, void** dev_out) {
   void* p = nullptr;
   if (!cuda_ok(c, cudaMalloc(&p, (bytes + 255) & ~uint64_t(255)))) return EMELB_INTERNAL_ERROR;
   c->owned.insert(p);
+  c->dev_ranges[reinterpret_cast<uintptr_t>(p)] = bytes;
   *dev_out = p;
   return EMELB_OK;
 }
@@ -408,6 +426,7 @@ uint32_t emelb_device_free(emelb_ctx* c, void* dev) {
   cudaStreamSynchronize(c->stream);
   cudaFree(dev);
   c->owned.erase(dev);
+  c->dev_ranges.erase(reinterpret_cast<uintptr_t>(dev));
   return EMELB_OK;
 }
 
@@ -448,10 +467,15 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
   const uint64_t n = op->src1.ne[0];
   cudaSetDevice(c->device);
 
-  const uint8_t* W = static_cast<const uint8_t*>(resolve_weights(c, op->src0.data));
-  if (!W) return reject(c);
   const bool preq = op->src1.type != T_F32;
   const uint64_t src1_bytes = preq ? row_bytes_of(op->src1.type, K) : n * (uint64_t)K * 4;
+  // weights: resident span or device pointer; plain host weights (never uploaded)
+  // are copied through the staging area behind src1 on every call
+  const uint8_t* W = static_cast<const uint8_t*>(resolve_weights(c, op->src0.data));
+  if (!W) {
+    W = static_cast<const uint8_t*>(stage_in(c, op->src0.data, (uint64_t)M * op->src0.nb[1], (src1_bytes + 255) & ~uint64_t(255)));
+    if (!W) { c->diag.rejected_dispatch_calls += 1; return EMELB_UNSUPPORTED_OP; }
+  }
   const void* x = nullptr;
   if (prepared) {
     // the planes left by emelb_prepare_rhs must describe this src1
@@ -515,7 +539,7 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
 
   bool need_sync = false;
   if (argmax) {
-    const Where wd = classify(op->dst.data), wi = classify(op->index_out);
+    const Where wd = classify(c, op->dst.data), wi = classify(c, op->index_out);
     ok = cuda_ok(c, cudaMemcpyAsync(const_cast<void*>(op->dst.data), c->best_val, 4,
                                     wd == Where::device ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, c->stream));
     ok = ok && cuda_ok(c, cudaMemcpyAsync(op->index_out, c->best_idx, 4,
@@ -597,7 +621,7 @@ uint32_t emelb_flash_attn_ext(emelb_ctx* c, const emelb_op* op) {
     c->diag.optimized_flash_dispatch_calls += 1;
   } else {
     if ((uint64_t)H * (uint64_t)T > kFlashScoreFloats) { c->diag.rejected_dispatch_calls += 1; return EMELB_UNSUPPORTED_OP; }
-    ok = cuda_ok(c, launch_flash_reference_order(a, c->fa_scores, T, c->stream, &launches));
+    ok = cuda_ok(c, launch_flash_reference_order(a, c->fa_scores, T, c->attention_mode == 1 ? 1 : 2, c->stream, &launches));
     c->diag.shared_flash_dispatch_calls += 1;
   }
   c->diag.kernel_launches += launches;
@@ -657,6 +681,39 @@ uint32_t emelb_dequantize(emelb_ctx* c, const emelb_view* src, const emelb_view*
   ok = ok && finish_out(c, out, &need_sync);
   if (ok && need_sync) ok = cuda_ok(c, cudaStreamSynchronize(c->stream));
   return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+// ------------------------------------------------------------------ graphs
+uint32_t emelb_graph_begin(emelb_ctx* c) {
+  if (!c || c->capturing) return EMELB_INVALID_REQUEST;
+  cudaSetDevice(c->device);
+  if (!cuda_ok(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal))) return EMELB_INTERNAL_ERROR;
+  c->capturing = true;
+  return EMELB_OK;
+}
+
+uint32_t emelb_graph_end(emelb_ctx* c, void** graph_out) {
+  if (!c || !graph_out || !c->capturing) return EMELB_INVALID_REQUEST;
+  c->capturing = false;
+  cudaGraph_t g = nullptr;
+  if (!cuda_ok(c, cudaStreamEndCapture(c->stream, &g)) || !g) return EMELB_INTERNAL_ERROR;
+  cudaGraphExec_t ex = nullptr;
+  const bool ok = cuda_ok(c, cudaGraphInstantiate(&ex, g, 0));
+  cudaGraphDestroy(g);
+  if (!ok) return EMELB_INTERNAL_ERROR;
+  *graph_out = ex;
+  return EMELB_OK;
+}
+
+uint32_t emelb_graph_launch(emelb_ctx* c, void* graph) {
+  if (!c || !graph || c->capturing) return EMELB_INVALID_REQUEST;
+  return cuda_ok(c, cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph), c->stream)) ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_graph_destroy(emelb_ctx* c, void* graph) {
+  if (!c || !graph) return EMELB_INVALID_REQUEST;
+  cudaStreamSynchronize(c->stream);
+  return cuda_ok(c, cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph))) ? EMELB_OK : EMELB_INTERNAL_ERROR;
 }
 
 // ------------------------------------------------------------------ synthetic data

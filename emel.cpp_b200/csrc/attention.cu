@@ -11,11 +11,13 @@
 //    probabilities, then the V accumulation with 128-bit loads; f32 throughout.
 //    A small second kernel merges the ranges.  HBM-bound: K and V are each read
 //    once.
-//  * reference order: scores as f64 sums of exact f16 products, then the
-//    reference's sequential online softmax with an f16 accumulator rounded after
-//    every token — the same roundings in the same order as the scalar route, for
-//    parity runs and for shapes the split kernel does not take.
+//  * reference order: scores in the summation order of the reference's scalar
+//    route or of its x86 AVX2 route, then the reference's sequential online
+//    softmax with an f16 accumulator rounded after every token and libm-exact
+//    expf — the same roundings in the same order, for parity runs and for shapes
+//    the split kernel does not take.
 #include "common.cuh"
+#include "expf_exact.h"
 #include "kernels.h"
 
 namespace emelb {
@@ -225,31 +227,45 @@ __global__ void flash_merge_kernel(const FlashArgs a) {
 }
 
 // ---------------------------------------------------------------- reference order
-// scores[h][t] = (float)(sum_i (double)q16[i] * (double)k[t][i]) * scale
-// (dot_product_f16_f16_scores, src/emel/kernel/detail.hpp:2203-2208); one warp per
-// (token, head), f64 partial sums combined across lanes.
-__global__ void __launch_bounds__(128) flash_ref_scores_kernel(const FlashArgs a, float* scores, int t_stride) {
+// scores[h][t] in one of the reference's two summation orders; one warp per
+// (token, head):
+//  order 1 (scalar route): (float)(sum_i (double)q16[i] * (double)k[t][i]) * scale
+//    (dot_product_f16_f16_scores, src/emel/kernel/detail.hpp:2203-2208), f64
+//    partial sums combined across lanes;
+//  order 2 (x86 AVX2 route): four 8-lane f32 accumulators advanced by fused
+//    multiply-adds 32 elements at a time, folded (0+1)+(2+3) in f32, the 8 lanes
+//    then summed in f64 in lane order, the tail (< 32 elements) added as f64
+//    products (dot_product_f16_f16_scores_avx2_fma,
+//    src/emel/kernel/x86_64/actions.hpp:1388-1446).  Warp lane L = 8j + l plays
+//    lane l of accumulator j, so every rounding happens where the AVX2 code has it.
+__global__ void __launch_bounds__(128) flash_ref_scores_kernel(const FlashArgs a, float* scores, int t_stride, int order) {
   const int lane = threadIdx.x & 31;
   const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
   const int h = blockIdx.y;
   const int kh = h / (a.heads / a.kv_heads);
+  const int D = a.head_dim;
+  const float* qh = a.q + (size_t)h * D;
   for (int t = blockIdx.x * 4 + (threadIdx.x >> 5); t < T; t += gridDim.x * 4) {
     const __half* kr = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(a.k) + (size_t)t * a.k_nb1 + (size_t)kh * a.k_nb2);
     double s = 0.0;
-    for (int i = lane; i < a.head_dim; i += 32) {
-      const float qv = __half2float(__float2half_rn(a.q[(size_t)h * a.head_dim + i]));
-      s += (double)qv * (double)__half2float(kr[i]);
-    }
+    if (order == 2) {
+      const int vec = D & ~31;
+      float f = 0.0f;
+      for (int i = lane; i < vec; i += 32) f = __fmaf_rn(__half2float(__float2half_rn(qh[i])), __half2float(kr[i]), f);
+      f = __fadd_rn(f, __shfl_xor_sync(0xffffffffu, f, 8));    // sum0+sum1 | sum2+sum3
+      f = __fadd_rn(f, __shfl_xor_sync(0xffffffffu, f, 16));   // (sum0+sum1)+(sum2+sum3)
+      for (int l = 0; l < 8; ++l) s += (double)__shfl_sync(0xffffffffu, f, l);
+      for (int i = vec; i < D; ++i) s += (double)__half2float(__float2half_rn(qh[i])) * (double)__half2float(kr[i]);
+    } else {
+      for (int i = lane; i < D; i += 32) s += (double)__half2float(__float2half_rn(qh[i])) * (double)__half2float(kr[i]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    }
     if (lane == 0) scores[(size_t)h * t_stride + t] = __fmul_rn((float)s, a.scale);
   }
 }
 
 __device__ __forceinline__ float round16(float v) { return __half2float(__float2half_rn(v)); }
-// std::exp(float) of the host libm is correctly rounded in all but vanishingly
-// rare cases; the f64 exp rounded once to f32 reproduces that
-__device__ __forceinline__ float exp_cr(float x) { return (float)exp((double)x); }
 
 // One CTA per head; thread d owns accumulator dims d, d+blockDim, ...; every
 // thread replays the scalar recurrences (max, scales, sum) so no barrier sits
@@ -276,7 +292,7 @@ __global__ void flash_ref_sequential_kernel(const FlashArgs a, const float* scor
       const float old = mx;
       float ms = 1.0f, vsc = 1.0f;
       const bool bump = score > mx;
-      if (bump) { mx = score; ms = exp_cr(old - mx); } else { vsc = exp_cr(score - mx); }
+      if (bump) { mx = score; ms = expf_exact(old - mx); } else { vsc = expf_exact(score - mx); }
       const float rs = round16(ms), ra = round16(vsc);
       const __half* vr = reinterpret_cast<const __half*>(vbase + (size_t)(tb + tt) * a.v_nb1);
 #pragma unroll
@@ -340,10 +356,11 @@ cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t s
   return cudaGetLastError();
 }
 
-cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, cudaStream_t st, int* launches) {
+cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, int order, cudaStream_t st,
+                                         int* launches) {
   int gx = (a.tokens + 3) / 4;
   if (gx > 1024) gx = 1024;
-  flash_ref_scores_kernel<<<dim3(gx, a.heads), 128, 0, st>>>(a, score_ws, t_stride);
+  flash_ref_scores_kernel<<<dim3(gx, a.heads), 128, 0, st>>>(a, score_ws, t_stride, order);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int D = a.head_dim;

@@ -62,5 +62,7 @@ struct emelb_ctx {
   std::map<int32_t, emelb::Resident> residents;
   std::map<uintptr_t, int32_t> by_host;
   std::set<void*> owned;
+  std::map<uintptr_t, uint64_t> dev_ranges;  // device spans this context allocated (start -> bytes)
+  bool capturing = false;
   emelb_diag diag = {};
 };

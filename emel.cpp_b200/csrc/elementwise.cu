@@ -1,0 +1,276 @@
+// The element-wise steps between the matrix products of one decoder layer, as
+// the reference's generator computes them (src/emel/text/generator/detail.hpp):
+//   rms_norm                    :2735-2756   (f64 sum of f32 squares)
+//   apply_rope_pairing          :2905-2936   (adjacent or half-split pairs)
+//   store_attention_kv_cache    :3294-3332   (K, V rounded to f16)
+//   silu(gate) * up             :2967-2973, 3911-3913 (expf with the host libm's bits)
+//   copy_tensor_row             :819-872     (embedding row -> f32)
+// Each kernel also emits what the next matrix product consumes (the quantized
+// activation planes), so a layer is a short chain of launches.  Compiled with
+// -fmad=false: every product and sum rounds as written in the reference.
+#include "expf_exact.h"
+#include "quant_device.cuh"
+
+namespace emelb {
+
+namespace {
+
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- out = (x * 1/sqrt(mean(x^2) + eps)) * w ; optionally quantized for the
+// consumer family (FAMILY 0: none, 1: Q8_K planes, 2: Q8_0 planes).  One CTA.
+template <int FAMILY>
+__global__ void __launch_bounds__(1024)
+rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int n, float* out, ActPlanesMut planes) {
+  __shared__ double s_part[32];
+  __shared__ float s_scale;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  double acc = 0.0;
+  for (int i = tid; i < n; i += blockDim.x) {
+    const float v = x[i];
+    acc += (double)__fmul_rn(v, v);
+  }
+  acc = warp_sum_f64(acc);
+  if (lane == 0) s_part[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    double t = lane < nwarps ? s_part[lane] : 0.0;
+    t = warp_sum_f64(t);
+    if (lane == 0) {
+      const float mean = (float)(t / (double)n);
+      s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    }
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  if constexpr (FAMILY == 1) {
+    for (int blk = warp; blk < n / QK_K; blk += nwarps) {
+      float v[8];
+      const int e0 = blk * QK_K + 8 * lane;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(x[e0 + i], scale), w[e0 + i]);
+      if (out) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[e0 + i] = v[i];
+      }
+      uint32_t lo, hi; int s; float d;
+      q8_k_block_warp(v, lane, lo, hi, s, d);
+      q8_k_store_planes(planes, 0, n, blk, lane, lo, hi, s, d);
+    }
+  } else if constexpr (FAMILY == 2) {
+    for (int e0 = 4 * tid; e0 < n; e0 += 4 * blockDim.x) {
+      float v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = __fmul_rn(__fmul_rn(x[e0 + i], scale), w[e0 + i]);
+      if (out) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[e0 + i] = v[i];
+      }
+      uint32_t q; __half dh;
+      q8_0_block_oct(v, q, dh);
+      *reinterpret_cast<uint32_t*>(planes.qs + e0) = q;
+      if ((tid & 7) == 0) planes.d[e0 / QK32] = __half2float(dh);
+    }
+  } else {
+    for (int i = tid; i < n; i += blockDim.x) out[i] = __fmul_rn(__fmul_rn(x[i], scale), w[i]);
+  }
+}
+
+// ---- rotate q and k at `position` with the precomputed cos/sin table row,
+// store k and v as f16 into the KV cache rows of that position.
+// One thread per rotation pair / per copied element.
+__global__ void rope_store_kernel(float* q, const float* k, const float* v, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, const int* pos_dev, int n_head, int n_head_kv,
+                                  int head_dim, int rot_dim, int neox, __half* kcache, __half* vcache,
+                                  int64_t cache_head_stride /*halves*/) {
+  const int pos = *pos_dev;
+  const int pairs = rot_dim / 2;
+  const float* ct = cos_t + (int64_t)pos * pairs;
+  const float* st = sin_t + (int64_t)pos * pairs;
+  const int head = blockIdx.x;
+  const int x1_base = neox ? pairs : 1;
+  const int stride = neox ? 1 : 2;
+  if (head < n_head) {
+    float* h = q + (int64_t)head * head_dim;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+      const int d0 = p * stride, d1 = p * stride + x1_base;
+      const float x0 = h[d0], x1 = h[d1], c = ct[p], s = st[p];
+      h[d0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+      h[d1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    }
+  } else {
+    const int kh = head - n_head;
+    const float* h = k + (int64_t)kh * head_dim;
+    const float* vv = v + (int64_t)kh * head_dim;
+    __half* kd = kcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+    __half* vd = vcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+      const int d0 = p * stride, d1 = p * stride + x1_base;
+      const float x0 = h[d0], x1 = h[d1], c = ct[p], s = st[p];
+      kd[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+      kd[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
+    }
+    for (int d = rot_dim + threadIdx.x; d < head_dim; d += blockDim.x) kd[d] = __float2half_rn(h[d]);
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) vd[d] = __float2half_rn(vv[d]);
+  }
+}
+
+// ---- ffn = (gate / (1 + expf(-gate))) * up, quantized for the down projection
+template <int FAMILY>
+__global__ void __launch_bounds__(128)
+swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, int n, float* out, ActPlanesMut planes) {
+  const int lane = threadIdx.x & 31;
+  if constexpr (FAMILY == 1) {
+    const int blk = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (blk >= n / QK_K) return;
+    const int e0 = blk * QK_K + 8 * lane;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float g = gate[e0 + i];
+      v[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf_exact(-g))), up[e0 + i]);
+    }
+    if (out) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[e0 + i] = v[i];
+    }
+    uint32_t lo, hi; int s; float d;
+    q8_k_block_warp(v, lane, lo, hi, s, d);
+    q8_k_store_planes(planes, 0, n, blk, lane, lo, hi, s, d);
+  } else {
+    const int e0 = 4 * (blockIdx.x * 128 + threadIdx.x);
+    const bool live = e0 < n;
+    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float g = gate[e0 + i];
+        v[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf_exact(-g))), up[e0 + i]);
+      }
+    }
+    if constexpr (FAMILY == 2) {
+      uint32_t q; __half dh;
+      q8_0_block_oct(v, q, dh);
+      if (live) {
+        *reinterpret_cast<uint32_t*>(planes.qs + e0) = q;
+        if ((threadIdx.x & 7) == 0) planes.d[e0 / QK32] = __half2float(dh);
+      }
+    }
+    if (live && out) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) out[e0 + i] = v[i];
+    }
+  }
+}
+
+// ---- embedding row `*token_dev` of a {K, vocab} table -> f32 (same arithmetic
+// as the block dequantizers; f32 / f16 tables are copied / widened)
+__device__ __forceinline__ uint16_t ld16e(const uint8_t* p) { return (uint16_t)p[0] | ((uint16_t)p[1] << 8); }
+
+__global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, int64_t row_bytes, const int* token_dev,
+                                 float* __restrict__ dst, int K) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= K) return;
+  const uint8_t* r = table + (int64_t)(*token_dev) * row_bytes;
+  float out;
+  if (type == T_F32) {
+    out = reinterpret_cast<const float*>(r)[e];
+  } else if (type == T_F16) {
+    out = __half2float(reinterpret_cast<const __half*>(r)[e]);
+  } else if (type == T_Q4_K) {
+    const uint8_t* b = r + (e / QK_K) * Q4_K_BYTES;
+    const int p = e % QK_K, j = p / 32, l = p % 32;
+    const float d = h2f(ld16e(b)), mn = h2f(ld16e(b + 2));
+    const uint8_t* s = b + 4;
+    int sc, m;
+    if (j < 4) { sc = s[j] & 63; m = s[j + 4] & 63; }
+    else { sc = (s[j + 4] & 0x0f) | ((s[j - 4] >> 6) << 4); m = (s[j + 4] >> 4) | ((s[j] >> 6) << 4); }
+    const uint8_t qb = b[16 + 32 * (j >> 1) + l];
+    const int q = (j & 1) ? (qb >> 4) : (qb & 0x0f);
+    out = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(mn, (float)m));
+  } else if (type == T_Q6_K) {
+    const uint8_t* b = r + (e / QK_K) * Q6_K_BYTES;
+    const int p = e % QK_K, n = p / 128, pp = p % 128, g = pp / 32, l = pp % 32;
+    const uint8_t qlb = b[64 * n + l + 32 * (g & 1)];
+    const uint8_t qhb = b[128 + 32 * n + l];
+    const int lo = (g & 2) ? (qlb >> 4) : (qlb & 0x0f);
+    const int q = (int)(int8_t)(lo | (((qhb >> (2 * g)) & 3) << 4)) - 32;
+    const int sc = (int)(int8_t)b[192 + 8 * n + l / 16 + 2 * g];
+    out = __fmul_rn(__fmul_rn(h2f(ld16e(b + 208)), (float)sc), (float)q);
+  } else if (type == T_Q8_0) {
+    const uint8_t* b = r + (e / QK32) * Q8_0_BYTES;
+    out = __fmul_rn(h2f(ld16e(b)), (float)(int8_t)b[2 + e % QK32]);
+  } else {
+    const uint8_t* b = r + (e / QK32) * Q4_0_BYTES;
+    const int p = e % QK32;
+    const uint8_t qb = b[2 + (p & 15)];
+    out = __fmul_rn((float)((p < 16 ? (qb & 0x0f) : (qb >> 4)) - 8), h2f(ld16e(b)));
+  }
+  dst[e] = out;
+}
+
+// ---- step bookkeeping on the device so a captured graph can run token after
+// token without the host: state = {token, position, kv_tokens, step}
+__global__ void step_begin_kernel(int* state, int token, int position) {
+  state[0] = token;
+  state[1] = position;
+  state[2] = position + 1;
+  state[3] = 0;
+}
+__global__ void step_advance_kernel(int* state, const int* best_idx, int* tokens_out) {
+  const int t = *best_idx;
+  tokens_out[state[3]] = t;
+  state[0] = t;
+  state[1] += 1;
+  state[2] += 1;
+  state[3] += 1;
+}
+
+}  // namespace
+
+cudaError_t launch_rms_norm(const float* x, const float* w, float eps, int n, float* out, int family, ActPlanesMut planes,
+                            cudaStream_t st) {
+  const int threads = n >= 4096 ? 1024 : (n >= 1024 ? 256 : 128);
+  if (family == 1) rms_norm_kernel<1><<<1, threads, 0, st>>>(x, w, eps, n, out, planes);
+  else if (family == 2) rms_norm_kernel<2><<<1, threads, 0, st>>>(x, w, eps, n, out, planes);
+  else rms_norm_kernel<0><<<1, threads, 0, st>>>(x, w, eps, n, out, planes);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope_store(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t,
+                              const int* pos_dev, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
+                              __half* kcache, __half* vcache, int64_t cache_head_stride, cudaStream_t st) {
+  rope_store_kernel<<<n_head + n_head_kv, 64, 0, st>>>(q, k, v, cos_t, sin_t, pos_dev, n_head, n_head_kv, head_dim,
+                                                       rot_dim, neox, kcache, vcache, cache_head_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out, int family, ActPlanesMut planes,
+                          cudaStream_t st) {
+  if (family == 1) swiglu_kernel<1><<<(n / QK_K + 3) / 4, 128, 0, st>>>(gate, up, n, out, planes);
+  else if (family == 2) swiglu_kernel<2><<<(n / 4 + 127) / 128, 128, 0, st>>>(gate, up, n, out, planes);
+  else swiglu_kernel<0><<<(n / 4 + 127) / 128, 128, 0, st>>>(gate, up, n, out, planes);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, const int* token_dev, float* dst, int K,
+                             cudaStream_t st) {
+  embed_row_kernel<<<(K + 255) / 256, 256, 0, st>>>(type, table, row_bytes, token_dev, dst, K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_step_begin(int* state, int token, int position, cudaStream_t st) {
+  step_begin_kernel<<<1, 1, 0, st>>>(state, token, position);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out, cudaStream_t st) {
+  step_advance_kernel<<<1, 1, 0, st>>>(state, best_idx, tokens_out);
+  return cudaGetLastError();
+}
+
+}  // namespace emelb

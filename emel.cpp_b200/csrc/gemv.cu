@@ -15,10 +15,21 @@
 // own copies (cp.async.wait_group + __syncwarp), so up to STAGES-1 chunks per
 // warp stay in flight while a chunk is consumed.  Per chunk a lane owns 64
 // consecutive weights: it unpacks nibbles / 6-bit values in registers, runs
-// dp4a integer dots per 16/32-wide sub-block, applies the sub-block scales and
-// mins as integers and the block scales in f32, and the row sum is finished
-// with warp shuffles.  A task is R consecutive rows so that one activation
+// dp4a integer dots per 16/32-wide sub-block and applies the sub-block scales
+// and mins as integers.  A task is R consecutive rows so that one activation
 // register set serves R rows.
+//
+// Float order.  The integers of a block are exact whatever the order, so lanes
+// first reduce them per block; the f32 part then follows the reference's x86
+// route literally: one value per block — fma(d*dx, isum, -(dmin*dx)*msum) for
+// Q4_K, (d*dx)*isum for Q6_K, sumi*(dw*dx) for Q8_0/Q4_0 — added to the row sum
+// block after block in ascending order (dot_*_row_avx2_fma,
+// src/emel/kernel/x86_64/actions.hpp:876-896, 899-927, 999-1027, 1087-1107).
+// For the K-quants the 8 block values of a chunk are walked with shuffles; for
+// the 32-wide formats (64 blocks per chunk) they are parked in shared memory and
+// one lane per (row, column) walks them.  The result equals the reference's
+// AVX2 output bit for bit (and its scalar output for Q8_0/Q4_0, whose two routes
+// agree).
 #include "common.cuh"
 #include "kernels.h"
 
@@ -141,16 +152,23 @@ template <> struct WRegs<T_Q4_K> {
       m1 = (s[j1 + 4] >> 4) | ((s[j1] >> 6) << 4);
     }
   }
-  __device__ __forceinline__ float dot(const ARegs<T_Q4_K>& x) const {
+  // value of the lane's block (identical on its 4 lanes):
+  // fma(d_all, isum, -d_min * msum), src/emel/kernel/x86_64/actions.hpp:859-866
+  __device__ __forceinline__ float block_value(const ARegs<T_Q4_K>& x) const {
     int lo = 0, hi = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       lo = __dp4a((int)(q[i] & 0x0f0f0f0fu), x.a[i], lo);
       hi = __dp4a((int)((q[i] >> 4) & 0x0f0f0f0fu), x.a[8 + i], hi);
     }
-    const int isum = sc0 * lo + sc1 * hi;
-    const int msum = m0 * x.bs0 + m1 * x.bs1;
-    return (d * x.d) * (float)isum - (dmin * x.d) * (float)msum;
+    int isum = sc0 * lo + sc1 * hi;
+    int msum = m0 * x.bs0 + m1 * x.bs1;
+    isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+    msum += __shfl_xor_sync(0xffffffffu, msum, 1);
+    isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+    msum += __shfl_xor_sync(0xffffffffu, msum, 2);
+    const float d_all = __fmul_rn(x.d, d), d_min = __fmul_rn(x.d, dmin);
+    return __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, (float)msum));
   }
 };
 
@@ -182,7 +200,8 @@ template <> struct WRegs<T_Q6_K> {
     for (int g = 0; g < 4; ++g) sc[g] = s[2 * g];
     d = h2f(*reinterpret_cast<const uint16_t*>(sw + off + 208));
   }
-  __device__ __forceinline__ float dot(const ARegs<T_Q6_K>& x) const {
+  // (dx * d) * (isum - 32 * sum_mins), src/emel/kernel/x86_64/actions.hpp:1073-1077
+  __device__ __forceinline__ float block_value(const ARegs<T_Q6_K>& x) const {
     int isum = 0;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -191,7 +210,9 @@ template <> struct WRegs<T_Q6_K> {
       for (int i = 0; i < 4; ++i) s = __dp4a((int)v[4 * g + i], x.a[4 * g + i], s);
       isum += sc[g] * (s - 32 * x.bs[g]);
     }
-    return (d * x.d) * (float)isum;
+    isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+    isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+    return __fmul_rn(__fmul_rn(x.d, d), (float)isum);
   }
 };
 
@@ -214,14 +235,14 @@ template <> struct WRegs<T_Q8_0> {
     }
   }
   // per block: (float)sumi * (h(dw) * h(dx)), src/emel/kernel/detail.hpp:3257-3266
-  __device__ __forceinline__ float dot(const ARegs<T_Q8_0>& x) const {
+  __device__ __forceinline__ float2 block_values(const ARegs<T_Q8_0>& x) const {
     int s0 = 0, s1 = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       s0 = __dp4a(q0[i], x.a[i], s0);
       s1 = __dp4a(q1[i], x.a[8 + i], s1);
     }
-    return (float)s0 * (d0 * x.d0) + (float)s1 * (d1 * x.d1);
+    return make_float2(__fmul_rn((float)s0, __fmul_rn(d0, x.d0)), __fmul_rn((float)s1, __fmul_rn(d1, x.d1)));
   }
 };
 
@@ -245,7 +266,7 @@ template <> struct WRegs<T_Q4_0> {
       q1[i] = w[5 + i];
     }
   }
-  __device__ __forceinline__ float dot(const ARegs<T_Q4_0>& x) const {
+  __device__ __forceinline__ float2 block_values(const ARegs<T_Q4_0>& x) const {
     int s0 = 0, s1 = 0, t0 = 0, t1 = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -259,19 +280,30 @@ template <> struct WRegs<T_Q4_0> {
       t0 = __dp4a(0x01010101, x.a[i], t0);
       t1 = __dp4a(0x01010101, x.a[8 + i], t1);
     }
-    return (float)(s0 - 8 * t0) * (d0 * x.d0) + (float)(s1 - 8 * t1) * (d1 * x.d1);
+    return make_float2(__fmul_rn((float)(s0 - 8 * t0), __fmul_rn(d0, x.d0)),
+                       __fmul_rn((float)(s1 - 8 * t1), __fmul_rn(d1, x.d1)));
   }
 };
 
 // ---------------------------------------------------------------- streaming kernel
+constexpr int CHAIN_ROW = 68;  // 64 block values of a chunk + padding (bank spread)
+
+template <int T, int NCOLS, int R>
+__host__ __device__ constexpr int warp_smem_bytes(int stages) {
+  return stages * R * Geo<T>::CB + (is_k_type(T) ? 0 : R * NCOLS * CHAIN_ROW * 4);
+}
+
 template <int T, int NCOLS, int R, int STAGES, int WARPS, bool ARGMAX>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_stream_kernel(const GemvArgs p) {
   constexpr int CB = Geo<T>::CB;
   constexpr int V = CB / 16;  // 16-byte vectors per row chunk
+  constexpr bool KQ = is_k_type(T);
+  static_assert(KQ || R * NCOLS <= 32, "one lane per (row, column) walks the block values");
   extern __shared__ __align__(16) uint8_t smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint8_t* ring = smem + (size_t)warp * STAGES * R * CB;
+  uint8_t* ring = smem + (size_t)warp * warp_smem_bytes<T, NCOLS, R>(STAGES);
+  float* chain = reinterpret_cast<float*>(ring + STAGES * R * CB);
 
   const int nchunks = p.K / CHUNK;
   const int ntasks = (p.M + R - 1) / R;
@@ -297,7 +329,9 @@ gemv_stream_kernel(const GemvArgs p) {
     cp_async_commit();
   }
 
-  float acc[R][NCOLS];
+  // K-quants: every lane carries all R*NCOLS row sums (they stay identical across
+  // lanes); 32-wide formats: lane (r*NCOLS + j) carries the sum of (row r, column j)
+  float acc[KQ ? R : 1][KQ ? NCOLS : 1];
   float best = -INFINITY;
   int best_i = 0x7fffffff;
 
@@ -310,11 +344,25 @@ gemv_stream_kernel(const GemvArgs p) {
     const int ti = it / nchunks, c = it - ti * nchunks;
     if (c == 0) {
 #pragma unroll
-      for (int r = 0; r < R; ++r)
+      for (int r = 0; r < (KQ ? R : 1); ++r)
 #pragma unroll
-        for (int j = 0; j < NCOLS; ++j) acc[r][j] = 0.0f;
+        for (int j = 0; j < (KQ ? NCOLS : 1); ++j) acc[r][j] = 0.0f;
     }
     const uint8_t* st = ring + (size_t)(it % STAGES) * R * CB;
+
+    auto consume = [&](int r, int j, const WRegs<T>& w, const ARegs<T>& a) {
+      if constexpr (KQ) {
+        const float bv = w.block_value(a);
+        float s = acc[r][j];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) s = __fadd_rn(s, __shfl_sync(0xffffffffu, bv, 4 * b));
+        acc[r][j] = s;
+      } else {
+        const float2 bv = w.block_values(a);
+        *reinterpret_cast<float2*>(chain + (r * NCOLS + j) * CHAIN_ROW + 2 * lane) = bv;
+      }
+    };
+
     if constexpr (NCOLS == 1) {
       ARegs<T> a;
       a.load(p.act, p.col0, c, lane);
@@ -322,7 +370,7 @@ gemv_stream_kernel(const GemvArgs p) {
       for (int r = 0; r < R; ++r) {
         WRegs<T> w;
         w.load(st + r * CB, lane);
-        acc[r][0] += w.dot(a);
+        consume(r, 0, w, a);
       }
     } else {
 #pragma unroll
@@ -333,27 +381,56 @@ gemv_stream_kernel(const GemvArgs p) {
         for (int j = 0; j < NCOLS; ++j) {
           ARegs<T> a;
           a.load(p.act, p.col0 + j, c, lane);
-          acc[r][j] += w.dot(a);
+          consume(r, j, w, a);
         }
       }
     }
-    __syncwarp();  // every lane is done with this stage before it is refilled
+    __syncwarp();  // stage fully read (and, for the 32-wide formats, block values parked)
+    if constexpr (!KQ) {
+      if (lane < R * NCOLS) {
+        const float4* cv = reinterpret_cast<const float4*>(chain + lane * CHAIN_ROW);
+        float s = acc[0][0];
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+          const float4 v = cv[b];
+          s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, v.x), v.y), v.z), v.w);
+        }
+        acc[0][0] = s;
+      }
+      __syncwarp();
+    }
 
     if (c == nchunks - 1) {
       const int row0 = (wg + ti * tw) * R;
+      if constexpr (KQ) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
+        for (int r = 0; r < R; ++r) {
 #pragma unroll
-        for (int j = 0; j < NCOLS; ++j) {
-          const float v = warp_sum(acc[r][j]);
-          const int row = row0 + r;
+          for (int j = 0; j < NCOLS; ++j) {
+            const float v = acc[r][j];
+            const int row = row0 + r;
+            if (row < p.M) {
+              if constexpr (ARGMAX) {
+                // ascending rows inside a warp; strict > keeps the lowest row on ties
+                if (v > best || best_i == 0x7fffffff) { best = v; best_i = row; }
+              } else if (lane == 0) {
+                const size_t o = (size_t)row * p.ldy + p.col0 + j;
+                p.y[o] = p.residual ? __fadd_rn(p.residual[o], v) : v;
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < R * NCOLS; ++q) {
+          const float v = __shfl_sync(0xffffffffu, acc[0][0], q);
+          const int row = row0 + q / NCOLS, j = q % NCOLS;
           if (row < p.M) {
             if constexpr (ARGMAX) {
-              // ascending rows inside a warp; strict > keeps the lowest row on ties
               if (v > best || best_i == 0x7fffffff) { best = v; best_i = row; }
             } else if (lane == 0) {
               const size_t o = (size_t)row * p.ldy + p.col0 + j;
-              p.y[o] = p.residual ? p.residual[o] + v : v;
+              p.y[o] = p.residual ? __fadd_rn(p.residual[o], v) : v;
             }
           }
         }
@@ -402,6 +479,28 @@ __global__ void argmax_finish_kernel(const float* pv, const int* pi, int n, floa
   if (threadIdx.x == 0) { *out_val = sv[0]; *out_idx = si[0]; }
 }
 
+// greedy id over materialised logits: maximum value, lowest index on ties
+__global__ void argmax_f32_kernel(const float* x, int n, float* out_val, int* out_idx) {
+  __shared__ float sv[1024];
+  __shared__ int si[1024];
+  float bv = -INFINITY; int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = x[i];
+    if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; }
+  }
+  sv[threadIdx.x] = bv; si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float v = sv[threadIdx.x + s]; const int r = si[threadIdx.x + s];
+      const float cv = sv[threadIdx.x]; const int cr = si[threadIdx.x];
+      if (r != 0x7fffffff && (cr == 0x7fffffff || v > cv || (v == cv && r < cr))) { sv[threadIdx.x] = v; si[threadIdx.x] = r; }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { *out_val = sv[0]; *out_idx = si[0]; }
+}
+
 // ---------------------------------------------------------------- generic kernel
 // Any K that is a multiple of the block size, any 2-byte-aligned base: one warp
 // per row, lanes stride over blocks, byte loads.  Used for shapes the streaming
@@ -431,7 +530,7 @@ __device__ float generic_block_dot(const uint8_t* blk, const ActPlanes& act, int
       msum += scale_min_k4_m(j, s) * ((int)bs[2 * j] + (int)bs[2 * j + 1]);
     }
     const float dx = act.d[col * act.col_stride_d + ib];
-    return (d * dx) * (float)isum - (dmin * dx) * (float)msum;
+    return __fmaf_rn(__fmul_rn(dx, d), (float)isum, -__fmul_rn(__fmul_rn(dx, dmin), (float)msum));
   } else if constexpr (T == T_Q6_K) {
     const uint8_t* ql = blk; const uint8_t* qh = blk + 128;
     const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192);
@@ -450,12 +549,12 @@ __device__ float generic_block_dot(const uint8_t* blk, const ActPlanes& act, int
         isum += (int)sc[8 * n + is + 6] * q4 * (int)a[128 * n + l + 96];
       }
     }
-    return (d * act.d[col * act.col_stride_d + ib]) * (float)isum;
+    return __fmul_rn(__fmul_rn(act.d[col * act.col_stride_d + ib], d), (float)isum);
   } else if constexpr (T == T_Q8_0) {
     const int8_t* q = reinterpret_cast<const int8_t*>(blk + 2);
     int s = 0;
     for (int l = 0; l < 32; ++l) s += (int)q[l] * (int)a[l];
-    return (float)s * (h2f(ld16(blk)) * act.d[col * act.col_stride_d + ib]);
+    return __fmul_rn((float)s, __fmul_rn(h2f(ld16(blk)), act.d[col * act.col_stride_d + ib]));
   } else {
     const uint8_t* q = blk + 2;
     int s = 0;
@@ -463,7 +562,7 @@ __device__ float generic_block_dot(const uint8_t* blk, const ActPlanes& act, int
       s += ((int)(q[l] & 0x0f) - 8) * (int)a[l];
       s += ((int)(q[l] >> 4) - 8) * (int)a[l + 16];
     }
-    return (float)s * (h2f(ld16(blk)) * act.d[col * act.col_stride_d + ib]);
+    return __fmul_rn((float)s, __fmul_rn(h2f(ld16(blk)), act.d[col * act.col_stride_d + ib]));
   }
 }
 
@@ -476,13 +575,18 @@ __global__ void __launch_bounds__(128) gemv_generic_kernel(const GemvArgs p, int
     const uint8_t* wrow = p.W + (size_t)row * p.row_bytes;
     for (int j = 0; j < ncols; ++j) {
       float acc = 0.0f;
-      for (int ib = lane; ib < nblk; ib += 32) acc += generic_block_dot<T>(wrow + (size_t)ib * block_bytes(T), p.act, p.col0 + j, ib);
-      acc = warp_sum(acc);
+      // 32 block values at a time, added in ascending block order
+      for (int base = 0; base < nblk; base += 32) {
+        const int ib = base + lane;
+        const float bv = ib < nblk ? generic_block_dot<T>(wrow + (size_t)ib * block_bytes(T), p.act, p.col0 + j, ib) : 0.0f;
+        const int cnt = min(32, nblk - base);
+        for (int i = 0; i < cnt; ++i) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, bv, i));
+      }
       if constexpr (ARGMAX) {
         if (acc > best || best_i == 0x7fffffff) { best = acc; best_i = row; }
       } else if (lane == 0) {
         const size_t o = (size_t)row * p.ldy + p.col0 + j;
-        p.y[o] = p.residual ? p.residual[o] + acc : acc;
+        p.y[o] = p.residual ? __fadd_rn(p.residual[o], acc) : acc;
       }
     }
   }
@@ -507,14 +611,15 @@ constexpr int kStages = 3;
 
 template <int T, int NCOLS, int R, bool ARGMAX>
 cudaError_t launch_stream(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
-  constexpr int CB = Geo<T>::CB;
-  constexpr size_t smem = (size_t)kWarps * kStages * R * CB;
+  constexpr size_t smem = (size_t)kWarps * warp_smem_bytes<T, NCOLS, R>(kStages);
   auto kern = gemv_stream_kernel<T, NCOLS, R, kStages, kWarps, ARGMAX>;
-  static bool configured = false;  // per instantiation; attribute is per function
-  if (!configured) {
+  static unsigned configured = 0;  // per instantiation, one bit per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(configured & (1u << (dev & 31)))) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured |= 1u << (dev & 31);
   }
   const int ntasks = (a.M + R - 1) / R;
   const int per_sm = (int)((220 * 1024) / smem) > 0 ? (int)((220 * 1024) / smem) : 1;
@@ -574,6 +679,11 @@ cudaError_t launch_type(GemvArgs a, int ncols, bool argmax, bool fast, int sm_co
 }
 
 }  // namespace
+
+cudaError_t launch_argmax_f32(const float* x, int n, float* out_val, int* out_idx, cudaStream_t st) {
+  argmax_f32_kernel<<<1, 1024, 0, st>>>(x, n, out_val, out_idx);
+  return cudaGetLastError();
+}
 
 bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K) {
   (void)type;

@@ -32,6 +32,8 @@ bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K);
 cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
                         int* launches);
 
+cudaError_t launch_argmax_f32(const float* x, int n, float* out_val, int* out_idx, cudaStream_t st);
+
 // quantize.cu — built with -fmad=false: every float op rounds as written
 struct ActPlanesMut {
   int8_t* qs;
@@ -49,6 +51,21 @@ cudaError_t launch_blocks_to_planes(int type, const uint8_t* blocks, int K, ActP
 // src rows of native blocks -> f32 rows
 cudaError_t launch_dequantize(int type, const uint8_t* src, int64_t src_row_bytes, float* dst, int64_t dst_row_elems,
                               int K, int M, cudaStream_t st);
+
+// elementwise.cu — the steps between the matrix products of a decoder layer
+// family: 0 = f32 output only, 1 = also Q8_K planes, 2 = also Q8_0 planes
+cudaError_t launch_rms_norm(const float* x, const float* w, float eps, int n, float* out, int family, ActPlanesMut planes,
+                            cudaStream_t st);
+cudaError_t launch_rope_store(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t,
+                              const int* pos_dev, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
+                              __half* kcache, __half* vcache, int64_t cache_head_stride, cudaStream_t st);
+cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out, int family, ActPlanesMut planes,
+                          cudaStream_t st);
+cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, const int* token_dev, float* dst, int K,
+                             cudaStream_t st);
+// state = {token, position, kv_tokens, step}
+cudaError_t launch_step_begin(int* state, int token, int position, cudaStream_t st);
+cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out, cudaStream_t st);
 
 // synth.cu — synthetic N(0, sigma) data generated and block-encoded on the device
 cudaError_t launch_fill_normal(float* out, uint64_t n, uint64_t seed, float sigma, uint64_t offset, cudaStream_t st);
@@ -71,8 +88,9 @@ struct FlashArgs {
   float* part_ml;        // [H][splits][2]  (running max, running sum)
 };
 cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches);
-// score_ws: [heads][t_stride] f32 scratch
-cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, cudaStream_t st, int* launches);
+// score_ws: [heads][t_stride] f32 scratch; order 1 = scalar route, 2 = x86 AVX2 route
+cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, int order, cudaStream_t st,
+                                         int* launches);
 // true when the split-KV kernel takes this request (head_dim 64/128, 16-byte aligned rows)
 bool flash_split_supported(const FlashArgs& a);
 int flash_pick_splits(int tokens, int kv_heads, int sm_count, int max_splits);

@@ -1,0 +1,463 @@
+// Device-resident decode loop (include/emelb_llama.h): the reference
+// generator's per-token call sequence restated over this library's kernels.
+//   run_decode                         src/emel/text/generator/detail.hpp:4860-4914
+//   compute_layer_attention_residual   :3746-3840
+//   compute_layer_feed_forward         :3852-3926
+//   compute_logits                     :3997-4033
+// One token step is a fixed chain of kernels whose token id, position and KV
+// length live in device memory, so the chain is captured once as a CUDA graph
+// and replayed per token.
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/emelb_llama.h"
+#include "ctx.h"
+
+using namespace emelb;
+
+namespace emelb {
+const void* ctx_resolve_weights(emelb_ctx* c, const void* p);  // api.cu
+bool ctx_cuda_ok(emelb_ctx* c, cudaError_t e);
+#if defined(EMELB_HAVE_NCCL)
+cudaError_t comm_all_gather_inplace(emelb_ctx* c, float* buf, size_t count_per_rank, cudaStream_t st);  // comm.cu
+#endif
+}  // namespace emelb
+
+namespace {
+
+struct Tensor {
+  const uint8_t* dev = nullptr;
+  int type = EMELB_UNKNOWN;
+  int64_t row_bytes = 0;
+  int K = 0, M = 0;
+};
+
+struct Layer {
+  Tensor attn_norm, wq, wk, wv, wo, ffn_norm, gate, up, down;
+};
+
+enum Mode { MODE_PREFILL = 0, MODE_LOGITS = 1, MODE_ARGMAX = 2, MODE_COUNT = 3 };
+
+int family_of(int type) { return is_k_type(type) ? 1 : 2; }
+
+}  // namespace
+
+struct emelb_llama {
+  emelb_ctx* c = nullptr;
+  emelb_llama_config cfg{};
+  std::vector<Layer> layers;
+  Tensor tok_embd, out_norm, output;
+  int64_t capacity = 0;
+  // activations (f32, device)
+  float *hidden = nullptr, *norm = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr;
+  float *gate = nullptr, *up = nullptr, *ffn = nullptr, *logits = nullptr;
+  __half *kcache = nullptr, *vcache = nullptr;
+  float *rope_cos = nullptr, *rope_sin = nullptr;
+  int* state = nullptr;       // {token, position, kv_tokens, step}
+  int* tokens_dev = nullptr;  // generated ids (n_ctx)
+  int* host_pinned = nullptr;
+  int fa_splits = 1;
+  cudaGraphExec_t graphs[MODE_COUNT] = {nullptr, nullptr, nullptr};
+  int graph_attention_mode[MODE_COUNT] = {-1, -1, -1};
+  int launches_per_token = 0;          // of the argmax step
+  int launches_mode[MODE_COUNT] = {0, 0, 0};
+  // which f32 vector the context's activation planes currently hold, and for which family
+  const float* planes_src = nullptr;
+  int planes_family = 0;
+  std::vector<void*> owned;
+};
+
+namespace {
+
+bool dev_alloc(emelb_llama* s, void** p, size_t bytes) {
+  if (cudaMalloc(p, (bytes + 255) & ~size_t(255)) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  s->owned.push_back(*p);
+  return true;
+}
+
+bool bound(const Tensor& t) { return t.dev != nullptr; }
+
+bool all_bound(const emelb_llama* s) {
+  if (!bound(s->tok_embd) || !bound(s->out_norm) || !bound(s->output)) return false;
+  for (const Layer& l : s->layers)
+    if (!(bound(l.attn_norm) && bound(l.wq) && bound(l.wk) && bound(l.wv) && bound(l.wo) && bound(l.ffn_norm) &&
+          bound(l.gate) && bound(l.up) && bound(l.down)))
+      return false;
+  return true;
+}
+
+struct Enqueue {
+  emelb_llama* s;
+  cudaStream_t st;
+  int launches = 0;
+  bool ok = true;
+
+  void check(cudaError_t e) { ok = ok && ctx_cuda_ok(s->c, e); }
+
+  ActPlanesMut planes() const { return ActPlanesMut{s->c->act_qs, s->c->act_d, s->c->act_bsums}; }
+
+  // make the context's planes hold `src` (K f32) quantized for `family`
+  void ensure_planes(const float* src, int K, int family) {
+    if (s->planes_src == src && s->planes_family == family) return;
+    check(quantize_into_planes(family == 1 ? T_Q4_K : T_Q8_0, src, 1, 1, K, planes(), st));
+    ++launches;
+    s->planes_src = src;
+    s->planes_family = family;
+  }
+
+  void matvec(const Tensor& w, const float* x, float* y, const float* residual, bool argmax = false) {
+    ensure_planes(x, w.K, family_of(w.type));
+    GemvArgs a{};
+    a.W = w.dev;
+    a.row_bytes = w.row_bytes;
+    a.M = w.M;
+    a.K = w.K;
+    a.act = planes_view(planes(), w.type, w.K);
+    a.col0 = 0;
+    a.y = y;
+    a.ldy = 1;
+    a.residual = residual;
+    a.part_val = s->c->part_val;
+    a.part_idx = s->c->part_idx;
+    a.best_val = s->c->best_val;
+    a.best_idx = s->c->best_idx;
+    check(launch_gemv(w.type, a, 1, argmax, s->c->sm_count, st, &launches));
+  }
+
+  void rms_norm(const float* x, const Tensor& w, int family) {
+    check(launch_rms_norm(x, reinterpret_cast<const float*>(w.dev), s->cfg.rms_eps, s->cfg.n_embd, s->norm, family,
+                          planes(), st));
+    ++launches;
+    s->planes_src = s->norm;
+    s->planes_family = family;
+  }
+
+  void attention(int layer) {
+    const emelb_llama_config& c = s->cfg;
+    const int64_t layer_off = (int64_t)layer * c.n_head_kv * s->capacity * c.head_dim;
+    FlashArgs a{};
+    a.q = s->q;
+    a.k = s->kcache + layer_off;
+    a.v = s->vcache + layer_off;
+    a.dst = s->attn;
+    a.k_nb1 = a.v_nb1 = 2 * c.head_dim;
+    a.k_nb2 = a.v_nb2 = 2 * s->capacity * c.head_dim;
+    a.head_dim = c.head_dim;
+    a.heads = c.n_head;
+    a.kv_heads = c.n_head_kv;
+    a.tokens = c.n_ctx;            // upper bound; the live count is read on the device
+    a.tokens_dev = s->state + 2;
+    a.scale = 1.0f / std::sqrt((float)c.head_dim);
+    a.splits = s->fa_splits;
+    a.part_acc = s->c->fa_part_acc;
+    a.part_ml = s->c->fa_part_ml;
+    if (s->c->attention_mode == 0 && flash_split_supported(a)) {
+      check(launch_flash_decode(a, s->c->sm_count, st, &launches));
+    } else {
+      check(launch_flash_reference_order(a, s->c->fa_scores, c.n_ctx, s->c->attention_mode == 1 ? 1 : 2, st, &launches));
+    }
+  }
+
+  void token_step(Mode mode) {
+    const emelb_llama_config& c = s->cfg;
+    s->planes_src = nullptr;
+    check(launch_embed_row(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->state, s->hidden, c.n_embd, st));
+    ++launches;
+    for (int l = 0; l < c.n_layer; ++l) {
+      const Layer& w = s->layers[l];
+      rms_norm(s->hidden, w.attn_norm, family_of(w.wq.type));
+      matvec(w.wq, s->norm, s->q, nullptr);
+      matvec(w.wk, s->norm, s->k, nullptr);
+      matvec(w.wv, s->norm, s->v, nullptr);
+      const int64_t layer_off = (int64_t)l * c.n_head_kv * s->capacity * c.head_dim;
+      check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, c.n_head, c.n_head_kv, c.head_dim,
+                              c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
+                              s->vcache + layer_off, s->capacity * c.head_dim, st));
+      ++launches;
+      attention(l);
+      matvec(w.wo, s->attn, s->hidden, s->hidden);   // hidden += Wo * attn
+      rms_norm(s->hidden, w.ffn_norm, family_of(w.gate.type));
+      matvec(w.gate, s->norm, s->gate, nullptr);
+      matvec(w.up, s->norm, s->up, nullptr);
+      check(launch_swiglu(s->gate, s->up, c.n_ff, s->ffn, family_of(w.down.type), planes(), st));
+      ++launches;
+      s->planes_src = s->ffn;
+      s->planes_family = family_of(w.down.type);
+      matvec(w.down, s->ffn, s->hidden, s->hidden);  // hidden += Wdown * ffn
+    }
+    if (mode == MODE_PREFILL) return;
+    rms_norm(s->hidden, s->out_norm, family_of(s->output.type));
+    if (mode == MODE_ARGMAX) {
+      matvec(s->output, s->norm, nullptr, nullptr, true);
+      check(launch_step_advance(s->state, s->c->best_idx, s->tokens_dev, st));
+      ++launches;
+    } else {
+      matvec(s->output, s->norm, s->logits, nullptr);
+    }
+  }
+};
+
+// capture (once per mode and attention mode) and return the replayable step
+cudaGraphExec_t step_graph(emelb_llama* s, Mode mode) {
+  if (s->graphs[mode] && s->graph_attention_mode[mode] == s->c->attention_mode) return s->graphs[mode];
+  if (s->graphs[mode]) {
+    cudaStreamSynchronize(s->c->stream);
+    cudaGraphExecDestroy(s->graphs[mode]);
+    s->graphs[mode] = nullptr;
+  }
+  // one eager pass first: sets per-kernel attributes outside the capture
+  Enqueue warm{s, s->c->stream};
+  warm.token_step(mode);
+  if (!warm.ok || !ctx_cuda_ok(s->c, cudaStreamSynchronize(s->c->stream))) return nullptr;
+  if (!ctx_cuda_ok(s->c, cudaStreamBeginCapture(s->c->stream, cudaStreamCaptureModeThreadLocal))) return nullptr;
+  Enqueue e{s, s->c->stream};
+  e.token_step(mode);
+  cudaGraph_t g = nullptr;
+  const bool ended = ctx_cuda_ok(s->c, cudaStreamEndCapture(s->c->stream, &g));
+  if (!ended || !e.ok || !g) {
+    if (g) cudaGraphDestroy(g);
+    return nullptr;
+  }
+  cudaGraphExec_t ex = nullptr;
+  const bool inst = ctx_cuda_ok(s->c, cudaGraphInstantiate(&ex, g, 0));
+  cudaGraphDestroy(g);
+  if (!inst) return nullptr;
+  s->graphs[mode] = ex;
+  s->graph_attention_mode[mode] = s->c->attention_mode;
+  s->launches_mode[mode] = e.launches;
+  if (mode == MODE_ARGMAX) s->launches_per_token = e.launches;
+  return ex;
+}
+
+bool valid_step(const emelb_llama* s, int token, int position) {
+  return token >= 0 && token < s->cfg.n_vocab && position >= 0 && position < s->cfg.n_ctx;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_llama** out) {
+  if (!c || !cfg || !out) return EMELB_INVALID_REQUEST;
+  *out = nullptr;
+  const emelb_llama_config& g = *cfg;
+  const bool sane = g.n_layer > 0 && g.n_embd > 0 && g.n_embd % 256 == 0 && g.n_head > 0 && g.n_head_kv > 0 &&
+                    g.n_head % g.n_head_kv == 0 && g.head_dim > 1 && g.n_ff > 0 && g.n_ff % 256 == 0 && g.n_vocab > 0 &&
+                    g.n_ctx > 0 && g.rope_dim > 1 && g.rope_dim % 2 == 0 && g.shard_count >= 1 && g.shard_rank >= 0 &&
+                    g.shard_rank < g.shard_count && (int64_t)g.n_head * g.head_dim <= (int64_t)c->act_capacity &&
+                    (int64_t)g.n_ff <= (int64_t)c->act_capacity;
+  if (!sane) return EMELB_INVALID_REQUEST;
+  if (g.shard_count != 1) return EMELB_UNSUPPORTED_OP;
+  cudaSetDevice(c->device);
+  emelb_llama* s = new (std::nothrow) emelb_llama();
+  if (!s) return EMELB_INTERNAL_ERROR;
+  s->c = c;
+  s->cfg = g;
+  s->layers.resize(g.n_layer);
+  const int kvb = g.kv_block > 0 ? g.kv_block : 16;
+  s->capacity = ((int64_t)g.n_ctx + kvb - 1) / kvb * kvb;
+  const size_t qd = (size_t)g.n_head * g.head_dim, kvd = (size_t)g.n_head_kv * g.head_dim;
+  const size_t cache_halves = (size_t)g.n_layer * g.n_head_kv * s->capacity * g.head_dim;
+  const int pairs = (g.rope_dim < g.head_dim ? g.rope_dim : g.head_dim) / 2;
+  bool ok = true;
+  ok = ok && dev_alloc(s, (void**)&s->hidden, 4 * (size_t)g.n_embd);
+  ok = ok && dev_alloc(s, (void**)&s->norm, 4 * (size_t)g.n_embd);
+  ok = ok && dev_alloc(s, (void**)&s->q, 4 * qd);
+  ok = ok && dev_alloc(s, (void**)&s->k, 4 * kvd);
+  ok = ok && dev_alloc(s, (void**)&s->v, 4 * kvd);
+  ok = ok && dev_alloc(s, (void**)&s->attn, 4 * qd);
+  ok = ok && dev_alloc(s, (void**)&s->gate, 4 * (size_t)g.n_ff);
+  ok = ok && dev_alloc(s, (void**)&s->up, 4 * (size_t)g.n_ff);
+  ok = ok && dev_alloc(s, (void**)&s->ffn, 4 * (size_t)g.n_ff);
+  ok = ok && dev_alloc(s, (void**)&s->logits, 4 * (size_t)g.n_vocab);
+  ok = ok && dev_alloc(s, (void**)&s->kcache, 2 * cache_halves);
+  ok = ok && dev_alloc(s, (void**)&s->vcache, 2 * cache_halves);
+  ok = ok && dev_alloc(s, (void**)&s->rope_cos, 4 * (size_t)g.n_ctx * pairs);
+  ok = ok && dev_alloc(s, (void**)&s->rope_sin, 4 * (size_t)g.n_ctx * pairs);
+  ok = ok && dev_alloc(s, (void**)&s->state, 4 * sizeof(int));
+  ok = ok && dev_alloc(s, (void**)&s->tokens_dev, sizeof(int) * (size_t)(g.n_ctx + 8));
+  ok = ok && cudaMallocHost((void**)&s->host_pinned, sizeof(int) * (size_t)(g.n_ctx + 4)) == cudaSuccess;
+  if (ok) {
+    ok = cudaMemsetAsync(s->kcache, 0, 2 * cache_halves, c->stream) == cudaSuccess &&
+         cudaMemsetAsync(s->vcache, 0, 2 * cache_halves, c->stream) == cudaSuccess &&
+         cudaMemsetAsync(s->state, 0, 4 * sizeof(int), c->stream) == cudaSuccess;
+  }
+  if (ok) {
+    // cos/sin of theta_p = position * base^(-2p/rot) built with the host libm and the
+    // same recurrence as apply_rope_pairing (:2918-2934), so the table holds
+    // exactly the floats the reference multiplies by
+    std::vector<float> hc((size_t)g.n_ctx * pairs), hs((size_t)g.n_ctx * pairs);
+    const float theta_scale = ::powf(g.rope_freq_base, -2.0f / (float)(2 * pairs));
+    for (int pos = 0; pos < g.n_ctx; ++pos) {
+      float theta = (float)pos;
+      for (int p = 0; p < pairs; ++p) {
+        hc[(size_t)pos * pairs + p] = ::cosf(theta);
+        hs[(size_t)pos * pairs + p] = ::sinf(theta);
+        theta *= theta_scale;
+      }
+    }
+    ok = cudaMemcpyAsync(s->rope_cos, hc.data(), hc.size() * 4, cudaMemcpyHostToDevice, c->stream) == cudaSuccess &&
+         cudaMemcpyAsync(s->rope_sin, hs.data(), hs.size() * 4, cudaMemcpyHostToDevice, c->stream) == cudaSuccess &&
+         cudaStreamSynchronize(c->stream) == cudaSuccess;
+  }
+  if (ok) {
+    int max_splits = (int)(kFlashPartFloats / ((uint64_t)g.n_head * g.head_dim));
+    if (max_splits > 64) max_splits = 64;
+    s->fa_splits = max_splits >= 1 ? flash_pick_splits(g.n_ctx, g.n_head_kv, c->sm_count, max_splits) : 1;
+    ok = (uint64_t)g.n_head * (uint64_t)g.n_ctx <= kFlashScoreFloats;
+  }
+  if (!ok) {
+    cudaGetLastError();
+    emelb_llama_destroy(s);
+    return EMELB_INTERNAL_ERROR;
+  }
+  *out = s;
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_destroy(emelb_llama* s) {
+  if (!s) return EMELB_INVALID_REQUEST;
+  cudaSetDevice(s->c->device);
+  cudaStreamSynchronize(s->c->stream);
+  for (auto& g : s->graphs)
+    if (g) cudaGraphExecDestroy(g);
+  for (void* p : s->owned) cudaFree(p);
+  if (s->host_pinned) cudaFreeHost(s->host_pinned);
+  cudaGetLastError();
+  delete s;
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_bind(emelb_llama* s, int32_t layer, int32_t role, const emelb_view* t) {
+  if (!s || !t || !t->data) return EMELB_INVALID_REQUEST;
+  const emelb_llama_config& c = s->cfg;
+  const bool model_level = role <= EMELB_T_OUTPUT;
+  if (role < 0 || role > EMELB_T_FFN_DOWN || (model_level ? layer != -1 : (layer < 0 || layer >= c.n_layer)))
+    return EMELB_INVALID_REQUEST;
+  const int qd = c.n_head * c.head_dim, kvd = c.n_head_kv * c.head_dim;
+  int K = 0, M = 0;
+  bool vector = false;
+  switch (role) {
+    case EMELB_T_TOKEN_EMBD: K = c.n_embd; M = c.n_vocab; break;
+    case EMELB_T_OUTPUT: K = c.n_embd; M = c.n_vocab; break;
+    case EMELB_T_OUTPUT_NORM: case EMELB_T_ATTN_NORM: case EMELB_T_FFN_NORM: K = c.n_embd; M = 1; vector = true; break;
+    case EMELB_T_ATTN_Q: K = c.n_embd; M = qd; break;
+    case EMELB_T_ATTN_K: case EMELB_T_ATTN_V: K = c.n_embd; M = kvd; break;
+    case EMELB_T_ATTN_OUT: K = qd; M = c.n_embd; break;
+    case EMELB_T_FFN_GATE: case EMELB_T_FFN_UP: K = c.n_embd; M = c.n_ff; break;
+    case EMELB_T_FFN_DOWN: K = c.n_ff; M = c.n_embd; break;
+  }
+  Tensor x;
+  x.type = t->type;
+  x.K = K;
+  x.M = M;
+  if ((int64_t)t->ne[0] != K || (int64_t)t->ne[1] != M) return EMELB_INVALID_REQUEST;
+  if (vector) {
+    if (t->type != EMELB_F32) return EMELB_INVALID_REQUEST;
+    x.row_bytes = 4 * (int64_t)K;
+  } else if (role == EMELB_T_TOKEN_EMBD && (t->type == EMELB_F32 || t->type == EMELB_F16)) {
+    x.row_bytes = (t->type == EMELB_F32 ? 4 : 2) * (int64_t)K;
+    if ((int64_t)t->nb[1] != x.row_bytes) return EMELB_INVALID_REQUEST;
+  } else {
+    const int be = block_elems(t->type);
+    if (be == 0 || t->type == EMELB_Q8_K || K % be != 0) return EMELB_INVALID_REQUEST;
+    const int lim = is_k_type(t->type) ? MAX_Q8_K_BLOCKS : MAX_Q8_0_BLOCKS;
+    x.row_bytes = (int64_t)(K / be) * block_bytes(t->type);
+    if (role != EMELB_T_TOKEN_EMBD && K / be > lim) return EMELB_INVALID_REQUEST;
+    if ((int64_t)t->nb[1] != x.row_bytes || t->nb[0] != 1) return EMELB_INVALID_REQUEST;
+  }
+  x.dev = static_cast<const uint8_t*>(ctx_resolve_weights(s->c, t->data));
+  if (!x.dev) return EMELB_INVALID_REQUEST;
+  Tensor* slot = nullptr;
+  if (model_level) slot = role == EMELB_T_TOKEN_EMBD ? &s->tok_embd : (role == EMELB_T_OUTPUT_NORM ? &s->out_norm : &s->output);
+  else {
+    Layer& l = s->layers[layer];
+    Tensor* slots[] = {&l.attn_norm, &l.wq, &l.wk, &l.wv, &l.wo, &l.ffn_norm, &l.gate, &l.up, &l.down};
+    slot = slots[role - EMELB_T_ATTN_NORM];
+  }
+  *slot = x;
+  // bindings changed: captured steps hold stale pointers
+  for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t position, float* logits_out, int32_t* token_out) {
+  if (!s || !valid_step(s, token, position) || !all_bound(s)) return EMELB_INVALID_REQUEST;
+  emelb_ctx* c = s->c;
+  cudaSetDevice(c->device);
+  const Mode mode = logits_out ? MODE_LOGITS : MODE_ARGMAX;
+  cudaGraphExec_t g = step_graph(s, mode);
+  if (!g) return EMELB_INTERNAL_ERROR;
+  bool ok = ctx_cuda_ok(c, launch_step_begin(s->state, token, position, c->stream));
+  ok = ok && ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+  c->diag.kernel_launches += 1 + s->launches_mode[mode];
+  if (ok && logits_out) {
+    cudaPointerAttributes at{};
+    const bool dev = cudaPointerGetAttributes(&at, logits_out) == cudaSuccess && at.type == cudaMemoryTypeDevice;
+    cudaGetLastError();
+    ok = ctx_cuda_ok(c, cudaMemcpyAsync(logits_out, s->logits, 4 * (size_t)s->cfg.n_vocab,
+                                        dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, c->stream));
+    if (!dev) c->diag.d2h_bytes += 4 * (uint64_t)s->cfg.n_vocab;
+    if (ok && token_out) {
+      ok = ctx_cuda_ok(c, launch_argmax_f32(s->logits, s->cfg.n_vocab, c->best_val, c->best_idx, c->stream));
+      c->diag.kernel_launches += 1;
+      ok = ok && ctx_cuda_ok(c, cudaMemcpyAsync(s->host_pinned, c->best_idx, 4, cudaMemcpyDeviceToHost, c->stream));
+      c->diag.d2h_bytes += 4;
+    }
+  } else if (ok && token_out) {
+    ok = ctx_cuda_ok(c, cudaMemcpyAsync(s->host_pinned, c->best_idx, 4, cudaMemcpyDeviceToHost, c->stream));
+    c->diag.d2h_bytes += 4;
+  }
+  ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
+  if (ok && token_out) *token_out = s->host_pinned[0];
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n, int32_t start_pos) {
+  if (!s || !tokens || n <= 0 || !all_bound(s) || start_pos < 0 || start_pos + n > s->cfg.n_ctx) return EMELB_INVALID_REQUEST;
+  for (int i = 0; i < n; ++i)
+    if (!valid_step(s, tokens[i], start_pos + i)) return EMELB_INVALID_REQUEST;
+  emelb_ctx* c = s->c;
+  cudaSetDevice(c->device);
+  cudaGraphExec_t g = step_graph(s, MODE_PREFILL);
+  if (!g) return EMELB_INTERNAL_ERROR;
+  bool ok = true;
+  for (int i = 0; ok && i < n; ++i) {
+    ok = ctx_cuda_ok(c, launch_step_begin(s->state, tokens[i], start_pos + i, c->stream));
+    ok = ok && ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+  }
+  c->diag.kernel_launches += (uint64_t)n * (1 + s->launches_mode[MODE_PREFILL]);
+  ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token, int32_t start_pos, int32_t n, int32_t* tokens_out) {
+  if (!s || !tokens_out || n <= 0 || !all_bound(s) || !valid_step(s, first_token, start_pos) || start_pos + n > s->cfg.n_ctx)
+    return EMELB_INVALID_REQUEST;
+  emelb_ctx* c = s->c;
+  cudaSetDevice(c->device);
+  cudaGraphExec_t g = step_graph(s, MODE_ARGMAX);
+  if (!g) return EMELB_INTERNAL_ERROR;
+  bool ok = ctx_cuda_ok(c, launch_step_begin(s->state, first_token, start_pos, c->stream));
+  for (int i = 0; ok && i < n; ++i) ok = ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+  c->diag.kernel_launches += 1 + (uint64_t)n * s->launches_per_token;
+  ok = ok && ctx_cuda_ok(c, cudaMemcpyAsync(s->host_pinned, s->tokens_dev, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, c->stream));
+  ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
+  if (!ok) return EMELB_INTERNAL_ERROR;
+  c->diag.d2h_bytes += sizeof(int) * (uint64_t)n;
+  std::memcpy(tokens_out, s->host_pinned, sizeof(int) * (size_t)n);
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_launches_per_token(const emelb_llama* s, int32_t* out) {
+  if (!s || !out) return EMELB_INVALID_REQUEST;
+  *out = s->launches_per_token;
+  return EMELB_OK;
+}
+
+}  // extern "C"

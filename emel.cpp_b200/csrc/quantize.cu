@@ -5,21 +5,13 @@
 //   quantize_row_q8_k_strided   src/emel/kernel/detail.hpp:826-867
 //   quantize_row_q8_0_strided   src/emel/kernel/detail.hpp:804-824
 //   dequantize_row_q4_k/q6_k/q8_0/q4_0   :523-552, 592-629, 679-690, 487-502
-#include "common.cuh"
-#include "kernels.h"
+#include "quant_device.cuh"
 
 namespace emelb {
 
 namespace {
 
-// nearest_int, src/emel/kernel/detail.hpp:692-697 (1.5*2^23 magic add)
-__device__ __forceinline__ int nearest_int(float v) {
-  const float biased = __fadd_rn(v, 12582912.0f);
-  return (__float_as_int(biased) & 0x007fffff) - 0x00400000;
-}
-
-// One warp per (256-block, column).  Lane l owns elements 8l..8l+7 so that two
-// neighbouring lanes form one 16-wide bsum group.
+// One warp per (256-block, column).
 template <bool BLOCKS>
 __global__ void __launch_bounds__(128)
 quantize_q8_k_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut planes, uint8_t* blocks, int64_t row_bytes) {
@@ -29,46 +21,12 @@ quantize_q8_k_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut pla
   if (blk >= K / QK_K) return;
   const float* src = x + ((int64_t)blk * QK_K + 8 * lane) * n + col;
   float v[8];
-  float amax = 0.0f, mx = 0.0f;
-  int idx = 8 * lane;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[i] = src[(int64_t)i * n];
-    const float a = fabsf(v[i]);
-    if (a > amax) { amax = a; mx = v[i]; idx = 8 * lane + i; }
-  }
-  // first element attaining the largest |x| wins (strict > scan in the reference)
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
-    const float om = __shfl_xor_sync(0xffffffffu, mx, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (oa > amax || (oa == amax && oi < idx)) { amax = oa; mx = om; idx = oi; }
-  }
-  int q[8];
-  float d = 0.0f;
-  if (amax == 0.0f) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = 0;
-  } else {
-    const float iscale = __fdiv_rn(-127.0f, mx);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int t = nearest_int(__fmul_rn(iscale, v[i]));
-      q[i] = (int)(int8_t)(t < 127 ? t : 127);
-    }
-    d = __fdiv_rn(1.0f, iscale);
-  }
-  int s = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) s += q[i];
-  s += __shfl_xor_sync(0xffffffffu, s, 1);
-  uint32_t lo = 0, hi = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    lo |= (uint32_t)(q[i] & 0xff) << (8 * i);
-    hi |= (uint32_t)(q[4 + i] & 0xff) << (8 * i);
-  }
+  for (int i = 0; i < 8; ++i) v[i] = src[(int64_t)i * n];
+  uint32_t lo, hi;
+  int s;
+  float d;
+  q8_k_block_warp(v, lane, lo, hi, s, d);
   if constexpr (BLOCKS) {
     // reference layout: f32 d, i8 qs[256], i16 bsums[16]; 4-byte aligned only
     uint8_t* b = blocks + (int64_t)col * row_bytes + (int64_t)blk * Q8_K_BYTES;
@@ -77,14 +35,11 @@ quantize_q8_k_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut pla
     if ((lane & 1) == 0) *reinterpret_cast<int16_t*>(b + 260 + 2 * (lane >> 1)) = (int16_t)s;
     if (lane == 0) *reinterpret_cast<float*>(b) = d;
   } else {
-    const int64_t e0 = (int64_t)blk * QK_K + 8 * lane;
-    *reinterpret_cast<uint2*>(planes.qs + (int64_t)col * K + e0) = make_uint2(lo, hi);
-    if ((lane & 1) == 0) planes.bsums[(int64_t)col * (K / 16) + blk * 16 + (lane >> 1)] = (int16_t)s;
-    if (lane == 0) planes.d[(int64_t)col * (K / QK_K) + blk] = d;
+    q8_k_store_planes(planes, col, K, blk, lane, lo, hi, s, d);
   }
 }
 
-// Eight lanes per 32-block, four elements per lane; std::round = roundf
+// Eight lanes per 32-block, four elements per lane
 template <bool BLOCKS>
 __global__ void __launch_bounds__(128)
 quantize_q8_0_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut planes, uint8_t* blocks, int64_t row_bytes) {
@@ -95,25 +50,12 @@ quantize_q8_0_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut pla
   const int cb = live ? blk : 0;
   const float* src = x + ((int64_t)cb * QK32 + 4 * sub) * n + col;
   float v[4];
-  float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[i] = src[(int64_t)i * n];
-    amax = fmaxf(amax, fabsf(v[i]));
-  }
-#pragma unroll
-  for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float d = __fdiv_rn(amax, 127.0f);
-  const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-  uint32_t w = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    int t = (int)roundf(__fmul_rn(v[i], id));
-    t = t < -127 ? -127 : (t > 127 ? 127 : t);
-    w |= (uint32_t)(t & 0xff) << (8 * i);
-  }
+  for (int i = 0; i < 4; ++i) v[i] = src[(int64_t)i * n];
+  uint32_t w;
+  __half dh;
+  q8_0_block_oct(v, w, dh);
   if (!live) return;
-  const __half dh = __float2half_rn(d);  // fp32_to_fp16, src/emel/kernel/detail.hpp:372-392 (RNE)
   if constexpr (BLOCKS) {
     uint8_t* b = blocks + (int64_t)col * row_bytes + (int64_t)blk * Q8_0_BYTES;
     uint16_t* qh = reinterpret_cast<uint16_t*>(b + 2 + 4 * sub);  // 2-byte aligned payload

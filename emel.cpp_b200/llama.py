@@ -1,1 +1,115 @@
-"""Decoder-session bindings (include/emelb_llama.h); filled in with the session API."""
+"""Decoder-session bindings (include/emelb_llama.h): a Llama-architecture decode
+loop that stays on the device, mirroring the reference generator's run_decode
+(src/emel/text/generator/detail.hpp:4860-4914)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+import emel_cpp_b200 as eb
+
+_P = C.c_void_p
+
+# tensor roles (include/emelb_llama.h)
+TOKEN_EMBD, OUTPUT_NORM, OUTPUT, ATTN_NORM, ATTN_Q, ATTN_K, ATTN_V, ATTN_OUT, FFN_NORM, FFN_GATE, FFN_UP, FFN_DOWN = range(12)
+LAYER_ROLES = (ATTN_NORM, ATTN_Q, ATTN_K, ATTN_V, ATTN_OUT, FFN_NORM, FFN_GATE, FFN_UP, FFN_DOWN)
+
+
+class Config(C.Structure):
+    _fields_ = [("n_layer", C.c_int32), ("n_embd", C.c_int32), ("n_head", C.c_int32), ("n_head_kv", C.c_int32),
+                ("head_dim", C.c_int32), ("n_ff", C.c_int32), ("n_vocab", C.c_int32), ("n_ctx", C.c_int32),
+                ("rope_dim", C.c_int32), ("rope_neox", C.c_int32), ("rope_freq_base", C.c_float), ("rms_eps", C.c_float),
+                ("kv_block", C.c_int32), ("shard_rank", C.c_int32), ("shard_count", C.c_int32)]
+
+
+SIGNATURES = {
+    "emelb_llama_create": [_P, C.POINTER(Config), C.POINTER(_P)],
+    "emelb_llama_destroy": [_P],
+    "emelb_llama_bind": [_P, C.c_int32, C.c_int32, C.POINTER(eb.View)],
+    "emelb_llama_decode": [_P, C.c_int32, C.c_int32, _P, C.POINTER(C.c_int32)],
+    "emelb_llama_prefill": [_P, C.POINTER(C.c_int32), C.c_int32, C.c_int32],
+    "emelb_llama_generate": [_P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32)],
+    "emelb_llama_launches_per_token": [_P, C.POINTER(C.c_int32)],
+}
+
+
+def register(lib):
+    for name, args in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = C.c_uint32
+        fn.argtypes = args
+
+
+def config(n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx, rope_freq_base=500000.0, rms_eps=1e-5,
+           rope_dim=None, rope_neox=0, kv_block=16, shard_rank=0, shard_count=1) -> Config:
+    return Config(n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx,
+                  head_dim if rope_dim is None else rope_dim, rope_neox, rope_freq_base, rms_eps, kv_block,
+                  shard_rank, shard_count)
+
+
+def matrix_shapes(cfg: Config):
+    """role -> (K, M) of each matrix, as emelb_llama_bind checks them."""
+    qd, kvd = cfg.n_head * cfg.head_dim, cfg.n_head_kv * cfg.head_dim
+    return {TOKEN_EMBD: (cfg.n_embd, cfg.n_vocab), OUTPUT: (cfg.n_embd, cfg.n_vocab),
+            ATTN_Q: (cfg.n_embd, qd), ATTN_K: (cfg.n_embd, kvd), ATTN_V: (cfg.n_embd, kvd), ATTN_OUT: (qd, cfg.n_embd),
+            FFN_GATE: (cfg.n_embd, cfg.n_ff), FFN_UP: (cfg.n_embd, cfg.n_ff), FFN_DOWN: (cfg.n_ff, cfg.n_embd)}
+
+
+class Session:
+    def __init__(self, backend: eb.Backend, cfg: Config):
+        self.be, self.cfg = backend, cfg
+        self._h = _P()
+        err = eb.lib().emelb_llama_create(backend.handle, C.byref(cfg), C.byref(self._h))
+        if err != eb.OK:
+            raise eb.BackendError(f"emelb_llama_create failed with error mask {err}")
+        self.last_error = eb.OK
+
+    def close(self):
+        if self._h:
+            eb.lib().emelb_llama_destroy(self._h)
+            self._h = _P()
+
+    def _ret(self, err):
+        self.last_error = err
+        return err == eb.OK
+
+    def bind_matrix(self, layer: int, role: int, data, t: int) -> bool:
+        k, m = matrix_shapes(self.cfg)[role]
+        if t in (eb.F32, eb.F16):
+            v = eb.dense_view(data, t, [k, m])
+        else:
+            v = eb.quant_view(data, t, k, m)
+        return self._ret(eb.lib().emelb_llama_bind(self._h, layer, role, C.byref(v)))
+
+    def bind_norm(self, layer: int, role: int, data) -> bool:
+        v = eb.dense_view(data, eb.F32, [self.cfg.n_embd, 1])
+        return self._ret(eb.lib().emelb_llama_bind(self._h, layer, role, C.byref(v)))
+
+    def decode(self, token: int, position: int, want_logits: bool = False):
+        """-> next token id (greedy) or, with want_logits, the f32 logits."""
+        if want_logits:
+            logits = np.zeros(self.cfg.n_vocab, np.float32)
+            if not self._ret(eb.lib().emelb_llama_decode(self._h, token, position, logits.ctypes.data, None)):
+                raise eb.BackendError(f"decode failed with error mask {self.last_error}")
+            return logits
+        out = C.c_int32(-1)
+        if not self._ret(eb.lib().emelb_llama_decode(self._h, token, position, None, C.byref(out))):
+            raise eb.BackendError(f"decode failed with error mask {self.last_error}")
+        return out.value
+
+    def prefill(self, tokens, start_pos: int = 0) -> bool:
+        arr = np.ascontiguousarray(tokens, np.int32)
+        return self._ret(eb.lib().emelb_llama_prefill(self._h, arr.ctypes.data_as(C.POINTER(C.c_int32)), arr.size, start_pos))
+
+    def generate(self, first_token: int, start_pos: int, n: int):
+        out = np.zeros(n, np.int32)
+        if not self._ret(eb.lib().emelb_llama_generate(self._h, first_token, start_pos, n,
+                                                       out.ctypes.data_as(C.POINTER(C.c_int32)))):
+            raise eb.BackendError(f"generate failed with error mask {self.last_error}")
+        return out
+
+    def launches_per_token(self) -> int:
+        v = C.c_int32(0)
+        eb.lib().emelb_llama_launches_per_token(self._h, C.byref(v))
+        return v.value

@@ -142,8 +142,11 @@ EMELB_API uint32_t emelb_get_stream(emelb_ctx* ctx, void** stream_out);
 /* event::capture_diagnostics: src/emel/kernel/any.hpp:38-74 */
 EMELB_API uint32_t emelb_diagnostics(const emelb_ctx* ctx, emelb_diag* out);
 /* attention numerics: 0 = split-KV f32 accumulators (fast, default);
- * 1 = reference order: sequential over tokens with an f16-rounded accumulator
- * (src/emel/kernel/detail.hpp:5238-5291). */
+ * 1 = reference order, scalar route: sequential over tokens with an f16-rounded
+ * accumulator, f64 score sums (src/emel/kernel/detail.hpp:5238-5291);
+ * 2 = reference order, x86 AVX2 route: same accumulator, scores summed as the
+ * AVX2/FMA kernel does (src/emel/kernel/x86_64/actions.hpp:1388-1446, 1575-1641).
+ * Shapes the split-KV kernel does not take run in order 2 under mode 0. */
 EMELB_API uint32_t emelb_set_attention_mode(emelb_ctx* ctx, int mode);
 
 /* ---- residency: replaces io::loader strategy `external_buffer`
@@ -228,6 +231,17 @@ EMELB_API uint32_t emelb_dequantize(emelb_ctx* ctx, const emelb_view* src,
 EMELB_API uint32_t emelb_row_slice(const emelb_op* op, uint32_t lane,
                          uint32_t lane_count, emelb_op* out,
                          uint64_t* row_begin, uint64_t* row_count);
+
+/* ---- stream capture (no reference counterpart: the reference dispatches
+ * synchronously on the calling thread).  Between begin and end, calls whose
+ * operands are all device-resident are recorded instead of run; the resulting
+ * graph replays them with one launch.  Calls that would touch host memory
+ * (staged copies, argmax results written to host pointers) must not be made
+ * while capturing. ---- */
+EMELB_API uint32_t emelb_graph_begin(emelb_ctx* ctx);
+EMELB_API uint32_t emelb_graph_end(emelb_ctx* ctx, void** graph_out);
+EMELB_API uint32_t emelb_graph_launch(emelb_ctx* ctx, void* graph);
+EMELB_API uint32_t emelb_graph_destroy(emelb_ctx* ctx, void* graph);
 
 /* ---- synthetic data (no reference counterpart; the reference's benches fill
  * buffers with closed-form patterns on the host,

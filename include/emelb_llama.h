@@ -1,0 +1,102 @@
+/*
+ * emelb_llama.h — device-resident Llama-architecture decode loop over the
+ * kernels of emelb.h.
+ *
+ * Restates the caller side of the hot path: the reference's generator issues,
+ * per token, the embedding row copy, per layer rms_norm -> Q/K/V mat-vecs ->
+ * RoPE -> f16 KV store -> flash attention -> output projection + residual ->
+ * rms_norm -> gate/up mat-vecs -> SwiGLU -> down projection + residual, then
+ * the output norm and the logits mat-vec
+ * (src/emel/text/generator/detail.hpp:3746-3840 compute_layer_attention_residual,
+ *  :3852-3926 compute_layer_feed_forward, :3997-4033 compute_logits,
+ *  :4860-4914 run_decode).  Here the whole token step is enqueued on the
+ * context's stream (captured once as a CUDA graph) with every intermediate
+ * kept in HBM; only the token id goes in and the next token id (or the logits)
+ * comes out.
+ */
+#ifndef EMELB_LLAMA_H
+#define EMELB_LLAMA_H
+
+#include "emelb.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct emelb_llama_config {
+  int32_t n_layer;
+  int32_t n_embd;
+  int32_t n_head;
+  int32_t n_head_kv;
+  int32_t head_dim;
+  int32_t n_ff;
+  int32_t n_vocab;
+  int32_t n_ctx;
+  int32_t rope_dim;        /* rotated dims per head (n_rot) */
+  int32_t rope_neox;       /* 0: adjacent pairs (Llama), 1: half-split pairs
+                              (src/emel/text/generator/detail.hpp:38-50) */
+  float rope_freq_base;
+  float rms_eps;
+  int32_t kv_block;        /* KV capacity is n_ctx rounded up to this (16 in the
+                              reference, src/emel/memory/view.hpp:18,47-56) */
+  int32_t shard_rank;      /* row sharding across GPUs: this rank ... */
+  int32_t shard_count;     /* ... of this many (1 = unsharded) */
+} emelb_llama_config;
+
+/* tensor roles for emelb_llama_bind; layer = -1 for the three model-level ones */
+enum {
+  EMELB_T_TOKEN_EMBD = 0,
+  EMELB_T_OUTPUT_NORM = 1,
+  EMELB_T_OUTPUT = 2,
+  EMELB_T_ATTN_NORM = 3,
+  EMELB_T_ATTN_Q = 4,
+  EMELB_T_ATTN_K = 5,
+  EMELB_T_ATTN_V = 6,
+  EMELB_T_ATTN_OUT = 7,
+  EMELB_T_FFN_NORM = 8,
+  EMELB_T_FFN_GATE = 9,
+  EMELB_T_FFN_UP = 10,
+  EMELB_T_FFN_DOWN = 11
+};
+
+typedef struct emelb_llama emelb_llama;
+
+/* allocates activations, the f16 KV cache in the flash layout
+ * [layer][kv_head][capacity][head_dim]
+ * (src/emel/text/generator/detail.hpp:3010-3048) and the RoPE table */
+EMELB_API uint32_t emelb_llama_create(emelb_ctx* ctx, const emelb_llama_config* cfg,
+                                      emelb_llama** out);
+EMELB_API uint32_t emelb_llama_destroy(emelb_llama* s);
+
+/* binds one tensor (replaces bind_tensor_rows / make_src_view,
+ * src/emel/text/generator/detail.hpp:788-817, 1886-1919): a {K, M} view of
+ * native blocks (matrices) or f32 (norm vectors) whose data is a device
+ * pointer or a host pointer inside a resident span */
+EMELB_API uint32_t emelb_llama_bind(emelb_llama* s, int32_t layer, int32_t role,
+                                    const emelb_view* tensor);
+
+/* one decode step at `position` (replaces run_decode).  logits_out (n_vocab
+ * f32, host or device) and token_out (greedy argmax, lowest id on ties) may
+ * each be null; with logits_out null the logits are never materialised
+ * (op_mul_mat_argmax route, src/emel/text/generator/detail.hpp:4035-4060). */
+EMELB_API uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t position,
+                                      float* logits_out, int32_t* token_out);
+
+/* feeds `n` prompt tokens at positions start_pos.. without computing logits
+ * (token-at-a-time, as the reference's x86 prefill does:
+ * src/emel/text/generator/detail.hpp:4064-4092) */
+EMELB_API uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n,
+                                       int32_t start_pos);
+
+/* greedy generation of `n` tokens with the token fed back on the device: no
+ * host round trip between steps; tokens_out (host) is written at the end */
+EMELB_API uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token,
+                                        int32_t start_pos, int32_t n, int32_t* tokens_out);
+
+/* kernels launched per decode step (for launch accounting) */
+EMELB_API uint32_t emelb_llama_launches_per_token(const emelb_llama* s, int32_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMELB_LLAMA_H */

@@ -280,3 +280,79 @@ def rel_l2(a, b) -> float:
     b = np.asarray(b, np.float64).ravel()
     den = np.linalg.norm(b)
     return float(np.linalg.norm(a - b) / (den if den > 0 else 1.0))
+
+
+# ---------------------------------------------------------------- decoder restatement (llama_oracle.c)
+class LConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab",
+                                         "n_ctx", "rope_dim", "rope_neox", "kv_block")] + \
+               [("rope_freq_base", C.c_float), ("rms_eps", C.c_float)]
+
+
+class CpuLlama:
+    """The reference generator's decode loop restated on the CPU.  `kernels` picks who does the
+    matrix products and attention: "ref-avx2" / "ref-scalar" (the reference's own kernels from
+    oracle/_ref) or "port" (emel_oracle.c)."""
+
+    def __init__(self, cfg: dict, kernels: str = "port"):
+        lib = port().lib
+        r = ref()
+        if kernels.startswith("ref") and r is None:
+            raise RuntimeError("oracle/_ref is not built")
+        if kernels == "ref-avx2":
+            mm, fa = r.lib.ref_mul_mat_avx2, r.lib.ref_flash_attn_avx2
+        elif kernels == "ref-scalar":
+            mm, fa = r.lib.ref_mul_mat_scalar, r.lib.ref_flash_attn_scalar
+        else:
+            mm, fa = lib.orc_mul_mat, lib.orc_flash_attn
+        self.cfg = LConfig(cfg["n_layer"], cfg["n_embd"], cfg["n_head"], cfg["n_head_kv"], cfg["head_dim"], cfg["n_ff"],
+                           cfg["n_vocab"], cfg["n_ctx"], cfg.get("rope_dim", cfg["head_dim"]), cfg.get("rope_neox", 0),
+                           cfg.get("kv_block", 16), cfg.get("rope_freq_base", 500000.0), cfg.get("rms_eps", 1e-5))
+        lib.orc_llama_create.restype = C.c_void_p
+        lib.orc_llama_create.argtypes = [C.POINTER(LConfig), C.c_void_p, C.c_void_p]
+        lib.orc_llama_bind.restype = C.c_int
+        lib.orc_llama_bind.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        lib.orc_llama_decode.restype = C.c_int
+        lib.orc_llama_decode.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        lib.orc_llama_destroy.argtypes = [C.c_void_p]
+        self.lib = lib
+        self.h = lib.orc_llama_create(C.byref(self.cfg), C.cast(mm, C.c_void_p), C.cast(fa, C.c_void_p))
+        self.keep = []
+
+    def bind(self, layer, role, data, t):
+        self.keep.append(data)
+        assert self.lib.orc_llama_bind(self.h, layer, role, ptr(data), t)
+
+    def decode(self, token, position, want_logits=True):
+        logits = np.zeros(self.cfg.n_vocab, np.float32) if want_logits else None
+        assert self.lib.orc_llama_decode(self.h, token, position, logits.ctypes.data if want_logits else None)
+        return logits
+
+    def close(self):
+        if self.h:
+            self.lib.orc_llama_destroy(self.h)
+            self.h = None
+
+
+def cpu_rms_norm(x, w, eps):
+    lib = port().lib
+    out = np.zeros_like(x)
+    lib.orc_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p]
+    lib.orc_rms_norm(x.ctypes.data, w.ctypes.data, eps, x.size, out.ctypes.data)
+    return out
+
+
+def cpu_rope(vec, heads, head_dim, n_rot, neox, position, base):
+    lib = port().lib
+    out = np.ascontiguousarray(vec, np.float32).copy()
+    lib.orc_rope.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]
+    lib.orc_rope(out.ctypes.data, heads, head_dim, n_rot, neox, position, base)
+    return out
+
+
+def cpu_swiglu(gate, up):
+    lib = port().lib
+    out = np.zeros_like(gate)
+    lib.orc_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    lib.orc_swiglu(gate.ctypes.data, up.ctypes.data, gate.size, out.ctypes.data)
+    return out

@@ -132,3 +132,24 @@ def test_row_slice_matches_reference_arithmetic(port):
                 assert eb.lib().emelb_can_run(None, eb.OP_MUL_MAT, C.byref(s)) == eb.OK
             covered += c
         assert covered == m
+
+
+def test_cuda_actor_adapter_compiles_against_reference_events():
+    """emel::kernel::cuda::sm takes the reference's own event structs (needs the reference checkout)."""
+    import subprocess
+    import tempfile
+    ref = "/root/reference"
+    if not os.path.isdir(os.path.join(ref, "src", "emel", "kernel")):
+        pytest.skip("reference checkout not present")
+    exe = os.path.join(tempfile.gettempdir(), "emelb_cuda_sm_check")
+    subprocess.run(["g++", "-std=c++20", f"-I{ref}/src", f"-I{ref}/include", f"-I{ROOT}/include",
+                    os.path.join(ROOT, "tests", "cuda_sm_check.cc"), "-o", exe, eb.LIB_PATH,
+                    f"-Wl,-rpath,{os.path.dirname(eb.LIB_PATH)}"], check=True)
+    out = subprocess.run([exe], check=True, capture_output=True, text=True).stdout
+    fields = dict(kv.split("=") for kv in out.split())
+    assert fields["other"] == "0"
+    import torch
+    if torch.cuda.is_available():
+        assert fields["engaged"] == "1" and fields["accepted"] == "1"
+    else:
+        assert fields["engaged"] == "0" and fields["accepted"] == "0"
