@@ -3,6 +3,12 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 One JSON line on stdout (rank 0).  Workloads (synthetic data, seeded):
+  decode_8b   (default) configuration 3: Llama-8B-shape decoder, Q4_K attention/FFN weights and a
+              Q6_K output projection drawn N(0, 0.02) and encoded on the device, f16 KV cache.
+              A 4096-token random prompt is prefilled, then one step = one greedy decode token.
+              `roofline` times the dominant kernel (the Q4_K mat-vec) alone over one token's
+              matrices: that figure is the Q4_K GEMV HBM GB/s of the headline metric.
+  decode_70b  configuration 5 at batch 1 on one GPU (39 GB of Q4_K weights).
   gemv_q4_k   configuration 1: Q4_K 4096x4096 mat-vec, x ~ N(0,1) quantized to Q8_K.
               One step = one mat-vec over each of COPIES distinct weight copies
               (COPIES x 9.4 MB > the 126 MB L2, so every step streams from HBM).
@@ -331,21 +337,274 @@ def run_reference_gemv(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------ decode workload (configurations 3 and 5)
+DECODE_SHAPES = {
+    "decode_8b": dict(n_layer=32, n_embd=4096, n_head=32, n_head_kv=8, head_dim=128, n_ff=14336, n_vocab=128256,
+                      prompt=4096, name="cfg3: Llama-8B shape, Q4_K attn/FFN + Q6_K output, greedy decode after a 4096-token prompt, f16 KV"),
+    "decode_70b": dict(n_layer=80, n_embd=8192, n_head=64, n_head_kv=8, head_dim=128, n_ff=28672, n_vocab=128256,
+                       prompt=8192 - 160, name="cfg5: Llama-70B shape, Q4_K weights, batch-1 decode at context 8192, f16 KV"),
+}
+
+
+def decode_tensors(sh, out_type):
+    """(layer, role, K, M, type) of every matrix, in the roles of include/emelb_llama.h."""
+    import emel_cpp_b200 as eb
+    from emel_cpp_b200 import llama as el
+    qd, kvd = sh["n_head"] * sh["head_dim"], sh["n_head_kv"] * sh["head_dim"]
+    per_layer = [(el.ATTN_Q, sh["n_embd"], qd), (el.ATTN_K, sh["n_embd"], kvd), (el.ATTN_V, sh["n_embd"], kvd),
+                 (el.ATTN_OUT, qd, sh["n_embd"]), (el.FFN_GATE, sh["n_embd"], sh["n_ff"]), (el.FFN_UP, sh["n_embd"], sh["n_ff"]),
+                 (el.FFN_DOWN, sh["n_ff"], sh["n_embd"])]
+    out = [(-1, el.TOKEN_EMBD, sh["n_embd"], sh["n_vocab"], eb.Q4_K), (-1, el.OUTPUT, sh["n_embd"], sh["n_vocab"], out_type)]
+    for l in range(sh["n_layer"]):
+        out += [(l, role, k, m, eb.Q4_K) for role, k, m in per_layer]
+    return out
+
+
+def run_decode(args):
+    import torch
+    import emel_cpp_b200 as eb
+    from emel_cpp_b200 import llama as el
+
+    rank, world, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    sh = DECODE_SHAPES[args.workload]
+    out_type = eb.Q6_K if args.workload == "decode_8b" else eb.Q4_K
+    steps, warmup = args.steps, args.warmup
+    prompt_len = sh["prompt"] if args.prompt is None else args.prompt
+    n_ctx = ((prompt_len + warmup + steps + 15) // 16) * 16
+    be = eb.Backend(local)
+    stream = torch.cuda.ExternalStream(be.stream(), device=dev)
+    cfg = el.config(sh["n_layer"], sh["n_embd"], sh["n_head"], sh["n_head_kv"], sh["head_dim"], sh["n_ff"], sh["n_vocab"], n_ctx)
+    sess = el.Session(be, cfg)
+
+    # weights N(0, 0.02) encoded on the device; norm weights 1.0 (each rank builds its own replica)
+    tensors = decode_tensors(sh, out_type)
+    weight_bytes, q4k_bytes, q4k_ops = 0, 0, []
+    for i, (layer, role, k, m, t) in enumerate(tensors):
+        nbytes = m * eb.row_bytes(t, k)
+        d = be.alloc(nbytes)
+        assert be.synth_fill(d, t, m * k, 5000 + i, 0.02, 0), be.last_error
+        assert sess.bind_matrix(layer, role, d, t), sess.last_error
+        if role != el.TOKEN_EMBD:
+            weight_bytes += nbytes
+            if t == eb.Q4_K and layer >= 0:
+                q4k_bytes += nbytes
+                q4k_ops.append((d, t, k, m))
+    ones = be.alloc(4 * sh["n_embd"])
+    assert be.to_device(ones, np.ones(sh["n_embd"], np.float32))
+    assert sess.bind_norm(-1, el.OUTPUT_NORM, ones)
+    for l in range(sh["n_layer"]):
+        assert sess.bind_norm(l, el.ATTN_NORM, ones) and sess.bind_norm(l, el.FFN_NORM, ones)
+    assert be.sync()
+
+    prompt = np.random.Generator(np.random.PCG64(42 + rank)).integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32)
+    t0 = time.perf_counter()
+    assert sess.prefill(prompt[:-1], 0), sess.last_error
+    prefill_s = time.perf_counter() - t0
+    pos0 = prompt_len - 1
+
+    def timed_region(fn):
+        be.sync()
+        barrier(world)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = fn()
+        e1.record(stream)
+        be.sync()
+        torch.cuda.synchronize()
+        barrier(world)
+        return max_over_ranks(e0.elapsed_time(e1), world, dev), out
+
+    with ClockSampler(local) as clk:
+        # device-fed greedy loop: W warm-up tokens, then K timed tokens, no host round trip between steps
+        warm_ids = sess.generate(int(prompt[-1]), pos0, warmup)
+        ms, ids = timed_region(lambda: sess.generate(int(warm_ids[-1]), pos0 + warmup, steps))
+        # end to end: one C-ABI call per token, token id in, next token id out (host round trip every step)
+        d0 = be.diagnostics()
+        tok = int(prompt[-1])
+        for i in range(warmup):
+            tok = sess.decode(tok, pos0 + i)
+
+        def host_loop():
+            t, out = tok, []
+            for i in range(steps):
+                t = sess.decode(t, pos0 + warmup + i)
+                out.append(t)
+            return out
+        ms_e, ids_e = timed_region(host_loop)
+        d1 = be.diagnostics()
+        # the dominant kernel alone: every Q4_K layer matrix of one token, activations already quantized
+        x8 = be.alloc(4 * sh["n_ff"])
+        assert be.synth_fill(x8, eb.F32, sh["n_ff"], 9, 1.0, 0)
+        ybuf = be.alloc(4 * max(sh["n_ff"], sh["n_embd"]))
+        by_k = {}
+        for d, t, k, m in q4k_ops:
+            by_k.setdefault(k, []).append(eb.mul_mat_op(d, t, k, m, x8, 1, ybuf))
+        graphs = []
+        for k, ops in by_k.items():
+            assert be.prepare_rhs(eb.dense_view(x8, eb.F32, [1, k]), eb.Q4_K)
+            for op in ops[:2]:
+                assert be.mul_mat_prepared(op)
+            be.sync()
+            assert be.graph_begin()
+            for op in ops:
+                assert be.mul_mat_prepared(op)
+            graphs.append((k, be.graph_end(), len(ops)))
+        ms_k, n_k = 0.0, 0
+        for k, g, n_ops in graphs:
+            assert be.prepare_rhs(eb.dense_view(x8, eb.F32, [1, k]), eb.Q4_K)
+            for _ in range(3):
+                be.graph_launch(g)
+            t_ms, _ = timed_region(lambda: [be.graph_launch(g) for _ in range(5)])
+            ms_k += t_ms / 5
+            n_k += n_ops
+    clocks = clk.summary()
+    assert list(ids) == list(ids_e), "device-fed and host-fed greedy loops disagree"
+
+    tok_s = steps * world / (ms * 1e-3)
+    tok_s_e2e = steps * world / (ms_e * 1e-3)
+    kv_bytes_per_pos = sh["n_layer"] * 2 * sh["n_head_kv"] * sh["head_dim"] * 2
+    ctx_mid = prompt_len + warmup + steps // 2
+    bytes_per_token = weight_bytes + kv_bytes_per_pos * ctx_mid
+    peaks, peak_kind = measured_peaks()
+    kernel_gbs = q4k_bytes / (ms_k * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s", "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 dot (dp4a) + f32 scales; f16 KV", "data": "synthetic",
+        "config": {"workload": sh["name"], "prompt_tokens": prompt_len, "decoded_tokens": steps, "n_ctx": n_ctx,
+                   "launch": "one CUDA-graph replay per token; the next token id is fed back on the device",
+                   "l2_policy": f"inputs larger than L2: {weight_bytes / 1e9:.2f} GB of weights streamed per token",
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (one sequence per GPU), no collective",
+                   "kernel_launches_per_token": sess.launches_per_token(), "prefill_s": round(prefill_s, 2)},
+        "hbm_gbs_effective": round(bytes_per_token * tok_s / world / 1e9, 1),
+        "q4_k_gemv_hbm_gbs": round(kernel_gbs, 1), "pct_of_8tbs_nominal": round(100 * kernel_gbs / NOMINAL_HBM_GBS, 2),
+        "e2e": {"value": round(tok_s_e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 8,
+                "d2h_bytes_per_step": (d1["d2h_bytes"] - d0["d2h_bytes"]) // (steps + warmup)},
+        "gpu_launches": sess.launches_per_token() * steps,
+        "roofline": {"bound": "hbm", "kernel": "gemv_stream_q4_k_n1", "achieved": round(kernel_gbs, 2), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(kernel_gbs / peaks["hbm_gbs"], 4), "peak_source": f"of {peak_kind}",
+                     "us_per_launch": round(ms_k * 1e3 / n_k, 3), "algorithmic_bytes_per_launch": q4k_bytes // n_k,
+                     "launches_timed": n_k, "traffic": ncu_traffic("gemv_stream_q4_k_n1_decode")},
+        "clocks": clocks,
+    }
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline_decode(sh, out_type, budget_s=args.cpu_budget)
+        print(json.dumps(line), flush=True)
+    sess.close()
+    be.close()
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def cpu_decode_sample(sh, out_type, lanes, repeats, ctx):
+    """Seconds per token of the reference's CPU kernels on this shape, from a bounded sample: every
+    matrix product of ONE layer plus that layer's attention over `ctx` cached tokens plus 1/16 of the
+    output projection, scaled to n_layer layers and the full vocabulary."""
+    import emel_cpp_b200 as eb
+    from oracle import bindings as ob
+    lib = ob.ref()
+    kind = "reference" if lib is not None else "port"
+    lib = lib or ob.port()
+    rng = np.random.Generator(np.random.PCG64(1))
+
+    def blocks(t, k, m):
+        w = rng.integers(0, 256, size=m * eb.row_bytes(t, k), dtype=np.uint8).reshape(-1, eb.BLOCK_BYTES[t])
+        for off in ({eb.Q4_K: (0, 2), eb.Q6_K: (208,)}[t]):
+            w[:, off + 1] = rng.integers(0x18, 0x30, size=w.shape[0])
+        return w.reshape(-1)
+
+    qd, kvd = sh["n_head"] * sh["head_dim"], sh["n_head_kv"] * sh["head_dim"]
+    mats = [(sh["n_embd"], qd), (sh["n_embd"], kvd), (sh["n_embd"], kvd), (qd, sh["n_embd"]),
+            (sh["n_embd"], sh["n_ff"]), (sh["n_embd"], sh["n_ff"]), (sh["n_ff"], sh["n_embd"])]
+    vocab_part = sh["n_vocab"] // 16
+    ops, keep = [], []
+    for k, m in mats + [(sh["n_embd"], vocab_part)]:
+        t = eb.Q4_K if (k, m) != (sh["n_embd"], vocab_part) else out_type
+        w, x, y = blocks(t, k, m), rng.standard_normal(k, dtype=np.float32), np.zeros(m, np.float32)
+        keep += [w, x, y]
+        ops.append(ob.mul_mat_op(w, t, k, m, x, 1, y))
+    hd, T = sh["head_dim"], ctx
+    q = rng.standard_normal((sh["n_head"], hd), dtype=np.float32)
+    kc = (rng.standard_normal((sh["n_head_kv"], T, hd), dtype=np.float32) * 0.5).astype(np.float16).view(np.uint16)
+    vc = rng.standard_normal((sh["n_head_kv"], T, hd), dtype=np.float32).astype(np.float16).view(np.uint16)
+    dst = np.zeros((sh["n_head"], hd), np.float32)
+    fop = ob.flash_op(q, kc, vc, dst, hd, sh["n_head"], sh["n_head_kv"], T, T, scale=float(hd) ** -0.5, masked_total=T)
+    kw = {"route": "avx2", "lanes": lanes} if kind == "reference" else {}
+    fkw = {"route": "avx2"} if kind == "reference" else {}
+
+    def once():
+        t0 = time.perf_counter()
+        for op in ops[:-1]:
+            assert lib.mul_mat(op, **kw)
+        assert lib.flash_attn(fop, **fkw)
+        t_layer = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        assert lib.mul_mat(ops[-1], **kw)
+        return t_layer, time.perf_counter() - t0
+
+    once()
+    samples = [once() for _ in range(repeats)]
+    t_layer = float(np.median([a for a, _ in samples]))
+    t_out = float(np.median([b for _, b in samples])) * 16
+    return sh["n_layer"] * t_layer + t_out, kind
+
+
+def cpu_baseline_decode(sh, out_type, budget_s=8.0):
+    lanes = min(8, os.cpu_count() or 1)
+    ctx = sh["prompt"]
+    t0 = time.perf_counter()
+    sec, kind = cpu_decode_sample(sh, out_type, lanes, 1, ctx)
+    one = time.perf_counter() - t0
+    reps = int(max(1, min(10, budget_s / max(one, 1e-3))))
+    sec, kind = cpu_decode_sample(sh, out_type, lanes, reps, ctx)
+    return {"value": round(1.0 / sec, 4), "unit": "tok/s", "cores": lanes if kind == "reference" else 1, "kind": kind,
+            "sample": f"median of {reps} x (one layer's 7 mat-vecs + its attention over {ctx} tokens + 1/16 of the output "
+                      f"projection), scaled to {sh['n_layer']} layers and the full vocabulary; AVX2/FMA route, "
+                      f"mat-vecs row-sliced over {lanes} threads, attention single-threaded as in the reference"}
+
+
+def run_reference_decode(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    sh = DECODE_SHAPES[args.workload]
+    import emel_cpp_b200 as eb
+    out_type = eb.Q6_K if args.workload == "decode_8b" else eb.Q4_K
+    lanes = min(os.cpu_count() or 1, 64)
+    ctx = sh["prompt"] if args.prompt is None else args.prompt
+    sec, kind = cpu_decode_sample(sh, out_type, lanes, max(1, min(args.steps, 8)), ctx)
+    v = round(1.0 / sec, 4)
+    line = {"impl": "reference", "metric": "decode tok/s", "value": v, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot (AVX2 maddubs) + f32 scales; f16 KV", "data": "synthetic",
+            "config": {"workload": sh["name"], "prompt_tokens": ctx},
+            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": lanes if kind == "reference" else 1, "kind": kind,
+                             "sample": f"each step = one layer's 7 mat-vecs + its attention over {ctx} tokens + 1/16 of the "
+                                       f"output projection, scaled to {sh['n_layer']} layers and the full vocabulary"},
+            "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemv_q4_k", choices=["gemv_q4_k", "gemv_q8_0"])
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_70b", "gemv_q4_k", "gemv_q8_0"])
+    ap.add_argument("--prompt", type=int, default=None, help="prompt length override for the decode workloads")
     ap.add_argument("--ncols", type=int, default=1)
     ap.add_argument("--cpu-budget", type=float, default=8.0)
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    decode = args.workload.startswith("decode")
     if args.impl == "reference":
-        run_reference_gemv(args)
+        (run_reference_decode if decode else run_reference_gemv)(args)
     else:
-        run_gemv(args)
+        (run_decode if decode else run_gemv)(args)
 
 
 if __name__ == "__main__":

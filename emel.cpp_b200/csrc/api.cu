@@ -299,6 +299,8 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
   ok = ok && cudaMalloc(&c->act_qs, c->act_capacity) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_d, c->act_capacity / 32 * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_bsums, c->act_capacity / 16 * sizeof(int16_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&c->gemv_sched, 2 * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(c->gemv_sched, 0, 2 * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_val, kMaxArgmaxParts * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_idx, kMaxArgmaxParts * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->best_val, sizeof(float)) == cudaSuccess;
@@ -324,7 +326,7 @@ uint32_t emelb_destroy(emelb_ctx* c) {
   for (auto& kv : c->residents)
     if (kv.second.dev) cudaFree(kv.second.dev);
   for (void* p : c->owned) cudaFree(p);
-  void* bufs[] = {c->stage_in, c->stage_out, c->act_qs, c->act_d, c->act_bsums, c->part_val, c->part_idx,
+  void* bufs[] = {c->gemv_sched, c->stage_in, c->stage_out, c->act_qs, c->act_d, c->act_bsums, c->part_val, c->part_idx,
                   c->best_val, c->best_idx, c->fa_part_acc, c->fa_part_ml, c->fa_scores};
   for (void* p : bufs)
     if (p) cudaFree(p);
@@ -504,6 +506,7 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
   a.y = static_cast<float*>(out.dev);
   a.ldy = (int64_t)n;
   a.residual = nullptr;
+  a.sched = c->gemv_sched;
   a.part_val = c->part_val;
   a.part_idx = c->part_idx;
   a.best_val = c->best_val;

@@ -103,7 +103,10 @@ __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
   for (int r = 0; r < NREP; ++r) mx[r] = -INFINITY;
   const char* kbase = reinterpret_cast<const char*>(a.k) + (size_t)kh * a.k_nb2 + (size_t)l8 * DPL * 2;
   constexpr int U = 4;
-  for (int t = slot; t < n; t += 16 * U) {
+  // the loop bound is uniform across the warp (the score reduction below shuffles
+  // over all 32 lanes); rows past the range are clamped on load and masked on store
+  for (int tb = 0; tb < n; tb += 16 * U) {
+    const int t = tb + slot;
     uint4 kv[U][DPL / 8];
 #pragma unroll
     for (int u = 0; u < U; ++u) {

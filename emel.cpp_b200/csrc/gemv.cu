@@ -30,6 +30,8 @@
 // one lane per (row, column) walks them.  The result equals the reference's
 // AVX2 output bit for bit (and its scalar output for Q8_0/Q4_0, whose two routes
 // agree).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -290,7 +292,8 @@ constexpr int CHAIN_ROW = 68;  // 64 block values of a chunk + padding (bank spr
 
 template <int T, int NCOLS, int R>
 __host__ __device__ constexpr int warp_smem_bytes(int stages) {
-  return stages * R * Geo<T>::CB + (is_k_type(T) ? 0 : R * NCOLS * CHAIN_ROW * 4);
+  // stage ring + parked block values (32-wide formats) + per-stage (task, chunk) words, 16-byte rounded
+  return stages * R * Geo<T>::CB + (is_k_type(T) ? 0 : R * NCOLS * CHAIN_ROW * 4) + ((2 * stages * 4 + 15) / 16) * 16;
 }
 
 template <int T, int NCOLS, int R, int STAGES, int WARPS, bool ARGMAX>
@@ -307,25 +310,39 @@ gemv_stream_kernel(const GemvArgs p) {
 
   const int nchunks = p.K / CHUNK;
   const int ntasks = (p.M + R - 1) / R;
-  const int tw = gridDim.x * WARPS;
-  const int wg = blockIdx.x * WARPS + warp;
-  const int my_tasks = wg < ntasks ? (ntasks - wg + tw - 1) / tw : 0;
-  const int items = my_tasks * nchunks;
-
-  auto issue = [&](int it) {
-    const int ti = it / nchunks, c = it - ti * nchunks;
-    const int row0 = (wg + ti * tw) * R;
-    uint8_t* dst = ring + (size_t)(it % STAGES) * R * CB;
-    for (int i = lane; i < R * V; i += 32) {
-      const int r = i / V, o = i - r * V;
-      const int row = min(row0 + r, p.M - 1);
-      cp_async16(dst + r * CB + o * 16, p.W + (size_t)row * p.row_bytes + (size_t)c * CB + (size_t)o * 16);
+  // Tasks (R rows each) are handed out through an atomic counter, so a warp that
+  // finishes early takes more and the launch has no long tail.  Per stage the warp
+  // records which (task, chunk) the stage holds; task -1 marks the end.
+  int* meta = reinterpret_cast<int*>(ring + warp_smem_bytes<T, NCOLS, R>(STAGES)) - 2 * STAGES;
+  int iss_task = 0, iss_chunk = nchunks;
+  bool drained = false;
+  auto issue_next = [&](int slot) {
+    if (iss_chunk == nchunks && !drained) {
+      int t = 0;
+      if (lane == 0) t = atomicAdd(p.sched, 1);
+      iss_task = __shfl_sync(0xffffffffu, t, 0);
+      iss_chunk = 0;
+      drained = iss_task >= ntasks;
     }
+    if (!drained) {
+      const int row0 = iss_task * R;
+      uint8_t* dst = ring + (size_t)slot * R * CB;
+      for (int i = lane; i < R * V; i += 32) {
+        const int r = i / V, o = i - r * V;
+        const int row = min(row0 + r, p.M - 1);
+        cp_async16(dst + r * CB + o * 16, p.W + (size_t)row * p.row_bytes + (size_t)iss_chunk * CB + (size_t)o * 16);
+      }
+    }
+    if (lane == 0) {
+      meta[2 * slot] = drained ? -1 : iss_task;
+      meta[2 * slot + 1] = iss_chunk;
+    }
+    if (!drained) ++iss_chunk;
   };
 
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < items) issue(s);
+    issue_next(s);
     cp_async_commit();
   }
 
@@ -335,20 +352,23 @@ gemv_stream_kernel(const GemvArgs p) {
   float best = -INFINITY;
   int best_i = 0x7fffffff;
 
-  for (int it = 0; it < items; ++it) {
-    if (it + STAGES - 1 < items) issue(it + STAGES - 1);
+  int slot_c = 0, slot_i = STAGES - 1;
+  for (;;) {
+    issue_next(slot_i);
     cp_async_commit();
+    slot_i = slot_i + 1 == STAGES ? 0 : slot_i + 1;
     cp_async_wait<STAGES - 1>();
     __syncwarp();
 
-    const int ti = it / nchunks, c = it - ti * nchunks;
+    const int task = meta[2 * slot_c], c = meta[2 * slot_c + 1];
+    if (task < 0) break;
     if (c == 0) {
 #pragma unroll
       for (int r = 0; r < (KQ ? R : 1); ++r)
 #pragma unroll
         for (int j = 0; j < (KQ ? NCOLS : 1); ++j) acc[r][j] = 0.0f;
     }
-    const uint8_t* st = ring + (size_t)(it % STAGES) * R * CB;
+    const uint8_t* st = ring + (size_t)slot_c * R * CB;
 
     auto consume = [&](int r, int j, const WRegs<T>& w, const ARegs<T>& a) {
       if constexpr (KQ) {
@@ -401,7 +421,7 @@ gemv_stream_kernel(const GemvArgs p) {
     }
 
     if (c == nchunks - 1) {
-      const int row0 = (wg + ti * tw) * R;
+      const int row0 = task * R;
       if constexpr (KQ) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -436,8 +456,19 @@ gemv_stream_kernel(const GemvArgs p) {
         }
       }
     }
+    slot_c = slot_c + 1 == STAGES ? 0 : slot_c + 1;
   }
   cp_async_wait<0>();
+  // the last block to finish rearms the task counter for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
+  }
 
   if constexpr (ARGMAX) {
     __shared__ float sv[WARPS];
@@ -632,16 +663,27 @@ cudaError_t launch_stream(const GemvArgs& a, int sm_count, cudaStream_t st, int*
   return cudaGetLastError();
 }
 
+// rows per task: more rows share one activation register set, fewer rows give
+// finer scheduling granules and more resident warps.  EMELB_GEMV_R overrides.
+inline int rows_per_task_override() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("EMELB_GEMV_R");
+    v = e ? atoi(e) : 0;
+  }
+  return v;
+}
+
 template <int T, int NCOLS, bool ARGMAX>
 cudaError_t launch_pick_r(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
-  // rows per task: enough tasks to give every SM several warps first, then
-  // amortise the activation registers over more rows
+  int r = a.M >= sm_count * kWarps * 4 ? 2 : 1;
+  if (rows_per_task_override() > 0) r = rows_per_task_override();
   if constexpr (NCOLS == 1) {
-    if (a.M >= sm_count * kWarps * 8) return launch_stream<T, NCOLS, 4, ARGMAX>(a, sm_count, st, grid_out);
-    if (a.M >= sm_count * kWarps * 4) return launch_stream<T, NCOLS, 2, ARGMAX>(a, sm_count, st, grid_out);
+    if (r >= 4) return launch_stream<T, NCOLS, 4, ARGMAX>(a, sm_count, st, grid_out);
+    if (r >= 2) return launch_stream<T, NCOLS, 2, ARGMAX>(a, sm_count, st, grid_out);
     return launch_stream<T, NCOLS, 1, ARGMAX>(a, sm_count, st, grid_out);
   } else {
-    if (a.M >= sm_count * kWarps * 4) return launch_stream<T, NCOLS, 2, ARGMAX>(a, sm_count, st, grid_out);
+    if (r >= 2) return launch_stream<T, NCOLS, 2, ARGMAX>(a, sm_count, st, grid_out);
     return launch_stream<T, NCOLS, 1, ARGMAX>(a, sm_count, st, grid_out);
   }
 }

@@ -21,6 +21,7 @@ struct GemvArgs {
   float* y;              // y[row*ldy + col]
   int64_t ldy;
   const float* residual; // optional: y = residual + W x  (same indexing as y)
+  int* sched;            // {next task, finished blocks}: zero between launches (self-rearming)
   float* part_val;       // argmax: per-block candidates (kMaxArgmaxParts)
   int* part_idx;
   float* best_val;       // argmax result

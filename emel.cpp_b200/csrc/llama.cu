@@ -122,6 +122,7 @@ struct Enqueue {
     a.y = y;
     a.ldy = 1;
     a.residual = residual;
+    a.sched = s->c->gemv_sched;
     a.part_val = s->c->part_val;
     a.part_idx = s->c->part_idx;
     a.best_val = s->c->best_val;

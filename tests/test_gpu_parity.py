@@ -329,10 +329,15 @@ def test_flash_split_kv(be, port, checker, hd, heads, kvh, T, cap):
     assert be.diagnostics()["optimized_flash_dispatch_calls"] == before + 1
     dst = np.zeros((heads, hd), np.float32)
     truth = port.flash_attn_f64(ob.flash_op(q, k, v, dst, hd, heads, kvh, T, cap, scale=float(1 / np.sqrt(hd))), heads, hd)
-    assert np.abs(got - truth).max() <= 2e-5          # f32 split-KV sits on the exact softmax
+    err_split = np.abs(got - truth).max()
+    assert err_split <= 2e-5                           # f32 split-KV sits on the exact softmax
     if T <= 1024:                                      # sequential CPU reference: keep the big ones out of the test time
         want = run_flash(checker.flash_attn, q, k, v, hd, heads, kvh, T, cap, ob.flash_op)
-        assert np.abs(got - want).max() <= 1e-3        # the reference's own tolerance
+        err_ref = np.abs(want - truth).max()
+        # the reference rounds its accumulator to f16 after every token, so it carries the larger
+        # error; the two agree to within that error (1e-3 is the reference's tolerance for small values)
+        assert err_split <= err_ref + 1e-7
+        assert np.abs(got - want).max() <= max(1e-3, 2 * err_ref)
 
 
 @pytest.mark.parametrize("hd,heads,kvh,T,cap", [(4, 1, 1, 2, 2), (128, 32, 8, 769, 784), (64, 12, 12, 104, 104),
