@@ -24,7 +24,6 @@ SOURCES = {
     "gemm_tc.cu": [],
     "llama.cu": [],
     "comm.cu": [],
-    "noalloc.cu": [],
     "api.cu": [],
 }
 
