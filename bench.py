@@ -137,8 +137,8 @@ def max_over_ranks(x, world, device):
 def gemv_spec(args):
     import emel_cpp_b200 as eb
     if args.workload == "gemv_q4_k":
-        t, k, m, n = eb.Q4_K, 4096, 4096, 1
-        name = "cfg1: Q4_K 4096x4096 mat-vec, x~N(0,1) -> Q8_K"
+        t, k, m, n = eb.Q4_K, args.cols or 4096, args.rows or 4096, 1
+        name = f"cfg1: Q4_K {m}x{k} mat-vec, x~N(0,1) -> Q8_K"
     else:
         t, k, m, n = eb.Q8_0, 4096, 14336, args.ncols
         name = f"cfg2: Q8_0 14336x4096, token batch {n}"
@@ -597,6 +597,8 @@ def main():
     ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_70b", "gemv_q4_k", "gemv_q8_0"])
     ap.add_argument("--prompt", type=int, default=None, help="prompt length override for the decode workloads")
     ap.add_argument("--ncols", type=int, default=1)
+    ap.add_argument("--rows", type=int, default=None, help="row count override for gemv_q4_k")
+    ap.add_argument("--cols", type=int, default=None, help="column count override for gemv_q4_k")
     ap.add_argument("--cpu-budget", type=float, default=8.0)
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)

@@ -19,6 +19,7 @@ SOURCES = {
     "quantize.cu": ["-fmad=false"],
     "elementwise.cu": ["-fmad=false"],
     "gemv.cu": [],
+    "gemv2.cu": [],
     "synth.cu": [],
     "attention.cu": [],
     "gemm_tc.cu": [],

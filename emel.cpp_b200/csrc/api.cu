@@ -299,8 +299,8 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
   ok = ok && cudaMalloc(&c->act_qs, c->act_capacity) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_d, c->act_capacity / 32 * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_bsums, c->act_capacity / 16 * sizeof(int16_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&c->gemv_sched, 2 * sizeof(int)) == cudaSuccess;
-  ok = ok && cudaMemset(c->gemv_sched, 0, 2 * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMalloc(&c->gemv_sched, 4 * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(c->gemv_sched, 0, 4 * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_val, kMaxArgmaxParts * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_idx, kMaxArgmaxParts * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->best_val, sizeof(float)) == cudaSuccess;
@@ -338,7 +338,15 @@ uint32_t emelb_destroy(emelb_ctx* c) {
 
 uint32_t emelb_sync(emelb_ctx* c) {
   if (!c) return EMELB_INVALID_REQUEST;
-  return cuda_ok(c, cudaStreamSynchronize(c->stream)) ? EMELB_OK : EMELB_INTERNAL_ERROR;
+  if (!cuda_ok(c, cudaStreamSynchronize(c->stream))) return EMELB_INTERNAL_ERROR;
+  // a kernel whose bounded wait ran out leaves 1 in the status word
+  int status = 0;
+  if (!cuda_ok(c, cudaMemcpy(&status, c->gemv_sched + 2, sizeof(int), cudaMemcpyDeviceToHost))) return EMELB_INTERNAL_ERROR;
+  if (status != 0) {
+    cudaMemset(c->gemv_sched, 0, 4 * sizeof(int));
+    return EMELB_INTERNAL_ERROR;
+  }
+  return EMELB_OK;
 }
 
 uint32_t emelb_get_stream(emelb_ctx* c, void** stream_out) {
@@ -507,6 +515,7 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
   a.ldy = (int64_t)n;
   a.residual = nullptr;
   a.sched = c->gemv_sched;
+  a.status = c->gemv_sched + 2;
   a.part_val = c->part_val;
   a.part_idx = c->part_idx;
   a.best_val = c->best_val;

@@ -49,7 +49,7 @@ struct emelb_ctx {
   uint64_t prepared_n = 0;
   uint64_t prepared_k = 0;
   bool prepared_k_family = false;
-  int* gemv_sched = nullptr;  // task counter of the streaming mat-vec kernel
+  int* gemv_sched = nullptr;  // task counter of the streaming mat-vec kernel; [2] = status word (bounded wait ran out)
   // argmax candidates and result cells
   float* part_val = nullptr;
   int* part_idx = nullptr;

@@ -702,6 +702,9 @@ cudaError_t launch_type(GemvArgs a, int ncols, bool argmax, bool fast, int sm_co
     ++*launches;
     return cudaGetLastError();
   }
+  // second-generation streaming kernel (gemv2.cu) unless EMELB_GEMV_V1 asks for the first
+  static const bool v1 = getenv("EMELB_GEMV_V1") != nullptr;
+  if (!v1) return launch_gemv_stream2(T, a, ncols, argmax, sm_count, st, launches, grid_out);
   if (argmax) {
     ++*launches;
     return launch_pick_r<T, 1, true>(a, sm_count, st, grid_out);

@@ -1,0 +1,506 @@
+// Streaming mat-vec, second generation: one lane per 256 weights.
+//
+// Same contract and same float order as gemv.cu's first streaming kernel (the
+// reference's x86 route block by block, see the notes there); what changes is
+// how a warp spends its instructions, because that kernel turned out to be
+// bound by instruction issue (about 270 warp instructions per 2048-weight row
+// chunk, 46 % issue utilisation at 20 % of HBM bandwidth), not by memory:
+//   * copies: one elected lane issues one bulk-async copy (TMA unit,
+//     cp.async.bulk) per row chunk into the warp's private stage ring and the
+//     warp waits on an mbarrier — no per-lane copy instructions or address math;
+//   * a stage holds 4 rows x 2048 weights, i.e. 32 spans of 256 weights: lane
+//     (r, b) = (lane / 8, lane % 8) owns span b of row r, so the 6-bit scale
+//     unpacking, the integer reductions and the block value need no shuffles,
+//     and the block-order row sum costs 8 shuffles + 8 adds per 4 rows;
+//   * the 256 activations a lane needs depend only on b: they are loaded once per
+//     chunk into registers and reused for every 4-row pass of the task.
+// Every mbarrier wait is bounded; a wait that runs out raises the status word
+// the host turns into internal_error, and the warp leaves.
+#include <cstdlib>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace emelb {
+
+namespace {
+
+constexpr int CHUNK = 2048;
+constexpr int ROWS_PER_STAGE = 4;
+
+template <int T> struct Geo2;
+template <> struct Geo2<T_Q4_K> { static constexpr int CB = 8 * Q4_K_BYTES; };
+template <> struct Geo2<T_Q6_K> { static constexpr int CB = 8 * Q6_K_BYTES; };
+template <> struct Geo2<T_Q8_0> { static constexpr int CB = 64 * Q8_0_BYTES; };
+template <> struct Geo2<T_Q4_0> { static constexpr int CB = 64 * Q4_0_BYTES; };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// global -> this CTA's shared memory, completion counted in bytes on `bar`;
+// both addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, int b_signed, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_unsigned), "r"(b_signed), "r"(c));
+  return d;
+}
+
+// ---------------------------------------------------------------- activations
+// the 256 quantized activations of span b of chunk c, one column
+struct Act256 {
+  int a[64];
+  int bs[8];   // Q8_K: sums of the 8 sub-blocks of 32 (pairs of 16-wide bsums); unused for Q8_0
+  int bs16[16];
+  float d[8];  // Q8_K: d[0]; Q8_0: the 8 block scales
+};
+
+template <bool KQ, bool NEED16>
+__device__ __forceinline__ void load_act(Act256& x, const ActPlanes& act, int col, int chunk, int b) {
+  const int64_t e0 = (int64_t)chunk * CHUNK + 256 * b;
+  const int4* q = reinterpret_cast<const int4*>(act.qs + col * act.col_stride_qs + e0);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int4 v = __ldg(q + i);
+    x.a[4 * i + 0] = v.x; x.a[4 * i + 1] = v.y; x.a[4 * i + 2] = v.z; x.a[4 * i + 3] = v.w;
+  }
+  if constexpr (KQ) {
+    const int4* s = reinterpret_cast<const int4*>(act.bsums + col * act.col_stride_bs + e0 / 16);
+    const int4 s0 = __ldg(s), s1 = __ldg(s + 1);
+    const int w[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int lo = (int)(short)(w[j] & 0xffff), hi = w[j] >> 16;
+      x.bs[j] = lo + hi;
+      if constexpr (NEED16) { x.bs16[2 * j] = lo; x.bs16[2 * j + 1] = hi; }
+    }
+    x.d[0] = __ldg(act.d + col * act.col_stride_d + e0 / QK_K);
+  } else {
+    const float4* dd = reinterpret_cast<const float4*>(act.d + col * act.col_stride_d + e0 / 32);
+    const float4 d0 = __ldg(dd), d1 = __ldg(dd + 1);
+    x.d[0] = d0.x; x.d[1] = d0.y; x.d[2] = d0.z; x.d[3] = d0.w;
+    x.d[4] = d1.x; x.d[5] = d1.y; x.d[6] = d1.z; x.d[7] = d1.w;
+  }
+}
+
+// ---------------------------------------------------------------- block values
+// Q4_K super-block at a 16-byte aligned shared address: value of the block
+// against the lane's activations, fma(d*dx, isum, -(dmin*dx)*msum)
+// (src/emel/kernel/x86_64/actions.hpp:859-866); scales/mins per
+// get_scale_min_k4 through the kmask word shuffle (:793-801)
+__device__ __forceinline__ float q4_k_block_value(const uint8_t* blk, const Act256& x) {
+  const uint4 h = *reinterpret_cast<const uint4*>(blk);
+  const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
+  const uint32_t sc_lo = s0 & 0x3f3f3f3fu;                                        // scales 0..3
+  const uint32_t mn_lo = s1 & 0x3f3f3f3fu;                                        // mins 0..3
+  const uint32_t sc_hi = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);   // scales 4..7
+  const uint32_t mn_hi = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+  int isum = 0, msum = 0;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const uint4 v0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * r);
+    const uint4 v1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * r);
+    const uint32_t q[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    int lo = 0, hi16 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo = __dp4a((int)(q[i] & 0x0f0f0f0fu), x.a[16 * r + i], lo);
+      hi16 = dp4a_us(q[i] & 0xf0f0f0f0u, x.a[16 * r + 8 + i], hi16);   // 16 x the high-nibble dot
+    }
+    const uint32_t scw = r < 2 ? sc_lo : sc_hi, mnw = r < 2 ? mn_lo : mn_hi;
+    const int sh = 16 * (r & 1);
+    isum += (int)((scw >> sh) & 0xff) * lo + (int)((scw >> (sh + 8)) & 0xff) * (hi16 >> 4);
+    msum += (int)((mnw >> sh) & 0xff) * x.bs[2 * r] + (int)((mnw >> (sh + 8)) & 0xff) * x.bs[2 * r + 1];
+  }
+  const float d = h2f((uint16_t)(h.x & 0xffffu)), dmin = h2f((uint16_t)(h.x >> 16));
+  const float d_all = __fmul_rn(x.d[0], d), d_min = __fmul_rn(x.d[0], dmin);
+  return __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, (float)msum));
+}
+
+// Q6_K super-block at a 2-byte aligned shared address (210-byte blocks): the 52
+// payload words are realigned with funnel shifts, then
+// (dx*d) * sum_g scale_g * (dot16_g - 32*bsum_g)
+// (src/emel/kernel/x86_64/actions.hpp:1036-1077; layout src/emel/kernel/detail.hpp:592-629)
+__device__ __forceinline__ float q6_k_block_value(const uint8_t* blk, const Act256& x) {
+  const uint32_t addr = smem_u32(blk);
+  const uint32_t base = addr & ~3u;
+  const int sh = (addr & 2u) * 8;
+  uint32_t w[53];
+#pragma unroll
+  for (int i = 0; i < 53; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[i]) : "r"(base + 4 * i));
+  uint32_t u[52];  // ql: u[0..31], qh: u[32..47], scales: u[48..51]
+#pragma unroll
+  for (int i = 0; i < 52; ++i) u[i] = __funnelshift_r(w[i], w[i + 1], sh);
+  const uint32_t dbits = sh ? (w[52] >> 16) : (w[52] & 0xffffu);
+  int isum = 0;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    int s[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) s[g] = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t qa = u[16 * n + i], qb = u[16 * n + 8 + i], qh = u[32 + 8 * n + i];
+      const uint32_t v1 = (qa & 0x0f0f0f0fu) | ((qh & 0x03030303u) << 4);
+      const uint32_t v2 = (qb & 0x0f0f0f0fu) | (((qh >> 2) & 0x03030303u) << 4);
+      const uint32_t v3 = ((qa >> 4) & 0x0f0f0f0fu) | (((qh >> 4) & 0x03030303u) << 4);
+      const uint32_t v4 = ((qb >> 4) & 0x0f0f0f0fu) | (((qh >> 6) & 0x03030303u) << 4);
+      const int g = i >> 2;  // which 16-wide group inside each 32-wide quarter
+      s[0 + g] = __dp4a((int)v1, x.a[32 * n + i], s[0 + g]);
+      s[2 + g] = __dp4a((int)v2, x.a[32 * n + 8 + i], s[2 + g]);
+      s[4 + g] = __dp4a((int)v3, x.a[32 * n + 16 + i], s[4 + g]);
+      s[6 + g] = __dp4a((int)v4, x.a[32 * n + 24 + i], s[6 + g]);
+    }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const int sc = (int)(int8_t)((u[48 + 2 * n + (g >> 2)] >> (8 * (g & 3))) & 0xff);
+      isum += sc * (s[g] - 32 * x.bs16[8 * n + g]);
+    }
+  }
+  return __fmul_rn(__fmul_rn(x.d[0], h2f((uint16_t)dbits)), (float)isum);
+}
+
+// eight consecutive Q8_0 blocks = 272 bytes at a 16-byte aligned shared address;
+// per block (float)sumi * (h(dw) * h(dx)) (src/emel/kernel/detail.hpp:3257-3266)
+__device__ __forceinline__ void q8_0_block_values(const uint8_t* span, const Act256& x, float (&bv)[8]) {
+  uint32_t w[68];
+#pragma unroll
+  for (int i = 0; i < 17; ++i) {
+    const uint4 v = *reinterpret_cast<const uint4*>(span + 16 * i);
+    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int w0 = 17 * (j >> 1) + ((j & 1) ? 8 : 0);
+    int s = 0;
+    float dw;
+    if ((j & 1) == 0) {
+      dw = h2f((uint16_t)(w[w0] & 0xffffu));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s = __dp4a((int)__funnelshift_r(w[w0 + i], w[w0 + i + 1], 16), x.a[8 * j + i], s);
+    } else {
+      dw = h2f((uint16_t)(w[w0] >> 16));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s = __dp4a((int)w[w0 + 1 + i], x.a[8 * j + i], s);
+    }
+    bv[j] = __fmul_rn((float)s, __fmul_rn(dw, x.d[j]));
+  }
+}
+
+// eight consecutive Q4_0 blocks = 144 bytes; element l = low nibble of byte l,
+// element l+16 = high nibble, value = nibble - 8 (src/emel/kernel/detail.hpp:3131-3153)
+__device__ __forceinline__ void q4_0_block_values(const uint8_t* span, const Act256& x, float (&bv)[8]) {
+  uint32_t w[36];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) {
+    const uint4 v = *reinterpret_cast<const uint4*>(span + 16 * i);
+    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int w0 = 9 * (j >> 1) + ((j & 1) ? 4 : 0);
+    int s = 0, t = 0;
+    float dw;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t q;
+      if ((j & 1) == 0) q = __funnelshift_r(w[w0 + i], w[w0 + i + 1], 16);
+      else q = w[w0 + 1 + i];
+      s = __dp4a((int)(q & 0x0f0f0f0fu), x.a[8 * j + i], s);
+      s = __dp4a((int)((q >> 4) & 0x0f0f0f0fu), x.a[8 * j + 4 + i], s);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t = __dp4a(0x01010101, x.a[8 * j + i], t);
+    dw = (j & 1) == 0 ? h2f((uint16_t)(w[w0] & 0xffffu)) : h2f((uint16_t)(w[w0] >> 16));
+    bv[j] = __fmul_rn((float)(s - 8 * t), __fmul_rn(dw, x.d[j]));
+  }
+}
+
+// ---------------------------------------------------------------- kernel
+template <int T, int STAGES>
+__host__ __device__ constexpr int warp_bytes2() {
+  // stage ring + STAGES mbarriers + STAGES (task, chunk, pass) records, 16-byte rounded
+  return STAGES * ROWS_PER_STAGE * Geo2<T>::CB + ((STAGES * 8 + STAGES * 16 + 15) / 16) * 16;
+}
+
+constexpr int kWaitLimit = 1 << 22;
+
+// One task = 4*RP rows (RP passes of 4 rows); its items run chunk-major, pass-minor,
+// so a row meets its chunks in ascending order and the activations of a chunk serve
+// all passes.
+template <int T, int NCOLS, int RP, int STAGES, int WARPS, bool ARGMAX>
+__global__ void __launch_bounds__(WARPS * 32)
+gemv2_kernel(const GemvArgs p) {
+  constexpr int CB = Geo2<T>::CB;
+  constexpr bool KQ = is_k_type(T);
+  constexpr int SPAN = CB / 8;  // bytes of 256 weights of one row
+  extern __shared__ __align__(128) uint8_t smem2[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint8_t* ring = smem2 + (size_t)warp * warp_bytes2<T, STAGES>();
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + STAGES * ROWS_PER_STAGE * CB);
+  int* meta = reinterpret_cast<int*>(bars + STAGES);  // 4 ints per stage: task, chunk, pass, -
+
+  const int nchunks = p.K / CHUNK;
+  const int rows_per_task = ROWS_PER_STAGE * RP;
+  const int ntasks = (p.M + rows_per_task - 1) / rows_per_task;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bars + s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+
+  int iss_task = 0, iss_chunk = nchunks, iss_pass = 0;
+  bool drained = false;
+  auto issue_next = [&](int slot) {
+    if (!drained) {
+      if (iss_chunk == nchunks) {  // previous task finished: take the next one
+        int t = 0;
+        if (lane == 0) t = atomicAdd(p.sched, 1);
+        iss_task = __shfl_sync(0xffffffffu, t, 0);
+        iss_chunk = 0;
+        iss_pass = 0;
+        drained = iss_task >= ntasks;
+      }
+    }
+    if (lane == 0) {
+      meta[4 * slot] = drained ? -1 : iss_task;
+      meta[4 * slot + 1] = iss_chunk;
+      meta[4 * slot + 2] = iss_pass;
+      if (!drained) {
+        uint8_t* dst = ring + (size_t)slot * ROWS_PER_STAGE * CB;
+        mbar_expect_tx(bars + slot, ROWS_PER_STAGE * CB);
+        const int row0 = iss_task * rows_per_task + iss_pass * ROWS_PER_STAGE;
+#pragma unroll
+        for (int r = 0; r < ROWS_PER_STAGE; ++r) {
+          const int row = min(row0 + r, p.M - 1);
+          bulk_g2s(dst + r * CB, p.W + (size_t)row * p.row_bytes + (size_t)iss_chunk * CB, CB, bars + slot);
+        }
+      }
+    }
+    if (!drained) {
+      if (++iss_pass == RP) { iss_pass = 0; ++iss_chunk; }
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue_next(s);
+
+  const int r4 = lane >> 3, b = lane & 7;
+  float acc[RP][NCOLS];
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  uint32_t phase = 0;
+  int slot_c = 0, slot_i = STAGES - 1;
+  bool failed = false;
+  Act256 x;
+  int x_task = -1, x_chunk = -1;
+
+  for (;;) {
+    issue_next(slot_i);
+    slot_i = slot_i + 1 == STAGES ? 0 : slot_i + 1;
+    __syncwarp();
+    const int task = meta[4 * slot_c], c = meta[4 * slot_c + 1], pass = meta[4 * slot_c + 2];
+    if (task < 0) break;
+    {
+      int spins = 0;
+      bool ok = false;
+      while (!(ok = mbar_try_wait(bars + slot_c, (phase >> slot_c) & 1u)) && ++spins < kWaitLimit) {}
+      if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
+      phase ^= 1u << slot_c;
+    }
+    if (c == 0) {
+#pragma unroll
+      for (int j = 0; j < NCOLS; ++j) {
+#pragma unroll
+        for (int q = 0; q < RP; ++q)
+          if (q == pass) acc[q][j] = 0.0f;
+      }
+    }
+    const uint8_t* st = ring + (size_t)slot_c * ROWS_PER_STAGE * CB + r4 * CB;
+#pragma unroll
+    for (int j = 0; j < NCOLS; ++j) {
+      if (NCOLS > 1 || x_task != task || x_chunk != c) {
+        load_act<KQ, T == T_Q6_K>(x, p.act, p.col0 + j, c, b);
+        x_task = task;
+        x_chunk = c;
+      }
+      float s = 0.0f;
+#pragma unroll
+      for (int q = 0; q < RP; ++q)
+        if (q == pass) s = acc[q][j];
+      if constexpr (KQ) {
+        float bv;
+        if constexpr (T == T_Q4_K) bv = q4_k_block_value(st + b * SPAN, x);
+        else bv = q6_k_block_value(st + b * SPAN, x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = __fadd_rn(s, __shfl_sync(0xffffffffu, bv, (lane & ~7) + i));
+      } else {
+        float bv[8];
+        if constexpr (T == T_Q8_0) q8_0_block_values(st + b * SPAN, x, bv);
+        else q4_0_block_values(st + b * SPAN, x, bv);
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s = __fadd_rn(s, __shfl_sync(0xffffffffu, bv[i], (lane & ~7) + g));
+      }
+#pragma unroll
+      for (int q = 0; q < RP; ++q)
+        if (q == pass) acc[q][j] = s;
+      if (c == nchunks - 1) {
+        const int row = task * rows_per_task + pass * ROWS_PER_STAGE + r4;
+        if (row < p.M) {
+          if constexpr (ARGMAX) {
+            if (s > best || best_i == 0x7fffffff) { best = s; best_i = row; }
+          } else if (b == 0) {
+            const size_t o = (size_t)row * p.ldy + p.col0 + j;
+            p.y[o] = p.residual ? __fadd_rn(p.residual[o], s) : s;
+          }
+        }
+      }
+    }
+    __syncwarp();  // the stage is free for the next bulk copy
+    slot_c = slot_c + 1 == STAGES ? 0 : slot_c + 1;
+  }
+  if (failed && lane == 0 && p.status) atomicExch(p.status, 1);
+
+  // the last block to finish rearms the task counter for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
+  }
+
+  if constexpr (ARGMAX) {
+    // lanes of a warp hold different rows: lowest row among the maxima wins
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (oi != 0x7fffffff && (best_i == 0x7fffffff || ov > best || (ov == best && oi < best_i))) { best = ov; best_i = oi; }
+    }
+    __shared__ float sv[WARPS];
+    __shared__ int si[WARPS];
+    if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float bvv = sv[0]; int bi = si[0];
+      for (int w = 1; w < WARPS; ++w)
+        if (si[w] != 0x7fffffff && (bi == 0x7fffffff || sv[w] > bvv || (sv[w] == bvv && si[w] < bi))) { bvv = sv[w]; bi = si[w]; }
+      p.part_val[blockIdx.x] = bvv;
+      p.part_idx[blockIdx.x] = bi;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- launch
+constexpr int kWarps2 = 4;
+
+template <int T> constexpr int stages_for() { return (T == T_Q4_K || T == T_Q4_0) ? 4 : 3; }
+
+template <int T, int NCOLS, int RP, bool ARGMAX>
+cudaError_t launch2(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
+  constexpr int STAGES = stages_for<T>();
+  constexpr size_t smem = (size_t)kWarps2 * warp_bytes2<T, STAGES>();
+  auto kern = gemv2_kernel<T, NCOLS, RP, STAGES, kWarps2, ARGMAX>;
+  static unsigned configured = 0;  // per instantiation, one bit per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(configured & (1u << (dev & 31)))) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured |= 1u << (dev & 31);
+  }
+  const int rows_per_task = ROWS_PER_STAGE * RP;
+  const int ntasks = (a.M + rows_per_task - 1) / rows_per_task;
+  int per_sm = (int)((220 * 1024) / smem);
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 6) per_sm = 6;
+  int grid = (ntasks + kWarps2 - 1) / kWarps2;
+  if (grid > sm_count * per_sm) grid = sm_count * per_sm;
+  if (ARGMAX && grid > kMaxArgmaxParts) grid = kMaxArgmaxParts;
+  if (grid_out) *grid_out = grid;
+  kern<<<grid, kWarps2 * 32, smem, st>>>(a);
+  return cudaGetLastError();
+}
+
+inline int passes_override() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("EMELB_GEMV_RP");
+    v = e ? atoi(e) : 0;
+  }
+  return v;
+}
+
+template <int T>
+cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaStream_t st, int* launches, int* grid_out) {
+  // two 4-row passes per task once there are plenty of rows: the activation
+  // registers of a chunk then serve 8 rows
+  int rp = a.M >= 8192 ? 2 : 1;
+  if (passes_override() > 0) rp = passes_override();
+  if (argmax) {
+    ++*launches;
+    return rp >= 2 ? launch2<T, 1, 2, true>(a, sm_count, st, grid_out) : launch2<T, 1, 1, true>(a, sm_count, st, grid_out);
+  }
+  cudaError_t e = cudaSuccess;
+  int done = 0;
+  while (done < ncols && e == cudaSuccess) {
+    GemvArgs b = a;
+    b.col0 = a.col0 + done;
+    const int left = ncols - done;
+    if (left >= 8) { e = launch2<T, 8, 1, false>(b, sm_count, st, grid_out); done += 8; }
+    else if (left >= 4) { e = launch2<T, 4, 1, false>(b, sm_count, st, grid_out); done += 4; }
+    else if (left >= 2) { e = launch2<T, 2, 1, false>(b, sm_count, st, grid_out); done += 2; }
+    else {
+      e = rp >= 2 ? launch2<T, 1, 2, false>(b, sm_count, st, grid_out) : launch2<T, 1, 1, false>(b, sm_count, st, grid_out);
+      done += 1;
+    }
+    ++*launches;
+  }
+  return e;
+}
+
+}  // namespace
+
+// the streaming path for K % 2048 == 0 and 16-byte aligned rows; the caller runs the
+// argmax finishing kernel over *grid_out candidates
+cudaError_t launch_gemv_stream2(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
+                                int* launches, int* grid_out) {
+  switch (type) {
+    case T_Q4_K: return launch_type2<T_Q4_K>(a, ncols, argmax, sm_count, st, launches, grid_out);
+    case T_Q6_K: return launch_type2<T_Q6_K>(a, ncols, argmax, sm_count, st, launches, grid_out);
+    case T_Q8_0: return launch_type2<T_Q8_0>(a, ncols, argmax, sm_count, st, launches, grid_out);
+    case T_Q4_0: return launch_type2<T_Q4_0>(a, ncols, argmax, sm_count, st, launches, grid_out);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace emelb

@@ -22,6 +22,7 @@ struct GemvArgs {
   int64_t ldy;
   const float* residual; // optional: y = residual + W x  (same indexing as y)
   int* sched;            // {next task, finished blocks}: zero between launches (self-rearming)
+  int* status;           // optional: set to 1 by a kernel whose bounded wait ran out
   float* part_val;       // argmax: per-block candidates (kMaxArgmaxParts)
   int* part_idx;
   float* best_val;       // argmax result
@@ -32,6 +33,10 @@ struct GemvArgs {
 bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K);
 cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
                         int* launches);
+
+// gemv2.cu
+cudaError_t launch_gemv_stream2(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
+                                int* launches, int* grid_out);
 
 cudaError_t launch_argmax_f32(const float* x, int n, float* out_val, int* out_idx, cudaStream_t st);
 

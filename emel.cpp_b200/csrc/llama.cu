@@ -123,6 +123,7 @@ struct Enqueue {
     a.ldy = 1;
     a.residual = residual;
     a.sched = s->c->gemv_sched;
+    a.status = s->c->gemv_sched + 2;
     a.part_val = s->c->part_val;
     a.part_idx = s->c->part_idx;
     a.best_val = s->c->best_val;

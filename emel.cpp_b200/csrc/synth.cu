@@ -39,8 +39,9 @@ __global__ void encode_k_kernel(int type, uint8_t* out, uint64_t nblocks, uint64
   if (b >= nblocks) return;
   float x[256];
   for (int i = 0; i < 256; ++i) x[i] = sigma * normal_at(seed, elem_offset + b * 256 + i);
+  uint8_t blk[Q6_K_BYTES];
+  uint8_t* const y = blk;
   if (type == T_Q4_K) {
-    uint8_t* y = out + b * Q4_K_BYTES;
     float sc[8], mn[8], max_sc = 0.0f, max_mn = 0.0f;
     for (int j = 0; j < 8; ++j) {
       float lo = x[32 * j], hi = x[32 * j];
@@ -79,7 +80,6 @@ __global__ void encode_k_kernel(int type, uint8_t* out, uint64_t nblocks, uint64
       }
     }
   } else {  // T_Q6_K
-    uint8_t* y = out + b * Q6_K_BYTES;
     float gs[16], mx = 0.0f;
     for (int g = 0; g < 16; ++g) {
       float am = 0.0f;
@@ -109,6 +109,10 @@ __global__ void encode_k_kernel(int type, uint8_t* out, uint64_t nblocks, uint64
         y[128 + 32 * n + l] = (uint8_t)((q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6));
       }
   }
+  // blocks are 2-byte aligned in the destination: copy as 16-bit words
+  const int bytes = type == T_Q4_K ? Q4_K_BYTES : Q6_K_BYTES;
+  uint16_t* dst = reinterpret_cast<uint16_t*>(out + b * bytes);
+  for (int i = 0; i < bytes / 2; ++i) dst[i] = (uint16_t)blk[2 * i] | ((uint16_t)blk[2 * i + 1] << 8);
 }
 
 // one thread per 32-element block
@@ -121,14 +125,14 @@ __global__ void encode_32_kernel(int type, uint8_t* out, uint64_t nblocks, uint6
     x[i] = sigma * normal_at(seed, elem_offset + b * 32 + i);
     if (fabsf(x[i]) > amax) { amax = fabsf(x[i]); mx = x[i]; }
   }
+  uint8_t blk[Q8_0_BYTES];
+  uint8_t* const y = blk;
   if (type == T_Q8_0) {
-    uint8_t* y = out + b * Q8_0_BYTES;
     const float d = amax / 127.0f, id = d != 0.0f ? 1.0f / d : 0.0f;
     const uint16_t dh = f2h_bits(d);
     y[0] = dh & 0xff; y[1] = dh >> 8;
     for (int i = 0; i < 32; ++i) y[2 + i] = (uint8_t)(int8_t)max(-127, min(127, (int)roundf(x[i] * id)));
   } else {
-    uint8_t* y = out + b * Q4_0_BYTES;
     const float d = mx / -8.0f, id = d != 0.0f ? 1.0f / d : 0.0f;
     const uint16_t dh = f2h_bits(d);
     y[0] = dh & 0xff; y[1] = dh >> 8;
@@ -138,6 +142,9 @@ __global__ void encode_32_kernel(int type, uint8_t* out, uint64_t nblocks, uint6
       y[2 + j] = (uint8_t)(a | (c << 4));
     }
   }
+  const int bytes = type == T_Q8_0 ? Q8_0_BYTES : Q4_0_BYTES;
+  uint16_t* dst = reinterpret_cast<uint16_t*>(out + b * bytes);
+  for (int i = 0; i < bytes / 2; ++i) dst[i] = (uint16_t)blk[2 * i] | ((uint16_t)blk[2 * i + 1] << 8);
 }
 
 }  // namespace
