@@ -88,6 +88,7 @@ _SIGNATURES = {
     "emelb_graph_end": [_P, C.POINTER(_P)],
     "emelb_graph_launch": [_P, _P],
     "emelb_graph_destroy": [_P, _P],
+    "emelb_mul_mat_vec_noalloc": [C.c_int, _P, C.c_int32, _P, C.c_uint64, C.c_uint64, _P, _P, C.c_char_p, C.c_uint64],
     "emelb_synth_fill": [_P, _P, C.c_int32, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64],
     "emelb_row_slice": [C.POINTER(Op), C.c_uint32, C.c_uint32, C.POINTER(Op), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
 }
@@ -314,6 +315,14 @@ class Backend:
     def synth_fill(self, dev: int, t: int, elems: int, seed: int, sigma: float, offset: int = 0) -> bool:
         """N(0, sigma) synthetic data, f32 or block-encoded on the device."""
         return self._ret(lib().emelb_synth_fill(self._h, dev, t, elems, seed, sigma, offset))
+
+
+def mul_mat_vec_noalloc(device: int, stream: int, weight_type: int, weights_dev: int, k: int, m: int, x_dev: int, y_dev: int):
+    """Context-free mat-vec that allocates nothing (fixed scratch inside the library; K <= 32768).
+    Returns (error mask, message)."""
+    buf = C.create_string_buffer(256)
+    err = lib().emelb_mul_mat_vec_noalloc(device, stream, weight_type, weights_dev, k, m, x_dev, y_dev, buf, 256)
+    return err, buf.value.decode()
 
 
 def row_slice(op: Op, lane: int, lanes: int):

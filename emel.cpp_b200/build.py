@@ -25,6 +25,7 @@ SOURCES = {
     "gemm_tc.cu": [],
     "llama.cu": [],
     "comm.cu": [],
+    "noalloc.cu": [],
     "api.cu": [],
 }
 

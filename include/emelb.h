@@ -243,6 +243,25 @@ EMELB_API uint32_t emelb_graph_end(emelb_ctx* ctx, void** graph_out);
 EMELB_API uint32_t emelb_graph_launch(emelb_ctx* ctx, void* graph);
 EMELB_API uint32_t emelb_graph_destroy(emelb_ctx* ctx, void* graph);
 
+/* ---- mat-vec for callers that cannot allocate.  No counterpart in the
+ * reference (its CPU kernels keep their scratch on the stack).  Computes
+ * y[m] = W{K, M} * x[K] like emelb_mul_mat with N = 1, for device-resident
+ * operands, without a context and without allocating anything: the quantized
+ * activations and the kernel's task counter live in a fixed array inside the
+ * library image (about 40 KB per GPU, held until the process exits).  For
+ * callers such as latency-bound serving loops or hooks where cudaMalloc is not
+ * permitted.  K <= 32768; larger K is refused with EMELB_INVALID_REQUEST and a
+ * message in error_text (optional buffer).  Calls on one device share the array:
+ * do not let two of them overlap on the GPU.  The first call on a device does a
+ * one-time address look-up; make it outside any stream capture.  `stream` is
+ * the cudaStream_t to enqueue on (NULL = default stream). ---- */
+EMELB_API uint32_t emelb_mul_mat_vec_noalloc(int device, void* stream,
+                                             int32_t weight_type,
+                                             const void* weights_dev, uint64_t k,
+                                             uint64_t m, const float* x_dev,
+                                             float* y_dev, char* error_text,
+                                             uint64_t error_text_bytes);
+
 /* ---- synthetic data (no reference counterpart; the reference's benches fill
  * buffers with closed-form patterns on the host,
  * tools/bench/text/generator/parallel_matmul_bench.cpp:177-238).  Fills `dev`
