@@ -250,6 +250,8 @@ void count_dispatch(emelb_ctx* c, int type, uint64_t n, bool argmax) {
 // ---- shared with the decoder (ctx.h)
 namespace emelb {
 
+thread_local bool g_pdl_launch = false;
+
 ActPlanesMut ctx_planes(emelb_ctx* c) { return ActPlanesMut{c->act_qs, c->act_d, c->act_bsums}; }
 
 ActPlanes planes_view(const ActPlanesMut& m, int type, int K) {
@@ -290,6 +292,9 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
     const uint64_t mb = v ? std::strtoull(v, nullptr, 10) : def_mb;
     return (mb ? mb : def_mb) << 20;
   };
+  // EMELB_PDL=1: the decoder launches its kernel chain with programmatic stream serialization, so a
+  // mat-vec starts prefetching weights while the kernel before it is still finishing
+  c->pdl = std::getenv("EMELB_PDL") && std::atoi(std::getenv("EMELB_PDL")) != 0 ? 1 : 0;
   c->stage_in_bytes = env_mb("EMELB_STAGE_IN_MB", 128);
   c->stage_out_bytes = env_mb("EMELB_STAGE_OUT_MB", 128);
   c->act_capacity = env_mb("EMELB_ACT_MELEMS", 64);  // quantized activation elements held at once
@@ -299,8 +304,8 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
   ok = ok && cudaMalloc(&c->act_qs, c->act_capacity) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_d, c->act_capacity / 32 * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_bsums, c->act_capacity / 16 * sizeof(int16_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&c->gemv_sched, 4 * sizeof(int)) == cudaSuccess;
-  ok = ok && cudaMemset(c->gemv_sched, 0, 4 * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMalloc(&c->gemv_sched, (2 * kSchedSlots + 2) * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(c->gemv_sched, 0, (2 * kSchedSlots + 2) * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_val, kMaxArgmaxParts * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_idx, kMaxArgmaxParts * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->best_val, sizeof(float)) == cudaSuccess;
@@ -341,9 +346,9 @@ uint32_t emelb_sync(emelb_ctx* c) {
   if (!cuda_ok(c, cudaStreamSynchronize(c->stream))) return EMELB_INTERNAL_ERROR;
   // a kernel whose bounded wait ran out leaves 1 in the status word
   int status = 0;
-  if (!cuda_ok(c, cudaMemcpy(&status, c->gemv_sched + 2, sizeof(int), cudaMemcpyDeviceToHost))) return EMELB_INTERNAL_ERROR;
+  if (!cuda_ok(c, cudaMemcpy(&status, c->status_word(), sizeof(int), cudaMemcpyDeviceToHost))) return EMELB_INTERNAL_ERROR;
   if (status != 0) {
-    cudaMemset(c->gemv_sched, 0, 4 * sizeof(int));
+    cudaMemset(c->gemv_sched, 0, (2 * kSchedSlots + 2) * sizeof(int));
     return EMELB_INTERNAL_ERROR;
   }
   return EMELB_OK;
@@ -514,8 +519,8 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
   a.y = static_cast<float*>(out.dev);
   a.ldy = (int64_t)n;
   a.residual = nullptr;
-  a.sched = c->gemv_sched;
-  a.status = c->gemv_sched + 2;
+  a.sched = c->next_sched();
+  a.status = c->status_word();
   a.part_val = c->part_val;
   a.part_idx = c->part_idx;
   a.best_val = c->best_val;
@@ -539,6 +544,7 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
       ok = cuda_ok(c, quantize_into_planes(t, static_cast<const float*>(x) + j0, (int)n, cols, K, planes, c->stream));
       ++launches;
       GemvArgs b = a;
+      b.sched = c->next_sched();
       b.col0 = 0;
       b.y = a.y + j0;
       if (argmax) b.y = nullptr;

@@ -60,6 +60,8 @@ __device__ __forceinline__ void block_reduce(float (&v)[NREP], float* scratch /*
 
 template <int D, int NREP>
 __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int DPL = D / 8;   // dims per lane while scoring (8 lanes per token row)
   constexpr int TPR = D / 8;   // threads per token row while accumulating V (8 halves each)
   constexpr int SLOTS = 128 / TPR;
@@ -212,6 +214,8 @@ __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
 
 // merge the ranges: out = sum_s e^{m_s-M} acc_s / sum_s e^{m_s-M} l_s
 __global__ void flash_merge_kernel(const FlashArgs a) {
+  pdl_trigger();
+  pdl_wait();
   const int h = blockIdx.x, D = a.head_dim;
   const float* ml = a.part_ml + (size_t)h * a.splits * 2;
   float M = -INFINITY;
@@ -242,6 +246,8 @@ __global__ void flash_merge_kernel(const FlashArgs a) {
 //    src/emel/kernel/x86_64/actions.hpp:1388-1446).  Warp lane L = 8j + l plays
 //    lane l of accumulator j, so every rounding happens where the AVX2 code has it.
 __global__ void __launch_bounds__(128) flash_ref_scores_kernel(const FlashArgs a, float* scores, int t_stride, int order) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
   const int h = blockIdx.y;
@@ -276,6 +282,8 @@ __device__ __forceinline__ float round16(float v) { return __half2float(__float2
 // scale_f16_buffer_scalar (:4312-4320) and axpy_f16_buffer_scalar (:4322-4332).
 template <int DPT>
 __global__ void flash_ref_sequential_kernel(const FlashArgs a, const float* scores, int t_stride) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float s_sc[256];
   const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
   const int h = blockIdx.x, D = a.head_dim;
@@ -321,11 +329,11 @@ __global__ void flash_ref_sequential_kernel(const FlashArgs a, const float* scor
 template <int D>
 cudaError_t launch_split(const FlashArgs& a, int n_rep, cudaStream_t st) {
   if (n_rep % 4 == 0) {
-    flash_split_kernel<D, 4><<<dim3(a.splits, a.kv_heads, n_rep / 4), 128, 0, st>>>(a);
+    EMELB_LAUNCH((flash_split_kernel<D, 4>), dim3(a.splits, a.kv_heads, n_rep / 4), 128, 0, st, a);
   } else if (n_rep % 2 == 0) {
-    flash_split_kernel<D, 2><<<dim3(a.splits, a.kv_heads, n_rep / 2), 128, 0, st>>>(a);
+    EMELB_LAUNCH((flash_split_kernel<D, 2>), dim3(a.splits, a.kv_heads, n_rep / 2), 128, 0, st, a);
   } else {
-    flash_split_kernel<D, 1><<<dim3(a.splits, a.kv_heads, n_rep), 128, 0, st>>>(a);
+    EMELB_LAUNCH((flash_split_kernel<D, 1>), dim3(a.splits, a.kv_heads, n_rep), 128, 0, st, a);
   }
   return cudaGetLastError();
 }
@@ -354,7 +362,7 @@ cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t s
   const int n_rep = a.heads / a.kv_heads;
   cudaError_t e = a.head_dim == 64 ? launch_split<64>(a, n_rep, st) : launch_split<128>(a, n_rep, st);
   if (e != cudaSuccess) return e;
-  flash_merge_kernel<<<a.heads, 128, 0, st>>>(a);
+  EMELB_LAUNCH(flash_merge_kernel, a.heads, 128, 0, st, a);
   *launches += 2;
   return cudaGetLastError();
 }
@@ -363,13 +371,13 @@ cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, in
                                          int* launches) {
   int gx = (a.tokens + 3) / 4;
   if (gx > 1024) gx = 1024;
-  flash_ref_scores_kernel<<<dim3(gx, a.heads), 128, 0, st>>>(a, score_ws, t_stride, order);
+  EMELB_LAUNCH(flash_ref_scores_kernel, dim3(gx, a.heads), 128, 0, st, a, score_ws, t_stride, order);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int D = a.head_dim;
-  if (D <= 256) flash_ref_sequential_kernel<1><<<a.heads, D < 32 ? 32 : ((D + 31) / 32) * 32, 0, st>>>(a, score_ws, t_stride);
-  else if (D <= 1024) flash_ref_sequential_kernel<4><<<a.heads, 256, 0, st>>>(a, score_ws, t_stride);
-  else flash_ref_sequential_kernel<16><<<a.heads, 256, 0, st>>>(a, score_ws, t_stride);
+  if (D <= 256) EMELB_LAUNCH(flash_ref_sequential_kernel<1>, a.heads, D < 32 ? 32 : ((D + 31) / 32) * 32, 0, st, a, score_ws, t_stride);
+  else if (D <= 1024) EMELB_LAUNCH(flash_ref_sequential_kernel<4>, a.heads, 256, 0, st, a, score_ws, t_stride);
+  else EMELB_LAUNCH(flash_ref_sequential_kernel<16>, a.heads, 256, 0, st, a, score_ws, t_stride);
   *launches += 2;
   return cudaGetLastError();
 }

@@ -59,6 +59,13 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization
+// attribute may start while its predecessor still runs.  pdl_trigger lets the
+// successor start; pdl_wait returns once every predecessor grid has completed
+// and its writes are visible.  Both are no-ops for a normal launch.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

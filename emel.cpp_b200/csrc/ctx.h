@@ -49,7 +49,13 @@ struct emelb_ctx {
   uint64_t prepared_n = 0;
   uint64_t prepared_k = 0;
   bool prepared_k_family = false;
-  int* gemv_sched = nullptr;  // task counter of the streaming mat-vec kernel; [2] = status word (bounded wait ran out)
+  // task counters of the streaming mat-vec kernel: kSchedSlots {next task, finished blocks} pairs used
+  // in rotation (consecutive launches may overlap), then the status word (a bounded wait ran out)
+  int* gemv_sched = nullptr;
+  int sched_next = 0;
+  int pdl = 0;  // launch decode-chain kernels with programmatic stream serialization
+  int* next_sched() { int* p = gemv_sched + 2 * sched_next; sched_next = (sched_next + 1) % emelb::kSchedSlots; return p; }
+  int* status_word() { return gemv_sched + 2 * emelb::kSchedSlots; }
   // argmax candidates and result cells
   float* part_val = nullptr;
   int* part_idx = nullptr;

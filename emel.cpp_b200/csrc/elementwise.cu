@@ -26,6 +26,8 @@ __device__ __forceinline__ double warp_sum_f64(double v) {
 template <int FAMILY>
 __global__ void __launch_bounds__(1024)
 rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int n, float* out, ActPlanesMut planes) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ double s_part[32];
   __shared__ float s_scale;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -87,6 +89,8 @@ __global__ void rope_store_kernel(float* q, const float* k, const float* v, cons
                                   const float* __restrict__ sin_t, const int* pos_dev, int n_head, int n_head_kv,
                                   int head_dim, int rot_dim, int neox, __half* kcache, __half* vcache,
                                   int64_t cache_head_stride /*halves*/) {
+  pdl_trigger();
+  pdl_wait();
   const int pos = *pos_dev;
   const int pairs = rot_dim / 2;
   const float* ct = cos_t + (int64_t)pos * pairs;
@@ -123,6 +127,8 @@ __global__ void rope_store_kernel(float* q, const float* k, const float* v, cons
 template <int FAMILY>
 __global__ void __launch_bounds__(128)
 swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, int n, float* out, ActPlanesMut planes) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   if constexpr (FAMILY == 1) {
     const int blk = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -173,6 +179,8 @@ __device__ __forceinline__ uint16_t ld16e(const uint8_t* p) { return (uint16_t)p
 
 __global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, int64_t row_bytes, const int* token_dev,
                                  float* __restrict__ dst, int K) {
+  pdl_trigger();
+  pdl_wait();
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= K) return;
   const uint8_t* r = table + (int64_t)(*token_dev) * row_bytes;
@@ -222,6 +230,8 @@ __global__ void step_begin_kernel(int* state, int token, int position) {
   state[3] = 0;
 }
 __global__ void step_advance_kernel(int* state, const int* best_idx, int* tokens_out) {
+  pdl_trigger();
+  pdl_wait();
   const int t = *best_idx;
   tokens_out[state[3]] = t;
   state[0] = t;
@@ -235,31 +245,31 @@ __global__ void step_advance_kernel(int* state, const int* best_idx, int* tokens
 cudaError_t launch_rms_norm(const float* x, const float* w, float eps, int n, float* out, int family, ActPlanesMut planes,
                             cudaStream_t st) {
   const int threads = n >= 4096 ? 1024 : (n >= 1024 ? 256 : 128);
-  if (family == 1) rms_norm_kernel<1><<<1, threads, 0, st>>>(x, w, eps, n, out, planes);
-  else if (family == 2) rms_norm_kernel<2><<<1, threads, 0, st>>>(x, w, eps, n, out, planes);
-  else rms_norm_kernel<0><<<1, threads, 0, st>>>(x, w, eps, n, out, planes);
+  if (family == 1) EMELB_LAUNCH(rms_norm_kernel<1>, 1, threads, 0, st, x, w, eps, n, out, planes);
+  else if (family == 2) EMELB_LAUNCH(rms_norm_kernel<2>, 1, threads, 0, st, x, w, eps, n, out, planes);
+  else EMELB_LAUNCH(rms_norm_kernel<0>, 1, threads, 0, st, x, w, eps, n, out, planes);
   return cudaGetLastError();
 }
 
 cudaError_t launch_rope_store(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t,
                               const int* pos_dev, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
                               __half* kcache, __half* vcache, int64_t cache_head_stride, cudaStream_t st) {
-  rope_store_kernel<<<n_head + n_head_kv, 64, 0, st>>>(q, k, v, cos_t, sin_t, pos_dev, n_head, n_head_kv, head_dim,
+  EMELB_LAUNCH(rope_store_kernel, n_head + n_head_kv, 64, 0, st, q, k, v, cos_t, sin_t, pos_dev, n_head, n_head_kv, head_dim,
                                                        rot_dim, neox, kcache, vcache, cache_head_stride);
   return cudaGetLastError();
 }
 
 cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out, int family, ActPlanesMut planes,
                           cudaStream_t st) {
-  if (family == 1) swiglu_kernel<1><<<(n / QK_K + 3) / 4, 128, 0, st>>>(gate, up, n, out, planes);
-  else if (family == 2) swiglu_kernel<2><<<(n / 4 + 127) / 128, 128, 0, st>>>(gate, up, n, out, planes);
-  else swiglu_kernel<0><<<(n / 4 + 127) / 128, 128, 0, st>>>(gate, up, n, out, planes);
+  if (family == 1) EMELB_LAUNCH(swiglu_kernel<1>, (n / QK_K + 3) / 4, 128, 0, st, gate, up, n, out, planes);
+  else if (family == 2) EMELB_LAUNCH(swiglu_kernel<2>, (n / 4 + 127) / 128, 128, 0, st, gate, up, n, out, planes);
+  else EMELB_LAUNCH(swiglu_kernel<0>, (n / 4 + 127) / 128, 128, 0, st, gate, up, n, out, planes);
   return cudaGetLastError();
 }
 
 cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, const int* token_dev, float* dst, int K,
                              cudaStream_t st) {
-  embed_row_kernel<<<(K + 255) / 256, 256, 0, st>>>(type, table, row_bytes, token_dev, dst, K);
+  EMELB_LAUNCH(embed_row_kernel, (K + 255) / 256, 256, 0, st, type, table, row_bytes, token_dev, dst, K);
   return cudaGetLastError();
 }
 
@@ -269,7 +279,7 @@ cudaError_t launch_step_begin(int* state, int token, int position, cudaStream_t 
 }
 
 cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out, cudaStream_t st) {
-  step_advance_kernel<<<1, 1, 0, st>>>(state, best_idx, tokens_out);
+  EMELB_LAUNCH(step_advance_kernel, 1, 1, 0, st, state, best_idx, tokens_out);
   return cudaGetLastError();
 }
 

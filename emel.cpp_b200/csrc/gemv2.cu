@@ -245,6 +245,7 @@ __host__ __device__ constexpr int warp_bytes2() {
 }
 
 constexpr int kWaitLimit = 1 << 22;
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // 1 s
 
 // One task = 4*RP rows (RP passes of 4 rows); its items run chunk-major, pass-minor,
 // so a row meets its chunks in ascending order and the activations of a chunk serve
@@ -263,7 +264,11 @@ gemv2_kernel(const GemvArgs p) {
 
   const int nchunks = p.K / CHUNK;
   const int rows_per_task = ROWS_PER_STAGE * RP;
-  const int ntasks = (p.M + rows_per_task - 1) / rows_per_task;
+  // tasks of the (up to three) matrices are numbered back to back
+  const int nt0 = (p.M + rows_per_task - 1) / rows_per_task;
+  const int nt1 = (p.M2 + rows_per_task - 1) / rows_per_task;
+  const int nt2 = (p.M3 + rows_per_task - 1) / rows_per_task;
+  const int ntasks = nt0 + nt1 + nt2;
 
   if (lane == 0) {
 #pragma unroll
@@ -273,14 +278,17 @@ gemv2_kernel(const GemvArgs p) {
   }
   __syncwarp();
 
-  int iss_task = 0, iss_chunk = nchunks, iss_pass = 0;
-  bool drained = false;
+  // the first task of a warp is its global index; later ones come from the counter
+  const int total_warps = gridDim.x * WARPS;
+  int iss_task = blockIdx.x * WARPS + warp, iss_chunk = 0, iss_pass = 0;
+  bool drained = iss_task >= ntasks;
+  pdl_trigger();
   auto issue_next = [&](int slot) {
     if (!drained) {
       if (iss_chunk == nchunks) {  // previous task finished: take the next one
         int t = 0;
         if (lane == 0) t = atomicAdd(p.sched, 1);
-        iss_task = __shfl_sync(0xffffffffu, t, 0);
+        iss_task = __shfl_sync(0xffffffffu, t, 0) + total_warps;
         iss_chunk = 0;
         iss_pass = 0;
         drained = iss_task >= ntasks;
@@ -293,11 +301,15 @@ gemv2_kernel(const GemvArgs p) {
       if (!drained) {
         uint8_t* dst = ring + (size_t)slot * ROWS_PER_STAGE * CB;
         mbar_expect_tx(bars + slot, ROWS_PER_STAGE * CB);
-        const int row0 = iss_task * rows_per_task + iss_pass * ROWS_PER_STAGE;
+        const int seg = iss_task < nt0 ? 0 : (iss_task < nt0 + nt1 ? 1 : 2);
+        const int lt = iss_task - (seg == 0 ? 0 : (seg == 1 ? nt0 : nt0 + nt1));
+        const uint8_t* wbase = seg == 0 ? p.W : (seg == 1 ? p.W2 : p.W3);
+        const int mseg = seg == 0 ? p.M : (seg == 1 ? p.M2 : p.M3);
+        const int row0 = lt * rows_per_task + iss_pass * ROWS_PER_STAGE;
 #pragma unroll
         for (int r = 0; r < ROWS_PER_STAGE; ++r) {
-          const int row = min(row0 + r, p.M - 1);
-          bulk_g2s(dst + r * CB, p.W + (size_t)row * p.row_bytes + (size_t)iss_chunk * CB, CB, bars + slot);
+          const int row = min(row0 + r, mseg - 1);
+          bulk_g2s(dst + r * CB, wbase + (size_t)row * p.row_bytes + (size_t)iss_chunk * CB, CB, bars + slot);
         }
       }
     }
@@ -308,6 +320,8 @@ gemv2_kernel(const GemvArgs p) {
 
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue_next(s);
+  // weights do not depend on the previous kernel; everything read below does
+  pdl_wait();
 
   const int r4 = lane >> 3, b = lane & 7;
   float acc[RP][NCOLS];
@@ -325,10 +339,24 @@ gemv2_kernel(const GemvArgs p) {
     __syncwarp();
     const int task = meta[4 * slot_c], c = meta[4 * slot_c + 1], pass = meta[4 * slot_c + 2];
     if (task < 0) break;
+    if (NCOLS == 1 && (x_task != task || x_chunk != c)) {  // issued ahead of the wait: independent of the weights
+      load_act<KQ, T == T_Q6_K>(x, p.act, p.col0, c, b);
+      x_task = task;
+      x_chunk = c;
+    }
     {
+      // bounded twice: by poll count and by wall time (a poll may itself block for a while)
       int spins = 0;
       bool ok = false;
-      while (!(ok = mbar_try_wait(bars + slot_c, (phase >> slot_c) & 1u)) && ++spins < kWaitLimit) {}
+      unsigned long long t_start = 0;
+      while (!(ok = mbar_try_wait(bars + slot_c, (phase >> slot_c) & 1u)) && ++spins < kWaitLimit) {
+        if ((spins & 255) == 0) {
+          unsigned long long now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (t_start == 0) t_start = now;
+          else if (now - t_start > kWaitLimitNs) break;
+        }
+      }
       if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
       phase ^= 1u << slot_c;
     }
@@ -371,13 +399,17 @@ gemv2_kernel(const GemvArgs p) {
       for (int q = 0; q < RP; ++q)
         if (q == pass) acc[q][j] = s;
       if (c == nchunks - 1) {
-        const int row = task * rows_per_task + pass * ROWS_PER_STAGE + r4;
-        if (row < p.M) {
+        const int seg = task < nt0 ? 0 : (task < nt0 + nt1 ? 1 : 2);
+        const int lt = task - (seg == 0 ? 0 : (seg == 1 ? nt0 : nt0 + nt1));
+        const int mseg = seg == 0 ? p.M : (seg == 1 ? p.M2 : p.M3);
+        float* yseg = seg == 0 ? p.y : (seg == 1 ? p.y2 : p.y3);
+        const int row = lt * rows_per_task + pass * ROWS_PER_STAGE + r4;
+        if (row < mseg) {
           if constexpr (ARGMAX) {
             if (s > best || best_i == 0x7fffffff) { best = s; best_i = row; }
           } else if (b == 0) {
             const size_t o = (size_t)row * p.ldy + p.col0 + j;
-            p.y[o] = p.residual ? __fadd_rn(p.residual[o], s) : s;
+            yseg[o] = (p.residual && seg == 0) ? __fadd_rn(p.residual[o], s) : s;
           }
         }
       }
@@ -439,7 +471,8 @@ cudaError_t launch2(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_
     configured |= 1u << (dev & 31);
   }
   const int rows_per_task = ROWS_PER_STAGE * RP;
-  const int ntasks = (a.M + rows_per_task - 1) / rows_per_task;
+  const int ntasks = (a.M + rows_per_task - 1) / rows_per_task + (a.M2 + rows_per_task - 1) / rows_per_task +
+                     (a.M3 + rows_per_task - 1) / rows_per_task;
   int per_sm = (int)((220 * 1024) / smem);
   if (per_sm < 1) per_sm = 1;
   if (per_sm > 6) per_sm = 6;
@@ -447,8 +480,7 @@ cudaError_t launch2(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_
   if (grid > sm_count * per_sm) grid = sm_count * per_sm;
   if (ARGMAX && grid > kMaxArgmaxParts) grid = kMaxArgmaxParts;
   if (grid_out) *grid_out = grid;
-  kern<<<grid, kWarps2 * 32, smem, st>>>(a);
-  return cudaGetLastError();
+  return launch_kernel(kern, dim3(grid), dim3(kWarps2 * 32), smem, st, a.pdl != 0, a);
 }
 
 inline int passes_override() {
@@ -464,7 +496,7 @@ template <int T>
 cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaStream_t st, int* launches, int* grid_out) {
   // two 4-row passes per task once there are plenty of rows: the activation
   // registers of a chunk then serve 8 rows
-  int rp = a.M >= 8192 ? 2 : 1;
+  int rp = a.M + a.M2 + a.M3 >= 8192 ? 2 : 1;
   if (passes_override() > 0) rp = passes_override();
   if (argmax) {
     ++*launches;

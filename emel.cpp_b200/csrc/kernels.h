@@ -9,7 +9,31 @@
 
 namespace emelb {
 
+// kernel launch, optionally with the programmatic-stream-serialization attribute
+template <class... KArgs, class... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// set by the decoder while it enqueues a token step: launches made through EMELB_LAUNCH then carry the
+// programmatic-stream-serialization attribute (every such kernel begins with pdl_trigger(); pdl_wait();)
+extern thread_local bool g_pdl_launch;
+#define EMELB_LAUNCH(kern, grid, block, smem, st, ...) \
+  ::emelb::launch_kernel(kern, dim3(grid), dim3(block), smem, st, ::emelb::g_pdl_launch, __VA_ARGS__)
+
 constexpr int kMaxArgmaxParts = 2048;
+constexpr int kSchedSlots = 64;   // task-counter slots rotated over consecutive mat-vec launches
 
 struct GemvArgs {
   const uint8_t* W;      // {K, M} native block rows
@@ -21,8 +45,16 @@ struct GemvArgs {
   float* y;              // y[row*ldy + col]
   int64_t ldy;
   const float* residual; // optional: y = residual + W x  (same indexing as y)
+  // up to two more matrices of the same type and K multiplied by the same activations in the same
+  // launch (Q/K/V, gate/up): rows of segment s go to ys[s]; M2 = M3 = 0 when unused
+  const uint8_t* W2;
+  const uint8_t* W3;
+  int M2, M3;
+  float* y2;
+  float* y3;
   int* sched;            // {next task, finished blocks}: zero between launches (self-rearming)
   int* status;           // optional: set to 1 by a kernel whose bounded wait ran out
+  int pdl;               // launch with programmatic stream serialization (kernels wait before dependent reads)
   float* part_val;       // argmax: per-block candidates (kMaxArgmaxParts)
   int* part_idx;
   float* best_val;       // argmax result

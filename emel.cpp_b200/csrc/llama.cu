@@ -8,6 +8,7 @@
 // length live in device memory, so the chain is captured once as a CUDA graph
 // and replayed per token.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -122,13 +123,41 @@ struct Enqueue {
     a.y = y;
     a.ldy = 1;
     a.residual = residual;
-    a.sched = s->c->gemv_sched;
-    a.status = s->c->gemv_sched + 2;
+    a.sched = s->c->next_sched();
+    a.status = s->c->status_word();
+    a.pdl = s->c->pdl;
     a.part_val = s->c->part_val;
     a.part_idx = s->c->part_idx;
     a.best_val = s->c->best_val;
     a.best_idx = s->c->best_idx;
     check(launch_gemv(w.type, a, 1, argmax, s->c->sm_count, st, &launches));
+  }
+
+  // several matrices of one type and K against the same activations: one launch when the
+  // streaming kernel takes the shape, else one launch each
+  void matvec_group(const Tensor* const* w, float* const* y, int n, const float* x) {
+    bool same = n >= 2 && n <= 3;
+    for (int i = 1; same && i < n; ++i) same = w[i]->type == w[0]->type && w[i]->K == w[0]->K && w[i]->row_bytes == w[0]->row_bytes;
+    for (int i = 0; same && i < n; ++i) same = gemv_fast_path_ok(w[i]->type, w[i]->dev, w[i]->row_bytes, w[i]->K);
+    if (!same || getenv("EMELB_GEMV_V1")) {
+      for (int i = 0; i < n; ++i) matvec(*w[i], x, y[i], nullptr);
+      return;
+    }
+    ensure_planes(x, w[0]->K, family_of(w[0]->type));
+    GemvArgs a{};
+    a.W = w[0]->dev;
+    a.row_bytes = w[0]->row_bytes;
+    a.M = w[0]->M;
+    a.K = w[0]->K;
+    a.act = planes_view(planes(), w[0]->type, w[0]->K);
+    a.y = y[0];
+    a.ldy = 1;
+    a.W2 = w[1]->dev; a.M2 = w[1]->M; a.y2 = y[1];
+    if (n == 3) { a.W3 = w[2]->dev; a.M3 = w[2]->M; a.y3 = y[2]; }
+    a.sched = s->c->next_sched();
+    a.status = s->c->status_word();
+    a.pdl = s->c->pdl;
+    check(launch_gemv(w[0]->type, a, 1, false, s->c->sm_count, st, &launches));
   }
 
   void rms_norm(const float* x, const Tensor& w, int family) {
@@ -167,15 +196,21 @@ struct Enqueue {
 
   void token_step(Mode mode) {
     const emelb_llama_config& c = s->cfg;
+    struct PdlScope {  // launches of this step carry the programmatic-serialization attribute when enabled
+      explicit PdlScope(bool on) { g_pdl_launch = on; }
+      ~PdlScope() { g_pdl_launch = false; }
+    } pdl_scope(s->c->pdl != 0);
     s->planes_src = nullptr;
     check(launch_embed_row(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->state, s->hidden, c.n_embd, st));
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
       const Layer& w = s->layers[l];
       rms_norm(s->hidden, w.attn_norm, family_of(w.wq.type));
-      matvec(w.wq, s->norm, s->q, nullptr);
-      matvec(w.wk, s->norm, s->k, nullptr);
-      matvec(w.wv, s->norm, s->v, nullptr);
+      {
+        const Tensor* ws[3] = {&w.wq, &w.wk, &w.wv};
+        float* ys[3] = {s->q, s->k, s->v};
+        matvec_group(ws, ys, 3, s->norm);
+      }
       const int64_t layer_off = (int64_t)l * c.n_head_kv * s->capacity * c.head_dim;
       check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, c.n_head, c.n_head_kv, c.head_dim,
                               c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
@@ -184,8 +219,11 @@ struct Enqueue {
       attention(l);
       matvec(w.wo, s->attn, s->hidden, s->hidden);   // hidden += Wo * attn
       rms_norm(s->hidden, w.ffn_norm, family_of(w.gate.type));
-      matvec(w.gate, s->norm, s->gate, nullptr);
-      matvec(w.up, s->norm, s->up, nullptr);
+      {
+        const Tensor* ws[2] = {&w.gate, &w.up};
+        float* ys[2] = {s->gate, s->up};
+        matvec_group(ws, ys, 2, s->norm);
+      }
       check(launch_swiglu(s->gate, s->up, c.n_ff, s->ffn, family_of(w.down.type), planes(), st));
       ++launches;
       s->planes_src = s->ffn;

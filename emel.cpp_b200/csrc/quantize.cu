@@ -15,6 +15,8 @@ namespace {
 template <bool BLOCKS>
 __global__ void __launch_bounds__(128)
 quantize_q8_k_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut planes, uint8_t* blocks, int64_t row_bytes) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int blk = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int col = blockIdx.y;
@@ -43,6 +45,8 @@ quantize_q8_k_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut pla
 template <bool BLOCKS>
 __global__ void __launch_bounds__(128)
 quantize_q8_0_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut planes, uint8_t* blocks, int64_t row_bytes) {
+  pdl_trigger();
+  pdl_wait();
   const int sub = threadIdx.x & 7;
   const int blk = blockIdx.x * 16 + (threadIdx.x >> 3);
   const int col = blockIdx.y;
@@ -138,22 +142,22 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ src, int64_t src_r
 
 cudaError_t launch_quantize_q8_k_planes(const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st) {
   const dim3 grid((K / QK_K + 3) / 4, ncols);
-  quantize_q8_k_kernel<false><<<grid, 128, 0, st>>>(x, n, K, out, nullptr, 0);
+  EMELB_LAUNCH(quantize_q8_k_kernel<false>, grid, 128, 0, st, x, n, K, out, nullptr, 0);
   return cudaGetLastError();
 }
 cudaError_t launch_quantize_q8_0_planes(const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st) {
   const dim3 grid((K / QK32 + 15) / 16, ncols);
-  quantize_q8_0_kernel<false><<<grid, 128, 0, st>>>(x, n, K, out, nullptr, 0);
+  EMELB_LAUNCH(quantize_q8_0_kernel<false>, grid, 128, 0, st, x, n, K, out, nullptr, 0);
   return cudaGetLastError();
 }
 cudaError_t launch_quantize_q8_k_blocks(const float* x, int n, int K, uint8_t* out, int64_t row_bytes, cudaStream_t st) {
   const dim3 grid((K / QK_K + 3) / 4, n);
-  quantize_q8_k_kernel<true><<<grid, 128, 0, st>>>(x, n, K, ActPlanesMut{}, out, row_bytes);
+  EMELB_LAUNCH(quantize_q8_k_kernel<true>, grid, 128, 0, st, x, n, K, ActPlanesMut{}, out, row_bytes);
   return cudaGetLastError();
 }
 cudaError_t launch_quantize_q8_0_blocks(const float* x, int n, int K, uint8_t* out, int64_t row_bytes, cudaStream_t st) {
   const dim3 grid((K / QK32 + 15) / 16, n);
-  quantize_q8_0_kernel<true><<<grid, 128, 0, st>>>(x, n, K, ActPlanesMut{}, out, row_bytes);
+  EMELB_LAUNCH(quantize_q8_0_kernel<true>, grid, 128, 0, st, x, n, K, ActPlanesMut{}, out, row_bytes);
   return cudaGetLastError();
 }
 
