@@ -452,6 +452,294 @@ gemv2_kernel(const GemvArgs p) {
   }
 }
 
+// ---------------------------------------------------------------- third generation (one column)
+// Profiling the kernel above showed a warp retiring one instruction every ~13
+// cycles with only 3 warps per scheduler resident (122 registers, 18 KB of stages
+// per warp): the copies were fine (the same ring without arithmetic reaches the
+// copy roofline), the arithmetic was latency-bound.  This variant trades software
+// pipelining for thread-level parallelism: activations are staged once per CTA in
+// shared memory instead of living in 70 registers per lane, each warp keeps a
+// single (or two) 4-row stage(s), and up to 32 warps per SM overlap one another's
+// copy latency and dependent-instruction latency.
+// The eight lanes of a row read the same 16-byte unit index of eight different
+// 256-byte spans at once; stored plainly those are one bank group (an 8-way
+// conflict per load).  Unit i of span s is therefore kept at i ^ (s & 7).
+__device__ __forceinline__ int act_swizzle(int e0) { return (e0 >> 8) & 7; }
+
+struct ActSmem {
+  const int8_t* qs;     // K int8, 16-byte units swizzled inside each 256-byte span
+  const int16_t* bs;    // K/16 int16 (Q8_K only)
+  const float* d;       // K/256 (Q8_K) or K/32 (Q8_0) f32
+};
+
+__device__ __forceinline__ float q4_k_block_value_s(const uint8_t* blk, const ActSmem& x, int e0) {
+  const uint4 h = *reinterpret_cast<const uint4*>(blk);
+  const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
+  const uint32_t sc_lo = s0 & 0x3f3f3f3fu, mn_lo = s1 & 0x3f3f3f3fu;
+  const uint32_t sc_hi = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
+  const uint32_t mn_hi = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+  const int4* aq = reinterpret_cast<const int4*>(x.qs + e0);
+  const int sw = act_swizzle(e0);
+  const int4* bq = reinterpret_cast<const int4*>(x.bs + e0 / 16);
+  const int4 b0 = bq[0], b1 = bq[1];
+  const int bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  int isum = 0, msum = 0;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const uint4 v0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * r);
+    const uint4 v1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * r);
+    const int4 a0 = aq[(4 * r) ^ sw], a1 = aq[(4 * r + 1) ^ sw], a2 = aq[(4 * r + 2) ^ sw], a3 = aq[(4 * r + 3) ^ sw];
+    const uint32_t q[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    const int al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const int ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+    int lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;   // two chains each: shorter dependency paths
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      lo0 = __dp4a((int)(q[i] & 0x0f0f0f0fu), al[i], lo0);
+      lo1 = __dp4a((int)(q[i + 1] & 0x0f0f0f0fu), al[i + 1], lo1);
+      hi0 = dp4a_us(q[i] & 0xf0f0f0f0u, ah[i], hi0);
+      hi1 = dp4a_us(q[i + 1] & 0xf0f0f0f0u, ah[i + 1], hi1);
+    }
+    const uint32_t scw = r < 2 ? sc_lo : sc_hi, mnw = r < 2 ? mn_lo : mn_hi;
+    const int sh = 16 * (r & 1);
+    const int bs_lo = (int)(short)(bw[2 * r] & 0xffff) + (bw[2 * r] >> 16);
+    const int bs_hi = (int)(short)(bw[2 * r + 1] & 0xffff) + (bw[2 * r + 1] >> 16);
+    isum += (int)((scw >> sh) & 0xff) * (lo0 + lo1) + (int)((scw >> (sh + 8)) & 0xff) * ((hi0 + hi1) >> 4);
+    msum += (int)((mnw >> sh) & 0xff) * bs_lo + (int)((mnw >> (sh + 8)) & 0xff) * bs_hi;
+  }
+  const float dx = x.d[e0 / QK_K];
+  const float d = h2f((uint16_t)(h.x & 0xffffu)), dmin = h2f((uint16_t)(h.x >> 16));
+  return __fmaf_rn(__fmul_rn(dx, d), (float)isum, -__fmul_rn(__fmul_rn(dx, dmin), (float)msum));
+}
+
+// the register-resident block-value functions above, fed from the shared copy
+template <int T>
+__device__ __forceinline__ void fill_act_from_smem(Act256& x, const ActSmem& s, int e0) {
+  const int4* q = reinterpret_cast<const int4*>(s.qs + e0);
+  const int sw = act_swizzle(e0);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int4 v = q[i ^ sw];
+    x.a[4 * i + 0] = v.x; x.a[4 * i + 1] = v.y; x.a[4 * i + 2] = v.z; x.a[4 * i + 3] = v.w;
+  }
+  if constexpr (is_k_type(T)) {
+    const int4* b = reinterpret_cast<const int4*>(s.bs + e0 / 16);
+    const int4 b0 = b[0], b1 = b[1];
+    const int w[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int lo = (int)(short)(w[j] & 0xffff), hi = w[j] >> 16;
+      x.bs[j] = lo + hi;
+      x.bs16[2 * j] = lo;
+      x.bs16[2 * j + 1] = hi;
+    }
+    x.d[0] = s.d[e0 / QK_K];
+  } else {
+    const float4* dd = reinterpret_cast<const float4*>(s.d + e0 / 32);
+    const float4 d0 = dd[0], d1 = dd[1];
+    x.d[0] = d0.x; x.d[1] = d0.y; x.d[2] = d0.z; x.d[3] = d0.w;
+    x.d[4] = d1.x; x.d[5] = d1.y; x.d[6] = d1.z; x.d[7] = d1.w;
+  }
+}
+
+__host__ __device__ constexpr int act_smem_bytes(bool kq, int K) {
+  // qs | bsums (K-quants) | d ; each part 16-byte rounded
+  return ((K + 15) / 16) * 16 + (kq ? ((K / 8 + 15) / 16) * 16 : 0) + (((kq ? K / 256 : K / 32) * 4 + 15) / 16) * 16;
+}
+
+template <int T, int STAGES>
+__host__ __device__ constexpr int warp_bytes3() {
+  return STAGES * ROWS_PER_STAGE * Geo2<T>::CB + ((STAGES * 8 + STAGES * 8 + 15) / 16) * 16;  // ring + barriers + (task, chunk)
+}
+
+template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
+gemv3_kernel(const GemvArgs p) {
+  constexpr int CB = Geo2<T>::CB;
+  constexpr bool KQ = is_k_type(T);
+  constexpr int SPAN = CB / 8;
+  extern __shared__ __align__(128) uint8_t smem3[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int act_bytes = act_smem_bytes(KQ, p.K);
+  uint8_t* ring = smem3 + act_bytes + (size_t)warp * warp_bytes3<T, STAGES>();
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + STAGES * ROWS_PER_STAGE * CB);
+  int* meta = reinterpret_cast<int*>(bars + STAGES);  // 2 ints per stage: task, chunk
+
+  const int nchunks = p.K / CHUNK;
+  const int nt0 = (p.M + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
+  const int nt1 = (p.M2 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
+  const int nt2 = (p.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
+  const int ntasks = nt0 + nt1 + nt2;
+
+  pdl_trigger();
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bars + s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+
+  const int total_warps = gridDim.x * WARPS;
+  int iss_task = blockIdx.x * WARPS + warp, iss_chunk = 0;
+  bool drained = iss_task >= ntasks;
+  auto issue_next = [&](int slot) {
+    if (!drained && iss_chunk == nchunks) {
+      int t = 0;
+      if (lane == 0) t = atomicAdd(p.sched, 1);
+      iss_task = __shfl_sync(0xffffffffu, t, 0) + total_warps;
+      iss_chunk = 0;
+      drained = iss_task >= ntasks;
+    }
+    if (lane == 0) {
+      meta[2 * slot] = drained ? -1 : iss_task;
+      meta[2 * slot + 1] = iss_chunk;
+      if (!drained) {
+        const int seg = iss_task < nt0 ? 0 : (iss_task < nt0 + nt1 ? 1 : 2);
+        const int lt = iss_task - (seg == 0 ? 0 : (seg == 1 ? nt0 : nt0 + nt1));
+        const uint8_t* wbase = seg == 0 ? p.W : (seg == 1 ? p.W2 : p.W3);
+        const int mseg = seg == 0 ? p.M : (seg == 1 ? p.M2 : p.M3);
+        uint8_t* dst = ring + (size_t)slot * ROWS_PER_STAGE * CB;
+        mbar_expect_tx(bars + slot, ROWS_PER_STAGE * CB);
+#pragma unroll
+        for (int r = 0; r < ROWS_PER_STAGE; ++r) {
+          const int row = min(lt * ROWS_PER_STAGE + r, mseg - 1);
+          bulk_g2s(dst + r * CB, wbase + (size_t)row * p.row_bytes + (size_t)iss_chunk * CB, CB, bars + slot);
+        }
+      }
+    }
+    if (!drained) ++iss_chunk;
+  };
+
+  // the weight copies do not depend on the previous kernel: start them first
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) issue_next(s);
+  pdl_wait();
+
+  // stage this column's quantized activations in shared memory for the whole CTA
+  ActSmem x;
+  {
+    int8_t* sq = reinterpret_cast<int8_t*>(smem3);
+    int16_t* sb = reinterpret_cast<int16_t*>(smem3 + ((p.K + 15) / 16) * 16);
+    float* sd = reinterpret_cast<float*>(smem3 + ((p.K + 15) / 16) * 16 + (KQ ? ((p.K / 8 + 15) / 16) * 16 : 0));
+    const int4* gq = reinterpret_cast<const int4*>(p.act.qs + (int64_t)p.col0 * p.act.col_stride_qs);
+    for (int i = threadIdx.x; i < p.K / 16; i += WARPS * 32) reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = __ldg(gq + i);
+    if constexpr (KQ) {
+      const int4* gb = reinterpret_cast<const int4*>(p.act.bsums + (int64_t)p.col0 * p.act.col_stride_bs);
+      for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = __ldg(gb + i);
+    }
+    const float* gd = p.act.d + (int64_t)p.col0 * p.act.col_stride_d;
+    const int nd = KQ ? p.K / QK_K : p.K / 32;
+    for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = __ldg(gd + i);
+    x.qs = sq;
+    x.bs = sb;
+    x.d = sd;
+  }
+  __syncthreads();
+
+  const int r4 = lane >> 3, b = lane & 7;
+  float acc = 0.0f;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  uint32_t phase = 0;
+  int slot_c = 0;
+  bool failed = false;
+
+  for (;;) {
+    const int task = meta[2 * slot_c], c = meta[2 * slot_c + 1];
+    if (task < 0) break;
+    {
+      int spins = 0;
+      bool ok = false;
+      unsigned long long t_start = 0;
+      while (!(ok = mbar_try_wait(bars + slot_c, (phase >> slot_c) & 1u)) && ++spins < kWaitLimit) {
+        if ((spins & 255) == 0) {
+          unsigned long long now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (t_start == 0) t_start = now;
+          else if (now - t_start > kWaitLimitNs) break;
+        }
+      }
+      if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
+      phase ^= 1u << slot_c;
+    }
+    if (c == 0) acc = 0.0f;
+    const uint8_t* st = ring + (size_t)slot_c * ROWS_PER_STAGE * CB + r4 * CB + b * SPAN;
+    const int e0 = c * CHUNK + 256 * b;
+    if constexpr (T == T_Q4_K) {
+      const float bv = q4_k_block_value_s(st, x, e0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, bv, (lane & ~7) + i));
+    } else {
+      Act256 xr;
+      fill_act_from_smem<T>(xr, x, e0);
+      if constexpr (T == T_Q6_K) {
+        const float bv = q6_k_block_value(st, xr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, bv, (lane & ~7) + i));
+      } else {
+        float bv[8];
+        if constexpr (T == T_Q8_0) q8_0_block_values(st, xr, bv);
+        else q4_0_block_values(st, xr, bv);
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, bv[i], (lane & ~7) + g));
+      }
+    }
+    if (c == nchunks - 1) {
+      const int seg = task < nt0 ? 0 : (task < nt0 + nt1 ? 1 : 2);
+      const int lt = task - (seg == 0 ? 0 : (seg == 1 ? nt0 : nt0 + nt1));
+      const int mseg = seg == 0 ? p.M : (seg == 1 ? p.M2 : p.M3);
+      float* yseg = seg == 0 ? p.y : (seg == 1 ? p.y2 : p.y3);
+      const int row = lt * ROWS_PER_STAGE + r4;
+      if (row < mseg) {
+        if constexpr (ARGMAX) {
+          if (acc > best || best_i == 0x7fffffff) { best = acc; best_i = row; }
+        } else if (b == 0) {
+          const size_t o = (size_t)row * p.ldy + p.col0;
+          yseg[o] = (p.residual && seg == 0) ? __fadd_rn(p.residual[o], acc) : acc;
+        }
+      }
+    }
+    __syncwarp();            // the stage is free
+    issue_next(slot_c);      // refill it right away
+    __syncwarp();
+    slot_c = slot_c + 1 == STAGES ? 0 : slot_c + 1;
+  }
+  if (failed && lane == 0 && p.status) atomicExch(p.status, 1);
+
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
+  }
+
+  if constexpr (ARGMAX) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (oi != 0x7fffffff && (best_i == 0x7fffffff || ov > best || (ov == best && oi < best_i))) { best = ov; best_i = oi; }
+    }
+    __shared__ float sv[WARPS];
+    __shared__ int si[WARPS];
+    if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float bvv = sv[0]; int bi = si[0];
+      for (int w = 1; w < WARPS; ++w)
+        if (si[w] != 0x7fffffff && (bi == 0x7fffffff || sv[w] > bvv || (sv[w] == bvv && si[w] < bi))) { bvv = sv[w]; bi = si[w]; }
+      p.part_val[blockIdx.x] = bvv;
+      p.part_idx[blockIdx.x] = bi;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- launch
 constexpr int kWarps2 = 4;
 
@@ -483,6 +771,54 @@ cudaError_t launch2(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_
   return launch_kernel(kern, dim3(grid), dim3(kWarps2 * 32), smem, st, a.pdl != 0, a);
 }
 
+// third generation: one column (or the argmax head), activations in shared memory
+template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX>
+cudaError_t launch3(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
+  auto kern = gemv3_kernel<T, STAGES, WARPS, MINB, ARGMAX>;
+  const size_t smem = (size_t)act_smem_bytes(is_k_type(T), a.K) + (size_t)WARPS * warp_bytes3<T, STAGES>();
+  static size_t configured_smem[32] = {};
+  static int per_sm_cache[32] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 31;
+  if (configured_smem[dev] != smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    int n = 0;
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, WARPS * 32, smem);
+    if (e != cudaSuccess) return e;
+    if (n < 1) return cudaErrorInvalidConfiguration;
+    per_sm_cache[dev] = n;
+    configured_smem[dev] = smem;
+  }
+  const int ntasks = (a.M + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE + (a.M2 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE +
+                     (a.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
+  int grid = (ntasks + WARPS - 1) / WARPS;
+  if (grid > sm_count * per_sm_cache[dev]) grid = sm_count * per_sm_cache[dev];
+  if (ARGMAX && grid > kMaxArgmaxParts) grid = kMaxArgmaxParts;
+  if (grid_out) *grid_out = grid;
+  return launch_kernel(kern, dim3(grid), dim3(WARPS * 32), smem, st, a.pdl != 0, a);
+}
+
+inline int gen3_config() {
+  static int v = -2;
+  if (v == -2) {
+    const char* e = getenv("EMELB_GEMV_CFG");
+    v = e ? atoi(e) : 0;
+  }
+  return v;  // < 0: use the second-generation kernel for single columns too
+}
+
+template <int T, bool ARGMAX>
+cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
+  constexpr bool kLight = T == T_Q4_K || T == T_Q4_0;  // few registers: 32 warps per SM
+  switch (gen3_config()) {
+    case 1: return launch3<T, 2, 8, 2, ARGMAX>(a, sm_count, st, grid_out);
+    case 2: return launch3<T, 1, 8, 2, ARGMAX>(a, sm_count, st, grid_out);
+    case 3: return launch3<T, 2, 4, kLight ? 4 : 3, ARGMAX>(a, sm_count, st, grid_out);
+    default: return launch3<T, 1, 8, kLight ? 4 : 2, ARGMAX>(a, sm_count, st, grid_out);
+  }
+}
+
 inline int passes_override() {
   static int v = -1;
   if (v < 0) {
@@ -500,6 +836,7 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
   if (passes_override() > 0) rp = passes_override();
   if (argmax) {
     ++*launches;
+    if (gen3_config() >= 0) return launch3_cfg<T, true>(a, sm_count, st, grid_out);
     return rp >= 2 ? launch2<T, 1, 2, true>(a, sm_count, st, grid_out) : launch2<T, 1, 1, true>(a, sm_count, st, grid_out);
   }
   cudaError_t e = cudaSuccess;
@@ -511,7 +848,10 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
     if (left >= 8) { e = launch2<T, 8, 1, false>(b, sm_count, st, grid_out); done += 8; }
     else if (left >= 4) { e = launch2<T, 4, 1, false>(b, sm_count, st, grid_out); done += 4; }
     else if (left >= 2) { e = launch2<T, 2, 1, false>(b, sm_count, st, grid_out); done += 2; }
-    else {
+    else if (gen3_config() >= 0) {
+      e = launch3_cfg<T, false>(b, sm_count, st, grid_out);
+      done += 1;
+    } else {
       e = rp >= 2 ? launch2<T, 1, 2, false>(b, sm_count, st, grid_out) : launch2<T, 1, 1, false>(b, sm_count, st, grid_out);
       done += 1;
     }
