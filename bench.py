@@ -375,16 +375,27 @@ def run_decode(args):
     n_ctx = ((prompt_len + warmup + steps + 15) // 16) * 16
     be = eb.Backend(local)
     stream = torch.cuda.ExternalStream(be.stream(), device=dev)
-    cfg = el.config(sh["n_layer"], sh["n_embd"], sh["n_head"], sh["n_head_kv"], sh["head_dim"], sh["n_ff"], sh["n_vocab"], n_ctx)
+    shard = args.shard and world > 1
+    if shard:
+        import torch.distributed as dist
+        box = [eb.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        assert be.comm_init(rank, world, box[0]), be.last_error
+    G, r = (world, rank) if shard else (1, 0)
+    cfg = el.config(sh["n_layer"], sh["n_embd"], sh["n_head"], sh["n_head_kv"], sh["head_dim"], sh["n_ff"], sh["n_vocab"], n_ctx,
+                    shard_rank=r, shard_count=G)
     sess = el.Session(be, cfg)
 
     # weights N(0, 0.02) encoded on the device; norm weights 1.0 (each rank builds its own replica)
     tensors = decode_tensors(sh, out_type)
     weight_bytes, q4k_bytes, q4k_ops = 0, 0, []
     for i, (layer, role, k, m, t) in enumerate(tensors):
+        row0 = 0
+        if role != el.TOKEN_EMBD:
+            row0, m = el.shard_rows(m, r, G)     # this rank's rows of the same seeded matrix
         nbytes = m * eb.row_bytes(t, k)
         d = be.alloc(nbytes)
-        assert be.synth_fill(d, t, m * k, 5000 + i, 0.02, 0), be.last_error
+        assert be.synth_fill(d, t, m * k, 5000 + i, 0.02, row0 * k), be.last_error
         assert sess.bind_matrix(layer, role, d, t), sess.last_error
         if role != el.TOKEN_EMBD:
             weight_bytes += nbytes
@@ -398,9 +409,10 @@ def run_decode(args):
         assert sess.bind_norm(l, el.ATTN_NORM, ones) and sess.bind_norm(l, el.FFN_NORM, ones)
     assert be.sync()
 
-    prompt = np.random.Generator(np.random.PCG64(42 + rank)).integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32)
+    prompt = np.random.Generator(np.random.PCG64(42 + (0 if shard else rank))).integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32)
     t0 = time.perf_counter()
-    assert sess.prefill(prompt[:-1], 0), sess.last_error
+    if not args.profile_skip_prefill:
+        assert sess.prefill(prompt[:-1], 0), sess.last_error
     prefill_s = time.perf_counter() - t0
     pos0 = prompt_len - 1
 
@@ -463,8 +475,9 @@ def run_decode(args):
     clocks = clk.summary()
     assert list(ids) == list(ids_e), "device-fed and host-fed greedy loops disagree"
 
-    tok_s = steps * world / (ms * 1e-3)
-    tok_s_e2e = steps * world / (ms_e * 1e-3)
+    seqs = 1 if shard else world
+    tok_s = steps * seqs / (ms * 1e-3)
+    tok_s_e2e = steps * seqs / (ms_e * 1e-3)
     kv_bytes_per_pos = sh["n_layer"] * 2 * sh["n_head_kv"] * sh["head_dim"] * 2
     ctx_mid = prompt_len + warmup + steps // 2
     bytes_per_token = weight_bytes + kv_bytes_per_pos * ctx_mid
@@ -472,14 +485,18 @@ def run_decode(args):
     kernel_gbs = q4k_bytes / (ms_k * 1e-3) / 1e9
     line = {
         "metric": "decode tok/s", "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "strong" if shard else "weak", "vs_baseline": None,
         "dtype": "int8 dot (dp4a) + f32 scales; f16 KV", "data": "synthetic",
         "config": {"workload": sh["name"], "prompt_tokens": prompt_len, "decoded_tokens": steps, "n_ctx": n_ctx,
                    "launch": "one CUDA-graph replay per token; the next token id is fed back on the device",
                    "l2_policy": f"inputs larger than L2: {weight_bytes / 1e9:.2f} GB of weights streamed per token",
-                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (one sequence per GPU), no collective",
-                   "kernel_launches_per_token": sess.launches_per_token(), "prefill_s": round(prefill_s, 2)},
-        "hbm_gbs_effective": round(bytes_per_token * tok_s / world / 1e9, 1),
+                   "parallelism": "single GPU" if world == 1 else (
+                       f"one sequence, matrices row-sharded over {world} GPUs, 4 f32 all-gathers per layer (NCCL)" if shard
+                       else f"{world} independent replicas (one sequence per GPU), no collective"),
+                   "kernel_launches_per_token": sess.launches_per_token(),
+                   "prefill_s": "skipped: zero-filled KV cache, profiling aid, not a benchmark number" if args.profile_skip_prefill
+                   else round(prefill_s, 2)},
+        "hbm_gbs_effective": round(bytes_per_token * tok_s / seqs / 1e9, 1),
         "q4_k_gemv_hbm_gbs": round(kernel_gbs, 1), "pct_of_8tbs_nominal": round(100 * kernel_gbs / NOMINAL_HBM_GBS, 2),
         "e2e": {"value": round(tok_s_e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": (d1["d2h_bytes"] - d0["d2h_bytes"]) // (steps + warmup)},
@@ -600,6 +617,12 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="row count override for gemv_q4_k")
     ap.add_argument("--cols", type=int, default=None, help="column count override for gemv_q4_k")
     ap.add_argument("--cpu-budget", type=float, default=8.0)
+    ap.add_argument("--shard", action="store_true",
+                    help="decode workloads at --gpus N > 1: ONE sequence with every matrix row-sharded over the N GPUs "
+                         "(4 all-gathers per layer) instead of N independent replicas")
+    ap.add_argument("--profile-skip-prefill", action="store_true",
+                    help="decode workloads: leave the KV cache zero-filled instead of running the prompt (keeps a profiler's "
+                         "launch list short; the printed value is then not a benchmark number)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     decode = args.workload.startswith("decode")

@@ -90,6 +90,10 @@ _SIGNATURES = {
     "emelb_graph_destroy": [_P, _P],
     "emelb_mul_mat_vec_noalloc": [C.c_int, _P, C.c_int32, _P, C.c_uint64, C.c_uint64, _P, _P, C.c_char_p, C.c_uint64],
     "emelb_synth_fill": [_P, _P, C.c_int32, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64],
+    "emelb_comm_unique_id": [_P, C.c_uint64],
+    "emelb_comm_init": [_P, C.c_int32, C.c_int32, _P, C.c_uint64],
+    "emelb_comm_destroy": [_P],
+    "emelb_all_gather_rows": [_P, _P, C.c_uint64, C.c_uint64],
     "emelb_row_slice": [C.POINTER(Op), C.c_uint32, C.c_uint32, C.POINTER(Op), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
 }
 
@@ -315,6 +319,31 @@ class Backend:
     def synth_fill(self, dev: int, t: int, elems: int, seed: int, sigma: float, offset: int = 0) -> bool:
         """N(0, sigma) synthetic data, f32 or block-encoded on the device."""
         return self._ret(lib().emelb_synth_fill(self._h, dev, t, elems, seed, sigma, offset))
+
+
+    # ---- row-shard exchange (one rank per GPU)
+    def comm_init(self, rank: int, world: int, comm_id: bytes) -> bool:
+        """Join the exchange group; comm_id comes from comm_unique_id() on rank 0, broadcast by the caller."""
+        buf = (C.c_uint8 * COMM_ID_BYTES).from_buffer_copy(comm_id)
+        return self._ret(lib().emelb_comm_init(self._h, rank, world, C.addressof(buf), COMM_ID_BYTES))
+
+    def comm_destroy(self) -> bool:
+        return self._ret(lib().emelb_comm_destroy(self._h))
+
+    def all_gather_rows(self, dst_dev: int, rows_per_rank: int, row_floats: int = 1) -> bool:
+        """Join the ranks' row intervals of a full f32 result (own interval already in place)."""
+        return self._ret(lib().emelb_all_gather_rows(self._h, dst_dev, rows_per_rank, row_floats))
+
+
+COMM_ID_BYTES = 128
+
+
+def comm_unique_id() -> bytes:
+    buf = (C.c_uint8 * COMM_ID_BYTES)()
+    err = lib().emelb_comm_unique_id(C.addressof(buf), COMM_ID_BYTES)
+    if err != OK:
+        raise BackendError(f"emelb_comm_unique_id failed with error mask {err}")
+    return bytes(buf)
 
 
 def mul_mat_vec_noalloc(device: int, stream: int, weight_type: int, weights_dev: int, k: int, m: int, x_dev: int, y_dev: int):

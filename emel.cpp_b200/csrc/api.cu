@@ -275,6 +275,10 @@ cudaError_t quantize_into_planes(int wtype, const float* x, int n, int ncols, in
 
 }  // namespace emelb
 
+namespace emelb {
+void comm_release(emelb_ctx* c);  // comm.cu
+}
+
 extern "C" {
 
 uint32_t emelb_create(int device, emelb_ctx** out) {
@@ -328,6 +332,7 @@ uint32_t emelb_destroy(emelb_ctx* c) {
   if (!c) return EMELB_INVALID_REQUEST;
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
+  comm_release(c);
   for (auto& kv : c->residents)
     if (kv.second.dev) cudaFree(kv.second.dev);
   for (void* p : c->owned) cudaFree(p);

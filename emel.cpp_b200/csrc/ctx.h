@@ -71,5 +71,9 @@ struct emelb_ctx {
   std::set<void*> owned;
   std::map<uintptr_t, uint64_t> dev_ranges;  // device spans this context allocated (start -> bytes)
   bool capturing = false;
+  // row-shard exchange (comm.cu): one communicator per context, one rank per GPU
+  void* comm = nullptr;  // ncclComm_t
+  int comm_rank = 0;
+  int comm_world = 1;
   emelb_diag diag = {};
 };

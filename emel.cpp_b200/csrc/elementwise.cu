@@ -273,6 +273,36 @@ cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, 
   return cudaGetLastError();
 }
 
+// sharded greedy head: this rank's winner as {value bits, global row}, then the
+// winner over all ranks with the reference's tie rule (highest value, lowest row;
+// src/emel/kernel/detail.hpp:3720-3723)
+__global__ void argmax_pair_store_kernel(const float* best_val, const int* best_idx, int row_offset, int* pair) {
+  pair[0] = __float_as_int(*best_val);
+  pair[1] = *best_idx + row_offset;
+}
+
+__global__ void argmax_pair_finish_kernel(const int* pairs, int n, float* out_val, int* out_idx) {
+  float bv = __int_as_float(pairs[0]);
+  int bi = pairs[1];
+  for (int i = 1; i < n; ++i) {
+    const float v = __int_as_float(pairs[2 * i]);
+    const int r = pairs[2 * i + 1];
+    if (v > bv || (v == bv && r < bi)) { bv = v; bi = r; }
+  }
+  *out_val = bv;
+  *out_idx = bi;
+}
+
+cudaError_t launch_argmax_pair_store(const float* best_val, const int* best_idx, int row_offset, int* pair, cudaStream_t st) {
+  argmax_pair_store_kernel<<<1, 1, 0, st>>>(best_val, best_idx, row_offset, pair);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_pair_finish(const int* pairs, int n, float* out_val, int* out_idx, cudaStream_t st) {
+  argmax_pair_finish_kernel<<<1, 1, 0, st>>>(pairs, n, out_val, out_idx);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_step_begin(int* state, int token, int position, cudaStream_t st) {
   step_begin_kernel<<<1, 1, 0, st>>>(state, token, position);
   return cudaGetLastError();

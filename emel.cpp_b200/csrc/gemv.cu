@@ -737,6 +737,12 @@ bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K) {
 
 cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
                         int* launches) {
+  // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
+  static const bool no_tc = getenv("EMELB_NO_TC") != nullptr;
+  if (!argmax && !no_tc && gemm_tc_supported(type, a.K, ncols, a.W, a.row_bytes, a.act)) {
+    ++*launches;
+    return launch_gemm_q4k_tc(a, ncols, sm_count, st);
+  }
   const bool fast = gemv_fast_path_ok(type, a.W, a.row_bytes, a.K);
   int grid = 0;
   cudaError_t e;

@@ -810,13 +810,20 @@ inline int gen3_config() {
 
 template <int T, bool ARGMAX>
 cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
-  constexpr bool kLight = T == T_Q4_K || T == T_Q4_0;  // few registers: 32 warps per SM
+  constexpr bool kLight = T == T_Q4_K || T == T_Q4_0;  // 64 registers: 32 warps per SM; the others 16
+  constexpr int kWarpsPerSm = kLight ? 32 : 16;
   switch (gen3_config()) {
     case 1: return launch3<T, 2, 8, 2, ARGMAX>(a, sm_count, st, grid_out);
-    case 2: return launch3<T, 1, 8, 2, ARGMAX>(a, sm_count, st, grid_out);
+    case 2: return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX>(a, sm_count, st, grid_out);
     case 3: return launch3<T, 2, 4, kLight ? 4 : 3, ARGMAX>(a, sm_count, st, grid_out);
-    default: return launch3<T, 1, 8, kLight ? 4 : 2, ARGMAX>(a, sm_count, st, grid_out);
+    default: break;
   }
+  // few rows: smaller CTAs, so that every SM gets about the same number of 4-row tasks
+  const int ntasks = (a.M + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE + (a.M2 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE +
+                     (a.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
+  if (ntasks >= 8 * 3 * sm_count || ARGMAX) return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX>(a, sm_count, st, grid_out);
+  if (ntasks >= 4 * 3 * sm_count) return launch3<T, 1, 4, kWarpsPerSm / 4, ARGMAX>(a, sm_count, st, grid_out);
+  return launch3<T, 1, 2, kWarpsPerSm / 2, ARGMAX>(a, sm_count, st, grid_out);
 }
 
 inline int passes_override() {

@@ -105,6 +105,15 @@ cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, 
 cudaError_t launch_step_begin(int* state, int token, int position, cudaStream_t st);
 cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out, cudaStream_t st);
 
+// gemm_tc.cu — Q4_K x Q8_K for many columns on the tensor cores (tcgen05, TMEM accumulators);
+// same numbers as the mat-vec kernels.  a.col0/a.y/a.ldy address the output as for launch_gemv.
+constexpr int kGemmTcMinCols = 32;
+bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act);
+cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st);
+
+cudaError_t launch_argmax_pair_store(const float* best_val, const int* best_idx, int row_offset, int* pair, cudaStream_t st);
+cudaError_t launch_argmax_pair_finish(const int* pairs, int n, float* out_val, int* out_idx, cudaStream_t st);
+
 // synth.cu — synthetic N(0, sigma) data generated and block-encoded on the device
 cudaError_t launch_fill_normal(float* out, uint64_t n, uint64_t seed, float sigma, uint64_t offset, cudaStream_t st);
 cudaError_t launch_encode_normal(int type, uint8_t* out, uint64_t elems, uint64_t seed, float sigma, uint64_t offset,

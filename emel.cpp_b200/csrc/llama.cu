@@ -7,6 +7,16 @@
 // One token step is a fixed chain of kernels whose token id, position and KV
 // length live in device memory, so the chain is captured once as a CUDA graph
 // and replayed per token.
+//
+// Row sharding (shard_count = G > 1, one process per GPU): rank r holds rows
+// [r*M/G, (r+1)*M/G) of every matrix, which for Q/K/V means n_head/G query heads
+// and n_head_kv/G KV heads, so the KV cache and attention are local.  Four f32
+// all-gathers per layer join the row intervals (attention context, hidden after
+// the output projection, the SwiGLU product, hidden after the down projection);
+// every vector that gets quantized is the full, identical vector on every rank,
+// so the token stream equals the unsharded one bit for bit — the contract the
+// reference's row-slice fork/join keeps across lane counts
+// (src/emel/kernel/matmul/detail.hpp:36-57).
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -21,9 +31,7 @@ using namespace emelb;
 namespace emelb {
 const void* ctx_resolve_weights(emelb_ctx* c, const void* p);  // api.cu
 bool ctx_cuda_ok(emelb_ctx* c, cudaError_t e);
-#if defined(EMELB_HAVE_NCCL)
-cudaError_t comm_all_gather_inplace(emelb_ctx* c, float* buf, size_t count_per_rank, cudaStream_t st);  // comm.cu
-#endif
+cudaError_t comm_all_gather_bytes(emelb_ctx* c, void* buf, size_t bytes_per_rank, cudaStream_t st);  // comm.cu
 }  // namespace emelb
 
 namespace {
@@ -60,6 +68,8 @@ struct emelb_llama {
   int* tokens_dev = nullptr;  // generated ids (n_ctx)
   int* host_pinned = nullptr;
   int fa_splits = 1;
+  int G = 1, rank = 0;        // row sharding
+  int* pair_buf = nullptr;    // G x {value bits, global row} argmax candidates
   cudaGraphExec_t graphs[MODE_COUNT] = {nullptr, nullptr, nullptr};
   int graph_attention_mode[MODE_COUNT] = {-1, -1, -1};
   int launches_per_token = 0;          // of the argmax step
@@ -170,17 +180,17 @@ struct Enqueue {
 
   void attention(int layer) {
     const emelb_llama_config& c = s->cfg;
-    const int64_t layer_off = (int64_t)layer * c.n_head_kv * s->capacity * c.head_dim;
+    const int64_t layer_off = (int64_t)layer * (c.n_head_kv / s->G) * s->capacity * c.head_dim;
     FlashArgs a{};
     a.q = s->q;
     a.k = s->kcache + layer_off;
     a.v = s->vcache + layer_off;
-    a.dst = s->attn;
+    a.dst = s->attn + (size_t)s->rank * (c.n_head / s->G) * c.head_dim;
     a.k_nb1 = a.v_nb1 = 2 * c.head_dim;
     a.k_nb2 = a.v_nb2 = 2 * s->capacity * c.head_dim;
     a.head_dim = c.head_dim;
-    a.heads = c.n_head;
-    a.kv_heads = c.n_head_kv;
+    a.heads = c.n_head / s->G;
+    a.kv_heads = c.n_head_kv / s->G;
     a.tokens = c.n_ctx;            // upper bound; the live count is read on the device
     a.tokens_dev = s->state + 2;
     a.scale = 1.0f / std::sqrt((float)c.head_dim);
@@ -194,12 +204,21 @@ struct Enqueue {
     }
   }
 
+  // join the ranks' row intervals of a full-length f32 vector (no-op unsharded)
+  void gather(float* full, size_t count_per_rank) {
+    if (s->G > 1) check(comm_all_gather_bytes(s->c, full, count_per_rank * sizeof(float), st));
+  }
+
   void token_step(Mode mode) {
     const emelb_llama_config& c = s->cfg;
     struct PdlScope {  // launches of this step carry the programmatic-serialization attribute when enabled
       explicit PdlScope(bool on) { g_pdl_launch = on; }
       ~PdlScope() { g_pdl_launch = false; }
     } pdl_scope(s->c->pdl != 0);
+    const int G = s->G, r = s->rank;
+    const int heads_l = c.n_head / G, kv_l = c.n_head_kv / G;
+    const size_t q_l = (size_t)heads_l * c.head_dim, embd_l = (size_t)c.n_embd / G, ff_l = (size_t)c.n_ff / G;
+    float* hidden_mine = s->hidden + r * embd_l;
     s->planes_src = nullptr;
     check(launch_embed_row(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->state, s->hidden, c.n_embd, st));
     ++launches;
@@ -211,33 +230,52 @@ struct Enqueue {
         float* ys[3] = {s->q, s->k, s->v};
         matvec_group(ws, ys, 3, s->norm);
       }
-      const int64_t layer_off = (int64_t)l * c.n_head_kv * s->capacity * c.head_dim;
-      check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, c.n_head, c.n_head_kv, c.head_dim,
+      const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
+      check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, heads_l, kv_l, c.head_dim,
                               c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
                               s->vcache + layer_off, s->capacity * c.head_dim, st));
       ++launches;
       attention(l);
-      matvec(w.wo, s->attn, s->hidden, s->hidden);   // hidden += Wo * attn
+      gather(s->attn, q_l);
+      matvec(w.wo, s->attn, hidden_mine, hidden_mine);   // hidden += Wo * attn (this rank's rows)
+      gather(s->hidden, embd_l);
       rms_norm(s->hidden, w.ffn_norm, family_of(w.gate.type));
       {
         const Tensor* ws[2] = {&w.gate, &w.up};
         float* ys[2] = {s->gate, s->up};
         matvec_group(ws, ys, 2, s->norm);
       }
-      check(launch_swiglu(s->gate, s->up, c.n_ff, s->ffn, family_of(w.down.type), planes(), st));
+      if (G == 1) {
+        check(launch_swiglu(s->gate, s->up, c.n_ff, s->ffn, family_of(w.down.type), planes(), st));
+        s->planes_src = s->ffn;
+        s->planes_family = family_of(w.down.type);
+      } else {
+        // the product is quantized after the join, over the full vector
+        check(launch_swiglu(s->gate, s->up, (int)ff_l, s->ffn + r * ff_l, 0, planes(), st));
+        s->planes_src = nullptr;
+      }
       ++launches;
-      s->planes_src = s->ffn;
-      s->planes_family = family_of(w.down.type);
-      matvec(w.down, s->ffn, s->hidden, s->hidden);  // hidden += Wdown * ffn
+      gather(s->ffn, ff_l);
+      matvec(w.down, s->ffn, hidden_mine, hidden_mine);  // hidden += Wdown * ffn
+      gather(s->hidden, embd_l);
     }
     if (mode == MODE_PREFILL) return;
     rms_norm(s->hidden, s->out_norm, family_of(s->output.type));
+    const size_t vocab_l = (size_t)c.n_vocab / G;
     if (mode == MODE_ARGMAX) {
       matvec(s->output, s->norm, nullptr, nullptr, true);
+      if (G > 1) {
+        // candidates {value, global row} of every rank, then the same lowest-row tie rule
+        check(launch_argmax_pair_store(s->c->best_val, s->c->best_idx, (int)(r * vocab_l), s->pair_buf + 2 * r, st));
+        check(comm_all_gather_bytes(s->c, s->pair_buf, 2 * sizeof(int), st));
+        check(launch_argmax_pair_finish(s->pair_buf, G, s->c->best_val, s->c->best_idx, st));
+        launches += 2;
+      }
       check(launch_step_advance(s->state, s->c->best_idx, s->tokens_dev, st));
       ++launches;
     } else {
-      matvec(s->output, s->norm, s->logits, nullptr);
+      matvec(s->output, s->norm, s->logits + r * vocab_l, nullptr);
+      gather(s->logits, vocab_l);
     }
   }
 };
@@ -292,17 +330,24 @@ uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_l
                     g.shard_rank < g.shard_count && (int64_t)g.n_head * g.head_dim <= (int64_t)c->act_capacity &&
                     (int64_t)g.n_ff <= (int64_t)c->act_capacity;
   if (!sane) return EMELB_INVALID_REQUEST;
-  if (g.shard_count != 1) return EMELB_UNSUPPORTED_OP;
+  const int G = g.shard_count;
+  if (G > 1) {
+    // row intervals must be whole heads / whole rows on every rank, and the context's communicator must match
+    if (g.n_head_kv % G != 0 || g.n_embd % G != 0 || g.n_ff % G != 0 || g.n_vocab % G != 0) return EMELB_INVALID_REQUEST;
+    if (!c->comm || c->comm_world != G || c->comm_rank != g.shard_rank) return EMELB_INVALID_REQUEST;
+  }
   cudaSetDevice(c->device);
   emelb_llama* s = new (std::nothrow) emelb_llama();
   if (!s) return EMELB_INTERNAL_ERROR;
   s->c = c;
   s->cfg = g;
+  s->G = G;
+  s->rank = g.shard_rank;
   s->layers.resize(g.n_layer);
   const int kvb = g.kv_block > 0 ? g.kv_block : 16;
   s->capacity = ((int64_t)g.n_ctx + kvb - 1) / kvb * kvb;
   const size_t qd = (size_t)g.n_head * g.head_dim, kvd = (size_t)g.n_head_kv * g.head_dim;
-  const size_t cache_halves = (size_t)g.n_layer * g.n_head_kv * s->capacity * g.head_dim;
+  const size_t cache_halves = (size_t)g.n_layer * (g.n_head_kv / G) * s->capacity * g.head_dim;  // this rank's KV heads
   const int pairs = (g.rope_dim < g.head_dim ? g.rope_dim : g.head_dim) / 2;
   bool ok = true;
   ok = ok && dev_alloc(s, (void**)&s->hidden, 4 * (size_t)g.n_embd);
@@ -320,6 +365,7 @@ uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_l
   ok = ok && dev_alloc(s, (void**)&s->rope_cos, 4 * (size_t)g.n_ctx * pairs);
   ok = ok && dev_alloc(s, (void**)&s->rope_sin, 4 * (size_t)g.n_ctx * pairs);
   ok = ok && dev_alloc(s, (void**)&s->state, 4 * sizeof(int));
+  ok = ok && dev_alloc(s, (void**)&s->pair_buf, 2 * sizeof(int) * (size_t)G);
   ok = ok && dev_alloc(s, (void**)&s->tokens_dev, sizeof(int) * (size_t)(g.n_ctx + 8));
   ok = ok && cudaMallocHost((void**)&s->host_pinned, sizeof(int) * (size_t)(g.n_ctx + 4)) == cudaSuccess;
   if (ok) {
@@ -348,7 +394,7 @@ uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_l
   if (ok) {
     int max_splits = (int)(kFlashPartFloats / ((uint64_t)g.n_head * g.head_dim));
     if (max_splits > 64) max_splits = 64;
-    s->fa_splits = max_splits >= 1 ? flash_pick_splits(g.n_ctx, g.n_head_kv, c->sm_count, max_splits) : 1;
+    s->fa_splits = max_splits >= 1 ? flash_pick_splits(g.n_ctx, g.n_head_kv / G, c->sm_count, max_splits) : 1;
     ok = (uint64_t)g.n_head * (uint64_t)g.n_ctx <= kFlashScoreFloats;
   }
   if (!ok) {
@@ -379,18 +425,20 @@ uint32_t emelb_llama_bind(emelb_llama* s, int32_t layer, int32_t role, const eme
   const bool model_level = role <= EMELB_T_OUTPUT;
   if (role < 0 || role > EMELB_T_FFN_DOWN || (model_level ? layer != -1 : (layer < 0 || layer >= c.n_layer)))
     return EMELB_INVALID_REQUEST;
-  const int qd = c.n_head * c.head_dim, kvd = c.n_head_kv * c.head_dim;
+  // a sharded session binds this rank's row interval of each matrix (M/G rows, all K columns);
+  // the embedding table and the norm vectors are whole on every rank
+  const int qd = c.n_head * c.head_dim, kvd = c.n_head_kv * c.head_dim, G = s->G;
   int K = 0, M = 0;
   bool vector = false;
   switch (role) {
     case EMELB_T_TOKEN_EMBD: K = c.n_embd; M = c.n_vocab; break;
-    case EMELB_T_OUTPUT: K = c.n_embd; M = c.n_vocab; break;
+    case EMELB_T_OUTPUT: K = c.n_embd; M = c.n_vocab / G; break;
     case EMELB_T_OUTPUT_NORM: case EMELB_T_ATTN_NORM: case EMELB_T_FFN_NORM: K = c.n_embd; M = 1; vector = true; break;
-    case EMELB_T_ATTN_Q: K = c.n_embd; M = qd; break;
-    case EMELB_T_ATTN_K: case EMELB_T_ATTN_V: K = c.n_embd; M = kvd; break;
-    case EMELB_T_ATTN_OUT: K = qd; M = c.n_embd; break;
-    case EMELB_T_FFN_GATE: case EMELB_T_FFN_UP: K = c.n_embd; M = c.n_ff; break;
-    case EMELB_T_FFN_DOWN: K = c.n_ff; M = c.n_embd; break;
+    case EMELB_T_ATTN_Q: K = c.n_embd; M = qd / G; break;
+    case EMELB_T_ATTN_K: case EMELB_T_ATTN_V: K = c.n_embd; M = kvd / G; break;
+    case EMELB_T_ATTN_OUT: K = qd; M = c.n_embd / G; break;
+    case EMELB_T_FFN_GATE: case EMELB_T_FFN_UP: K = c.n_embd; M = c.n_ff / G; break;
+    case EMELB_T_FFN_DOWN: K = c.n_ff; M = c.n_embd / G; break;
   }
   Tensor x;
   x.type = t->type;

@@ -49,11 +49,31 @@ def config(n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx, r
 
 
 def matrix_shapes(cfg: Config):
-    """role -> (K, M) of each matrix, as emelb_llama_bind checks them."""
-    qd, kvd = cfg.n_head * cfg.head_dim, cfg.n_head_kv * cfg.head_dim
-    return {TOKEN_EMBD: (cfg.n_embd, cfg.n_vocab), OUTPUT: (cfg.n_embd, cfg.n_vocab),
-            ATTN_Q: (cfg.n_embd, qd), ATTN_K: (cfg.n_embd, kvd), ATTN_V: (cfg.n_embd, kvd), ATTN_OUT: (qd, cfg.n_embd),
-            FFN_GATE: (cfg.n_embd, cfg.n_ff), FFN_UP: (cfg.n_embd, cfg.n_ff), FFN_DOWN: (cfg.n_ff, cfg.n_embd)}
+    """role -> (K, M) of each matrix, as emelb_llama_bind checks them.  In a row-sharded session
+    (shard_count G > 1) M is this rank's interval: M/G rows, all K columns; the embedding table is whole."""
+    qd, kvd, g = cfg.n_head * cfg.head_dim, cfg.n_head_kv * cfg.head_dim, max(1, cfg.shard_count)
+    return {TOKEN_EMBD: (cfg.n_embd, cfg.n_vocab), OUTPUT: (cfg.n_embd, cfg.n_vocab // g),
+            ATTN_Q: (cfg.n_embd, qd // g), ATTN_K: (cfg.n_embd, kvd // g), ATTN_V: (cfg.n_embd, kvd // g),
+            ATTN_OUT: (qd, cfg.n_embd // g), FFN_GATE: (cfg.n_embd, cfg.n_ff // g), FFN_UP: (cfg.n_embd, cfg.n_ff // g),
+            FFN_DOWN: (cfg.n_ff, cfg.n_embd // g)}
+
+
+def shard_rows(m: int, rank: int, count: int):
+    """(first row, row count) of rank's interval of an M-row matrix: equal contiguous intervals, the split
+    the reference's fixed row slices make when M divides evenly (src/emel/kernel/matmul/actions.hpp:49-66)."""
+    if count < 1 or not 0 <= rank < count or m % count != 0:
+        raise ValueError(f"{m} rows do not split evenly over {count} ranks")
+    return rank * (m // count), m // count
+
+
+def merge_argmax_pairs(pairs):
+    """Host mirror of the sharded greedy head's last step: from each rank's (value, global row)
+    candidate, the highest value and on ties the lowest row (src/emel/kernel/detail.hpp:3720-3723)."""
+    best_v, best_r = pairs[0]
+    for v, r in pairs[1:]:
+        if v > best_v or (v == best_v and r < best_r):
+            best_v, best_r = v, r
+    return best_r
 
 
 class Session:

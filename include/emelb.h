@@ -232,6 +232,26 @@ EMELB_API uint32_t emelb_row_slice(const emelb_op* op, uint32_t lane,
                          uint32_t lane_count, emelb_op* out,
                          uint64_t* row_begin, uint64_t* row_count);
 
+/* ---- the join of the row-sliced path across GPUs.  The reference forks one
+ * op_mul_mat into lane_count disjoint dst-row intervals with a shared RHS and
+ * joins them in host memory (effect_execute_parallel,
+ * src/emel/kernel/matmul/actions.hpp:49-136; lane-count invariance
+ * docs/determinism.md:29-32).  With one process per GPU, lane = rank: each rank
+ * runs emelb_mul_mat on its emelb_row_slice and emelb_all_gather_rows joins the
+ * intervals.  dst_dev is the FULL result (rows_per_rank * world rows of
+ * row_floats f32, device memory); the caller's own interval is already in place
+ * at row rank*rows_per_rank.  Stream-ordered; every rank must call it with the
+ * same sizes.  Without a communicator (world 1) it is a no-op.
+ * emelb_comm_unique_id (rank 0) -> the caller broadcasts the id -> every rank
+ * calls emelb_comm_init once per context. ---- */
+#define EMELB_COMM_ID_BYTES 128
+EMELB_API uint32_t emelb_comm_unique_id(uint8_t* id_out, uint64_t id_bytes);
+EMELB_API uint32_t emelb_comm_init(emelb_ctx* ctx, int32_t rank, int32_t world,
+                         const uint8_t* id, uint64_t id_bytes);
+EMELB_API uint32_t emelb_comm_destroy(emelb_ctx* ctx);
+EMELB_API uint32_t emelb_all_gather_rows(emelb_ctx* ctx, float* dst_dev,
+                         uint64_t rows_per_rank, uint64_t row_floats);
+
 /* ---- stream capture (no reference counterpart: the reference dispatches
  * synchronously on the calling thread).  Between begin and end, calls whose
  * operands are all device-resident are recorded instead of run; the resulting

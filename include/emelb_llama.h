@@ -40,7 +40,17 @@ typedef struct emelb_llama_config {
   int32_t kv_block;        /* KV capacity is n_ctx rounded up to this (16 in the
                               reference, src/emel/memory/view.hpp:18,47-56) */
   int32_t shard_rank;      /* row sharding across GPUs: this rank ... */
-  int32_t shard_count;     /* ... of this many (1 = unsharded) */
+  int32_t shard_count;     /* ... of this many (1 = unsharded).  With G > 1 the
+                              context must have joined a G-rank exchange group
+                              (emelb_comm_init) as this rank; n_head_kv, n_embd,
+                              n_ff and n_vocab must be multiples of G; each
+                              matrix is bound as this rank's contiguous row
+                              interval (M/G rows: whole query/KV heads for
+                              Q/K/V), the embedding table and norms whole.
+                              Every rank calls decode/prefill/generate with
+                              the same arguments; results are identical on
+                              all ranks and equal to the unsharded session's
+                              (src/emel/kernel/matmul/detail.hpp:36-57). */
 } emelb_llama_config;
 
 /* tensor roles for emelb_llama_bind; layer = -1 for the three model-level ones */

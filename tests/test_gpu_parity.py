@@ -131,6 +131,36 @@ def test_mul_mat_parity(be, checker, port, t, k, m, n):
     assert_mul_mat_parity(got, want, checker, t)
 
 
+@pytest.mark.parametrize("k,m,n", [
+    (256, 128, 32), (512, 5, 33), (1024, 300, 130), (2048, 129, 257), (4096, 260, 64), (1280, 384, 200),
+])
+def test_mul_mat_many_columns_tensor_core_kernel(be, checker, port, k, m, n):
+    """32 or more columns of Q4_K take the tcgen05 kernel: ragged tiles in both directions, one and
+    many super-blocks, and the same bits as the mat-vec route."""
+    w = synth.encoded_weights(port, eb.Q4_K, 300 + m, m, k)
+    x = synth.activations_f32(400 + n, k, n)
+    got, want = gpu_mul_mat(be, eb.Q4_K, w, k, m, x, n), cpu_mul_mat(checker, eb.Q4_K, w, k, m, x, n)
+    assert_mul_mat_parity(got, want, checker, eb.Q4_K)
+    # the first 8 columns alone run the mat-vec kernels: identical bits
+    x8 = np.ascontiguousarray(x.reshape(k, n)[:, :8])
+    got8 = gpu_mul_mat(be, eb.Q4_K, w, k, m, x8, 8)
+    assert np.array_equal(got.reshape(m, n)[:, :8].view(np.uint32), got8.view(np.uint32))
+    assert be.sync()       # a bounded wait that ran out would surface here
+
+
+def test_mul_mat_many_columns_random_block_bytes(be, checker):
+    """Arbitrary scale/min bits (all 6-bit values, extreme nibbles) through the tensor-core kernel."""
+    k, m, n = 1024, 192, 96
+    rng = synth.rng(77)
+    w = rng.integers(0, 256, size=m * eb.row_bytes(eb.Q4_K, k), dtype=np.uint8)
+    blocks = w.reshape(-1, eb.BLOCK_BYTES[eb.Q4_K])
+    blocks[:, 1] = rng.integers(0x18, 0x30, size=blocks.shape[0])     # sane f16 exponents for d and dmin
+    blocks[:, 3] = rng.integers(0x18, 0x30, size=blocks.shape[0])
+    x = synth.activations_f32(78, k, n)
+    got, want = gpu_mul_mat(be, eb.Q4_K, w, k, m, x, n), cpu_mul_mat(checker, eb.Q4_K, w, k, m, x, n)
+    assert_mul_mat_parity(got, want, checker, eb.Q4_K)
+
+
 @pytest.mark.parametrize("t", WEIGHT_TYPES)
 def test_mul_mat_random_block_bytes(be, checker, t):
     """Arbitrary block bytes (all scale/min/quant codes), not just encoder output."""
