@@ -337,6 +337,166 @@ def run_reference_gemv(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------ prompt-processing products (configuration 4)
+def prefill_spec(args):
+    n = args.ncols if args.ncols > 1 else 2048
+    return dict(n=n, n_embd=4096, n_ff=14336,
+                name=f"cfg4: {n} tokens x (gate, up 14336x4096 + down 4096x14336) Q4_K, activations -> Q8_K",
+                flops=2.0 * n * 3 * 4096 * 14336)
+
+
+def run_prefill(args):
+    """One step = the three FFN matrix products of one layer for a token batch (gate and up share the
+    quantized activations).  The dominant kernel is the tcgen05 int8 kernel; its roofline is the tensor
+    pipe, reported against the measured bf16 GEMM peak (the int8 pipe's nominal peak is twice that)."""
+    import torch
+    import emel_cpp_b200 as eb
+
+    rank, world, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    sp = prefill_spec(args)
+    n, ke, kf = sp["n"], sp["n_embd"], sp["n_ff"]
+    be = eb.Backend(local)
+    stream = torch.cuda.ExternalStream(be.stream(), device=dev)
+    t = eb.Q4_K
+    wg, wu, wd = (be.alloc(kf * eb.row_bytes(t, ke)), be.alloc(kf * eb.row_bytes(t, ke)), be.alloc(ke * eb.row_bytes(t, kf)))
+    for i, (w, m, k) in enumerate(((wg, kf, ke), (wu, kf, ke), (wd, ke, kf))):
+        assert be.synth_fill(w, t, m * k, 3000 + 10 * rank + i, 0.02, 0)
+    x, h = be.alloc(4 * ke * n), be.alloc(4 * kf * n)
+    assert be.synth_fill(x, eb.F32, ke * n, 11 + rank, 1.0, 0) and be.synth_fill(h, eb.F32, kf * n, 12 + rank, 1.0, 0)
+    yg, yu, yd = be.alloc(4 * kf * n), be.alloc(4 * kf * n), be.alloc(4 * ke * n)
+    x_host = torch.empty(ke * n, dtype=torch.float32).pin_memory()
+    h_host = torch.empty(kf * n, dtype=torch.float32).pin_memory()
+    y_host = torch.empty(kf * n, dtype=torch.float32).pin_memory()
+    assert be.to_host(x_host.numpy(), x) and be.to_host(h_host.numpy(), h) and be.sync()
+    op_g, op_u, op_d = (eb.mul_mat_op(wg, t, ke, kf, x, n, yg), eb.mul_mat_op(wu, t, ke, kf, x, n, yu),
+                        eb.mul_mat_op(wd, t, kf, ke, h, n, yd))
+    xv, hv = eb.dense_view(x, eb.F32, [n, ke]), eb.dense_view(h, eb.F32, [n, kf])
+
+    def step_dev():            # quantize once per distinct right-hand side, then the products
+        assert be.prepare_rhs(xv, t) and be.mul_mat_prepared(op_g) and be.mul_mat_prepared(op_u)
+        assert be.prepare_rhs(hv, t) and be.mul_mat_prepared(op_d)
+
+    def step_host():           # host activations in, host results out, through the plain op_mul_mat call
+        assert be.mul_mat(eb.mul_mat_op(wg, t, ke, kf, x_host, n, y_host))
+        assert be.mul_mat(eb.mul_mat_op(wu, t, ke, kf, x_host, n, y_host))
+        assert be.mul_mat(eb.mul_mat_op(wd, t, kf, ke, h_host, n, y_host[:ke * n]))
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        be.sync()
+        barrier(world)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0 = be.diagnostics()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        be.sync()
+        torch.cuda.synchronize()
+        barrier(world)
+        d1 = be.diagnostics()
+        return max_over_ranks(e0.elapsed_time(e1), world, dev), {k_: d1[k_] - d0[k_] for k_ in d1}
+
+    l0 = be.diagnostics()["kernel_launches"]
+    step_dev()
+    be.sync()
+    launches_per_step = be.diagnostics()["kernel_launches"] - l0
+    assert be.graph_begin()
+    step_dev()
+    g = be.graph_end()
+    # the products alone (activations already quantized): gate + up share one graph, timed per launch
+    assert be.prepare_rhs(xv, t)
+    assert be.graph_begin()
+    assert be.mul_mat_prepared(op_g) and be.mul_mat_prepared(op_u)
+    gk = be.graph_end()
+    with ClockSampler(local) as clk:
+        ms, dd = timed(lambda: be.graph_launch(g), args.steps, args.warmup)
+        assert be.prepare_rhs(xv, t)
+        ms_k, _ = timed(lambda: be.graph_launch(gk), args.steps, args.warmup)
+        e_steps = max(1, min(args.steps, 4))
+        ms_e, de = timed(step_host, e_steps, 1)
+    clocks = clk.summary()
+    peaks, peak_kind = measured_peaks()
+    tflops = sp["flops"] * args.steps * world / (ms * 1e-3) / 1e12
+    tflops_e = sp["flops"] * e_steps * world / (ms_e * 1e-3) / 1e12
+    k_flops = 2.0 * n * ke * kf                                  # one 14336x4096 product
+    k_tflops = k_flops / (ms_k * 1e-3 / (2 * args.steps)) / 1e12
+    line = {
+        "metric": "prefill GEMM TFLOP/s", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 tcgen05.mma (s32 accumulators in TMEM) + f32 block scales", "data": "synthetic",
+        "config": {"workload": sp["name"], "tokens": n, "launch": "each step is one CUDA-graph replay: 2 activation quantizers + 3 products",
+                   "l2_policy": f"inputs larger than L2: {(4 * (ke + kf) * n + 3 * kf * eb.row_bytes(t, ke)) / 1e6:.0f} MB of operands, "
+                                f"{4 * (2 * kf + ke) * n / 1e6:.0f} MB of results per step",
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas, no collective"},
+        "e2e": {"value": round(tflops_e, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": de["h2d_bytes"] // e_steps,
+                "d2h_bytes_per_step": de["d2h_bytes"] // e_steps},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "roofline": {"bound": "tensor", "kernel": "gemm_q4k_tc", "achieved": round(k_tflops, 2), "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": round(k_tflops / peaks["bf16_tflops"], 4),
+                     "peak_source": f"of {peak_kind} (cuBLAS bf16 burst; the kernel's MMAs are int8 and issue two per useful one)",
+                     "us_per_launch": round(ms_k * 1e3 / (2 * args.steps), 2), "flops_per_launch": k_flops, "traffic": None},
+        "clocks": clocks,
+    }
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline_prefill(sp, args.cpu_budget)
+        print(json.dumps(line), flush=True)
+    be.close()
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def cpu_baseline_prefill(sp, budget_s, lanes=None):
+    """The reference's AVX2 op_mul_mat on a bounded sample: the gate product for 16 of the tokens."""
+    import emel_cpp_b200 as eb
+    from oracle import bindings as ob
+    lib = ob.ref()
+    kind = "reference" if lib is not None else "port"
+    lib = lib or ob.port()
+    k, m, n = sp["n_embd"], sp["n_ff"], 16
+    rng = np.random.Generator(np.random.PCG64(5))
+    w = rng.integers(0, 256, size=m * eb.row_bytes(eb.Q4_K, k), dtype=np.uint8).reshape(-1, eb.BLOCK_BYTES[eb.Q4_K])
+    w[:, 1] = rng.integers(0x18, 0x30, size=w.shape[0])
+    w[:, 3] = rng.integers(0x18, 0x30, size=w.shape[0])
+    x, y = rng.standard_normal((k, n), dtype=np.float32), np.zeros((m, n), np.float32)
+    op = ob.mul_mat_op(w.reshape(-1), eb.Q4_K, k, m, x, n, y)
+    lanes = lanes or min(8, os.cpu_count() or 1)
+    kw = {"route": "avx2", "lanes": lanes} if kind == "reference" else {}
+    assert lib.mul_mat(op, **kw)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        assert lib.mul_mat(op, **kw)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or reps >= 200:
+            break
+    tf = 2.0 * k * m * n * reps / dt / 1e12
+    return {"value": round(tf, 5), "unit": "TFLOP/s", "cores": lanes if kind == "reference" else 1, "kind": kind,
+            "sample": f"{reps} x (14336x4096 Q4_K product for {n} tokens) in {dt:.1f} s, AVX2/FMA route, row-sliced over {lanes} threads"}
+
+
+def run_reference_prefill(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    sp = prefill_spec(args)
+    t0 = time.perf_counter()
+    res = [cpu_baseline_prefill(sp, 2.0, lanes=min(os.cpu_count() or 1, 64)) for _ in range(max(1, min(args.steps, 5)))]
+    v = float(np.median([r["value"] for r in res]))
+    line = {"impl": "reference", "metric": "prefill GEMM TFLOP/s", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sp["flops"] / (v * 1e12) * 1e3, 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot (AVX2 maddubs) + f32 scales",
+            "data": "synthetic", "config": {"workload": sp["name"], "tokens": sp["n"]},
+            "cpu_baseline": dict(res[0], value=v),
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+
 # ------------------------------------------------------------------ decode workload (configurations 3 and 5)
 DECODE_SHAPES = {
     "decode_8b": dict(n_layer=32, n_embd=4096, n_head=32, n_head_kv=8, head_dim=128, n_ff=14336, n_vocab=128256,
@@ -504,7 +664,9 @@ def run_decode(args):
         "roofline": {"bound": "hbm", "kernel": "gemv_stream_q4_k_n1", "achieved": round(kernel_gbs, 2), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(kernel_gbs / peaks["hbm_gbs"], 4), "peak_source": f"of {peak_kind}",
                      "us_per_launch": round(ms_k * 1e3 / n_k, 3), "algorithmic_bytes_per_launch": q4k_bytes // n_k,
-                     "launches_timed": n_k, "traffic": ncu_traffic("gemv_stream_q4_k_n1_decode")},
+                     "launches_timed": n_k,
+                     # ncu capture of the 14336x4096 launch, scaled by bytes (traffic grows with the weight bytes)
+                     "traffic": (lambda r: None if r is None else int(r * (q4k_bytes // n_k)))(ncu_traffic("q4_k_n1_traffic_over_algorithmic"))},
         "clocks": clocks,
     }
     if rank == 0:
@@ -611,7 +773,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_70b", "gemv_q4_k", "gemv_q8_0"])
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_70b", "gemv_q4_k", "gemv_q8_0", "prefill_q4_k"])
     ap.add_argument("--prompt", type=int, default=None, help="prompt length override for the decode workloads")
     ap.add_argument("--ncols", type=int, default=1)
     ap.add_argument("--rows", type=int, default=None, help="row count override for gemv_q4_k")
@@ -626,7 +788,9 @@ def main():
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     decode = args.workload.startswith("decode")
-    if args.impl == "reference":
+    if args.workload == "prefill_q4_k":
+        (run_reference_prefill if args.impl == "reference" else run_prefill)(args)
+    elif args.impl == "reference":
         (run_reference_decode if decode else run_reference_gemv)(args)
     else:
         (run_decode if decode else run_gemv)(args)

@@ -640,7 +640,7 @@ uint32_t emelb_flash_attn_ext(emelb_ctx* c, const emelb_op* op) {
   bool ok;
   const bool fast = c->attention_mode == 0 && a.splits >= 1 && flash_split_supported(a);
   if (fast) {
-    ok = cuda_ok(c, launch_flash_decode(a, c->sm_count, c->stream, &launches));
+    ok = cuda_ok(c, launch_flash_decode(a, c->sm_count, c->stream, &launches, 0, ActPlanesMut{}));
     c->diag.optimized_flash_dispatch_calls += 1;
   } else {
     if ((uint64_t)H * (uint64_t)T > kFlashScoreFloats) { c->diag.rejected_dispatch_calls += 1; return EMELB_UNSUPPORTED_OP; }

@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "expf_exact.h"
 #include "kernels.h"
+#include "quant_device.cuh"
 
 namespace emelb {
 
@@ -212,8 +213,86 @@ __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
   }
 }
 
-// merge the ranges: out = sum_s e^{m_s-M} acc_s / sum_s e^{m_s-M} l_s
-__global__ void flash_merge_kernel(const FlashArgs a) {
+// merge the ranges: out = sum_s e^{m_s-M} acc_s / sum_s e^{m_s-M} l_s.
+// One CTA of 256 threads = 256 consecutive output values (256/D heads), which is
+// also one Q8_K block / eight Q8_0 blocks of the vector the output projection
+// consumes, so the CTA can hand the projection its quantized planes directly
+// (family 1 / 2; 0 = f32 only).  Warp w < 256/D first turns head w's (max, sum)
+// pairs into weights in shared memory; then thread (head, d) walks the ranges
+// with independent loads.
+constexpr int kMergeMaxSplits = 64;
+
+template <int FAMILY>
+__global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, ActPlanesMut planes) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float s_w[4][kMergeMaxSplits];
+  __shared__ float s_inv[4];
+  __shared__ float s_out[256];
+  const int D = a.head_dim, hp = 256 / D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h0 = blockIdx.x * hp;
+  if (warp < hp) {
+    const float* ml = a.part_ml + (size_t)(h0 + warp) * a.splits * 2;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    if (lane < a.splits) { m0 = ml[2 * lane]; l0 = ml[2 * lane + 1]; }
+    if (lane + 32 < a.splits) { m1 = ml[2 * (lane + 32)]; l1 = ml[2 * (lane + 32) + 1]; }
+    float M = fmaxf(m0, m1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float w0 = m0 == -INFINITY ? 0.0f : expf(m0 - M), w1 = m1 == -INFINITY ? 0.0f : expf(m1 - M);
+    s_w[warp][lane] = w0;
+    s_w[warp][lane + 32] = w1;
+    float den = w0 * l0 + w1 * l1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    if (lane == 0) s_inv[warp] = den == 0.0f ? 0.0f : 1.0f / den;
+  }
+  __syncthreads();
+  const int hl = threadIdx.x / D, d = threadIdx.x - hl * D;
+  const float* pa = a.part_acc + (size_t)(h0 + hl) * a.splits * D + d;
+  float o = 0.0f;
+  int s = 0;
+  for (; s + 4 <= a.splits; s += 4) {
+    const float v0 = pa[(size_t)s * D], v1 = pa[(size_t)(s + 1) * D], v2 = pa[(size_t)(s + 2) * D], v3 = pa[(size_t)(s + 3) * D];
+    o = fmaf(s_w[hl][s], v0, o);
+    o = fmaf(s_w[hl][s + 1], v1, o);
+    o = fmaf(s_w[hl][s + 2], v2, o);
+    o = fmaf(s_w[hl][s + 3], v3, o);
+  }
+  for (; s < a.splits; ++s) o = fmaf(s_w[hl][s], pa[(size_t)s * D], o);
+  o *= s_inv[hl];
+  a.dst[(size_t)h0 * D + threadIdx.x] = o;
+  if constexpr (FAMILY != 0) {
+    s_out[threadIdx.x] = o;
+    __syncthreads();
+    const int K = a.heads * D;
+    if constexpr (FAMILY == 1) {
+      if (warp == 0) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = s_out[8 * lane + i];
+        uint32_t lo, hi; int bs; float dq;
+        q8_k_block_warp(v, lane, lo, hi, bs, dq);
+        q8_k_store_planes(planes, 0, K, blockIdx.x, lane, lo, hi, bs, dq);
+      }
+    } else {
+      if (threadIdx.x < 64) {
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = s_out[4 * threadIdx.x + i];
+        uint32_t q; __half dh;
+        q8_0_block_oct(v, q, dh);
+        const int e0 = blockIdx.x * 256 + 4 * threadIdx.x;
+        *reinterpret_cast<uint32_t*>(planes.qs + e0) = q;
+        if ((threadIdx.x & 7) == 0) planes.d[e0 / QK32] = __half2float(dh);
+      }
+    }
+  }
+}
+
+// any head count: one CTA per head, f32 output only
+__global__ void flash_merge_tail_kernel(const FlashArgs a) {
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.x, D = a.head_dim;
@@ -357,12 +436,22 @@ bool flash_split_supported(const FlashArgs& a) {
   return d_ok && al && (int64_t)a.splits * LMAX >= a.tokens;
 }
 
-cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches) {
+bool flash_merge_can_quantize(const FlashArgs& a) { return (a.heads * a.head_dim) % 256 == 0; }
+
+cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches, int out_family,
+                                ActPlanesMut out_planes) {
   (void)sm_count;
   const int n_rep = a.heads / a.kv_heads;
   cudaError_t e = a.head_dim == 64 ? launch_split<64>(a, n_rep, st) : launch_split<128>(a, n_rep, st);
   if (e != cudaSuccess) return e;
-  EMELB_LAUNCH(flash_merge_kernel, a.heads, 128, 0, st, a);
+  const int total = a.heads * a.head_dim;
+  if (total % 256 == 0) {
+    if (out_family == 1) EMELB_LAUNCH(flash_merge_kernel<1>, total / 256, 256, 0, st, a, out_planes);
+    else if (out_family == 2) EMELB_LAUNCH(flash_merge_kernel<2>, total / 256, 256, 0, st, a, out_planes);
+    else EMELB_LAUNCH(flash_merge_kernel<0>, total / 256, 256, 0, st, a, out_planes);
+  } else {
+    EMELB_LAUNCH(flash_merge_tail_kernel, a.heads, 128, 0, st, a);   // head counts that do not fill 256-value groups
+  }
   *launches += 2;
   return cudaGetLastError();
 }

@@ -14,13 +14,15 @@
 //     folded into f32 registers with the block's scales — the float chain stays on
 //     the CUDA cores because its order and roundings are part of the contract.
 //
-// CTA = 128 rows x 128 columns, 13 warps:
-//   warps 0-3   producers: thread p builds row p's two int8 operands for the next
-//               super-block straight from the GGUF bytes and copies column p's 256
-//               activations (cp.async) into the canonical no-swizzle K-major layout
-//               (8 rows x 16 bytes core matrices)
+// CTA = 128 rows x 128 columns, 21 warps:
+//   warps 0-3   producers: the 128 GGUF blocks of a super-block column arrive by
+//               cp.async.bulk (one 144-byte copy per row) in a raw staging buffer;
+//               thread p expands row p into the two int8 operands, and the warp
+//               copies 32 columns' activations with cp.async (8 columns x 64
+//               contiguous bytes per instruction), both into the canonical
+//               no-swizzle K-major layout (8 rows x 16 bytes core matrices)
 //   warp  4     allocates TMEM, issues the MMAs, commits to an mbarrier
-//   warps 5-12  epilogue: two warps per TMEM lane quarter, 64 columns each
+//   warps 5-20  epilogue: four warps per TMEM lane quarter, 32 columns each
 // Two shared-memory stages and two TMEM accumulator pairs (2 x 256 columns) let
 // producers, tensor cores and epilogue work on different super-blocks at once.
 // Every mbarrier wait is bounded; on a timeout the CTA raises the status word,
@@ -38,7 +40,8 @@ constexpr int BM = 128, BN = 128;
 constexpr int kProducerThreads = 128;
 constexpr int kMmaWarp = 4;
 constexpr int kEpilogueWarp0 = 5;
-constexpr int kThreads = 13 * 32;
+constexpr int kThreads = 21 * 32;
+constexpr int kEpilogueWarps = 16;
 constexpr int kStages = 2;
 
 // shared memory map (bytes)
@@ -51,8 +54,9 @@ constexpr int kStageBytes = 3 * kOperandBytes           // A_lo, A_hi, B
                             + BN * 4;                   // column scale dx
 constexpr int kOffAlo = 0, kOffAhi = kOperandBytes, kOffB = 2 * kOperandBytes, kOffRowMeta = 3 * kOperandBytes,
               kOffColMeta = kOffRowMeta + BM * 16, kOffDx = kOffColMeta + BN * 16;
-constexpr int kBarBytes = 64;                           // full[2], tmem_full[2], epi_done[2], tmem base, abort
-constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 128;  // + alignment slack
+constexpr int kRawBytes = BM * Q4_K_BYTES;              // raw GGUF blocks of one super-block column: 18,432 B
+constexpr int kBarBytes = 64;                           // full[2], tmem_full[2], epi_done[2], raw_full, tmem base, abort
+constexpr int kSmemBytes = kStages * kStageBytes + kRawBytes + kBarBytes + 128;  // + alignment slack
 
 constexpr int kWaitSpins = 1 << 22;
 constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s
@@ -120,13 +124,20 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 struct GemmArgs {
@@ -143,11 +154,13 @@ struct GemmArgs {
 __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint8_t* raw = smem + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawBytes);
   uint64_t* full = bars;            // [2] producers -> MMA: operands of a super-block are in shared memory
   uint64_t* tmem_full = bars + 2;   // [2] MMA -> epilogue: the accumulator pair holds a finished super-block
   uint64_t* epi_done = bars + 4;    // [2] epilogue -> producers: stage and accumulator pair are free again
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* raw_full = bars + 6;    // bulk copies -> producers: the raw blocks of the next super-block landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -155,10 +168,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full + s, kProducerThreads);
       mbar_init(tmem_full + s, 1);
-      mbar_init(epi_done + s, 8);
+      mbar_init(epi_done + s, kEpilogueWarps);
     }
+    mbar_init(raw_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
@@ -173,27 +188,55 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
 
   if (warp < 4) {
     // ---------------------------------------------------------------- producers
-    const int t = threadIdx.x;  // row t of the weight tile and column t of the activation tile
+    const int t = threadIdx.x;  // row t of the weight tile; column t for the per-column scales
     const uint32_t core_off = (uint32_t)(t >> 3) * kGroupStride + (uint32_t)(t & 7) * 16;
-    int it = 0;
-    bool live = true;
-    for (int tile = blockIdx.x; live && tile < ntiles; tile += gridDim.x) {
-      const int tm = tile / nt, tn = tile - tm * nt;
+    // raw copy of row t's block of iteration (tile, kb); thread 0 also arms the barrier
+    auto issue_raw = [&](int tile, int kb) {
+      const int tm = tile / nt;
       const int row = min(tm * BM + t, p.M - 1);          // out-of-range rows/columns repeat the last one; never stored
-      const int col = p.col0 + min(tn * BN + t, p.N - 1);
-      const uint8_t* wrow = p.W + (size_t)row * p.row_bytes;
-      const int8_t* xq = p.act.qs + (int64_t)col * p.act.col_stride_qs;
-      const int16_t* xb = p.act.bsums + (int64_t)col * p.act.col_stride_bs;
-      const float* xd = p.act.d + (int64_t)col * p.act.col_stride_d;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(epi_done + s, ((it >> 1) & 1) ^ 1, abort_flag)) { live = false; break; }
-        uint8_t* st = smem + s * kStageBytes;
-        // activations of column t: 16 chunks of 16 int8
-        const uint32_t bdst = smem_u32(st + kOffB) + core_off;
+      if (t == 0) mbar_arrive_expect_tx(raw_full, kRawBytes);
+      bulk_g2s(raw + t * Q4_K_BYTES, p.W + (size_t)row * p.row_bytes + (size_t)kb * Q4_K_BYTES, Q4_K_BYTES, raw_full);
+    };
+    // One flat loop over (tile, super-block).  The 128 producers meet at a named barrier every
+    // iteration, so nobody leaves early: a wait that gave up only skips work, and the loop ends
+    // for everyone at the abort check right after the barrier.
+    int it = 0, tile = blockIdx.x, kb = 0;
+    if (tile < ntiles) issue_raw(tile, 0);
+    for (; tile < ntiles; ++it) {
+      const int tn = tile % nt;
+      const int s = it & 1;
+      // this row's 144 raw bytes -> registers, then the staging buffer is free for the next copy
+      bool ok = mbar_wait(raw_full, it & 1, abort_flag);
+      uint4 blk[9];
 #pragma unroll
-        for (int c = 0; c < 16; ++c)
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(bdst + c * kChunkStride), "l"(xq + kb * QK_K + 16 * c) : "memory");
+      for (int i = 0; i < 9; ++i) blk[i] = *reinterpret_cast<const uint4*>(raw + t * Q4_K_BYTES + 16 * i);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag) break;
+      int ntile = tile, nkbi = kb + 1;
+      if (nkbi == nkb) { nkbi = 0; ntile += gridDim.x; }
+      if (ntile < ntiles) issue_raw(ntile, nkbi);
+      ok = ok && mbar_wait(epi_done + s, ((it >> 1) & 1) ^ 1, abort_flag);
+      if (ok) {
+        const int col = p.col0 + min(tn * BN + t, p.N - 1);
+        const int16_t* xb = p.act.bsums + (int64_t)col * p.act.col_stride_bs;
+        const float* xd = p.act.d + (int64_t)col * p.act.col_stride_d;
+        uint8_t* st = smem + s * kStageBytes;
+        // activations: this warp's 32 columns, 8 columns x 4 chunks (64 contiguous bytes each) per instruction
+        {
+          const int col8 = lane & 7, cq = lane >> 3;
+          const uint32_t bbase = smem_u32(st + kOffB);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int cl = 32 * warp + 8 * g + col8;                       // column within the tile
+            const int8_t* src = p.act.qs + (int64_t)(p.col0 + min(tn * BN + cl, p.N - 1)) * p.act.col_stride_qs + kb * QK_K;
+            const uint32_t dst = bbase + (uint32_t)(cl >> 3) * kGroupStride + (uint32_t)(cl & 7) * 16;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = 4 * i + cq;
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c * kChunkStride), "l"(src + 16 * c) : "memory");
+            }
+          }
+        }
         {
           const int4* bs = reinterpret_cast<const int4*>(xb + kb * 16);
           const int4 b0 = __ldg(bs), b1 = __ldg(bs + 1);
@@ -206,8 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
           *reinterpret_cast<float*>(st + kOffDx + t * 4) = __ldg(xd + kb);
         }
         // weights of row t: scales, then the two int8 operands
-        const uint4* blk = reinterpret_cast<const uint4*>(wrow + (size_t)kb * Q4_K_BYTES);
-        const uint4 h = __ldg(blk);
+        const uint4 h = blk[0];
         const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
         const uint32_t sc_lo4 = s0 & 0x3f3f3f3fu, mn_lo4 = s1 & 0x3f3f3f3fu;
         const uint32_t sc_hi4 = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
@@ -218,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
         uint8_t* ahi = st + kOffAhi + core_off;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const uint4 v0 = __ldg(blk + 1 + 2 * g), v1 = __ldg(blk + 2 + 2 * g);
+          const uint4 v0 = blk[1 + 2 * g], v1 = blk[2 + 2 * g];
           const uint32_t scw = g < 2 ? sc_lo4 : sc_hi4;
           const uint32_t sca = (scw >> (16 * (g & 1))) & 0xffu, scb = (scw >> (16 * (g & 1) + 8)) & 0xffu;
           const uint32_t la = sca & 7u, ha = sca >> 3, lb = scb & 7u, hb = scb >> 3;
@@ -240,6 +282,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core's reads
         mbar_arrive(full + s);
       }
+      tile = ntile;
+      kb = nkbi;
+    }
+    if (*abort_flag) {
+      // a raw copy may still be in flight: give it a bounded moment before the CTA's shared memory goes away
+      for (int spins = 0; spins < (1 << 16) && !mbar_try_wait(raw_full, it & 1); ++spins) {}
     }
   } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------------- MMA issue (one thread)
@@ -274,16 +322,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;                       // the TMEM lanes this warp may read: 32*quarter ..
-    const int half = (warp - kEpilogueWarp0) >> 2;      // columns 64*half .. 64*half+63
+    const int cgroup = (warp - kEpilogueWarp0) >> 2;    // columns 32*cgroup .. 32*cgroup+31
     const int r = 32 * quarter + lane;                  // row of the tile = TMEM lane
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(64 * half);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(32 * cgroup);
     int it = 0;
     bool live = true;
     for (int tile = blockIdx.x; live && tile < ntiles; tile += gridDim.x) {
       const int tm = tile / nt, tn = tile - tm * nt;
-      float acc[64];
+      float acc[32];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+      for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it & 1;
         if (!mbar_wait(tmem_full + s, (it >> 1) & 1, abort_flag)) { live = false; break; }
@@ -293,14 +341,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
         const float d = __uint_as_float(rm.x), dmin = __uint_as_float(rm.y);
         const int mn_lo4 = (int)rm.z, mn_hi4 = (int)rm.w;
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          uint32_t lo[16], hi[16];
-          tmem_ld16(lane_addr + (uint32_t)s * 256u + (uint32_t)(16 * c4), lo);
-          tmem_ld16(lane_addr + (uint32_t)s * 256u + 128u + (uint32_t)(16 * c4), hi);
+        for (int c8 = 0; c8 < 4; ++c8) {
+          uint32_t lo[8], hi[8];
+          tmem_ld8(lane_addr + (uint32_t)s * 256u + (uint32_t)(8 * c8), lo);
+          tmem_ld8(lane_addr + (uint32_t)s * 256u + 128u + (uint32_t)(8 * c8), hi);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int col = 64 * half + 16 * c4 + i;
+          for (int i = 0; i < 8; ++i) {
+            const int col = 32 * cgroup + 8 * c8 + i;
             const uint4 cm = *reinterpret_cast<const uint4*>(st + kOffColMeta + col * 16);
             const float dx = *reinterpret_cast<const float*>(st + kOffDx + col * 4);
             const int isum = (int)lo[i] + 8 * (int)hi[i];
@@ -310,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
             msum = __dp2a_hi((int)cm.w, mn_hi4, msum);
             const float d_all = __fmul_rn(dx, d), d_min = __fmul_rn(dx, dmin);
             const float bv = __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, (float)msum));
-            acc[16 * c4 + i] = __fadd_rn(acc[16 * c4 + i], bv);
+            acc[8 * c8 + i] = __fadd_rn(acc[8 * c8 + i], bv);
           }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -321,9 +369,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
       const int row = tm * BM + r;
       if (row < p.M) {
         float* yr = p.y + (size_t)row * p.ldy + p.col0;
-        const int c0 = tn * BN + 64 * half;
+        const int c0 = tn * BN + 32 * cgroup;
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i)
           if (c0 + i < p.N) yr[c0 + i] = acc[i];
       }
     }

@@ -134,7 +134,11 @@ struct FlashArgs {
   float* part_acc;       // [H][splits][d]
   float* part_ml;        // [H][splits][2]  (running max, running sum)
 };
-cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches);
+// out_family 1 / 2: the merge step also writes the result quantized (Q8_K / Q8_0 planes, one column) for the
+// matrix product that consumes it; only when flash_merge_can_quantize(a)
+cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches, int out_family,
+                                ActPlanesMut out_planes);
+bool flash_merge_can_quantize(const FlashArgs& a);
 // score_ws: [heads][t_stride] f32 scratch; order 1 = scalar route, 2 = x86 AVX2 route
 cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, int order, cudaStream_t st,
                                          int* launches);

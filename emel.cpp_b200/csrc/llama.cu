@@ -178,7 +178,9 @@ struct Enqueue {
     s->planes_family = family;
   }
 
-  void attention(int layer) {
+  // attention of one layer; when the split-KV kernels run unsharded, their merge step also leaves the
+  // context quantized for the output projection (family of wo's type)
+  void attention(int layer, int out_family) {
     const emelb_llama_config& c = s->cfg;
     const int64_t layer_off = (int64_t)layer * (c.n_head_kv / s->G) * s->capacity * c.head_dim;
     FlashArgs a{};
@@ -198,7 +200,12 @@ struct Enqueue {
     a.part_acc = s->c->fa_part_acc;
     a.part_ml = s->c->fa_part_ml;
     if (s->c->attention_mode == 0 && flash_split_supported(a)) {
-      check(launch_flash_decode(a, s->c->sm_count, st, &launches));
+      const bool fuse = s->G == 1 && flash_merge_can_quantize(a);
+      check(launch_flash_decode(a, s->c->sm_count, st, &launches, fuse ? out_family : 0, planes()));
+      if (fuse) {
+        s->planes_src = s->attn;
+        s->planes_family = out_family;
+      }
     } else {
       check(launch_flash_reference_order(a, s->c->fa_scores, c.n_ctx, s->c->attention_mode == 1 ? 1 : 2, st, &launches));
     }
@@ -235,7 +242,7 @@ struct Enqueue {
                               c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
                               s->vcache + layer_off, s->capacity * c.head_dim, st));
       ++launches;
-      attention(l);
+      attention(l, family_of(w.wo.type));
       gather(s->attn, q_l);
       matvec(w.wo, s->attn, hidden_mine, hidden_mine);   // hidden += Wo * attn (this rank's rows)
       gather(s->hidden, embd_l);
