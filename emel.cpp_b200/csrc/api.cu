@@ -308,6 +308,9 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
   ok = ok && cudaMalloc(&c->act_qs, c->act_capacity) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_d, c->act_capacity / 32 * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->act_bsums, c->act_capacity / 16 * sizeof(int16_t)) == cudaSuccess;
+  // tiles of 128 columns x 256 K: 32 KB of int8 + 2.5 KB of block sums and scales; columns padded to 128
+  c->tc_ws_bytes = c->act_capacity / 32768 * 35328 + (64u << 20);
+  ok = ok && cudaMalloc(&c->tc_ws, c->tc_ws_bytes) == cudaSuccess;
   ok = ok && cudaMalloc(&c->gemv_sched, (2 * kSchedSlots + 2) * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMemset(c->gemv_sched, 0, (2 * kSchedSlots + 2) * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_val, kMaxArgmaxParts * sizeof(float)) == cudaSuccess;
@@ -336,7 +339,7 @@ uint32_t emelb_destroy(emelb_ctx* c) {
   for (auto& kv : c->residents)
     if (kv.second.dev) cudaFree(kv.second.dev);
   for (void* p : c->owned) cudaFree(p);
-  void* bufs[] = {c->gemv_sched, c->stage_in, c->stage_out, c->act_qs, c->act_d, c->act_bsums, c->part_val, c->part_idx,
+  void* bufs[] = {c->gemv_sched, c->stage_in, c->stage_out, c->act_qs, c->act_d, c->act_bsums, c->tc_ws, c->part_val, c->part_idx,
                   c->best_val, c->best_idx, c->fa_part_acc, c->fa_part_ml, c->fa_scores};
   for (void* p : bufs)
     if (p) cudaFree(p);
@@ -524,6 +527,8 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
   a.y = static_cast<float*>(out.dev);
   a.ldy = (int64_t)n;
   a.residual = nullptr;
+  a.tc_ws = c->tc_ws;
+  a.tc_ws_bytes = c->tc_ws_bytes;
   a.sched = c->next_sched();
   a.status = c->status_word();
   a.part_val = c->part_val;

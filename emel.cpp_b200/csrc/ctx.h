@@ -45,6 +45,8 @@ struct emelb_ctx {
   float* act_d = nullptr;
   int16_t* act_bsums = nullptr;
   uint64_t act_capacity = 0;  // elements
+  uint8_t* tc_ws = nullptr;   // the many-column kernel's copy of the planes in operand order
+  uint64_t tc_ws_bytes = 0;
   // shape of the activations emelb_prepare_rhs left in the planes (0 = none)
   uint64_t prepared_n = 0;
   uint64_t prepared_k = 0;

@@ -15,16 +15,21 @@
 //     the CUDA cores because its order and roundings are part of the contract.
 //
 // CTA = 128 rows x 128 columns, 21 warps:
-//   warps 0-3   producers: the 128 GGUF blocks of a super-block column arrive by
-//               cp.async.bulk (one 144-byte copy per row) in a raw staging buffer;
-//               thread p expands row p into the two int8 operands, and the warp
-//               copies 32 columns' activations with cp.async (8 columns x 64
-//               contiguous bytes per instruction), both into the canonical
-//               no-swizzle K-major layout (8 rows x 16 bytes core matrices)
-//   warp  4     allocates TMEM, issues the MMAs, commits to an mbarrier
+//   warps 0-3   producers: the 128 GGUF blocks of a super-block column are staged
+//               raw (16-byte cp.async, coalesced along rows) one iteration ahead;
+//               thread p expands row p into the two int8 operands in the
+//               canonical no-swizzle K-major layout (8 rows x 16 bytes core
+//               matrices).  The activation tile comes by bulk copy: a small
+//               pre-pass has already laid it out in that same layout (one
+//               contiguous 32 KB slab + per-column block sums and scales per
+//               128 columns x 256 K)
+//   warp  4     allocates TMEM, issues the MMAs, commits to two mbarriers
 //   warps 5-20  epilogue: four warps per TMEM lane quarter, 32 columns each
-// Two shared-memory stages and two TMEM accumulator pairs (2 x 256 columns) let
-// producers, tensor cores and epilogue work on different super-blocks at once.
+//   warp  21    one thread starts the bulk copies of the next activation tile the
+//               moment an operand stage is released
+// Two operand stages are released by the MMA's completion, two TMEM accumulator
+// pairs and four small per-block scale slots by the epilogue, so producers,
+// tensor cores and epilogue work on different super-blocks at once.
 // Every mbarrier wait is bounded; on a timeout the CTA raises the status word,
 // stops issuing, and still frees its TMEM.
 #include <cuda_runtime.h>
@@ -40,7 +45,8 @@ constexpr int BM = 128, BN = 128;
 constexpr int kProducerThreads = 128;
 constexpr int kMmaWarp = 4;
 constexpr int kEpilogueWarp0 = 5;
-constexpr int kThreads = 21 * 32;
+constexpr int kLoaderWarp = 21;
+constexpr int kThreads = 22 * 32;
 constexpr int kEpilogueWarps = 16;
 constexpr int kStages = 2;
 
@@ -48,15 +54,18 @@ constexpr int kStages = 2;
 constexpr int kOperandBytes = BM * 256;                 // one int8 operand tile of a super-block: 32 KB
 constexpr int kChunkStride = (BM / 8) * 128;            // next 16-byte K chunk: 2048 B (leading byte offset)
 constexpr int kGroupStride = 128;                       // next 8-row core matrix (stride byte offset)
-constexpr int kStageBytes = 3 * kOperandBytes           // A_lo, A_hi, B
-                            + BM * 16                   // row meta {d, dmin, mins[8]}
-                            + BN * 16                   // column meta: 8 pair sums (int16)
-                            + BN * 4;                   // column scale dx
-constexpr int kOffAlo = 0, kOffAhi = kOperandBytes, kOffB = 2 * kOperandBytes, kOffRowMeta = 3 * kOperandBytes,
-              kOffColMeta = kOffRowMeta + BM * 16, kOffDx = kOffColMeta + BN * 16;
+constexpr int kStageBytes = 3 * kOperandBytes;          // A_lo, A_hi, B
+constexpr int kOffAlo = 0, kOffAhi = kOperandBytes, kOffB = 2 * kOperandBytes;
+constexpr int kMetaSlots = 4;
+constexpr int kColMetaBytes = BN * 16 + BN * 4;         // per column: 8 pair sums as int8 low/high parts, then the scales dx
+constexpr int kRowMetaBytes = 12;                       // per row: {d, dmin} as f16 bits, mins[8]
+constexpr int kMetaBytes = BM * kRowMetaBytes + kColMetaBytes;
+constexpr int kOffRowMeta = 0, kOffColMeta = BM * kRowMetaBytes, kOffDx = kOffColMeta + BN * 16;
 constexpr int kRawBytes = BM * Q4_K_BYTES;              // raw GGUF blocks of one super-block column: 18,432 B
-constexpr int kBarBytes = 64;                           // full[2], tmem_full[2], epi_done[2], raw_full, tmem base, abort
-constexpr int kSmemBytes = kStages * kStageBytes + kRawBytes + kBarBytes + 128;  // + alignment slack
+constexpr int kBarBytes = 128;                          // full[2], mma_done[2], tmem_full[2], epi_done[2], tmem base, abort
+constexpr int kSmemBytes = kStages * kStageBytes + kMetaSlots * kMetaBytes + kRawBytes + kBarBytes + 128;  // + alignment slack
+// the activation tile a pre-pass writes for (128 columns, one super-block): operand B, then the column meta
+constexpr int kTileBytes = kOperandBytes + kColMetaBytes;
 
 constexpr int kWaitSpins = 1 << 22;
 constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s
@@ -144,33 +153,70 @@ struct GemmArgs {
   const uint8_t* W;
   int64_t row_bytes;
   int M, K, N;
-  ActPlanes act;
-  int col0;
+  const uint8_t* tiles;   // [ceil(N/128)][K/256][kTileBytes]
   float* y;
   int64_t ldy;
   int* status;
 };
 
+// pre-pass: the quantized activation planes of columns col0.. -> tiles in operand order.
+// grid (K/256, ceil(N/128)), 256 threads; columns past N are zero.
+__global__ void __launch_bounds__(256) tile_activations_kernel(ActPlanes act, int col0, int N, int K, uint8_t* tiles) {
+  const int kb = blockIdx.x, tn = blockIdx.y, nkb = K / QK_K;
+  uint8_t* tile = tiles + ((size_t)tn * nkb + kb) * kTileBytes;
+  for (int q = threadIdx.x; q < BN * 16; q += 256) {
+    const int col = q & (BN - 1), c = q >> 7;           // piece q = (chunk c, column col) lands at q*16
+    const int gc = tn * BN + col;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (gc < N) v = *reinterpret_cast<const uint4*>(act.qs + (int64_t)(col0 + gc) * act.col_stride_qs + kb * QK_K + 16 * c);
+    *reinterpret_cast<uint4*>(tile + (size_t)q * 16) = v;
+  }
+  if (threadIdx.x < BN) {
+    const int col = threadIdx.x, gc = tn * BN + col;
+    uint4 cm = make_uint4(0, 0, 0, 0);
+    float dx = 0.0f;
+    if (gc < N) {
+      const int4* bs = reinterpret_cast<const int4*>(act.bsums + (int64_t)(col0 + gc) * act.col_stride_bs + kb * 16);
+      const int4 b0 = bs[0], b1 = bs[1];
+      const int w[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      // pair sums (|s| <= 4064) split as s = 128*hi + lo with 0 <= lo < 128, so both parts are int8 for dp4a
+      uint32_t bl[8], bh[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int sj = (int)(short)(w[j] & 0xffff) + (w[j] >> 16);
+        bl[j] = (uint32_t)(sj & 127);
+        bh[j] = (uint32_t)(sj >> 7) & 0xffu;
+      }
+      cm = make_uint4(bl[0] | (bl[1] << 8) | (bl[2] << 16) | (bl[3] << 24), bl[4] | (bl[5] << 8) | (bl[6] << 16) | (bl[7] << 24),
+                      bh[0] | (bh[1] << 8) | (bh[2] << 16) | (bh[3] << 24), bh[4] | (bh[5] << 8) | (bh[6] << 16) | (bh[7] << 24));
+      dx = act.d[(int64_t)(col0 + gc) * act.col_stride_d + kb];
+    }
+    *reinterpret_cast<uint4*>(tile + kOperandBytes + col * 16) = cm;
+    *reinterpret_cast<float*>(tile + kOperandBytes + BN * 16 + col * 4) = dx;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-  uint8_t* raw = smem + kStages * kStageBytes;
+  uint8_t* meta = smem + kStages * kStageBytes;
+  uint8_t* raw = meta + kMetaSlots * kMetaBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawBytes);
-  uint64_t* full = bars;            // [2] producers -> MMA: operands of a super-block are in shared memory
-  uint64_t* tmem_full = bars + 2;   // [2] MMA -> epilogue: the accumulator pair holds a finished super-block
-  uint64_t* epi_done = bars + 4;    // [2] epilogue -> producers: stage and accumulator pair are free again
-  uint64_t* raw_full = bars + 6;    // bulk copies -> producers: the raw blocks of the next super-block landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* full = bars;            // [2] producers + bulk copies -> MMA: operands of a super-block are in shared memory
+  uint64_t* mma_done = bars + 2;    // [2] MMA -> producers: the operand stage may be overwritten
+  uint64_t* tmem_full = bars + 4;   // [2] MMA -> epilogue: the accumulator pair holds a finished super-block
+  uint64_t* epi_done = bars + 6;    // [2] epilogue -> MMA (accumulator pair free) and producers (scale slot free)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full + s, kProducerThreads);
+      mbar_init(full + s, kProducerThreads + 1);
+      mbar_init(mma_done + s, 1);
       mbar_init(tmem_full + s, 1);
       mbar_init(epi_done + s, kEpilogueWarps);
     }
-    mbar_init(raw_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -188,74 +234,58 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
 
   if (warp < 4) {
     // ---------------------------------------------------------------- producers
-    const int t = threadIdx.x;  // row t of the weight tile; column t for the per-column scales
+    const int t = threadIdx.x;  // row t of the weight tile
     const uint32_t core_off = (uint32_t)(t >> 3) * kGroupStride + (uint32_t)(t & 7) * 16;
-    // raw copy of row t's block of iteration (tile, kb); thread 0 also arms the barrier
+    // raw staging of iteration (tile, kb): 1152 16-byte pieces, piece g = (row g/9, part g%9) lands at g*16
     auto issue_raw = [&](int tile, int kb) {
       const int tm = tile / nt;
-      const int row = min(tm * BM + t, p.M - 1);          // out-of-range rows/columns repeat the last one; never stored
-      if (t == 0) mbar_arrive_expect_tx(raw_full, kRawBytes);
-      bulk_g2s(raw + t * Q4_K_BYTES, p.W + (size_t)row * p.row_bytes + (size_t)kb * Q4_K_BYTES, Q4_K_BYTES, raw_full);
+      const uint32_t rbase = smem_u32(raw);
+#pragma unroll
+      for (int j = 0; j < 9; ++j) {
+        const int g = t + 128 * j;
+        const int rr = g / 9, part = g - 9 * rr;
+        const int row = min(tm * BM + rr, p.M - 1);           // rows past M repeat the last one; never stored
+        const uint8_t* src = p.W + (size_t)row * p.row_bytes + (size_t)kb * Q4_K_BYTES + 16 * part;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(rbase + 16u * (uint32_t)g), "l"(src) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    // One flat loop over (tile, super-block).  The 128 producers meet at a named barrier every
+    // One flat loop over (tile, super-block).  The 128 producers meet at named barriers every
     // iteration, so nobody leaves early: a wait that gave up only skips work, and the loop ends
-    // for everyone at the abort check right after the barrier.
+    // for everyone at the abort check right after a barrier.
     int it = 0, tile = blockIdx.x, kb = 0;
     if (tile < ntiles) issue_raw(tile, 0);
     for (; tile < ntiles; ++it) {
       const int tn = tile % nt;
-      const int s = it & 1;
-      // this row's 144 raw bytes -> registers, then the staging buffer is free for the next copy
-      bool ok = mbar_wait(raw_full, it & 1, abort_flag);
+      const int s = it & 1, m = it & (kMetaSlots - 1);
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // everybody's pieces of this iteration's raw blocks landed
       uint4 blk[9];
 #pragma unroll
       for (int i = 0; i < 9; ++i) blk[i] = *reinterpret_cast<const uint4*>(raw + t * Q4_K_BYTES + 16 * i);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // everybody has read: the staging buffer is free
       if (*abort_flag) break;
       int ntile = tile, nkbi = kb + 1;
       if (nkbi == nkb) { nkbi = 0; ntile += gridDim.x; }
       if (ntile < ntiles) issue_raw(ntile, nkbi);
-      ok = ok && mbar_wait(epi_done + s, ((it >> 1) & 1) ^ 1, abort_flag);
+      // operand stage s was consumed by the MMAs of iteration it-2; those were issued after the epilogue of
+      // it-4 had finished, which is the last reader of scale slot m
+      const bool ok = mbar_wait(mma_done + s, ((it >> 1) & 1) ^ 1, abort_flag);
       if (ok) {
-        const int col = p.col0 + min(tn * BN + t, p.N - 1);
-        const int16_t* xb = p.act.bsums + (int64_t)col * p.act.col_stride_bs;
-        const float* xd = p.act.d + (int64_t)col * p.act.col_stride_d;
         uint8_t* st = smem + s * kStageBytes;
-        // activations: this warp's 32 columns, 8 columns x 4 chunks (64 contiguous bytes each) per instruction
-        {
-          const int col8 = lane & 7, cq = lane >> 3;
-          const uint32_t bbase = smem_u32(st + kOffB);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int cl = 32 * warp + 8 * g + col8;                       // column within the tile
-            const int8_t* src = p.act.qs + (int64_t)(p.col0 + min(tn * BN + cl, p.N - 1)) * p.act.col_stride_qs + kb * QK_K;
-            const uint32_t dst = bbase + (uint32_t)(cl >> 3) * kGroupStride + (uint32_t)(cl & 7) * 16;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int c = 4 * i + cq;
-              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c * kChunkStride), "l"(src + 16 * c) : "memory");
-            }
-          }
-        }
-        {
-          const int4* bs = reinterpret_cast<const int4*>(xb + kb * 16);
-          const int4 b0 = __ldg(bs), b1 = __ldg(bs + 1);
-          const int w[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-          uint32_t ps[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ps[j] = (uint32_t)((int)(short)(w[j] & 0xffff) + (w[j] >> 16)) & 0xffffu;
-          *reinterpret_cast<uint4*>(st + kOffColMeta + t * 16) =
-              make_uint4(ps[0] | (ps[1] << 16), ps[2] | (ps[3] << 16), ps[4] | (ps[5] << 16), ps[6] | (ps[7] << 16));
-          *reinterpret_cast<float*>(st + kOffDx + t * 4) = __ldg(xd + kb);
-        }
+        uint8_t* mt_ = meta + m * kMetaBytes;
         // weights of row t: scales, then the two int8 operands
         const uint4 h = blk[0];
         const uint32_t s0 = h.y, s1 = h.z, s2 = h.w;
         const uint32_t sc_lo4 = s0 & 0x3f3f3f3fu, mn_lo4 = s1 & 0x3f3f3f3fu;
         const uint32_t sc_hi4 = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
         const uint32_t mn_hi4 = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
-        *reinterpret_cast<uint4*>(st + kOffRowMeta + t * 16) =
-            make_uint4(__float_as_uint(h2f((uint16_t)(h.x & 0xffffu))), __float_as_uint(h2f((uint16_t)(h.x >> 16))), mn_lo4, mn_hi4);
+        {
+          uint32_t* rmw = reinterpret_cast<uint32_t*>(mt_ + kOffRowMeta + t * kRowMetaBytes);
+          rmw[0] = h.x;
+          rmw[1] = mn_lo4;
+          rmw[2] = mn_hi4;
+        }
         uint8_t* alo = st + kOffAlo + core_off;
         uint8_t* ahi = st + kOffAhi + core_off;
 #pragma unroll
@@ -278,17 +308,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
           *reinterpret_cast<uint4*>(ahi + (4 * g + 2) * kChunkStride) = make_uint4(hi[0] * hb, hi[1] * hb, hi[2] * hb, hi[3] * hb);
           *reinterpret_cast<uint4*>(ahi + (4 * g + 3) * kChunkStride) = make_uint4(hi[4] * hb, hi[5] * hb, hi[6] * hb, hi[7] * hb);
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core's reads
         mbar_arrive(full + s);
       }
       tile = ntile;
       kb = nkbi;
     }
-    if (*abort_flag) {
-      // a raw copy may still be in flight: give it a bounded moment before the CTA's shared memory goes away
-      for (int spins = 0; spins < (1 << 16) && !mbar_try_wait(raw_full, it & 1); ++spins) {}
-    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------------- MMA issue (one thread)
     if (lane == 0) {
@@ -297,7 +323,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
       for (int tile = blockIdx.x; live && tile < ntiles; tile += gridDim.x) {
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it & 1;
+          // operands in place, and the accumulator pair drained by the epilogue of iteration it-2
           if (!mbar_wait(full + s, (it >> 1) & 1, abort_flag)) { live = false; break; }
+          if (!mbar_wait(epi_done + s, ((it >> 1) & 1) ^ 1, abort_flag)) { live = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           uint8_t* st = smem + s * kStageBytes;
           const uint32_t a_lo = smem_u32(st + kOffAlo), a_hi = smem_u32(st + kOffAhi), b = smem_u32(st + kOffB);
@@ -308,6 +336,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
             mma_i8(d_lo, operand_desc(a_lo + 2 * j * kChunkStride), db, j > 0 ? 1u : 0u);
             mma_i8(d_hi, operand_desc(a_hi + 2 * j * kChunkStride), db, j > 0 ? 1u : 0u);
           }
+          mma_commit(mma_done + s);
           mma_commit(tmem_full + s);
           last_commit = it;
         }
@@ -317,6 +346,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
         uint64_t* bar = tmem_full + (last_commit & 1);
         const uint32_t parity = (last_commit >> 1) & 1;
         for (int spins = 0; spins < (1 << 20) && !mbar_try_wait(bar, parity); ++spins) {}
+      }
+    }
+  } else if (warp == kLoaderWarp) {
+    // ---------------------------------------------------------------- activation tile loader (one thread)
+    if (lane == 0) {
+      int it = 0;
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < ntiles; tile += gridDim.x) {
+        const int tn = tile % nt;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it & 1;
+          if (!mbar_wait(mma_done + s, ((it >> 1) & 1) ^ 1, abort_flag)) { live = false; break; }
+          uint8_t* st = smem + s * kStageBytes;
+          uint8_t* mt_ = meta + (it & (kMetaSlots - 1)) * kMetaBytes;
+          const uint8_t* tile_src = p.tiles + ((size_t)tn * nkb + kb) * kTileBytes;
+          mbar_arrive_expect_tx(full + s, kTileBytes);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            bulk_g2s(st + kOffB + q * (kOperandBytes / 4), tile_src + q * (kOperandBytes / 4), kOperandBytes / 4, full + s);
+          bulk_g2s(mt_ + kOffColMeta, tile_src + kOperandBytes, kColMetaBytes, full + s);
+        }
       }
     }
   } else {
@@ -336,28 +386,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
         const int s = it & 1;
         if (!mbar_wait(tmem_full + s, (it >> 1) & 1, abort_flag)) { live = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint8_t* st = smem + s * kStageBytes;
-        const uint4 rm = *reinterpret_cast<const uint4*>(st + kOffRowMeta + r * 16);
-        const float d = __uint_as_float(rm.x), dmin = __uint_as_float(rm.y);
-        const int mn_lo4 = (int)rm.z, mn_hi4 = (int)rm.w;
+        const uint8_t* mt_ = meta + (it & (kMetaSlots - 1)) * kMetaBytes;
+        const uint32_t* rmw = reinterpret_cast<const uint32_t*>(mt_ + kOffRowMeta + r * kRowMetaBytes);
+        const uint32_t dbits = rmw[0];
+        const float d = h2f((uint16_t)(dbits & 0xffffu)), dmin = h2f((uint16_t)(dbits >> 16));
+        const int mn_lo4 = (int)rmw[1], mn_hi4 = (int)rmw[2];
+        // the accumulator reads are software-pipelined: chunk c+1 is in flight while chunk c is folded in
+        uint32_t lo[2][8], hi[2][8];
+        const uint32_t tbase = lane_addr + (uint32_t)s * 256u;
+        tmem_ld8(tbase, lo[0]);
+        tmem_ld8(tbase + 128u, hi[0]);
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
-          uint32_t lo[8], hi[8];
-          tmem_ld8(lane_addr + (uint32_t)s * 256u + (uint32_t)(8 * c8), lo);
-          tmem_ld8(lane_addr + (uint32_t)s * 256u + 128u + (uint32_t)(8 * c8), hi);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (c8 < 3) {
+            tmem_ld8(tbase + (uint32_t)(8 * (c8 + 1)), lo[(c8 + 1) & 1]);
+            tmem_ld8(tbase + 128u + (uint32_t)(8 * (c8 + 1)), hi[(c8 + 1) & 1]);
+          }
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int col = 32 * cgroup + 8 * c8 + i;
-            const uint4 cm = *reinterpret_cast<const uint4*>(st + kOffColMeta + col * 16);
-            const float dx = *reinterpret_cast<const float*>(st + kOffDx + col * 4);
-            const int isum = (int)lo[i] + 8 * (int)hi[i];
-            int msum = __dp2a_lo((int)cm.x, mn_lo4, 0);
-            msum = __dp2a_hi((int)cm.y, mn_lo4, msum);
-            msum = __dp2a_lo((int)cm.z, mn_hi4, msum);
-            msum = __dp2a_hi((int)cm.w, mn_hi4, msum);
+            const uint4 cm = *reinterpret_cast<const uint4*>(mt_ + kOffColMeta + col * 16);
+            const float dx = *reinterpret_cast<const float*>(mt_ + kOffDx + col * 4);
+            const int isum = (int)lo[c8 & 1][i] + 8 * (int)hi[c8 & 1][i];
+            const int ml = __dp4a((int)cm.y, mn_hi4, __dp4a((int)cm.x, mn_lo4, 0));
+            const int mh = __dp4a((int)cm.w, mn_hi4, __dp4a((int)cm.z, mn_lo4, 0));
+            const int msum = ml + 128 * mh;                                     // |msum| <= 8*63*4064 < 2^22
+            const float msum_f = __fsub_rn(__int_as_float(msum + 0x4B400000), 12582912.0f);   // exact int -> float off the conversion pipe
             const float d_all = __fmul_rn(dx, d), d_min = __fmul_rn(dx, dmin);
-            const float bv = __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, (float)msum));
+            const float bv = __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, msum_f));
             acc[8 * c8 + i] = __fadd_rn(acc[8 * c8 + i], bv);
           }
         }
@@ -368,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
       if (!live) break;
       const int row = tm * BM + r;
       if (row < p.M) {
-        float* yr = p.y + (size_t)row * p.ldy + p.col0;
+        float* yr = p.y + (size_t)row * p.ldy;
         const int c0 = tn * BN + 32 * cgroup;
 #pragma unroll
         for (int i = 0; i < 32; ++i)
@@ -388,13 +445,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
 
 }  // namespace
 
+size_t gemm_tc_workspace_bytes(int K, int ncols) {
+  return (size_t)((ncols + BN - 1) / BN) * (size_t)(K / QK_K) * kTileBytes;
+}
+
 bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act) {
   return type == T_Q4_K && ncols >= kGemmTcMinCols && K % QK_K == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0 && row_bytes % 16 == 0 &&
          act.bsums != nullptr && (reinterpret_cast<uintptr_t>(act.qs) & 15) == 0 && act.col_stride_qs % 16 == 0 &&
          (reinterpret_cast<uintptr_t>(act.bsums) & 15) == 0 && act.col_stride_bs % 8 == 0;
 }
 
-cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
+// two launches: the activation tiling pre-pass (into `workspace`, gemm_tc_workspace_bytes) and the product
+cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, uint8_t* workspace, cudaStream_t st) {
   static unsigned configured = 0;  // one bit per device
   int dev = 0;
   cudaGetDevice(&dev);
@@ -403,18 +465,21 @@ cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, cudaS
     if (e != cudaSuccess) return e;
     configured |= 1u << (dev & 31);
   }
+  const int nt = (ncols + BN - 1) / BN;
+  tile_activations_kernel<<<dim3(a.K / QK_K, nt), 256, 0, st>>>(a.act, a.col0, ncols, a.K, workspace);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
   GemmArgs g{};
   g.W = a.W;
   g.row_bytes = a.row_bytes;
   g.M = a.M;
   g.K = a.K;
   g.N = ncols;
-  g.act = a.act;
-  g.col0 = a.col0;
-  g.y = a.y;
+  g.tiles = workspace;
+  g.y = a.y + a.col0;
   g.ldy = a.ldy;
   g.status = a.status;
-  const int tiles = ((a.M + BM - 1) / BM) * ((ncols + BN - 1) / BN);
+  const int tiles = ((a.M + BM - 1) / BM) * nt;
   const int grid = tiles < sm_count ? tiles : sm_count;
   gemm_q4k_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(g);
   return cudaGetLastError();

@@ -739,9 +739,10 @@ cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int
                         int* launches) {
   // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
   static const bool no_tc = getenv("EMELB_NO_TC") != nullptr;
-  if (!argmax && !no_tc && gemm_tc_supported(type, a.K, ncols, a.W, a.row_bytes, a.act)) {
-    ++*launches;
-    return launch_gemm_q4k_tc(a, ncols, sm_count, st);
+  if (!argmax && !no_tc && a.tc_ws && gemm_tc_supported(type, a.K, ncols, a.W, a.row_bytes, a.act) &&
+      gemm_tc_workspace_bytes(a.K, ncols) <= a.tc_ws_bytes) {
+    *launches += 2;
+    return launch_gemm_q4k_tc(a, ncols, sm_count, a.tc_ws, st);
   }
   const bool fast = gemv_fast_path_ok(type, a.W, a.row_bytes, a.K);
   int grid = 0;

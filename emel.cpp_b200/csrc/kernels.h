@@ -52,6 +52,8 @@ struct GemvArgs {
   int M2, M3;
   float* y2;
   float* y3;
+  uint8_t* tc_ws;        // workspace of the many-column tensor-core kernel (null: that kernel is not used)
+  size_t tc_ws_bytes;
   int* sched;            // {next task, finished blocks}: zero between launches (self-rearming)
   int* status;           // optional: set to 1 by a kernel whose bounded wait ran out
   int pdl;               // launch with programmatic stream serialization (kernels wait before dependent reads)
@@ -109,7 +111,8 @@ cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out
 // same numbers as the mat-vec kernels.  a.col0/a.y/a.ldy address the output as for launch_gemv.
 constexpr int kGemmTcMinCols = 32;
 bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act);
-cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st);
+size_t gemm_tc_workspace_bytes(int K, int ncols);
+cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, uint8_t* workspace, cudaStream_t st);
 
 cudaError_t launch_argmax_pair_store(const float* best_val, const int* best_idx, int row_offset, int* pair, cudaStream_t st);
 cudaError_t launch_argmax_pair_finish(const int* pairs, int n, float* out_val, int* out_idx, cudaStream_t st);
