@@ -125,28 +125,29 @@ __global__ void rope_store_kernel(float* q, const float* k, const float* v, cons
 
 // ---- ffn = (gate / (1 + expf(-gate))) * up, quantized for the down projection
 template <int FAMILY>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, int n, float* out, ActPlanesMut planes) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   if constexpr (FAMILY == 1) {
-    const int blk = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (blk >= n / QK_K) return;
-    const int e0 = blk * QK_K + 8 * lane;
-    float v[8];
+    // one 256-block per CTA: each of 256 threads one element (the expf dominates), then warp 0 quantizes
+    __shared__ float s_v[QK_K];
+    const int blk = blockIdx.x;
+    const int e = blk * QK_K + threadIdx.x;
+    const float g = gate[e];
+    const float r = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf_exact(-g))), up[e]);
+    if (out) out[e] = r;
+    s_v[threadIdx.x] = r;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float g = gate[e0 + i];
-      v[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf_exact(-g))), up[e0 + i]);
+      for (int i = 0; i < 8; ++i) v[i] = s_v[8 * lane + i];
+      uint32_t lo, hi; int s; float d;
+      q8_k_block_warp(v, lane, lo, hi, s, d);
+      q8_k_store_planes(planes, 0, n, blk, lane, lo, hi, s, d);
     }
-    if (out) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) out[e0 + i] = v[i];
-    }
-    uint32_t lo, hi; int s; float d;
-    q8_k_block_warp(v, lane, lo, hi, s, d);
-    q8_k_store_planes(planes, 0, n, blk, lane, lo, hi, s, d);
   } else {
     const int e0 = 4 * (blockIdx.x * 128 + threadIdx.x);
     const bool live = e0 < n;
@@ -261,7 +262,7 @@ cudaError_t launch_rope_store(float* q, const float* k, const float* v, const fl
 
 cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out, int family, ActPlanesMut planes,
                           cudaStream_t st) {
-  if (family == 1) EMELB_LAUNCH(swiglu_kernel<1>, (n / QK_K + 3) / 4, 128, 0, st, gate, up, n, out, planes);
+  if (family == 1) EMELB_LAUNCH(swiglu_kernel<1>, n / QK_K, 256, 0, st, gate, up, n, out, planes);
   else if (family == 2) EMELB_LAUNCH(swiglu_kernel<2>, (n / 4 + 127) / 128, 128, 0, st, gate, up, n, out, planes);
   else EMELB_LAUNCH(swiglu_kernel<0>, (n / 4 + 127) / 128, 128, 0, st, gate, up, n, out, planes);
   return cudaGetLastError();

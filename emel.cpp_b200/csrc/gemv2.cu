@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "quant_device.cuh"
 
 namespace emelb {
 
@@ -616,21 +617,62 @@ gemv3_kernel(const GemvArgs p) {
   for (int s = 0; s < STAGES; ++s) issue_next(s);
   pdl_wait();
 
-  // stage this column's quantized activations in shared memory for the whole CTA
+  // this column's quantized activations in shared memory for the whole CTA: copied from the planes, or
+  // (fused prologue) normalised and quantized here from the f32 vector
   ActSmem x;
   {
     int8_t* sq = reinterpret_cast<int8_t*>(smem3);
     int16_t* sb = reinterpret_cast<int16_t*>(smem3 + ((p.K + 15) / 16) * 16);
     float* sd = reinterpret_cast<float*>(smem3 + ((p.K + 15) / 16) * 16 + (KQ ? ((p.K / 8 + 15) / 16) * 16 : 0));
-    const int4* gq = reinterpret_cast<const int4*>(p.act.qs + (int64_t)p.col0 * p.act.col_stride_qs);
-    for (int i = threadIdx.x; i < p.K / 16; i += WARPS * 32) reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = __ldg(gq + i);
+    bool fused = false;
     if constexpr (KQ) {
-      const int4* gb = reinterpret_cast<const int4*>(p.act.bsums + (int64_t)p.col0 * p.act.col_stride_bs);
-      for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = __ldg(gb + i);
+      if (p.pro_x) {
+        fused = true;
+        // rms_norm (src/emel/text/generator/detail.hpp:2735-2756): f64 sum of the f32 squares
+        __shared__ double s_part[WARPS];
+        double ss = 0.0;
+        for (int i = threadIdx.x; i < p.K; i += WARPS * 32) {
+          const float v = __ldg(p.pro_x + i);
+          ss += (double)__fmul_rn(v, v);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s_part[warp] = ss;
+        __syncthreads();
+        double total = 0.0;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) total += s_part[w];
+        const float mean = (float)(total / (double)p.K);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.pro_eps)));
+        for (int blk = warp; blk < p.K / QK_K; blk += WARPS) {
+          float v[8];
+          const int e0 = blk * QK_K + 8 * lane;
+          const float4 x0 = __ldg(reinterpret_cast<const float4*>(p.pro_x + e0)), x1 = __ldg(reinterpret_cast<const float4*>(p.pro_x + e0) + 1);
+          const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.pro_w + e0)), w1 = __ldg(reinterpret_cast<const float4*>(p.pro_w + e0) + 1);
+          const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+          const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(xs[i], scale), ws[i]);
+          uint32_t lo, hi; int bs16; float dq;
+          q8_k_block_warp(v, lane, lo, hi, bs16, dq);
+          const int unit = blk * 16 + ((lane >> 1) ^ (blk & 7));        // the swizzled 16-byte unit of elements 8*lane..
+          *reinterpret_cast<uint2*>(sq + unit * 16 + (lane & 1) * 8) = make_uint2(lo, hi);
+          if ((lane & 1) == 0) sb[blk * 16 + (lane >> 1)] = (int16_t)bs16;
+          if (lane == 0) sd[blk] = dq;
+        }
+      }
     }
-    const float* gd = p.act.d + (int64_t)p.col0 * p.act.col_stride_d;
-    const int nd = KQ ? p.K / QK_K : p.K / 32;
-    for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = __ldg(gd + i);
+    if (!fused) {
+      const int4* gq = reinterpret_cast<const int4*>(p.act.qs + (int64_t)p.col0 * p.act.col_stride_qs);
+      for (int i = threadIdx.x; i < p.K / 16; i += WARPS * 32) reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = __ldg(gq + i);
+      if constexpr (KQ) {
+        const int4* gb = reinterpret_cast<const int4*>(p.act.bsums + (int64_t)p.col0 * p.act.col_stride_bs);
+        for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = __ldg(gb + i);
+      }
+      const float* gd = p.act.d + (int64_t)p.col0 * p.act.col_stride_d;
+      const int nd = KQ ? p.K / QK_K : p.K / 32;
+      for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = __ldg(gd + i);
+    }
     x.qs = sq;
     x.bs = sb;
     x.d = sd;
@@ -868,6 +910,12 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
 }
 
 }  // namespace
+
+bool gemv_prologue_supported(int type, const void* w, int64_t row_bytes, int K) {
+  static const bool v1 = getenv("EMELB_GEMV_V1") != nullptr;
+  return !v1 && gen3_config() >= 0 && is_k_type(type) && (K % CHUNK) == 0 && (reinterpret_cast<uintptr_t>(w) % 16) == 0 &&
+         (row_bytes % 16) == 0;
+}
 
 // the streaming path for K % 2048 == 0 and 16-byte aligned rows; the caller runs the
 // argmax finishing kernel over *grid_out candidates

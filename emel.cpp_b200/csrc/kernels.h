@@ -52,6 +52,12 @@ struct GemvArgs {
   int M2, M3;
   float* y2;
   float* y3;
+  // optional fused prologue of the one-column streaming kernel (K-quant weights only): instead of reading
+  // `act`, every CTA normalises pro_x itself, out = (x * 1/sqrt(mean(x^2) + eps)) * pro_w, and quantizes it to
+  // Q8_K in shared memory — the rms_norm step of the layer without its own launch
+  const float* pro_x;
+  const float* pro_w;
+  float pro_eps;
   uint8_t* tc_ws;        // workspace of the many-column tensor-core kernel (null: that kernel is not used)
   size_t tc_ws_bytes;
   int* sched;            // {next task, finished blocks}: zero between launches (self-rearming)
@@ -111,6 +117,8 @@ cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out
 // same numbers as the mat-vec kernels.  a.col0/a.y/a.ldy address the output as for launch_gemv.
 constexpr int kGemmTcMinCols = 32;
 bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act);
+// true when launch_gemv would run the kernel that honours GemvArgs::pro_x for this matrix
+bool gemv_prologue_supported(int type, const void* w, int64_t row_bytes, int K);
 size_t gemm_tc_workspace_bytes(int K, int ncols);
 cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, uint8_t* workspace, cudaStream_t st);
 

@@ -178,6 +178,44 @@ struct Enqueue {
     s->planes_family = family;
   }
 
+  // norm(x) -> up to three matrices of one type, or the argmax head.  When the streaming kernel takes the
+  // shapes, the normalisation and quantization run inside the mat-vec launch (no rms_norm kernel).
+  void normed_matvec_group(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax = false) {
+    bool fuse = getenv("EMELB_NO_FUSED_NORM") == nullptr && (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
+                (reinterpret_cast<uintptr_t>(nw.dev) % 16) == 0 && n >= 1 && n <= 3;
+    for (int i = 0; fuse && i < n; ++i)
+      fuse = gemv_prologue_supported(w[i]->type, w[i]->dev, w[i]->row_bytes, w[i]->K) && w[i]->type == w[0]->type &&
+             w[i]->K == w[0]->K && w[i]->row_bytes == w[0]->row_bytes && w[i]->K == s->cfg.n_embd;
+    if (!fuse) {
+      rms_norm(x, nw, family_of(w[0]->type));
+      if (n == 1) matvec(*w[0], s->norm, y ? y[0] : nullptr, nullptr, argmax);
+      else matvec_group(w, y, n, s->norm);
+      return;
+    }
+    GemvArgs a{};
+    a.W = w[0]->dev;
+    a.row_bytes = w[0]->row_bytes;
+    a.M = w[0]->M;
+    a.K = w[0]->K;
+    a.act = planes_view(planes(), w[0]->type, w[0]->K);   // unused by the fused prologue
+    a.y = y ? y[0] : nullptr;
+    a.ldy = 1;
+    if (n >= 2) { a.W2 = w[1]->dev; a.M2 = w[1]->M; a.y2 = y[1]; }
+    if (n == 3) { a.W3 = w[2]->dev; a.M3 = w[2]->M; a.y3 = y[2]; }
+    a.pro_x = x;
+    a.pro_w = reinterpret_cast<const float*>(nw.dev);
+    a.pro_eps = s->cfg.rms_eps;
+    a.sched = s->c->next_sched();
+    a.status = s->c->status_word();
+    a.pdl = s->c->pdl;
+    a.part_val = s->c->part_val;
+    a.part_idx = s->c->part_idx;
+    a.best_val = s->c->best_val;
+    a.best_idx = s->c->best_idx;
+    check(launch_gemv(w[0]->type, a, 1, argmax, s->c->sm_count, st, &launches));
+    s->planes_src = nullptr;
+  }
+
   // attention of one layer; when the split-KV kernels run unsharded, their merge step also leaves the
   // context quantized for the output projection (family of wo's type)
   void attention(int layer, int out_family) {
@@ -231,11 +269,10 @@ struct Enqueue {
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
       const Layer& w = s->layers[l];
-      rms_norm(s->hidden, w.attn_norm, family_of(w.wq.type));
       {
         const Tensor* ws[3] = {&w.wq, &w.wk, &w.wv};
         float* ys[3] = {s->q, s->k, s->v};
-        matvec_group(ws, ys, 3, s->norm);
+        normed_matvec_group(s->hidden, w.attn_norm, ws, ys, 3);
       }
       const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
       check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, heads_l, kv_l, c.head_dim,
@@ -246,14 +283,13 @@ struct Enqueue {
       gather(s->attn, q_l);
       matvec(w.wo, s->attn, hidden_mine, hidden_mine);   // hidden += Wo * attn (this rank's rows)
       gather(s->hidden, embd_l);
-      rms_norm(s->hidden, w.ffn_norm, family_of(w.gate.type));
       {
         const Tensor* ws[2] = {&w.gate, &w.up};
         float* ys[2] = {s->gate, s->up};
-        matvec_group(ws, ys, 2, s->norm);
+        normed_matvec_group(s->hidden, w.ffn_norm, ws, ys, 2);
       }
       if (G == 1) {
-        check(launch_swiglu(s->gate, s->up, c.n_ff, s->ffn, family_of(w.down.type), planes(), st));
+        check(launch_swiglu(s->gate, s->up, c.n_ff, nullptr, family_of(w.down.type), planes(), st));  // only the quantized product is consumed
         s->planes_src = s->ffn;
         s->planes_family = family_of(w.down.type);
       } else {
@@ -267,10 +303,10 @@ struct Enqueue {
       gather(s->hidden, embd_l);
     }
     if (mode == MODE_PREFILL) return;
-    rms_norm(s->hidden, s->out_norm, family_of(s->output.type));
     const size_t vocab_l = (size_t)c.n_vocab / G;
+    const Tensor* head[1] = {&s->output};
     if (mode == MODE_ARGMAX) {
-      matvec(s->output, s->norm, nullptr, nullptr, true);
+      normed_matvec_group(s->hidden, s->out_norm, head, nullptr, 1, true);
       if (G > 1) {
         // candidates {value, global row} of every rank, then the same lowest-row tie rule
         check(launch_argmax_pair_store(s->c->best_val, s->c->best_idx, (int)(r * vocab_l), s->pair_buf + 2 * r, st));
@@ -281,7 +317,8 @@ struct Enqueue {
       check(launch_step_advance(s->state, s->c->best_idx, s->tokens_dev, st));
       ++launches;
     } else {
-      matvec(s->output, s->norm, s->logits + r * vocab_l, nullptr);
+      float* ys[1] = {s->logits + r * vocab_l};
+      normed_matvec_group(s->hidden, s->out_norm, head, ys, 1);
       gather(s->logits, vocab_l);
     }
   }

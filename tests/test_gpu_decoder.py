@@ -134,7 +134,10 @@ def test_argmax_route_generate_and_split_kv_attention(be, port):
         cpu.close()
 
 
-def test_decoder_rejects_bad_requests(be, port):
+def test_decoder_rejects_bad_requests(port):
+    # own context: the shared one still maps host spans of arrays earlier tests uploaded and freed, and a
+    # new array may be handed one of those addresses
+    be = eb.Backend(0)
     c = el.config(**TINY)
     sess = el.Session(be, c)
     try:
@@ -148,3 +151,4 @@ def test_decoder_rejects_bad_requests(be, port):
     bad = dict(TINY, n_embd=500)
     with pytest.raises(eb.BackendError):
         el.Session(be, el.config(**bad))
+    be.close()
