@@ -865,7 +865,9 @@ cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* g
                      (a.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
   if (ntasks >= 8 * 3 * sm_count || ARGMAX) return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX>(a, sm_count, st, grid_out);
   if (ntasks >= 4 * 3 * sm_count) return launch3<T, 1, 4, kWarpsPerSm / 4, ARGMAX>(a, sm_count, st, grid_out);
-  return launch3<T, 1, 2, kWarpsPerSm / 2, ARGMAX>(a, sm_count, st, grid_out);
+  // about one task per warp: keep the whole row group of a warp in flight (2 chunks), or a deeper ring for long rows
+  if (a.K / CHUNK >= 4) return launch3<T, 4, 2, kLight ? 4 : 3, ARGMAX>(a, sm_count, st, grid_out);
+  return launch3<T, 2, 2, kLight ? 8 : 4, ARGMAX>(a, sm_count, st, grid_out);
 }
 
 inline int passes_override() {
