@@ -298,7 +298,7 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
   };
   // EMELB_PDL=1: the decoder launches its kernel chain with programmatic stream serialization, so a
   // mat-vec starts prefetching weights while the kernel before it is still finishing
-  c->pdl = std::getenv("EMELB_PDL") && std::atoi(std::getenv("EMELB_PDL")) != 0 ? 1 : 0;
+  c->pdl = std::getenv("EMELB_PDL") ? std::atoi(std::getenv("EMELB_PDL")) : 1;  // bit mask, see llama.cu
   c->stage_in_bytes = env_mb("EMELB_STAGE_IN_MB", 128);
   c->stage_out_bytes = env_mb("EMELB_STAGE_OUT_MB", 128);
   c->act_capacity = env_mb("EMELB_ACT_MELEMS", 64);  // quantized activation elements held at once

@@ -92,6 +92,12 @@ __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
     return;
   }
 
+  // pull this range's V rows towards L2 while the scores are computed
+  {
+    const char* vrange = reinterpret_cast<const char*>(a.v) + (size_t)kh * a.v_nb2 + (size_t)t0 * a.v_nb1;
+    const size_t vbytes = (size_t)n * a.v_nb1;
+    for (size_t off = (size_t)tid * 128; off < vbytes; off += 128 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(vrange + off));
+  }
   // ---- scores: q is rounded to f16 first, as the reference does (detail.hpp:5255)
   const int l8 = tid & 7, slot = tid >> 3;
   float q[NREP][DPL];
@@ -421,7 +427,7 @@ cudaError_t launch_split(const FlashArgs& a, int n_rep, cudaStream_t st) {
 
 int flash_pick_splits(int tokens, int kv_heads, int sm_count, int max_splits) {
   int need = (tokens + LMAX - 1) / LMAX;          // score buffer bound
-  int want = (2 * sm_count + kv_heads - 1) / kv_heads;  // ~2 CTAs per SM
+  int want = (2 * sm_count + kv_heads - 1) / kv_heads;  // ~2 CTAs per SM (3 and 4 measured slower in the decode loop)
   const int by_len = tokens / 32 > 0 ? tokens / 32 : 1; // at least 32 tokens per range
   if (want > by_len) want = by_len;
   if (want < need) want = need;

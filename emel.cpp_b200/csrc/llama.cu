@@ -135,7 +135,7 @@ struct Enqueue {
     a.residual = residual;
     a.sched = s->c->next_sched();
     a.status = s->c->status_word();
-    a.pdl = s->c->pdl;
+    a.pdl = s->c->pdl & 1;
     a.part_val = s->c->part_val;
     a.part_idx = s->c->part_idx;
     a.best_val = s->c->best_val;
@@ -166,7 +166,7 @@ struct Enqueue {
     if (n == 3) { a.W3 = w[2]->dev; a.M3 = w[2]->M; a.y3 = y[2]; }
     a.sched = s->c->next_sched();
     a.status = s->c->status_word();
-    a.pdl = s->c->pdl;
+    a.pdl = s->c->pdl & 1;
     check(launch_gemv(w[0]->type, a, 1, false, s->c->sm_count, st, &launches));
   }
 
@@ -207,7 +207,7 @@ struct Enqueue {
     a.pro_eps = s->cfg.rms_eps;
     a.sched = s->c->next_sched();
     a.status = s->c->status_word();
-    a.pdl = s->c->pdl;
+    a.pdl = s->c->pdl & 1;
     a.part_val = s->c->part_val;
     a.part_idx = s->c->part_idx;
     a.best_val = s->c->best_val;
@@ -256,10 +256,14 @@ struct Enqueue {
 
   void token_step(Mode mode) {
     const emelb_llama_config& c = s->cfg;
-    struct PdlScope {  // launches of this step carry the programmatic-serialization attribute when enabled
+    // which launches of the step carry the programmatic-serialization attribute (bit mask: 1 mat-vecs,
+    // 2 RoPE/KV store, 4 attention, 8 SwiGLU, 16 the rest); the flag is read by EMELB_LAUNCH
+    struct PdlScope {
       explicit PdlScope(bool on) { g_pdl_launch = on; }
       ~PdlScope() { g_pdl_launch = false; }
-    } pdl_scope(s->c->pdl != 0);
+    };
+    const int pm = s->c->pdl;
+    PdlScope pdl_rest((pm & 16) != 0);
     const int G = s->G, r = s->rank;
     const int heads_l = c.n_head / G, kv_l = c.n_head_kv / G;
     const size_t q_l = (size_t)heads_l * c.head_dim, embd_l = (size_t)c.n_embd / G, ff_l = (size_t)c.n_ff / G;
@@ -275,11 +279,14 @@ struct Enqueue {
         normed_matvec_group(s->hidden, w.attn_norm, ws, ys, 3);
       }
       const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
+      g_pdl_launch = (pm & 2) != 0;
       check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, heads_l, kv_l, c.head_dim,
                               c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
                               s->vcache + layer_off, s->capacity * c.head_dim, st));
       ++launches;
+      g_pdl_launch = (pm & 4) != 0;
       attention(l, family_of(w.wo.type));
+      g_pdl_launch = (pm & 16) != 0;
       gather(s->attn, q_l);
       matvec(w.wo, s->attn, hidden_mine, hidden_mine);   // hidden += Wo * attn (this rank's rows)
       gather(s->hidden, embd_l);
@@ -288,6 +295,7 @@ struct Enqueue {
         float* ys[2] = {s->gate, s->up};
         normed_matvec_group(s->hidden, w.ffn_norm, ws, ys, 2);
       }
+      g_pdl_launch = (pm & 8) != 0;
       if (G == 1) {
         check(launch_swiglu(s->gate, s->up, c.n_ff, nullptr, family_of(w.down.type), planes(), st));  // only the quantized product is consumed
         s->planes_src = s->ffn;
@@ -298,6 +306,7 @@ struct Enqueue {
         s->planes_src = nullptr;
       }
       ++launches;
+      g_pdl_launch = (pm & 16) != 0;
       gather(s->ffn, ff_l);
       matvec(w.down, s->ffn, hidden_mine, hidden_mine);  // hidden += Wdown * ffn
       gather(s->hidden, embd_l);
