@@ -545,6 +545,12 @@ def run_decode(args):
     cfg = el.config(sh["n_layer"], sh["n_embd"], sh["n_head"], sh["n_head_kv"], sh["head_dim"], sh["n_ff"], sh["n_vocab"], n_ctx,
                     shard_rank=r, shard_count=G)
     sess = el.Session(be, cfg)
+    peer_joins = False
+    if shard and os.environ.get("EMELB_SHARD_JOIN", "peer") == "peer":
+        handles = [None] * world
+        dist.all_gather_object(handles, sess.exchange_export())
+        assert sess.exchange_attach(handles), sess.last_error
+        peer_joins = True
 
     # weights N(0, 0.02) encoded on the device; norm weights 1.0 (each rank builds its own replica)
     tensors = decode_tensors(sh, out_type)
@@ -651,7 +657,8 @@ def run_decode(args):
                    "launch": "one CUDA-graph replay per token; the next token id is fed back on the device",
                    "l2_policy": f"inputs larger than L2: {weight_bytes / 1e9:.2f} GB of weights streamed per token",
                    "parallelism": "single GPU" if world == 1 else (
-                       f"one sequence, matrices row-sharded over {world} GPUs, 4 f32 all-gathers per layer (NCCL)" if shard
+                       f"one sequence, matrices row-sharded over {world} GPUs, 4 joins of f32 row intervals per layer "
+                       f"({'peer stores over NVLink, one kernel per join' if peer_joins else 'NCCL all-gather'})" if shard
                        else f"{world} independent replicas (one sequence per GPU), no collective"),
                    "kernel_launches_per_token": sess.launches_per_token(),
                    "prefill_s": "skipped: zero-filled KV cache, profiling aid, not a benchmark number" if args.profile_skip_prefill
@@ -672,6 +679,7 @@ def run_decode(args):
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline_decode(sh, out_type, budget_s=args.cpu_budget)
         print(json.dumps(line), flush=True)
+    barrier(world)              # no rank frees an exchange arena while a peer may still store into it
     sess.close()
     be.close()
     if world > 1:

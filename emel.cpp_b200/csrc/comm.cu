@@ -32,6 +32,65 @@ cudaError_t comm_all_gather_bytes(emelb_ctx* c, void* buf, size_t bytes_per_rank
 #endif
 }
 
+// ---- peer-store join (same node): each rank copies its row interval straight into every peer's copy of the
+// vector over NVLink, raises a per-sender sequence flag on the peer, and waits for every peer's flag.  One small
+// kernel per join instead of a collective launch; plain peer stores and loads (no multimem), so a rank that
+// leaves between steps cannot fault its peers.  Waits are bounded: on a timeout the status word is raised and
+// the kernel returns.
+namespace {
+
+constexpr int kPeerWaitSpins = 1 << 24;
+constexpr unsigned long long kPeerWaitNs = 2000000000ull;  // 2 s
+
+__global__ void __launch_bounds__(1024) peer_gather_kernel(PeerGatherArgs a) {
+  const int peers = a.world - 1;
+  // 1. my interval -> every peer's buffer (16-byte stores; intervals are multiples of 16 bytes)
+  const uint4* src = reinterpret_cast<const uint4*>(a.local_base + a.offset_bytes);
+  const size_t n16 = a.bytes_per_rank / 16;
+  for (size_t i = threadIdx.x; i < n16 * (size_t)peers; i += blockDim.x) {
+    const int pi = (int)(i / n16);
+    const size_t j = i - (size_t)pi * n16;
+    const int peer = pi < a.rank ? pi : pi + 1;
+    reinterpret_cast<uint4*>(a.peer_base[peer] + a.offset_bytes)[j] = src[j];
+  }
+  __threadfence_system();
+  __syncthreads();
+  // 2. advance my sequence number and publish it on every peer
+  __shared__ unsigned int s_seq;
+  if (threadIdx.x == 0) s_seq = ++(*a.seq);
+  __syncthreads();
+  const unsigned int seq = s_seq;
+  if (threadIdx.x < a.world && (int)threadIdx.x != a.rank) {
+    unsigned int* flag = reinterpret_cast<unsigned int*>(a.peer_base[threadIdx.x] + a.flags_offset) + a.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+  }
+  // 3. wait until every peer's data for this join has landed here
+  if (threadIdx.x < a.world && (int)threadIdx.x != a.rank) {
+    const unsigned int* flag = reinterpret_cast<const unsigned int*>(a.local_base + a.flags_offset) + threadIdx.x;
+    unsigned long long t0 = 0;
+    bool ok = false;
+    for (int spins = 0; spins < kPeerWaitSpins; ++spins) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if ((int)(v - seq) >= 0) { ok = true; break; }
+      if ((spins & 1023) == 1023) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kPeerWaitNs) break;
+      }
+    }
+    if (!ok && a.status) atomicExch(a.status, 1);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_peer_gather(const PeerGatherArgs& a, cudaStream_t st) {
+  peer_gather_kernel<<<1, 1024, 0, st>>>(a);
+  return cudaGetLastError();
+}
+
 void comm_release(emelb_ctx* c) {
 #if defined(EMELB_HAVE_NCCL)
   if (c->comm) ncclCommDestroy(static_cast<ncclComm_t>(c->comm));

@@ -286,8 +286,8 @@ __global__ void argmax_pair_finish_kernel(const int* pairs, int n, float* out_va
   float bv = __int_as_float(pairs[0]);
   int bi = pairs[1];
   for (int i = 1; i < n; ++i) {
-    const float v = __int_as_float(pairs[2 * i]);
-    const int r = pairs[2 * i + 1];
+    const float v = __int_as_float(pairs[4 * i]);   // one 16-byte record per rank
+    const int r = pairs[4 * i + 1];
     if (v > bv || (v == bv && r < bi)) { bv = v; bi = r; }
   }
   *out_val = bv;

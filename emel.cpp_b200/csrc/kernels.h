@@ -125,6 +125,20 @@ cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, uint8
 cudaError_t launch_argmax_pair_store(const float* best_val, const int* best_idx, int row_offset, int* pair, cudaStream_t st);
 cudaError_t launch_argmax_pair_finish(const int* pairs, int n, float* out_val, int* out_idx, cudaStream_t st);
 
+// comm.cu — join of row intervals by peer stores (one rank per GPU, same node)
+constexpr int kMaxPeers = 8;
+struct PeerGatherArgs {
+  char* local_base;            // this rank's arena
+  char* peer_base[kMaxPeers];  // every rank's arena as mapped here (own entry = local_base)
+  size_t offset_bytes;         // of this rank's interval inside the arena (vector offset + rank * bytes_per_rank)
+  size_t bytes_per_rank;
+  size_t flags_offset;         // kMaxPeers u32 sequence flags inside the arena, indexed by sender
+  unsigned int* seq;           // this rank's join counter
+  int rank, world;
+  int* status;
+};
+cudaError_t launch_peer_gather(const PeerGatherArgs& a, cudaStream_t st);
+
 // synth.cu — synthetic N(0, sigma) data generated and block-encoded on the device
 cudaError_t launch_fill_normal(float* out, uint64_t n, uint64_t seed, float sigma, uint64_t offset, cudaStream_t st);
 cudaError_t launch_encode_normal(int type, uint8_t* out, uint64_t elems, uint64_t seed, float sigma, uint64_t offset,

@@ -69,7 +69,13 @@ struct emelb_llama {
   int* host_pinned = nullptr;
   int fa_splits = 1;
   int G = 1, rank = 0;        // row sharding
-  int* pair_buf = nullptr;    // G x {value bits, global row} argmax candidates
+  int* pair_buf = nullptr;    // G x 16-byte records {value bits, global row, -, -}: argmax candidates
+  // sharded sessions keep the vectors that are joined across ranks in one allocation (the exchange arena) so
+  // peers can map it; with every peer attached the joins run as peer stores instead of NCCL calls
+  char* arena = nullptr;
+  size_t arena_bytes = 0, flags_off = 0, seq_off = 0;
+  char* peer_base[kMaxPeers] = {};
+  bool peers_attached = false;
   cudaGraphExec_t graphs[MODE_COUNT] = {nullptr, nullptr, nullptr};
   int graph_attention_mode[MODE_COUNT] = {-1, -1, -1};
   int launches_per_token = 0;          // of the argmax step
@@ -249,10 +255,27 @@ struct Enqueue {
     }
   }
 
-  // join the ranks' row intervals of a full-length f32 vector (no-op unsharded)
-  void gather(float* full, size_t count_per_rank) {
-    if (s->G > 1) check(comm_all_gather_bytes(s->c, full, count_per_rank * sizeof(float), st));
+  // join the ranks' row intervals of a full-length vector inside the arena (no-op unsharded)
+  void gather_bytes(void* full, size_t bytes_per_rank) {
+    if (s->G <= 1) return;
+    if (!s->peers_attached) {
+      check(comm_all_gather_bytes(s->c, full, bytes_per_rank, st));
+      return;
+    }
+    PeerGatherArgs a{};
+    a.local_base = s->arena;
+    for (int g = 0; g < s->G; ++g) a.peer_base[g] = s->peer_base[g];
+    a.offset_bytes = (size_t)(static_cast<char*>(full) - s->arena) + (size_t)s->rank * bytes_per_rank;
+    a.bytes_per_rank = bytes_per_rank;
+    a.flags_offset = s->flags_off;
+    a.seq = reinterpret_cast<unsigned int*>(s->arena + s->seq_off);
+    a.rank = s->rank;
+    a.world = s->G;
+    a.status = s->c->status_word();
+    check(launch_peer_gather(a, st));
+    ++launches;
   }
+  void gather(float* full, size_t count_per_rank) { gather_bytes(full, count_per_rank * sizeof(float)); }
 
   void token_step(Mode mode) {
     const emelb_llama_config& c = s->cfg;
@@ -318,8 +341,8 @@ struct Enqueue {
       normed_matvec_group(s->hidden, s->out_norm, head, nullptr, 1, true);
       if (G > 1) {
         // candidates {value, global row} of every rank, then the same lowest-row tie rule
-        check(launch_argmax_pair_store(s->c->best_val, s->c->best_idx, (int)(r * vocab_l), s->pair_buf + 2 * r, st));
-        check(comm_all_gather_bytes(s->c, s->pair_buf, 2 * sizeof(int), st));
+        check(launch_argmax_pair_store(s->c->best_val, s->c->best_idx, (int)(r * vocab_l), s->pair_buf + 4 * r, st));
+        gather_bytes(s->pair_buf, 4 * sizeof(int));
         check(launch_argmax_pair_finish(s->pair_buf, G, s->c->best_val, s->c->best_idx, st));
         launches += 2;
       }
@@ -403,22 +426,42 @@ uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_l
   const size_t cache_halves = (size_t)g.n_layer * (g.n_head_kv / G) * s->capacity * g.head_dim;  // this rank's KV heads
   const int pairs = (g.rope_dim < g.head_dim ? g.rope_dim : g.head_dim) / 2;
   bool ok = true;
-  ok = ok && dev_alloc(s, (void**)&s->hidden, 4 * (size_t)g.n_embd);
+  if (G > 1) {
+    // [hidden | attn | ffn | logits | pairs | flags | seq], each part 256-byte aligned, zero-filled
+    auto up = [](size_t b) { return (b + 255) & ~size_t(255); };
+    const size_t o_hidden = 0, o_attn = o_hidden + up(4 * (size_t)g.n_embd), o_ffn = o_attn + up(4 * qd),
+                 o_logits = o_ffn + up(4 * (size_t)g.n_ff), o_pairs = o_logits + up(4 * (size_t)g.n_vocab),
+                 o_flags = o_pairs + up(16 * (size_t)kMaxPeers), o_seq = o_flags + up(4 * (size_t)kMaxPeers);
+    s->arena_bytes = o_seq + 256;
+    ok = ok && dev_alloc(s, (void**)&s->arena, s->arena_bytes);
+    if (ok) {
+      ok = cudaMemsetAsync(s->arena, 0, s->arena_bytes, c->stream) == cudaSuccess;
+      s->hidden = reinterpret_cast<float*>(s->arena + o_hidden);
+      s->attn = reinterpret_cast<float*>(s->arena + o_attn);
+      s->ffn = reinterpret_cast<float*>(s->arena + o_ffn);
+      s->logits = reinterpret_cast<float*>(s->arena + o_logits);
+      s->pair_buf = reinterpret_cast<int*>(s->arena + o_pairs);
+      s->flags_off = o_flags;
+      s->seq_off = o_seq;
+      s->peer_base[g.shard_rank] = s->arena;
+    }
+  }
+  if (G == 1) ok = ok && dev_alloc(s, (void**)&s->hidden, 4 * (size_t)g.n_embd);
   ok = ok && dev_alloc(s, (void**)&s->norm, 4 * (size_t)g.n_embd);
   ok = ok && dev_alloc(s, (void**)&s->q, 4 * qd);
   ok = ok && dev_alloc(s, (void**)&s->k, 4 * kvd);
   ok = ok && dev_alloc(s, (void**)&s->v, 4 * kvd);
-  ok = ok && dev_alloc(s, (void**)&s->attn, 4 * qd);
+  if (G == 1) ok = ok && dev_alloc(s, (void**)&s->attn, 4 * qd);
   ok = ok && dev_alloc(s, (void**)&s->gate, 4 * (size_t)g.n_ff);
   ok = ok && dev_alloc(s, (void**)&s->up, 4 * (size_t)g.n_ff);
-  ok = ok && dev_alloc(s, (void**)&s->ffn, 4 * (size_t)g.n_ff);
-  ok = ok && dev_alloc(s, (void**)&s->logits, 4 * (size_t)g.n_vocab);
+  if (G == 1) ok = ok && dev_alloc(s, (void**)&s->ffn, 4 * (size_t)g.n_ff);
+  if (G == 1) ok = ok && dev_alloc(s, (void**)&s->logits, 4 * (size_t)g.n_vocab);
   ok = ok && dev_alloc(s, (void**)&s->kcache, 2 * cache_halves);
   ok = ok && dev_alloc(s, (void**)&s->vcache, 2 * cache_halves);
   ok = ok && dev_alloc(s, (void**)&s->rope_cos, 4 * (size_t)g.n_ctx * pairs);
   ok = ok && dev_alloc(s, (void**)&s->rope_sin, 4 * (size_t)g.n_ctx * pairs);
   ok = ok && dev_alloc(s, (void**)&s->state, 4 * sizeof(int));
-  ok = ok && dev_alloc(s, (void**)&s->pair_buf, 2 * sizeof(int) * (size_t)G);
+  if (G == 1) ok = ok && dev_alloc(s, (void**)&s->pair_buf, 4 * sizeof(int));
   ok = ok && dev_alloc(s, (void**)&s->tokens_dev, sizeof(int) * (size_t)(g.n_ctx + 8));
   ok = ok && cudaMallocHost((void**)&s->host_pinned, sizeof(int) * (size_t)(g.n_ctx + 4)) == cudaSuccess;
   if (ok) {
@@ -465,6 +508,8 @@ uint32_t emelb_llama_destroy(emelb_llama* s) {
   cudaStreamSynchronize(s->c->stream);
   for (auto& g : s->graphs)
     if (g) cudaGraphExecDestroy(g);
+  for (int g = 0; g < kMaxPeers; ++g)
+    if (s->peer_base[g] && g != s->rank) cudaIpcCloseMemHandle(s->peer_base[g]);
   for (void* p : s->owned) cudaFree(p);
   if (s->host_pinned) cudaFreeHost(s->host_pinned);
   cudaGetLastError();
@@ -592,6 +637,36 @@ uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token, int32_t start
   if (!ok) return EMELB_INTERNAL_ERROR;
   c->diag.d2h_bytes += sizeof(int) * (uint64_t)n;
   std::memcpy(tokens_out, s->host_pinned, sizeof(int) * (size_t)n);
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_exchange_export(emelb_llama* s, uint8_t* handle_out, uint64_t handle_bytes) {
+  if (!s || !handle_out || handle_bytes < EMELB_EXCHANGE_HANDLE_BYTES || s->G <= 1 || !s->arena) return EMELB_INVALID_REQUEST;
+  static_assert(sizeof(cudaIpcMemHandle_t) <= EMELB_EXCHANGE_HANDLE_BYTES, "handle buffer too small");
+  cudaSetDevice(s->c->device);
+  // the arena must be zero before any peer can see it
+  if (!ctx_cuda_ok(s->c, cudaStreamSynchronize(s->c->stream))) return EMELB_INTERNAL_ERROR;
+  cudaIpcMemHandle_t h;
+  if (!ctx_cuda_ok(s->c, cudaIpcGetMemHandle(&h, s->arena))) return EMELB_INTERNAL_ERROR;
+  std::memset(handle_out, 0, EMELB_EXCHANGE_HANDLE_BYTES);
+  std::memcpy(handle_out, &h, sizeof h);
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* handles, uint64_t handles_bytes) {
+  if (!s || !handles || s->G <= 1 || s->G > kMaxPeers || handles_bytes < (uint64_t)s->G * EMELB_EXCHANGE_HANDLE_BYTES || s->peers_attached)
+    return EMELB_INVALID_REQUEST;
+  cudaSetDevice(s->c->device);
+  for (int g = 0; g < s->G; ++g) {
+    if (g == s->rank) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handles + (size_t)g * EMELB_EXCHANGE_HANDLE_BYTES, sizeof h);
+    void* p = nullptr;
+    if (!ctx_cuda_ok(s->c, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess))) return EMELB_INTERNAL_ERROR;
+    s->peer_base[g] = static_cast<char*>(p);
+  }
+  s->peers_attached = true;
+  for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;   // captured steps hold the NCCL joins
   return EMELB_OK;
 }
 

@@ -31,7 +31,12 @@ SIGNATURES = {
     "emelb_llama_prefill": [_P, C.POINTER(C.c_int32), C.c_int32, C.c_int32],
     "emelb_llama_generate": [_P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32)],
     "emelb_llama_launches_per_token": [_P, C.POINTER(C.c_int32)],
+    "emelb_llama_exchange_export": [_P, _P, C.c_uint64],
+    "emelb_llama_exchange_attach": [_P, _P, C.c_uint64],
 }
+
+
+EXCHANGE_HANDLE_BYTES = 64
 
 
 def register(lib):
@@ -128,6 +133,19 @@ class Session:
                                                        out.ctypes.data_as(C.POINTER(C.c_int32)))):
             raise eb.BackendError(f"generate failed with error mask {self.last_error}")
         return out
+
+    def exchange_export(self) -> bytes:
+        """Handle of this rank's exchange arena (sharded sessions), to be all-gathered by the caller."""
+        buf = (C.c_uint8 * EXCHANGE_HANDLE_BYTES)()
+        if not self._ret(eb.lib().emelb_llama_exchange_export(self._h, C.addressof(buf), EXCHANGE_HANDLE_BYTES)):
+            raise eb.BackendError(f"exchange_export failed with error mask {self.last_error}")
+        return bytes(buf)
+
+    def exchange_attach(self, handles) -> bool:
+        """handles: every rank's exchange_export() in rank order; switches the joins to peer stores."""
+        blob = b"".join(handles)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        return self._ret(eb.lib().emelb_llama_exchange_attach(self._h, C.addressof(buf), len(blob)))
 
     def launches_per_token(self) -> int:
         v = C.c_int32(0)

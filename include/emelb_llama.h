@@ -103,6 +103,19 @@ EMELB_API uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, in
 EMELB_API uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token,
                                         int32_t start_pos, int32_t n, int32_t* tokens_out);
 
+/* Row-sharded sessions on one node: the joins of the ranks' row intervals can run as
+ * peer stores over NVLink instead of NCCL all-gathers (one small kernel per join).
+ * Each rank exports a handle of its exchange arena (the joined vectors live in it),
+ * the caller all-gathers the G handles, and each rank attaches them (rank order,
+ * G x EMELB_EXCHANGE_HANDLE_BYTES).  Attach on every rank before the first step;
+ * without it the session keeps using the context's NCCL communicator.  No reference
+ * counterpart beyond the lane join of src/emel/kernel/matmul/actions.hpp:108-136. */
+#define EMELB_EXCHANGE_HANDLE_BYTES 64
+EMELB_API uint32_t emelb_llama_exchange_export(emelb_llama* s, uint8_t* handle_out,
+                                               uint64_t handle_bytes);
+EMELB_API uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* handles,
+                                               uint64_t handles_bytes);
+
 /* kernels launched per decode step (for launch accounting) */
 EMELB_API uint32_t emelb_llama_launches_per_token(const emelb_llama* s, int32_t* out);
 

@@ -40,6 +40,10 @@ def build(be, alloc_be, cfg_kw, rank, world, buffers):
     return sess
 
 
+def idf0_first(results):
+    return results[("full", 0)][1][0]
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     dist.init_process_group("gloo")
@@ -82,20 +86,29 @@ def main():
 
     prompt = np.random.Generator(np.random.PCG64(7)).integers(0, CFG["n_vocab"], size=9).tolist()
     results = {}
-    for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world)):
+    for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world), ("shard-peer", be_shard, rank, world)):
         for mode in (2, 0):
             be.set_attention_mode(mode)
             sess = build(be, be_full, CFG, r, g, buffers)
+            if name == "shard-peer":       # joins by peer stores instead of NCCL all-gathers
+                handles = [None] * world
+                dist.all_gather_object(handles, sess.exchange_export())
+                assert sess.exchange_attach(handles), sess.last_error
             assert sess.prefill(prompt[:-1], 0), sess.last_error
             logits = sess.decode(prompt[-1], len(prompt) - 1, want_logits=True)
             ids = sess.generate(prompt[-1], len(prompt) - 1, 12)
             ids_host = [sess.decode(prompt[-1], len(prompt) - 1)]
             results[(name, mode)] = (logits, list(ids), ids_host)
+            assert be.sync(), "a bounded device wait ran out"
+            dist.barrier()                 # nobody unmaps an arena a peer may still write to
             sess.close()
     lf, idf, hf = results[("full", 2)]
     ls, ids_, hs = results[("shard", 2)]
     assert np.array_equal(lf, ls), float(np.abs(lf - ls).max())
     assert idf == ids_ and hf == hs and hf[0] == idf[0], (idf, ids_, hf, hs)
+    lp, idp, hp = results[("shard-peer", 2)]
+    assert np.array_equal(lf, lp) and idf == idp and hf == hp, (float(np.abs(lf - lp).max()), idf, idp)
+    assert results[("shard-peer", 0)][1][0] == idf0_first(results)
     lf0, idf0, _ = results[("full", 0)]
     ls0, ids0, _ = results[("shard", 0)]
     assert float(np.abs(lf0 - ls0).max()) <= 1e-3
