@@ -735,7 +735,30 @@ gemv3_kernel(const GemvArgs p) {
       const int mseg = seg == 0 ? p.M : (seg == 1 ? p.M2 : p.M3);
       float* yseg = seg == 0 ? p.y : (seg == 1 ? p.y2 : p.y3);
       const int row = lt * ROWS_PER_STAGE + r4;
-      if (row < mseg) {
+      bool plain = true;
+      if constexpr (!ARGMAX) {
+        if (p.rope_cos) {
+          // rows 2p, 2p+1 of a head are one rotation pair and sit in neighbouring 8-lane groups of this warp
+          // (apply_rope_pairing, src/emel/text/generator/detail.hpp:2905-2936; KV rows rounded to f16, :3294-3332)
+          plain = false;
+          const float other = __shfl_sync(0xffffffffu, acc, ((r4 ^ 1) << 3));
+          if (b == 0 && row < mseg) {
+            const int hd = p.rope_head_dim, head = row / hd, d = row - head * hd;
+            float out = acc;
+            if (seg < 2 && d < p.rope_rot_dim) {
+              const int pos = *p.rope_pos, pairs = p.rope_rot_dim >> 1;
+              const float cs = p.rope_cos[(int64_t)pos * pairs + (d >> 1)], sn = p.rope_sin[(int64_t)pos * pairs + (d >> 1)];
+              out = (d & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(acc, cs)) : __fsub_rn(__fmul_rn(acc, cs), __fmul_rn(other, sn));
+            }
+            if (seg == 0) yseg[row] = out;
+            else {
+              __half* cache = seg == 1 ? p.rope_kcache : p.rope_vcache;
+              cache[(int64_t)head * p.rope_cache_head_stride + (int64_t)(*p.rope_pos) * hd + d] = __float2half_rn(out);
+            }
+          }
+        }
+      }
+      if (plain && row < mseg) {
         if constexpr (ARGMAX) {
           if (acc > best || best_i == 0x7fffffff) { best = acc; best_i = row; }
         } else if (b == 0) {

@@ -52,6 +52,16 @@ struct GemvArgs {
   int M2, M3;
   float* y2;
   float* y3;
+  // optional fused epilogue of the one-column streaming kernel for a grouped Q/K/V launch (segments 0/1/2):
+  // rotate q and k at the device-resident position (adjacent pairs only) and store k, v as f16 KV-cache rows —
+  // the RoPE / KV-store step of the layer without its own launch
+  const float* rope_cos;   // null: plain f32 outputs
+  const float* rope_sin;
+  const int* rope_pos;
+  int rope_head_dim, rope_rot_dim;
+  __half* rope_kcache;     // this layer's cache planes, [kv head][capacity][head_dim]
+  __half* rope_vcache;
+  int64_t rope_cache_head_stride;
   // optional fused prologue of the one-column streaming kernel (K-quant weights only): instead of reading
   // `act`, every CTA normalises pro_x itself, out = (x * 1/sqrt(mean(x^2) + eps)) * pro_w, and quantizes it to
   // Q8_K in shared memory — the rms_norm step of the layer without its own launch

@@ -186,7 +186,10 @@ struct Enqueue {
 
   // norm(x) -> up to three matrices of one type, or the argmax head.  When the streaming kernel takes the
   // shapes, the normalisation and quantization run inside the mat-vec launch (no rms_norm kernel).
-  void normed_matvec_group(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax = false) {
+  // rope_layer >= 0: the group is this layer's Q, K, V and the launch also applies RoPE and writes the KV rows;
+  // returns whether that happened (false: the caller runs the RoPE / KV-store kernel)
+  bool normed_matvec_group(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax = false,
+                           int rope_layer = -1) {
     bool fuse = getenv("EMELB_NO_FUSED_NORM") == nullptr && (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
                 (reinterpret_cast<uintptr_t>(nw.dev) % 16) == 0 && n >= 1 && n <= 3;
     for (int i = 0; fuse && i < n; ++i)
@@ -196,8 +199,11 @@ struct Enqueue {
       rms_norm(x, nw, family_of(w[0]->type));
       if (n == 1) matvec(*w[0], s->norm, y ? y[0] : nullptr, nullptr, argmax);
       else matvec_group(w, y, n, s->norm);
-      return;
+      return false;
     }
+    const emelb_llama_config& cfg = s->cfg;
+    const bool rope = rope_layer >= 0 && n == 3 && !cfg.rope_neox && cfg.head_dim % 2 == 0 && w[0]->M % cfg.head_dim == 0 &&
+                      getenv("EMELB_NO_FUSED_ROPE") == nullptr;
     GemvArgs a{};
     a.W = w[0]->dev;
     a.row_bytes = w[0]->row_bytes;
@@ -211,6 +217,17 @@ struct Enqueue {
     a.pro_x = x;
     a.pro_w = reinterpret_cast<const float*>(nw.dev);
     a.pro_eps = s->cfg.rms_eps;
+    if (rope) {
+      const int64_t layer_off = (int64_t)rope_layer * (cfg.n_head_kv / s->G) * s->capacity * cfg.head_dim;
+      a.rope_cos = s->rope_cos;
+      a.rope_sin = s->rope_sin;
+      a.rope_pos = s->state + 1;
+      a.rope_head_dim = cfg.head_dim;
+      a.rope_rot_dim = cfg.rope_dim < cfg.head_dim ? cfg.rope_dim : cfg.head_dim;
+      a.rope_kcache = s->kcache + layer_off;
+      a.rope_vcache = s->vcache + layer_off;
+      a.rope_cache_head_stride = s->capacity * cfg.head_dim;
+    }
     a.sched = s->c->next_sched();
     a.status = s->c->status_word();
     a.pdl = s->c->pdl & 1;
@@ -220,6 +237,7 @@ struct Enqueue {
     a.best_idx = s->c->best_idx;
     check(launch_gemv(w[0]->type, a, 1, argmax, s->c->sm_count, st, &launches));
     s->planes_src = nullptr;
+    return rope;
   }
 
   // attention of one layer; when the split-KV kernels run unsharded, their merge step also leaves the
@@ -296,17 +314,20 @@ struct Enqueue {
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
       const Layer& w = s->layers[l];
+      bool roped = false;
       {
         const Tensor* ws[3] = {&w.wq, &w.wk, &w.wv};
         float* ys[3] = {s->q, s->k, s->v};
-        normed_matvec_group(s->hidden, w.attn_norm, ws, ys, 3);
+        roped = normed_matvec_group(s->hidden, w.attn_norm, ws, ys, 3, false, l);
       }
-      const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
-      g_pdl_launch = (pm & 2) != 0;
-      check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, heads_l, kv_l, c.head_dim,
-                              c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
-                              s->vcache + layer_off, s->capacity * c.head_dim, st));
-      ++launches;
+      if (!roped) {
+        const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
+        g_pdl_launch = (pm & 2) != 0;
+        check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, heads_l, kv_l, c.head_dim,
+                                c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
+                                s->vcache + layer_off, s->capacity * c.head_dim, st));
+        ++launches;
+      }
       g_pdl_launch = (pm & 4) != 0;
       attention(l, family_of(w.wo.type));
       g_pdl_launch = (pm & 16) != 0;
