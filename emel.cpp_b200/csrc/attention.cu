@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
 #pragma unroll
   for (int r = 0; r < NREP; ++r) mx[r] = -INFINITY;
   const char* kbase = reinterpret_cast<const char*>(a.k) + (size_t)kh * a.k_nb2 + (size_t)l8 * DPL * 2;
-  constexpr int U = 4;
+  constexpr int U = 8;
   // the loop bound is uniform across the warp (the score reduction below shuffles
   // over all 32 lanes); rows past the range are clamped on load and masked on store
   for (int tb = 0; tb < n; tb += 16 * U) {

@@ -68,6 +68,7 @@ constexpr int kSmemBytes = kStages * kStageBytes + kMetaSlots * kMetaBytes + kRa
 constexpr int kTileBytes = kOperandBytes + kColMetaBytes;
 
 constexpr int kWaitSpins = 1 << 22;
+constexpr uint32_t kSuspendHintNs = 10000;
 constexpr unsigned long long kWaitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -82,10 +83,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"   // may sleep up to the hint instead of spinning
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -95,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   unsigned long long t0 = 0;
   for (int spins = 0; spins < kWaitSpins; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spins & 63) == 63) {
+    if ((spins & 15) == 15) {
       if (*abort_flag) return false;
       unsigned long long now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));

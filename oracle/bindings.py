@@ -104,6 +104,10 @@ def flash_op(q, kc, vc, dst, head_dim, heads, kv_heads, tokens, capacity, scale=
     return op
 
 
+# where the reference checkout lies when it is present (same default as the Makefile's REFERENCE)
+REFERENCE_DIR = os.environ.get("EMEL_REFERENCE_DIR", "/root/reference")
+
+
 def _load(path):
     return C.CDLL(path) if os.path.exists(path) else None
 
@@ -111,9 +115,9 @@ def _load(path):
 def build(force: bool = False) -> None:
     """Compile both checkers (the reference one only where its checkout exists)."""
     if force or not os.path.exists(os.path.join(HERE, "libemel_oracle.so")) or \
-            (os.path.isdir("/root/reference/src/emel/kernel") and
+            (os.path.isdir(os.path.join(REFERENCE_DIR, "src", "emel", "kernel")) and
              not os.path.exists(os.path.join(HERE, "_ref", "libemel_ref.so"))):
-        subprocess.run(["make", "-C", HERE] + (["-B"] if force else []), check=True,
+        subprocess.run(["make", "-C", HERE, f"REFERENCE={REFERENCE_DIR}"] + (["-B"] if force else []), check=True,
                        stdout=subprocess.DEVNULL)
 
 

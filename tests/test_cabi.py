@@ -138,7 +138,8 @@ def test_cuda_actor_adapter_compiles_against_reference_events():
     """emel::kernel::cuda::sm takes the reference's own event structs (needs the reference checkout)."""
     import subprocess
     import tempfile
-    ref = "/root/reference"
+    from oracle import bindings as ob
+    ref = ob.REFERENCE_DIR
     if not os.path.isdir(os.path.join(ref, "src", "emel", "kernel")):
         pytest.skip("reference checkout not present")
     exe = os.path.join(tempfile.gettempdir(), "emelb_cuda_sm_check")
