@@ -24,7 +24,8 @@
 //               contiguous 32 KB slab + per-column block sums and scales per
 //               128 columns x 256 K)
 //   warp  4     allocates TMEM, issues the MMAs, commits to two mbarriers
-//   warps 5-20  epilogue: four warps per TMEM lane quarter, 32 columns each
+//   warps 5-20  epilogue: four warps per TMEM lane quarter, 32 columns each; msum
+//               on the legacy mma.sync path in the accumulator-fragment layout
 //   warp  21    one thread starts the bulk copies of the next activation tile the
 //               moment an operand stage is released
 // Two operand stages are released by the MMA's completion, two TMEM accumulator
@@ -139,6 +140,24 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                : "r"(taddr)
                : "memory");
+}
+
+// 16 TMEM lanes x 16 columns in the m16n8 accumulator-fragment layout: v[0..3] = columns 0-7, v[4..7] = columns
+// 8-15; within a block thread (g, t) gets (row g, col 2t), (row g, col 2t+1), (row g+8, col 2t), (row g+8, col 2t+1)
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
+
+// D(16x8, f32) = A(16x16, f16) * B(16x8, f16) with A[row][k] = A[row][k+8] = the row's k-th min (a0/a1: rows g,
+// g+8) and B[k][col] = low parts (k < 8, bl) and 128 * high parts (k >= 8, bh) of the column's block sums
+__device__ __forceinline__ void mma_m16n8k16_f16(float (&dd)[4], uint32_t a_row0, uint32_t a_row1, uint32_t bl, uint32_t bh) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(dd[0]), "=f"(dd[1]), "=f"(dd[2]), "=f"(dd[3])
+      : "r"(a_row0), "r"(a_row1), "r"(a_row0), "r"(a_row1), "r"(bl), "r"(bh), "f"(0.0f), "f"(0.0f), "f"(0.0f), "f"(0.0f));
 }
 
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
@@ -372,51 +391,82 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    // The warp owns 32 rows (its TMEM lane quarter) x 32 columns.  Accumulators are read in the 16x256b
+    // shape, whose register layout is the m16n8 C fragment: thread (g = lane/4, t = lane%4) holds rows g and
+    // g+8, columns 2t and 2t+1 of every 8-column block.  msum = sum_j m_j * bsum_j for the same elements then
+    // comes from one legacy-path mma.sync per (16 rows x 8 columns): A = the row's 8 mins (twice), B = the
+    // column's block sums split as lo + 128*hi so that every f16 operand and every f32 sum is an exact integer.
     const int quarter = warp & 3;                       // the TMEM lanes this warp may read: 32*quarter ..
     const int cgroup = (warp - kEpilogueWarp0) >> 2;    // columns 32*cgroup .. 32*cgroup+31
-    const int r = 32 * quarter + lane;                  // row of the tile = TMEM lane
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(32 * cgroup);
+    const int g = lane >> 2, t = lane & 3;
     int it = 0;
     bool live = true;
     for (int tile = blockIdx.x; live && tile < ntiles; tile += gridDim.x) {
       const int tm = tile / nt, tn = tile - tm * nt;
-      float acc[32];
+      float acc[4][4][2];   // [row g + 8*j][8-column block][column 2t + e]
 #pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int nb = 0; nb < 4; ++nb) acc[j][nb][0] = acc[j][nb][1] = 0.0f;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it & 1;
         if (!mbar_wait(tmem_full + s, (it >> 1) & 1, abort_flag)) { live = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint8_t* mt_ = meta + (it & (kMetaSlots - 1)) * kMetaBytes;
-        const uint32_t* rmw = reinterpret_cast<const uint32_t*>(mt_ + kOffRowMeta + r * kRowMetaBytes);
-        const uint32_t dbits = rmw[0];
-        const float d = h2f((uint16_t)(dbits & 0xffffu)), dmin = h2f((uint16_t)(dbits >> 16));
-        const int mn_lo4 = (int)rmw[1], mn_hi4 = (int)rmw[2];
-        // the accumulator reads are software-pipelined: chunk c+1 is in flight while chunk c is folded in
-        uint32_t lo[2][8], hi[2][8];
-        const uint32_t tbase = lane_addr + (uint32_t)s * 256u;
-        tmem_ld8(tbase, lo[0]);
-        tmem_ld8(tbase + 128u, hi[0]);
+        const uint8_t* colmeta = mt_ + kOffColMeta + (32 * cgroup) * 16;
+        const float* dxs = reinterpret_cast<const float*>(mt_ + kOffDx) + 32 * cgroup;
+        // B fragments of the four 8-column blocks: column g of the block, sums 2t and 2t+1 (low part, high part)
+        uint32_t bfl[4], bfh[4];
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (c8 < 3) {
-            tmem_ld8(tbase + (uint32_t)(8 * (c8 + 1)), lo[(c8 + 1) & 1]);
-            tmem_ld8(tbase + 128u + (uint32_t)(8 * (c8 + 1)), hi[(c8 + 1) & 1]);
+        for (int nb = 0; nb < 4; ++nb) {
+          const uint8_t* cmeta = colmeta + (8 * nb + g) * 16;
+          const uint32_t l2 = *reinterpret_cast<const uint16_t*>(cmeta + 2 * t);
+          const uint32_t h2 = *reinterpret_cast<const uint16_t*>(cmeta + 8 + 2 * t);
+          const __half2 fl = __halves2half2(__ushort2half_rn((unsigned short)(l2 & 0xffu)), __ushort2half_rn((unsigned short)(l2 >> 8)));
+          const __half2 fh = __halves2half2(__short2half_rn((short)((int)(int8_t)(h2 & 0xffu) * 128)),
+                                            __short2half_rn((short)((int)(int8_t)(h2 >> 8) * 128)));
+          bfl[nb] = *reinterpret_cast<const uint32_t*>(&fl);
+          bfh[nb] = *reinterpret_cast<const uint32_t*>(&fh);
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          // rows g + 16*hh and g + 8 + 16*hh: scales and the A fragments (mins 2t, 2t+1 of each row)
+          float d[2], dmin[2];
+          uint32_t af[2];
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const uint32_t* rmw = reinterpret_cast<const uint32_t*>(mt_ + kOffRowMeta + (32 * quarter + 16 * hh + 8 * rr + g) * kRowMetaBytes);
+            const uint32_t dbits = rmw[0];
+            d[rr] = h2f((uint16_t)(dbits & 0xffffu));
+            dmin[rr] = h2f((uint16_t)(dbits >> 16));
+            const uint32_t mw = (t < 2 ? rmw[1] : rmw[2]) >> (16 * (t & 1));
+            const __half2 fm = __halves2half2(__ushort2half_rn((unsigned short)(mw & 0xffu)), __ushort2half_rn((unsigned short)((mw >> 8) & 0xffu)));
+            af[rr] = *reinterpret_cast<const uint32_t*>(&fm);
           }
+          const uint32_t tbase = tmem_base + ((uint32_t)(32 * quarter + 16 * hh) << 16) + (uint32_t)s * 256u + (uint32_t)(32 * cgroup);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int col = 32 * cgroup + 8 * c8 + i;
-            const uint4 cm = *reinterpret_cast<const uint4*>(mt_ + kOffColMeta + col * 16);
-            const float dx = *reinterpret_cast<const float*>(mt_ + kOffDx + col * 4);
-            const int isum = (int)lo[c8 & 1][i] + 8 * (int)hi[c8 & 1][i];
-            const int ml = __dp4a((int)cm.y, mn_hi4, __dp4a((int)cm.x, mn_lo4, 0));
-            const int mh = __dp4a((int)cm.w, mn_hi4, __dp4a((int)cm.z, mn_lo4, 0));
-            const int msum = ml + 128 * mh;                                     // |msum| <= 8*63*4064 < 2^22
-            const float msum_f = __fsub_rn(__int_as_float(msum + 0x4B400000), 12582912.0f);   // exact int -> float off the conversion pipe
-            const float d_all = __fmul_rn(dx, d), d_min = __fmul_rn(dx, dmin);
-            const float bv = __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, msum_f));
-            acc[8 * c8 + i] = __fadd_rn(acc[8 * c8 + i], bv);
+          for (int cp = 0; cp < 2; ++cp) {
+            uint32_t lo[8], hi[8];
+            tmem_ld_16x256b_x2(tbase + (uint32_t)(16 * cp), lo);
+            tmem_ld_16x256b_x2(tbase + 128u + (uint32_t)(16 * cp), hi);
+            float ms[2][4];
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) mma_m16n8k16_f16(ms[q2], af[0], af[1], bfl[2 * cp + q2], bfh[2 * cp + q2]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
+              const int nb = 2 * cp + q2;
+              const float2 dx2 = *reinterpret_cast<const float2*>(dxs + 8 * nb + 2 * t);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int rr = e >> 1, ce = e & 1;
+                const float dx = ce ? dx2.y : dx2.x;
+                const int isum = (int)lo[4 * q2 + e] + 8 * (int)hi[4 * q2 + e];
+                const float d_all = __fmul_rn(dx, d[rr]), d_min = __fmul_rn(dx, dmin[rr]);
+                const float bv = __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, ms[q2][e]));
+                acc[2 * hh + rr][nb][ce] = __fadd_rn(acc[2 * hh + rr][nb][ce], bv);
+              }
+            }
           }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -424,13 +474,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
         if (lane == 0) mbar_arrive(epi_done + s);
       }
       if (!live) break;
-      const int row = tm * BM + r;
-      if (row < p.M) {
-        float* yr = p.y + (size_t)row * p.ldy;
-        const int c0 = tn * BN + 32 * cgroup;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c0 + i < p.N) yr[c0 + i] = acc[i];
+      for (int j = 0; j < 4; ++j) {
+        const int row = tm * BM + 32 * quarter + 8 * j + g;
+        if (row < p.M) {
+          float* yr = p.y + (size_t)row * p.ldy;
+#pragma unroll
+          for (int nb = 0; nb < 4; ++nb) {
+            const int c0 = tn * BN + 32 * cgroup + 8 * nb + 2 * t;
+            if (c0 < p.N) yr[c0] = acc[j][nb][0];
+            if (c0 + 1 < p.N) yr[c0 + 1] = acc[j][nb][1];
+          }
+        }
       }
     }
   }
