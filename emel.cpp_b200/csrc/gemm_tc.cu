@@ -9,8 +9,12 @@
 //   * a 6-bit scale times a 4-bit quant does not fit int8, so sc_j = 8*hi_j + lo_j
 //     and two int8 operands are built per row, q*lo_j and q*hi_j (each <= 105);
 //     isum = D_lo + 8*D_hi, exact in int32;
-//   * one MMA has K = 32 = one sub-block, 16 MMAs (8 sub-blocks x {lo, hi}) cover
-//     a super-block of 256; then the accumulators are read back (tcgen05.ld) and
+//   * one MMA has K = 32 = one sub-block.  The activations are the M operand (128
+//     tokens = TMEM lanes) and the two weight operands sit side by side in the N
+//     operand (128 rows of q*lo, then 128 rows of q*hi), so ONE 128 x 256 x 32 MMA
+//     per sub-block produces both D_lo (columns 0-127) and D_hi (128-255) and the
+//     activation slice is fetched from shared memory once; 8 MMAs cover a
+//     super-block of 256; then the accumulators are read back (tcgen05.ld) and
 //     folded into f32 registers with the block's scales — the float chain stays on
 //     the CUDA cores because its order and roundings are part of the contract.
 //
@@ -53,10 +57,11 @@ constexpr int kStages = 2;
 
 // shared memory map (bytes)
 constexpr int kOperandBytes = BM * 256;                 // one int8 operand tile of a super-block: 32 KB
-constexpr int kChunkStride = (BM / 8) * 128;            // next 16-byte K chunk: 2048 B (leading byte offset)
+constexpr int kChunkStride = (BM / 8) * 128;            // activation tile: next 16-byte K chunk of the 128 tokens (2048 B)
+constexpr int kChunkStrideW = 2 * kChunkStride;         // weight tile: 256 operand rows (q*lo, then q*hi) per chunk (4096 B)
 constexpr int kGroupStride = 128;                       // next 8-row core matrix (stride byte offset)
-constexpr int kStageBytes = 3 * kOperandBytes;          // A_lo, A_hi, B
-constexpr int kOffAlo = 0, kOffAhi = kOperandBytes, kOffB = 2 * kOperandBytes;
+constexpr int kStageBytes = 3 * kOperandBytes;          // weights (q*lo | q*hi interleaved per K chunk: 64 KB), activations
+constexpr int kOffW = 0, kOffX = 2 * kOperandBytes;
 constexpr int kMetaSlots = 4;
 constexpr int kColMetaBytes = BN * 16 + BN * 4;         // per column: 8 pair sums as int8 low/high parts, then the scales dx
 constexpr int kRowMetaBytes = 12;                       // per row: {d, dmin} as f16 bits, mins[8]
@@ -109,18 +114,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr, uint32_t chunk_stride) {
   // K-major, no swizzle: 14-bit fields in 16-byte units; descriptor version 1 (sm_100)
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3fffu);
-  d |= (uint64_t)((kChunkStride >> 4) & 0x3fffu) << 16;   // leading byte offset: between the two 16-byte K chunks
+  d |= (uint64_t)((chunk_stride >> 4) & 0x3fffu) << 16;   // leading byte offset: between the two 16-byte K chunks
   d |= (uint64_t)((kGroupStride >> 4) & 0x3fffu) << 32;   // stride byte offset: between 8-row groups
   d |= (uint64_t)1 << 46;
   return d;
 }
 
-// instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N = 128, M = 128
-constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, M = 128 tokens, N = 256 weight-operand rows
+constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((2 * BM) >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
 
 __device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
   asm volatile(
@@ -151,13 +156,15 @@ __device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&v)
                : "memory");
 }
 
-// D(16x8, f32) = A(16x16, f16) * B(16x8, f16) with A[row][k] = A[row][k+8] = the row's k-th min (a0/a1: rows g,
-// g+8) and B[k][col] = low parts (k < 8, bl) and 128 * high parts (k >= 8, bh) of the column's block sums
-__device__ __forceinline__ void mma_m16n8k16_f16(float (&dd)[4], uint32_t a_row0, uint32_t a_row1, uint32_t bl, uint32_t bh) {
+// D(16 tokens x 8 weight rows, f32) = A(16x16, f16) * B(16x8, f16) with A[token][k] = low parts (k < 8) and
+// 128 * high parts (k >= 8) of the token's block sums (a_lo0/a_lo1, a_hi0/a_hi1: tokens g, g+8) and
+// B[k][row] = B[k+8][row] = the weight row's k-th min
+__device__ __forceinline__ void mma_m16n8k16_f16(float (&dd)[4], uint32_t a_lo0, uint32_t a_lo1, uint32_t a_hi0, uint32_t a_hi1,
+                                                 uint32_t b_mins) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=f"(dd[0]), "=f"(dd[1]), "=f"(dd[2]), "=f"(dd[3])
-      : "r"(a_row0), "r"(a_row1), "r"(a_row0), "r"(a_row1), "r"(bl), "r"(bh), "f"(0.0f), "f"(0.0f), "f"(0.0f), "f"(0.0f));
+      : "r"(a_lo0), "r"(a_lo1), "r"(a_hi0), "r"(a_hi1), "r"(b_mins), "r"(b_mins), "f"(0.0f), "f"(0.0f), "f"(0.0f), "f"(0.0f));
 }
 
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
@@ -306,8 +313,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
           rmw[1] = mn_lo4;
           rmw[2] = mn_hi4;
         }
-        uint8_t* alo = st + kOffAlo + core_off;
-        uint8_t* ahi = st + kOffAhi + core_off;
+        uint8_t* alo = st + kOffW + core_off;                  // operand rows 0-127: q*lo
+        uint8_t* ahi = alo + kChunkStride;                     // operand rows 128-255: q*hi (16 core-matrix groups further)
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const uint4 v0 = blk[1 + 2 * g], v1 = blk[2 + 2 * g];
@@ -319,14 +326,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
 #pragma unroll
           for (int i = 0; i < 8; ++i) { lo[i] = q[i] & 0x0f0f0f0fu; hi[i] = (q[i] >> 4) & 0x0f0f0f0fu; }
           // sub-block 2g (low nibbles): chunks 4g, 4g+1; sub-block 2g+1 (high nibbles): chunks 4g+2, 4g+3
-          *reinterpret_cast<uint4*>(alo + (4 * g + 0) * kChunkStride) = make_uint4(lo[0] * la, lo[1] * la, lo[2] * la, lo[3] * la);
-          *reinterpret_cast<uint4*>(alo + (4 * g + 1) * kChunkStride) = make_uint4(lo[4] * la, lo[5] * la, lo[6] * la, lo[7] * la);
-          *reinterpret_cast<uint4*>(alo + (4 * g + 2) * kChunkStride) = make_uint4(hi[0] * lb, hi[1] * lb, hi[2] * lb, hi[3] * lb);
-          *reinterpret_cast<uint4*>(alo + (4 * g + 3) * kChunkStride) = make_uint4(hi[4] * lb, hi[5] * lb, hi[6] * lb, hi[7] * lb);
-          *reinterpret_cast<uint4*>(ahi + (4 * g + 0) * kChunkStride) = make_uint4(lo[0] * ha, lo[1] * ha, lo[2] * ha, lo[3] * ha);
-          *reinterpret_cast<uint4*>(ahi + (4 * g + 1) * kChunkStride) = make_uint4(lo[4] * ha, lo[5] * ha, lo[6] * ha, lo[7] * ha);
-          *reinterpret_cast<uint4*>(ahi + (4 * g + 2) * kChunkStride) = make_uint4(hi[0] * hb, hi[1] * hb, hi[2] * hb, hi[3] * hb);
-          *reinterpret_cast<uint4*>(ahi + (4 * g + 3) * kChunkStride) = make_uint4(hi[4] * hb, hi[5] * hb, hi[6] * hb, hi[7] * hb);
+          *reinterpret_cast<uint4*>(alo + (4 * g + 0) * kChunkStrideW) = make_uint4(lo[0] * la, lo[1] * la, lo[2] * la, lo[3] * la);
+          *reinterpret_cast<uint4*>(alo + (4 * g + 1) * kChunkStrideW) = make_uint4(lo[4] * la, lo[5] * la, lo[6] * la, lo[7] * la);
+          *reinterpret_cast<uint4*>(alo + (4 * g + 2) * kChunkStrideW) = make_uint4(hi[0] * lb, hi[1] * lb, hi[2] * lb, hi[3] * lb);
+          *reinterpret_cast<uint4*>(alo + (4 * g + 3) * kChunkStrideW) = make_uint4(hi[4] * lb, hi[5] * lb, hi[6] * lb, hi[7] * lb);
+          *reinterpret_cast<uint4*>(ahi + (4 * g + 0) * kChunkStrideW) = make_uint4(lo[0] * ha, lo[1] * ha, lo[2] * ha, lo[3] * ha);
+          *reinterpret_cast<uint4*>(ahi + (4 * g + 1) * kChunkStrideW) = make_uint4(lo[4] * ha, lo[5] * ha, lo[6] * ha, lo[7] * ha);
+          *reinterpret_cast<uint4*>(ahi + (4 * g + 2) * kChunkStrideW) = make_uint4(hi[0] * hb, hi[1] * hb, hi[2] * hb, hi[3] * hb);
+          *reinterpret_cast<uint4*>(ahi + (4 * g + 3) * kChunkStrideW) = make_uint4(hi[4] * hb, hi[5] * hb, hi[6] * hb, hi[7] * hb);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core's reads
         mbar_arrive(full + s);
@@ -348,14 +355,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
           if (!mbar_wait(epi_done + s, ((it >> 1) & 1) ^ 1, abort_flag)) { live = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           uint8_t* st = smem + s * kStageBytes;
-          const uint32_t a_lo = smem_u32(st + kOffAlo), a_hi = smem_u32(st + kOffAhi), b = smem_u32(st + kOffB);
-          const uint32_t d_lo = tmem_base + (uint32_t)s * 256u, d_hi = d_lo + 128u;
+          const uint32_t xop = smem_u32(st + kOffX), wop = smem_u32(st + kOffW);
+          const uint32_t d_acc = tmem_base + (uint32_t)s * 256u;   // columns 0-127: D_lo, 128-255: D_hi
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint64_t db = operand_desc(b + 2 * j * kChunkStride);
-            mma_i8(d_lo, operand_desc(a_lo + 2 * j * kChunkStride), db, j > 0 ? 1u : 0u);
-            mma_i8(d_hi, operand_desc(a_hi + 2 * j * kChunkStride), db, j > 0 ? 1u : 0u);
-          }
+          for (int j = 0; j < 8; ++j)
+            mma_i8(d_acc, operand_desc(xop + 2 * j * kChunkStride, kChunkStride), operand_desc(wop + 2 * j * kChunkStrideW, kChunkStrideW),
+                   j > 0 ? 1u : 0u);
           mma_commit(mma_done + s);
           mma_commit(tmem_full + s);
           last_commit = it;
@@ -384,26 +389,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
           mbar_arrive_expect_tx(full + s, kTileBytes);
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            bulk_g2s(st + kOffB + q * (kOperandBytes / 4), tile_src + q * (kOperandBytes / 4), kOperandBytes / 4, full + s);
+            bulk_g2s(st + kOffX + q * (kOperandBytes / 4), tile_src + q * (kOperandBytes / 4), kOperandBytes / 4, full + s);
           bulk_g2s(mt_ + kOffColMeta, tile_src + kOperandBytes, kColMetaBytes, full + s);
         }
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    // The warp owns 32 rows (its TMEM lane quarter) x 32 columns.  Accumulators are read in the 16x256b
-    // shape, whose register layout is the m16n8 C fragment: thread (g = lane/4, t = lane%4) holds rows g and
-    // g+8, columns 2t and 2t+1 of every 8-column block.  msum = sum_j m_j * bsum_j for the same elements then
-    // comes from one legacy-path mma.sync per (16 rows x 8 columns): A = the row's 8 mins (twice), B = the
-    // column's block sums split as lo + 128*hi so that every f16 operand and every f32 sum is an exact integer.
-    const int quarter = warp & 3;                       // the TMEM lanes this warp may read: 32*quarter ..
-    const int cgroup = (warp - kEpilogueWarp0) >> 2;    // columns 32*cgroup .. 32*cgroup+31
+    // TMEM lanes are tokens, TMEM columns weight rows.  The warp owns 32 tokens (its lane quarter) x 32 weight
+    // rows.  Accumulators are read in the 16x256b shape, whose register layout is the m16n8 C fragment: thread
+    // (g = lane/4, t = lane%4) holds tokens g and g+8, weight rows 2t and 2t+1 of every 8-row block.
+    // msum = sum_j bsum_j * m_j for the same elements comes from one legacy-path mma.sync per (16 tokens x 8
+    // weight rows): A = the token's block sums split as lo + 128*hi, B = the weight row's 8 mins (twice), so
+    // every f16 operand and every f32 partial sum is an exact integer.
+    const int quarter = warp & 3;                       // the TMEM lanes this warp may read: tokens 32*quarter ..
+    const int cgroup = (warp - kEpilogueWarp0) >> 2;    // weight rows 32*cgroup .. 32*cgroup+31
     const int g = lane >> 2, t = lane & 3;
     int it = 0;
     bool live = true;
     for (int tile = blockIdx.x; live && tile < ntiles; tile += gridDim.x) {
       const int tm = tile / nt, tn = tile - tm * nt;
-      float acc[4][4][2];   // [row g + 8*j][8-column block][column 2t + e]
+      float acc[4][4][2];   // [token g + 8*j][8-row block][weight row 2t + e]
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -413,35 +419,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
         if (!mbar_wait(tmem_full + s, (it >> 1) & 1, abort_flag)) { live = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint8_t* mt_ = meta + (it & (kMetaSlots - 1)) * kMetaBytes;
-        const uint8_t* colmeta = mt_ + kOffColMeta + (32 * cgroup) * 16;
-        const float* dxs = reinterpret_cast<const float*>(mt_ + kOffDx) + 32 * cgroup;
-        // B fragments of the four 8-column blocks: column g of the block, sums 2t and 2t+1 (low part, high part)
-        uint32_t bfl[4], bfh[4];
+        const uint8_t* tokmeta = mt_ + kOffColMeta + (32 * quarter) * 16;                       // per token: 8 lo, 8 hi parts
+        const float* dxs = reinterpret_cast<const float*>(mt_ + kOffDx) + 32 * quarter;          // per token: dx
+        const uint8_t* wmeta = mt_ + kOffRowMeta + (32 * cgroup) * kRowMetaBytes;                // per weight row: {d, dmin}, mins
+        // B fragments of the four 8-row blocks: weight row g of the block, mins 2t and 2t+1
+        uint32_t bfm[4];
 #pragma unroll
         for (int nb = 0; nb < 4; ++nb) {
-          const uint8_t* cmeta = colmeta + (8 * nb + g) * 16;
-          const uint32_t l2 = *reinterpret_cast<const uint16_t*>(cmeta + 2 * t);
-          const uint32_t h2 = *reinterpret_cast<const uint16_t*>(cmeta + 8 + 2 * t);
-          const __half2 fl = __halves2half2(__ushort2half_rn((unsigned short)(l2 & 0xffu)), __ushort2half_rn((unsigned short)(l2 >> 8)));
-          const __half2 fh = __halves2half2(__short2half_rn((short)((int)(int8_t)(h2 & 0xffu) * 128)),
-                                            __short2half_rn((short)((int)(int8_t)(h2 >> 8) * 128)));
-          bfl[nb] = *reinterpret_cast<const uint32_t*>(&fl);
-          bfh[nb] = *reinterpret_cast<const uint32_t*>(&fh);
+          const uint32_t m2 = *reinterpret_cast<const uint16_t*>(wmeta + (8 * nb + g) * kRowMetaBytes + 4 + 2 * t);
+          const __half2 fm = __halves2half2(__ushort2half_rn((unsigned short)(m2 & 0xffu)), __ushort2half_rn((unsigned short)(m2 >> 8)));
+          bfm[nb] = *reinterpret_cast<const uint32_t*>(&fm);
         }
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          // rows g + 16*hh and g + 8 + 16*hh: scales and the A fragments (mins 2t, 2t+1 of each row)
-          float d[2], dmin[2];
-          uint32_t af[2];
+          // tokens g + 16*hh and g + 8 + 16*hh: scale and the A fragments (block sums 2t, 2t+1: low parts, high parts)
+          float dx[2];
+          uint32_t afl[2], afh[2];
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
-            const uint32_t* rmw = reinterpret_cast<const uint32_t*>(mt_ + kOffRowMeta + (32 * quarter + 16 * hh + 8 * rr + g) * kRowMetaBytes);
-            const uint32_t dbits = rmw[0];
-            d[rr] = h2f((uint16_t)(dbits & 0xffffu));
-            dmin[rr] = h2f((uint16_t)(dbits >> 16));
-            const uint32_t mw = (t < 2 ? rmw[1] : rmw[2]) >> (16 * (t & 1));
-            const __half2 fm = __halves2half2(__ushort2half_rn((unsigned short)(mw & 0xffu)), __ushort2half_rn((unsigned short)((mw >> 8) & 0xffu)));
-            af[rr] = *reinterpret_cast<const uint32_t*>(&fm);
+            const int tok = 16 * hh + 8 * rr + g;
+            dx[rr] = dxs[tok];
+            const uint32_t l2 = *reinterpret_cast<const uint16_t*>(tokmeta + tok * 16 + 2 * t);
+            const uint32_t h2 = *reinterpret_cast<const uint16_t*>(tokmeta + tok * 16 + 8 + 2 * t);
+            const __half2 fl = __halves2half2(__ushort2half_rn((unsigned short)(l2 & 0xffu)), __ushort2half_rn((unsigned short)(l2 >> 8)));
+            const __half2 fh = __halves2half2(__short2half_rn((short)((int)(int8_t)(h2 & 0xffu) * 128)),
+                                              __short2half_rn((short)((int)(int8_t)(h2 >> 8) * 128)));
+            afl[rr] = *reinterpret_cast<const uint32_t*>(&fl);
+            afh[rr] = *reinterpret_cast<const uint32_t*>(&fh);
           }
           const uint32_t tbase = tmem_base + ((uint32_t)(32 * quarter + 16 * hh) << 16) + (uint32_t)s * 256u + (uint32_t)(32 * cgroup);
 #pragma unroll
@@ -451,18 +455,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
             tmem_ld_16x256b_x2(tbase + 128u + (uint32_t)(16 * cp), hi);
             float ms[2][4];
 #pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) mma_m16n8k16_f16(ms[q2], af[0], af[1], bfl[2 * cp + q2], bfh[2 * cp + q2]);
+            for (int q2 = 0; q2 < 2; ++q2) mma_m16n8k16_f16(ms[q2], afl[0], afl[1], afh[0], afh[1], bfm[2 * cp + q2]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
             for (int q2 = 0; q2 < 2; ++q2) {
               const int nb = 2 * cp + q2;
-              const float2 dx2 = *reinterpret_cast<const float2*>(dxs + 8 * nb + 2 * t);
+              const uint8_t* wm = wmeta + (8 * nb + 2 * t) * kRowMetaBytes;
+              const uint32_t db0 = *reinterpret_cast<const uint32_t*>(wm), db1 = *reinterpret_cast<const uint32_t*>(wm + kRowMetaBytes);
+              const float dw[2] = {h2f((uint16_t)(db0 & 0xffffu)), h2f((uint16_t)(db1 & 0xffffu))};
+              const float dminw[2] = {h2f((uint16_t)(db0 >> 16)), h2f((uint16_t)(db1 >> 16))};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int rr = e >> 1, ce = e & 1;
-                const float dx = ce ? dx2.y : dx2.x;
                 const int isum = (int)lo[4 * q2 + e] + 8 * (int)hi[4 * q2 + e];
-                const float d_all = __fmul_rn(dx, d[rr]), d_min = __fmul_rn(dx, dmin[rr]);
+                const float d_all = __fmul_rn(dx[rr], dw[ce]), d_min = __fmul_rn(dx[rr], dminw[ce]);
                 const float bv = __fmaf_rn(d_all, (float)isum, -__fmul_rn(d_min, ms[q2][e]));
                 acc[2 * hh + rr][nb][ce] = __fadd_rn(acc[2 * hh + rr][nb][ce], bv);
               }
@@ -475,18 +481,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
       }
       if (!live) break;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int row = tm * BM + 32 * quarter + 8 * j + g;
-        if (row < p.M) {
-          float* yr = p.y + (size_t)row * p.ldy;
+      for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
-          for (int nb = 0; nb < 4; ++nb) {
-            const int c0 = tn * BN + 32 * cgroup + 8 * nb + 2 * t;
-            if (c0 < p.N) yr[c0] = acc[j][nb][0];
-            if (c0 + 1 < p.N) yr[c0 + 1] = acc[j][nb][1];
+        for (int ce = 0; ce < 2; ++ce) {
+          const int row = tm * BM + 32 * cgroup + 8 * nb + 2 * t + ce;      // weight row
+          if (row < p.M) {
+            float* yr = p.y + (size_t)row * p.ldy + tn * BN + 32 * quarter + g;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (tn * BN + 32 * quarter + 8 * j + g < p.N) yr[8 * j] = acc[j][nb][ce];
           }
         }
-      }
     }
   }
 
