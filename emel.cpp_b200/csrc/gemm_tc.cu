@@ -391,6 +391,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_q4k_tc_kernel(const GemmArgs
           for (int q = 0; q < 4; ++q)
             bulk_g2s(st + kOffX + q * (kOperandBytes / 4), tile_src + q * (kOperandBytes / 4), kOperandBytes / 4, full + s);
           bulk_g2s(mt_ + kOffColMeta, tile_src + kOperandBytes, kColMetaBytes, full + s);
+          // the tile this stage gets next (two super-blocks ahead, same tile row while kb + 2 < nkb) towards L2:
+          // the copy above is issued only when the stage frees up, so its latency is on the critical path
+          if (kb + 2 < nkb)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(tile_src + 2 * (size_t)kTileBytes), "r"(kTileBytes) : "memory");
         }
       }
     }
