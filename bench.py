@@ -550,6 +550,7 @@ def run_decode(args):
         handles = [None] * world
         dist.all_gather_object(handles, sess.exchange_export())
         assert sess.exchange_attach(handles), sess.last_error
+        dist.barrier()          # every rank has mapped its peers before anybody's first join
         peer_joins = True
 
     # weights N(0, 0.02) encoded on the device; norm weights 1.0 (each rank builds its own replica)
@@ -679,7 +680,9 @@ def run_decode(args):
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline_decode(sh, out_type, budget_s=args.cpu_budget)
         print(json.dumps(line), flush=True)
-    barrier(world)              # no rank frees an exchange arena while a peer may still store into it
+    barrier(world)              # no rank unmaps an exchange arena while a peer may still store into it
+    sess.exchange_detach()
+    barrier(world)              # ... nor frees one that a peer still maps
     sess.close()
     be.close()
     if world > 1:

@@ -39,8 +39,8 @@ cudaError_t comm_all_gather_bytes(emelb_ctx* c, void* buf, size_t bytes_per_rank
 // the kernel returns.
 namespace {
 
-constexpr int kPeerWaitSpins = 1 << 24;
-constexpr unsigned long long kPeerWaitNs = 2000000000ull;  // 2 s
+constexpr int kPeerWaitSpins = 1 << 30;   // the wall-clock limit below is the effective bound
+constexpr unsigned long long kPeerWaitNs = 10000000000ull;  // 10 s: covers host-side skew between the ranks' launches
 
 __global__ void __launch_bounds__(1024) peer_gather_kernel(PeerGatherArgs a) {
   const int peers = a.world - 1;

@@ -691,6 +691,22 @@ uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* handles, uin
   return EMELB_OK;
 }
 
+uint32_t emelb_llama_exchange_detach(emelb_llama* s) {
+  if (!s) return EMELB_INVALID_REQUEST;
+  cudaSetDevice(s->c->device);
+  if (!ctx_cuda_ok(s->c, cudaStreamSynchronize(s->c->stream))) return EMELB_INTERNAL_ERROR;
+  for (int g = 0; g < kMaxPeers; ++g)
+    if (s->peer_base[g] && g != s->rank) {
+      cudaIpcCloseMemHandle(s->peer_base[g]);
+      s->peer_base[g] = nullptr;
+    }
+  if (s->peers_attached)
+    for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;   // captured steps hold the peer pointers
+  s->peers_attached = false;
+  cudaGetLastError();
+  return EMELB_OK;
+}
+
 uint32_t emelb_llama_launches_per_token(const emelb_llama* s, int32_t* out) {
   if (!s || !out) return EMELB_INVALID_REQUEST;
   *out = s->launches_per_token;

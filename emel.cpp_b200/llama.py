@@ -33,6 +33,7 @@ SIGNATURES = {
     "emelb_llama_launches_per_token": [_P, C.POINTER(C.c_int32)],
     "emelb_llama_exchange_export": [_P, _P, C.c_uint64],
     "emelb_llama_exchange_attach": [_P, _P, C.c_uint64],
+    "emelb_llama_exchange_detach": [_P],
 }
 
 
@@ -146,6 +147,10 @@ class Session:
         blob = b"".join(handles)
         buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         return self._ret(eb.lib().emelb_llama_exchange_attach(self._h, C.addressof(buf), len(blob)))
+
+    def exchange_detach(self) -> bool:
+        """Unmap the peers' arenas; call on every rank, synchronise the ranks, then close()."""
+        return self._ret(eb.lib().emelb_llama_exchange_detach(self._h))
 
     def launches_per_token(self) -> int:
         v = C.c_int32(0)

@@ -107,7 +107,9 @@ EMELB_API uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token,
  * peer stores over NVLink instead of NCCL all-gathers (one small kernel per join).
  * Each rank exports a handle of its exchange arena (the joined vectors live in it),
  * the caller all-gathers the G handles, and each rank attaches them (rank order,
- * G x EMELB_EXCHANGE_HANDLE_BYTES).  Attach on every rank before the first step;
+ * G x EMELB_EXCHANGE_HANDLE_BYTES).  Attach on every rank and synchronise the ranks
+ * before the first step (a join waits at most 10 s for a peer, then the step fails with
+ * EMELB_INTERNAL_ERROR at the next emelb_sync);
  * without it the session keeps using the context's NCCL communicator.  No reference
  * counterpart beyond the lane join of src/emel/kernel/matmul/actions.hpp:108-136. */
 #define EMELB_EXCHANGE_HANDLE_BYTES 64
@@ -115,6 +117,10 @@ EMELB_API uint32_t emelb_llama_exchange_export(emelb_llama* s, uint8_t* handle_o
                                                uint64_t handle_bytes);
 EMELB_API uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* handles,
                                                uint64_t handles_bytes);
+/* unmaps the peers' arenas (the session falls back to NCCL joins).  Tear-down order
+ * across ranks: every rank detaches, the caller synchronises the ranks, then the
+ * sessions are destroyed — no arena is freed while a peer still maps it. */
+EMELB_API uint32_t emelb_llama_exchange_detach(emelb_llama* s);
 
 /* kernels launched per decode step (for launch accounting) */
 EMELB_API uint32_t emelb_llama_launches_per_token(const emelb_llama* s, int32_t* out);

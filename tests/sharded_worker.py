@@ -94,6 +94,7 @@ def main():
                 handles = [None] * world
                 dist.all_gather_object(handles, sess.exchange_export())
                 assert sess.exchange_attach(handles), sess.last_error
+                dist.barrier()             # every rank has mapped its peers before anybody's first join
             assert sess.prefill(prompt[:-1], 0), sess.last_error
             logits = sess.decode(prompt[-1], len(prompt) - 1, want_logits=True)
             ids = sess.generate(prompt[-1], len(prompt) - 1, 12)
@@ -101,6 +102,8 @@ def main():
             results[(name, mode)] = (logits, list(ids), ids_host)
             assert be.sync(), "a bounded device wait ran out"
             dist.barrier()                 # nobody unmaps an arena a peer may still write to
+            assert sess.exchange_detach()
+            dist.barrier()                 # nobody frees an arena a peer still maps
             sess.close()
     lf, idf, hf = results[("full", 2)]
     ls, ids_, hs = results[("shard", 2)]
