@@ -529,6 +529,10 @@ static uint32_t run_mul_mat(emelb_ctx* c, const emelb_op* op, bool argmax, bool 
   a.residual = nullptr;
   a.tc_ws = c->tc_ws;
   a.tc_ws_bytes = c->tc_ws_bytes;
+  // streaming mat-vec launches carry the programmatic-serialization attribute: the kernel starts its weight
+  // copies while the previous kernel of the stream drains and waits (griddepcontrol.wait) before it reads
+  // activations or writes results, so stream order is kept
+  a.pdl = c->pdl & 1;
   a.sched = c->next_sched();
   a.status = c->status_word();
   a.part_val = c->part_val;
