@@ -553,16 +553,19 @@ __host__ __device__ constexpr int warp_bytes3() {
   return STAGES * ROWS_PER_STAGE * Geo2<T>::CB + ((STAGES * 8 + STAGES * 8 + 15) / 16) * 16;  // ring + barriers + (task, chunk)
 }
 
-template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX>
+// NCOLS > 1: the same rows against NCOLS activation columns (plain outputs only): the weights of a stage
+// are decoded once per column from shared memory, every column keeps its own f32 chain
+template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX, int NCOLS = 1>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 gemv3_kernel(const GemvArgs p) {
+  static_assert(NCOLS == 1 || !ARGMAX, "the fused argmax is a one-column path");
   constexpr int CB = Geo2<T>::CB;
   constexpr bool KQ = is_k_type(T);
   constexpr int SPAN = CB / 8;
   extern __shared__ __align__(128) uint8_t smem3[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int act_bytes = act_smem_bytes(KQ, p.K);
-  uint8_t* ring = smem3 + act_bytes + (size_t)warp * warp_bytes3<T, STAGES>();
+  uint8_t* ring = smem3 + NCOLS * act_bytes + (size_t)warp * warp_bytes3<T, STAGES>();
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + STAGES * ROWS_PER_STAGE * CB);
   int* meta = reinterpret_cast<int*>(bars + STAGES);  // 2 ints per stage: task, chunk
 
@@ -619,13 +622,15 @@ gemv3_kernel(const GemvArgs p) {
 
   // this column's quantized activations in shared memory for the whole CTA: copied from the planes, or
   // (fused prologue) normalised and quantized here from the f32 vector
-  ActSmem x;
-  {
-    int8_t* sq = reinterpret_cast<int8_t*>(smem3);
-    int16_t* sb = reinterpret_cast<int16_t*>(smem3 + ((p.K + 15) / 16) * 16);
-    float* sd = reinterpret_cast<float*>(smem3 + ((p.K + 15) / 16) * 16 + (KQ ? ((p.K / 8 + 15) / 16) * 16 : 0));
+  ActSmem x;   // column 0; column j lies j * act_bytes further
+#pragma unroll 1
+  for (int col = 0; col < NCOLS; ++col) {
+    uint8_t* abase = smem3 + (size_t)col * act_bytes;
+    int8_t* sq = reinterpret_cast<int8_t*>(abase);
+    int16_t* sb = reinterpret_cast<int16_t*>(abase + ((p.K + 15) / 16) * 16);
+    float* sd = reinterpret_cast<float*>(abase + ((p.K + 15) / 16) * 16 + (KQ ? ((p.K / 8 + 15) / 16) * 16 : 0));
     bool fused = false;
-    if constexpr (KQ) {
+    if constexpr (KQ && NCOLS == 1) {
       if (p.pro_x) {
         fused = true;
         // rms_norm (src/emel/text/generator/detail.hpp:2735-2756): f64 sum of the f32 squares
@@ -663,24 +668,29 @@ gemv3_kernel(const GemvArgs p) {
       }
     }
     if (!fused) {
-      const int4* gq = reinterpret_cast<const int4*>(p.act.qs + (int64_t)p.col0 * p.act.col_stride_qs);
+      const int64_t gcol = p.col0 + col;
+      const int4* gq = reinterpret_cast<const int4*>(p.act.qs + gcol * p.act.col_stride_qs);
       for (int i = threadIdx.x; i < p.K / 16; i += WARPS * 32) reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = __ldg(gq + i);
       if constexpr (KQ) {
-        const int4* gb = reinterpret_cast<const int4*>(p.act.bsums + (int64_t)p.col0 * p.act.col_stride_bs);
+        const int4* gb = reinterpret_cast<const int4*>(p.act.bsums + gcol * p.act.col_stride_bs);
         for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = __ldg(gb + i);
       }
-      const float* gd = p.act.d + (int64_t)p.col0 * p.act.col_stride_d;
+      const float* gd = p.act.d + gcol * p.act.col_stride_d;
       const int nd = KQ ? p.K / QK_K : p.K / 32;
       for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = __ldg(gd + i);
     }
-    x.qs = sq;
-    x.bs = sb;
-    x.d = sd;
+    if (col == 0) {
+      x.qs = sq;
+      x.bs = sb;
+      x.d = sd;
+    }
   }
   __syncthreads();
 
   const int r4 = lane >> 3, b = lane & 7;
-  float acc = 0.0f;
+  float accs[NCOLS];
+#pragma unroll
+  for (int j = 0; j < NCOLS; ++j) accs[j] = 0.0f;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   uint32_t phase = 0;
@@ -705,16 +715,26 @@ gemv3_kernel(const GemvArgs p) {
       if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
       phase ^= 1u << slot_c;
     }
-    if (c == 0) acc = 0.0f;
+    if (c == 0) {
+#pragma unroll
+      for (int j = 0; j < NCOLS; ++j) accs[j] = 0.0f;
+    }
     const uint8_t* st = ring + (size_t)slot_c * ROWS_PER_STAGE * CB + r4 * CB + b * SPAN;
     const int e0 = c * CHUNK + 256 * b;
+#pragma unroll
+    for (int j = 0; j < NCOLS; ++j) {
+      ActSmem xj;
+      xj.qs = x.qs + (size_t)j * act_bytes;
+      xj.bs = reinterpret_cast<const int16_t*>(reinterpret_cast<const uint8_t*>(x.bs) + (size_t)j * act_bytes);
+      xj.d = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(x.d) + (size_t)j * act_bytes);
+      float acc = accs[j];
     if constexpr (T == T_Q4_K) {
-      const float bv = q4_k_block_value_s(st, x, e0);
+      const float bv = q4_k_block_value_s(st, xj, e0);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, bv, (lane & ~7) + i));
     } else {
       Act256 xr;
-      fill_act_from_smem<T>(xr, x, e0);
+      fill_act_from_smem<T>(xr, xj, e0);
       if constexpr (T == T_Q6_K) {
         const float bv = q6_k_block_value(st, xr);
 #pragma unroll
@@ -729,6 +749,9 @@ gemv3_kernel(const GemvArgs p) {
           for (int i = 0; i < 8; ++i) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, bv[i], (lane & ~7) + g));
       }
     }
+      accs[j] = acc;
+    }
+    const float acc = accs[0];
     if (c == nchunks - 1) {
       const int seg = task < nt0 ? 0 : (task < nt0 + nt1 ? 1 : 2);
       const int lt = task - (seg == 0 ? 0 : (seg == 1 ? nt0 : nt0 + nt1));
@@ -736,7 +759,7 @@ gemv3_kernel(const GemvArgs p) {
       float* yseg = seg == 0 ? p.y : (seg == 1 ? p.y2 : p.y3);
       const int row = lt * ROWS_PER_STAGE + r4;
       bool plain = true;
-      if constexpr (!ARGMAX) {
+      if constexpr (!ARGMAX && NCOLS == 1) {
         if (p.rope_cos) {
           // rows 2p, 2p+1 of a head are one rotation pair and sit in neighbouring 8-lane groups of this warp
           // (apply_rope_pairing, src/emel/text/generator/detail.hpp:2905-2936; KV rows rounded to f16, :3294-3332)
@@ -762,8 +785,11 @@ gemv3_kernel(const GemvArgs p) {
         if constexpr (ARGMAX) {
           if (acc > best || best_i == 0x7fffffff) { best = acc; best_i = row; }
         } else if (b == 0) {
-          const size_t o = (size_t)row * p.ldy + p.col0;
-          yseg[o] = (p.residual && seg == 0) ? __fadd_rn(p.residual[o], acc) : acc;
+#pragma unroll
+          for (int j = 0; j < NCOLS; ++j) {
+            const size_t o = (size_t)row * p.ldy + p.col0 + j;
+            yseg[o] = (p.residual && seg == 0) ? __fadd_rn(p.residual[o], accs[j]) : accs[j];
+          }
         }
       }
     }
@@ -837,10 +863,10 @@ cudaError_t launch2(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_
 }
 
 // third generation: one column (or the argmax head), activations in shared memory
-template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX>
+template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX, int NCOLS = 1>
 cudaError_t launch3(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
-  auto kern = gemv3_kernel<T, STAGES, WARPS, MINB, ARGMAX>;
-  const size_t smem = (size_t)act_smem_bytes(is_k_type(T), a.K) + (size_t)WARPS * warp_bytes3<T, STAGES>();
+  auto kern = gemv3_kernel<T, STAGES, WARPS, MINB, ARGMAX, NCOLS>;
+  const size_t smem = (size_t)NCOLS * act_smem_bytes(is_k_type(T), a.K) + (size_t)WARPS * warp_bytes3<T, STAGES>();
   static size_t configured_smem[32] = {};
   static int per_sm_cache[32] = {};
   int dev = 0;
@@ -919,7 +945,13 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
     GemvArgs b = a;
     b.col0 = a.col0 + done;
     const int left = ncols - done;
-    if (left >= 8) { e = launch2<T, 8, 1, false>(b, sm_count, st, grid_out); done += 8; }
+    // several columns: the third-generation kernel while their activations fit beside the rings
+    const bool multi3 = gen3_config() >= 0 && !b.pro_x && !b.rope_cos;
+    const size_t act1 = (size_t)act_smem_bytes(is_k_type(T), a.K);
+    if (left >= 8 && multi3 && 8 * act1 <= 64 * 1024) { e = launch3<T, 1, 8, 2, false, 8>(b, sm_count, st, grid_out); done += 8; }
+    else if (left >= 4 && multi3 && 4 * act1 <= 64 * 1024) { e = launch3<T, 1, 8, 2, false, 4>(b, sm_count, st, grid_out); done += 4; }
+    else if (left >= 2 && multi3 && 2 * act1 <= 64 * 1024) { e = launch3<T, 1, 8, 2, false, 2>(b, sm_count, st, grid_out); done += 2; }
+    else if (left >= 8) { e = launch2<T, 8, 1, false>(b, sm_count, st, grid_out); done += 8; }
     else if (left >= 4) { e = launch2<T, 4, 1, false>(b, sm_count, st, grid_out); done += 4; }
     else if (left >= 2) { e = launch2<T, 2, 1, false>(b, sm_count, st, grid_out); done += 2; }
     else if (gen3_config() >= 0) {
