@@ -99,8 +99,8 @@ _SIGNATURES = {
 
 
 def declared_symbols():
-    from . import llama as _llama
-    return sorted(list(_SIGNATURES) + list(_llama.SIGNATURES))
+    from . import gguf as _gguf, llama as _llama
+    return sorted(list(_SIGNATURES) + list(_llama.SIGNATURES) + list(_gguf.SIGNATURES))
 
 
 def lib():
@@ -115,8 +115,9 @@ def lib():
             fn = getattr(_lib, name)
             fn.restype = C.c_uint32
             fn.argtypes = args
-        from . import llama as _llama
+        from . import gguf as _gguf, llama as _llama
         _llama.register(_lib)
+        _gguf.register(_lib)
     return _lib
 
 

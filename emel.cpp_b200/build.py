@@ -26,6 +26,7 @@ SOURCES = {
     "llama.cu": [],
     "comm.cu": [],
     "noalloc.cu": [],
+    "gguf.cu": [],
     "api.cu": [],
 }
 
@@ -54,6 +55,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "emelb.h"))
     headers.append(os.path.join(os.path.dirname(HERE), "include", "emelb_llama.h"))
+    headers.append(os.path.join(os.path.dirname(HERE), "include", "emelb_gguf.h"))
     headers = [h for h in headers if os.path.exists(h)]
     nccl_inc, nccl_lib = _nccl_paths()
     objs = []

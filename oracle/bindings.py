@@ -238,8 +238,39 @@ class Ref(_Lib):
             self.f(n).restype = C.c_float
             self.f(n).argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_uint64]
 
+        self.f("gguf_probe").restype = C.c_uint32
+        self.f("gguf_probe").argtypes = [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]
+        self.f("gguf_parse").restype = C.c_uint32
+        self.f("gguf_parse").argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
+
     def can_run(self, code, op):
         return bool(self.f("can_run")(code, C.byref(op)))
+
+    def gguf_probe(self, image: bytes):
+        """-> (error, (tensor_count, kv_count, max_key_bytes, max_value_bytes, tensor_data_bytes))"""
+        buf = np.frombuffer(image, np.uint8) if len(image) else np.zeros(0, np.uint8)
+        req4, total = (C.c_uint32 * 4)(), C.c_uint64(0)
+        err = self.f("gguf_probe")(buf.ctypes.data if len(image) else None, len(image), req4, C.byref(total))
+        return err, (req4[0], req4[1], req4[2], req4[3], total.value)
+
+    def gguf_parse(self, image: bytes):
+        """-> (error, [(key, value type, payload)], [tensor record dicts]) through probe + parse"""
+        err, req = self.gguf_probe(image)
+        if err != 0:
+            return err, [], []
+        buf = np.frombuffer(image, np.uint8)
+        arena = np.zeros(max(1, req[1] * (req[2] + req[3])), np.uint8)
+        kv = np.zeros((max(1, req[1]), 5), np.uint32)
+        ten = np.zeros((max(1, req[0]), 11), np.uint64)
+        err = self.f("gguf_parse")(buf.ctypes.data, len(image), arena.ctypes.data, kv.ctypes.data, ten.ctypes.data)
+        if err != 0:
+            return err, [], []
+        a = arena.tobytes()
+        kvs = [(a[int(r[0]):int(r[0] + r[1])], int(r[4]), a[int(r[2]):int(r[2]) + int(r[3])]) for r in kv[:req[1]]]
+        tensors = [{"name": image[int(r[0]):int(r[0] + r[1])], "type": int(np.int64(r[2])), "n_dims": int(r[3]),
+                    "dims": tuple(int(x) for x in r[4:8]), "data_offset": int(r[8]), "file_offset": int(r[9]),
+                    "data_size": int(r[10])} for r in ten[:req[0]]]
+        return 0, kvs, tensors
 
     def mul_mat(self, op, route="scalar", lanes=1):
         if route == "scalar":

@@ -16,6 +16,7 @@
 #include <thread>
 #include <vector>
 
+#include "emel/gguf/loader/detail.hpp"
 #include "emel/kernel/x86_64/actions.hpp"
 
 #include "../include/emelb.h"
@@ -257,6 +258,69 @@ float ref_row_dot_avx2(int type, const void* lhs, const void* rhs, uint64_t bloc
 
 int ref_host_has_avx2_fma_f16c(void) {
   return kx::detect_avx2() && kx::detect_fma() ? 1 : 0;
+}
+
+// ---- GGUF loader (src/emel/gguf/loader/detail.hpp:419-733).  The loader's state
+// machine needs a header-only dependency that is not in the checkout, so the two
+// functions it dispatches to are called directly, behind the request guard it
+// applies first (an absent or empty image is invalid_request,
+// src/emel/gguf/loader/guards.hpp:9-11, 33-43).
+// req_out: {tensor_count, kv_count, max_key_bytes, max_value_bytes} then tensor_data_bytes
+uint32_t ref_gguf_probe(const uint8_t* image, uint64_t bytes, uint32_t* req4_out, uint64_t* data_bytes_out) {
+  namespace gl = ::emel::gguf::loader;
+  if (image == nullptr || bytes == 0) return static_cast<uint32_t>(gl::error::invalid_request);
+  gl::requirements req{};
+  const auto err = gl::detail::probe_requirements(std::span<const uint8_t>{image, bytes}, req);
+  req4_out[0] = req.tensor_count;
+  req4_out[1] = req.kv_count;
+  req4_out[2] = req.max_key_bytes;
+  req4_out[3] = req.max_value_bytes;
+  *data_bytes_out = req.tensor_data_bytes;
+  return static_cast<uint32_t>(err);
+}
+
+// probe + bind + parse with exactly the storage the probe asked for.  Outputs, when
+// the pointers are non-null and the parse succeeded:
+//   kv_out[i*5..]     = {key_offset, key_length, value_offset, value_length, value_type}
+//                       (offsets into arena_out, which must hold kv_count*(max_key+max_value) bytes)
+//   tensor_out[i*11..] = {name_offset, name_length, type, n_dims, dims[4], data_offset, file_offset, data_size}
+uint32_t ref_gguf_parse(const uint8_t* image, uint64_t bytes, uint8_t* arena_out, uint32_t* kv_out,
+                        uint64_t* tensor_out) {
+  namespace gl = ::emel::gguf::loader;
+  if (image == nullptr || bytes == 0) return static_cast<uint32_t>(gl::error::invalid_request);
+  const std::span<const uint8_t> file{image, bytes};
+  gl::requirements req{};
+  auto err = gl::detail::probe_requirements(file, req);
+  if (err != 0) return static_cast<uint32_t>(err);
+  std::vector<uint8_t> arena(gl::detail::required_kv_arena_bytes(req));
+  std::vector<gl::kv_entry> kvs(req.kv_count);
+  std::vector<::emel::model::data::tensor_record> tensors(req.tensor_count);
+  err = gl::detail::parse_bound_storage(file, arena, kvs, tensors, req);
+  if (err != 0) return static_cast<uint32_t>(err);
+  if (arena_out != nullptr && !arena.empty()) std::memcpy(arena_out, arena.data(), arena.size());
+  if (kv_out != nullptr) {
+    for (size_t i = 0; i < kvs.size(); ++i) {
+      const gl::kv_entry& e = kvs[i];
+      const uint32_t row[5] = {e.key_offset, e.key_length, e.value_offset, e.value_length, e.value_type};
+      std::memcpy(kv_out + i * 5, row, sizeof(row));
+    }
+  }
+  if (tensor_out != nullptr) {
+    for (size_t i = 0; i < tensors.size(); ++i) {
+      const auto& t = tensors[i];
+      uint64_t* row = tensor_out + i * 11;
+      row[0] = t.name_offset;
+      row[1] = t.name_length;
+      row[2] = static_cast<uint64_t>(static_cast<int64_t>(t.type));
+      row[3] = static_cast<uint64_t>(static_cast<int64_t>(t.n_dims));
+      for (int d = 0; d < 4; ++d) row[4 + d] = static_cast<uint64_t>(t.dims[d]);
+      row[8] = t.data_offset;
+      row[9] = t.file_offset;
+      row[10] = t.data_size;
+      if (t.data != image + t.file_offset) return 0x8000u;  // the record must point into the image
+    }
+  }
+  return 0u;
 }
 
 }  // extern "C"
