@@ -13,6 +13,8 @@ One JSON line on stdout (rank 0).  Workloads (synthetic data, seeded):
               One step = one mat-vec over each of COPIES distinct weight copies
               (COPIES x 9.4 MB > the 126 MB L2, so every step streams from HBM).
   gemv_q8_0   configuration 2: Q8_0 14336x4096, token batch --ncols in {1, 8, 64}.
+  prefill_q4_k configuration 4: the three FFN products of a 2048-token batch on the tensor cores.
+  load_gguf   a GGUF file of --layers Llama-8B-shape layers: open + parse + upload to HBM (GB/s).
 `value` is measured with operands resident in HBM; `e2e` through the same C-ABI
 calls with host (pinned) activation and result buffers, copies inside the timed
 region.  `--impl reference` times the reference's own AVX2 kernels
@@ -497,6 +499,204 @@ def run_reference_prefill(args):
 
 
 
+# ------------------------------------------------------------------ GGUF file -> HBM
+def load_spec(args):
+    layers = args.layers
+    per_layer = [("attn_q", 4096, 4096), ("attn_k", 4096, 1024), ("attn_v", 4096, 1024), ("attn_output", 4096, 4096),
+                 ("ffn_gate", 4096, 14336), ("ffn_up", 4096, 14336), ("ffn_down", 14336, 4096)]
+    return dict(layers=layers, per_layer=per_layer,
+                name=f"GGUF file of {layers} Llama-8B-shape layers (Q4_K matrices, f32 norms): open + parse + upload every tensor")
+
+
+def write_load_file(sp, path, seed=20):
+    """Streams a GGUF v3 file to `path`: random block bytes (the loader never decodes them)."""
+    from tests import gguf_image as gi
+    rng = np.random.default_rng(seed)
+    pool = rng.integers(0, 256, size=64 << 20, dtype=np.uint8)
+    tensors = []
+    for l in range(sp["layers"]):
+        tensors.append((f"blk.{l}.attn_norm.weight", (4096,), 0, 4096 * 4))
+        tensors.append((f"blk.{l}.ffn_norm.weight", (4096,), 0, 4096 * 4))
+        for stem, k, m in sp["per_layer"]:
+            tensors.append((f"blk.{l}.{stem}.weight", (k, m), 12, k // 256 * 144 * m))
+    head = bytearray(b"GGUF" + np.array([3], "<u4").tobytes() + np.array([len(tensors), 2], "<u8").tobytes())
+    head += gi.kv("general.architecture", gi.T_STRING, "llama") + gi.kv("general.alignment", gi.T_UINT32, 32)
+    off = 0
+    for name, dims, t, nbytes in tensors:
+        head += gi.tensor_info(name, dims, t, off)
+        off += gi.pad(nbytes, 32)
+    head += b"\0" * (gi.pad(len(head), 32) - len(head))
+    with open(path, "wb") as fh:
+        fh.write(head)
+        at = 0
+        for _name, _dims, _t, nbytes in tensors:
+            left = gi.pad(nbytes, 32)
+            while left:
+                n = min(left, pool.size - at)
+                fh.write(pool[at:at + n].data)
+                at = (at + n) % pool.size
+                left -= n
+    return len(head) + off
+
+
+def load_dir():
+    for d in ("/dev/shm", tempfile.gettempdir()):
+        if os.path.isdir(d) and os.access(d, os.W_OK):
+            return tempfile.mkdtemp(prefix="emelb_gguf_", dir=d)
+    return tempfile.mkdtemp(prefix="emelb_gguf_")
+
+
+def reference_parse_us(path, repeats=5):
+    """-> (reference us, this library us, kind): probe + parse of the file's metadata by the reference's
+    own functions (oracle/_ref; the oracle port when that was not built) and by emelb_gguf_open_image,
+    both on an in-memory image of the file's size whose tensor data is left zero (neither reads it)."""
+    import ctypes as C
+    import emel_cpp_b200 as eb
+    from emel_cpp_b200 import gguf
+    from oracle import bindings as ob, gguf_oracle as go
+    with gguf.File(path) as f:
+        meta_end = f.data_section_offset
+    buf = np.zeros(os.path.getsize(path), np.uint8)
+    with open(path, "rb") as fh:
+        buf[:meta_end] = np.frombuffer(fh.read(meta_end), np.uint8)
+    ref = ob.ref()
+    t_ref, t_lib = [], []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        err = ref.f("gguf_parse")(buf.ctypes.data, buf.size, None, None, None) if ref is not None else go.parse(buf.data)[0]
+        t_ref.append(time.perf_counter() - t0)
+        assert err == 0, err
+        h = C.c_void_p()
+        t0 = time.perf_counter()
+        err = eb.lib().emelb_gguf_open_image(buf.ctypes.data, buf.size, C.byref(h))
+        t_lib.append(time.perf_counter() - t0)
+        assert err == 0, err
+        eb.lib().emelb_gguf_close(h)
+    return float(np.median(t_ref) * 1e6), float(np.median(t_lib) * 1e6), ("reference" if ref is not None else "port")
+
+
+def run_load(args):
+    import torch
+    import emel_cpp_b200 as eb
+    from emel_cpp_b200 import gguf
+    rank, world, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    be = eb.Backend(local)
+    sp = load_spec(args)
+    d = load_dir()
+    path = os.path.join(d, f"bench_{rank}.gguf")
+    try:
+        file_bytes = write_load_file(sp, path)
+        steps, warmup = min(args.steps, 8), args.warmup
+
+        def one_load(mode):
+            """mode: None = the default route (one pipelined pass over the file); "each" = the same route, one
+            call per tensor; "plain" / "register" = the alternative routes of the library, whole file."""
+            if mode in ("plain", "register"):
+                os.environ["EMELB_UPLOAD_MODE"] = mode
+            else:
+                os.environ.pop("EMELB_UPLOAD_MODE", None)
+            t0 = time.perf_counter()
+            f = gguf.File(path)
+            t1 = time.perf_counter()
+            n = f.requirements.tensor_count
+            lib, h, bh = eb.lib(), f.handle, be.handle
+            if mode == "each":
+                for i in range(n):
+                    err = lib.emelb_gguf_upload(bh, h, i, 100000 + i, None)
+                    assert err == 0, (i, err)
+            else:
+                err = lib.emelb_gguf_upload_all(bh, h, 100000)
+                assert err == 0, err
+            be.sync()
+            t2 = time.perf_counter()
+            return f, n, t1 - t0, t2 - t0
+
+        def unload(f, n, check=False):
+            if check:      # bytes in HBM == bytes in the file, for three tensors
+                for i in (0, n // 2, n - 1):
+                    rec = f.tensor(i)
+                    st = be.state(100000 + i)
+                    got = np.empty(rec["data_size"], np.uint8)
+                    assert be.to_host(got, st.buffer, rec["data_size"])
+                    want = np.ctypeslib.as_array((C.c_uint8 * rec["data_size"]).from_address(rec["data"]))
+                    assert np.array_equal(got, want), f"tensor {i} differs after upload"
+            for i in range(n):
+                be.evict(100000 + i)
+            f.close()
+
+        import ctypes as C
+        results = {}
+        with ClockSampler(local) as clocks:
+            for mode in (None, "each", "plain", "register"):
+                for _ in range(warmup if mode is None else 1):
+                    f, n, _p, _t = one_load(mode)
+                    unload(f, n)
+                barrier(world)
+                parse_s, total_s = [], []
+                for k in range(steps if mode is None else min(steps, 3)):
+                    f, n, p, t = one_load(mode)
+                    parse_s.append(p)
+                    total_s.append(t)
+                    unload(f, n, check=(k == 0))
+                results[{None: "staged", "each": "staged_per_tensor"}.get(mode, mode)] = (float(np.mean(total_s)), float(np.median(parse_s)))
+            os.environ.pop("EMELB_UPLOAD_MODE", None)
+        sec = max_over_ranks(results["staged"][0], world, f"cuda:{local}")
+        if rank != 0:
+            return
+        gbs = file_bytes * world / sec / 1e9
+        ref_us, lib_us, kind = reference_parse_us(path)
+        peaks, peak_kind = measured_peaks()
+        peak = float(peaks["hbm_gbs"])
+        line = {"metric": "GGUF file to HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "u8", "data": "synthetic",
+                "config": {"workload": sp["name"], "file_bytes": file_bytes, "tensors": n, "file_dir": os.path.dirname(path),
+                           "timer": "host wall clock around the synchronous open + upload calls (page cache warm)",
+                           "open_file_us": results["staged"][1] * 1e6, "parse_us": lib_us,
+                           "routes_gbs": {k: file_bytes / v[0] / 1e9 for k, v in results.items()},
+                           "upload_threads": int(os.environ.get("EMELB_UPLOAD_THREADS", min(16, os.cpu_count() or 1)))},
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": file_bytes, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                             "note": f"copy-engine transfers only, no kernel: bounded by the host link, not by HBM ({peak_kind} HBM peak shown)"},
+                "cpu_baseline": {"value": ref_us, "unit": "us per probe + parse of the same metadata", "cores": 1, "kind": kind,
+                                 "sample": "median of 5 parses; the reference maps the file and does not copy tensor data"},
+                "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+    finally:
+        be.close()
+        try:
+            os.unlink(path)
+            os.rmdir(d)
+        except OSError:
+            pass
+
+
+def run_reference_load(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    sp = load_spec(args)
+    d = load_dir()
+    path = os.path.join(d, "bench_ref.gguf")
+    try:
+        write_load_file(sp, path)
+        us, _lib_us, kind = reference_parse_us(path, repeats=max(3, min(args.steps, 9)))
+        line = {"impl": "reference", "metric": "GGUF probe + parse us", "value": us, "unit": "us", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False,
+                "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                "config": {"workload": sp["name"]},
+                "cpu_baseline": {"value": us, "unit": "us", "cores": 1, "kind": kind, "sample": "probe + parse of the file's metadata"},
+                "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+    finally:
+        try:
+            os.unlink(path)
+            os.rmdir(d)
+        except OSError:
+            pass
+
+
 # ------------------------------------------------------------------ decode workload (configurations 3 and 5)
 DECODE_SHAPES = {
     "decode_8b": dict(n_layer=32, n_embd=4096, n_head=32, n_head_kv=8, head_dim=128, n_ff=14336, n_vocab=128256,
@@ -784,7 +984,8 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_70b", "gemv_q4_k", "gemv_q8_0", "prefill_q4_k"])
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "decode_70b", "gemv_q4_k", "gemv_q8_0", "prefill_q4_k", "load_gguf"])
+    ap.add_argument("--layers", type=int, default=16, help="load_gguf: layers in the synthetic file (122.7 MB each)")
     ap.add_argument("--prompt", type=int, default=None, help="prompt length override for the decode workloads")
     ap.add_argument("--ncols", type=int, default=1)
     ap.add_argument("--rows", type=int, default=None, help="row count override for gemv_q4_k")
@@ -801,6 +1002,8 @@ def main():
     decode = args.workload.startswith("decode")
     if args.workload == "prefill_q4_k":
         (run_reference_prefill if args.impl == "reference" else run_prefill)(args)
+    elif args.workload == "load_gguf":
+        (run_reference_load if args.impl == "reference" else run_load)(args)
     elif args.impl == "reference":
         (run_reference_decode if decode else run_reference_gemv)(args)
     else:

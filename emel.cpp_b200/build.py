@@ -27,6 +27,7 @@ SOURCES = {
     "comm.cu": [],
     "noalloc.cu": [],
     "gguf.cu": [],
+    "upload.cu": [],
     "api.cu": [],
 }
 

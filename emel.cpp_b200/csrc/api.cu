@@ -336,6 +336,7 @@ uint32_t emelb_destroy(emelb_ctx* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   comm_release(c);
+  upload_ring_release(c);
   for (auto& kv : c->residents)
     if (kv.second.dev) cudaFree(kv.second.dev);
   for (void* p : c->owned) cudaFree(p);
@@ -383,30 +384,53 @@ uint32_t emelb_set_attention_mode(emelb_ctx* c, int mode) {
 // ------------------------------------------------------------------ residency
 uint32_t emelb_residency_upload(emelb_ctx* c, int32_t tensor_id, const void* host, uint64_t bytes, int32_t tensor_type,
                                 const void** dev_out) {
-  if (!c || !host || bytes == 0) return EMELB_INVALID_REQUEST;
-  auto found = c->residents.find(tensor_id);
-  if (found != c->residents.end() && found->second.state == EMELB_LIFECYCLE_RESIDENT) return EMELB_INVALID_REQUEST;
+  UploadSpan span{tensor_id, host, bytes, tensor_type, 0, nullptr};
+  const uint32_t err = emelb::residency_upload_many(c, &span, 1, -1);
+  if (err == EMELB_OK && dev_out) *dev_out = span.dev;
+  return err;
+}
+
+}  // extern "C"
+
+uint32_t emelb::residency_upload_many(emelb_ctx* c, UploadSpan* spans, size_t count, int fd) {
+  if (!c || !spans || count == 0) return EMELB_INVALID_REQUEST;
+  for (size_t i = 0; i < count; ++i) {
+    if (!spans[i].host || spans[i].bytes == 0) return EMELB_INVALID_REQUEST;
+    auto found = c->residents.find(spans[i].tensor_id);
+    if (found != c->residents.end() && found->second.state == EMELB_LIFECYCLE_RESIDENT) return EMELB_INVALID_REQUEST;
+    for (size_t k = 0; k < i; ++k)
+      if (spans[k].tensor_id == spans[i].tensor_id) return EMELB_INVALID_REQUEST;
+  }
   cudaSetDevice(c->device);
-  void* dev = nullptr;
-  // padded so that 16-byte vector loads of the last row chunk stay inside the allocation
-  if (!cuda_ok(c, cudaMalloc(&dev, (bytes + 255) & ~uint64_t(255)))) {
-    Resident& r = c->residents[tensor_id];
-    r.state = EMELB_LIFECYCLE_INTERNAL_ERROR;
+  auto release = [&](size_t upto) {
+    for (size_t k = 0; k < upto; ++k) {
+      cudaFree(spans[k].dev);
+      spans[k].dev = nullptr;
+    }
+  };
+  for (size_t i = 0; i < count; ++i) {
+    // padded so that 16-byte vector loads of the last row chunk stay inside the allocation
+    if (!cuda_ok(c, cudaMalloc(&spans[i].dev, (spans[i].bytes + 255) & ~uint64_t(255)))) {
+      release(i);
+      c->residents[spans[i].tensor_id].state = EMELB_LIFECYCLE_INTERNAL_ERROR;
+      return EMELB_INTERNAL_ERROR;
+    }
+  }
+  if (!cuda_ok(c, upload_spans(c, spans, count, fd))) {
+    release(count);
     return EMELB_INTERNAL_ERROR;
   }
-  if (!cuda_ok(c, cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, c->stream)) ||
-      !cuda_ok(c, cudaStreamSynchronize(c->stream))) {
-    cudaFree(dev);
-    return EMELB_INTERNAL_ERROR;
+  for (size_t i = 0; i < count; ++i) {
+    Resident& r = c->residents[spans[i].tensor_id];
+    if (r.host) c->by_host.erase(reinterpret_cast<uintptr_t>(r.host));
+    r = Resident{EMELB_LIFECYCLE_RESIDENT, spans[i].dev, spans[i].bytes, spans[i].host, spans[i].tensor_type};
+    c->by_host[reinterpret_cast<uintptr_t>(spans[i].host)] = spans[i].tensor_id;
+    c->dev_ranges[reinterpret_cast<uintptr_t>(spans[i].dev)] = spans[i].bytes;
   }
-  Resident& r = c->residents[tensor_id];
-  if (r.host) c->by_host.erase(reinterpret_cast<uintptr_t>(r.host));
-  r = Resident{EMELB_LIFECYCLE_RESIDENT, dev, bytes, host, tensor_type};
-  c->by_host[reinterpret_cast<uintptr_t>(host)] = tensor_id;
-  c->dev_ranges[reinterpret_cast<uintptr_t>(dev)] = bytes;
-  if (dev_out) *dev_out = dev;
   return EMELB_OK;
 }
+
+extern "C" {
 
 uint32_t emelb_residency_evict(emelb_ctx* c, int32_t tensor_id) {
   if (!c) return EMELB_INVALID_REQUEST;

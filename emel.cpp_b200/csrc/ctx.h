@@ -7,6 +7,7 @@
 
 #include <map>
 #include <set>
+#include <vector>
 
 #include "../../include/emelb.h"
 #include "kernels.h"
@@ -24,9 +25,35 @@ struct Resident {
   int32_t type = 0;
 };
 
+// one uploader thread's share of the page-locked staging ring (upload.cu)
+struct UploadLane {
+  cudaStream_t stream = nullptr;
+  void* pinned[2] = {nullptr, nullptr};
+  cudaEvent_t drained[2] = {nullptr, nullptr};
+};
+
 ActPlanes planes_view(const ActPlanesMut& m, int type, int K);
 cudaError_t quantize_into_planes(int wtype, const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st);
 
+}  // namespace emelb
+
+struct emelb_ctx;
+namespace emelb {
+// one span of a residency upload: `host` is the key and, when no file is named, the source
+struct UploadSpan {
+  int32_t tensor_id;
+  const void* host;
+  uint64_t bytes;
+  int32_t tensor_type;
+  uint64_t file_offset;  // of the span in the file `fd` names (unused when fd < 0)
+  void* dev;             // filled by residency_upload_many
+};
+// spans -> their device buffers, complete on return.  Spans outside page-locked memory go through the
+// staging ring in one pipeline over all of them; fd >= 0 names the file the spans map (read by pread).
+cudaError_t upload_spans(emelb_ctx* c, const UploadSpan* spans, size_t count, int fd);
+void upload_ring_release(emelb_ctx* c);
+// emelb_residency_upload for several tensors at once: all or nothing
+uint32_t residency_upload_many(emelb_ctx* c, UploadSpan* spans, size_t count, int fd);
 }  // namespace emelb
 
 struct emelb_ctx {
@@ -73,6 +100,7 @@ struct emelb_ctx {
   std::set<void*> owned;
   std::map<uintptr_t, uint64_t> dev_ranges;  // device spans this context allocated (start -> bytes)
   bool capturing = false;
+  std::vector<emelb::UploadLane> upload_lanes;  // created by the first large residency upload
   // row-shard exchange (comm.cu): one communicator per context, one rank per GPU
   void* comm = nullptr;  // ncclComm_t
   int comm_rank = 0;

@@ -26,6 +26,7 @@
 #include <vector>
 
 #include "../../include/emelb_gguf.h"
+#include "ctx.h"
 
 namespace {
 
@@ -251,6 +252,7 @@ struct emelb_gguf {
   const uint8_t* image = nullptr;
   uint64_t bytes = 0;
   void* mapping = nullptr;  // non-null when the handle owns an mmap of `bytes`
+  int fd = -1;              // the mapped file, kept open so that uploads can read it without page faults
   Walked walked;
   std::vector<emelb_gguf_kv> kvs;
   std::vector<emelb_gguf_tensor> tensors;
@@ -331,21 +333,25 @@ uint32_t emelb_gguf_open_file(const char* path, emelb_gguf** out) {
   }
   const uint64_t bytes = uint64_t(st.st_size);
   void* m = ::mmap(nullptr, bytes, PROT_READ, MAP_PRIVATE, fd, 0);
-  ::close(fd);
-  if (m == MAP_FAILED) return EMELB_GGUF_INTERNAL_ERROR;
-  ::madvise(m, bytes, MADV_SEQUENTIAL);
+  if (m == MAP_FAILED) {
+    ::close(fd);
+    return EMELB_GGUF_INTERNAL_ERROR;
+  }
   const uint32_t err = emelb_gguf_open_image(static_cast<const uint8_t*>(m), bytes, out);
   if (err != EMELB_GGUF_OK) {
     ::munmap(m, bytes);
+    ::close(fd);
     return err;
   }
   (*out)->mapping = m;
+  (*out)->fd = fd;
   return EMELB_GGUF_OK;
 }
 
 uint32_t emelb_gguf_close(emelb_gguf* g) {
   if (!g) return EMELB_GGUF_INVALID_REQUEST;
   if (g->mapping) ::munmap(g->mapping, g->bytes);
+  if (g->fd >= 0) ::close(g->fd);
   delete g;
   return EMELB_GGUF_OK;
 }
@@ -394,9 +400,30 @@ uint32_t emelb_gguf_upload(emelb_ctx* ctx, const emelb_gguf* g, uint32_t tensor_
   if (!ctx || !g || tensor_index >= g->tensors.size()) return EMELB_GGUF_INVALID_REQUEST;
   const emelb_gguf_tensor& t = g->tensors[tensor_index];
   if (t.data_size == 0) return EMELB_GGUF_INVALID_REQUEST;
-  const uint32_t err = emelb_residency_upload(ctx, tensor_id, t.data, t.data_size, t.type, dev_out);
+  emelb::UploadSpan span{tensor_id, t.data, t.data_size, t.type, t.file_offset, nullptr};
+  const uint32_t err = emelb::residency_upload_many(ctx, &span, 1, g->fd);
+  if (err == EMELB_OK && dev_out) *dev_out = span.dev;
   if (err == EMELB_OK) return EMELB_GGUF_OK;
   // a tensor id that is already resident is the caller's mistake; anything else is the device's
+  return err == EMELB_INVALID_REQUEST ? EMELB_GGUF_INVALID_REQUEST : EMELB_GGUF_INTERNAL_ERROR;
+}
+
+uint32_t emelb_gguf_upload_all(emelb_ctx* ctx, const emelb_gguf* g, int32_t first_tensor_id) {
+  if (!ctx || !g) return EMELB_GGUF_INVALID_REQUEST;
+  std::vector<emelb::UploadSpan> spans;
+  try {
+    spans.reserve(g->tensors.size());
+    for (size_t i = 0; i < g->tensors.size(); ++i) {
+      const emelb_gguf_tensor& t = g->tensors[i];
+      if (t.data_size == 0) continue;  // nothing to hold in HBM
+      spans.push_back(emelb::UploadSpan{int32_t(first_tensor_id + int32_t(i)), t.data, t.data_size, t.type, t.file_offset, nullptr});
+    }
+  } catch (const std::bad_alloc&) {
+    return EMELB_GGUF_CAPACITY;
+  }
+  if (spans.empty()) return EMELB_GGUF_OK;
+  const uint32_t err = emelb::residency_upload_many(ctx, spans.data(), spans.size(), g->fd);
+  if (err == EMELB_OK) return EMELB_GGUF_OK;
   return err == EMELB_INVALID_REQUEST ? EMELB_GGUF_INVALID_REQUEST : EMELB_GGUF_INTERNAL_ERROR;
 }
 
@@ -411,7 +438,9 @@ uint32_t emelb_gguf_upload_rows(emelb_ctx* ctx, const emelb_gguf* g, uint32_t te
   const uint64_t total_rows = t.data_size / row_bytes;
   if (first_row > total_rows || rows > total_rows - first_row) return EMELB_GGUF_INVALID_REQUEST;
   const uint8_t* host = static_cast<const uint8_t*>(t.data) + first_row * row_bytes;
-  const uint32_t err = emelb_residency_upload(ctx, tensor_id, host, rows * row_bytes, t.type, dev_out);
+  emelb::UploadSpan span{tensor_id, host, rows * row_bytes, t.type, t.file_offset + first_row * row_bytes, nullptr};
+  const uint32_t err = emelb::residency_upload_many(ctx, &span, 1, g->fd);
+  if (err == EMELB_OK && dev_out) *dev_out = span.dev;
   if (err != EMELB_OK) return err == EMELB_INVALID_REQUEST ? EMELB_GGUF_INVALID_REQUEST : EMELB_GGUF_INTERNAL_ERROR;
   if (host_out) *host_out = host;
   return EMELB_GGUF_OK;

@@ -58,6 +58,7 @@ SIGNATURES = {
     "emelb_gguf_find_tensor": (C.c_int32, [_P, C.c_char_p]),
     "emelb_gguf_find_kv": (C.c_int32, [_P, C.c_char_p]),
     "emelb_gguf_upload": (C.c_uint32, [_P, _P, C.c_uint32, C.c_int32, C.POINTER(_P)]),
+    "emelb_gguf_upload_all": (C.c_uint32, [_P, _P, C.c_int32]),
     "emelb_gguf_upload_rows": (C.c_uint32, [_P, _P, C.c_uint32, C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(_P),
                                             C.POINTER(_P)]),
 }
@@ -192,6 +193,12 @@ class File:
             raise GgufError("gguf upload", err)
         return dev.value
 
+    def upload_all(self, backend: eb.Backend, first_tensor_id: int = 0) -> None:
+        """Every tensor of the file -> HBM in one pipelined pass; tensor i gets id first_tensor_id + i."""
+        err = eb.lib().emelb_gguf_upload_all(backend.handle, self._h, first_tensor_id)
+        if err != OK:
+            raise GgufError("gguf upload_all", err)
+
     def upload_rows(self, backend: eb.Backend, tensor_index: int, tensor_id: int, first_row: int, rows: int):
         """Rows [first_row, first_row + rows) -> HBM; returns (address in the image, device address)."""
         host, dev = _P(), _P()
@@ -248,13 +255,16 @@ def load_llama(backend: eb.Backend, f: File, n_ctx: int | None = None, first_ten
     sess = el.Session(backend, cfg)
     shapes = el.matrix_shapes(cfg)
 
+    whole = shard_count <= 1     # unsharded: the whole file goes up in one pipelined pass
+
     def bind(layer, role, name):
         t = f.find_tensor(name)
         if t is None:
             raise GgufError(f"gguf tensor {name}", MODEL_INVALID)
         tid = first_tensor_id + t["index"]
         if role in _NORMS:
-            f.upload(backend, t["index"], tid)
+            if not whole:
+                f.upload(backend, t["index"], tid)
             ok = t["type"] == eb.F32 and t["dims"][0] == cfg.n_embd and sess.bind_norm(layer, role, t["data"])
         elif shard_count > 1 and role != el.TOKEN_EMBD:
             k, m = shapes[role]
@@ -263,12 +273,15 @@ def load_llama(backend: eb.Backend, f: File, n_ctx: int | None = None, first_ten
                 host, _dev = f.upload_rows(backend, t["index"], tid, shard_rank * m, m)
                 ok = sess.bind_matrix(layer, role, host, t["type"])
         else:
-            f.upload(backend, t["index"], tid)
+            if not whole:
+                f.upload(backend, t["index"], tid)
             ok = (t["dims"][0], t["dims"][1]) == shapes[role] and sess.bind_matrix(layer, role, t["data"], t["type"])
         if not ok:
             raise GgufError(f"gguf bind {name}", MODEL_INVALID)
 
     try:
+        if whole:
+            f.upload_all(backend, first_tensor_id)
         for role, name in _GLOBAL_TENSORS.items():
             bind(-1, role, name)
         for layer in range(cfg.n_layer):

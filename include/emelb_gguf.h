@@ -115,6 +115,12 @@ EMELB_API uint32_t emelb_gguf_upload(emelb_ctx* ctx, const emelb_gguf* g,
                                      uint32_t tensor_index, int32_t tensor_id,
                                      const void** dev_out);
 
+/* every tensor of the file in one pipelined pass (tensor i gets id
+ * first_tensor_id + i; tensors without data are skipped).  All or nothing: on an
+ * error no tensor of the file has become resident through this call. */
+EMELB_API uint32_t emelb_gguf_upload_all(emelb_ctx* ctx, const emelb_gguf* g,
+                                         int32_t first_tensor_id);
+
 /* rows [first_row, first_row + rows) of a tensor of two or more dimensions (a row
  * is dims[0] elements; rows count over the remaining dimensions): what one rank
  * of a row-sharded product holds (src/emel/kernel/matmul/actions.hpp:49-66).

@@ -128,3 +128,47 @@ def test_upload_rows_feeds_a_row_sharded_product(be, port, tmp_path):
         with pytest.raises(gguf.GgufError):
             f.upload_rows(be, f.find_tensor("pad.f32")["index"], 7003, 0, 1)   # one dimension: no rows to slice
         be.evict(7002)
+        # the whole file at once is all or nothing: id 7101 (tensor 1) is taken, so tensor 0 must not stay behind
+        f.upload(be, rec["index"], 7101)
+        with pytest.raises(gguf.GgufError) as e:
+            f.upload_all(be, 7100)
+        assert e.value.err == gguf.INVALID_REQUEST
+        assert eb.LIFECYCLE[be.state(7100).lifecycle_state] == "unbound"
+        be.evict(7101)
+        f.upload_all(be, 7100)
+        for t in f.tensors():
+            st = be.state(7100 + t["index"])
+            got = np.empty(t["data_size"], np.uint8)
+            assert be.to_host(got, st.buffer, t["data_size"])
+            assert got.tobytes() == image[t["file_offset"]:t["file_offset"] + t["data_size"]]
+            be.evict(7100 + t["index"])
+
+
+def test_large_tensor_goes_through_the_staging_ring_unchanged(be, tmp_path):
+    """Spans above the direct-copy threshold are cut into chunks filled by several threads (pread from the
+    file, or memcpy from a host array): the bytes in HBM must be the file's, whatever the route."""
+    import os
+    rng = synth.rng(8)
+    sizes = [(1 << 20) + 32, 37 * (1 << 20) + 96, 5 * (1 << 20)]      # one direct-sized, two chunked (ragged ends)
+    blobs = [rng.integers(0, 256, size=n, dtype=np.uint8) for n in sizes]
+    image = gi.build([], [(f"t{i}", (len(b),), 24, b.tobytes()) for i, b in enumerate(blobs)], 32)
+    path = tmp_path / "big.gguf"
+    path.write_bytes(image)
+    for mode in (None, "plain", "register"):
+        if mode:
+            os.environ["EMELB_UPLOAD_MODE"] = mode
+        try:
+            with gguf.File(str(path)) as f:
+                f.upload_all(be, 7200)
+                for i, b in enumerate(blobs):
+                    st = be.state(7200 + i)
+                    got = np.empty(len(b), np.uint8)
+                    assert be.to_host(got, st.buffer, len(b)) and np.array_equal(got, b), (mode, i)
+                    be.evict(7200 + i)
+        finally:
+            os.environ.pop("EMELB_UPLOAD_MODE", None)
+    # a plain host array (no file behind it) takes the memcpy-fed ring
+    be.upload(7300, blobs[1], tensor_type=24)
+    got = np.empty(len(blobs[1]), np.uint8)
+    assert be.to_host(got, be.state(7300).buffer, len(got)) and np.array_equal(got, blobs[1])
+    be.evict(7300)
