@@ -92,6 +92,7 @@ _SIGNATURES = {
     "emelb_synth_fill": [_P, _P, C.c_int32, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64],
     "emelb_comm_unique_id": [_P, C.c_uint64],
     "emelb_comm_init": [_P, C.c_int32, C.c_int32, _P, C.c_uint64],
+    "emelb_flash_attn_batch": [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_float],
     "emelb_comm_destroy": [_P],
     "emelb_all_gather_rows": [_P, _P, C.c_uint64, C.c_uint64],
     "emelb_row_slice": [C.POINTER(Op), C.c_uint32, C.c_uint32, C.POINTER(Op), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
@@ -294,6 +295,11 @@ class Backend:
 
     def flash_attn_ext(self, op: Op) -> bool:
         return self._ret(lib().emelb_flash_attn_ext(self._h, C.byref(op)))
+
+    def flash_attn_batch(self, q_dev, k_dev, v_dev, dst_dev, head_dim, heads, kv_heads, batch, pos0, cache_head_stride, scale) -> bool:
+        """Causal attention of `batch` prompt tokens over the f16 cache; device pointers, token-fastest q / dst."""
+        return self._ret(lib().emelb_flash_attn_batch(self._h, q_dev, k_dev, v_dev, dst_dev, head_dim, heads, kv_heads, batch,
+                                                      pos0, cache_head_stride, scale))
 
     def quantize(self, src: View, dst: View) -> bool:
         return self._ret(lib().emelb_quantize(self._h, C.byref(src), C.byref(dst)))

@@ -22,6 +22,7 @@ SOURCES = {
     "gemv2.cu": [],
     "synth.cu": [],
     "attention.cu": [],
+    "prefill_attention.cu": [],
     "gemm_tc.cu": [],
     "llama.cu": [],
     "comm.cu": [],

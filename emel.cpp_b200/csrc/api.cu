@@ -635,6 +635,29 @@ uint32_t emelb_prepare_rhs(emelb_ctx* c, const emelb_view* src1, int32_t weight_
   return EMELB_OK;
 }
 
+// ------------------------------------------------------------------ attention over a token batch
+uint32_t emelb_flash_attn_batch(emelb_ctx* c, const float* q, const void* k, const void* v, float* dst, int32_t head_dim,
+                                int32_t heads, int32_t kv_heads, int32_t batch, int32_t pos0, int64_t cache_head_stride,
+                                float scale) {
+  if (!c) return EMELB_INVALID_REQUEST;
+  if (!q || !k || !v || !dst || batch <= 0 || pos0 < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
+      cache_head_stride < (int64_t)(pos0 + batch) * head_dim)
+    return reject(c);
+  for (const void* p : {(const void*)q, k, v, (const void*)dst})
+    if (classify(c, p) != Where::device) return reject(c);
+  cudaSetDevice(c->device);
+  PrefillAttnArgs a{q, dst, static_cast<const __half*>(k), static_cast<const __half*>(v), cache_head_stride,
+                    head_dim, heads, kv_heads, batch, pos0, scale};
+  if (!prefill_attention_supported(a)) {
+    c->diag.rejected_dispatch_calls += 1;
+    return EMELB_UNSUPPORTED_OP;
+  }
+  if (!cuda_ok(c, launch_prefill_attention(a, c->stream))) return EMELB_INTERNAL_ERROR;
+  c->diag.kernel_launches += 1;
+  c->diag.optimized_flash_dispatch_calls += 1;
+  return EMELB_OK;
+}
+
 // ------------------------------------------------------------------ op_flash_attn_ext
 uint32_t emelb_flash_attn_ext(emelb_ctx* c, const emelb_op* op) {
   if (!c || !op) return EMELB_INVALID_REQUEST;

@@ -178,13 +178,8 @@ swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, int 
 // as the block dequantizers; f32 / f16 tables are copied / widened)
 __device__ __forceinline__ uint16_t ld16e(const uint8_t* p) { return (uint16_t)p[0] | ((uint16_t)p[1] << 8); }
 
-__global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, int64_t row_bytes, const int* token_dev,
-                                 float* __restrict__ dst, int K) {
-  pdl_trigger();
-  pdl_wait();
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= K) return;
-  const uint8_t* r = table + (int64_t)(*token_dev) * row_bytes;
+// element e of the table row at r
+__device__ __forceinline__ float embed_value(int type, const uint8_t* __restrict__ r, int e) {
   float out;
   if (type == T_F32) {
     out = reinterpret_cast<const float*>(r)[e];
@@ -219,7 +214,96 @@ __global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, in
     const uint8_t qb = b[2 + (p & 15)];
     out = __fmul_rn((float)((p < 16 ? (qb & 0x0f) : (qb >> 4)) - 8), h2f(ld16e(b)));
   }
-  dst[e] = out;
+  return out;
+}
+
+__global__ void embed_row_kernel(int type, const uint8_t* __restrict__ table, int64_t row_bytes, const int* token_dev,
+                                 float* __restrict__ dst, int K) {
+  pdl_trigger();
+  pdl_wait();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= K) return;
+  dst[e] = embed_value(type, table + (int64_t)(*token_dev) * row_bytes, e);
+}
+
+// ================= token batches (prompt processing) =================
+// Activations of a batch of B tokens are kept feature-major: element e of token j at x[e * B + j], the
+// layout op_mul_mat reads its right-hand side in and writes its result in (src/emel/kernel/detail.hpp:3356-3571).
+// Per token the arithmetic of each kernel is that of its one-token counterpart above.
+
+__global__ void embed_rows_kernel(int type, const uint8_t* __restrict__ table, int64_t row_bytes, const int* __restrict__ tokens,
+                                  int B, float* __restrict__ dst, int K) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x, j = blockIdx.y;
+  if (e >= K) return;
+  dst[(int64_t)e * B + j] = embed_value(type, table + (int64_t)tokens[j] * row_bytes, e);
+}
+
+// 32 tokens per CTA (threadIdx.x), features strided over threadIdx.y
+__global__ void __launch_bounds__(1024)
+rms_norm_batch_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int K, int B, float* __restrict__ out) {
+  __shared__ double s_part[32][33];
+  __shared__ float s_scale[32];
+  const int tx = threadIdx.x, ty = threadIdx.y, j = blockIdx.x * 32 + tx;
+  double acc = 0.0;
+  if (j < B) {
+    for (int e = ty; e < K; e += blockDim.y) {
+      const float v = x[(int64_t)e * B + j];
+      acc += (double)__fmul_rn(v, v);
+    }
+  }
+  s_part[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0) {
+    double t = 0.0;
+    for (int i = 0; i < (int)blockDim.y; ++i) t += s_part[i][tx];
+    const float mean = (float)(t / (double)K);
+    s_scale[tx] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+  }
+  __syncthreads();
+  if (j >= B) return;
+  const float scale = s_scale[tx];
+  for (int e = ty; e < K; e += blockDim.y) out[(int64_t)e * B + j] = __fmul_rn(__fmul_rn(x[(int64_t)e * B + j], scale), w[e]);
+}
+
+// thread = (token j fastest, rotation pair or copied element, head)
+__global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, const float* __restrict__ v,
+                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pos0, int B,
+                                        int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,
+                                        __half* vcache, int64_t cache_head_stride) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= B) return;
+  const int head = blockIdx.y, pos = pos0 + j, pairs = rot_dim / 2;
+  const float* ct = cos_t + (int64_t)pos * pairs;
+  const float* st = sin_t + (int64_t)pos * pairs;
+  const int x1_base = neox ? pairs : 1, stride = neox ? 1 : 2;
+  if (head < n_head) {
+    float* h = q + (int64_t)head * head_dim * B + j;
+    for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
+      const int64_t d0 = (int64_t)(p * stride) * B, d1 = (int64_t)(p * stride + x1_base) * B;
+      const float x0 = h[d0], x1 = h[d1], c = ct[p], s = st[p];
+      h[d0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+      h[d1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    }
+  } else {
+    const int kh = head - n_head;
+    const float* h = k + (int64_t)kh * head_dim * B + j;
+    const float* vv = v + (int64_t)kh * head_dim * B + j;
+    __half* kd = kcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+    __half* vd = vcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+    for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
+      const int d0 = p * stride, d1 = p * stride + x1_base;
+      const float x0 = h[(int64_t)d0 * B], x1 = h[(int64_t)d1 * B], c = ct[p], s = st[p];
+      kd[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+      kd[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
+    }
+    for (int d = rot_dim + threadIdx.y; d < head_dim; d += blockDim.y) kd[d] = __float2half_rn(h[(int64_t)d * B]);
+    for (int d = threadIdx.y; d < head_dim; d += blockDim.y) vd[d] = __float2half_rn(vv[(int64_t)d * B]);
+  }
+}
+
+__global__ void add_inplace_kernel(float* __restrict__ acc, const float* __restrict__ y, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) acc[i] = __fadd_rn(acc[i], y[i]);
 }
 
 // ---- step bookkeeping on the device so a captured graph can run token after
@@ -271,6 +355,30 @@ cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out,
 cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, const int* token_dev, float* dst, int K,
                              cudaStream_t st) {
   EMELB_LAUNCH(embed_row_kernel, (K + 255) / 256, 256, 0, st, type, table, row_bytes, token_dev, dst, K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_embed_rows(int type, const uint8_t* table, int64_t row_bytes, const int* tokens_dev, int B, float* dst,
+                              int K, cudaStream_t st) {
+  embed_rows_kernel<<<dim3((K + 255) / 256, B), 256, 0, st>>>(type, table, row_bytes, tokens_dev, B, dst, K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rms_norm_batch(const float* x, const float* w, float eps, int K, int B, float* out, cudaStream_t st) {
+  rms_norm_batch_kernel<<<(B + 31) / 32, dim3(32, 32), 0, st>>>(x, w, eps, K, B, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope_store_batch(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t, int pos0,
+                                    int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,
+                                    __half* vcache, int64_t cache_head_stride, cudaStream_t st) {
+  rope_store_batch_kernel<<<dim3((B + 31) / 32, n_head + n_head_kv), dim3(32, 8), 0, st>>>(
+      q, k, v, cos_t, sin_t, pos0, B, n_head, n_head_kv, head_dim, rot_dim, neox, kcache, vcache, cache_head_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_add_inplace(float* acc, const float* y, int64_t n, cudaStream_t st) {
+  add_inplace_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(acc, y, n);
   return cudaGetLastError();
 }
 

@@ -119,6 +119,27 @@ cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out,
                           cudaStream_t st);
 cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, const int* token_dev, float* dst, int K,
                              cudaStream_t st);
+// token batches (prompt processing): activations feature-major, element e of token j at x[e * B + j]
+cudaError_t launch_embed_rows(int type, const uint8_t* table, int64_t row_bytes, const int* tokens_dev, int B, float* dst,
+                              int K, cudaStream_t st);
+cudaError_t launch_rms_norm_batch(const float* x, const float* w, float eps, int K, int B, float* out, cudaStream_t st);
+cudaError_t launch_rope_store_batch(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t, int pos0,
+                                    int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,
+                                    __half* vcache, int64_t cache_head_stride, cudaStream_t st);
+cudaError_t launch_add_inplace(float* acc, const float* y, int64_t n, cudaStream_t st);
+// causal attention of a batch of B query tokens at positions pos0 .. pos0 + B - 1 over the f16 KV cache
+// (q, dst feature-major {heads * head_dim, B}; f32 online softmax); false from the predicate: not taken
+struct PrefillAttnArgs {
+  const float* q;
+  float* dst;
+  const __half* k;   // one layer's cache: [kv_head][position][head_dim]
+  const __half* v;
+  int64_t cache_head_stride;  // halves
+  int head_dim, heads, kv_heads, B, pos0;
+  float scale;
+};
+bool prefill_attention_supported(const PrefillAttnArgs& a);
+cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t st);
 // state = {token, position, kv_tokens, step}
 cudaError_t launch_step_begin(int* state, int token, int position, cudaStream_t st);
 cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out, cudaStream_t st);

@@ -67,6 +67,11 @@ struct emelb_llama {
   int* state = nullptr;       // {token, position, kv_tokens, step}
   int* tokens_dev = nullptr;  // generated ids (n_ctx)
   int* host_pinned = nullptr;
+  // token-batch buffers of the prompt path (feature-major {features, batch}), allocated by the first batched prefill
+  int batch_cap = 0;
+  int* batch_tokens = nullptr;
+  float *b_hidden = nullptr, *b_norm = nullptr, *b_q = nullptr, *b_k = nullptr, *b_v = nullptr, *b_attn = nullptr;
+  float *b_gate = nullptr, *b_up = nullptr, *b_ffn = nullptr, *b_y = nullptr;
   int fa_splits = 1;
   int G = 1, rank = 0;        // row sharding
   int* pair_buf = nullptr;    // G x 16-byte records {value bits, global row, -, -}: argmax candidates
@@ -295,6 +300,69 @@ struct Enqueue {
   }
   void gather(float* full, size_t count_per_rank) { gather_bytes(full, count_per_rank * sizeof(float)); }
 
+  // y {w.M, B} = w x quantized(x {w.K, B}); the Q4_K products of 32 and more tokens run on the tensor cores
+  void batch_matmul(const Tensor& w, const float* x, float* y, int B) {
+    check(quantize_into_planes(w.type, x, B, B, w.K, planes(), st));
+    ++launches;
+    GemvArgs a{};
+    a.W = w.dev;
+    a.row_bytes = w.row_bytes;
+    a.M = w.M;
+    a.K = w.K;
+    a.act = planes_view(planes(), w.type, w.K);
+    a.col0 = 0;
+    a.y = y;
+    a.ldy = B;
+    a.tc_ws = s->c->tc_ws;
+    a.tc_ws_bytes = s->c->tc_ws_bytes;
+    a.sched = s->c->next_sched();
+    a.status = s->c->status_word();
+    a.part_val = s->c->part_val;
+    a.part_idx = s->c->part_idx;
+    a.best_val = s->c->best_val;
+    a.best_idx = s->c->best_idx;
+    check(launch_gemv(w.type, a, B, false, s->c->sm_count, st, &launches));
+  }
+
+  // B prompt tokens (ids in s->batch_tokens) at positions pos0 .. pos0 + B - 1 through every layer: fills the
+  // KV cache rows of those positions.  Same arithmetic per token as token_step except the attention, which
+  // is the f32 online-softmax kernel for token batches (attention mode 0 only).
+  void prefill_chunk(int B, int pos0) {
+    const emelb_llama_config& c = s->cfg;
+    const int q_dim = c.n_head * c.head_dim, kv_dim = c.n_head_kv * c.head_dim;
+    const int rot = c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim;
+    s->planes_src = nullptr;
+    check(launch_embed_rows(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->batch_tokens, B, s->b_hidden, c.n_embd, st));
+    ++launches;
+    for (int l = 0; l < c.n_layer; ++l) {
+      const Layer& w = s->layers[l];
+      const int64_t layer_off = (int64_t)l * c.n_head_kv * s->capacity * c.head_dim;
+      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, st));
+      ++launches;
+      batch_matmul(w.wq, s->b_norm, s->b_q, B);
+      batch_matmul(w.wk, s->b_norm, s->b_k, B);
+      batch_matmul(w.wv, s->b_norm, s->b_v, B);
+      check(launch_rope_store_batch(s->b_q, s->b_k, s->b_v, s->rope_cos, s->rope_sin, pos0, B, c.n_head, c.n_head_kv, c.head_dim,
+                                    rot, c.rope_neox, s->kcache + layer_off, s->vcache + layer_off, s->capacity * c.head_dim, st));
+      ++launches;
+      PrefillAttnArgs pa{s->b_q, s->b_attn, s->kcache + layer_off, s->vcache + layer_off, s->capacity * c.head_dim,
+                         c.head_dim, c.n_head, c.n_head_kv, B, pos0, 1.0f / std::sqrt((float)c.head_dim)};
+      check(launch_prefill_attention(pa, st));
+      ++launches;
+      batch_matmul(w.wo, s->b_attn, s->b_y, B);
+      check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
+      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.ffn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, st));
+      batch_matmul(w.gate, s->b_norm, s->b_gate, B);
+      batch_matmul(w.up, s->b_norm, s->b_up, B);
+      check(launch_swiglu(s->b_gate, s->b_up, c.n_ff * B, s->b_ffn, 0, planes(), st));
+      batch_matmul(w.down, s->b_ffn, s->b_y, B);
+      check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
+      launches += 4;
+    }
+    (void)q_dim;
+    (void)kv_dim;
+  }
+
   void token_step(Mode mode) {
     const emelb_llama_config& c = s->cfg;
     // which launches of the step carry the programmatic-serialization attribute (bit mask: 1 mat-vecs,
@@ -377,8 +445,10 @@ struct Enqueue {
   }
 };
 
-// capture (once per mode and attention mode) and return the replayable step
-cudaGraphExec_t step_graph(emelb_llama* s, Mode mode) {
+// capture (once per mode and attention mode) and return the replayable step.  The eager pass that precedes a
+// capture is a real step: it runs for (token, position), the step the caller is about to replay, so the KV row
+// it writes is the one the replay writes again (a stale position would overwrite a live row of the cache)
+cudaGraphExec_t step_graph(emelb_llama* s, Mode mode, int token, int position) {
   if (s->graphs[mode] && s->graph_attention_mode[mode] == s->c->attention_mode) return s->graphs[mode];
   if (s->graphs[mode]) {
     cudaStreamSynchronize(s->c->stream);
@@ -386,6 +456,7 @@ cudaGraphExec_t step_graph(emelb_llama* s, Mode mode) {
     s->graphs[mode] = nullptr;
   }
   // one eager pass first: sets per-kernel attributes outside the capture
+  if (!ctx_cuda_ok(s->c, launch_step_begin(s->state, token, position, s->c->stream))) return nullptr;
   Enqueue warm{s, s->c->stream};
   warm.token_step(mode);
   if (!warm.ok || !ctx_cuda_ok(s->c, cudaStreamSynchronize(s->c->stream))) return nullptr;
@@ -598,7 +669,7 @@ uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t position, flo
   emelb_ctx* c = s->c;
   cudaSetDevice(c->device);
   const Mode mode = logits_out ? MODE_LOGITS : MODE_ARGMAX;
-  cudaGraphExec_t g = step_graph(s, mode);
+  cudaGraphExec_t g = step_graph(s, mode, token, position);
   if (!g) return EMELB_INTERNAL_ERROR;
   bool ok = ctx_cuda_ok(c, launch_step_begin(s->state, token, position, c->stream));
   ok = ok && ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
@@ -625,20 +696,78 @@ uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t position, flo
   return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
 }
 
+namespace {
+
+// token-batch size of the prompt path: 0 = walk the prompt token by token.  Batches need the batch attention
+// kernel (attention mode 0: the reference-order modes exist to be compared one token at a time), an unsharded
+// session, and room for one batch in the context's activation planes.
+int prefill_batch_size(emelb_llama* s, int n) {
+  const char* off = getenv("EMELB_NO_BATCH_PREFILL");
+  const emelb_llama_config& c = s->cfg;
+  if (off || s->G != 1 || s->c->attention_mode != 0 || n < 2) return 0;
+  PrefillAttnArgs pa{nullptr, nullptr, s->kcache, s->vcache, s->capacity * c.head_dim, c.head_dim, c.n_head, c.n_head_kv, 1, 0, 1.0f};
+  if (!prefill_attention_supported(pa)) return 0;
+  int widest = c.n_ff > c.n_embd ? c.n_ff : c.n_embd;
+  if (c.n_head * c.head_dim > widest) widest = c.n_head * c.head_dim;
+  int cap = 512;
+  if (const char* e = getenv("EMELB_PREFILL_BATCH")) cap = atoi(e);
+  const int64_t fits = (int64_t)(s->c->act_capacity / (uint64_t)widest);
+  if (cap > fits) cap = (int)fits;
+  if ((int64_t)c.n_ff * cap > 0x7fffffff) cap = 0x7fffffff / c.n_ff;
+  return cap < 2 ? 0 : cap;
+}
+
+bool reserve_batch(emelb_llama* s, int B) {
+  if (s->batch_cap != 0) return true;  // sized by the first batched prompt; later batches are cut to fit
+  const emelb_llama_config& c = s->cfg;
+  const size_t q_dim = (size_t)c.n_head * c.head_dim, kv_dim = (size_t)c.n_head_kv * c.head_dim, b = (size_t)B;
+  bool ok = dev_alloc(s, (void**)&s->batch_tokens, sizeof(int) * b);
+  ok = ok && dev_alloc(s, (void**)&s->b_hidden, 4 * b * c.n_embd) && dev_alloc(s, (void**)&s->b_norm, 4 * b * c.n_embd);
+  ok = ok && dev_alloc(s, (void**)&s->b_y, 4 * b * c.n_embd);
+  ok = ok && dev_alloc(s, (void**)&s->b_q, 4 * b * q_dim) && dev_alloc(s, (void**)&s->b_attn, 4 * b * q_dim);
+  ok = ok && dev_alloc(s, (void**)&s->b_k, 4 * b * kv_dim) && dev_alloc(s, (void**)&s->b_v, 4 * b * kv_dim);
+  ok = ok && dev_alloc(s, (void**)&s->b_gate, 4 * b * c.n_ff) && dev_alloc(s, (void**)&s->b_up, 4 * b * c.n_ff);
+  ok = ok && dev_alloc(s, (void**)&s->b_ffn, 4 * b * c.n_ff);
+  if (ok) s->batch_cap = B;
+  return ok;
+}
+
+}  // namespace
+
 uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n, int32_t start_pos) {
   if (!s || !tokens || n <= 0 || !all_bound(s) || start_pos < 0 || start_pos + n > s->cfg.n_ctx) return EMELB_INVALID_REQUEST;
   for (int i = 0; i < n; ++i)
     if (!valid_step(s, tokens[i], start_pos + i)) return EMELB_INVALID_REQUEST;
   emelb_ctx* c = s->c;
   cudaSetDevice(c->device);
-  cudaGraphExec_t g = step_graph(s, MODE_PREFILL);
-  if (!g) return EMELB_INTERNAL_ERROR;
   bool ok = true;
-  for (int i = 0; ok && i < n; ++i) {
-    ok = ctx_cuda_ok(c, launch_step_begin(s->state, tokens[i], start_pos + i, c->stream));
-    ok = ok && ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+  int done = 0;
+  const int batch = prefill_batch_size(s, n);
+  if (batch > 0 && reserve_batch(s, batch < s->cfg.n_ctx ? batch : s->cfg.n_ctx)) {
+    // whole batches, then whatever is left as one shorter batch
+    while (ok && n - done >= 2) {
+      const int lim = batch < s->batch_cap ? batch : s->batch_cap;
+      const int B = n - done < lim ? n - done : lim;
+      std::memcpy(s->host_pinned, tokens + done, sizeof(int) * (size_t)B);
+      ok = ctx_cuda_ok(c, cudaMemcpyAsync(s->batch_tokens, s->host_pinned, sizeof(int) * (size_t)B, cudaMemcpyHostToDevice, c->stream));
+      c->diag.h2d_bytes += sizeof(int) * (uint64_t)B;
+      Enqueue e{s, c->stream};
+      e.prefill_chunk(B, start_pos + done);
+      ok = ok && e.ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));  // host_pinned is reused by the next batch
+      c->diag.kernel_launches += e.launches;
+      done += B;
+    }
+    if (!ok) return EMELB_INTERNAL_ERROR;
   }
-  c->diag.kernel_launches += (uint64_t)n * (1 + s->launches_mode[MODE_PREFILL]);
+  if (done < n) {
+    cudaGraphExec_t g = step_graph(s, MODE_PREFILL, tokens[done], start_pos + done);
+    if (!g) return EMELB_INTERNAL_ERROR;
+    for (int i = done; ok && i < n; ++i) {
+      ok = ctx_cuda_ok(c, launch_step_begin(s->state, tokens[i], start_pos + i, c->stream));
+      ok = ok && ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+    }
+    c->diag.kernel_launches += (uint64_t)(n - done) * (1 + s->launches_mode[MODE_PREFILL]);
+  }
   ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
   return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
 }
@@ -648,7 +777,7 @@ uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token, int32_t start
     return EMELB_INVALID_REQUEST;
   emelb_ctx* c = s->c;
   cudaSetDevice(c->device);
-  cudaGraphExec_t g = step_graph(s, MODE_ARGMAX);
+  cudaGraphExec_t g = step_graph(s, MODE_ARGMAX, first_token, start_pos);
   if (!g) return EMELB_INTERNAL_ERROR;
   bool ok = ctx_cuda_ok(c, launch_step_begin(s->state, first_token, start_pos, c->stream));
   for (int i = 0; ok && i < n; ++i) ok = ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));

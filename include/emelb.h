@@ -210,6 +210,21 @@ EMELB_API uint32_t emelb_mul_mat_argmax(emelb_ctx* ctx, const emelb_op* op);
  * (src/emel/kernel/x86_64/actions.hpp:1575-1641). ---- */
 EMELB_API uint32_t emelb_flash_attn_ext(emelb_ctx* ctx, const emelb_op* op);
 
+/* ---- the same attention for a batch of prompt tokens: query token j (of `batch`)
+ * sits at position pos0 + j and attends to cache positions 0 .. pos0 + j.  The
+ * reference walks a prompt through op_flash_attn_ext one token at a time
+ * (src/emel/text/generator/detail.hpp:3232-3279); here one launch covers the
+ * batch.  All pointers are device memory: q and dst are f32 {heads * head_dim,
+ * batch} with the token index fastest (op_mul_mat's result layout), k and v the
+ * f16 cache [kv_head][position][head_dim] with cache_head_stride halves between
+ * kv heads, holding positions 0 .. pos0 + batch - 1.  f32 online softmax
+ * (within 2e-5 of the exact softmax); head_dim 64 or 128, heads / kv_heads a
+ * divisor of 64, else EMELB_UNSUPPORTED_OP. ---- */
+EMELB_API uint32_t emelb_flash_attn_batch(emelb_ctx* ctx, const float* q, const void* k,
+                                          const void* v, float* dst, int32_t head_dim,
+                                          int32_t heads, int32_t kv_heads, int32_t batch,
+                                          int32_t pos0, int64_t cache_head_stride, float scale);
+
 /* ---- activation quantizers: replace quantize_row_q8_k_strided /
  * quantize_row_q8_0_strided (src/emel/kernel/detail.hpp:826-867, 804-824).
  * src = f32 {N, K} (token fastest, as op_mul_mat's src1); dst type selects

@@ -152,3 +152,87 @@ def test_decoder_rejects_bad_requests(port):
     with pytest.raises(eb.BackendError):
         el.Session(be, el.config(**bad))
     be.close()
+
+
+def _prompt_then_logits(be, sess, prompt, pieces, mode=0):
+    """Prefill `prompt[:-1]` in the given pieces (attention mode `mode`), then the logits of the last token
+    (always with the split-KV attention, so only the prompt path differs between calls)."""
+    be.set_attention_mode(mode)
+    pos = 0
+    for n in pieces:
+        assert sess.prefill(prompt[pos:pos + n], pos), sess.last_error
+        pos += n
+    be.set_attention_mode(0)
+    assert pos == len(prompt) - 1
+    return sess.decode(prompt[-1], pos, want_logits=True)
+
+
+def _rel(a, b):
+    return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+
+@pytest.mark.parametrize("cfg,types", [
+    (TINY, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K}),
+    (MIXED, {"embd": eb.Q8_0, "output": eb.Q8_0, "default": eb.Q8_0, el.ATTN_K: eb.Q4_K, el.FFN_DOWN: eb.Q4_0}),
+])
+def test_batched_prompt_one_layer_is_bit_identical(be, port, cfg, types, monkeypatch):
+    """With one layer the logits after a prompt depend on the prompt only through the layer's K and V rows:
+    embedding, norm, quantization, the matrix products (tensor-core kernel for batches of 32 and more Q4_K
+    columns, multi-column mat-vec kernels below), RoPE and the f16 store.  Those are the same arithmetic per
+    token in the batched path, so the logits must be bit-identical to a token-by-token walk."""
+    cfg = dict(cfg, n_layer=1, n_ctx=192)
+    sess, cpu = build_model(be, port, cfg, types, seed=13)
+    cpu.close()
+    try:
+        prompt = synth.rng(17).integers(0, cfg["n_vocab"], size=151).tolist()
+        monkeypatch.setenv("EMELB_NO_BATCH_PREFILL", "1")
+        l0 = be.diagnostics()["kernel_launches"]
+        base = _prompt_then_logits(be, sess, prompt, [150])
+        launches_token = be.diagnostics()["kernel_launches"] - l0
+        monkeypatch.delenv("EMELB_NO_BATCH_PREFILL")
+        for batch, pieces in ((None, [150]), ("64", [150]), (None, [1, 2, 33, 100, 14]), ("40", [70, 80])):
+            if batch:
+                monkeypatch.setenv("EMELB_PREFILL_BATCH", batch)
+            # scrub the cache rows first so that stale rows of the previous walk cannot stand in for missing ones
+            junk = synth.rng(5).integers(0, cfg["n_vocab"], size=150).tolist()
+            assert sess.prefill(junk, 0)
+            l0 = be.diagnostics()["kernel_launches"]
+            got = _prompt_then_logits(be, sess, prompt, pieces)
+            launches = be.diagnostics()["kernel_launches"] - l0
+            monkeypatch.delenv("EMELB_PREFILL_BATCH", raising=False)
+            assert np.array_equal(got.view(np.uint32), base.view(np.uint32)), (batch, pieces, float(np.abs(got - base).max()))
+            assert launches < launches_token / 3
+    finally:
+        sess.close()
+
+
+@pytest.mark.parametrize("cfg,types", [
+    (TINY, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K}),
+    (MIXED, {"embd": eb.Q8_0, "output": eb.Q8_0, "default": eb.Q8_0, el.ATTN_K: eb.Q4_K, el.FFN_DOWN: eb.Q4_0}),
+])
+def test_batched_prompt_many_layers_within_attention_noise(be, port, cfg, types, monkeypatch):
+    """With more layers the prompt's attention outputs feed the next layer's int8 quantizers, where a
+    difference in the last bits flips roundings (the decoder is chaotic at that scale: the reference's own
+    routes drift apart the same way).  The batch attention kernel is held to 2e-5 of the exact softmax on its
+    own (test_gpu_attention_batch.py); here the batched walk must stay closer to the token-by-token walk
+    than the reference-order attention (f16 accumulators) does."""
+    cfg = dict(cfg, n_ctx=192)
+    sess, cpu = build_model(be, port, cfg, types, seed=13)
+    cpu.close()
+    try:
+        prompt = synth.rng(17).integers(0, cfg["n_vocab"], size=151).tolist()
+        monkeypatch.setenv("EMELB_NO_BATCH_PREFILL", "1")
+        base = _prompt_then_logits(be, sess, prompt, [150])
+        ref_order = _prompt_then_logits(be, sess, prompt, [150], mode=2)
+        monkeypatch.delenv("EMELB_NO_BATCH_PREFILL")
+        yard = _rel(ref_order, base)
+        for batch, pieces in ((None, [150]), ("64", [150]), (None, [1, 2, 33, 100, 14])):
+            if batch:
+                monkeypatch.setenv("EMELB_PREFILL_BATCH", batch)
+            got = _prompt_then_logits(be, sess, prompt, pieces)
+            monkeypatch.delenv("EMELB_PREFILL_BATCH", raising=False)
+            d = _rel(got, base)
+            print(pieces, "batched vs token-by-token %.2e, reference-order vs token-by-token %.2e" % (d, yard))
+            assert np.isfinite(got).all() and d <= yard and d <= 5e-2, (pieces, d, yard)
+    finally:
+        sess.close()

@@ -124,6 +124,7 @@ def test_reference_block_fixtures(be, checker, t, salt):
     (2048, 1, 1), (2048, 257, 1), (4096, 1000, 1),    # streaming kernel, ragged row counts
     (4096, 64, 2), (2048, 129, 3), (4096, 40, 8), (2048, 31, 13),
     (14336, 24, 2), (14336, 24, 4), (8192, 19, 7),    # long rows: column copies that fit / do not fit in shared memory
+    (2048, 2048, 12), (2048, 4096, 20), (4096, 2048, 16), (2048, 512, 20),   # column groups after the first, many CTAs
 ])
 def test_mul_mat_parity(be, checker, port, t, k, m, n):
     w = synth.encoded_weights(port, t, 100 + t, m, k)
