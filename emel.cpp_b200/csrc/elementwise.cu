@@ -238,31 +238,48 @@ __global__ void embed_rows_kernel(int type, const uint8_t* __restrict__ table, i
   dst[(int64_t)e * B + j] = embed_value(type, table + (int64_t)tokens[j] * row_bytes, e);
 }
 
-// 32 tokens per CTA (threadIdx.x), features strided over threadIdx.y
-__global__ void __launch_bounds__(1024)
-rms_norm_batch_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int K, int B, float* __restrict__ out) {
-  __shared__ double s_part[32][33];
-  __shared__ float s_scale[32];
+// rms_norm of a token batch in two launches that both fill the machine: (a) f64 sums of squares of one
+// feature slice per CTA row (blockIdx.y) for 32 tokens (threadIdx.x), written as partials [slice][token];
+// (b) every element scaled, each thread adding its token's partials in slice order.
+constexpr int kNormSlices = 16;
+
+__global__ void __launch_bounds__(256)
+rms_partial_batch_kernel(const float* __restrict__ x, int K, int B, double* __restrict__ partial) {
+  __shared__ double s_part[8][33];
   const int tx = threadIdx.x, ty = threadIdx.y, j = blockIdx.x * 32 + tx;
+  const int per = (K + kNormSlices - 1) / kNormSlices;
+  const int e0 = blockIdx.y * per, e1 = min(K, e0 + per);
   double acc = 0.0;
   if (j < B) {
-    for (int e = ty; e < K; e += blockDim.y) {
+    for (int e = e0 + ty; e < e1; e += 8) {
       const float v = x[(int64_t)e * B + j];
       acc += (double)__fmul_rn(v, v);
     }
   }
   s_part[ty][tx] = acc;
   __syncthreads();
-  if (ty == 0) {
+  if (ty == 0 && j < B) {
     double t = 0.0;
-    for (int i = 0; i < (int)blockDim.y; ++i) t += s_part[i][tx];
-    const float mean = (float)(t / (double)K);
-    s_scale[tx] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += s_part[i][tx];
+    partial[(int64_t)blockIdx.y * B + j] = t;
   }
-  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256)
+rms_apply_batch_kernel(const float* __restrict__ x, const float* __restrict__ w, const double* __restrict__ partial, float eps,
+                       int K, int B, float* __restrict__ out) {
+  const int j = blockIdx.x * 32 + threadIdx.x;
   if (j >= B) return;
-  const float scale = s_scale[tx];
-  for (int e = ty; e < K; e += blockDim.y) out[(int64_t)e * B + j] = __fmul_rn(__fmul_rn(x[(int64_t)e * B + j], scale), w[e]);
+  double t = 0.0;
+#pragma unroll
+  for (int i = 0; i < kNormSlices; ++i) t += partial[(int64_t)i * B + j];
+  const float mean = (float)(t / (double)K);
+  const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+  const int per = (K + gridDim.y - 1) / gridDim.y;
+  const int e0 = blockIdx.y * per, e1 = min(K, e0 + per);
+  for (int e = e0 + threadIdx.y; e < e1; e += blockDim.y)
+    out[(int64_t)e * B + j] = __fmul_rn(__fmul_rn(x[(int64_t)e * B + j], scale), w[e]);
 }
 
 // thread = (token j fastest, rotation pair or copied element, head)
@@ -364,10 +381,17 @@ cudaError_t launch_embed_rows(int type, const uint8_t* table, int64_t row_bytes,
   return cudaGetLastError();
 }
 
-cudaError_t launch_rms_norm_batch(const float* x, const float* w, float eps, int K, int B, float* out, cudaStream_t st) {
-  rms_norm_batch_kernel<<<(B + 31) / 32, dim3(32, 32), 0, st>>>(x, w, eps, K, B, out);
+cudaError_t launch_rms_norm_batch(const float* x, const float* w, float eps, int K, int B, float* out, double* partial,
+                                  cudaStream_t st) {
+  const int tiles = (B + 31) / 32;
+  rms_partial_batch_kernel<<<dim3(tiles, kNormSlices), dim3(32, 8), 0, st>>>(x, K, B, partial);
+  int slices = K / 64 > 0 ? K / 64 : 1;        // 64 features x 32 tokens per CTA
+  if (slices > 1024) slices = 1024;
+  rms_apply_batch_kernel<<<dim3(tiles, slices), dim3(32, 8), 0, st>>>(x, w, partial, eps, K, B, out);
   return cudaGetLastError();
 }
+
+int rms_norm_batch_partials(int B) { return kNormSlices * B; }
 
 cudaError_t launch_rope_store_batch(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t, int pos0,
                                     int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,

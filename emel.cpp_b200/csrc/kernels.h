@@ -122,7 +122,10 @@ cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, 
 // token batches (prompt processing): activations feature-major, element e of token j at x[e * B + j]
 cudaError_t launch_embed_rows(int type, const uint8_t* table, int64_t row_bytes, const int* tokens_dev, int B, float* dst,
                               int K, cudaStream_t st);
-cudaError_t launch_rms_norm_batch(const float* x, const float* w, float eps, int K, int B, float* out, cudaStream_t st);
+// partial: scratch of rms_norm_batch_partials(B) doubles
+cudaError_t launch_rms_norm_batch(const float* x, const float* w, float eps, int K, int B, float* out, double* partial,
+                                  cudaStream_t st);
+int rms_norm_batch_partials(int B);
 cudaError_t launch_rope_store_batch(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t, int pos0,
                                     int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,
                                     __half* vcache, int64_t cache_head_stride, cudaStream_t st);

@@ -72,6 +72,7 @@ struct emelb_llama {
   int* batch_tokens = nullptr;
   float *b_hidden = nullptr, *b_norm = nullptr, *b_q = nullptr, *b_k = nullptr, *b_v = nullptr, *b_attn = nullptr;
   float *b_gate = nullptr, *b_up = nullptr, *b_ffn = nullptr, *b_y = nullptr;
+  double* b_partial = nullptr;
   int fa_splits = 1;
   int G = 1, rank = 0;        // row sharding
   int* pair_buf = nullptr;    // G x 16-byte records {value bits, global row, -, -}: argmax candidates
@@ -337,7 +338,7 @@ struct Enqueue {
     for (int l = 0; l < c.n_layer; ++l) {
       const Layer& w = s->layers[l];
       const int64_t layer_off = (int64_t)l * c.n_head_kv * s->capacity * c.head_dim;
-      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, st));
+      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       ++launches;
       batch_matmul(w.wq, s->b_norm, s->b_q, B);
       batch_matmul(w.wk, s->b_norm, s->b_k, B);
@@ -351,7 +352,7 @@ struct Enqueue {
       ++launches;
       batch_matmul(w.wo, s->b_attn, s->b_y, B);
       check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
-      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.ffn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, st));
+      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.ffn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       batch_matmul(w.gate, s->b_norm, s->b_gate, B);
       batch_matmul(w.up, s->b_norm, s->b_up, B);
       check(launch_swiglu(s->b_gate, s->b_up, c.n_ff * B, s->b_ffn, 0, planes(), st));
@@ -728,6 +729,7 @@ bool reserve_batch(emelb_llama* s, int B) {
   ok = ok && dev_alloc(s, (void**)&s->b_k, 4 * b * kv_dim) && dev_alloc(s, (void**)&s->b_v, 4 * b * kv_dim);
   ok = ok && dev_alloc(s, (void**)&s->b_gate, 4 * b * c.n_ff) && dev_alloc(s, (void**)&s->b_up, 4 * b * c.n_ff);
   ok = ok && dev_alloc(s, (void**)&s->b_ffn, 4 * b * c.n_ff);
+  ok = ok && dev_alloc(s, (void**)&s->b_partial, sizeof(double) * (size_t)rms_norm_batch_partials(B));
   if (ok) s->batch_cap = B;
   return ok;
 }
