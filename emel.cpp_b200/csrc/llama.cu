@@ -119,6 +119,7 @@ struct Enqueue {
   cudaStream_t st;
   int launches = 0;
   bool ok = true;
+  int batch_family = 0;  // family the planes were last quantized for by batch_matmul
 
   void check(cudaError_t e) { ok = ok && ctx_cuda_ok(s->c, e); }
 
@@ -302,9 +303,13 @@ struct Enqueue {
   void gather(float* full, size_t count_per_rank) { gather_bytes(full, count_per_rank * sizeof(float)); }
 
   // y {w.M, B} = w x quantized(x {w.K, B}); the Q4_K products of 32 and more tokens run on the tensor cores
-  void batch_matmul(const Tensor& w, const float* x, float* y, int B) {
-    check(quantize_into_planes(w.type, x, B, B, w.K, planes(), st));
-    ++launches;
+  void batch_matmul(const Tensor& w, const float* x, float* y, int B, bool same_input = false) {
+    // same_input: the planes still hold x quantized for this family (the previous product read the same x)
+    if (!same_input || batch_family != family_of(w.type)) {
+      check(quantize_into_planes(w.type, x, B, B, w.K, planes(), st));
+      ++launches;
+      batch_family = family_of(w.type);
+    }
     GemvArgs a{};
     a.W = w.dev;
     a.row_bytes = w.row_bytes;
@@ -341,8 +346,8 @@ struct Enqueue {
       check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       ++launches;
       batch_matmul(w.wq, s->b_norm, s->b_q, B);
-      batch_matmul(w.wk, s->b_norm, s->b_k, B);
-      batch_matmul(w.wv, s->b_norm, s->b_v, B);
+      batch_matmul(w.wk, s->b_norm, s->b_k, B, true);
+      batch_matmul(w.wv, s->b_norm, s->b_v, B, true);
       check(launch_rope_store_batch(s->b_q, s->b_k, s->b_v, s->rope_cos, s->rope_sin, pos0, B, c.n_head, c.n_head_kv, c.head_dim,
                                     rot, c.rope_neox, s->kcache + layer_off, s->vcache + layer_off, s->capacity * c.head_dim, st));
       ++launches;
@@ -354,7 +359,7 @@ struct Enqueue {
       check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
       check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.ffn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       batch_matmul(w.gate, s->b_norm, s->b_gate, B);
-      batch_matmul(w.up, s->b_norm, s->b_up, B);
+      batch_matmul(w.up, s->b_norm, s->b_up, B, true);
       check(launch_swiglu(s->b_gate, s->b_up, c.n_ff * B, s->b_ffn, 0, planes(), st));
       batch_matmul(w.down, s->b_ffn, s->b_y, B);
       check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));

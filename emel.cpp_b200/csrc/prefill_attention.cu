@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -172,13 +173,209 @@ __global__ void __launch_bounds__(kThreads) prefill_attention_kernel(const Prefi
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// The same computation on the tensor cores (mma.sync m16n8k16, f16 operands, f32 accumulators).  Scores are
+// exact products of f16 values either way.  The softmax weights stay f32-accurate: each weight p is fed as
+// two f16 operands, hi = f16(p) and lo = f16(p - hi), in two MMAs against the f16 V tile, so the only
+// rounding left is the f32 accumulation (the 2e-5 bar of the fast attention holds).
+// One warp = 16 query rows; lane = 4g + t.  Fragments (PTX ISA, m16n8k16):
+//   A: a0 (row g, k 2t..2t+1)  a1 (row g+8, same k)  a2 (row g, k 2t+8..)  a3 (row g+8, k 2t+8..)
+//   B: b0 (k 2t..2t+1, n g)    b1 (k 2t+8.., n g)
+//   C: c0,c1 (row g, n 2t..2t+1)   c2,c3 (row g+8, n 2t..2t+1)
+// so two adjacent score tiles (8 positions each) are, packed to f16, the A fragment of the P.V product.
+constexpr int kMmaThreads = 128;
+
+template <int D>
+struct PrefillMmaSmem {
+  static constexpr int kRowStride = D + 8;     // halves; 4g + t banks for the fragment loads
+  static constexpr int kVtStride = kKT + 8;
+  __half q[kRows][kRowStride];
+  __half k[kKT][kRowStride];
+  __half vt[D][kVtStride];                     // V tile transposed: [dim][position]
+};
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kMmaThreads) prefill_attention_mma_kernel(const PrefillAttnArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  PrefillMmaSmem<D>& sm = *reinterpret_cast<PrefillMmaSmem<D>*>(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int n_rep = a.heads / a.kv_heads, QT = kRows / n_rep;
+  const int kh = blockIdx.y, j0 = blockIdx.x * QT, B = a.B;
+
+  for (int idx = tid; idx < kRows * D; idx += kMmaThreads) {
+    const int jt = idx % QT, d = (idx / QT) % D, rep = idx / (QT * D);
+    const int j = j0 + jt;
+    float val = 0.0f;
+    if (j < B) val = a.q[((int64_t)(kh * n_rep + rep) * D + d) * B + j];
+    sm.q[rep * QT + jt][d] = __float2half_rn(val);
+  }
+  __syncthreads();
+
+  // this warp's query fragments, kept in registers for the whole walk
+  const int r0 = warp * 16 + g, r1 = r0 + 8;
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    qf[kk][0] = *reinterpret_cast<const uint32_t*>(&sm.q[r0][kk * 16 + 2 * t]);
+    qf[kk][1] = *reinterpret_cast<const uint32_t*>(&sm.q[r1][kk * 16 + 2 * t]);
+    qf[kk][2] = *reinterpret_cast<const uint32_t*>(&sm.q[r0][kk * 16 + 2 * t + 8]);
+    qf[kk][3] = *reinterpret_cast<const uint32_t*>(&sm.q[r1][kk * 16 + 2 * t + 8]);
+  }
+  int t_row[2];
+  {
+    const int ja = j0 + r0 % QT, jb = j0 + r1 % QT;
+    t_row[0] = ja < B ? a.pos0 + ja + 1 : 0;
+    t_row[1] = jb < B ? a.pos0 + jb + 1 : 0;
+  }
+  const int j_last = min(B, j0 + QT) - 1;
+  const int t_cta = a.pos0 + j_last + 1;
+  const int t_written = a.pos0 + B;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int dn = 0; dn < D / 8; ++dn)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[dn][i] = 0.0f;
+  const __half* kbase = a.k + (int64_t)kh * a.cache_head_stride;
+  const __half* vbase = a.v + (int64_t)kh * a.cache_head_stride;
+
+  for (int t0 = 0; t0 < t_cta; t0 += kKT) {
+    __syncthreads();  // the previous tile's readers are done
+    for (int idx = tid; idx < kKT * (D / 8); idx += kMmaThreads) {
+      const int tt = idx / (D / 8), c = idx % (D / 8);
+      uint4 kk = make_uint4(0u, 0u, 0u, 0u), vv = kk;
+      if (t0 + tt < t_written) {
+        kk = *reinterpret_cast<const uint4*>(kbase + (int64_t)(t0 + tt) * D + 8 * c);
+        vv = *reinterpret_cast<const uint4*>(vbase + (int64_t)(t0 + tt) * D + 8 * c);
+      }
+      *reinterpret_cast<uint4*>(&sm.k[tt][8 * c]) = kk;
+      const __half* vh = reinterpret_cast<const __half*>(&vv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sm.vt[8 * c + i][tt] = vh[i];
+    }
+    __syncthreads();
+
+    // scores of 16 rows x 64 positions
+    float s[kKT / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < kKT / 8; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[nt][i] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.k[nt * 8 + g][kk * 16 + 2 * t]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.k[nt * 8 + g][kk * 16 + 2 * t + 8]);
+        mma_f16(s[nt], qf[kk], b0, b1);
+      }
+    }
+
+    // online softmax: thread holds rows r0 (values 0,1) and r1 (values 2,3); 4 lanes share a row
+    float keep[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < kKT / 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const bool live = t0 + nt * 8 + 2 * t + i < t_row[h];
+          float& v = s[nt][2 * h + i];
+          v = live ? v * a.scale : -INFINITY;
+          mx = fmaxf(mx, v);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m[h], mx);
+      keep[h] = m_new == -INFINITY ? 1.0f : expf(m[h] - m_new);
+      float sum = 0.0f;
+#pragma unroll
+      for (int nt = 0; nt < kKT / 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          float& v = s[nt][2 * h + i];
+          v = v == -INFINITY ? 0.0f : expf(v - m_new);
+          sum += v;
+        }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l[h] = l[h] * keep[h] + sum;
+      m[h] = m_new;
+    }
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn) {
+      o[dn][0] *= keep[0];
+      o[dn][1] *= keep[0];
+      o[dn][2] *= keep[1];
+      o[dn][3] *= keep[1];
+    }
+
+    // O += P V, 16 positions per step, weights as hi + lo
+#pragma unroll
+    for (int jj = 0; jj < kKT / 16; ++jj) {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {        // score tiles 2jj and 2jj + 1
+        const float* p = s[2 * jj + part];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const __half2 ph = __floats2half2_rn(p[2 * h], p[2 * h + 1]);
+          const float2 back = __half22float2(ph);
+          hi[2 * part + h] = *reinterpret_cast<const uint32_t*>(&ph);
+          lo[2 * part + h] = pack_half2(p[2 * h] - back.x, p[2 * h + 1] - back.y);
+        }
+      }
+#pragma unroll
+      for (int dn = 0; dn < D / 8; ++dn) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.vt[dn * 8 + g][jj * 16 + 2 * t]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.vt[dn * 8 + g][jj * 16 + 2 * t + 8]);
+        mma_f16(o[dn], hi, b0, b1);
+        mma_f16(o[dn], lo, b0, b1);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = h == 0 ? r0 : r1, rep = row / QT, j = j0 + row % QT;
+    if (j >= B) continue;
+    const float inv = l[h] > 0.0f ? 1.0f / l[h] : 0.0f;
+    float* out = a.dst + ((int64_t)(kh * n_rep + rep) * D) * B + j;
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn) {
+      out[(int64_t)(dn * 8 + 2 * t) * B] = o[dn][2 * h] * inv;
+      out[(int64_t)(dn * 8 + 2 * t + 1) * B] = o[dn][2 * h + 1] * inv;
+    }
+  }
+}
+
 template <int D>
 cudaError_t launch_d(const PrefillAttnArgs& a, cudaStream_t st) {
+  const int n_rep = a.heads / a.kv_heads, QT = kRows / n_rep;
+  const dim3 grid((a.B + QT - 1) / QT, a.kv_heads);
+  if (getenv("EMELB_PREFILL_ATTN_SIMT") == nullptr) {
+    const int smem = (int)sizeof(PrefillMmaSmem<D>);
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    prefill_attention_mma_kernel<D><<<grid, kMmaThreads, smem, st>>>(a);
+    return cudaGetLastError();
+  }
   const int smem = (int)sizeof(PrefillSmem<D>);
   cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  const int n_rep = a.heads / a.kv_heads, QT = kRows / n_rep;
-  prefill_attention_kernel<D><<<dim3((a.B + QT - 1) / QT, a.kv_heads), kThreads, smem, st>>>(a);
+  prefill_attention_kernel<D><<<grid, kThreads, smem, st>>>(a);
   return cudaGetLastError();
 }
 
