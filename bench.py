@@ -871,7 +871,7 @@ def run_decode(args):
                    "prefill_s": "skipped: zero-filled KV cache, profiling aid, not a benchmark number" if args.profile_skip_prefill
                    else round(prefill_s, 3),
                    "prefill_tok_s": None if prefill_warm_s is None else round((prompt_len - 1) / prefill_warm_s, 1),
-                   "prefill": "prompt tokens in batches of 512: tensor-core Q4_K products, batch attention kernel" if not shard
+                   "prefill": "prompt tokens in batches of up to 2048: tcgen05 Q4_K products, mma.sync batch attention" if not shard
                    else "token by token (sharded sessions)"},
         "hbm_gbs_effective": round(bytes_per_token * tok_s / seqs / 1e9, 1),
         "q4_k_gemv_hbm_gbs": round(kernel_gbs, 1), "pct_of_8tbs_nominal": round(100 * kernel_gbs / NOMINAL_HBM_GBS, 2),

@@ -715,7 +715,7 @@ int prefill_batch_size(emelb_llama* s, int n) {
   if (!prefill_attention_supported(pa)) return 0;
   int widest = c.n_ff > c.n_embd ? c.n_ff : c.n_embd;
   if (c.n_head * c.head_dim > widest) widest = c.n_head * c.head_dim;
-  int cap = 512;
+  int cap = 2048;  // 64 to 224 weight-row x token tiles per product at the 8B shape: the tensor-core kernel's grid fills
   if (const char* e = getenv("EMELB_PREFILL_BATCH")) cap = atoi(e);
   const int64_t fits = (int64_t)(s->c->act_capacity / (uint64_t)widest);
   if (cap > fits) cap = (int)fits;
