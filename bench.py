@@ -255,6 +255,18 @@ def run_gemv(args):
                      "traffic": ncu_traffic(kname)},
         "clocks": clocks,
     }
+    flops = 2.0 * m * k * n
+    if flops / sp["alg_bytes"] > peaks["bf16_tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9):
+        # past the ridge point the product is bound by the tensor pipe, not by HBM (configuration 2 at 512 tokens)
+        tf = flops / (ms_k * 1e-3 / launches) / 1e12
+        line["dtype"] = "int8 mma.sync (one 32-weight block per instruction) + f32 scales"
+        line["roofline"] = {"bound": "tensor", "kernel": f"gemm_q8_mma_n{n}", "achieved": round(tf, 2), "peak": peaks["bf16_tflops"],
+                            "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops"], 4),
+                            "peak_source": f"of {peak_kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms_k * 1e3 / launches, 3),
+                            "flops_per_launch": flops, "traffic": None}
+    elif n >= 32 and t == eb.Q8_0:
+        line["dtype"] = "int8 mma.sync (one 32-weight block per instruction) + f32 scales"
+        line["roofline"]["kernel"] = f"gemm_q8_mma_n{n}"
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline_gemv(be, sp, wdev, x_host.numpy().copy(), budget_s=args.cpu_budget)
         print(json.dumps(line), flush=True)

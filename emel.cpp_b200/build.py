@@ -24,6 +24,7 @@ SOURCES = {
     "attention.cu": [],
     "prefill_attention.cu": [],
     "gemm_tc.cu": [],
+    "gemm_q8_mma.cu": [],
     "llama.cu": [],
     "comm.cu": [],
     "noalloc.cu": [],

@@ -737,6 +737,11 @@ bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K) {
 
 cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
                         int* launches) {
+  // many columns of Q8_0 / Q4_0: one tensor-core instruction per 32-weight block (gemm_q8_mma.cu)
+  if (!argmax && gemm_q8_mma_supported(type, a, ncols)) {
+    ++*launches;
+    return launch_gemm_q8_mma(type, a, ncols, st);
+  }
   // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
   static const bool no_tc = getenv("EMELB_NO_TC") != nullptr;
   if (!argmax && !no_tc && a.tc_ws && gemm_tc_supported(type, a.K, ncols, a.W, a.row_bytes, a.act) &&

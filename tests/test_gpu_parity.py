@@ -133,6 +133,22 @@ def test_mul_mat_parity(be, checker, port, t, k, m, n):
     assert_mul_mat_parity(got, want, checker, t)
 
 
+@pytest.mark.parametrize("t", [eb.Q8_0, eb.Q4_0])
+@pytest.mark.parametrize("k,m,n", [
+    (256, 128, 32), (512, 5, 33), (1024, 300, 130), (2048, 129, 257), (4096, 260, 64), (1280, 384, 200), (14336, 150, 70),
+])
+def test_mul_mat_many_columns_block32_tensor_core_kernel(be, checker, port, t, k, m, n):
+    """32 or more columns of Q8_0 / Q4_0 take the mma.sync kernel (one 32-weight block per instruction, scales
+    applied block by block in order): ragged tiles in both directions and the same bits as the mat-vec route."""
+    w = synth.encoded_weights(port, t, 500 + m, m, k)
+    x = synth.activations_f32(600 + n, k, n)
+    got, want = gpu_mul_mat(be, t, w, k, m, x, n), cpu_mul_mat(checker, t, w, k, m, x, n)
+    assert_mul_mat_parity(got, want, checker, t)
+    x8 = np.ascontiguousarray(x.reshape(k, n)[:, :8])
+    got8 = gpu_mul_mat(be, t, w, k, m, x8, 8)
+    assert np.array_equal(got.reshape(m, n)[:, :8].view(np.uint32), got8.view(np.uint32))
+
+
 @pytest.mark.parametrize("k,m,n", [
     (256, 128, 32), (512, 5, 33), (1024, 300, 130), (2048, 129, 257), (4096, 260, 64), (1280, 384, 200),
 ])
