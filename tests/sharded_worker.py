@@ -86,6 +86,9 @@ def main():
 
     prompt = np.random.Generator(np.random.PCG64(7)).integers(0, CFG["n_vocab"], size=9).tolist()
     results = {}
+    # sharded sessions walk the prompt token by token; the unsharded one is held to the same walk here so that
+    # the comparison is about sharding alone (the batched prompt path has its own tests)
+    os.environ["EMELB_NO_BATCH_PREFILL"] = "1"
     for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world), ("shard-peer", be_shard, rank, world)):
         for mode in (2, 0):
             be.set_attention_mode(mode)
