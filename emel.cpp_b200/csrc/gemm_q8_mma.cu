@@ -8,7 +8,9 @@
 // kernel, not the MMAs; a tcgen05 tile would only move the same scaling work behind a TMEM load.
 //
 // One CTA = 128 weight rows x 64 activation columns, 8 warps of 16 rows each; K is walked in chunks of 8
-// blocks staged in shared memory as plain int8 rows (Q4_0 nibbles are widened to value - 8 while staging).
+// blocks through a two-stage cp.async ring.  Weight rows are staged as they lie in memory (scale + quants,
+// 34 or 18 bytes per block) and the A fragments are read from there with 2-byte loads (Q4_0 nibbles are
+// widened to value - 8 in registers), so staging is pure asynchronous copying.
 // Fragments (PTX ISA, m16n8k32, lane = 4g + t):
 //   A: a0 (row g, k 4t..4t+3)  a1 (row g+8, same k)  a2 (row g, k 16+4t..)  a3 (row g+8, k 16+4t..)
 //   B: b0 (k 4t..4t+3, col g)  b1 (k 16+4t.., col g)
@@ -25,11 +27,17 @@ namespace {
 constexpr int kTM = 128, kTN = 64, kChunkBlocks = 8, kChunk = kChunkBlocks * QK32;
 constexpr int kRowStride = kChunk + 16;  // bytes: fragment loads of 8 rows x 4 lanes hit 32 distinct banks
 constexpr int kThreadsQ8 = 256;
+constexpr int kStagesQ8 = 2;
 
-struct Q8Smem {
-  int8_t a[kTM][kRowStride];
+// One stage of the ring: the weight rows as they lie in memory (8 blocks = 272 B of Q8_0 or 144 B of Q4_0 per
+// row, copied 16 bytes at a time by cp.async; both row strides put 8 rows x 4 lanes on distinct banks), the
+// activation rows and their block scales.
+template <int T>
+struct Q8Stage {
+  static constexpr int kBB = T == T_Q8_0 ? Q8_0_BYTES : Q4_0_BYTES;
+  static constexpr int kRaw = kChunkBlocks * kBB;
+  uint8_t a[kTM][kRaw];
   int8_t b[kTN][kRowStride];
-  float dw[kTM][kChunkBlocks];
   float dx[kTN][kChunkBlocks];
 };
 
@@ -39,15 +47,43 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t ld16u(const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8); }
+// 4 bytes at a 2-byte aligned shared-memory address
+__device__ __forceinline__ uint32_t lds32_h(const uint8_t* p) {
+  const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
+  return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+}
+// per byte: nibble value (0..15) - 8 as int8
+__device__ __forceinline__ uint32_t nibbles_minus_8(uint32_t v) { return ((v | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
 template <int T>
 __global__ void __launch_bounds__(kThreadsQ8, 2) gemm_q8_mma_kernel(const GemvArgs p, int ncols) {
+  using Stage = Q8Stage<T>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  Q8Smem& sm = *reinterpret_cast<Q8Smem*>(smem_raw);
-  constexpr int BB = T == T_Q8_0 ? Q8_0_BYTES : Q4_0_BYTES;
+  Stage* stages = reinterpret_cast<Stage*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * kTM, c0 = blockIdx.y * kTN;
+  const int chunks = p.K / kChunk;
+
+  // rows and columns past the edge are read from the last valid one (their results are never stored)
+  auto issue = [&](int kc, Stage& st) {
+    constexpr int kPieces = Stage::kRaw / 16;
+    for (int idx = tid; idx < kTM * kPieces; idx += kThreadsQ8) {
+      const int r = idx / kPieces, piece = idx % kPieces;
+      const int row = min(row0 + r, p.M - 1);
+      cp_async16(&st.a[r][16 * piece], p.W + (int64_t)row * p.row_bytes + (int64_t)kc * Stage::kRaw + 16 * piece);
+    }
+    for (int idx = tid; idx < kTN * (kChunk / 16); idx += kThreadsQ8) {
+      const int c = idx / (kChunk / 16), piece = idx % (kChunk / 16);
+      const int col = p.col0 + min(c0 + c, ncols - 1);
+      cp_async16(&st.b[c][16 * piece], p.act.qs + (int64_t)col * p.act.col_stride_qs + (int64_t)kc * kChunk + 16 * piece);
+    }
+    for (int idx = tid; idx < kTN * 2; idx += kThreadsQ8) {
+      const int c = idx >> 1, half = idx & 1;
+      const int col = p.col0 + min(c0 + c, ncols - 1);
+      cp_async16(&st.dx[c][4 * half], p.act.d + (int64_t)col * p.act.col_stride_d + kc * kChunkBlocks + 4 * half);
+    }
+    cp_async_commit();
+  };
 
   float acc[kTN / 8][4];
 #pragma unroll
@@ -55,95 +91,68 @@ __global__ void __launch_bounds__(kThreadsQ8, 2) gemm_q8_mma_kernel(const GemvAr
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
 
-  for (int kc = 0; kc < p.K / kChunk; ++kc) {
-    __syncthreads();  // the previous chunk's readers are done
-    // weights: one (row, block) per thread and pass
-    for (int idx = tid; idx < kTM * kChunkBlocks; idx += kThreadsQ8) {
-      const int r = idx / kChunkBlocks, b = idx % kChunkBlocks;
-      uint32_t w[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-      float d = 0.0f;
-      if (row0 + r < p.M) {
-        const uint8_t* src = p.W + (int64_t)(row0 + r) * p.row_bytes + (int64_t)(kc * kChunkBlocks + b) * BB;
-        d = h2f((uint16_t)ld16u(src));
-        if constexpr (T == T_Q8_0) {
-          // 32 int8 values at a 2-byte aligned address
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint16_t* h = reinterpret_cast<const uint16_t*>(src + 2 + 4 * i);
-            w[i] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
-          }
-        } else {
-          // 16 bytes: low nibbles = values 0..15, high nibbles = values 16..31, each minus 8
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint16_t* h = reinterpret_cast<const uint16_t*>(src + 2 + 4 * i);
-            const uint32_t q = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
-            const uint32_t lo = q & 0x0f0f0f0fu, hi = (q >> 4) & 0x0f0f0f0fu;
-            // per byte: value - 8 in two's complement (values 0..15, no borrow across bytes after the bias trick)
-            w[i] = ((lo | 0x80808080u) - 0x08080808u) ^ 0x80808080u;
-            w[4 + i] = ((hi | 0x80808080u) - 0x08080808u) ^ 0x80808080u;
-          }
-        }
-      }
-      uint4* dst = reinterpret_cast<uint4*>(&sm.a[r][b * QK32]);
-      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-      sm.dw[r][b] = d;
-    }
-    // activations: 16 bytes per thread and pass
-    for (int idx = tid; idx < kTN * (kChunk / 16); idx += kThreadsQ8) {
-      const int c = idx / (kChunk / 16), piece = idx % (kChunk / 16);
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (c0 + c < ncols)
-        v = *reinterpret_cast<const uint4*>(p.act.qs + (int64_t)(p.col0 + c0 + c) * p.act.col_stride_qs + (int64_t)kc * kChunk + 16 * piece);
-      *reinterpret_cast<uint4*>(&sm.b[c][16 * piece]) = v;
-    }
-    for (int idx = tid; idx < kTN * kChunkBlocks; idx += kThreadsQ8) {
-      const int c = idx / kChunkBlocks, b = idx % kChunkBlocks;
-      sm.dx[c][b] = c0 + c < ncols ? p.act.d[(int64_t)(p.col0 + c0 + c) * p.act.col_stride_d + kc * kChunkBlocks + b] : 0.0f;
+  issue(0, stages[0]);
+  const int ra = warp * 16 + g, rb = ra + 8;
+  for (int kc = 0; kc < chunks; ++kc) {
+    if (kc + 1 < chunks) {
+      issue(kc + 1, stages[(kc + 1) % kStagesQ8]);   // that buffer's readers finished before the barrier below (last turn)
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
-
-    const int ra = warp * 16 + g, rb = ra + 8;
+    const Stage& st = stages[kc % kStagesQ8];
 #pragma unroll
     for (int b = 0; b < kChunkBlocks; ++b) {
+      const uint8_t* ba = &st.a[ra][b * Stage::kBB];
+      const uint8_t* bb = &st.a[rb][b * Stage::kBB];
+      const float dwa = h2f(*reinterpret_cast<const uint16_t*>(ba)), dwb = h2f(*reinterpret_cast<const uint16_t*>(bb));
       uint32_t af[4];
-      af[0] = *reinterpret_cast<const uint32_t*>(&sm.a[ra][b * QK32 + 4 * t]);
-      af[1] = *reinterpret_cast<const uint32_t*>(&sm.a[rb][b * QK32 + 4 * t]);
-      af[2] = *reinterpret_cast<const uint32_t*>(&sm.a[ra][b * QK32 + 16 + 4 * t]);
-      af[3] = *reinterpret_cast<const uint32_t*>(&sm.a[rb][b * QK32 + 16 + 4 * t]);
-      const float dwa = sm.dw[ra][b], dwb = sm.dw[rb][b];
+      if constexpr (T == T_Q8_0) {
+        af[0] = lds32_h(ba + 2 + 4 * t);
+        af[1] = lds32_h(bb + 2 + 4 * t);
+        af[2] = lds32_h(ba + 2 + 16 + 4 * t);
+        af[3] = lds32_h(bb + 2 + 16 + 4 * t);
+      } else {
+        // bytes 4t..4t+3 of the block: low nibbles = values 4t.., high nibbles = values 16+4t..
+        const uint32_t qa = lds32_h(ba + 2 + 4 * t), qb = lds32_h(bb + 2 + 4 * t);
+        af[0] = nibbles_minus_8(qa & 0x0f0f0f0fu);
+        af[1] = nibbles_minus_8(qb & 0x0f0f0f0fu);
+        af[2] = nibbles_minus_8((qa >> 4) & 0x0f0f0f0fu);
+        af[3] = nibbles_minus_8((qb >> 4) & 0x0f0f0f0fu);
+      }
 #pragma unroll
       for (int nt = 0; nt < kTN / 8; ++nt) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.b[nt * 8 + g][b * QK32 + 4 * t]);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.b[nt * 8 + g][b * QK32 + 16 + 4 * t]);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&st.b[nt * 8 + g][b * QK32 + 4 * t]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&st.b[nt * 8 + g][b * QK32 + 16 + 4 * t]);
         int c[4] = {0, 0, 0, 0};
         mma_s8(c, af, b0, b1);
-        const float dx0 = sm.dx[nt * 8 + 2 * t][b], dx1 = sm.dx[nt * 8 + 2 * t + 1][b];
+        const float dx0 = st.dx[nt * 8 + 2 * t][b], dx1 = st.dx[nt * 8 + 2 * t + 1][b];
         acc[nt][0] = __fadd_rn(acc[nt][0], __fmul_rn((float)c[0], __fmul_rn(dwa, dx0)));
         acc[nt][1] = __fadd_rn(acc[nt][1], __fmul_rn((float)c[1], __fmul_rn(dwa, dx1)));
         acc[nt][2] = __fadd_rn(acc[nt][2], __fmul_rn((float)c[2], __fmul_rn(dwb, dx0)));
         acc[nt][3] = __fadd_rn(acc[nt][3], __fmul_rn((float)c[3], __fmul_rn(dwb, dx1)));
       }
     }
+    __syncthreads();  // this stage is free for the copy issued two turns from now
   }
 
-  const int ra = row0 + warp * 16 + g, rb = ra + 8;
+  const int ya = row0 + ra, yb = row0 + rb;
 #pragma unroll
   for (int nt = 0; nt < kTN / 8; ++nt) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int c = c0 + nt * 8 + 2 * t + i;
       if (c >= ncols) continue;
-      if (ra < p.M) p.y[(int64_t)ra * p.ldy + p.col0 + c] = acc[nt][i];
-      if (rb < p.M) p.y[(int64_t)rb * p.ldy + p.col0 + c] = acc[nt][2 + i];
+      if (ya < p.M) p.y[(int64_t)ya * p.ldy + p.col0 + c] = acc[nt][i];
+      if (yb < p.M) p.y[(int64_t)yb * p.ldy + p.col0 + c] = acc[nt][2 + i];
     }
   }
 }
 
 template <int T>
 cudaError_t launch_t(const GemvArgs& a, int ncols, cudaStream_t st) {
-  const int smem = (int)sizeof(Q8Smem);
+  const int smem = (int)(kStagesQ8 * sizeof(Q8Stage<T>));
   cudaError_t e = cudaFuncSetAttribute(gemm_q8_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   gemm_q8_mma_kernel<T><<<dim3((a.M + kTM - 1) / kTM, (ncols + kTN - 1) / kTN), kThreadsQ8, smem, st>>>(a, ncols);
@@ -155,8 +164,8 @@ cudaError_t launch_t(const GemvArgs& a, int ncols, cudaStream_t st) {
 bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols) {
   if (type != T_Q8_0 && type != T_Q4_0) return false;
   if (ncols < kGemmTcMinCols || a.K % kChunk != 0 || a.residual || a.W2 || a.W3 || a.pro_x || a.rope_cos) return false;
-  return reinterpret_cast<uintptr_t>(a.W) % 2 == 0 && a.row_bytes % 2 == 0 && reinterpret_cast<uintptr_t>(a.act.qs) % 16 == 0 &&
-         a.act.col_stride_qs % 16 == 0 && getenv("EMELB_NO_Q8_MMA") == nullptr;
+  return reinterpret_cast<uintptr_t>(a.W) % 16 == 0 && a.row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.qs) % 16 == 0 &&
+         a.act.col_stride_qs % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.d) % 16 == 0 && getenv("EMELB_NO_Q8_MMA") == nullptr;
 }
 
 cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, cudaStream_t st) {
