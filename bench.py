@@ -780,7 +780,7 @@ def run_decode(args):
             weight_bytes += nbytes
             if t == eb.Q4_K and layer >= 0:
                 q4k_bytes += nbytes
-                q4k_ops.append((d, t, k, m))
+                q4k_ops.append((layer, role, d, t, k, m))
     ones = be.alloc(4 * sh["n_embd"])
     assert be.to_device(ones, np.ones(sh["n_embd"], np.float32))
     assert sess.bind_norm(-1, el.OUTPUT_NORM, ones)
@@ -835,20 +835,36 @@ def run_decode(args):
         # the dominant kernel alone: every Q4_K layer matrix of one token, activations already quantized
         x8 = be.alloc(4 * sh["n_ff"])
         assert be.synth_fill(x8, eb.F32, sh["n_ff"], 9, 1.0, 0)
-        ybuf = be.alloc(4 * max(sh["n_ff"], sh["n_embd"]))
+        # launched the way the decode step launches them: Q, K, V of a layer in one launch, gate and up in one
+        # launch (emelb_mul_mat_prepared_group), Wo and down on their own
+        ybuf = be.alloc(4 * (2 * sh["n_ff"] + 2 * sh["n_embd"]))
         by_k = {}
-        for d, t, k, m in q4k_ops:
-            by_k.setdefault(k, []).append(eb.mul_mat_op(d, t, k, m, x8, 1, ybuf))
+        per_layer = {}
+        for layer, role, d, t, k, m in q4k_ops:
+            per_layer.setdefault(layer, {})[role] = (d, t, k, m)
+        for layer in sorted(per_layer):
+            roles = per_layer[layer]
+            for group in ((el.ATTN_Q, el.ATTN_K, el.ATTN_V), (el.ATTN_OUT,), (el.FFN_GATE, el.FFN_UP), (el.FFN_DOWN,)):
+                ops, off = [], 0
+                for role in group:
+                    d, t, k, m = roles[role]
+                    ops.append(eb.mul_mat_op(d, t, k, m, x8, 1, ybuf + 4 * off))
+                    off += m
+                by_k.setdefault(roles[group[0]][2], []).append(ops)
         graphs = []
-        for k, ops in by_k.items():
+
+        def run_group(ops):
+            assert (be.mul_mat_prepared(ops[0]) if len(ops) == 1 else be.mul_mat_prepared_group(ops)), be.last_error
+
+        for k, groups in by_k.items():
             assert be.prepare_rhs(eb.dense_view(x8, eb.F32, [1, k]), eb.Q4_K)
-            for op in ops[:2]:
-                assert be.mul_mat_prepared(op)
+            for ops in groups[:4]:
+                run_group(ops)
             be.sync()
             assert be.graph_begin()
-            for op in ops:
-                assert be.mul_mat_prepared(op)
-            graphs.append((k, be.graph_end(), len(ops)))
+            for ops in groups:
+                run_group(ops)
+            graphs.append((k, be.graph_end(), len(groups)))
         ms_k, n_k = 0.0, 0
         for k, g, n_ops in graphs:
             assert be.prepare_rhs(eb.dense_view(x8, eb.F32, [1, k]), eb.Q4_K)

@@ -92,6 +92,7 @@ _SIGNATURES = {
     "emelb_synth_fill": [_P, _P, C.c_int32, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64],
     "emelb_comm_unique_id": [_P, C.c_uint64],
     "emelb_comm_init": [_P, C.c_int32, C.c_int32, _P, C.c_uint64],
+    "emelb_mul_mat_prepared_group": [_P, C.POINTER(Op), C.c_uint32],
     "emelb_flash_attn_batch": [_P, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_float],
     "emelb_comm_destroy": [_P],
     "emelb_all_gather_rows": [_P, _P, C.c_uint64, C.c_uint64],
@@ -292,6 +293,11 @@ class Backend:
 
     def mul_mat_prepared(self, op: Op) -> bool:
         return self._ret(lib().emelb_mul_mat_prepared(self._h, C.byref(op)))
+
+    def mul_mat_prepared_group(self, ops) -> bool:
+        """Several products against the prepared column; one launch when the grouped kernel takes them."""
+        arr = (Op * len(ops))(*ops)
+        return self._ret(lib().emelb_mul_mat_prepared_group(self._h, arr, len(ops)))
 
     def flash_attn_ext(self, op: Op) -> bool:
         return self._ret(lib().emelb_flash_attn_ext(self._h, C.byref(op)))

@@ -614,6 +614,56 @@ uint32_t emelb_mul_mat(emelb_ctx* c, const emelb_op* op) { return run_mul_mat(c,
 uint32_t emelb_mul_mat_argmax(emelb_ctx* c, const emelb_op* op) { return run_mul_mat(c, op, true, false); }
 uint32_t emelb_mul_mat_prepared(emelb_ctx* c, const emelb_op* op) { return run_mul_mat(c, op, false, true); }
 
+// two or three products against the same prepared column in one launch (what the decoder does for Q, K, V and
+// for gate, up); anything the grouped launch does not take runs as `count` single products, same results
+uint32_t emelb_mul_mat_prepared_group(emelb_ctx* c, const emelb_op* ops, uint32_t count) {
+  if (!c || !ops || count == 0) return EMELB_INVALID_REQUEST;
+  bool group = count >= 2 && count <= 3 && getenv("EMELB_GEMV_V1") == nullptr;
+  const uint8_t* W[3] = {nullptr, nullptr, nullptr};
+  for (uint32_t i = 0; group && i < count; ++i) {
+    const emelb_op& o = ops[i];
+    group = can_run_mul_mat(o) && o.src1.type == T_F32 && o.src1.ne[0] == 1 && o.src0.type == ops[0].src0.type &&
+            o.src0.ne[0] == ops[0].src0.ne[0] && o.src0.nb[1] == ops[0].src0.nb[1] && c->prepared_n == 1 &&
+            c->prepared_k == o.src0.ne[0] && c->prepared_k_family == is_k_type(o.src0.type) &&
+            classify(c, o.dst.data) == Where::device;
+    if (group) W[i] = static_cast<const uint8_t*>(resolve_weights(c, o.src0.data));
+    group = group && W[i] && gemv_fast_path_ok(o.src0.type, W[i], (int64_t)o.src0.nb[1], (int)o.src0.ne[0]);
+  }
+  if (!group) {
+    for (uint32_t i = 0; i < count; ++i) {
+      const uint32_t err = run_mul_mat(c, &ops[i], false, true);
+      if (err != EMELB_OK) return err;
+    }
+    return EMELB_OK;
+  }
+  cudaSetDevice(c->device);
+  const int t = ops[0].src0.type, K = (int)ops[0].src0.ne[0];
+  GemvArgs a{};
+  a.W = W[0];
+  a.row_bytes = (int64_t)ops[0].src0.nb[1];
+  a.M = (int)ops[0].src0.ne[1];
+  a.K = K;
+  a.act = planes_view(ctx_planes(c), t, K);
+  a.y = static_cast<float*>(const_cast<void*>(ops[0].dst.data));
+  a.ldy = 1;
+  a.W2 = W[1];
+  a.M2 = (int)ops[1].src0.ne[1];
+  a.y2 = static_cast<float*>(const_cast<void*>(ops[1].dst.data));
+  if (count == 3) {
+    a.W3 = W[2];
+    a.M3 = (int)ops[2].src0.ne[1];
+    a.y3 = static_cast<float*>(const_cast<void*>(ops[2].dst.data));
+  }
+  a.pdl = c->pdl & 1;
+  a.sched = c->next_sched();
+  a.status = c->status_word();
+  int launches = 0;
+  if (!cuda_ok(c, launch_gemv(t, a, 1, false, c->sm_count, c->stream, &launches))) return EMELB_INTERNAL_ERROR;
+  c->diag.kernel_launches += launches;
+  for (uint32_t i = 0; i < count; ++i) count_dispatch(c, t, 1, false);
+  return EMELB_OK;
+}
+
 uint32_t emelb_prepare_rhs(emelb_ctx* c, const emelb_view* src1, int32_t weight_type) {
   if (!c || !src1 || !src1->data) return EMELB_INVALID_REQUEST;
   const uint64_t n = src1->ne[0], K = src1->ne[1];

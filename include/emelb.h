@@ -198,6 +198,12 @@ EMELB_API uint32_t emelb_mul_mat(emelb_ctx* ctx, const emelb_op* op);
 EMELB_API uint32_t emelb_prepare_rhs(emelb_ctx* ctx, const emelb_view* src1_f32,
                                      int32_t weight_type);
 EMELB_API uint32_t emelb_mul_mat_prepared(emelb_ctx* ctx, const emelb_op* op);
+/* `count` products against the same prepared column, results as `count` calls of
+ * emelb_mul_mat_prepared.  Two or three matrices of one type and row length with
+ * device outputs (Q, K, V or gate, up of one layer) run as ONE launch of the
+ * streaming mat-vec kernel, the way the decoder session issues them. */
+EMELB_API uint32_t emelb_mul_mat_prepared_group(emelb_ctx* ctx, const emelb_op* ops,
+                                                uint32_t count);
 
 /* ---- op_mul_mat_argmax: replaces run_mul_mat_argmax
  * (src/emel/kernel/detail.hpp:3608-3731): dst[0] = best value,

@@ -484,3 +484,42 @@ def test_synth_encoders_emit_valid_blocks(be, port, t, tol):
     assert abs(float(f.std()) - 0.02) < 0.002 and abs(float(f.mean())) < 0.001
     assert ob.rel_l2(port.dequantize(t, q, k, m), f) < tol
     assert be.free(fdev) and be.free(qdev)
+
+
+@pytest.mark.parametrize("t", WEIGHT_TYPES)
+def test_prepared_group_equals_single_products(be, port, t):
+    """Q, K, V (or gate, up) against one prepared column in one launch: the same bits as one
+    emelb_mul_mat_prepared per matrix; requests the grouped launch does not take fall back to those calls."""
+    k, ms = 4096, (512, 128, 136)
+    ws = [synth.encoded_weights(port, t, 700 + i, m, k) for i, m in enumerate(ms)]
+    x = synth.activations_f32(710 + t, k, 1)
+    bufs = [be.alloc(w.nbytes) for w in ws]
+    xd, yd = be.alloc(4 * k), be.alloc(4 * sum(ms) * 2)
+    try:
+        for d, w in zip(bufs, ws):
+            assert be.to_device(d, w)
+        assert be.to_device(xd, x)
+        offs = np.cumsum([0] + list(ms))
+        single = [eb.mul_mat_op(d, t, k, m, xd, 1, yd + 4 * int(o)) for d, m, o in zip(bufs, ms, offs)]
+        grouped = [eb.mul_mat_op(d, t, k, m, xd, 1, yd + 4 * int(sum(ms) + o)) for d, m, o in zip(bufs, ms, offs)]
+        assert be.prepare_rhs(eb.dense_view(xd, eb.F32, [1, k]), t)
+        for op in single:
+            assert be.mul_mat_prepared(op), be.last_error
+        l0 = be.diagnostics()["kernel_launches"]
+        assert be.mul_mat_prepared_group(grouped), be.last_error
+        assert be.diagnostics()["kernel_launches"] - l0 == 1
+        assert be.mul_mat_prepared_group(grouped[:2]), be.last_error
+        out = np.zeros(2 * sum(ms), np.float32)
+        assert be.to_host(out, yd)
+        assert np.array_equal(out[:sum(ms)].view(np.uint32), out[sum(ms):].view(np.uint32))
+        # host outputs: not grouped, still right
+        host = [np.zeros(m, np.float32) for m in ms]
+        assert be.prepare_rhs(eb.dense_view(xd, eb.F32, [1, k]), t)
+        assert be.mul_mat_prepared_group([eb.mul_mat_op(d, t, k, m, xd, 1, h) for d, m, h in zip(bufs, ms, host)])
+        assert np.array_equal(np.concatenate(host).view(np.uint32), out[:sum(ms)].view(np.uint32))
+        # without prepared planes the request is rejected like emelb_mul_mat_prepared rejects it
+        assert be.mul_mat(single[0])
+        assert not be.mul_mat_prepared_group(grouped)
+    finally:
+        for d in bufs + [xd, yd]:
+            be.free(d)
