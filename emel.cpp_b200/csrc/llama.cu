@@ -724,7 +724,8 @@ int prefill_batch_size(emelb_llama* s, int n) {
 }
 
 bool reserve_batch(emelb_llama* s, int B) {
-  if (s->batch_cap != 0) return true;  // sized by the first batched prompt; later batches are cut to fit
+  if (s->batch_cap > 0) return true;   // sized by the first batched prompt; later batches are cut to fit
+  if (s->batch_cap < 0) return false;  // the buffers did not fit once: prompts are walked token by token
   const emelb_llama_config& c = s->cfg;
   const size_t q_dim = (size_t)c.n_head * c.head_dim, kv_dim = (size_t)c.n_head_kv * c.head_dim, b = (size_t)B;
   bool ok = dev_alloc(s, (void**)&s->batch_tokens, sizeof(int) * b);
@@ -735,7 +736,7 @@ bool reserve_batch(emelb_llama* s, int B) {
   ok = ok && dev_alloc(s, (void**)&s->b_gate, 4 * b * c.n_ff) && dev_alloc(s, (void**)&s->b_up, 4 * b * c.n_ff);
   ok = ok && dev_alloc(s, (void**)&s->b_ffn, 4 * b * c.n_ff);
   ok = ok && dev_alloc(s, (void**)&s->b_partial, sizeof(double) * (size_t)rms_norm_batch_partials(B));
-  if (ok) s->batch_cap = B;
+  s->batch_cap = ok ? B : -1;
   return ok;
 }
 
