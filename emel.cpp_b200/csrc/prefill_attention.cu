@@ -207,7 +207,7 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(kMmaThreads) prefill_attention_mma_kernel(const PrefillAttnArgs a) {
+__global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(const PrefillAttnArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   PrefillMmaSmem<D>& sm = *reinterpret_cast<PrefillMmaSmem<D>*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
