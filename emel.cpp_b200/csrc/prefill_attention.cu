@@ -188,12 +188,23 @@ constexpr int kMmaThreads = 128;
 
 template <int D>
 struct PrefillMmaSmem {
-  static constexpr int kRowStride = D + 8;     // halves; 4g + t banks for the fragment loads
-  static constexpr int kVtStride = kKT + 8;
+  static constexpr int kRowStride = D + 8;     // halves; rows 16 bytes x 17 apart: 8 rows of a fragment load cover all banks
   __half q[kRows][kRowStride];
   __half k[kKT][kRowStride];
-  __half vt[D][kVtStride];                     // V tile transposed: [dim][position]
+  __half v[kKT][kRowStride];                   // row-major like K; ldmatrix.trans hands out the V fragments
 };
+
+// four 8x8 b16 matrices; lane l supplies the address of row l % 8 of matrix l / 8
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(row));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -262,9 +273,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
         vv = *reinterpret_cast<const uint4*>(vbase + (int64_t)(t0 + tt) * D + 8 * c);
       }
       *reinterpret_cast<uint4*>(&sm.k[tt][8 * c]) = kk;
-      const __half* vh = reinterpret_cast<const __half*>(&vv);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) sm.vt[8 * c + i][tt] = vh[i];
+      *reinterpret_cast<uint4*>(&sm.v[tt][8 * c]) = vv;
     }
     __syncthreads();
 
@@ -274,11 +283,13 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
     for (int nt = 0; nt < kKT / 8; ++nt) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) s[nt][i] = 0.0f;
+      // K fragments of two 16-dim steps per load: matrices (dims kk*16..+7, +8..+15, (kk+1)*16..+7, +8..+15)
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.k[nt * 8 + g][kk * 16 + 2 * t]);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.k[nt * 8 + g][kk * 16 + 2 * t + 8]);
-        mma_f16(s[nt], qf[kk], b0, b1);
+      for (int kk = 0; kk < D / 16; kk += 2) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, &sm.k[nt * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8 + (lane >> 4) * 16]);
+        mma_f16(s[nt], qf[kk], kb[0], kb[1]);
+        mma_f16(s[nt], qf[kk + 1], kb[2], kb[3]);
       }
     }
 
@@ -337,12 +348,16 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
           lo[2 * part + h] = pack_half2(p[2 * h] - back.x, p[2 * h + 1] - back.y);
         }
       }
+      // V fragments of two 8-dim column tiles per load, transposed on the way out of shared memory:
+      // matrices (positions jj*16..+7 | +8..+15) x (dims dn*8..+7 | (dn+1)*8..+7)
 #pragma unroll
-      for (int dn = 0; dn < D / 8; ++dn) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.vt[dn * 8 + g][jj * 16 + 2 * t]);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.vt[dn * 8 + g][jj * 16 + 2 * t + 8]);
-        mma_f16(o[dn], hi, b0, b1);
-        mma_f16(o[dn], lo, b0, b1);
+      for (int dn = 0; dn < D / 8; dn += 2) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, &sm.v[jj * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][(dn + (lane >> 4)) * 8]);
+        mma_f16(o[dn], hi, vb[0], vb[1]);
+        mma_f16(o[dn], lo, vb[0], vb[1]);
+        mma_f16(o[dn + 1], hi, vb[2], vb[3]);
+        mma_f16(o[dn + 1], lo, vb[2], vb[3]);
       }
     }
   }
