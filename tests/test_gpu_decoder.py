@@ -236,3 +236,26 @@ def test_batched_prompt_many_layers_within_attention_noise(be, port, cfg, types,
             assert np.isfinite(got).all() and d <= yard and d <= 5e-2, (pieces, d, yard)
     finally:
         sess.close()
+
+
+def test_batched_prompt_fills_the_context_to_the_last_row(be, port, monkeypatch):
+    """A prompt that ends on the last but one cache row, batches of 2 and of 61 tokens, and the decode step
+    on the last row: bit-identical to the token-by-token walk (one layer), and requests past the context
+    are refused before anything runs."""
+    cfg = dict(TINY, n_layer=1, n_ctx=64)
+    sess, cpu = build_model(be, port, cfg, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K}, seed=29)
+    cpu.close()
+    try:
+        prompt = synth.rng(31).integers(0, cfg["n_vocab"], size=64).tolist()
+        monkeypatch.setenv("EMELB_NO_BATCH_PREFILL", "1")
+        base = _prompt_then_logits(be, sess, prompt, [63])
+        monkeypatch.delenv("EMELB_NO_BATCH_PREFILL")
+        assert sess.prefill(synth.rng(5).integers(0, cfg["n_vocab"], size=63).tolist(), 0)    # scrub
+        got = _prompt_then_logits(be, sess, prompt, [2, 61])
+        assert np.array_equal(got.view(np.uint32), base.view(np.uint32))
+        assert not sess.prefill(prompt[:2], 63) and sess.last_error == eb.INVALID_REQUEST       # would pass the last row
+        assert not sess.prefill([cfg["n_vocab"]], 0) and sess.last_error == eb.INVALID_REQUEST  # no such token
+        again = sess.decode(prompt[-1], 63, want_logits=True)                                    # the session still works
+        assert np.array_equal(again.view(np.uint32), base.view(np.uint32))
+    finally:
+        sess.close()
