@@ -531,9 +531,12 @@ cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, uint8
     configured |= 1u << (dev & 31);
   }
   const int nt = (ncols + BN - 1) / BN;
-  tile_activations_kernel<<<dim3(a.K / QK_K, nt), 256, 0, st>>>(a.act, a.col0, ncols, a.K, workspace);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  cudaError_t e = cudaSuccess;
+  if (!a.tc_ws_reuse) {  // else the workspace still holds these planes in operand order (same K, columns, col0)
+    tile_activations_kernel<<<dim3(a.K / QK_K, nt), 256, 0, st>>>(a.act, a.col0, ncols, a.K, workspace);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
   GemmArgs g{};
   g.W = a.W;
   g.row_bytes = a.row_bytes;

@@ -735,6 +735,12 @@ bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K) {
   return (K % CHUNK) == 0 && (reinterpret_cast<uintptr_t>(w) % 16) == 0 && (row_bytes % 16) == 0;
 }
 
+bool gemv_takes_tensor_core(int type, const GemvArgs& a, int ncols) {
+  static const bool no_tc = getenv("EMELB_NO_TC") != nullptr;
+  return !no_tc && a.tc_ws && gemm_tc_supported(type, a.K, ncols, a.W, a.row_bytes, a.act) &&
+         gemm_tc_workspace_bytes(a.K, ncols) <= a.tc_ws_bytes;
+}
+
 cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
                         int* launches) {
   // many columns of Q8_0 / Q4_0: one tensor-core instruction per 32-weight block (gemm_q8_mma.cu)
@@ -743,10 +749,8 @@ cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int
     return launch_gemm_q8_mma(type, a, ncols, st);
   }
   // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
-  static const bool no_tc = getenv("EMELB_NO_TC") != nullptr;
-  if (!argmax && !no_tc && a.tc_ws && gemm_tc_supported(type, a.K, ncols, a.W, a.row_bytes, a.act) &&
-      gemm_tc_workspace_bytes(a.K, ncols) <= a.tc_ws_bytes) {
-    *launches += 2;
+  if (!argmax && gemv_takes_tensor_core(type, a, ncols)) {
+    *launches += a.tc_ws_reuse ? 1 : 2;
     return launch_gemm_q4k_tc(a, ncols, sm_count, a.tc_ws, st);
   }
   const bool fast = gemv_fast_path_ok(type, a.W, a.row_bytes, a.K);

@@ -70,6 +70,7 @@ struct GemvArgs {
   float pro_eps;
   uint8_t* tc_ws;        // workspace of the many-column tensor-core kernel (null: that kernel is not used)
   size_t tc_ws_bytes;
+  int tc_ws_reuse;       // the previous many-column Q4_K product of this stream used the same planes, K, columns and col0
   int* sched;            // {next task, finished blocks}: zero between launches (self-rearming)
   int* status;           // optional: set to 1 by a kernel whose bounded wait ran out
   int pdl;               // launch with programmatic stream serialization (kernels wait before dependent reads)
@@ -83,6 +84,8 @@ struct GemvArgs {
 bool gemv_fast_path_ok(int type, const void* w, int64_t row_bytes, int K);
 cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
                         int* launches);
+// whether launch_gemv (without argmax) hands this product to the tcgen05 kernel
+bool gemv_takes_tensor_core(int type, const GemvArgs& a, int ncols);
 
 // gemm_q8_mma.cu: 32 and more columns of Q8_0 / Q4_0 weights (mma.sync int8, one block per instruction)
 bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols);

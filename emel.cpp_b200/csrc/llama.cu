@@ -120,6 +120,7 @@ struct Enqueue {
   int launches = 0;
   bool ok = true;
   int batch_family = 0;  // family the planes were last quantized for by batch_matmul
+  bool batch_tc_tiled = false;  // the tensor-core workspace holds the current planes in operand order
 
   void check(cudaError_t e) { ok = ok && ctx_cuda_ok(s->c, e); }
 
@@ -305,11 +306,14 @@ struct Enqueue {
   // y {w.M, B} = w x quantized(x {w.K, B}); the Q4_K products of 32 and more tokens run on the tensor cores
   void batch_matmul(const Tensor& w, const float* x, float* y, int B, bool same_input = false) {
     // same_input: the planes still hold x quantized for this family (the previous product read the same x)
+    bool requantized = false;
     if (!same_input || batch_family != family_of(w.type)) {
       check(quantize_into_planes(w.type, x, B, B, w.K, planes(), st));
       ++launches;
       batch_family = family_of(w.type);
+      requantized = true;
     }
+    if (requantized) batch_tc_tiled = false;
     GemvArgs a{};
     a.W = w.dev;
     a.row_bytes = w.row_bytes;
@@ -321,6 +325,11 @@ struct Enqueue {
     a.ldy = B;
     a.tc_ws = s->c->tc_ws;
     a.tc_ws_bytes = s->c->tc_ws_bytes;
+    // the tensor-core product keeps its own operand-ordered copy of the planes: still good for the next
+    // Q4_K product of the same input
+    const bool tc = gemv_takes_tensor_core(w.type, a, B);
+    a.tc_ws_reuse = tc && batch_tc_tiled ? 1 : 0;
+    if (tc) batch_tc_tiled = true;
     a.sched = s->c->next_sched();
     a.status = s->c->status_word();
     a.part_val = s->c->part_val;
