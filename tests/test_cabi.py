@@ -154,3 +154,15 @@ def test_cuda_actor_adapter_compiles_against_reference_events():
         assert fields["engaged"] == "1" and fields["accepted"] == "1"
     else:
         assert fields["engaged"] == "0" and fields["accepted"] == "0"
+
+
+def test_entry_points_refuse_null_contexts_without_a_gpu():
+    """No compute without a GPU, but every newer entry point must answer a null context with
+    invalid_request instead of touching it."""
+    lib = eb.lib()
+    op = eb.Op()
+    assert lib.emelb_mul_mat_prepared_group(None, C.byref(op), 2) == eb.INVALID_REQUEST
+    assert lib.emelb_flash_attn_batch(None, None, None, None, None, 64, 8, 2, 1, 0, 64, 0.125) == eb.INVALID_REQUEST
+    from emel_cpp_b200 import gguf
+    assert lib.emelb_gguf_upload_all(None, None, 0) == gguf.INVALID_REQUEST
+    assert lib.emelb_gguf_upload(None, None, 0, 0, None) == gguf.INVALID_REQUEST
