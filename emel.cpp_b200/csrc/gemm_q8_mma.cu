@@ -7,7 +7,7 @@
 // same bits as the mat-vec kernels.  The scaling, 4 float operations per product and block, bounds the
 // kernel, not the MMAs; a tcgen05 tile would only move the same scaling work behind a TMEM load.
 //
-// One CTA = 128 weight rows x 64 activation columns, 8 warps of 16 rows each; K is walked in chunks of 8
+// One CTA = 128 (or, for small grids, 64) weight rows x 64 activation columns, one warp per 16 rows; K is walked in chunks of 8
 // blocks through a two-stage cp.async ring.  Weight rows are staged as they lie in memory (scale + quants,
 // 34 or 18 bytes per block) and the A fragments are read from there with 2-byte loads (Q4_0 nibbles are
 // widened to value - 8 in registers), so staging is pure asynchronous copying.
@@ -24,16 +24,16 @@ namespace emelb {
 
 namespace {
 
-constexpr int kTM = 128, kTN = 64, kChunkBlocks = 8, kChunk = kChunkBlocks * QK32;
+constexpr int kTN = 64, kChunkBlocks = 8, kChunk = kChunkBlocks * QK32;
 constexpr int kRowStride = kChunk + 16;  // bytes: fragment loads of 8 rows x 4 lanes hit 32 distinct banks
-constexpr int kThreadsQ8 = 256;
 constexpr int kStagesQ8 = 2;
 
 // One stage of the ring: the weight rows as they lie in memory (8 blocks = 272 B of Q8_0 or 144 B of Q4_0 per
 // row, copied 16 bytes at a time by cp.async; both row strides put 8 rows x 4 lanes on distinct banks), the
 // activation rows and their block scales.
-template <int T>
+template <int T, int WARPS>
 struct Q8Stage {
+  static constexpr int kTM = 16 * WARPS;
   static constexpr int kBB = T == T_Q8_0 ? Q8_0_BYTES : Q4_0_BYTES;
   static constexpr int kRaw = kChunkBlocks * kBB;
   uint8_t a[kTM][kRaw];
@@ -55,9 +55,10 @@ __device__ __forceinline__ uint32_t lds32_h(const uint8_t* p) {
 // per byte: nibble value (0..15) - 8 as int8
 __device__ __forceinline__ uint32_t nibbles_minus_8(uint32_t v) { return ((v | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
-template <int T>
-__global__ void __launch_bounds__(kThreadsQ8, 2) gemm_q8_mma_kernel(const GemvArgs p, int ncols) {
-  using Stage = Q8Stage<T>;
+template <int T, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_kernel(const GemvArgs p, int ncols) {
+  using Stage = Q8Stage<T, WARPS>;
+  constexpr int kTM = Stage::kTM, kThreadsQ8 = 32 * WARPS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Stage* stages = reinterpret_cast<Stage*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -150,13 +151,21 @@ __global__ void __launch_bounds__(kThreadsQ8, 2) gemm_q8_mma_kernel(const GemvAr
   }
 }
 
-template <int T>
-cudaError_t launch_t(const GemvArgs& a, int ncols, cudaStream_t st) {
-  const int smem = (int)(kStagesQ8 * sizeof(Q8Stage<T>));
-  cudaError_t e = cudaFuncSetAttribute(gemm_q8_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+template <int T, int WARPS>
+cudaError_t launch_w(const GemvArgs& a, int ncols, cudaStream_t st) {
+  constexpr int kTM = 16 * WARPS;
+  const int smem = (int)(kStagesQ8 * sizeof(Q8Stage<T, WARPS>));
+  cudaError_t e = cudaFuncSetAttribute(gemm_q8_mma_kernel<T, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  gemm_q8_mma_kernel<T><<<dim3((a.M + kTM - 1) / kTM, (ncols + kTN - 1) / kTN), kThreadsQ8, smem, st>>>(a, ncols);
+  gemm_q8_mma_kernel<T, WARPS><<<dim3((a.M + kTM - 1) / kTM, (ncols + kTN - 1) / kTN), 32 * WARPS, smem, st>>>(a, ncols);
   return cudaGetLastError();
+}
+
+// 128-row tiles; 64-row tiles (4 warps) while the 128-row grid would leave SMs without a CTA pair
+template <int T>
+cudaError_t launch_t(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
+  const int64_t big = (int64_t)((a.M + 127) / 128) * ((ncols + kTN - 1) / kTN);
+  return big >= 2 * (int64_t)sm_count ? launch_w<T, 8>(a, ncols, st) : launch_w<T, 4>(a, ncols, st);
 }
 
 }  // namespace
@@ -168,8 +177,8 @@ bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols) {
          a.act.col_stride_qs % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.d) % 16 == 0 && getenv("EMELB_NO_Q8_MMA") == nullptr;
 }
 
-cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, cudaStream_t st) {
-  return type == T_Q8_0 ? launch_t<T_Q8_0>(a, ncols, st) : launch_t<T_Q4_0>(a, ncols, st);
+cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
+  return type == T_Q8_0 ? launch_t<T_Q8_0>(a, ncols, sm_count, st) : launch_t<T_Q4_0>(a, ncols, sm_count, st);
 }
 
 }  // namespace emelb

@@ -746,7 +746,7 @@ cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int
   // many columns of Q8_0 / Q4_0: one tensor-core instruction per 32-weight block (gemm_q8_mma.cu)
   if (!argmax && gemm_q8_mma_supported(type, a, ncols)) {
     ++*launches;
-    return launch_gemm_q8_mma(type, a, ncols, st);
+    return launch_gemm_q8_mma(type, a, ncols, sm_count, st);
   }
   // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
   if (!argmax && gemv_takes_tensor_core(type, a, ncols)) {

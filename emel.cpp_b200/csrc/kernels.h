@@ -89,7 +89,7 @@ bool gemv_takes_tensor_core(int type, const GemvArgs& a, int ncols);
 
 // gemm_q8_mma.cu: 32 and more columns of Q8_0 / Q4_0 weights (mma.sync int8, one block per instruction)
 bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols);
-cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, cudaStream_t st);
+cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, int sm_count, cudaStream_t st);
 
 // gemv2.cu
 cudaError_t launch_gemv_stream2(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
