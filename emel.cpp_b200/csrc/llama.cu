@@ -342,40 +342,56 @@ struct Enqueue {
   // B prompt tokens (ids in s->batch_tokens) at positions pos0 .. pos0 + B - 1 through every layer: fills the
   // KV cache rows of those positions.  Same arithmetic per token as token_step except the attention, which
   // is the f32 online-softmax kernel for token batches (attention mode 0 only).
+  // join the ranks' row intervals of a batch tensor {rows, B}: rows are feature-major, so a rank's interval
+  // is one contiguous block (NCCL all-gather in place; no-op unsharded)
+  void batch_gather(float* full, size_t rows_per_rank, int B) {
+    if (s->G <= 1) return;
+    check(comm_all_gather_bytes(s->c, full, rows_per_rank * (size_t)B * sizeof(float), st));
+    ++launches;
+  }
+
   void prefill_chunk(int B, int pos0) {
     const emelb_llama_config& c = s->cfg;
-    const int q_dim = c.n_head * c.head_dim, kv_dim = c.n_head_kv * c.head_dim;
+    const int G = s->G, r = s->rank;
+    const int heads_l = c.n_head / G, kv_l = c.n_head_kv / G;
+    const size_t q_l = (size_t)heads_l * c.head_dim, embd_l = (size_t)c.n_embd / G, ff_l = (size_t)c.n_ff / G, b = (size_t)B;
     const int rot = c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim;
+    // this rank's row intervals inside the full-length batch tensors
+    float* attn_mine = s->b_attn + r * q_l * b;
+    float* y_mine = s->b_y + r * embd_l * b;
+    float* ffn_mine = s->b_ffn + r * ff_l * b;
     s->planes_src = nullptr;
     check(launch_embed_rows(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->batch_tokens, B, s->b_hidden, c.n_embd, st));
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
       const Layer& w = s->layers[l];
-      const int64_t layer_off = (int64_t)l * c.n_head_kv * s->capacity * c.head_dim;
+      const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
       check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       ++launches;
       batch_matmul(w.wq, s->b_norm, s->b_q, B);
       batch_matmul(w.wk, s->b_norm, s->b_k, B, true);
       batch_matmul(w.wv, s->b_norm, s->b_v, B, true);
-      check(launch_rope_store_batch(s->b_q, s->b_k, s->b_v, s->rope_cos, s->rope_sin, pos0, B, c.n_head, c.n_head_kv, c.head_dim,
+      check(launch_rope_store_batch(s->b_q, s->b_k, s->b_v, s->rope_cos, s->rope_sin, pos0, B, heads_l, kv_l, c.head_dim,
                                     rot, c.rope_neox, s->kcache + layer_off, s->vcache + layer_off, s->capacity * c.head_dim, st));
       ++launches;
-      PrefillAttnArgs pa{s->b_q, s->b_attn, s->kcache + layer_off, s->vcache + layer_off, s->capacity * c.head_dim,
-                         c.head_dim, c.n_head, c.n_head_kv, B, pos0, 1.0f / std::sqrt((float)c.head_dim)};
+      PrefillAttnArgs pa{s->b_q, attn_mine, s->kcache + layer_off, s->vcache + layer_off, s->capacity * c.head_dim,
+                         c.head_dim, heads_l, kv_l, B, pos0, 1.0f / std::sqrt((float)c.head_dim)};
       check(launch_prefill_attention(pa, st));
       ++launches;
-      batch_matmul(w.wo, s->b_attn, s->b_y, B);
+      batch_gather(s->b_attn, q_l, B);
+      batch_matmul(w.wo, s->b_attn, y_mine, B);
+      batch_gather(s->b_y, embd_l, B);
       check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
       check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.ffn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       batch_matmul(w.gate, s->b_norm, s->b_gate, B);
       batch_matmul(w.up, s->b_norm, s->b_up, B, true);
-      check(launch_swiglu(s->b_gate, s->b_up, c.n_ff * B, s->b_ffn, 0, planes(), st));
-      batch_matmul(w.down, s->b_ffn, s->b_y, B);
+      check(launch_swiglu(s->b_gate, s->b_up, (int)(ff_l * b), ffn_mine, 0, planes(), st));
+      batch_gather(s->b_ffn, ff_l, B);
+      batch_matmul(w.down, s->b_ffn, y_mine, B);
+      batch_gather(s->b_y, embd_l, B);
       check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
       launches += 4;
     }
-    (void)q_dim;
-    (void)kv_dim;
   }
 
   void token_step(Mode mode) {
@@ -714,13 +730,15 @@ uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t position, flo
 namespace {
 
 // token-batch size of the prompt path: 0 = walk the prompt token by token.  Batches need the batch attention
-// kernel (attention mode 0: the reference-order modes exist to be compared one token at a time), an unsharded
-// session, and room for one batch in the context's activation planes.
+// kernel (attention mode 0: the reference-order modes exist to be compared one token at a time), room for one
+// batch in the context's activation planes and, in a sharded session, the context's communicator for the joins.
 int prefill_batch_size(emelb_llama* s, int n) {
   const char* off = getenv("EMELB_NO_BATCH_PREFILL");
   const emelb_llama_config& c = s->cfg;
-  if (off || s->G != 1 || s->c->attention_mode != 0 || n < 2) return 0;
-  PrefillAttnArgs pa{nullptr, nullptr, s->kcache, s->vcache, s->capacity * c.head_dim, c.head_dim, c.n_head, c.n_head_kv, 1, 0, 1.0f};
+  if (off || s->c->attention_mode != 0 || n < 2) return 0;
+  if (s->G > 1 && (!s->c->comm || s->c->comm_world != s->G)) return 0;   // batch joins go through the communicator
+  PrefillAttnArgs pa{nullptr, nullptr, s->kcache, s->vcache, s->capacity * c.head_dim, c.head_dim, c.n_head / s->G,
+                     c.n_head_kv / s->G, 1, 0, 1.0f};
   if (!prefill_attention_supported(pa)) return 0;
   int widest = c.n_ff > c.n_embd ? c.n_ff : c.n_embd;
   if (c.n_head * c.head_dim > widest) widest = c.n_head * c.head_dim;

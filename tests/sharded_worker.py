@@ -120,6 +120,28 @@ def main():
     assert float(np.abs(lf0 - ls0).max()) <= 1e-3
     assert idf0[0] == ids0[0]
 
+    # batched prompt path: the sharded session processes the prompt in token batches too (row intervals of every
+    # product joined by NCCL); per head and per row it runs the same kernels on the same numbers as the
+    # unsharded session, so the logits that follow are bit-identical
+    del os.environ["EMELB_NO_BATCH_PREFILL"]
+    os.environ["EMELB_PREFILL_BATCH"] = "24"          # 50 prompt tokens = 24 + 24 + 2
+    long_prompt = np.random.Generator(np.random.PCG64(11)).integers(0, CFG["n_vocab"], size=51).tolist()
+    batched = {}
+    for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world)):
+        be.set_attention_mode(0)
+        sess = build(be, be_full, CFG, r, g, buffers)
+        l0 = be.diagnostics()["kernel_launches"]
+        assert sess.prefill(long_prompt[:-1], 0), sess.last_error
+        launches = be.diagnostics()["kernel_launches"] - l0
+        assert launches < 50 * 10, launches            # batches, not 50 token steps of 15+ launches
+        batched[name] = sess.decode(long_prompt[-1], 50, want_logits=True)
+        assert be.sync()
+        dist.barrier()
+        sess.close()
+    del os.environ["EMELB_PREFILL_BATCH"]
+    assert np.array_equal(batched["full"].view(np.uint32), batched["shard"].view(np.uint32)), \
+        float(np.abs(batched["full"] - batched["shard"]).max())
+
     # op level: each rank runs its row slice of one op_mul_mat, then the join
     k, m, n = 2048, 4096, 3
     w = be_full.alloc(m * eb.row_bytes(eb.Q4_K, k))
