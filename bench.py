@@ -794,7 +794,7 @@ def run_decode(args):
         assert sess.prefill(prompt[:-1], 0), sess.last_error
     prefill_s = time.perf_counter() - t0
     prefill_warm_s = None
-    if not args.profile_skip_prefill and not shard:
+    if not args.profile_skip_prefill:
         # the same prompt again (same KV rows): the first pass also sized the batch buffers
         t0 = time.perf_counter()
         assert sess.prefill(prompt[:-1], 0), sess.last_error
@@ -899,8 +899,8 @@ def run_decode(args):
                    "prefill_s": "skipped: zero-filled KV cache, profiling aid, not a benchmark number" if args.profile_skip_prefill
                    else round(prefill_s, 3),
                    "prefill_tok_s": None if prefill_warm_s is None else round((prompt_len - 1) / prefill_warm_s, 1),
-                   "prefill": "prompt tokens in batches of up to 2048: tcgen05 Q4_K products, mma.sync batch attention" if not shard
-                   else "token by token (sharded sessions)"},
+                   "prefill": "prompt tokens in batches of up to 2048: tcgen05 Q4_K products, mma.sync batch attention"
+                              + (", row intervals joined by NCCL all-gather" if shard else "")},
         "hbm_gbs_effective": round(bytes_per_token * tok_s / seqs / 1e9, 1),
         "q4_k_gemv_hbm_gbs": round(kernel_gbs, 1), "pct_of_8tbs_nominal": round(100 * kernel_gbs / NOMINAL_HBM_GBS, 2),
         "e2e": {"value": round(tok_s_e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 8,

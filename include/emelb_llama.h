@@ -94,11 +94,13 @@ EMELB_API uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t pos
 
 /* feeds `n` prompt tokens at positions start_pos.. without computing logits:
  * fills their KV rows.  The reference's x86 prefill walks the prompt one token
- * at a time (src/emel/text/generator/detail.hpp:4064-4092).  Unsharded
- * sessions with the fast attention (mode 0) process the prompt in batches of up
- * to 2048 tokens instead: per token the same arithmetic except the attention,
- * which is an f32 online softmax over the batch (emelb_flash_attn_batch).
- * Sharded sessions and the reference-order attention modes walk token by token. */
+ * at a time (src/emel/text/generator/detail.hpp:4064-4092).  With the fast
+ * attention (mode 0) the prompt is processed in batches of up to 2048 tokens
+ * instead: per token the same arithmetic except the attention, which is an f32
+ * online softmax over the batch (emelb_flash_attn_batch).  Sharded sessions do
+ * the same when their context has a communicator (emelb_comm_init), joining the
+ * ranks' row intervals of every product by all-gather.  The reference-order
+ * attention modes walk token by token. */
 EMELB_API uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n,
                                        int32_t start_pos);
 
