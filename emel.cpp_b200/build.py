@@ -20,8 +20,9 @@ SOURCES = {
     "elementwise.cu": ["-fmad=false"],
     "gemv.cu": [],
     "gemv2.cu": [],
+    "token_kernel.cu": ["-fmad=false"],
     "synth.cu": [],
-    "attention.cu": [],
+    "attention.cu": ["-fmad=false"],
     "prefill_attention.cu": [],
     "gemm_tc.cu": [],
     "gemm_q8_mma.cu": [],

@@ -313,6 +313,15 @@ uint32_t emelb_create(int device, emelb_ctx** out) {
   ok = ok && cudaMalloc(&c->tc_ws, c->tc_ws_bytes) == cudaSuccess;
   ok = ok && cudaMalloc(&c->gemv_sched, (2 * kSchedSlots + 2) * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMemset(c->gemv_sched, 0, (2 * kSchedSlots + 2) * sizeof(int)) == cudaSuccess;
+  c->bv_table_floats = 8u << 20;   // 32 MB: 57344 rows x 32 blocks (gate + up of the 70B shape) with room to spare
+  c->grp_cnt_ints = 64u << 10;
+  ok = ok && cudaMalloc(&c->bv_table, c->bv_table_floats * sizeof(float)) == cudaSuccess;
+  ok = ok && cudaMalloc(&c->grp_cnt, c->grp_cnt_ints * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(c->grp_cnt, 0, c->grp_cnt_ints * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMalloc(&c->token_bar, 4 * sizeof(unsigned)) == cudaSuccess;
+  ok = ok && cudaMemset(c->token_bar, 0, 4 * sizeof(unsigned)) == cudaSuccess;
+  ok = ok && cudaMalloc(&c->token_cnt, emelb_ctx::kTokenCounters * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(c->token_cnt, 0, emelb_ctx::kTokenCounters * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_val, kMaxArgmaxParts * sizeof(float)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->part_idx, kMaxArgmaxParts * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMalloc(&c->best_val, sizeof(float)) == cudaSuccess;
@@ -340,7 +349,7 @@ uint32_t emelb_destroy(emelb_ctx* c) {
   for (auto& kv : c->residents)
     if (kv.second.dev) cudaFree(kv.second.dev);
   for (void* p : c->owned) cudaFree(p);
-  void* bufs[] = {c->gemv_sched, c->stage_in, c->stage_out, c->act_qs, c->act_d, c->act_bsums, c->tc_ws, c->part_val, c->part_idx,
+  void* bufs[] = {c->token_bar, c->token_cnt, c->bv_table, c->grp_cnt, c->gemv_sched, c->stage_in, c->stage_out, c->act_qs, c->act_d, c->act_bsums, c->tc_ws, c->part_val, c->part_idx,
                   c->best_val, c->best_idx, c->fa_part_acc, c->fa_part_ml, c->fa_scores};
   for (void* p : bufs)
     if (p) cudaFree(p);
@@ -357,7 +366,11 @@ uint32_t emelb_sync(emelb_ctx* c) {
   int status = 0;
   if (!cuda_ok(c, cudaMemcpy(&status, c->status_word(), sizeof(int), cudaMemcpyDeviceToHost))) return EMELB_INTERNAL_ERROR;
   if (status != 0) {
+    // a kernel that gave up leaves task and arrival counters half-way
     cudaMemset(c->gemv_sched, 0, (2 * kSchedSlots + 2) * sizeof(int));
+    cudaMemset(c->grp_cnt, 0, c->grp_cnt_ints * sizeof(int));
+    cudaMemset(c->token_bar, 0, 4 * sizeof(unsigned));
+    cudaMemset(c->token_cnt, 0, emelb_ctx::kTokenCounters * sizeof(int));
     return EMELB_INTERNAL_ERROR;
   }
   return EMELB_OK;

@@ -16,6 +16,7 @@
 //    softmax with an f16 accumulator rounded after every token and libm-exact
 //    expf — the same roundings in the same order, for parity runs and for shapes
 //    the split kernel does not take.
+#include "attention_core.cuh"
 #include "common.cuh"
 #include "expf_exact.h"
 #include "kernels.h"
@@ -27,206 +28,23 @@ namespace {
 
 constexpr int LMAX = 1024;  // tokens per split the shared score buffer holds
 
-__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8]) {
-  const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __half22float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-template <int NREP>
-__device__ __forceinline__ void block_reduce(float (&v)[NREP], float* scratch /*[4][NREP]*/, bool is_max) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int r = 0; r < NREP; ++r) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float t = __shfl_xor_sync(0xffffffffu, v[r], o);
-      v[r] = is_max ? fmaxf(v[r], t) : v[r] + t;
-    }
-    if (lane == 0) scratch[warp * NREP + r] = v[r];
-  }
-  __syncthreads();
-#pragma unroll
-  for (int r = 0; r < NREP; ++r) {
-    float t = scratch[r];
-    for (int w = 1; w < 4; ++w) t = is_max ? fmaxf(t, scratch[w * NREP + r]) : t + scratch[w * NREP + r];
-    v[r] = t;
-  }
-  __syncthreads();
-}
-
 template <int D, int NREP>
 __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
   pdl_trigger();
   pdl_wait();
-  constexpr int DPL = D / 8;   // dims per lane while scoring (8 lanes per token row)
-  constexpr int TPR = D / 8;   // threads per token row while accumulating V (8 halves each)
-  constexpr int SLOTS = 128 / TPR;
-  static_assert(SLOTS * NREP * D <= NREP * LMAX, "V reduction reuses the score buffer");
   __shared__ __align__(16) float s_p[NREP * LMAX];
   __shared__ float s_red[4 * NREP];
-
-  const int tid = threadIdx.x;
-  const int split = blockIdx.x, kh = blockIdx.y;
   const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
-  const int n_rep = a.heads / a.kv_heads;
-  const int head0 = kh * n_rep + blockIdx.z * NREP;
-  int L = (T + a.splits - 1) / a.splits;
-  L = L > LMAX ? LMAX : L;  // host sizes `splits` so this never clips
-  const int t0 = split * L;
-  const int t1 = min(T, t0 + L);
-  const int n = t1 > t0 ? t1 - t0 : 0;
-
-  if (n == 0) {
-    for (int idx = tid; idx < NREP * D; idx += 128)
-      a.part_acc[((size_t)(head0 + idx / D) * a.splits + split) * D + idx % D] = 0.0f;
-    if (tid < NREP) {
-      float* ml = a.part_ml + ((size_t)(head0 + tid) * a.splits + split) * 2;
-      ml[0] = -INFINITY;
-      ml[1] = 0.0f;
-    }
-    return;
-  }
-
-  // pull this range's V rows towards L2 while the scores are computed
-  {
-    const char* vrange = reinterpret_cast<const char*>(a.v) + (size_t)kh * a.v_nb2 + (size_t)t0 * a.v_nb1;
-    const size_t vbytes = (size_t)n * a.v_nb1;
-    for (size_t off = (size_t)tid * 128; off < vbytes; off += 128 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(vrange + off));
-  }
-  // ---- scores: q is rounded to f16 first, as the reference does (detail.hpp:5255)
-  const int l8 = tid & 7, slot = tid >> 3;
-  float q[NREP][DPL];
-#pragma unroll
-  for (int r = 0; r < NREP; ++r)
-#pragma unroll
-    for (int i = 0; i < DPL; ++i)
-      q[r][i] = __half2float(__float2half_rn(a.q[(size_t)(head0 + r) * D + l8 * DPL + i]));
-
-  float mx[NREP];
-#pragma unroll
-  for (int r = 0; r < NREP; ++r) mx[r] = -INFINITY;
-  const char* kbase = reinterpret_cast<const char*>(a.k) + (size_t)kh * a.k_nb2 + (size_t)l8 * DPL * 2;
-  constexpr int U = 8;
-  // the loop bound is uniform across the warp (the score reduction below shuffles
-  // over all 32 lanes); rows past the range are clamped on load and masked on store
-  for (int tb = 0; tb < n; tb += 16 * U) {
-    const int t = tb + slot;
-    uint4 kv[U][DPL / 8];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int tt = min(t + 16 * u, n - 1);
-      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)(t0 + tt) * a.k_nb1);
-#pragma unroll
-      for (int c = 0; c < DPL / 8; ++c) kv[u][c] = __ldg(kp + c);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      float s[NREP];
-#pragma unroll
-      for (int r = 0; r < NREP; ++r) s[r] = 0.0f;
-#pragma unroll
-      for (int c = 0; c < DPL / 8; ++c) {
-        float kf[8];
-        unpack8(kv[u][c], kf);
-#pragma unroll
-        for (int r = 0; r < NREP; ++r)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) s[r] = fmaf(q[r][8 * c + i], kf[i], s[r]);
-      }
-      const int tt = t + 16 * u;
-#pragma unroll
-      for (int r = 0; r < NREP; ++r) {
-        float v = s[r];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        v *= a.scale;
-        if (tt < n) {
-          mx[r] = fmaxf(mx[r], v);
-          if (l8 == 0) s_p[r * LMAX + tt] = v;
-        }
-      }
-    }
-  }
-  block_reduce<NREP>(mx, s_red, true);  // also orders the score writes before the reads below
-
-  // ---- probabilities relative to the range maximum
-  float lsum[NREP];
-#pragma unroll
-  for (int r = 0; r < NREP; ++r) lsum[r] = 0.0f;
-  for (int idx = tid; idx < n; idx += 128) {
-#pragma unroll
-    for (int r = 0; r < NREP; ++r) {
-      const float pr = expf(s_p[r * LMAX + idx] - mx[r]);
-      s_p[r * LMAX + idx] = pr;
-      lsum[r] += pr;
-    }
-  }
-  block_reduce<NREP>(lsum, s_red, false);
-
-  // ---- V accumulation: TPR threads cover one token row with 128-bit loads
-  const int c = tid % TPR, vs = tid / TPR;
-  float acc[NREP][8];
-#pragma unroll
-  for (int r = 0; r < NREP; ++r)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[r][i] = 0.0f;
-  const char* vbase = reinterpret_cast<const char*>(a.v) + (size_t)kh * a.v_nb2 + (size_t)c * 16;
-  for (int t = vs; t < n; t += SLOTS * U) {
-    uint4 vv[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int tt = min(t + SLOTS * u, n - 1);
-      vv[u] = __ldg(reinterpret_cast<const uint4*>(vbase + (size_t)(t0 + tt) * a.v_nb1));
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int tt = t + SLOTS * u;
-      if (tt < n) {
-        float vf[8];
-        unpack8(vv[u], vf);
-#pragma unroll
-        for (int r = 0; r < NREP; ++r) {
-          const float pr = s_p[r * LMAX + tt];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[r][i] = fmaf(pr, vf[i], acc[r][i]);
-        }
-      }
-    }
-  }
-  __syncthreads();  // all probability reads done; the buffer becomes the slot reduction area
-#pragma unroll
-  for (int r = 0; r < NREP; ++r)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s_p[(vs * NREP + r) * D + c * 8 + i] = acc[r][i];
-  __syncthreads();
-  for (int idx = tid; idx < NREP * D; idx += 128) {
-    const int r = idx / D, d = idx % D;
-    float sum = 0.0f;
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) sum += s_p[(s * NREP + r) * D + d];
-    a.part_acc[((size_t)(head0 + r) * a.splits + split) * D + d] = sum;
-  }
-  if (tid < NREP) {
-    float* ml = a.part_ml + ((size_t)(head0 + tid) * a.splits + split) * 2;
-    ml[0] = mx[tid];
-    ml[1] = lsum[tid];
-  }
+  fa::split_unit<D, NREP, LMAX, 8, false>(a, blockIdx.x, blockIdx.y, blockIdx.z, T, threadIdx.x, s_p, s_red, fa::CtaSync{});
 }
 
-// merge the ranges: out = sum_s e^{m_s-M} acc_s / sum_s e^{m_s-M} l_s.
-// One CTA of 256 threads = 256 consecutive output values (256/D heads), which is
-// also one Q8_K block / eight Q8_0 blocks of the vector the output projection
-// consumes, so the CTA can hand the projection its quantized planes directly
-// (family 1 / 2; 0 = f32 only).  Warp w < 256/D first turns head w's (max, sum)
-// pairs into weights in shared memory; then thread (head, d) walks the ranges
-// with independent loads.
-constexpr int kMergeMaxSplits = 64;
+// merge the ranges (attention_core.cuh).  One CTA of 256 threads = 256 consecutive
+// output values (256/D heads), which is also one Q8_K block / eight Q8_0 blocks of the
+// vector the output projection consumes, so the CTA can hand the projection its
+// quantized planes directly (family 1 / 2; 0 = f32 only).  Warp w < 256/D first turns
+// head w's (max, sum) pairs into weights in shared memory; then thread (head, d) walks
+// the ranges with independent loads.
+using fa::kMergeMaxSplits;
 
 template <int FAMILY>
 __global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, ActPlanesMut planes) {
@@ -238,36 +56,10 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, Act
   const int D = a.head_dim, hp = 256 / D;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h0 = blockIdx.x * hp;
-  if (warp < hp) {
-    const float* ml = a.part_ml + (size_t)(h0 + warp) * a.splits * 2;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
-    if (lane < a.splits) { m0 = ml[2 * lane]; l0 = ml[2 * lane + 1]; }
-    if (lane + 32 < a.splits) { m1 = ml[2 * (lane + 32)]; l1 = ml[2 * (lane + 32) + 1]; }
-    float M = fmaxf(m0, m1);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    const float w0 = m0 == -INFINITY ? 0.0f : expf(m0 - M), w1 = m1 == -INFINITY ? 0.0f : expf(m1 - M);
-    s_w[warp][lane] = w0;
-    s_w[warp][lane + 32] = w1;
-    float den = w0 * l0 + w1 * l1;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-    if (lane == 0) s_inv[warp] = den == 0.0f ? 0.0f : 1.0f / den;
-  }
+  if (warp < hp) fa::merge_head_weights(a, h0 + warp, lane, s_w[warp], &s_inv[warp]);
   __syncthreads();
   const int hl = threadIdx.x / D, d = threadIdx.x - hl * D;
-  const float* pa = a.part_acc + (size_t)(h0 + hl) * a.splits * D + d;
-  float o = 0.0f;
-  int s = 0;
-  for (; s + 4 <= a.splits; s += 4) {
-    const float v0 = pa[(size_t)s * D], v1 = pa[(size_t)(s + 1) * D], v2 = pa[(size_t)(s + 2) * D], v3 = pa[(size_t)(s + 3) * D];
-    o = fmaf(s_w[hl][s], v0, o);
-    o = fmaf(s_w[hl][s + 1], v1, o);
-    o = fmaf(s_w[hl][s + 2], v2, o);
-    o = fmaf(s_w[hl][s + 3], v3, o);
-  }
-  for (; s < a.splits; ++s) o = fmaf(s_w[hl][s], pa[(size_t)s * D], o);
-  o *= s_inv[hl];
+  const float o = fa::merge_output(a, h0 + hl, d, s_w[hl], s_inv[hl]);
   a.dst[(size_t)h0 * D + threadIdx.x] = o;
   if constexpr (FAMILY != 0) {
     s_out[threadIdx.x] = o;
@@ -438,6 +230,7 @@ int flash_pick_splits(int tokens, int kv_heads, int sm_count, int max_splits) {
 bool flash_split_supported(const FlashArgs& a) {
   const bool d_ok = a.head_dim == 64 || a.head_dim == 128;
   const bool al = (reinterpret_cast<uintptr_t>(a.k) % 16 == 0) && (reinterpret_cast<uintptr_t>(a.v) % 16 == 0) &&
+                  (reinterpret_cast<uintptr_t>(a.q) % 16 == 0) &&
                   a.k_nb1 % 16 == 0 && a.k_nb2 % 16 == 0 && a.v_nb1 % 16 == 0 && a.v_nb2 % 16 == 0;
   return d_ok && al && (int64_t)a.splits * LMAX >= a.tokens;
 }

@@ -85,6 +85,17 @@ struct emelb_ctx {
   int pdl = 0;  // launch decode-chain kernels with programmatic stream serialization
   int* next_sched() { int* p = gemv_sched + 2 * sched_next; sched_next = (sched_next + 1) % emelb::kSchedSlots; return p; }
   int* status_word() { return gemv_sched + 2 * emelb::kSchedSlots; }
+  // scratch of the whole-token decode kernel's products: block values per row (rows whose K spans several
+  // chunk pairs are completed through it) and row-group arrival counters, zero between launches
+  float* bv_table = nullptr;
+  uint64_t bv_table_floats = 0;
+  int* grp_cnt = nullptr;
+  uint64_t grp_cnt_ints = 0;
+  // whole-token decode kernel: grid barrier {arrivals, generation, abort, -} and the attention units' arrival
+  // counters (kTokenCounters ints), all zero between launches
+  unsigned* token_bar = nullptr;
+  int* token_cnt = nullptr;
+  static constexpr int kTokenCounters = 1024;
   // argmax candidates and result cells
   float* part_val = nullptr;
   int* part_idx = nullptr;

@@ -33,6 +33,7 @@ extern thread_local bool g_pdl_launch;
   ::emelb::launch_kernel(kern, dim3(grid), dim3(block), smem, st, ::emelb::g_pdl_launch, __VA_ARGS__)
 
 constexpr int kMaxArgmaxParts = 2048;
+
 constexpr int kSchedSlots = 64;   // task-counter slots rotated over consecutive mat-vec launches
 
 struct GemvArgs {
@@ -179,6 +180,41 @@ struct PeerGatherArgs {
   int* status;
 };
 cudaError_t launch_peer_gather(const PeerGatherArgs& a, cudaStream_t st);
+
+// token_kernel.cu — one decode token (all layers) as one persistent kernel
+struct TokenLayerW {       // one layer's weights (device pointers; Q4_K matrices, f32 norm vectors)
+  const uint8_t *wq, *wk, *wv, *wo, *gate, *up, *down;
+  const float *attn_norm, *ffn_norm;
+};
+struct TokenArgs {
+  const TokenLayerW* layers;   // device array, n_layer entries
+  int n_layer, n_embd, n_ff, heads, kv_heads, head_dim;
+  float eps;
+  const int* state;            // {token, position, kv_tokens, step}
+  float *hidden, *q, *ffn;     // f32 vectors: residual stream, rotated queries, SwiGLU product
+  ActPlanesMut attn_planes;    // attention context quantized for the output projection
+  float* attn_f32;             // optional f32 copy of the attention context
+  __half *kcache, *vcache;     // [layer][kv_head][capacity][head_dim]
+  int64_t capacity;
+  const float *rope_cos, *rope_sin;
+  int rope_rot_dim;
+  float attn_scale;
+  int fa_splits;               // KV ranges per KV head (the stand-alone split kernel's choice)
+  float *part_acc, *part_ml;   // split partials (FlashArgs layout)
+  int* kv_cnt;                 // one arrival counter per (KV head, query-head quad): zero between launches
+  float* bv_table;             // block-value table and row-group counters of the products
+  int* grp_cnt;
+  unsigned* bar;               // grid barrier {arrivals, generation, abort}: arrivals and abort zero between launches
+  int* status;
+  unsigned long long* trace;   // optional: CTA 0 stamps %globaltimer at 16 points per layer (phase profile)
+};
+constexpr int kTokenTracePoints = 16;
+struct TokenLaunchState {      // per session, host side
+  size_t smem = 0;
+};
+size_t llama_token_smem_bytes(int n_embd, int n_ff);
+bool llama_token_supported(const TokenArgs& a, int attention_splits, int n_ctx);
+cudaError_t launch_llama_token(const TokenArgs& a, int sm_count, TokenLaunchState* state, cudaStream_t st);
 
 // synth.cu — synthetic N(0, sigma) data generated and block-encoded on the device
 cudaError_t launch_fill_normal(float* out, uint64_t n, uint64_t seed, float sigma, uint64_t offset, cudaStream_t st);

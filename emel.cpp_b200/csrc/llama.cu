@@ -17,6 +17,7 @@
 // so the token stream equals the unsharded one bit for bit — the contract the
 // reference's row-slice fork/join keeps across lane counts
 // (src/emel/kernel/matmul/detail.hpp:36-57).
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -89,6 +90,13 @@ struct emelb_llama {
   // which f32 vector the context's activation planes currently hold, and for which family
   const float* planes_src = nullptr;
   int planes_family = 0;
+  // whole-token kernel (token_kernel.cu): the layers' weight pointers as a device array, rebuilt after a bind
+  TokenLayerW* token_layers = nullptr;
+  bool token_layers_valid = false;
+  bool token_usable = false;     // the model's shapes and types fit that kernel
+  int step_mode = 0;             // 0: the chain of per-operation launches, 1: one kernel per token where it applies
+  TokenLaunchState token_launch;
+  unsigned long long* token_trace = nullptr;   // device stamps of emelb_llama_decode_profile
   std::vector<void*> owned;
 };
 
@@ -112,6 +120,76 @@ bool all_bound(const emelb_llama* s) {
           bound(l.gate) && bound(l.up) && bound(l.down)))
       return false;
   return true;
+}
+
+TokenArgs token_args(emelb_llama* s) {
+  const emelb_llama_config& c = s->cfg;
+  TokenArgs a{};
+  a.layers = s->token_layers;
+  a.n_layer = c.n_layer;
+  a.n_embd = c.n_embd;
+  a.n_ff = c.n_ff;
+  a.heads = c.n_head;
+  a.kv_heads = c.n_head_kv;
+  a.head_dim = c.head_dim;
+  a.eps = c.rms_eps;
+  a.state = s->state;
+  a.hidden = s->hidden;
+  a.q = s->q;
+  a.ffn = s->ffn;
+  a.attn_planes = ActPlanesMut{s->c->act_qs, s->c->act_d, s->c->act_bsums};
+  a.attn_f32 = nullptr;
+  a.kcache = s->kcache;
+  a.vcache = s->vcache;
+  a.capacity = s->capacity;
+  a.rope_cos = s->rope_cos;
+  a.rope_sin = s->rope_sin;
+  a.rope_rot_dim = c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim;
+  a.attn_scale = 1.0f / std::sqrt((float)c.head_dim);
+  a.fa_splits = s->fa_splits;
+  a.part_acc = s->c->fa_part_acc;
+  a.part_ml = s->c->fa_part_ml;
+  a.kv_cnt = s->c->token_cnt;
+  a.bv_table = s->c->bv_table;
+  a.grp_cnt = s->c->grp_cnt;
+  a.bar = s->c->token_bar;
+  a.status = s->c->status_word();
+  a.trace = nullptr;
+  return a;
+}
+
+// Whether one decode token of this session can run as the single persistent kernel, and its device-side layer
+// table (uploaded here, outside any capture).  The kernel takes unsharded sessions whose layer matrices are all
+// Q4_K with 16-byte aligned rows, adjacent-pair RoPE and the fast attention.
+void prepare_token_kernel(emelb_llama* s) {
+  if (s->token_layers_valid) return;
+  s->token_layers_valid = true;
+  s->token_usable = false;
+  const emelb_llama_config& c = s->cfg;
+  if (s->G != 1 || c.rope_neox || (c.head_dim & 1) || !all_bound(s)) return;
+  std::vector<TokenLayerW> host(c.n_layer);
+  for (int l = 0; l < c.n_layer; ++l) {
+    const Layer& w = s->layers[l];
+    const Tensor* mats[7] = {&w.wq, &w.wk, &w.wv, &w.wo, &w.gate, &w.up, &w.down};
+    for (const Tensor* t : mats)
+      if (t->type != T_Q4_K || (t->K % 2048) != 0 || (reinterpret_cast<uintptr_t>(t->dev) % 16) != 0) return;
+    if ((reinterpret_cast<uintptr_t>(w.attn_norm.dev) % 16) != 0 || (reinterpret_cast<uintptr_t>(w.ffn_norm.dev) % 16) != 0) return;
+    host[l] = TokenLayerW{w.wq.dev, w.wk.dev, w.wv.dev, w.wo.dev, w.gate.dev, w.up.dev, w.down.dev,
+                          reinterpret_cast<const float*>(w.attn_norm.dev), reinterpret_cast<const float*>(w.ffn_norm.dev)};
+  }
+  TokenArgs probe = token_args(s);
+  if (!llama_token_supported(probe, s->fa_splits, c.n_ctx)) return;
+  if (c.n_head > emelb_ctx::kTokenCounters) return;   // one arrival counter per group of query heads
+  // the widest product's block-value table: rows padded to 4, K/256 floats each
+  const uint64_t need = std::max<uint64_t>((uint64_t)c.n_embd * (c.n_ff / 256), (uint64_t)c.n_embd * (c.n_head * c.head_dim / 256));
+  if (need > s->c->bv_table_floats || (uint64_t)(2 * c.n_ff + 3) / 4 > s->c->grp_cnt_ints) return;
+  if (!s->token_layers && !dev_alloc(s, (void**)&s->token_layers, sizeof(TokenLayerW) * (size_t)c.n_layer)) return;
+  if (cudaMemcpyAsync(s->token_layers, host.data(), sizeof(TokenLayerW) * host.size(), cudaMemcpyHostToDevice, s->c->stream) != cudaSuccess ||
+      cudaStreamSynchronize(s->c->stream) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  s->token_usable = true;
 }
 
 struct Enqueue {
@@ -411,7 +489,13 @@ struct Enqueue {
     s->planes_src = nullptr;
     check(launch_embed_row(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->state, s->hidden, c.n_embd, st));
     ++launches;
-    for (int l = 0; l < c.n_layer; ++l) {
+    const bool one_kernel = s->token_usable && s->step_mode == 1 && s->c->attention_mode == 0 && G == 1;
+    if (one_kernel) {
+      // every layer inside one persistent kernel (token_kernel.cu)
+      check(launch_llama_token(token_args(s), s->c->sm_count, &s->token_launch, st));
+      ++launches;
+    }
+    for (int l = 0; l < c.n_layer && !one_kernel; ++l) {
       const Layer& w = s->layers[l];
       bool roped = false;
       {
@@ -486,6 +570,7 @@ cudaGraphExec_t step_graph(emelb_llama* s, Mode mode, int token, int position) {
     cudaGraphExecDestroy(s->graphs[mode]);
     s->graphs[mode] = nullptr;
   }
+  prepare_token_kernel(s);
   // one eager pass first: sets per-kernel attributes outside the capture
   if (!ctx_cuda_ok(s->c, launch_step_begin(s->state, token, position, s->c->stream))) return nullptr;
   Enqueue warm{s, s->c->stream};
@@ -519,22 +604,35 @@ bool valid_step(const emelb_llama* s, int token, int position) {
 
 extern "C" {
 
-uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_llama** out) {
-  if (!c || !cfg || !out) return EMELB_INVALID_REQUEST;
-  *out = nullptr;
+uint32_t emelb_llama_check_config(const emelb_llama_config* cfg) {
+  if (!cfg) return EMELB_INVALID_REQUEST;
   const emelb_llama_config& g = *cfg;
   const bool sane = g.n_layer > 0 && g.n_embd > 0 && g.n_embd % 256 == 0 && g.n_head > 0 && g.n_head_kv > 0 &&
                     g.n_head % g.n_head_kv == 0 && g.head_dim > 1 && g.n_ff > 0 && g.n_ff % 256 == 0 && g.n_vocab > 0 &&
                     g.n_ctx > 0 && g.rope_dim > 1 && g.rope_dim % 2 == 0 && g.shard_count >= 1 && g.shard_rank >= 0 &&
-                    g.shard_rank < g.shard_count && (int64_t)g.n_head * g.head_dim <= (int64_t)c->act_capacity &&
-                    (int64_t)g.n_ff <= (int64_t)c->act_capacity;
+                    g.shard_rank < g.shard_count;
   if (!sane) return EMELB_INVALID_REQUEST;
   const int G = g.shard_count;
   if (G > 1) {
-    // row intervals must be whole heads / whole rows on every rank, and the context's communicator must match
-    if (g.n_head_kv % G != 0 || g.n_embd % G != 0 || g.n_ff % G != 0 || g.n_vocab % G != 0) return EMELB_INVALID_REQUEST;
-    if (!c->comm || c->comm_world != G || c->comm_rank != g.shard_rank) return EMELB_INVALID_REQUEST;
+    // row intervals must be whole heads / whole rows on every rank ...
+    if (G > kMaxPeers || g.n_head_kv % G != 0 || g.n_embd % G != 0 || g.n_ff % G != 0 || g.n_vocab % G != 0) return EMELB_INVALID_REQUEST;
+    // ... and every interval that is joined across ranks is moved in 16-byte units: the f32 intervals of the
+    // attention context, the hidden vector, the gate / up / SwiGLU vectors and the logits
+    const int64_t q_l = (int64_t)g.n_head * g.head_dim / G;
+    if (q_l % 4 != 0 || (g.n_embd / G) % 4 != 0 || (g.n_ff / G) % 4 != 0 || (g.n_vocab / G) % 4 != 0) return EMELB_INVALID_REQUEST;
   }
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_llama** out) {
+  if (!c || !cfg || !out) return EMELB_INVALID_REQUEST;
+  *out = nullptr;
+  const emelb_llama_config& g = *cfg;
+  if (emelb_llama_check_config(cfg) != EMELB_OK) return EMELB_INVALID_REQUEST;
+  if ((int64_t)g.n_head * g.head_dim > (int64_t)c->act_capacity || (int64_t)g.n_ff > (int64_t)c->act_capacity) return EMELB_INVALID_REQUEST;
+  const int G = g.shard_count;
+  // the context's communicator must match the shard layout
+  if (G > 1 && (!c->comm || c->comm_world != G || c->comm_rank != g.shard_rank)) return EMELB_INVALID_REQUEST;
   cudaSetDevice(c->device);
   emelb_llama* s = new (std::nothrow) emelb_llama();
   if (!s) return EMELB_INTERNAL_ERROR;
@@ -692,6 +790,7 @@ uint32_t emelb_llama_bind(emelb_llama* s, int32_t layer, int32_t role, const eme
   *slot = x;
   // bindings changed: captured steps hold stale pointers
   for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;
+  s->token_layers_valid = false;
   return EMELB_OK;
 }
 
@@ -868,6 +967,35 @@ uint32_t emelb_llama_exchange_detach(emelb_llama* s) {
     for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;   // captured steps hold the peer pointers
   s->peers_attached = false;
   cudaGetLastError();
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_decode_profile(emelb_llama* s, int32_t token, int32_t position, uint64_t* stamps_ns, uint64_t stamps_count) {
+  if (!s || !stamps_ns || !valid_step(s, token, position) || !all_bound(s)) return EMELB_INVALID_REQUEST;
+  const uint64_t need = (uint64_t)s->cfg.n_layer * kTokenTracePoints;
+  if (stamps_count < need) return EMELB_INVALID_REQUEST;
+  emelb_ctx* c = s->c;
+  cudaSetDevice(c->device);
+  prepare_token_kernel(s);
+  if (!s->token_usable || c->attention_mode != 0) return EMELB_UNSUPPORTED_OP;
+  if (!s->token_trace && !dev_alloc(s, (void**)&s->token_trace, need * sizeof(unsigned long long))) return EMELB_INTERNAL_ERROR;
+  bool ok = ctx_cuda_ok(c, cudaMemsetAsync(s->token_trace, 0, need * sizeof(unsigned long long), c->stream));
+  ok = ok && ctx_cuda_ok(c, launch_step_begin(s->state, token, position, c->stream));
+  ok = ok && ctx_cuda_ok(c, launch_embed_row(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->state, s->hidden, s->cfg.n_embd, c->stream));
+  TokenArgs a = token_args(s);
+  a.trace = s->token_trace;
+  ok = ok && ctx_cuda_ok(c, launch_llama_token(a, c->sm_count, &s->token_launch, c->stream));
+  ok = ok && ctx_cuda_ok(c, cudaMemcpyAsync(stamps_ns, s->token_trace, need * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
+  ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
+  c->diag.kernel_launches += 3;
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_llama_set_step_mode(emelb_llama* s, int32_t mode) {
+  if (!s || mode < 0 || mode > 1) return EMELB_INVALID_REQUEST;
+  if (s->step_mode != mode)
+    for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;   // captured steps hold the other route
+  s->step_mode = mode;
   return EMELB_OK;
 }
 

@@ -22,6 +22,11 @@
 //  * The first call on each device looks up the array's device address (a host
 //    side step, done once per device with that device current).  Make that
 //    first call outside any stream capture.
+//  * The calling thread's current device is the same after the call as before it.
+//  * There is no context to report through, so a copy wait that ran out inside
+//    the kernel (the bounded waits of the streaming kernel) is not reported: the
+//    kernel raises a word in the scratch array that stays raised, nothing reads it.
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 
@@ -45,8 +50,23 @@ constexpr size_t kNoAllocScratchBytes = kQsBytes + kDBytes + kBsBytes + kSchedBy
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 constexpr int kMaxDevices = 64;
-unsigned char* g_scratch_addr[kMaxDevices] = {};
+// the address is published last, with release order: a thread that sees it also sees the SM count
+std::atomic<unsigned char*> g_scratch_addr[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
+
+// makes `device` current for the call and puts the caller's device back on every return path
+struct DeviceScope {
+  int previous = -1;
+  bool ok = false;
+  explicit DeviceScope(int device) {
+    if (cudaGetDevice(&previous) != cudaSuccess) previous = -1;
+    ok = cudaSetDevice(device) == cudaSuccess;
+  }
+  ~DeviceScope() {
+    if (previous >= 0) cudaSetDevice(previous);
+    cudaGetLastError();
+  }
+};
 
 void explain(char* text, uint64_t bytes, const char* msg) {
   if (text && bytes) {
@@ -79,12 +99,13 @@ extern "C" uint32_t emelb_mul_mat_vec_noalloc(int device, void* stream, int32_t 
   }
   if (m > 0x7fffffffull) return refuse(error_text, error_text_bytes, "row count out of range");
 
-  if (cudaSetDevice(device) != cudaSuccess) {
+  DeviceScope scope(device);
+  if (!scope.ok) {
     cudaGetLastError();
     explain(error_text, error_text_bytes, "cudaSetDevice failed");
     return EMELB_INTERNAL_ERROR;
   }
-  if (!g_scratch_addr[device]) {
+  if (!g_scratch_addr[device].load(std::memory_order_acquire)) {
     // once per device, with that device current
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
@@ -95,9 +116,9 @@ extern "C" uint32_t emelb_mul_mat_vec_noalloc(int device, void* stream, int32_t 
       return EMELB_INTERNAL_ERROR;
     }
     g_sm_count[device] = prop.multiProcessorCount;
-    g_scratch_addr[device] = static_cast<unsigned char*>(p);
+    g_scratch_addr[device].store(static_cast<unsigned char*>(p), std::memory_order_release);
   }
-  unsigned char* base = g_scratch_addr[device];
+  unsigned char* base = g_scratch_addr[device].load(std::memory_order_acquire);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   ActPlanesMut planes{};
@@ -106,8 +127,9 @@ extern "C" uint32_t emelb_mul_mat_vec_noalloc(int device, void* stream, int32_t 
   planes.bsums = reinterpret_cast<int16_t*>(base + kQsBytes + kDBytes);
   int* sched = reinterpret_cast<int*>(base + kQsBytes + kDBytes + kBsBytes);
 
-  // the task counter must start at zero whatever the previous call left behind
-  cudaError_t e = cudaMemsetAsync(sched, 0, 4 * sizeof(int), st);
+  // the task counter (two ints) must start at zero whatever the previous call left behind; the word after
+  // it is the kernel's "a wait ran out" mark and is left alone
+  cudaError_t e = cudaMemsetAsync(sched, 0, 2 * sizeof(int), st);
   if (e == cudaSuccess) e = quantize_into_planes(weight_type, x_dev, 1, 1, (int)k, planes, st);
   if (e == cudaSuccess) {
     GemvArgs a{};

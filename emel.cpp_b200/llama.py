@@ -24,6 +24,7 @@ class Config(C.Structure):
 
 
 SIGNATURES = {
+    "emelb_llama_check_config": [C.POINTER(Config)],
     "emelb_llama_create": [_P, C.POINTER(Config), C.POINTER(_P)],
     "emelb_llama_destroy": [_P],
     "emelb_llama_bind": [_P, C.c_int32, C.c_int32, C.POINTER(eb.View)],
@@ -31,6 +32,8 @@ SIGNATURES = {
     "emelb_llama_prefill": [_P, C.POINTER(C.c_int32), C.c_int32, C.c_int32],
     "emelb_llama_generate": [_P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32)],
     "emelb_llama_launches_per_token": [_P, C.POINTER(C.c_int32)],
+    "emelb_llama_set_step_mode": [_P, C.c_int32],
+    "emelb_llama_decode_profile": [_P, C.c_int32, C.c_int32, _P, C.c_uint64],
     "emelb_llama_exchange_export": [_P, _P, C.c_uint64],
     "emelb_llama_exchange_attach": [_P, _P, C.c_uint64],
     "emelb_llama_exchange_detach": [_P],
@@ -52,6 +55,11 @@ def config(n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx, r
     return Config(n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx,
                   head_dim if rope_dim is None else rope_dim, rope_neox, rope_freq_base, rms_eps, kv_block,
                   shard_rank, shard_count)
+
+
+def check_config(cfg: Config) -> int:
+    """emelb_llama_check_config: the error bitmask for a configuration, without a device."""
+    return int(eb.lib().emelb_llama_check_config(C.byref(cfg)))
 
 
 def matrix_shapes(cfg: Config):
@@ -156,3 +164,14 @@ class Session:
         v = C.c_int32(0)
         eb.lib().emelb_llama_launches_per_token(self._h, C.byref(v))
         return v.value
+
+    def set_step_mode(self, mode: int) -> bool:
+        """0: the chain of per-operation launches (default); 1: one persistent kernel per token where the session qualifies."""
+        return self._ret(eb.lib().emelb_llama_set_step_mode(self._h, mode))
+
+    def decode_profile(self, token: int, position: int):
+        """-> (n_layer, 16) nanosecond stamps of the one-kernel step (see emelb_llama_decode_profile)."""
+        out = np.zeros((self.cfg.n_layer, 16), np.uint64)
+        if not self._ret(eb.lib().emelb_llama_decode_profile(self._h, token, position, out.ctypes.data, out.size)):
+            raise eb.BackendError(f"decode_profile failed with error mask {self.last_error}")
+        return out

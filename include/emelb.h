@@ -295,7 +295,10 @@ EMELB_API uint32_t emelb_graph_destroy(emelb_ctx* ctx, void* graph);
  * message in error_text (optional buffer).  Calls on one device share the array:
  * do not let two of them overlap on the GPU.  The first call on a device does a
  * one-time address look-up; make it outside any stream capture.  `stream` is
- * the cudaStream_t to enqueue on (NULL = default stream). ---- */
+ * the cudaStream_t to enqueue on (NULL = default stream).  The calling thread's
+ * current device is left as it was.  Having no context, the call cannot report
+ * a copy wait that ran out inside the kernel (emelb_sync does that for the
+ * context-based calls): use it where a lost device is detected by other means. ---- */
 EMELB_API uint32_t emelb_mul_mat_vec_noalloc(int device, void* stream,
                                              int32_t weight_type,
                                              const void* weights_dev, uint64_t k,

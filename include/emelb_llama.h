@@ -71,6 +71,14 @@ enum {
 
 typedef struct emelb_llama emelb_llama;
 
+/* pure check of a configuration (no device needed): EMELB_OK or
+ * EMELB_INVALID_REQUEST.  Beyond the plain range checks, a sharded layout
+ * (shard_count G > 1, at most 8) must give every rank whole KV heads and whole
+ * rows, and every row interval that is joined across ranks — n_head*head_dim/G,
+ * n_embd/G, n_ff/G and n_vocab/G f32 values — must be a multiple of 4 values
+ * (joins move 16-byte units).  emelb_llama_create applies it first. */
+EMELB_API uint32_t emelb_llama_check_config(const emelb_llama_config* cfg);
+
 /* allocates activations, the f16 KV cache in the flash layout
  * [layer][kv_head][capacity][head_dim]
  * (src/emel/text/generator/detail.hpp:3010-3048) and the RoPE table */
@@ -127,6 +135,29 @@ EMELB_API uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* ha
  * across ranks: every rank detaches, the caller synchronises the ranks, then the
  * sessions are destroyed — no arena is freed while a peer still maps it. */
 EMELB_API uint32_t emelb_llama_exchange_detach(emelb_llama* s);
+
+/* How a decode step is enqueued.  0 (default): the chain of per-operation
+ * launches.  1: where the session qualifies (unsharded, Q4_K layer matrices with
+ * K a multiple of 2048, head size 128, adjacent-pair RoPE, fast attention mode),
+ * all layers of a token run as ONE persistent kernel, one CTA per SM, with grid
+ * barriers between the phases of a layer and producer warps that keep the
+ * weights streaming across them; sessions that do not qualify keep the chain.
+ * Both give the same numbers bit for bit.  No reference counterpart (its
+ * generator calls the kernel actor once per operation,
+ * src/emel/text/generator/detail.hpp:3746-3926). */
+EMELB_API uint32_t emelb_llama_set_step_mode(emelb_llama* s, int32_t mode);
+
+/* Phase profile of the one-kernel step (diagnostics, like the reference's
+ * capture_diagnostics counters): runs the layers of one decode step at
+ * (token, position) — the KV row of `position` is written as in a normal step,
+ * no logits are produced — and returns, for each layer, 16 nanosecond stamps
+ * taken by one CTA: 0 layer start, 1 Q/K/V input staged, 2 Q/K/V products done,
+ * 3/5/8/11/14 after the grid barriers, 4 attention done, 6 output-projection
+ * input staged, 7 output projection done, 9 gate/up input staged, 10 gate/up
+ * done, 12 SwiGLU staged, 13 down projection done.  stamps_count >= 16 * n_layer.
+ * EMELB_UNSUPPORTED_OP when the session does not qualify for the one-kernel step. */
+EMELB_API uint32_t emelb_llama_decode_profile(emelb_llama* s, int32_t token, int32_t position,
+                                              uint64_t* stamps_ns, uint64_t stamps_count);
 
 /* kernels launched per decode step (for launch accounting) */
 EMELB_API uint32_t emelb_llama_launches_per_token(const emelb_llama* s, int32_t* out);
