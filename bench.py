@@ -115,7 +115,7 @@ def dist_setup(n_gpus):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl" if os.environ.get("EMELB_BENCH_BACKEND", "nccl") == "nccl" else "gloo")
+        dist.init_process_group("nccl")
     return rank, world, local
 
 
@@ -329,10 +329,9 @@ def run_reference_gemv(args):
     x = rng.standard_normal((k, n), dtype=np.float32)
     y = np.zeros((m, n), np.float32)
     op = ob.mul_mat_op(w, t, k, m, x, n, y)
-    cores = os.cpu_count() or 1
-    lanes = min(cores, 64)
+    lanes = min(8, os.cpu_count() or 1)   # the reference's own maximum lane count (src/emel/kernel/matmul/guards.hpp:12-14)
     kw = {"route": "avx2", "lanes": lanes} if kind == "reference" else {}
-    per_step = max(1, min(sp["copies"], 8))           # bounded sample of the step's mat-vecs
+    per_step = sp["copies"]               # a step is the same number of mat-vecs as on the GPU arm
     for _ in range(args.warmup):
         assert lib.mul_mat(op, **kw)
     t0 = time.perf_counter()
@@ -342,11 +341,14 @@ def run_reference_gemv(args):
     gbs = sp["alg_bytes"] * args.steps * per_step / dt / 1e9
     line = {"impl": "reference", "metric": METRIC_GEMV if args.workload == "gemv_q4_k" else "Q8_0 GEMV HBM GB/s",
             "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(dt / args.steps * 1e3 * sp["copies"] / per_step, 4), "higher_is_better": True,
+            "ms_per_step": round(dt / args.steps * 1e3, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot (AVX2 maddubs) + f32 scales", "data": "synthetic",
-            "config": {"workload": sp["name"], "rows": m, "cols": k, "tokens": n},
+            "config": {"workload": sp["name"], "rows": m, "cols": k, "tokens": n, "weight_copies_per_step": sp["copies"],
+                       "launch": "each step is that many op_mul_mat calls on the host",
+                       "l2_policy": "one weight matrix reused (the CPU kernels are compute-bound)",
+                       "parallelism": f"{lanes} host threads (row slices, the reference's maximum lane count)"},
             "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": lanes if kind == "reference" else 1, "kind": kind,
-                             "sample": f"{per_step} of the step's {sp['copies']} mat-vecs per step, scaled"},
+                             "sample": f"{args.steps} steps of {per_step} mat-vecs, measured"},
             "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -499,7 +501,7 @@ def run_reference_prefill(args):
         return
     sp = prefill_spec(args)
     t0 = time.perf_counter()
-    res = [cpu_baseline_prefill(sp, 2.0, lanes=min(os.cpu_count() or 1, 64)) for _ in range(max(1, min(args.steps, 5)))]
+    res = [cpu_baseline_prefill(sp, 2.0, lanes=min(os.cpu_count() or 1, 8)) for _ in range(max(1, min(args.steps, 5)))]
     v = float(np.median([r["value"] for r in res]))
     line = {"impl": "reference", "metric": "prefill GEMM TFLOP/s", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sp["flops"] / (v * 1e12) * 1e3, 2),
@@ -522,7 +524,7 @@ def load_spec(args):
 
 def write_load_file(sp, path, seed=20):
     """Streams a GGUF v3 file to `path`: random block bytes (the loader never decodes them)."""
-    from tests import gguf_image as gi
+    from emel_cpp_b200 import gguf_image as gi
     rng = np.random.default_rng(seed)
     pool = rng.integers(0, 256, size=64 << 20, dtype=np.uint8)
     tensors = []
@@ -604,10 +606,7 @@ def run_load(args):
         def one_load(mode):
             """mode: None = the default route (one pipelined pass over the file); "each" = the same route, one
             call per tensor; "plain" / "register" = the alternative routes of the library, whole file."""
-            if mode in ("plain", "register"):
-                os.environ["EMELB_UPLOAD_MODE"] = mode
-            else:
-                os.environ.pop("EMELB_UPLOAD_MODE", None)
+            assert be.set_upload_route(mode if mode in ("plain", "register") else "ring")
             t0 = time.perf_counter()
             f = gguf.File(path)
             t1 = time.perf_counter()
@@ -652,7 +651,7 @@ def run_load(args):
                     total_s.append(t)
                     unload(f, n, check=(k == 0))
                 results[{None: "staged", "each": "staged_per_tensor"}.get(mode, mode)] = (float(np.mean(total_s)), float(np.median(parse_s)))
-            os.environ.pop("EMELB_UPLOAD_MODE", None)
+            assert be.set_upload_route("ring")
         sec = max_over_ranks(results["staged"][0], world, f"cuda:{local}")
         if rank != 0:
             return
@@ -667,7 +666,7 @@ def run_load(args):
                            "timer": "host wall clock around the synchronous open + upload calls (page cache warm)",
                            "open_file_us": results["staged"][1] * 1e6, "parse_us": lib_us,
                            "routes_gbs": {k: file_bytes / v[0] / 1e9 for k, v in results.items()},
-                           "upload_threads": int(os.environ.get("EMELB_UPLOAD_THREADS", min(16, os.cpu_count() or 1)))},
+                           "upload_threads": min(16, os.cpu_count() or 1)},
                 "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": file_bytes, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
@@ -732,6 +731,85 @@ def decode_tensors(sh, out_type):
     return out
 
 
+def build_decode_session(be, sh, out_type, n_ctx, rank, G, dist=None, seed0=5000, peer=True):
+    """A decoder session of shape `sh` with synthetic weights (N(0, 0.02) encoded on the device, norm
+    weights 1.0).  G > 1: this rank's row interval of every matrix, the joins over peer stores."""
+    import emel_cpp_b200 as eb
+    from emel_cpp_b200 import llama as el
+    cfg = el.config(sh["n_layer"], sh["n_embd"], sh["n_head"], sh["n_head_kv"], sh["head_dim"], sh["n_ff"], sh["n_vocab"], n_ctx,
+                    shard_rank=rank if G > 1 else 0, shard_count=G)
+    sess = el.Session(be, cfg)
+    peer_joins = False
+    if G > 1 and peer:
+        handles = [None] * G
+        dist.all_gather_object(handles, sess.exchange_export())
+        assert sess.exchange_attach(handles), sess.last_error
+        dist.barrier()          # every rank has mapped its peers before anybody's first join
+        peer_joins = True
+    info = dict(weight_bytes=0, q4k_bytes=0, q4k_ops=[], peer_joins=peer_joins, allocs=[])
+    r = rank if G > 1 else 0
+    for i, (layer, role, k, m, t) in enumerate(decode_tensors(sh, out_type)):
+        row0 = 0
+        if role != el.TOKEN_EMBD:
+            row0, m = el.shard_rows(m, r, G)     # this rank's rows of the same seeded matrix
+        nbytes = m * eb.row_bytes(t, k)
+        d = be.alloc(nbytes)
+        info["allocs"].append(d)
+        assert be.synth_fill(d, t, m * k, seed0 + i, 0.02, row0 * k), be.last_error
+        assert sess.bind_matrix(layer, role, d, t), sess.last_error
+        if role != el.TOKEN_EMBD:
+            info["weight_bytes"] += nbytes
+            if t == eb.Q4_K and layer >= 0:
+                info["q4k_bytes"] += nbytes
+                info["q4k_ops"].append((layer, role, d, t, k, m))
+    ones = be.alloc(4 * sh["n_embd"])
+    info["allocs"].append(ones)
+    assert be.to_device(ones, np.ones(sh["n_embd"], np.float32))
+    assert sess.bind_norm(-1, el.OUTPUT_NORM, ones)
+    for l in range(sh["n_layer"]):
+        assert sess.bind_norm(l, el.ATTN_NORM, ones) and sess.bind_norm(l, el.FFN_NORM, ones)
+    assert be.sync()
+    return sess, info
+
+
+def release_decode_session(be, sess, info, world):
+    barrier(world)              # no rank unmaps an exchange arena while a peer may still store into it
+    sess.exchange_detach()
+    barrier(world)              # ... nor frees one that a peer still maps
+    sess.close()
+    for d in info["allocs"]:
+        be.free(d)
+
+
+def time_cfg1_matvec(be, timed_region, copies=68):
+    """Configuration 1 inside the decode run: the 4096 x 4096 Q4_K mat-vec over `copies` distinct weight copies
+    (640 MB > L2), activations already quantized, one CUDA-graph replay per pass.  -> (us per launch, bytes)."""
+    import emel_cpp_b200 as eb
+    k = m = 4096
+    wbytes = m * eb.row_bytes(eb.Q4_K, k)
+    w = be.alloc(copies * wbytes)
+    for c in range(copies):
+        assert be.synth_fill(w + c * wbytes, eb.Q4_K, m * k, 900 + c, 0.02, 0)
+    x, y = be.alloc(4 * k), be.alloc(4 * m)
+    assert be.synth_fill(x, eb.F32, k, 11, 1.0, 0) and be.sync()
+    ops = [eb.mul_mat_op(w + c * wbytes, eb.Q4_K, k, m, x, 1, y) for c in range(copies)]
+    assert be.prepare_rhs(eb.dense_view(x, eb.F32, [1, k]), eb.Q4_K)
+    for op in ops[:4]:
+        assert be.mul_mat_prepared(op)
+    be.sync()
+    assert be.graph_begin()
+    for op in ops:
+        assert be.mul_mat_prepared(op)
+    g = be.graph_end()
+    for _ in range(3):
+        be.graph_launch(g)
+    ms, _ = timed_region(lambda: [be.graph_launch(g) for _ in range(5)])
+    be.graph_destroy(g)
+    for d in (w, x, y):
+        be.free(d)
+    return ms * 1e3 / (5 * copies), wbytes + 4672 + 4 * m
+
+
 def run_decode(args):
     import torch
     import emel_cpp_b200 as eb
@@ -747,59 +825,21 @@ def run_decode(args):
     n_ctx = ((prompt_len + warmup + steps + 15) // 16) * 16
     be = eb.Backend(local)
     stream = torch.cuda.ExternalStream(be.stream(), device=dev)
-    shard = args.shard and world > 1
-    if shard:
+    # N > 1: ONE sequence with every matrix row-sharded over the N GPUs (the multi-GPU design of this path);
+    # --replicas runs N independent sequences instead
+    shard = world > 1 and not args.replicas
+    dist = None
+    if world > 1:
         import torch.distributed as dist
+    if shard:
         box = [eb.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         assert be.comm_init(rank, world, box[0]), be.last_error
     G, r = (world, rank) if shard else (1, 0)
-    cfg = el.config(sh["n_layer"], sh["n_embd"], sh["n_head"], sh["n_head_kv"], sh["head_dim"], sh["n_ff"], sh["n_vocab"], n_ctx,
-                    shard_rank=r, shard_count=G)
-    sess = el.Session(be, cfg)
-    peer_joins = False
-    if shard and os.environ.get("EMELB_SHARD_JOIN", "peer") == "peer":
-        handles = [None] * world
-        dist.all_gather_object(handles, sess.exchange_export())
-        assert sess.exchange_attach(handles), sess.last_error
-        dist.barrier()          # every rank has mapped its peers before anybody's first join
-        peer_joins = True
-
-    # weights N(0, 0.02) encoded on the device; norm weights 1.0 (each rank builds its own replica)
-    tensors = decode_tensors(sh, out_type)
-    weight_bytes, q4k_bytes, q4k_ops = 0, 0, []
-    for i, (layer, role, k, m, t) in enumerate(tensors):
-        row0 = 0
-        if role != el.TOKEN_EMBD:
-            row0, m = el.shard_rows(m, r, G)     # this rank's rows of the same seeded matrix
-        nbytes = m * eb.row_bytes(t, k)
-        d = be.alloc(nbytes)
-        assert be.synth_fill(d, t, m * k, 5000 + i, 0.02, row0 * k), be.last_error
-        assert sess.bind_matrix(layer, role, d, t), sess.last_error
-        if role != el.TOKEN_EMBD:
-            weight_bytes += nbytes
-            if t == eb.Q4_K and layer >= 0:
-                q4k_bytes += nbytes
-                q4k_ops.append((layer, role, d, t, k, m))
-    ones = be.alloc(4 * sh["n_embd"])
-    assert be.to_device(ones, np.ones(sh["n_embd"], np.float32))
-    assert sess.bind_norm(-1, el.OUTPUT_NORM, ones)
-    for l in range(sh["n_layer"]):
-        assert sess.bind_norm(l, el.ATTN_NORM, ones) and sess.bind_norm(l, el.FFN_NORM, ones)
-    assert be.sync()
-
-    prompt = np.random.Generator(np.random.PCG64(42 + (0 if shard else rank))).integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32)
-    t0 = time.perf_counter()
-    if not args.profile_skip_prefill:
-        assert sess.prefill(prompt[:-1], 0), sess.last_error
-    prefill_s = time.perf_counter() - t0
-    prefill_warm_s = None
-    if not args.profile_skip_prefill:
-        # the same prompt again (same KV rows): the first pass also sized the batch buffers
-        t0 = time.perf_counter()
-        assert sess.prefill(prompt[:-1], 0), sess.last_error
-        prefill_warm_s = time.perf_counter() - t0
-    pos0 = prompt_len - 1
+    sess, info = build_decode_session(be, sh, out_type, n_ctx, r, G, dist, peer=args.join == "peer")
+    if args.one_kernel:
+        assert sess.set_step_mode(1)
+    peer_joins, weight_bytes, q4k_bytes, q4k_ops = info["peer_joins"], info["weight_bytes"], info["q4k_bytes"], info["q4k_ops"]
 
     def timed_region(fn):
         be.sync()
@@ -814,24 +854,43 @@ def run_decode(args):
         barrier(world)
         return max_over_ranks(e0.elapsed_time(e1), world, dev), out
 
-    with ClockSampler(local) as clk:
-        # device-fed greedy loop: W warm-up tokens, then K timed tokens, no host round trip between steps
-        warm_ids = sess.generate(int(prompt[-1]), pos0, warmup)
-        ms, ids = timed_region(lambda: sess.generate(int(warm_ids[-1]), pos0 + warmup, steps))
-        # end to end: one C-ABI call per token, token id in, next token id out (host round trip every step)
-        d0 = be.diagnostics()
-        tok = int(prompt[-1])
-        for i in range(warmup):
-            tok = sess.decode(tok, pos0 + i)
+    def decode_run(sess, prompt, n_steps, n_warm, host_loop=True):
+        """prefill (twice: the first pass also sizes the batch buffers), then the device-fed greedy loop and,
+        optionally, the loop with a host round trip per token.  -> dict"""
+        pos0 = len(prompt) - 1
+        t0 = time.perf_counter()
+        assert sess.prefill(prompt[:-1], 0), sess.last_error
+        first = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        assert sess.prefill(prompt[:-1], 0), sess.last_error
+        warm = time.perf_counter() - t0
+        warm_ids = sess.generate(int(prompt[-1]), pos0, n_warm)
+        ms, ids = timed_region(lambda: sess.generate(int(warm_ids[-1]), pos0 + n_warm, n_steps))
+        out = dict(ms=ms, ids=list(ids), prefill_s=first, prefill_warm_s=warm, launches=sess.launches_per_token())
+        if host_loop:
+            # end to end: one C-ABI call per token, token id in, next token id out (host round trip every step)
+            d0 = be.diagnostics()
+            tok = int(prompt[-1])
+            for i in range(n_warm):
+                tok = sess.decode(tok, pos0 + i)
 
-        def host_loop():
-            t, out = tok, []
-            for i in range(steps):
-                t = sess.decode(t, pos0 + warmup + i)
-                out.append(t)
-            return out
-        ms_e, ids_e = timed_region(host_loop)
-        d1 = be.diagnostics()
+            def loop():
+                t, o = tok, []
+                for i in range(n_steps):
+                    t = sess.decode(t, pos0 + n_warm + i)
+                    o.append(t)
+                return o
+            ms_e, ids_e = timed_region(loop)
+            d1 = be.diagnostics()
+            out.update(ms_e=ms_e, ids_e=list(ids_e), d2h=(d1["d2h_bytes"] - d0["d2h_bytes"]) // (n_steps + n_warm))
+        return out
+
+    prompt = np.random.Generator(np.random.PCG64(42 + (0 if shard else rank))).integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32)
+    extras = {}
+    with ClockSampler(local) as clk:
+        res = decode_run(sess, prompt, steps, warmup)
+        assert res["ids"] == res["ids_e"], "device-fed and host-fed greedy loops disagree"
+        ms, ms_e = res["ms"], res["ms_e"]
         # the dominant kernel alone: every Q4_K layer matrix of one token, activations already quantized
         x8 = be.alloc(4 * sh["n_ff"])
         assert be.synth_fill(x8, eb.F32, sh["n_ff"], 9, 1.0, 0)
@@ -873,144 +932,202 @@ def run_decode(args):
             t_ms, _ = timed_region(lambda: [be.graph_launch(g) for _ in range(5)])
             ms_k += t_ms / 5
             n_k += n_ops
+            be.graph_destroy(g)
+        # configuration 1, the mat-vec the headline metric is quoted on first
+        cfg1_us, cfg1_bytes = time_cfg1_matvec(be, timed_region)
+        # the same session through the one-kernel step (every layer of a token in one persistent kernel)
+        if not shard and not args.one_kernel and args.workload == "decode_8b":
+            assert sess.set_step_mode(1)
+            w_ids = sess.generate(int(prompt[-1]), prompt_len - 1, warmup)
+            ms1, ids1 = timed_region(lambda: sess.generate(int(w_ids[-1]), prompt_len - 1 + warmup, steps))
+            if sess.launches_per_token() < res["launches"]:
+                extras["one_kernel_step"] = {"tok_s": round(steps * (1 if shard else world) / (ms1 * 1e-3), 2),
+                                             "kernel_launches_per_token": sess.launches_per_token(),
+                                             "same_tokens_as_launch_chain": list(ids1) == res["ids"]}
+            assert sess.set_step_mode(0)
+        if world > 1 and shard:
+            # beside the headline: N independent replicas of the same model (no collective), and configuration 5
+            # (70B shape) row-sharded over the same N GPUs with a shortened prompt
+            release_decode_session(be, sess, info, world)
+            sess = None
+            s2, i2 = build_decode_session(be, sh, out_type, n_ctx, 0, 1)
+            p2 = np.random.Generator(np.random.PCG64(42 + rank)).integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32)
+            r2 = decode_run(s2, p2, min(steps, 32), warmup, host_loop=False)
+            extras["replicas"] = {"tok_s": round(min(steps, 32) * world / (r2["ms"] * 1e-3), 2), "sequences": world,
+                                  "parallelism": f"{world} independent replicas (one sequence per GPU), no collective"}
+            release_decode_session(be, s2, i2, 1)
+            sh5 = DECODE_SHAPES["decode_70b"]
+            p_len5, st5 = 512, min(steps, 16)
+            s5, i5 = build_decode_session(be, sh5, eb.Q4_K, ((p_len5 + warmup + st5 + 15) // 16) * 16, rank, world, dist, seed0=7000)
+            p5 = np.random.Generator(np.random.PCG64(45)).integers(0, sh5["n_vocab"], size=p_len5, dtype=np.int32)
+            r5 = decode_run(s5, p5, st5, warmup, host_loop=False)
+            extras["cfg5_sharded"] = {"tok_s": round(st5 / (r5["ms"] * 1e-3), 2), "workload": sh5["name"], "prompt_tokens": p_len5,
+                                      "decoded_tokens": st5, "kernel_launches_per_token": r5["launches"],
+                                      "note": "prompt shortened from 8032 to 512 tokens to bound the run"}
+            release_decode_session(be, s5, i5, world)
     clocks = clk.summary()
-    assert list(ids) == list(ids_e), "device-fed and host-fed greedy loops disagree"
 
     seqs = 1 if shard else world
     tok_s = steps * seqs / (ms * 1e-3)
     tok_s_e2e = steps * seqs / (ms_e * 1e-3)
     kv_bytes_per_pos = sh["n_layer"] * 2 * sh["n_head_kv"] * sh["head_dim"] * 2
     ctx_mid = prompt_len + warmup + steps // 2
-    bytes_per_token = weight_bytes + kv_bytes_per_pos * ctx_mid
+    bytes_per_token = weight_bytes * (world if shard else 1) + kv_bytes_per_pos * ctx_mid
     peaks, peak_kind = measured_peaks()
     kernel_gbs = q4k_bytes / (ms_k * 1e-3) / 1e9
+    cfg1_gbs = cfg1_bytes / (cfg1_us * 1e-6) / 1e9
     line = {
         "metric": "decode tok/s", "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "strong" if shard else "weak", "vs_baseline": None,
         "dtype": "int8 dot (dp4a) + f32 scales; f16 KV", "data": "synthetic",
         "config": {"workload": sh["name"], "prompt_tokens": prompt_len, "decoded_tokens": steps, "n_ctx": n_ctx,
-                   "launch": "one CUDA-graph replay per token; the next token id is fed back on the device",
-                   "l2_policy": f"inputs larger than L2: {weight_bytes / 1e9:.2f} GB of weights streamed per token",
+                   "launch": ("one persistent kernel per token plus the output head" if args.one_kernel else "one CUDA-graph replay per token")
+                             + "; the next token id is fed back on the device",
+                   "l2_policy": f"inputs larger than L2: {weight_bytes * (world if shard else 1) / 1e9:.2f} GB of weights streamed per token",
                    "parallelism": "single GPU" if world == 1 else (
                        f"one sequence, matrices row-sharded over {world} GPUs, 4 joins of f32 row intervals per layer "
-                       f"({'peer stores over NVLink, one kernel per join' if peer_joins else 'NCCL all-gather'})" if shard
+                       f"({'peer stores over NVLink, one kernel per join' if peer_joins else 'NCCL all-gather'}; "
+                       "the prompt's batch joins are NCCL all-gathers)" if shard
                        else f"{world} independent replicas (one sequence per GPU), no collective"),
-                   "kernel_launches_per_token": sess.launches_per_token(),
-                   "prefill_s": "skipped: zero-filled KV cache, profiling aid, not a benchmark number" if args.profile_skip_prefill
-                   else round(prefill_s, 3),
-                   "prefill_tok_s": None if prefill_warm_s is None else round((prompt_len - 1) / prefill_warm_s, 1),
+                   "kernel_launches_per_token": res["launches"],
+                   "prefill_s": round(res["prefill_s"], 3),
+                   "prefill_tok_s": round((prompt_len - 1) / res["prefill_warm_s"], 1),
                    "prefill": "prompt tokens in batches of up to 2048: tcgen05 Q4_K products, mma.sync batch attention"
                               + (", row intervals joined by NCCL all-gather" if shard else "")},
         "hbm_gbs_effective": round(bytes_per_token * tok_s / seqs / 1e9, 1),
         "q4_k_gemv_hbm_gbs": round(kernel_gbs, 1), "pct_of_8tbs_nominal": round(100 * kernel_gbs / NOMINAL_HBM_GBS, 2),
-        "e2e": {"value": round(tok_s_e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 8,
-                "d2h_bytes_per_step": (d1["d2h_bytes"] - d0["d2h_bytes"]) // (steps + warmup)},
-        "gpu_launches": sess.launches_per_token() * steps,
+        "e2e": {"value": round(tok_s_e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": res["d2h"]},
+        "gpu_launches": res["launches"] * steps,
         "roofline": {"bound": "hbm", "kernel": "gemv_stream_q4_k_n1", "achieved": round(kernel_gbs, 2), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(kernel_gbs / peaks["hbm_gbs"], 4), "peak_source": f"of {peak_kind}",
                      "us_per_launch": round(ms_k * 1e3 / n_k, 3), "algorithmic_bytes_per_launch": q4k_bytes // n_k,
                      "launches_timed": n_k,
                      # ncu capture of the 14336x4096 launch, scaled by bytes (traffic grows with the weight bytes)
-                     "traffic": (lambda r: None if r is None else int(r * (q4k_bytes // n_k)))(ncu_traffic("q4_k_n1_traffic_over_algorithmic"))},
+                     "traffic": (lambda rr: None if rr is None else int(rr * (q4k_bytes // n_k)))(ncu_traffic("q4_k_n1_traffic_over_algorithmic"))},
+        # configuration 1 (the 4096 x 4096 Q4_K mat-vec BASELINE's metric names first), timed in the same run
+        "roofline_cfg1": {"bound": "hbm", "kernel": "gemv_stream_q4_k_n1", "workload": "cfg1: Q4_K 4096x4096 mat-vec, 68 weight copies (640 MB > L2)",
+                          "achieved": round(cfg1_gbs, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(cfg1_gbs / peaks["hbm_gbs"], 4),
+                          "peak_source": f"of {peak_kind}", "us_per_launch": round(cfg1_us, 3), "algorithmic_bytes_per_launch": cfg1_bytes,
+                          "traffic": ncu_traffic("gemv_stream_q4_k_n1")},
         "clocks": clocks,
     }
+    line.update(extras)
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline_decode(sh, out_type, budget_s=args.cpu_budget)
         print(json.dumps(line), flush=True)
-    barrier(world)              # no rank unmaps an exchange arena while a peer may still store into it
-    sess.exchange_detach()
-    barrier(world)              # ... nor frees one that a peer still maps
-    sess.close()
+    if sess is not None:
+        release_decode_session(be, sess, info, world)
     be.close()
     if world > 1:
-        import torch.distributed as dist
         dist.destroy_process_group()
 
 
-def cpu_decode_sample(sh, out_type, lanes, repeats, ctx):
-    """Seconds per token of the reference's CPU kernels on this shape, from a bounded sample: every
-    matrix product of ONE layer plus that layer's attention over `ctx` cached tokens plus 1/16 of the
-    output projection, scaled to n_layer layers and the full vocabulary."""
-    import emel_cpp_b200 as eb
-    from oracle import bindings as ob
-    lib = ob.ref()
-    kind = "reference" if lib is not None else "port"
-    lib = lib or ob.port()
-    rng = np.random.Generator(np.random.PCG64(1))
+class CpuDecoder:
+    """The reference's CPU kernels driven through one whole decode token of shape `sh`: per layer the seven
+    mat-vecs (AVX2/FMA route, row-sliced over `lanes` threads as kernel::matmul does) and the flash attention
+    over `ctx` cached tokens (single-threaded, as in the reference), then the output projection.  The weight
+    bytes of ONE layer are reused for every layer (random block bytes with sane scales): the kernels' time does
+    not depend on the values, and 4.4 GB of distinct host weights would only add set-up time."""
 
-    def blocks(t, k, m):
-        w = rng.integers(0, 256, size=m * eb.row_bytes(t, k), dtype=np.uint8).reshape(-1, eb.BLOCK_BYTES[t])
-        for off in ({eb.Q4_K: (0, 2), eb.Q6_K: (208,)}[t]):
-            w[:, off + 1] = rng.integers(0x18, 0x30, size=w.shape[0])
-        return w.reshape(-1)
+    def __init__(self, sh, out_type, lanes, ctx):
+        import emel_cpp_b200 as eb
+        from oracle import bindings as ob
+        lib = ob.ref()
+        self.kind = "reference" if lib is not None else "port"
+        self.lib = lib or ob.port()
+        self.sh, self.lanes = sh, lanes
+        rng = np.random.Generator(np.random.PCG64(1))
 
-    qd, kvd = sh["n_head"] * sh["head_dim"], sh["n_head_kv"] * sh["head_dim"]
-    mats = [(sh["n_embd"], qd), (sh["n_embd"], kvd), (sh["n_embd"], kvd), (qd, sh["n_embd"]),
-            (sh["n_embd"], sh["n_ff"]), (sh["n_embd"], sh["n_ff"]), (sh["n_ff"], sh["n_embd"])]
-    vocab_part = sh["n_vocab"] // 16
-    ops, keep = [], []
-    for k, m in mats + [(sh["n_embd"], vocab_part)]:
-        t = eb.Q4_K if (k, m) != (sh["n_embd"], vocab_part) else out_type
-        w, x, y = blocks(t, k, m), rng.standard_normal(k, dtype=np.float32), np.zeros(m, np.float32)
-        keep += [w, x, y]
-        ops.append(ob.mul_mat_op(w, t, k, m, x, 1, y))
-    hd, T = sh["head_dim"], ctx
-    q = rng.standard_normal((sh["n_head"], hd), dtype=np.float32)
-    kc = (rng.standard_normal((sh["n_head_kv"], T, hd), dtype=np.float32) * 0.5).astype(np.float16).view(np.uint16)
-    vc = rng.standard_normal((sh["n_head_kv"], T, hd), dtype=np.float32).astype(np.float16).view(np.uint16)
-    dst = np.zeros((sh["n_head"], hd), np.float32)
-    fop = ob.flash_op(q, kc, vc, dst, hd, sh["n_head"], sh["n_head_kv"], T, T, scale=float(hd) ** -0.5, masked_total=T)
-    kw = {"route": "avx2", "lanes": lanes} if kind == "reference" else {}
-    fkw = {"route": "avx2"} if kind == "reference" else {}
+        def blocks(t, k, m):
+            w = rng.integers(0, 256, size=m * eb.row_bytes(t, k), dtype=np.uint8).reshape(-1, eb.BLOCK_BYTES[t])
+            for off in ({eb.Q4_K: (0, 2), eb.Q6_K: (208,)}[t]):
+                w[:, off + 1] = rng.integers(0x18, 0x30, size=w.shape[0])
+            return w.reshape(-1)
 
-    def once():
-        t0 = time.perf_counter()
-        for op in ops[:-1]:
-            assert lib.mul_mat(op, **kw)
-        assert lib.flash_attn(fop, **fkw)
-        t_layer = time.perf_counter() - t0
-        t0 = time.perf_counter()
-        assert lib.mul_mat(ops[-1], **kw)
-        return t_layer, time.perf_counter() - t0
+        qd, kvd = sh["n_head"] * sh["head_dim"], sh["n_head_kv"] * sh["head_dim"]
+        mats = [(sh["n_embd"], qd), (sh["n_embd"], kvd), (sh["n_embd"], kvd), (qd, sh["n_embd"]),
+                (sh["n_embd"], sh["n_ff"]), (sh["n_embd"], sh["n_ff"]), (sh["n_ff"], sh["n_embd"])]
+        self.keep, self.layer_ops = [], []
+        for k, m in mats:
+            w, x, y = blocks(eb.Q4_K, k, m), rng.standard_normal(k, dtype=np.float32), np.zeros(m, np.float32)
+            self.keep += [w, x, y]
+            self.layer_ops.append(ob.mul_mat_op(w, eb.Q4_K, k, m, x, 1, y))
+        w, x, y = blocks(out_type, sh["n_embd"], sh["n_vocab"]), rng.standard_normal(sh["n_embd"], dtype=np.float32), np.zeros(sh["n_vocab"], np.float32)
+        self.keep += [w, x, y]
+        self.head_op = ob.mul_mat_op(w, out_type, sh["n_embd"], sh["n_vocab"], x, 1, y)
+        hd, T = sh["head_dim"], ctx
+        q = rng.standard_normal((sh["n_head"], hd), dtype=np.float32)
+        kc = (rng.standard_normal((sh["n_head_kv"], T, hd), dtype=np.float32) * 0.5).astype(np.float16).view(np.uint16)
+        vc = rng.standard_normal((sh["n_head_kv"], T, hd), dtype=np.float32).astype(np.float16).view(np.uint16)
+        dst = np.zeros((sh["n_head"], hd), np.float32)
+        self.keep += [q, kc, vc, dst]
+        self.fop = ob.flash_op(q, kc, vc, dst, hd, sh["n_head"], sh["n_head_kv"], T, T, scale=float(hd) ** -0.5, masked_total=T)
+        self.kw = {"route": "avx2", "lanes": lanes} if self.kind == "reference" else {}
+        self.fkw = {"route": "avx2"} if self.kind == "reference" else {}
 
-    once()
-    samples = [once() for _ in range(repeats)]
-    t_layer = float(np.median([a for a, _ in samples]))
-    t_out = float(np.median([b for _, b in samples])) * 16
-    return sh["n_layer"] * t_layer + t_out, kind
+    def layer(self):
+        for op in self.layer_ops:
+            assert self.lib.mul_mat(op, **self.kw)
+        assert self.lib.flash_attn(self.fop, **self.fkw)
+
+    def token(self):
+        for _ in range(self.sh["n_layer"]):
+            self.layer()
+        assert self.lib.mul_mat(self.head_op, **self.kw)
 
 
 def cpu_baseline_decode(sh, out_type, budget_s=8.0):
+    """Beside the GPU number: the reference's CPU kernels on this host, min(8, cores) lanes (the reference's own
+    maximum lane count, src/emel/kernel/matmul/guards.hpp:12-14), timed on a bounded sample."""
     lanes = min(8, os.cpu_count() or 1)
-    ctx = sh["prompt"]
+    dec = CpuDecoder(sh, out_type, lanes, sh["prompt"])
+    dec.layer()
     t0 = time.perf_counter()
-    sec, kind = cpu_decode_sample(sh, out_type, lanes, 1, ctx)
+    dec.layer()
     one = time.perf_counter() - t0
-    reps = int(max(1, min(10, budget_s / max(one, 1e-3))))
-    sec, kind = cpu_decode_sample(sh, out_type, lanes, reps, ctx)
-    return {"value": round(1.0 / sec, 4), "unit": "tok/s", "cores": lanes if kind == "reference" else 1, "kind": kind,
-            "sample": f"median of {reps} x (one layer's 7 mat-vecs + its attention over {ctx} tokens + 1/16 of the output "
-                      f"projection), scaled to {sh['n_layer']} layers and the full vocabulary; AVX2/FMA route, "
-                      f"mat-vecs row-sliced over {lanes} threads, attention single-threaded as in the reference"}
+    reps = int(max(1, min(sh["n_layer"], budget_s / max(one, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        dec.layer()
+    t_layer = (time.perf_counter() - t0) / reps
+    t0 = time.perf_counter()
+    assert dec.lib.mul_mat(dec.head_op, **dec.kw)
+    t_head = time.perf_counter() - t0
+    sec = sh["n_layer"] * t_layer + t_head
+    return {"value": round(1.0 / sec, 4), "unit": "tok/s", "cores": lanes if dec.kind == "reference" else 1, "kind": dec.kind,
+            "sample": f"mean of {reps} layers (7 mat-vecs + attention over {sh['prompt']} tokens each) x {sh['n_layer']} layers + one "
+                      f"output projection; AVX2/FMA route, mat-vecs row-sliced over {lanes} threads, attention single-threaded "
+                      "as in the reference"}
 
 
 def run_reference_decode(args):
+    """--impl reference: every step is one whole decode token on the host cores (CpuDecoder), measured, not scaled."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     sh = DECODE_SHAPES[args.workload]
     import emel_cpp_b200 as eb
     out_type = eb.Q6_K if args.workload == "decode_8b" else eb.Q4_K
-    lanes = min(os.cpu_count() or 1, 64)
+    lanes = min(8, os.cpu_count() or 1)
     ctx = sh["prompt"] if args.prompt is None else args.prompt
-    sec, kind = cpu_decode_sample(sh, out_type, lanes, max(1, min(args.steps, 8)), ctx)
-    v = round(1.0 / sec, 4)
+    dec = CpuDecoder(sh, out_type, lanes, ctx)
+    for _ in range(args.warmup):
+        dec.token()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        dec.token()
+    dt = time.perf_counter() - t0
+    v = round(args.steps / dt, 4)
+    n_ctx = ((ctx + args.warmup + args.steps + 15) // 16) * 16
     line = {"impl": "reference", "metric": "decode tok/s", "value": v, "unit": "tok/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot (AVX2 maddubs) + f32 scales; f16 KV", "data": "synthetic",
-            "config": {"workload": sh["name"], "prompt_tokens": ctx},
-            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": lanes if kind == "reference" else 1, "kind": kind,
-                             "sample": f"each step = one layer's 7 mat-vecs + its attention over {ctx} tokens + 1/16 of the "
-                                       f"output projection, scaled to {sh['n_layer']} layers and the full vocabulary"},
+            "config": {"workload": sh["name"], "prompt_tokens": ctx, "decoded_tokens": args.steps, "n_ctx": n_ctx,
+                       "launch": "one whole token per step on the host: 7 mat-vecs + attention per layer, then the output projection",
+                       "l2_policy": "one layer's weight bytes reused for every layer (compute-bound kernels)",
+                       "parallelism": f"{lanes} host threads (the reference's maximum lane count), attention single-threaded",
+                       "kernel_launches_per_token": 0, "prefill_s": None, "prefill_tok_s": None, "prefill": "not run: the KV cache holds random rows"},
+            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": lanes if dec.kind == "reference" else 1, "kind": dec.kind,
+                             "sample": f"{args.steps} whole tokens after {args.warmup} warm-up tokens, attention over {ctx} cached tokens"},
             "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -1028,12 +1145,15 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="row count override for gemv_q4_k")
     ap.add_argument("--cols", type=int, default=None, help="column count override for gemv_q4_k")
     ap.add_argument("--cpu-budget", type=float, default=8.0)
-    ap.add_argument("--shard", action="store_true",
-                    help="decode workloads at --gpus N > 1: ONE sequence with every matrix row-sharded over the N GPUs "
-                         "(4 all-gathers per layer) instead of N independent replicas")
-    ap.add_argument("--profile-skip-prefill", action="store_true",
-                    help="decode workloads: leave the KV cache zero-filled instead of running the prompt (keeps a profiler's "
-                         "launch list short; the printed value is then not a benchmark number)")
+    ap.add_argument("--replicas", action="store_true",
+                    help="decode workloads at --gpus N > 1: N independent sequences (one per GPU, no collective) instead of "
+                         "ONE sequence with every matrix row-sharded over the N GPUs")
+    ap.add_argument("--shard", action="store_true", help="accepted for compatibility: sharding is what --gpus N > 1 does")
+    ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
+                    help="sharded decode: join the ranks' row intervals by peer stores over NVLink (default) or by NCCL all-gathers")
+    ap.add_argument("--one-kernel", action="store_true",
+                    help="decode workloads: run the headline through the one-kernel step (every layer of a token in one "
+                         "persistent kernel) instead of the launch chain")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     decode = args.workload.startswith("decode")

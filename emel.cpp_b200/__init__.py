@@ -69,6 +69,9 @@ _SIGNATURES = {
     "emelb_get_stream": [_P, C.POINTER(_P)],
     "emelb_diagnostics": [_P, C.POINTER(Diag)],
     "emelb_set_attention_mode": [_P, C.c_int],
+    "emelb_set_upload_route": [_P, C.c_int32, C.c_int32],
+    "emelb_set_peer_wait_ms": [_P, C.c_uint32],
+    "emelb_selftest_wait_timeout": [_P, C.c_uint32],
     "emelb_residency_upload": [_P, C.c_int32, _P, C.c_uint64, C.c_int32, C.POINTER(_P)],
     "emelb_residency_evict": [_P, C.c_int32],
     "emelb_residency_state": [_P, C.c_int32, C.POINTER(TensorState)],
@@ -246,6 +249,18 @@ class Backend:
 
     def set_attention_mode(self, mode: int) -> bool:
         return self._ret(lib().emelb_set_attention_mode(self._h, mode))
+
+    def set_peer_wait_ms(self, limit_ms: int) -> bool:
+        return self._ret(lib().emelb_set_peer_wait_ms(self._h, limit_ms))
+
+    def selftest_wait_timeout(self, limit_ms: int) -> bool:
+        """Enqueue a peer join nobody answers; the following sync() must then report a failure."""
+        return self._ret(lib().emelb_selftest_wait_timeout(self._h, limit_ms))
+
+    def set_upload_route(self, route: str = "ring", threads: int = 0) -> bool:
+        """route: "ring" (page-locked staging ring, the default), "plain" or "register"; threads 0 = automatic."""
+        code = {"ring": 0, "plain": 1, "register": 2}[route]
+        return self._ret(lib().emelb_set_upload_route(self._h, code, threads))
 
     # -- residency
     def upload(self, tensor_id: int, host, nbytes: int | None = None, tensor_type: int = 0) -> int:

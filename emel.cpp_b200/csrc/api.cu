@@ -388,6 +388,13 @@ uint32_t emelb_diagnostics(const emelb_ctx* c, emelb_diag* out) {
   return EMELB_OK;
 }
 
+uint32_t emelb_set_upload_route(emelb_ctx* c, int32_t route, int32_t threads) {
+  if (!c || route < EMELB_UPLOAD_RING || route > EMELB_UPLOAD_REGISTER || threads < 0) return EMELB_INVALID_REQUEST;
+  c->upload_route = route;
+  c->upload_threads = threads;
+  return EMELB_OK;
+}
+
 uint32_t emelb_set_attention_mode(emelb_ctx* c, int mode) {
   if (!c || mode < 0 || mode > 2) return EMELB_INVALID_REQUEST;
   c->attention_mode = mode;
@@ -631,7 +638,7 @@ uint32_t emelb_mul_mat_prepared(emelb_ctx* c, const emelb_op* op) { return run_m
 // for gate, up); anything the grouped launch does not take runs as `count` single products, same results
 uint32_t emelb_mul_mat_prepared_group(emelb_ctx* c, const emelb_op* ops, uint32_t count) {
   if (!c || !ops || count == 0) return EMELB_INVALID_REQUEST;
-  bool group = count >= 2 && count <= 3 && getenv("EMELB_GEMV_V1") == nullptr;
+  bool group = count >= 2 && count <= 3;
   const uint8_t* W[3] = {nullptr, nullptr, nullptr};
   for (uint32_t i = 0; group && i < count; ++i) {
     const emelb_op& o = ops[i];

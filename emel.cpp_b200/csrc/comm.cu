@@ -39,8 +39,7 @@ cudaError_t comm_all_gather_bytes(emelb_ctx* c, void* buf, size_t bytes_per_rank
 // the kernel returns.
 namespace {
 
-constexpr int kPeerWaitSpins = 1 << 30;   // the wall-clock limit below is the effective bound
-constexpr unsigned long long kPeerWaitNs = 10000000000ull;  // 10 s: covers host-side skew between the ranks' launches
+constexpr int kPeerWaitSpins = 1 << 30;   // the wall-clock limit (PeerGatherArgs::wait_ns) is the effective bound
 
 __global__ void __launch_bounds__(1024) peer_gather_kernel(PeerGatherArgs a) {
   const int peers = a.world - 1;
@@ -77,7 +76,7 @@ __global__ void __launch_bounds__(1024) peer_gather_kernel(PeerGatherArgs a) {
         unsigned long long now;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
         if (t0 == 0) t0 = now;
-        else if (now - t0 > kPeerWaitNs) break;
+        else if (now - t0 > a.wait_ns) break;
       }
     }
     if (!ok && a.status) atomicExch(a.status, 1);
@@ -135,6 +134,40 @@ uint32_t emelb_comm_init(emelb_ctx* c, int32_t rank, int32_t world, const uint8_
   (void)c; (void)rank; (void)world; (void)id; (void)id_bytes;
   return EMELB_UNSUPPORTED_OP;
 #endif
+}
+
+uint32_t emelb_set_peer_wait_ms(emelb_ctx* c, uint32_t limit_ms) {
+  if (!c || limit_ms == 0) return EMELB_INVALID_REQUEST;
+  c->peer_wait_ns = (unsigned long long)limit_ms * 1000000ull;
+  return EMELB_OK;
+}
+
+uint32_t emelb_selftest_wait_timeout(emelb_ctx* c, uint32_t limit_ms) {
+  if (!c || limit_ms == 0 || limit_ms > 10000 || c->stage_in_bytes < 8192) return EMELB_INVALID_REQUEST;
+  cudaSetDevice(c->device);
+  // a join of two "ranks" that are both this context's own staging buffer: rank 0 publishes its flag and waits
+  // for rank 1's, which nobody raises
+  char* arena = static_cast<char*>(c->stage_in);
+  if (cudaMemsetAsync(arena, 0, 8192, c->stream) != cudaSuccess) return EMELB_INTERNAL_ERROR;
+  PeerGatherArgs a{};
+  a.local_base = arena;
+  a.peer_base[0] = arena;
+  a.peer_base[1] = arena;
+  a.offset_bytes = 4096;
+  a.bytes_per_rank = 256;
+  a.flags_offset = 0;
+  a.seq = reinterpret_cast<unsigned int*>(arena + 1024);
+  a.rank = 0;
+  a.world = 2;
+  a.status = c->status_word();
+  a.wait_ns = (unsigned long long)limit_ms * 1000000ull;
+  const cudaError_t e = launch_peer_gather(a, c->stream);
+  c->diag.kernel_launches += 1;
+  if (e != cudaSuccess) {
+    c->last_cuda_error = (int)e;
+    return EMELB_INTERNAL_ERROR;
+  }
+  return EMELB_OK;
 }
 
 uint32_t emelb_comm_destroy(emelb_ctx* c) {

@@ -112,9 +112,12 @@ struct emelb_ctx {
   std::map<uintptr_t, uint64_t> dev_ranges;  // device spans this context allocated (start -> bytes)
   bool capturing = false;
   std::vector<emelb::UploadLane> upload_lanes;  // created by the first large residency upload
+  int upload_route = 0;    // EMELB_UPLOAD_RING / _PLAIN / _REGISTER (emelb_set_upload_route)
+  int upload_threads = 0;  // 0: one per host core, at most 16
   // row-shard exchange (comm.cu): one communicator per context, one rank per GPU
   void* comm = nullptr;  // ncclComm_t
   int comm_rank = 0;
   int comm_world = 1;
+  unsigned long long peer_wait_ns = emelb::kPeerWaitNsDefault;  // bound of a peer-store join's wait (emelb_set_peer_wait_ms)
   emelb_diag diag = {};
 };

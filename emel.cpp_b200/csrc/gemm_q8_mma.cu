@@ -174,7 +174,7 @@ bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols) {
   if (type != T_Q8_0 && type != T_Q4_0) return false;
   if (ncols < kGemmTcMinCols || a.K % kChunk != 0 || a.residual || a.W2 || a.W3 || a.pro_x || a.rope_cos) return false;
   return reinterpret_cast<uintptr_t>(a.W) % 16 == 0 && a.row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.qs) % 16 == 0 &&
-         a.act.col_stride_qs % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.d) % 16 == 0 && getenv("EMELB_NO_Q8_MMA") == nullptr;
+         a.act.col_stride_qs % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.d) % 16 == 0;
 }
 
 cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {

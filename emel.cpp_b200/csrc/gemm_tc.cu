@@ -522,7 +522,8 @@ bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_by
 
 // two launches: the activation tiling pre-pass (into `workspace`, gemm_tc_workspace_bytes) and the product
 cudaError_t launch_gemm_q4k_tc(const GemvArgs& a, int ncols, int sm_count, uint8_t* workspace, cudaStream_t st) {
-  static unsigned configured = 0;  // one bit per device
+  // per host thread (one context, one lane per thread): no shared mutable state between lanes
+  static thread_local unsigned configured = 0;  // one bit per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(configured & (1u << (dev & 31)))) {

@@ -841,7 +841,8 @@ cudaError_t launch2(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_
   constexpr int STAGES = stages_for<T>();
   constexpr size_t smem = (size_t)kWarps2 * warp_bytes2<T, STAGES>();
   auto kern = gemv2_kernel<T, NCOLS, RP, STAGES, kWarps2, ARGMAX>;
-  static unsigned configured = 0;  // per instantiation, one bit per device
+  // per instantiation and host thread (one context, one lane per thread), one bit per device
+  static thread_local unsigned configured = 0;
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(configured & (1u << (dev & 31)))) {
@@ -867,48 +868,48 @@ template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX, int NCOLS = 1>
 cudaError_t launch3(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
   auto kern = gemv3_kernel<T, STAGES, WARPS, MINB, ARGMAX, NCOLS>;
   const size_t smem = (size_t)NCOLS * act_smem_bytes(is_k_type(T), a.K) + (size_t)WARPS * warp_bytes3<T, STAGES>();
-  static size_t configured_smem[32] = {};
-  static int per_sm_cache[32] = {};
+  // Per instantiation, host thread (one context, one lane per thread) and device: the attribute is set once,
+  // and the CTAs per SM are remembered for the last few shared-memory sizes (matrices of different K alternate
+  // on one instantiation inside a decode step).
+  struct Cache {
+    bool attr = false;
+    size_t smem[4] = {};
+    int per_sm[4] = {};
+    int next = 0;
+  };
+  static thread_local Cache caches[32];
   int dev = 0;
   cudaGetDevice(&dev);
-  dev &= 31;
-  if (configured_smem[dev] != smem) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    int n = 0;
-    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, WARPS * 32, smem);
+  Cache& c = caches[dev & 31];
+  if (!c.attr) {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
-    if (n < 1) return cudaErrorInvalidConfiguration;
-    per_sm_cache[dev] = n;
-    configured_smem[dev] = smem;
+    c.attr = true;
+  }
+  int per_sm = 0;
+  for (int i = 0; i < 4; ++i)
+    if (c.smem[i] == smem && c.per_sm[i] > 0) per_sm = c.per_sm[i];
+  if (per_sm == 0) {
+    const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, WARPS * 32, smem);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) return cudaErrorInvalidConfiguration;
+    c.smem[c.next] = smem;
+    c.per_sm[c.next] = per_sm;
+    c.next = (c.next + 1) & 3;
   }
   const int ntasks = (a.M + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE + (a.M2 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE +
                      (a.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
   int grid = (ntasks + WARPS - 1) / WARPS;
-  if (grid > sm_count * per_sm_cache[dev]) grid = sm_count * per_sm_cache[dev];
+  if (grid > sm_count * per_sm) grid = sm_count * per_sm;
   if (ARGMAX && grid > kMaxArgmaxParts) grid = kMaxArgmaxParts;
   if (grid_out) *grid_out = grid;
   return launch_kernel(kern, dim3(grid), dim3(WARPS * 32), smem, st, a.pdl != 0, a);
-}
-
-inline int gen3_config() {
-  static int v = -2;
-  if (v == -2) {
-    const char* e = getenv("EMELB_GEMV_CFG");
-    v = e ? atoi(e) : 0;
-  }
-  return v;  // < 0: use the second-generation kernel for single columns too
 }
 
 template <int T, bool ARGMAX>
 cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
   constexpr bool kLight = T == T_Q4_K || T == T_Q4_0;  // 64 registers: 32 warps per SM; the others 16
   constexpr int kWarpsPerSm = kLight ? 32 : 16;
-  switch (gen3_config()) {
-    case 1: return launch3<T, 2, 8, 2, ARGMAX>(a, sm_count, st, grid_out);
-    case 2: return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX>(a, sm_count, st, grid_out);
-    case 3: return launch3<T, 2, 4, kLight ? 4 : 3, ARGMAX>(a, sm_count, st, grid_out);
-    default: break;
-  }
   // few rows: smaller CTAs, so that every SM gets about the same number of 4-row tasks
   const int ntasks = (a.M + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE + (a.M2 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE +
                      (a.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
@@ -919,25 +920,11 @@ cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* g
   return launch3<T, 2, 2, kLight ? 8 : 4, ARGMAX>(a, sm_count, st, grid_out);
 }
 
-inline int passes_override() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("EMELB_GEMV_RP");
-    v = e ? atoi(e) : 0;
-  }
-  return v;
-}
-
 template <int T>
 cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaStream_t st, int* launches, int* grid_out) {
-  // two 4-row passes per task once there are plenty of rows: the activation
-  // registers of a chunk then serve 8 rows
-  int rp = a.M + a.M2 + a.M3 >= 8192 ? 2 : 1;
-  if (passes_override() > 0) rp = passes_override();
   if (argmax) {
     ++*launches;
-    if (gen3_config() >= 0) return launch3_cfg<T, true>(a, sm_count, st, grid_out);
-    return rp >= 2 ? launch2<T, 1, 2, true>(a, sm_count, st, grid_out) : launch2<T, 1, 1, true>(a, sm_count, st, grid_out);
+    return launch3_cfg<T, true>(a, sm_count, st, grid_out);
   }
   cudaError_t e = cudaSuccess;
   int done = 0;
@@ -946,7 +933,7 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
     b.col0 = a.col0 + done;
     const int left = ncols - done;
     // several columns: the third-generation kernel while their activations fit beside the rings
-    const bool multi3 = gen3_config() >= 0 && !b.pro_x && !b.rope_cos;
+    const bool multi3 = !b.pro_x && !b.rope_cos;
     const size_t act1 = (size_t)act_smem_bytes(is_k_type(T), a.K);
     if (left >= 8 && multi3 && 8 * act1 <= 64 * 1024) { e = launch3<T, 1, 8, 2, false, 8>(b, sm_count, st, grid_out); done += 8; }
     else if (left >= 4 && multi3 && 4 * act1 <= 64 * 1024) { e = launch3<T, 1, 8, 2, false, 4>(b, sm_count, st, grid_out); done += 4; }
@@ -954,11 +941,8 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
     else if (left >= 8) { e = launch2<T, 8, 1, false>(b, sm_count, st, grid_out); done += 8; }
     else if (left >= 4) { e = launch2<T, 4, 1, false>(b, sm_count, st, grid_out); done += 4; }
     else if (left >= 2) { e = launch2<T, 2, 1, false>(b, sm_count, st, grid_out); done += 2; }
-    else if (gen3_config() >= 0) {
+    else {
       e = launch3_cfg<T, false>(b, sm_count, st, grid_out);
-      done += 1;
-    } else {
-      e = rp >= 2 ? launch2<T, 1, 2, false>(b, sm_count, st, grid_out) : launch2<T, 1, 1, false>(b, sm_count, st, grid_out);
       done += 1;
     }
     ++*launches;
@@ -969,8 +953,7 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
 }  // namespace
 
 bool gemv_prologue_supported(int type, const void* w, int64_t row_bytes, int K) {
-  static const bool v1 = getenv("EMELB_GEMV_V1") != nullptr;
-  return !v1 && gen3_config() >= 0 && is_k_type(type) && (K % CHUNK) == 0 && (reinterpret_cast<uintptr_t>(w) % 16) == 0 &&
+  return is_k_type(type) && (K % CHUNK) == 0 && (reinterpret_cast<uintptr_t>(w) % 16) == 0 &&
          (row_bytes % 16) == 0;
 }
 

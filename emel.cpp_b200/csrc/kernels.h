@@ -178,7 +178,9 @@ struct PeerGatherArgs {
   unsigned int* seq;           // this rank's join counter
   int rank, world;
   int* status;
+  unsigned long long wait_ns;  // how long the kernel waits for the peers' flags before it gives up
 };
+constexpr unsigned long long kPeerWaitNsDefault = 10000000000ull;  // 10 s: covers host-side skew between the ranks' launches
 cudaError_t launch_peer_gather(const PeerGatherArgs& a, cudaStream_t st);
 
 // token_kernel.cu — one decode token (all layers) as one persistent kernel

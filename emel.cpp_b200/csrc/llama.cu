@@ -94,6 +94,9 @@ struct emelb_llama {
   TokenLayerW* token_layers = nullptr;
   bool token_layers_valid = false;
   bool token_usable = false;     // the model's shapes and types fit that kernel
+  // prompt tokens per batch (0: walk the prompt token by token).  2048 gives 64 to 224 weight-row x token tiles
+  // per product at the 8B shape: the tensor-core kernel's grid fills
+  int prefill_batch = 2048;
   int step_mode = 0;             // 0: the chain of per-operation launches, 1: one kernel per token where it applies
   TokenLaunchState token_launch;
   unsigned long long* token_trace = nullptr;   // device stamps of emelb_llama_decode_profile
@@ -241,7 +244,7 @@ struct Enqueue {
     bool same = n >= 2 && n <= 3;
     for (int i = 1; same && i < n; ++i) same = w[i]->type == w[0]->type && w[i]->K == w[0]->K && w[i]->row_bytes == w[0]->row_bytes;
     for (int i = 0; same && i < n; ++i) same = gemv_fast_path_ok(w[i]->type, w[i]->dev, w[i]->row_bytes, w[i]->K);
-    if (!same || getenv("EMELB_GEMV_V1")) {
+    if (!same) {
       for (int i = 0; i < n; ++i) matvec(*w[i], x, y[i], nullptr);
       return;
     }
@@ -276,7 +279,7 @@ struct Enqueue {
   // returns whether that happened (false: the caller runs the RoPE / KV-store kernel)
   bool normed_matvec_group(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax = false,
                            int rope_layer = -1) {
-    bool fuse = getenv("EMELB_NO_FUSED_NORM") == nullptr && (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
+    bool fuse = (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
                 (reinterpret_cast<uintptr_t>(nw.dev) % 16) == 0 && n >= 1 && n <= 3;
     for (int i = 0; fuse && i < n; ++i)
       fuse = gemv_prologue_supported(w[i]->type, w[i]->dev, w[i]->row_bytes, w[i]->K) && w[i]->type == w[0]->type &&
@@ -288,8 +291,7 @@ struct Enqueue {
       return false;
     }
     const emelb_llama_config& cfg = s->cfg;
-    const bool rope = rope_layer >= 0 && n == 3 && !cfg.rope_neox && cfg.head_dim % 2 == 0 && w[0]->M % cfg.head_dim == 0 &&
-                      getenv("EMELB_NO_FUSED_ROPE") == nullptr;
+    const bool rope = rope_layer >= 0 && n == 3 && !cfg.rope_neox && cfg.head_dim % 2 == 0 && w[0]->M % cfg.head_dim == 0;
     GemvArgs a{};
     a.W = w[0]->dev;
     a.row_bytes = w[0]->row_bytes;
@@ -376,6 +378,7 @@ struct Enqueue {
     a.rank = s->rank;
     a.world = s->G;
     a.status = s->c->status_word();
+    a.wait_ns = s->c->peer_wait_ns;
     check(launch_peer_gather(a, st));
     ++launches;
   }
@@ -832,17 +835,15 @@ namespace {
 // kernel (attention mode 0: the reference-order modes exist to be compared one token at a time), room for one
 // batch in the context's activation planes and, in a sharded session, the context's communicator for the joins.
 int prefill_batch_size(emelb_llama* s, int n) {
-  const char* off = getenv("EMELB_NO_BATCH_PREFILL");
   const emelb_llama_config& c = s->cfg;
-  if (off || s->c->attention_mode != 0 || n < 2) return 0;
+  if (s->prefill_batch <= 0 || s->c->attention_mode != 0 || n < 2) return 0;
   if (s->G > 1 && (!s->c->comm || s->c->comm_world != s->G)) return 0;   // batch joins go through the communicator
   PrefillAttnArgs pa{nullptr, nullptr, s->kcache, s->vcache, s->capacity * c.head_dim, c.head_dim, c.n_head / s->G,
                      c.n_head_kv / s->G, 1, 0, 1.0f};
   if (!prefill_attention_supported(pa)) return 0;
   int widest = c.n_ff > c.n_embd ? c.n_ff : c.n_embd;
   if (c.n_head * c.head_dim > widest) widest = c.n_head * c.head_dim;
-  int cap = 2048;  // 64 to 224 weight-row x token tiles per product at the 8B shape: the tensor-core kernel's grid fills
-  if (const char* e = getenv("EMELB_PREFILL_BATCH")) cap = atoi(e);
+  int cap = s->prefill_batch;
   const int64_t fits = (int64_t)(s->c->act_capacity / (uint64_t)widest);
   if (cap > fits) cap = (int)fits;
   if ((int64_t)c.n_ff * cap > 0x7fffffff) cap = 0x7fffffff / c.n_ff;
@@ -989,6 +990,12 @@ uint32_t emelb_llama_decode_profile(emelb_llama* s, int32_t token, int32_t posit
   ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
   c->diag.kernel_launches += 3;
   return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_llama_set_prefill_batch(emelb_llama* s, int32_t max_tokens) {
+  if (!s || max_tokens < 0) return EMELB_INVALID_REQUEST;
+  s->prefill_batch = max_tokens == 1 ? 0 : max_tokens;   // a batch of one is the token-by-token walk
+  return EMELB_OK;
 }
 
 uint32_t emelb_llama_set_step_mode(emelb_llama* s, int32_t mode) {

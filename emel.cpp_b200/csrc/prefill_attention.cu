@@ -12,7 +12,6 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
-#include <cstdlib>
 
 #include "kernels.h"
 
@@ -22,161 +21,10 @@ namespace {
 
 constexpr int kRows = 64;     // query rows per CTA
 constexpr int kKT = 64;       // cache positions per tile
-constexpr int kThreads = 256;
-constexpr int kPStride = kKT + 4;
-
-template <int D>
-struct PrefillSmem {
-  static constexpr int kKStride = D + 4;  // halves: 16 lanes x 8-byte reads land on 32 distinct banks
-  float q[kRows][D];
-  __half k[kKT][kKStride];
-  __half v[kKT][D];
-  float p[kRows][kPStride];
-};
-
-template <int D>
-__global__ void __launch_bounds__(kThreads) prefill_attention_kernel(const PrefillAttnArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  PrefillSmem<D>& sm = *reinterpret_cast<PrefillSmem<D>*>(smem_raw);
-  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  const int n_rep = a.heads / a.kv_heads, QT = kRows / n_rep;
-  const int kh = blockIdx.y, j0 = blockIdx.x * QT, B = a.B;
-
-  // queries of the tile, rounded to f16 values; rows of tokens past the batch stay zero
-  for (int idx = tid; idx < kRows * D; idx += kThreads) {
-    const int jt = idx % QT, d = (idx / QT) % D, rep = idx / (QT * D);
-    const int j = j0 + jt;
-    float val = 0.0f;
-    if (j < B) val = __half2float(__float2half_rn(a.q[((int64_t)(kh * n_rep + rep) * D + d) * B + j]));
-    sm.q[rep * QT + jt][d] = val;
-  }
-
-  // last position + 1 each of this thread's rows may see
-  int t_row[4];
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int j = j0 + (4 * ty + r) % QT;
-    t_row[r] = j < B ? a.pos0 + j + 1 : 0;
-  }
-  const int j_last = min(B, j0 + QT) - 1;
-  const int t_cta = a.pos0 + j_last + 1;      // positions this CTA walks
-  const int t_written = a.pos0 + B;           // cache rows that hold data
-
-  float m[4], l[4], acc[4][D / 16];
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    m[r] = -INFINITY;
-    l[r] = 0.0f;
-#pragma unroll
-    for (int c = 0; c < D / 16; ++c) acc[r][c] = 0.0f;
-  }
-  const __half* kbase = a.k + (int64_t)kh * a.cache_head_stride;
-  const __half* vbase = a.v + (int64_t)kh * a.cache_head_stride;
-
-  for (int t0 = 0; t0 < t_cta; t0 += kKT) {
-    __syncthreads();  // the previous tile's readers are done (and, the first time, sm.q is complete)
-    for (int idx = tid; idx < kKT * (D / 8); idx += kThreads) {
-      const int t = idx / (D / 8), c = idx % (D / 8);
-      uint4 kk = make_uint4(0u, 0u, 0u, 0u), vv = kk;
-      if (t0 + t < t_written) {
-        kk = *reinterpret_cast<const uint4*>(kbase + (int64_t)(t0 + t) * D + 8 * c);
-        vv = *reinterpret_cast<const uint4*>(vbase + (int64_t)(t0 + t) * D + 8 * c);
-      }
-      uint2* kd = reinterpret_cast<uint2*>(&sm.k[t][8 * c]);
-      kd[0] = make_uint2(kk.x, kk.y);
-      kd[1] = make_uint2(kk.z, kk.w);
-      *reinterpret_cast<uint4*>(&sm.v[t][8 * c]) = vv;
-    }
-    __syncthreads();
-
-    // scores: rows 4ty .. 4ty+3, columns tx + 16c
-    float s[4][4];
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) s[r][c] = 0.0f;
-#pragma unroll 4
-    for (int d = 0; d < D; d += 4) {
-      float4 qv[4];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) qv[r] = *reinterpret_cast<const float4*>(&sm.q[4 * ty + r][d]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(&sm.k[tx + 16 * c][d]);
-        const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-        const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-          s[r][c] += qv[r].x * k01.x + qv[r].y * k01.y + qv[r].z * k23.x + qv[r].w * k23.y;
-      }
-    }
-
-    // online softmax per row (the 16 threads of a row share every statistic)
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const bool live = t0 + tx + 16 * c < t_row[r];
-        s[r][c] = live ? s[r][c] * a.scale : -INFINITY;
-        mx = fmaxf(mx, s[r][c]);
-      }
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      const float m_new = fmaxf(m[r], mx);
-      const float keep = m_new == -INFINITY ? 1.0f : expf(m[r] - m_new);   // m[r] = -inf gives 0
-      float sum = 0.0f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float pv = s[r][c] == -INFINITY ? 0.0f : expf(s[r][c] - m_new);
-        sm.p[4 * ty + r][tx + 16 * c] = pv;
-        sum += pv;
-      }
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      l[r] = l[r] * keep + sum;
-      m[r] = m_new;
-#pragma unroll
-      for (int c = 0; c < D / 16; ++c) acc[r][c] *= keep;
-    }
-    __syncthreads();
-
-    // output rows 4ty .. 4ty+3, dims 32i + 2tx, 32i + 2tx + 1
-    const int t_end = min(kKT, t_cta - t0);
-    for (int t = 0; t < t_end; ++t) {
-      float pr[4];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) pr[r] = sm.p[4 * ty + r][t];
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) {
-        const float2 vv = __half22float2(*reinterpret_cast<const __half2*>(&sm.v[t][32 * i + 2 * tx]));
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          acc[r][2 * i] += pr[r] * vv.x;
-          acc[r][2 * i + 1] += pr[r] * vv.y;
-        }
-      }
-    }
-  }
-
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int row = 4 * ty + r, rep = row / QT, j = j0 + row % QT;
-    if (j >= B) continue;
-    const float inv = l[r] > 0.0f ? 1.0f / l[r] : 0.0f;
-    float* out = a.dst + ((int64_t)(kh * n_rep + rep) * D) * B + j;
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
-      out[(int64_t)(32 * i + 2 * tx) * B] = acc[r][2 * i] * inv;
-      out[(int64_t)(32 * i + 2 * tx + 1) * B] = acc[r][2 * i + 1] * inv;
-    }
-  }
-}
-
 
 // ---------------------------------------------------------------------------------------------------------
-// The same computation on the tensor cores (mma.sync m16n8k16, f16 operands, f32 accumulators).  Scores are
-// exact products of f16 values either way.  The softmax weights stay f32-accurate: each weight p is fed as
+// Scores and weighted sums run on the tensor cores (mma.sync m16n8k16, f16 operands, f32 accumulators).
+// Scores are exact products of f16 values.  The softmax weights stay f32-accurate: each weight p is fed as
 // two f16 operands, hi = f16(p) and lo = f16(p - hi), in two MMAs against the f16 V tile, so the only
 // rounding left is the f32 accumulation (the 2e-5 bar of the fast attention holds).
 // One warp = 16 query rows; lane = 4g + t.  Fragments (PTX ISA, m16n8k16):
@@ -380,17 +228,10 @@ template <int D>
 cudaError_t launch_d(const PrefillAttnArgs& a, cudaStream_t st) {
   const int n_rep = a.heads / a.kv_heads, QT = kRows / n_rep;
   const dim3 grid((a.B + QT - 1) / QT, a.kv_heads);
-  if (getenv("EMELB_PREFILL_ATTN_SIMT") == nullptr) {
-    const int smem = (int)sizeof(PrefillMmaSmem<D>);
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    prefill_attention_mma_kernel<D><<<grid, kMmaThreads, smem, st>>>(a);
-    return cudaGetLastError();
-  }
-  const int smem = (int)sizeof(PrefillSmem<D>);
-  cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  const int smem = (int)sizeof(PrefillMmaSmem<D>);
+  cudaError_t e = cudaFuncSetAttribute(prefill_attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  prefill_attention_kernel<D><<<grid, kThreads, smem, st>>>(a);
+  prefill_attention_mma_kernel<D><<<grid, kMmaThreads, smem, st>>>(a);
   return cudaGetLastError();
 }
 

@@ -32,9 +32,9 @@ constexpr uint64_t kChunk = 4ull << 20;
 constexpr uint64_t kDirectBelow = 4ull << 20;
 constexpr int kMaxUploadThreads = 16;
 
-int upload_threads() {
+int upload_threads(const emelb_ctx* c) {
   int n = int(std::min<unsigned>(16u, std::max(1u, std::thread::hardware_concurrency())));
-  if (const char* e = std::getenv("EMELB_UPLOAD_THREADS")) n = std::atoi(e);
+  if (c->upload_threads > 0) n = c->upload_threads;
   return std::max(1, std::min(n, kMaxUploadThreads));
 }
 
@@ -95,9 +95,8 @@ void upload_ring_release(emelb_ctx* c) {
 }
 
 cudaError_t upload_spans(emelb_ctx* c, const UploadSpan* spans, size_t count, int fd) {
-  const char* mode = std::getenv("EMELB_UPLOAD_MODE");
-  const bool want_register = mode && std::strcmp(mode, "register") == 0;
-  const bool want_plain = mode && std::strcmp(mode, "plain") == 0;
+  const bool want_register = c->upload_route == EMELB_UPLOAD_REGISTER;
+  const bool want_plain = c->upload_route == EMELB_UPLOAD_PLAIN;
   // spans that go in one copy; the rest is cut into chunks for the lanes
   struct Chunk {
     void* dev;
@@ -122,7 +121,7 @@ cudaError_t upload_spans(emelb_ctx* c, const UploadSpan* spans, size_t count, in
   }
   if (chunks.empty()) return cudaSuccess;
 
-  const int threads = int(std::min<uint64_t>(uint64_t(upload_threads()), chunks.size()));
+  const int threads = int(std::min<uint64_t>(uint64_t(upload_threads(c)), chunks.size()));
   if (!upload_ring_reserve(c, threads)) return cudaErrorMemoryAllocation;
   std::atomic<int> first_error{int(cudaSuccess)};
   auto fill = [&](void* dst, const Chunk& ch) {

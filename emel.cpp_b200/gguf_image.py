@@ -1,4 +1,4 @@
-"""A small GGUF v3 writer for the tests: key/value pairs, tensor descriptions and
+"""A small GGUF v3 writer (test images, the load benchmark's file): key/value pairs, tensor descriptions and
 aligned tensor data, laid out as the reference's loader expects them
 (src/emel/gguf/loader/detail.hpp:419-543)."""
 from __future__ import annotations

@@ -33,6 +33,7 @@ SIGNATURES = {
     "emelb_llama_generate": [_P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32)],
     "emelb_llama_launches_per_token": [_P, C.POINTER(C.c_int32)],
     "emelb_llama_set_step_mode": [_P, C.c_int32],
+    "emelb_llama_set_prefill_batch": [_P, C.c_int32],
     "emelb_llama_decode_profile": [_P, C.c_int32, C.c_int32, _P, C.c_uint64],
     "emelb_llama_exchange_export": [_P, _P, C.c_uint64],
     "emelb_llama_exchange_attach": [_P, _P, C.c_uint64],
@@ -164,6 +165,10 @@ class Session:
         v = C.c_int32(0)
         eb.lib().emelb_llama_launches_per_token(self._h, C.byref(v))
         return v.value
+
+    def set_prefill_batch(self, max_tokens: int) -> bool:
+        """Prompt tokens per batch of prefill(): 0 walks the prompt token by token."""
+        return self._ret(eb.lib().emelb_llama_set_prefill_batch(self._h, max_tokens))
 
     def set_step_mode(self, mode: int) -> bool:
         """0: the chain of per-operation launches (default); 1: one persistent kernel per token where the session qualifies."""

@@ -158,6 +158,16 @@ EMELB_API uint32_t emelb_residency_upload(emelb_ctx* ctx, int32_t tensor_id,
                                 const void* host, uint64_t bytes,
                                 int32_t tensor_type, const void** dev_out);
 EMELB_API uint32_t emelb_residency_evict(emelb_ctx* ctx, int32_t tensor_id);
+/* how host spans outside page-locked memory reach the device (no reference
+ * counterpart: its loader strategies end at host memory,
+ * src/emel/io/loader/events.hpp:25-31).  RING (default): 4 MB chunks through a
+ * page-locked staging ring fed by `threads` host threads (0 = one per core, at
+ * most 16; pread-fed when the span maps a file).  PLAIN: one pageable copy per
+ * span.  REGISTER: the span is page-locked in place (read-only) and copied
+ * without a host copy. */
+enum { EMELB_UPLOAD_RING = 0, EMELB_UPLOAD_PLAIN = 1, EMELB_UPLOAD_REGISTER = 2 };
+EMELB_API uint32_t emelb_set_upload_route(emelb_ctx* ctx, int32_t route, int32_t threads);
+
 EMELB_API uint32_t emelb_residency_state(const emelb_ctx* ctx, int32_t tensor_id,
                                emelb_tensor_state* out);
 
@@ -270,6 +280,19 @@ EMELB_API uint32_t emelb_comm_unique_id(uint8_t* id_out, uint64_t id_bytes);
 EMELB_API uint32_t emelb_comm_init(emelb_ctx* ctx, int32_t rank, int32_t world,
                          const uint8_t* id, uint64_t id_bytes);
 EMELB_API uint32_t emelb_comm_destroy(emelb_ctx* ctx);
+/* how long a peer-store join waits on the device for the other ranks' flags
+ * before the kernel gives up, raises the context's status word and returns
+ * (default 10 s; the next emelb_sync then reports EMELB_INTERNAL_ERROR and the
+ * context stays usable).  Every device-side wait of the library is bounded this
+ * way; no reference counterpart (its lane join spins on the host,
+ * src/emel/kernel/matmul/actions.hpp:108-136). */
+EMELB_API uint32_t emelb_set_peer_wait_ms(emelb_ctx* ctx, uint32_t limit_ms);
+/* diagnostics: enqueues a two-rank peer-store join whose second rank never
+ * answers (both ranks' buffers are this context's own staging memory, so no
+ * second GPU is involved and nothing faults): the kernel's wait runs out after
+ * limit_ms (1..10000) and the status word is raised.  Exercises the path from a
+ * device-side timeout to emelb_sync's EMELB_INTERNAL_ERROR. */
+EMELB_API uint32_t emelb_selftest_wait_timeout(emelb_ctx* ctx, uint32_t limit_ms);
 EMELB_API uint32_t emelb_all_gather_rows(emelb_ctx* ctx, float* dst_dev,
                          uint64_t rows_per_rank, uint64_t row_floats);
 

@@ -104,13 +104,18 @@ EMELB_API uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t pos
  * fills their KV rows.  The reference's x86 prefill walks the prompt one token
  * at a time (src/emel/text/generator/detail.hpp:4064-4092).  With the fast
  * attention (mode 0) the prompt is processed in batches of up to 2048 tokens
- * instead: per token the same arithmetic except the attention, which is an f32
+ * (emelb_llama_set_prefill_batch) instead: per token the same arithmetic except the attention, which is an f32
  * online softmax over the batch (emelb_flash_attn_batch).  Sharded sessions do
  * the same when their context has a communicator (emelb_comm_init), joining the
  * ranks' row intervals of every product by all-gather.  The reference-order
  * attention modes walk token by token. */
 EMELB_API uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n,
                                        int32_t start_pos);
+
+/* prompt tokens per batch of emelb_llama_prefill: default 2048; 0 or 1 walks the
+ * prompt token by token (what the reference does); the first batched prompt sizes
+ * the session's batch buffers, later values are clamped to them */
+EMELB_API uint32_t emelb_llama_set_prefill_batch(emelb_llama* s, int32_t max_tokens);
 
 /* greedy generation of `n` tokens with the token fed back on the device: no
  * host round trip between steps; tokens_out (host) is written at the end */

@@ -104,8 +104,9 @@ def flash_op(q, kc, vc, dst, head_dim, heads, kv_heads, tokens, capacity, scale=
     return op
 
 
-# where the reference checkout lies when it is present (same default as the Makefile's REFERENCE)
-REFERENCE_DIR = os.environ.get("EMEL_REFERENCE_DIR", "/root/reference")
+# where the reference checkout lies when it is present: EMEL_REFERENCE_DIR, else a `reference` directory beside
+# this repository (the Makefile's default too)
+REFERENCE_DIR = os.environ.get("EMEL_REFERENCE_DIR") or os.path.abspath(os.path.join(HERE, "..", "..", "reference"))
 
 
 def _load(path):

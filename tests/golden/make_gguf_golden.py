@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 
 from oracle import bindings as ob          # noqa: E402
-from tests import gguf_image as gi         # noqa: E402
+from emel_cpp_b200 import gguf_image as gi         # noqa: E402
 
 
 def corruptions(image: bytes, head_bytes: int, stride: int):

@@ -88,11 +88,11 @@ def main():
     results = {}
     # sharded sessions walk the prompt token by token; the unsharded one is held to the same walk here so that
     # the comparison is about sharding alone (the batched prompt path has its own tests)
-    os.environ["EMELB_NO_BATCH_PREFILL"] = "1"
     for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world), ("shard-peer", be_shard, rank, world)):
         for mode in (2, 0):
             be.set_attention_mode(mode)
             sess = build(be, be_full, CFG, r, g, buffers)
+            assert sess.set_prefill_batch(0)
             if name == "shard-peer":       # joins by peer stores instead of NCCL all-gathers
                 handles = [None] * world
                 dist.all_gather_object(handles, sess.exchange_export())
@@ -123,13 +123,12 @@ def main():
     # batched prompt path: the sharded session processes the prompt in token batches too (row intervals of every
     # product joined by NCCL); per head and per row it runs the same kernels on the same numbers as the
     # unsharded session, so the logits that follow are bit-identical
-    del os.environ["EMELB_NO_BATCH_PREFILL"]
-    os.environ["EMELB_PREFILL_BATCH"] = "24"          # 50 prompt tokens = 24 + 24 + 2
     long_prompt = np.random.Generator(np.random.PCG64(11)).integers(0, CFG["n_vocab"], size=51).tolist()
     batched = {}
     for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world)):
         be.set_attention_mode(0)
         sess = build(be, be_full, CFG, r, g, buffers)
+        assert sess.set_prefill_batch(24)              # 50 prompt tokens = 24 + 24 + 2
         l0 = be.diagnostics()["kernel_launches"]
         assert sess.prefill(long_prompt[:-1], 0), sess.last_error
         launches = be.diagnostics()["kernel_launches"] - l0
@@ -138,7 +137,6 @@ def main():
         assert be.sync()
         dist.barrier()
         sess.close()
-    del os.environ["EMELB_PREFILL_BATCH"]
     assert np.array_equal(batched["full"].view(np.uint32), batched["shard"].view(np.uint32)), \
         float(np.abs(batched["full"] - batched["shard"]).max())
 

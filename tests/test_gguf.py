@@ -12,7 +12,7 @@ import pytest
 import emel_cpp_b200 as eb
 from emel_cpp_b200 import gguf
 from oracle import bindings as ob, gguf_oracle as go
-from tests import gguf_image as gi
+from emel_cpp_b200 import gguf_image as gi
 from tests.golden.make_gguf_golden import apply, corruptions
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gguf_golden.npz")

@@ -175,7 +175,7 @@ def _rel(a, b):
     (TINY, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K}),
     (MIXED, {"embd": eb.Q8_0, "output": eb.Q8_0, "default": eb.Q8_0, el.ATTN_K: eb.Q4_K, el.FFN_DOWN: eb.Q4_0}),
 ])
-def test_batched_prompt_one_layer_is_bit_identical(be, port, cfg, types, monkeypatch):
+def test_batched_prompt_one_layer_is_bit_identical(be, port, cfg, types):
     """With one layer the logits after a prompt depend on the prompt only through the layer's K and V rows:
     embedding, norm, quantization, the matrix products (tensor-core kernel for batches of 32 and more Q4_K
     columns, multi-column mat-vec kernels below), RoPE and the f16 store.  Those are the same arithmetic per
@@ -185,21 +185,21 @@ def test_batched_prompt_one_layer_is_bit_identical(be, port, cfg, types, monkeyp
     cpu.close()
     try:
         prompt = synth.rng(17).integers(0, cfg["n_vocab"], size=151).tolist()
-        monkeypatch.setenv("EMELB_NO_BATCH_PREFILL", "1")
+        assert sess.set_prefill_batch(0)
         l0 = be.diagnostics()["kernel_launches"]
         base = _prompt_then_logits(be, sess, prompt, [150])
         launches_token = be.diagnostics()["kernel_launches"] - l0
-        monkeypatch.delenv("EMELB_NO_BATCH_PREFILL")
+        assert sess.set_prefill_batch(2048)
         for batch, pieces in ((None, [150]), ("64", [150]), (None, [1, 2, 33, 100, 14]), ("40", [70, 80])):
             if batch:
-                monkeypatch.setenv("EMELB_PREFILL_BATCH", batch)
+                assert sess.set_prefill_batch(int(batch))
             # scrub the cache rows first so that stale rows of the previous walk cannot stand in for missing ones
             junk = synth.rng(5).integers(0, cfg["n_vocab"], size=150).tolist()
             assert sess.prefill(junk, 0)
             l0 = be.diagnostics()["kernel_launches"]
             got = _prompt_then_logits(be, sess, prompt, pieces)
             launches = be.diagnostics()["kernel_launches"] - l0
-            monkeypatch.delenv("EMELB_PREFILL_BATCH", raising=False)
+            assert sess.set_prefill_batch(2048)
             assert np.array_equal(got.view(np.uint32), base.view(np.uint32)), (batch, pieces, float(np.abs(got - base).max()))
             assert launches < launches_token / 3
     finally:
@@ -210,7 +210,7 @@ def test_batched_prompt_one_layer_is_bit_identical(be, port, cfg, types, monkeyp
     (TINY, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K}),
     (MIXED, {"embd": eb.Q8_0, "output": eb.Q8_0, "default": eb.Q8_0, el.ATTN_K: eb.Q4_K, el.FFN_DOWN: eb.Q4_0}),
 ])
-def test_batched_prompt_many_layers_within_attention_noise(be, port, cfg, types, monkeypatch):
+def test_batched_prompt_many_layers_within_attention_noise(be, port, cfg, types):
     """With more layers the prompt's attention outputs feed the next layer's int8 quantizers, where a
     difference in the last bits flips roundings (the decoder is chaotic at that scale: the reference's own
     routes drift apart the same way).  The batch attention kernel is held to 2e-5 of the exact softmax on its
@@ -221,16 +221,16 @@ def test_batched_prompt_many_layers_within_attention_noise(be, port, cfg, types,
     cpu.close()
     try:
         prompt = synth.rng(17).integers(0, cfg["n_vocab"], size=151).tolist()
-        monkeypatch.setenv("EMELB_NO_BATCH_PREFILL", "1")
+        assert sess.set_prefill_batch(0)
         base = _prompt_then_logits(be, sess, prompt, [150])
         ref_order = _prompt_then_logits(be, sess, prompt, [150], mode=2)
-        monkeypatch.delenv("EMELB_NO_BATCH_PREFILL")
+        assert sess.set_prefill_batch(2048)
         yard = _rel(ref_order, base)
         for batch, pieces in ((None, [150]), ("64", [150]), (None, [1, 2, 33, 100, 14])):
             if batch:
-                monkeypatch.setenv("EMELB_PREFILL_BATCH", batch)
+                assert sess.set_prefill_batch(int(batch))
             got = _prompt_then_logits(be, sess, prompt, pieces)
-            monkeypatch.delenv("EMELB_PREFILL_BATCH", raising=False)
+            assert sess.set_prefill_batch(2048)
             d = _rel(got, base)
             print(pieces, "batched vs token-by-token %.2e, reference-order vs token-by-token %.2e" % (d, yard))
             assert np.isfinite(got).all() and d <= yard and d <= 5e-2, (pieces, d, yard)
@@ -238,7 +238,7 @@ def test_batched_prompt_many_layers_within_attention_noise(be, port, cfg, types,
         sess.close()
 
 
-def test_batched_prompt_fills_the_context_to_the_last_row(be, port, monkeypatch):
+def test_batched_prompt_fills_the_context_to_the_last_row(be, port):
     """A prompt that ends on the last but one cache row, batches of 2 and of 61 tokens, and the decode step
     on the last row: bit-identical to the token-by-token walk (one layer), and requests past the context
     are refused before anything runs."""
@@ -247,9 +247,9 @@ def test_batched_prompt_fills_the_context_to_the_last_row(be, port, monkeypatch)
     cpu.close()
     try:
         prompt = synth.rng(31).integers(0, cfg["n_vocab"], size=64).tolist()
-        monkeypatch.setenv("EMELB_NO_BATCH_PREFILL", "1")
+        assert sess.set_prefill_batch(0)
         base = _prompt_then_logits(be, sess, prompt, [63])
-        monkeypatch.delenv("EMELB_NO_BATCH_PREFILL")
+        assert sess.set_prefill_batch(2048)
         assert sess.prefill(synth.rng(5).integers(0, cfg["n_vocab"], size=63).tolist(), 0)    # scrub
         got = _prompt_then_logits(be, sess, prompt, [2, 61])
         assert np.array_equal(got.view(np.uint32), base.view(np.uint32))

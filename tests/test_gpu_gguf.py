@@ -8,7 +8,8 @@ import pytest
 import emel_cpp_b200 as eb
 from emel_cpp_b200 import gguf, llama as el
 from oracle import bindings as ob
-from tests import gguf_image as gi, synth
+from emel_cpp_b200 import gguf_image as gi
+from tests import synth
 
 pytestmark = pytest.mark.gpu
 
@@ -154,9 +155,8 @@ def test_large_tensor_goes_through_the_staging_ring_unchanged(be, tmp_path):
     image = gi.build([], [(f"t{i}", (len(b),), 24, b.tobytes()) for i, b in enumerate(blobs)], 32)
     path = tmp_path / "big.gguf"
     path.write_bytes(image)
-    for mode in (None, "plain", "register"):
-        if mode:
-            os.environ["EMELB_UPLOAD_MODE"] = mode
+    for mode in ("ring", "plain", "register"):
+        assert be.set_upload_route(mode)
         try:
             with gguf.File(str(path)) as f:
                 f.upload_all(be, 7200)
@@ -166,7 +166,7 @@ def test_large_tensor_goes_through_the_staging_ring_unchanged(be, tmp_path):
                     assert be.to_host(got, st.buffer, len(b)) and np.array_equal(got, b), (mode, i)
                     be.evict(7200 + i)
         finally:
-            os.environ.pop("EMELB_UPLOAD_MODE", None)
+            assert be.set_upload_route("ring")
     # a plain host array (no file behind it) takes the memcpy-fed ring
     be.upload(7300, blobs[1], tensor_type=24)
     got = np.empty(len(blobs[1]), np.uint8)
