@@ -22,7 +22,7 @@ BLOCK_ELEMS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, Q8_K: 256}
 BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, Q8_K: 292}
 # error bitmask (src/emel/kernel/errors.hpp:7-13)
 OK, INVALID_REQUEST, UNSUPPORTED_OP, INTERNAL_ERROR, UNTRACKED = 0, 1, 2, 4, 8
-OP_MUL_MAT, OP_MUL_MAT_ARGMAX, OP_FLASH_ATTN_EXT = 1, 2, 3
+OP_MUL_MAT, OP_MUL_MAT_ARGMAX, OP_FLASH_ATTN_EXT, OP_RMS_NORM, OP_ROPE, OP_GLU = 1, 2, 3, 4, 5, 6
 LIFECYCLE = {0: "unbound", 1: "resident", 2: "evicted", 3: "internal_error", 4: "mmap_resident"}
 
 
@@ -85,6 +85,9 @@ _SIGNATURES = {
     "emelb_prepare_rhs": [_P, C.POINTER(View), C.c_int32],
     "emelb_mul_mat_prepared": [_P, C.POINTER(Op)],
     "emelb_flash_attn_ext": [_P, C.POINTER(Op)],
+    "emelb_rms_norm": [_P, C.POINTER(Op)],
+    "emelb_rope": [_P, C.POINTER(Op)],
+    "emelb_glu": [_P, C.POINTER(Op)],
     "emelb_quantize": [_P, C.POINTER(View), C.POINTER(View)],
     "emelb_dequantize": [_P, C.POINTER(View), C.POINTER(View)],
     "emelb_graph_begin": [_P],
@@ -203,6 +206,40 @@ def flash_op(q, kc, vc, dst, head_dim, heads, kv_heads, tokens, capacity, scale=
     return op
 
 
+def strided_view(data, t: int, ne, nb) -> View:
+    """A view with explicit byte strides (any valid layout)."""
+    v = View()
+    v.data, v.type = ptr(data), t
+    for i in range(4):
+        v.ne[i] = ne[i] if i < len(ne) else 1
+        v.nb[i] = nb[i] if i < len(nb) else (nb[-1] * ne[len(nb) - 1] if i == len(nb) else v.nb[i - 1] * v.ne[i - 1])
+    return v
+
+
+def rms_norm_op(src: View, dst: View, eps: float) -> Op:
+    """op_rms_norm request: op_params = {f32 eps} (src/emel/kernel/detail.hpp:4547-4553)."""
+    import struct
+    op = Op()
+    op.src0, op.dst = src, dst
+    for i, b in enumerate(struct.pack("<f", eps)):
+        op.op_params[i] = b
+    op.op_params_size = 4
+    return op
+
+
+def rope_op(src: View, positions: View, dst: View, n_dims: int, mode: int = 0, freq_base: float = 10000.0,
+            freq_scale: float = 1.0, ext_factor: float = 0.0, attn_factor: float = 1.0) -> Op:
+    """op_rope request with ggml's parameter layout (src/emel/kernel/detail.hpp:4650-4678)."""
+    import struct
+    op = Op()
+    op.src0, op.src1, op.dst = src, positions, dst
+    raw = struct.pack("<5i6f", 0, n_dims, mode, 0, 0, freq_base, freq_scale, ext_factor, attn_factor, 0.0, 0.0)
+    for i, b in enumerate(raw):
+        op.op_params[i] = b
+    op.op_params_size = len(raw)
+    return op
+
+
 class Backend:
     """One backend context = one kernel actor lane."""
 
@@ -249,6 +286,15 @@ class Backend:
 
     def set_attention_mode(self, mode: int) -> bool:
         return self._ret(lib().emelb_set_attention_mode(self._h, mode))
+
+    def rms_norm(self, op: Op) -> bool:
+        return self._ret(lib().emelb_rms_norm(self._h, C.byref(op)))
+
+    def rope(self, op: Op) -> bool:
+        return self._ret(lib().emelb_rope(self._h, C.byref(op)))
+
+    def glu(self, op: Op) -> bool:
+        return self._ret(lib().emelb_glu(self._h, C.byref(op)))
 
     def set_peer_wait_ms(self, limit_ms: int) -> bool:
         return self._ret(lib().emelb_set_peer_wait_ms(self._h, limit_ms))

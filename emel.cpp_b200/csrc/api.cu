@@ -143,6 +143,49 @@ bool can_run_flash(const emelb_op& r) {
 }
 
 // ------------------------------------------------------------------ pointers
+// ---- op_rms_norm / op_rope / op_glu guards (src/emel/kernel/detail.hpp:4547-4565, 4650-4702, 5315-5335)
+bool read_param_f32(const emelb_op& r, uint32_t slot, float* out) {
+  if (((uint64_t)slot + 1) * 4 > r.op_params_size || r.op_params_size > 64) return false;
+  std::memcpy(out, r.op_params + 4 * slot, 4);
+  return true;
+}
+bool read_param_i32(const emelb_op& r, uint32_t slot, int32_t* out) {
+  if (((uint64_t)slot + 1) * 4 > r.op_params_size || r.op_params_size > 64) return false;
+  std::memcpy(out, r.op_params + 4 * slot, 4);
+  return true;
+}
+bool same_shape(const emelb_view& a, const emelb_view& b) {
+  return a.ne[0] == b.ne[0] && a.ne[1] == b.ne[1] && a.ne[2] == b.ne[2] && a.ne[3] == b.ne[3];
+}
+// has_required_src0 / has_required_dst of a plain op: data, a supported dtype, a valid layout, elements
+bool required_tensor(const emelb_view& v) {
+  const bool supported = is_supported(v.type) || v.type == T_I32;
+  return v.data != nullptr && supported && valid_layout(v) && elem_count(v) > 0;
+}
+bool can_run_rms_norm(const emelb_op& r) {
+  float eps = 0.0f;
+  return required_tensor(r.src0) && required_tensor(r.dst) && r.op_params_size <= 64 && r.src0.ne[0] > 0 && same_shape(r.src0, r.dst) &&
+         r.src0.type == T_F32 && r.dst.type == T_F32 && read_param_f32(r, 0, &eps) && std::isfinite(eps) && eps >= 0.0f;
+}
+struct RopeParams {
+  int32_t n_dims = 0, mode = 0;
+  float freq_base = 0.0f, freq_scale = 0.0f, ext_factor = 0.0f, attn_factor = 0.0f;
+};
+bool read_rope_params(const emelb_op& r, RopeParams* p) {
+  return read_param_i32(r, 1, &p->n_dims) && read_param_i32(r, 2, &p->mode) && read_param_f32(r, 5, &p->freq_base) &&
+         read_param_f32(r, 6, &p->freq_scale) && read_param_f32(r, 7, &p->ext_factor) && read_param_f32(r, 8, &p->attn_factor);
+}
+constexpr int32_t kRopeNorm = 0, kRopeNeox = 2;
+bool can_run_rope(const emelb_op& r) {
+  RopeParams p;
+  // the positions are checked by the operator's own guard only (data, dtype, layout), not as a required source
+  return required_tensor(r.src0) && r.src1.data != nullptr && valid_layout(r.src1) && required_tensor(r.dst) && r.op_params_size <= 64 &&
+         read_rope_params(r, &p) && same_shape(r.src0, r.dst) && r.src0.ne[0] > 0 && r.src0.type == T_F32 && r.dst.type == T_F32 &&
+         r.src1.type == T_I32 && r.src2.data == nullptr && r.src1.ne[0] == r.src0.ne[2] && p.n_dims > 0 && (p.n_dims % 2) == 0 &&
+         (uint64_t)p.n_dims <= r.src0.ne[0] && p.ext_factor == 0.0f && std::isfinite(p.freq_base) && p.freq_base > 0.0f &&
+         std::isfinite(p.freq_scale) && p.freq_scale > 0.0f && std::isfinite(p.attn_factor);
+}
+
 enum class Where { device, host, unknown };
 
 // device ranges this context allocated itself are known without a driver query
@@ -519,6 +562,9 @@ uint32_t emelb_can_run(const emelb_ctx* c, uint32_t op_code, const emelb_op* op)
   if (op_code == EMELB_OP_MUL_MAT) ok = can_run_mul_mat(*op);
   else if (op_code == EMELB_OP_MUL_MAT_ARGMAX) ok = can_run_mul_mat_argmax(*op);
   else if (op_code == EMELB_OP_FLASH_ATTN_EXT) ok = can_run_flash(*op);
+  else if (op_code == EMELB_OP_RMS_NORM) ok = can_run_rms_norm(*op);
+  else if (op_code == EMELB_OP_ROPE) ok = can_run_rope(*op);
+  else if (op_code == EMELB_OP_GLU) ok = false;   // no row executes op_glu in the reference's kernel actors either
   else return EMELB_UNSUPPORTED_OP;
   return ok ? EMELB_OK : EMELB_INVALID_REQUEST;
 }
@@ -778,6 +824,97 @@ uint32_t emelb_flash_attn_ext(emelb_ctx* c, const emelb_op* op) {
   ok = ok && finish_out(c, out, &need_sync);
   if (ok && need_sync) ok = cuda_ok(c, cudaStreamSynchronize(c->stream));
   return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+// ------------------------------------------------------------------ op_rms_norm / op_rope
+namespace {
+
+// bytes from the first to one past the last element of a strided f32 / i32 tensor
+uint64_t covering_span(const emelb_view& v) {
+  uint64_t span = 4;
+  for (int i = 0; i < 4; ++i) span += (v.ne[i] - 1) * stride_bytes(v, i);
+  return span;
+}
+StridedF32 strided(const emelb_view& v, void* dev) {
+  StridedF32 s{};
+  s.base = static_cast<char*>(dev);
+  for (int i = 0; i < 4; ++i) {
+    s.ne[i] = (int64_t)v.ne[i];
+    s.nb[i] = (int64_t)stride_bytes(v, i);
+  }
+  return s;
+}
+// a host destination whose elements do not fill its covering span is staged in first, so that the bytes between
+// the elements go back unchanged
+bool bind_strided_out(emelb_ctx* c, const emelb_view& v, OutBinding* o) {
+  const uint64_t span = covering_span(v);
+  if (!bind_out(c, v.data, span, 0, o)) return false;
+  if (o->host && !dense(v)) {
+    if (!cuda_ok(c, cudaMemcpyAsync(o->dev, o->host, span, cudaMemcpyHostToDevice, c->stream))) return false;
+    c->diag.h2d_bytes += span;
+  }
+  return true;
+}
+
+}  // namespace
+
+uint32_t emelb_rms_norm(emelb_ctx* c, const emelb_op* op) {
+  if (!c || !op) return EMELB_INVALID_REQUEST;
+  if (!can_run_rms_norm(*op)) return reject(c);
+  cudaSetDevice(c->device);
+  float eps = 0.0f;
+  read_param_f32(*op, 0, &eps);
+  const void* x = stage_in(c, op->src0.data, covering_span(op->src0), 0);
+  OutBinding out{};
+  if (!x || !bind_strided_out(c, op->dst, &out)) {
+    c->diag.rejected_dispatch_calls += 1;
+    return EMELB_UNSUPPORTED_OP;
+  }
+  bool ok = cuda_ok(c, launch_rms_norm_rows(strided(op->src0, const_cast<void*>(x)), strided(op->dst, out.dev), eps, c->stream));
+  c->diag.kernel_launches += 1;
+  bool need_sync = false;
+  ok = ok && finish_out(c, out, &need_sync);
+  if (ok && need_sync) ok = cuda_ok(c, cudaStreamSynchronize(c->stream));
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_rope(emelb_ctx* c, const emelb_op* op) {
+  if (!c || !op) return EMELB_INVALID_REQUEST;
+  if (!can_run_rope(*op)) return reject(c);
+  RopeParams p;
+  read_rope_params(*op, &p);
+  // the adjacent-pair and the half-split pairing; the reference's third variant (mode 4, a timestep embedding with
+  // its own layout) is not on this path
+  if (p.mode != kRopeNorm && p.mode != kRopeNeox) { c->diag.rejected_dispatch_calls += 1; return EMELB_UNSUPPORTED_OP; }
+  cudaSetDevice(c->device);
+  const uint64_t xspan = covering_span(op->src0);
+  const uint64_t poff = (xspan + 255) & ~uint64_t(255);
+  const void* x = stage_in(c, op->src0.data, xspan, 0);
+  const void* pos = stage_in(c, op->src1.data, covering_span(op->src1), poff);
+  OutBinding out{};
+  if (!x || !pos || !bind_strided_out(c, op->dst, &out)) {
+    c->diag.rejected_dispatch_calls += 1;
+    return EMELB_UNSUPPORTED_OP;
+  }
+  // std::pow(freq_base, -2.0f / n_dims) with the host's libm, as the reference computes it: the angles are then
+  // the reference's floats bit for bit (the device's cosf / sinf differ from the host's in the last place at most)
+  const float theta_scale = ::powf(p.freq_base, -2.0f / (float)p.n_dims);
+  bool ok = cuda_ok(c, launch_rope_rows(strided(op->src0, const_cast<void*>(x)), strided(op->dst, out.dev), static_cast<const char*>(pos),
+                                        (int64_t)stride_bytes(op->src1, 0), p.n_dims, p.mode == kRopeNeox ? 1 : 0, theta_scale,
+                                        p.freq_scale, p.attn_factor, c->stream));
+  c->diag.kernel_launches += 1;
+  bool need_sync = false;
+  ok = ok && finish_out(c, out, &need_sync);
+  if (ok && need_sync) ok = cuda_ok(c, cudaStreamSynchronize(c->stream));
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_glu(emelb_ctx* c, const emelb_op* op) {
+  // every op_glu request is rejected by the reference's kernel actors (can_run_backend_request falls through to
+  // can_execute_scalar, which has no op_glu branch: src/emel/kernel/detail.hpp:5166-5203, 5315-5335); the SwiGLU
+  // of the decoder layer is the generator's own loop, restated inside emelb_llama
+  if (!c || !op) return EMELB_INVALID_REQUEST;
+  return reject(c);
 }
 
 // ------------------------------------------------------------------ quantize / dequantize

@@ -361,6 +361,76 @@ cudaError_t launch_rope_store(float* q, const float* k, const float* v, const fl
   return cudaGetLastError();
 }
 
+// ---- op_rms_norm as an op of its own (src/emel/kernel/detail.hpp:4567-4602): per row, f64 sum of the f32
+// squares, scale = 1 / sqrt(mean + eps), out = x * scale (no weight vector: that is the generator's rms_norm)
+__global__ void __launch_bounds__(256) rms_norm_rows_kernel(const StridedF32 src, const StridedF32 dst, float eps) {
+  __shared__ double s_part[8];
+  const int64_t row = blockIdx.x;
+  const int64_t i1 = row % src.ne[1], i2 = (row / src.ne[1]) % src.ne[2], i3 = row / (src.ne[1] * src.ne[2]);
+  const char* srow = src.base + i1 * src.nb[1] + i2 * src.nb[2] + i3 * src.nb[3];
+  char* drow = dst.base + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  double ss = 0.0;
+  for (int64_t i0 = threadIdx.x; i0 < src.ne[0]; i0 += 256) {
+    const float v = *reinterpret_cast<const float*>(srow + i0 * src.nb[0]);
+    ss += (double)__fmul_rn(v, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) s_part[warp] = ss;
+  __syncthreads();
+  double total = 0.0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) total += s_part[w];
+  const float mean = (float)(total / (double)src.ne[0]);
+  const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+  for (int64_t i0 = threadIdx.x; i0 < src.ne[0]; i0 += 256) {
+    const float v = *reinterpret_cast<const float*>(srow + i0 * src.nb[0]);
+    *reinterpret_cast<float*>(drow + i0 * dst.nb[0]) = __fmul_rn(v, scale);
+  }
+}
+
+// ---- op_rope as an op of its own (run_rope_as, src/emel/kernel/detail.hpp:4706-4765): one thread per row;
+// theta starts at the row's position and is multiplied by theta_scale pair after pair (the reference's float
+// recurrence), cos / sin of theta * freq_scale, times attn_factor; dims past n_dims are copied
+__global__ void __launch_bounds__(128) rope_rows_kernel(const StridedF32 src, const StridedF32 dst, const char* pos_base,
+                                                        int64_t pos_stride, int n_dims, int neox, float theta_scale,
+                                                        float freq_scale, float attn_factor) {
+  const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
+  const int64_t row = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  if (row >= rows) return;
+  const int64_t i1 = row % src.ne[1], i2 = (row / src.ne[1]) % src.ne[2], i3 = row / (src.ne[1] * src.ne[2]);
+  const char* srow = src.base + i1 * src.nb[1] + i2 * src.nb[2] + i3 * src.nb[3];
+  char* drow = dst.base + i1 * dst.nb[1] + i2 * dst.nb[2] + i3 * dst.nb[3];
+  const int half = n_dims / 2;
+  float theta = (float)*reinterpret_cast<const int32_t*>(pos_base + i2 * pos_stride);
+  for (int pair = 0; pair < half; ++pair, theta = __fmul_rn(theta, theta_scale)) {
+    const float rotated = __fmul_rn(theta, freq_scale);
+    const float cs = __fmul_rn(cosf(rotated), attn_factor), sn = __fmul_rn(sinf(rotated), attn_factor);
+    const int64_t a = neox ? pair : 2 * pair, b = neox ? pair + half : 2 * pair + 1;
+    const float x0 = *reinterpret_cast<const float*>(srow + a * src.nb[0]);
+    const float x1 = *reinterpret_cast<const float*>(srow + b * src.nb[0]);
+    *reinterpret_cast<float*>(drow + a * dst.nb[0]) = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+    *reinterpret_cast<float*>(drow + b * dst.nb[0]) = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+  }
+  for (int64_t i0 = n_dims; i0 < src.ne[0]; ++i0)
+    *reinterpret_cast<float*>(drow + i0 * dst.nb[0]) = *reinterpret_cast<const float*>(srow + i0 * src.nb[0]);
+}
+
+cudaError_t launch_rms_norm_rows(const StridedF32& src, const StridedF32& dst, float eps, cudaStream_t st) {
+  const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
+  rms_norm_rows_kernel<<<(unsigned)rows, 256, 0, st>>>(src, dst, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope_rows(const StridedF32& src, const StridedF32& dst, const char* pos_base, int64_t pos_stride, int n_dims,
+                             int neox, float theta_scale, float freq_scale, float attn_factor, cudaStream_t st) {
+  const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
+  rope_rows_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, st>>>(src, dst, pos_base, pos_stride, n_dims, neox, theta_scale,
+                                                                   freq_scale, attn_factor);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out, int family, ActPlanesMut planes,
                           cudaStream_t st) {
   if (family == 1) EMELB_LAUNCH(swiglu_kernel<1>, n / QK_K, 256, 0, st, gate, up, n, out, planes);

@@ -151,6 +151,16 @@ struct PrefillAttnArgs {
 };
 bool prefill_attention_supported(const PrefillAttnArgs& a);
 cudaError_t launch_prefill_attention(const PrefillAttnArgs& a, cudaStream_t st);
+// op_rms_norm / op_rope as stand-alone ops over strided f32 tensors (byte strides, up to 4 dims)
+struct StridedF32 {
+  char* base;
+  int64_t ne[4];
+  int64_t nb[4];
+};
+cudaError_t launch_rms_norm_rows(const StridedF32& src, const StridedF32& dst, float eps, cudaStream_t st);
+// positions: i32, element i2 at pos_base + i2 * pos_stride; theta_scale = powf(freq_base, -2 / n_dims) from the host libm
+cudaError_t launch_rope_rows(const StridedF32& src, const StridedF32& dst, const char* pos_base, int64_t pos_stride, int n_dims,
+                             int neox, float theta_scale, float freq_scale, float attn_factor, cudaStream_t st);
 // state = {token, position, kv_tokens, step}
 cudaError_t launch_step_begin(int* state, int token, int position, cudaStream_t st);
 cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out, cudaStream_t st);

@@ -96,6 +96,22 @@ class sm {
     return finish(emelb_flash_attn_ext(ctx_, &op));
   }
 
+  bool process_event(const ::emel::kernel::event::op_rms_norm& ev) noexcept {
+    const emelb_op op = detail::to_op(ev);
+    return finish(emelb_rms_norm(ctx_, &op));
+  }
+
+  bool process_event(const ::emel::kernel::event::op_rope& ev) noexcept {
+    const emelb_op op = detail::to_op(ev);
+    return finish(emelb_rope(ctx_, &op));
+  }
+
+  // rejected as by the reference's own backends (no row executes op_glu there)
+  bool process_event(const ::emel::kernel::event::op_glu& ev) noexcept {
+    const emelb_op op = detail::to_op(ev);
+    return finish(emelb_glu(ctx_, &op));
+  }
+
   // every other op event: no row in this backend
   template <class event_type>
   bool process_event(const event_type&) noexcept {

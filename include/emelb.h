@@ -87,7 +87,10 @@ typedef struct emelb_op {
 enum {
   EMELB_OP_MUL_MAT = 1,
   EMELB_OP_MUL_MAT_ARGMAX = 2,
-  EMELB_OP_FLASH_ATTN_EXT = 3
+  EMELB_OP_FLASH_ATTN_EXT = 3,
+  EMELB_OP_RMS_NORM = 4,
+  EMELB_OP_ROPE = 5,
+  EMELB_OP_GLU = 6
 };
 
 /* lifecycle: src/emel/model/tensor/events.hpp:18-24 */
@@ -225,6 +228,30 @@ EMELB_API uint32_t emelb_mul_mat_argmax(emelb_ctx* ctx, const emelb_op* op);
  * (src/emel/kernel/detail.hpp:5238-5300) and the AVX2 one-chunk route
  * (src/emel/kernel/x86_64/actions.hpp:1575-1641). ---- */
 EMELB_API uint32_t emelb_flash_attn_ext(emelb_ctx* ctx, const emelb_op* op);
+
+/* ---- op_rms_norm: replaces run_rms_norm (src/emel/kernel/detail.hpp:4567-4602;
+ * event src/emel/kernel/events.hpp:215): src0 and dst f32 of the same shape, any
+ * valid byte strides; per row out = x / sqrt(mean(x^2) + eps) with the f64 sum of
+ * the f32 squares; op_params = {f32 eps >= 0}.  (The weight multiply of the
+ * decoder's rms_norm is the generator's, not this op's.) ---- */
+EMELB_API uint32_t emelb_rms_norm(emelb_ctx* ctx, const emelb_op* op);
+
+/* ---- op_rope: replaces run_rope_as (src/emel/kernel/detail.hpp:4650-4765; event
+ * src/emel/kernel/events.hpp:242): src0/dst f32 {dims, heads, tokens, batch}, src1
+ * i32 positions {tokens}, op_params in ggml's layout (i32 slots 1 = n_dims,
+ * 2 = mode; f32 slots 5..8 = freq_base, freq_scale, ext_factor (must be 0),
+ * attn_factor).  mode 0 rotates adjacent pairs, mode 2 the half-split pairs; the
+ * angle recurrence (theta *= powf(freq_base, -2/n_dims), host libm) is the
+ * reference's float for float, cos/sin come from the device library (last-place
+ * differences).  Mode 4 (the timestep-embedding variant) returns
+ * EMELB_UNSUPPORTED_OP. ---- */
+EMELB_API uint32_t emelb_rope(emelb_ctx* ctx, const emelb_op* op);
+
+/* ---- op_glu (src/emel/kernel/events.hpp:307-310): the reference's kernel actors
+ * reject every op_glu request (no branch of can_execute_scalar takes it,
+ * src/emel/kernel/detail.hpp:5166-5203), and so does this backend:
+ * EMELB_INVALID_REQUEST.  The decoder layer's SwiGLU lives in emelb_llama. ---- */
+EMELB_API uint32_t emelb_glu(emelb_ctx* ctx, const emelb_op* op);
 
 /* ---- the same attention for a batch of prompt tokens: query token j (of `batch`)
  * sits at position pos0 + j and attends to cache positions 0 .. pos0 + j.  The

@@ -230,7 +230,7 @@ class Ref(_Lib):
         super().__init__(lib, "ref_")
         self.f("can_run").restype = C.c_int
         self.f("can_run").argtypes = [C.c_uint32, C.POINTER(Op)]
-        for n in ("mul_mat_scalar", "mul_mat_avx2", "mul_mat_argmax", "flash_attn_scalar", "flash_attn_avx2"):
+        for n in ("mul_mat_scalar", "mul_mat_avx2", "mul_mat_argmax", "flash_attn_scalar", "flash_attn_avx2", "rms_norm", "rope"):
             self.f(n).restype = C.c_int
             self.f(n).argtypes = [C.POINTER(Op)]
         self.f("mul_mat_avx2_lanes").restype = C.c_int
@@ -246,6 +246,12 @@ class Ref(_Lib):
 
     def can_run(self, code, op):
         return bool(self.f("can_run")(code, C.byref(op)))
+
+    def rms_norm(self, op):
+        return bool(self.f("rms_norm")(C.byref(op)))
+
+    def rope(self, op):
+        return bool(self.f("rope")(C.byref(op)))
 
     def gguf_probe(self, image: bytes):
         """-> (error, (tensor_count, kv_count, max_key_bytes, max_value_bytes, tensor_data_bytes))"""

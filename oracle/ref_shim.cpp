@@ -118,6 +118,38 @@ int ref_can_run(uint32_t op_code, const emelb_op* op) {
     const auto r = to_op<ev::op_flash_attn_ext>(*op);
     return kd::validate_dispatch_request(r) && kd::can_run_flash_attn_ext(r);
   }
+  // the x86 actor's guard for these: validate_dispatch_request && can_run_backend_request
+  // (src/emel/kernel/x86_64/guards.hpp valid_op; src/emel/kernel/detail.hpp:5315-5335)
+  if (op_code == EMELB_OP_RMS_NORM) {
+    const auto r = to_op<ev::op_rms_norm>(*op);
+    return kd::validate_dispatch_request(r) && kd::can_run_backend_request(r);
+  }
+  if (op_code == EMELB_OP_ROPE) {
+    const auto r = to_op<ev::op_rope>(*op);
+    return kd::validate_dispatch_request(r) && kd::can_run_backend_request(r);
+  }
+  if (op_code == EMELB_OP_GLU) {
+    const auto r = to_op<ev::op_glu>(*op);
+    return kd::validate_dispatch_request(r) && kd::can_run_backend_request(r);
+  }
+  return 0;
+}
+
+// ---- op_rms_norm (src/emel/kernel/detail.hpp:4567-4602)
+int ref_rms_norm(const emelb_op* op) {
+  const auto r = to_op<ev::op_rms_norm>(*op);
+  if (!(kd::validate_dispatch_request(r) && kd::can_run_norm_row_op(r))) return 0;
+  return kd::run_rms_norm(r) ? 1 : 0;
+}
+
+// ---- op_rope, adjacent-pair (mode 0) and half-split (mode 2) variants (src/emel/kernel/detail.hpp:4706-4765)
+int ref_rope(const emelb_op* op) {
+  const auto r = to_op<ev::op_rope>(*op);
+  if (!(kd::validate_dispatch_request(r) && kd::can_run_rope(r))) return 0;
+  kd::rope_op_params p{};
+  (void)kd::read_rope_params(r, p);
+  if (p.mode == kd::rope_mode_norm) return kd::run_rope_as<false>(r) ? 1 : 0;
+  if (p.mode == kd::rope_mode_neox) return kd::run_rope_as<true>(r) ? 1 : 0;
   return 0;
 }
 
