@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(1024) peer_gather_kernel(PeerGatherArgs a) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
       if ((int)(v - seq) >= 0) { ok = true; break; }
       if ((spins & 1023) == 1023) {
+        if (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) break;   // an earlier wait already ran out
         unsigned long long now;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
         if (t0 == 0) t0 = now;

@@ -10,6 +10,7 @@
 // -fmad=false: every product and sum rounds as written in the reference.
 #include "expf_exact.h"
 #include "quant_device.cuh"
+#include "peer_join.cuh"
 
 namespace emelb {
 
@@ -428,6 +429,34 @@ cudaError_t launch_rope_rows(const StridedF32& src, const StridedF32& dst, const
   const int64_t rows = src.ne[1] * src.ne[2] * src.ne[3];
   rope_rows_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, st>>>(src, dst, pos_base, pos_stride, n_dims, neox, theta_scale,
                                                                    freq_scale, attn_factor);
+  return cudaGetLastError();
+}
+
+// the SwiGLU of this rank's interval of the ffn vector: one 256-block per CTA, quantized to Q8_K once and written
+// into every rank's planes of the joined vector
+__global__ void __launch_bounds__(256) swiglu_join_kernel(const float* __restrict__ gate, const float* __restrict__ up, JoinOut join) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float s_v[QK_K];
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * QK_K + threadIdx.x;
+  const float g = gate[e];
+  s_v[threadIdx.x] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf_exact(-g))), up[e]);
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = s_v[8 * lane + i];
+    uint32_t lo, hi; int bs; float d;
+    q8_k_block_warp(v, lane, lo, hi, bs, d);
+    join_store_q8_k_block(join, join.first_block + blockIdx.x, lane, lo, hi, bs, d);
+  }
+  join_publish(join, gridDim.x);
+}
+
+cudaError_t launch_swiglu_join(const float* gate, const float* up, int n, const JoinOut& join, cudaStream_t st) {
+  if (n % QK_K != 0) return cudaErrorInvalidValue;
+  EMELB_LAUNCH(swiglu_join_kernel, n / QK_K, 256, 0, st, gate, up, join);
   return cudaGetLastError();
 }
 

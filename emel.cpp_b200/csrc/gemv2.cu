@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "peer_join.cuh"
 #include "quant_device.cuh"
 
 namespace emelb {
@@ -619,6 +620,14 @@ gemv3_kernel(const GemvArgs p) {
 #pragma unroll
   for (int s = 0; s < STAGES; ++s) issue_next(s);
   pdl_wait();
+  // a joined input vector: every peer's rows must have landed before the first read
+  bool joined_in = false;
+  if constexpr (KQ && NCOLS == 1) {
+    if (p.join_in.flags) {
+      joined_in = true;
+      join_wait(p.join_in, p.status);
+    }
+  }
 
   // this column's quantized activations in shared memory for the whole CTA: copied from the planes, or
   // (fused prologue) normalised and quantized here from the f32 vector
@@ -633,31 +642,42 @@ gemv3_kernel(const GemvArgs p) {
     if constexpr (KQ && NCOLS == 1) {
       if (p.pro_x) {
         fused = true;
-        // rms_norm (src/emel/text/generator/detail.hpp:2735-2756): f64 sum of the f32 squares
-        __shared__ double s_part[WARPS];
-        double ss = 0.0;
-        for (int i = threadIdx.x; i < p.K; i += WARPS * 32) {
-          const float v = __ldg(p.pro_x + i);
-          ss += (double)__fmul_rn(v, v);
+        // rows written by peers are read past the L1 (ld.cg): a line of an earlier read may still sit there
+        auto ldx = [&](const float* a) { return joined_in ? __ldcg(a) : __ldg(a); };
+        auto ldx4 = [&](const float* a) { return joined_in ? __ldcg(reinterpret_cast<const float4*>(a)) : __ldg(reinterpret_cast<const float4*>(a)); };
+        float scale = 1.0f;
+        if (p.pro_w) {
+          // rms_norm (src/emel/text/generator/detail.hpp:2735-2756): f64 sum of the f32 squares
+          __shared__ double s_part[WARPS];
+          double ss = 0.0;
+          for (int i = threadIdx.x; i < p.K; i += WARPS * 32) {
+            const float v = ldx(p.pro_x + i);
+            ss += (double)__fmul_rn(v, v);
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (lane == 0) s_part[warp] = ss;
+          __syncthreads();
+          double total = 0.0;
+#pragma unroll
+          for (int w = 0; w < WARPS; ++w) total += s_part[w];
+          const float mean = (float)(total / (double)p.K);
+          scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.pro_eps)));
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) s_part[warp] = ss;
-        __syncthreads();
-        double total = 0.0;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) total += s_part[w];
-        const float mean = (float)(total / (double)p.K);
-        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.pro_eps)));
         for (int blk = warp; blk < p.K / QK_K; blk += WARPS) {
           float v[8];
           const int e0 = blk * QK_K + 8 * lane;
-          const float4 x0 = __ldg(reinterpret_cast<const float4*>(p.pro_x + e0)), x1 = __ldg(reinterpret_cast<const float4*>(p.pro_x + e0) + 1);
-          const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.pro_w + e0)), w1 = __ldg(reinterpret_cast<const float4*>(p.pro_w + e0) + 1);
+          const float4 x0 = ldx4(p.pro_x + e0), x1 = ldx4(p.pro_x + e0 + 4);
           const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-          const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          if (p.pro_w) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(p.pro_w + e0)), w1 = __ldg(reinterpret_cast<const float4*>(p.pro_w + e0) + 1);
+            const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(xs[i], scale), ws[i]);
+            for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(xs[i], scale), ws[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = xs[i];
+          }
           uint32_t lo, hi; int bs16; float dq;
           q8_k_block_warp(v, lane, lo, hi, bs16, dq);
           const int unit = blk * 16 + ((lane >> 1) ^ (blk & 7));        // the swizzled 16-byte unit of elements 8*lane..
@@ -670,14 +690,16 @@ gemv3_kernel(const GemvArgs p) {
     if (!fused) {
       const int64_t gcol = p.col0 + col;
       const int4* gq = reinterpret_cast<const int4*>(p.act.qs + gcol * p.act.col_stride_qs);
-      for (int i = threadIdx.x; i < p.K / 16; i += WARPS * 32) reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = __ldg(gq + i);
+      // planes written by peers are read past the L1 (ld.cg): a line of an earlier read may still sit there
+      for (int i = threadIdx.x; i < p.K / 16; i += WARPS * 32)
+        reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = joined_in ? __ldcg(gq + i) : __ldg(gq + i);
       if constexpr (KQ) {
         const int4* gb = reinterpret_cast<const int4*>(p.act.bsums + gcol * p.act.col_stride_bs);
-        for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = __ldg(gb + i);
+        for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = joined_in ? __ldcg(gb + i) : __ldg(gb + i);
       }
       const float* gd = p.act.d + gcol * p.act.col_stride_d;
       const int nd = KQ ? p.K / QK_K : p.K / 32;
-      for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = __ldg(gd + i);
+      for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = joined_in ? __ldcg(gd + i) : __ldg(gd + i);
     }
     if (col == 0) {
       x.qs = sq;
@@ -781,6 +803,21 @@ gemv3_kernel(const GemvArgs p) {
           }
         }
       }
+      if constexpr (KQ && !ARGMAX && NCOLS == 1) {
+        if (p.join_out.world > 1) {
+          // this rank's rows go to every rank's copy of the vector: the four rows of the task are collected and
+          // lanes 0 .. world-1 store them to one rank each (row counts are multiples of four in a sharded session)
+          plain = false;
+          float o = acc;
+          if (b == 0 && row < mseg && p.residual) o = __fadd_rn(p.residual[row], acc);
+          const float4 o4 = make_float4(__shfl_sync(0xffffffffu, o, 0), __shfl_sync(0xffffffffu, o, 8),
+                                        __shfl_sync(0xffffffffu, o, 16), __shfl_sync(0xffffffffu, o, 24));
+          char* base = lane < p.join_out.world ? join_base(p.join_out, lane) : nullptr;
+          const int row0 = lt * ROWS_PER_STAGE;
+          if (base && row0 + ROWS_PER_STAGE <= mseg)
+            *reinterpret_cast<float4*>(base + p.join_out.out_offset + (int64_t)row0 * 4) = o4;
+        }
+      }
       if (plain && row < mseg) {
         if constexpr (ARGMAX) {
           if (acc > best || best_i == 0x7fffffff) { best = acc; best_i = row; }
@@ -800,6 +837,8 @@ gemv3_kernel(const GemvArgs p) {
   }
   if (failed && lane == 0 && p.status) atomicExch(p.status, 1);
 
+  constexpr bool kJoins = KQ && !ARGMAX && NCOLS == 1;
+  if (kJoins && p.join_out.world > 1) __threadfence_system();   // this thread's stores to the peers, before the block is counted
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -807,6 +846,7 @@ gemv3_kernel(const GemvArgs p) {
       p.sched[0] = 0;
       p.sched[1] = 0;
       __threadfence();
+      if (kJoins && p.join_out.world > 1) join_raise(p.join_out);
     }
   }
 

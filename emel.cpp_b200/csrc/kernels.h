@@ -36,6 +36,31 @@ constexpr int kMaxArgmaxParts = 2048;
 
 constexpr int kSchedSlots = 64;   // task-counter slots rotated over consecutive mat-vec launches
 
+// ---- joins of row intervals by peer stores, fused into the kernels either side of the join (same node, one
+// rank per GPU).  The producing kernel writes its output rows into every rank's copy of the vector (the
+// exchange arenas hold it at the same offset) and its last block raises this rank's flag on every peer with the
+// join's new sequence number; the consuming kernel waits, bounded, until every peer's flag has reached this
+// rank's own sequence number before it reads the vector.  Plain peer stores and loads only.
+constexpr int kMaxPeers = 8;
+struct JoinOut {
+  char* base[kMaxPeers];   // every rank's exchange arena as mapped here (base[rank] is this rank's own)
+  int64_t out_offset;      // f32 output: byte offset inside the arena of the first element this rank produces
+  // Q8_K output (the producer quantizes its interval once, every rank's next product reads the planes): byte
+  // offsets inside the arena of the full vector's planes, and the first 256-block this rank produces
+  int64_t qs_offset, bsums_offset, d_offset;
+  int first_block;
+  unsigned flag_offset;    // byte offset inside the arena of the join's flag row (one u32 per sender)
+  unsigned* seq;           // this rank's sequence counter of the join
+  int* done;               // finished-block counter, zero between launches (kernels without one of their own)
+  int world, rank;         // world <= 1: no join, a plain local store
+};
+struct JoinIn {
+  const unsigned* flags;   // this rank's copy of the join's flag row; null: nothing to wait for
+  const unsigned* seq;     // this rank's sequence counter of the join: the value every peer's flag must reach
+  int world, rank;
+  unsigned long long wait_ns;
+};
+
 struct GemvArgs {
   const uint8_t* W;      // {K, M} native block rows
   int64_t row_bytes;
@@ -66,9 +91,14 @@ struct GemvArgs {
   // optional fused prologue of the one-column streaming kernel (K-quant weights only): instead of reading
   // `act`, every CTA normalises pro_x itself, out = (x * 1/sqrt(mean(x^2) + eps)) * pro_w, and quantizes it to
   // Q8_K in shared memory — the rms_norm step of the layer without its own launch
+  // pro_w == null: no normalisation, the f32 vector is quantized as it is
   const float* pro_x;
   const float* pro_w;
   float pro_eps;
+  // one-column plain products of a row-sharded session: wait for join_in before reading pro_x or the planes,
+  // and / or write the f32 rows (ldy == 1, first matrix only) to every rank and raise join_out
+  JoinIn join_in;
+  JoinOut join_out;
   uint8_t* tc_ws;        // workspace of the many-column tensor-core kernel (null: that kernel is not used)
   size_t tc_ws_bytes;
   int tc_ws_reuse;       // the previous many-column Q4_K product of this stream used the same planes, K, columns and col0
@@ -123,6 +153,8 @@ cudaError_t launch_rms_norm(const float* x, const float* w, float eps, int n, fl
 cudaError_t launch_rope_store(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t,
                               const int* pos_dev, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
                               __half* kcache, __half* vcache, int64_t cache_head_stride, cudaStream_t st);
+// join: the product of this rank's n elements (a multiple of 256) goes, quantized to Q8_K, into every rank's planes
+cudaError_t launch_swiglu_join(const float* gate, const float* up, int n, const JoinOut& join, cudaStream_t st);
 cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out, int family, ActPlanesMut planes,
                           cudaStream_t st);
 cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, const int* token_dev, float* dst, int K,
@@ -178,7 +210,6 @@ cudaError_t launch_argmax_pair_store(const float* best_val, const int* best_idx,
 cudaError_t launch_argmax_pair_finish(const int* pairs, int n, float* out_val, int* out_idx, cudaStream_t st);
 
 // comm.cu — join of row intervals by peer stores (one rank per GPU, same node)
-constexpr int kMaxPeers = 8;
 struct PeerGatherArgs {
   char* local_base;            // this rank's arena
   char* peer_base[kMaxPeers];  // every rank's arena as mapped here (own entry = local_base)
@@ -247,6 +278,7 @@ struct FlashArgs {
   int splits;            // KV splits per kv head
   float* part_acc;       // [H][splits][d]
   float* part_ml;        // [H][splits][2]  (running max, running sum)
+  JoinOut join_out;      // split-KV merge step (world > 1): this rank's heads, quantized to Q8_K, go into every rank's planes
 };
 // out_family 1 / 2: the merge step also writes the result quantized (Q8_K / Q8_0 planes, one column) for the
 // matrix product that consumes it; only when flash_merge_can_quantize(a)

@@ -81,8 +81,10 @@ struct emelb_llama {
   // peers can map it; with every peer attached the joins run as peer stores instead of NCCL calls
   char* arena = nullptr;
   size_t arena_bytes = 0, flags_off = 0, seq_off = 0;
+  ActPlanesMut attn_planes{}, ffn_planes{};   // Q8_K planes of the joined attention context / SwiGLU product (in the arena)
   char* peer_base[kMaxPeers] = {};
   bool peers_attached = false;
+  bool fused_joins = true;    // peers attached: joins inside the producing / consuming kernels where a layer qualifies
   cudaGraphExec_t graphs[MODE_COUNT] = {nullptr, nullptr, nullptr};
   int graph_attention_mode[MODE_COUNT] = {-1, -1, -1};
   int launches_per_token = 0;          // of the argmax step
@@ -277,13 +279,89 @@ struct Enqueue {
   // shapes, the normalisation and quantization run inside the mat-vec launch (no rms_norm kernel).
   // rope_layer >= 0: the group is this layer's Q, K, V and the launch also applies RoPE and writes the KV rows;
   // returns whether that happened (false: the caller runs the RoPE / KV-store kernel)
-  bool normed_matvec_group(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax = false,
-                           int rope_layer = -1) {
+  // whether the normalisation of x can run inside the launch of this group of matrices
+  bool group_fusable(const float* x, const Tensor& nw, const Tensor* const* w, int n) const {
     bool fuse = (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
                 (reinterpret_cast<uintptr_t>(nw.dev) % 16) == 0 && n >= 1 && n <= 3;
     for (int i = 0; fuse && i < n; ++i)
       fuse = gemv_prologue_supported(w[i]->type, w[i]->dev, w[i]->row_bytes, w[i]->K) && w[i]->type == w[0]->type &&
              w[i]->K == w[0]->K && w[i]->row_bytes == w[0]->row_bytes && w[i]->K == s->cfg.n_embd;
+    return fuse;
+  }
+
+  // ---- joins fused into the kernels either side of them (peers attached).  One flag row, sequence counter and
+  // block counter per join of a layer; row 0 belongs to the stand-alone join kernel.
+  enum JoinId { J_NONE = 0, J_ATTN = 1, J_HIDDEN_A = 2, J_FFN = 3, J_HIDDEN_B = 4 };
+  JoinOut join_out(int id, const void* first) const {
+    JoinOut j{};
+    if (id == J_NONE) return j;
+    for (int g = 0; g < s->G; ++g) j.base[g] = s->peer_base[g];
+    j.out_offset = first ? static_cast<const char*>(first) - s->arena : 0;
+    j.flag_offset = (unsigned)(s->flags_off + 32 * (size_t)id);
+    j.seq = reinterpret_cast<unsigned*>(s->arena + s->seq_off) + id;
+    j.done = reinterpret_cast<int*>(s->arena + s->seq_off + 64) + id;
+    j.world = s->G;
+    j.rank = s->rank;
+    return j;
+  }
+  // the producer quantizes its interval (elems_per_rank, a multiple of 256) into every rank's planes
+  JoinOut join_out_planes(int id, const ActPlanesMut& pl, size_t elems_per_rank) const {
+    JoinOut j = join_out(id, nullptr);
+    j.qs_offset = reinterpret_cast<const char*>(pl.qs) - s->arena;
+    j.bsums_offset = reinterpret_cast<const char*>(pl.bsums) - s->arena;
+    j.d_offset = reinterpret_cast<const char*>(pl.d) - s->arena;
+    j.first_block = (int)((size_t)s->rank * elems_per_rank / QK_K);
+    return j;
+  }
+  JoinIn join_in(int id) const {
+    JoinIn j{};
+    if (id == J_NONE) return j;
+    j.flags = reinterpret_cast<const unsigned*>(s->arena + s->flags_off + 32 * (size_t)id);
+    j.seq = reinterpret_cast<const unsigned*>(s->arena + s->seq_off) + id;
+    j.world = s->G;
+    j.rank = s->rank;
+    j.wait_ns = s->c->peer_wait_ns;
+    return j;
+  }
+  // whether every join of layer l can run inside its neighbours: the split-KV merge step produces the attention
+  // context, and every product of the layer takes the streaming kernel with the quantization in its prologue
+  bool layer_joins_fusable(int l) const {
+    if (s->G <= 1 || !s->peers_attached || !s->fused_joins || s->c->attention_mode != 0) return false;
+    const emelb_llama_config& c = s->cfg;
+    const Layer& w = s->layers[l];
+    const int64_t q_l = (int64_t)(c.n_head / s->G) * c.head_dim;
+    if (q_l % 256 != 0 || (c.n_ff / s->G) % 256 != 0 || !flash_split_supported(flash_args(l))) return false;
+    const Tensor* qkv[3] = {&w.wq, &w.wk, &w.wv};
+    const Tensor* gu[2] = {&w.gate, &w.up};
+    if (!group_fusable(s->hidden, w.attn_norm, qkv, 3) || !group_fusable(s->hidden, w.ffn_norm, gu, 2)) return false;
+    const Tensor* ws[2] = {&w.wo, &w.down};
+    for (const Tensor* t : ws)
+      if (!gemv_prologue_supported(t->type, t->dev, t->row_bytes, t->K) || t->M % 4 != 0) return false;
+    return true;
+  }
+  // y (this rank's rows) = [residual +] w x, x the joined vector whose Q8_K planes the producers of join `in` have
+  // written into this rank's arena: the launch waits for that join and, with `out`, writes its rows to every rank
+  void joined_matvec(const Tensor& w, const ActPlanesMut& x_planes, float* y, const float* residual, int in, int out) {
+    GemvArgs a{};
+    a.W = w.dev;
+    a.row_bytes = w.row_bytes;
+    a.M = w.M;
+    a.K = w.K;
+    a.act = planes_view(x_planes, w.type, w.K);
+    a.y = y;
+    a.ldy = 1;
+    a.residual = residual;
+    a.join_in = join_in(in);
+    a.join_out = join_out(out, y);
+    a.sched = s->c->next_sched();
+    a.status = s->c->status_word();
+    a.pdl = s->c->pdl & 1;
+    check(launch_gemv(w.type, a, 1, false, s->c->sm_count, st, &launches));
+  }
+
+  bool normed_matvec_group(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax = false,
+                           int rope_layer = -1, int in_join = 0) {
+    const bool fuse = group_fusable(x, nw, w, n);
     if (!fuse) {
       rms_norm(x, nw, family_of(w[0]->type));
       if (n == 1) matvec(*w[0], s->norm, y ? y[0] : nullptr, nullptr, argmax);
@@ -305,6 +383,7 @@ struct Enqueue {
     a.pro_x = x;
     a.pro_w = reinterpret_cast<const float*>(nw.dev);
     a.pro_eps = s->cfg.rms_eps;
+    a.join_in = join_in(in_join);
     if (rope) {
       const int64_t layer_off = (int64_t)rope_layer * (cfg.n_head_kv / s->G) * s->capacity * cfg.head_dim;
       a.rope_cos = s->rope_cos;
@@ -330,7 +409,7 @@ struct Enqueue {
 
   // attention of one layer; when the split-KV kernels run unsharded, their merge step also leaves the
   // context quantized for the output projection (family of wo's type)
-  void attention(int layer, int out_family) {
+  FlashArgs flash_args(int layer) const {
     const emelb_llama_config& c = s->cfg;
     const int64_t layer_off = (int64_t)layer * (c.n_head_kv / s->G) * s->capacity * c.head_dim;
     FlashArgs a{};
@@ -349,6 +428,12 @@ struct Enqueue {
     a.splits = s->fa_splits;
     a.part_acc = s->c->fa_part_acc;
     a.part_ml = s->c->fa_part_ml;
+    return a;
+  }
+  void attention(int layer, int out_family, int out_join = 0) {
+    const emelb_llama_config& c = s->cfg;
+    FlashArgs a = flash_args(layer);
+    if (out_join) a.join_out = join_out_planes(out_join, s->attn_planes, (size_t)a.heads * a.head_dim);
     if (s->c->attention_mode == 0 && flash_split_supported(a)) {
       const bool fuse = s->G == 1 && flash_merge_can_quantize(a);
       check(launch_flash_decode(a, s->c->sm_count, st, &launches, fuse ? out_family : 0, planes()));
@@ -498,13 +583,14 @@ struct Enqueue {
       check(launch_llama_token(token_args(s), s->c->sm_count, &s->token_launch, st));
       ++launches;
     }
+    bool hidden_joined_in_next = false;   // the previous layer left the join of the hidden vector to this layer's first launch
     for (int l = 0; l < c.n_layer && !one_kernel; ++l) {
       const Layer& w = s->layers[l];
       bool roped = false;
       {
         const Tensor* ws[3] = {&w.wq, &w.wk, &w.wv};
         float* ys[3] = {s->q, s->k, s->v};
-        roped = normed_matvec_group(s->hidden, w.attn_norm, ws, ys, 3, false, l);
+        roped = normed_matvec_group(s->hidden, w.attn_norm, ws, ys, 3, false, l, hidden_joined_in_next ? J_HIDDEN_B : J_NONE);
       }
       if (!roped) {
         const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
@@ -514,22 +600,34 @@ struct Enqueue {
                                 s->vcache + layer_off, s->capacity * c.head_dim, st));
         ++launches;
       }
+      // joins of this layer inside its kernels (peers attached and every product qualifies), else one join kernel
+      // (or NCCL call) each; the hidden vector after the down projection is joined inside the next layer's first
+      // launch only when that layer qualifies too
+      const bool fj = layer_joins_fusable(l);
+      const bool fj_next = fj && l + 1 < c.n_layer && layer_joins_fusable(l + 1);
       g_pdl_launch = (pm & 4) != 0;
-      attention(l, family_of(w.wo.type));
+      attention(l, family_of(w.wo.type), fj ? J_ATTN : J_NONE);
       g_pdl_launch = (pm & 16) != 0;
-      gather(s->attn, q_l);
-      matvec(w.wo, s->attn, hidden_mine, hidden_mine);   // hidden += Wo * attn (this rank's rows)
-      gather(s->hidden, embd_l);
+      if (fj) {
+        joined_matvec(w.wo, s->attn_planes, hidden_mine, hidden_mine, J_ATTN, J_HIDDEN_A);   // hidden += Wo * attn (this rank's rows)
+      } else {
+        gather(s->attn, q_l);
+        matvec(w.wo, s->attn, hidden_mine, hidden_mine);
+        gather(s->hidden, embd_l);
+      }
       {
         const Tensor* ws[2] = {&w.gate, &w.up};
         float* ys[2] = {s->gate, s->up};
-        normed_matvec_group(s->hidden, w.ffn_norm, ws, ys, 2);
+        normed_matvec_group(s->hidden, w.ffn_norm, ws, ys, 2, false, -1, fj ? J_HIDDEN_A : J_NONE);
       }
       g_pdl_launch = (pm & 8) != 0;
       if (G == 1) {
         check(launch_swiglu(s->gate, s->up, c.n_ff, nullptr, family_of(w.down.type), planes(), st));  // only the quantized product is consumed
         s->planes_src = s->ffn;
         s->planes_family = family_of(w.down.type);
+      } else if (fj) {
+        check(launch_swiglu_join(s->gate, s->up, (int)ff_l, join_out_planes(J_FFN, s->ffn_planes, ff_l), st));
+        s->planes_src = nullptr;
       } else {
         // the product is quantized after the join, over the full vector
         check(launch_swiglu(s->gate, s->up, (int)ff_l, s->ffn + r * ff_l, 0, planes(), st));
@@ -537,9 +635,15 @@ struct Enqueue {
       }
       ++launches;
       g_pdl_launch = (pm & 16) != 0;
-      gather(s->ffn, ff_l);
-      matvec(w.down, s->ffn, hidden_mine, hidden_mine);  // hidden += Wdown * ffn
-      gather(s->hidden, embd_l);
+      if (fj) {
+        joined_matvec(w.down, s->ffn_planes, hidden_mine, hidden_mine, J_FFN, fj_next ? J_HIDDEN_B : J_NONE);   // hidden += Wdown * ffn
+        if (!fj_next) gather(s->hidden, embd_l);
+      } else {
+        gather(s->ffn, ff_l);
+        matvec(w.down, s->ffn, hidden_mine, hidden_mine);
+        gather(s->hidden, embd_l);
+      }
+      hidden_joined_in_next = fj_next;
     }
     if (mode == MODE_PREFILL) return;
     const size_t vocab_l = (size_t)c.n_vocab / G;
@@ -651,12 +755,17 @@ uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_l
   const int pairs = (g.rope_dim < g.head_dim ? g.rope_dim : g.head_dim) / 2;
   bool ok = true;
   if (G > 1) {
-    // [hidden | attn | ffn | logits | pairs | flags | seq], each part 256-byte aligned, zero-filled
+    // [hidden | attn | ffn | logits | pairs | flags | seq], each part 256-byte aligned, zero-filled.  flags: five
+    // rows of kMaxPeers u32 (the join kernel's, then one per fused join of a layer); seq: their sequence counters,
+    // then at byte 64 their finished-block counters
     auto up = [](size_t b) { return (b + 255) & ~size_t(255); };
     const size_t o_hidden = 0, o_attn = o_hidden + up(4 * (size_t)g.n_embd), o_ffn = o_attn + up(4 * qd),
                  o_logits = o_ffn + up(4 * (size_t)g.n_ff), o_pairs = o_logits + up(4 * (size_t)g.n_vocab),
-                 o_flags = o_pairs + up(16 * (size_t)kMaxPeers), o_seq = o_flags + up(4 * (size_t)kMaxPeers);
-    s->arena_bytes = o_seq + 256;
+                 o_flags = o_pairs + up(16 * (size_t)kMaxPeers), o_seq = o_flags + up(5 * 4 * (size_t)kMaxPeers);
+    // Q8_K planes {qs, bsums, d} of the two vectors whose producers quantize before the join
+    const size_t o_aqs = o_seq + 256, o_abs = o_aqs + up(qd), o_ad = o_abs + up(qd / 8), o_fqs = o_ad + up(qd / 64),
+                 o_fbs = o_fqs + up((size_t)g.n_ff), o_fd = o_fbs + up((size_t)g.n_ff / 8);
+    s->arena_bytes = o_fd + up((size_t)g.n_ff / 64);
     ok = ok && dev_alloc(s, (void**)&s->arena, s->arena_bytes);
     if (ok) {
       ok = cudaMemsetAsync(s->arena, 0, s->arena_bytes, c->stream) == cudaSuccess;
@@ -667,6 +776,10 @@ uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_l
       s->pair_buf = reinterpret_cast<int*>(s->arena + o_pairs);
       s->flags_off = o_flags;
       s->seq_off = o_seq;
+      s->attn_planes = ActPlanesMut{reinterpret_cast<int8_t*>(s->arena + o_aqs), reinterpret_cast<float*>(s->arena + o_ad),
+                                    reinterpret_cast<int16_t*>(s->arena + o_abs)};
+      s->ffn_planes = ActPlanesMut{reinterpret_cast<int8_t*>(s->arena + o_fqs), reinterpret_cast<float*>(s->arena + o_fd),
+                                   reinterpret_cast<int16_t*>(s->arena + o_fbs)};
       s->peer_base[g.shard_rank] = s->arena;
     }
   }
@@ -995,6 +1108,15 @@ uint32_t emelb_llama_decode_profile(emelb_llama* s, int32_t token, int32_t posit
 uint32_t emelb_llama_set_prefill_batch(emelb_llama* s, int32_t max_tokens) {
   if (!s || max_tokens < 0) return EMELB_INVALID_REQUEST;
   s->prefill_batch = max_tokens == 1 ? 0 : max_tokens;   // a batch of one is the token-by-token walk
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_set_join_fusion(emelb_llama* s, int32_t on) {
+  if (!s || (on != 0 && on != 1)) return EMELB_INVALID_REQUEST;
+  if (s->fused_joins != (on == 1)) {
+    s->fused_joins = on == 1;
+    for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;   // captured steps hold the other joins
+  }
   return EMELB_OK;
 }
 

@@ -34,6 +34,7 @@ SIGNATURES = {
     "emelb_llama_launches_per_token": [_P, C.POINTER(C.c_int32)],
     "emelb_llama_set_step_mode": [_P, C.c_int32],
     "emelb_llama_set_prefill_batch": [_P, C.c_int32],
+    "emelb_llama_set_join_fusion": [_P, C.c_int32],
     "emelb_llama_decode_profile": [_P, C.c_int32, C.c_int32, _P, C.c_uint64],
     "emelb_llama_exchange_export": [_P, _P, C.c_uint64],
     "emelb_llama_exchange_attach": [_P, _P, C.c_uint64],
@@ -169,6 +170,10 @@ class Session:
     def set_prefill_batch(self, max_tokens: int) -> bool:
         """Prompt tokens per batch of prefill(): 0 walks the prompt token by token."""
         return self._ret(eb.lib().emelb_llama_set_prefill_batch(self._h, max_tokens))
+
+    def set_join_fusion(self, on: bool) -> bool:
+        """Sharded sessions with peers attached: joins inside the neighbouring kernels (default) or one join kernel each."""
+        return self._ret(eb.lib().emelb_llama_set_join_fusion(self._h, 1 if on else 0))
 
     def set_step_mode(self, mode: int) -> bool:
         """0: the chain of per-operation launches (default); 1: one persistent kernel per token where the session qualifies."""

@@ -141,6 +141,13 @@ EMELB_API uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* ha
  * sessions are destroyed — no arena is freed while a peer still maps it. */
 EMELB_API uint32_t emelb_llama_exchange_detach(emelb_llama* s);
 
+/* Row-sharded sessions with every peer attached: where a layer's products all take the streaming kernel, its four
+ * joins run inside the kernels either side of them -- the producing kernel (attention merge, output projection,
+ * SwiGLU, down projection) stores its rows into every rank's copy of the vector and raises a flag, the consuming
+ * product waits for the flags and quantizes the joined f32 vector in its prologue -- instead of one join kernel
+ * each.  on = 1 (default) / 0: always one join kernel per join.  Same result bit for bit either way. */
+EMELB_API uint32_t emelb_llama_set_join_fusion(emelb_llama* s, int32_t on);
+
 /* How a decode step is enqueued.  0 (default): the chain of per-operation
  * launches.  1: where the session qualifies (unsharded, Q4_K layer matrices with
  * K a multiple of 2048, head size 128, adjacent-pair RoPE, fast attention mode),

@@ -22,7 +22,7 @@ import torch.distributed as dist  # noqa: E402
 import emel_cpp_b200 as eb  # noqa: E402
 from emel_cpp_b200 import llama as el  # noqa: E402
 
-CFG = dict(n_layer=2, n_embd=2048, n_head=16, n_head_kv=4, head_dim=128, n_ff=4096, n_vocab=4096, n_ctx=64)
+CFG = dict(n_layer=3, n_embd=2048, n_head=16, n_head_kv=4, head_dim=128, n_ff=4096, n_vocab=4096, n_ctx=64)
 
 
 def build(be, alloc_be, cfg_kw, rank, world, buffers):
@@ -80,7 +80,8 @@ def main():
         norm(l, el.FFN_NORM)
         for role in (el.ATTN_Q, el.ATTN_K, el.ATTN_V, el.ATTN_OUT, el.FFN_GATE, el.FFN_UP):
             matrix(l, role, eb.Q4_K, 0.05)
-        matrix(l, el.FFN_DOWN, eb.Q8_0 if l % 2 else eb.Q6_K, 0.05)
+        # layers 0 and 1 qualify for joins inside their kernels (K-quant products), layer 2 (Q8_0) takes a join kernel each
+        matrix(l, el.FFN_DOWN, (eb.Q6_K, eb.Q4_K, eb.Q8_0)[l % 3], 0.05)
     buffers["order"] = order
     assert be_full.sync()
 
@@ -88,12 +89,14 @@ def main():
     results = {}
     # sharded sessions walk the prompt token by token; the unsharded one is held to the same walk here so that
     # the comparison is about sharding alone (the batched prompt path has its own tests)
-    for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world), ("shard-peer", be_shard, rank, world)):
+    for name, be, r, g in (("full", be_full, 0, 1), ("shard", be_shard, rank, world), ("shard-peer", be_shard, rank, world),
+                           ("shard-peer-unfused", be_shard, rank, world)):
         for mode in (2, 0):
             be.set_attention_mode(mode)
             sess = build(be, be_full, CFG, r, g, buffers)
             assert sess.set_prefill_batch(0)
-            if name == "shard-peer":       # joins by peer stores instead of NCCL all-gathers
+            if name.startswith("shard-peer"):       # joins by peer stores instead of NCCL all-gathers
+                assert sess.set_join_fusion(name == "shard-peer")
                 handles = [None] * world
                 dist.all_gather_object(handles, sess.exchange_export())
                 assert sess.exchange_attach(handles), sess.last_error
@@ -115,10 +118,16 @@ def main():
     lp, idp, hp = results[("shard-peer", 2)]
     assert np.array_equal(lf, lp) and idf == idp and hf == hp, (float(np.abs(lf - lp).max()), idf, idp)
     assert results[("shard-peer", 0)][1][0] == idf0_first(results)
+    # the joins inside the kernels and the join kernels move the same floats: identical logits and ids
+    for mode in (2, 0):
+        la, ia, ha = results[("shard-peer", mode)]
+        lb, ib, hb = results[("shard-peer-unfused", mode)]
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32)) and ia == ib and ha == hb, (mode, float(np.abs(la - lb).max()))
     lf0, idf0, _ = results[("full", 0)]
     ls0, ids0, _ = results[("shard", 0)]
     assert float(np.abs(lf0 - ls0).max()) <= 1e-3
     assert idf0[0] == ids0[0]
+    assert float(np.abs(lf0 - results[("shard-peer", 0)][0]).max()) <= 1e-3
 
     # batched prompt path: the sharded session processes the prompt in token batches too (row intervals of every
     # product joined by NCCL); per head and per row it runs the same kernels on the same numbers as the
