@@ -26,6 +26,7 @@ SOURCES = {
     "prefill_attention.cu": [],
     "gemm_tc.cu": [],
     "gemm_q8_mma.cu": [],
+    "gemm_q4k_mma.cu": [],
     "llama.cu": [],
     "comm.cu": [],
     "noalloc.cu": [],

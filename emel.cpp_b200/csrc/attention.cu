@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(128) flash_split_kernel(const FlashArgs a) {
   pdl_wait();
   __shared__ __align__(16) float s_p[NREP * LMAX];
   __shared__ float s_red[4 * NREP];
-  const int T = a.tokens_dev ? *a.tokens_dev : a.tokens;
+  const int T = a.tokens_dev ? a.tokens_dev[a.kv_heads_per_seq > 0 ? blockIdx.y / a.kv_heads_per_seq : 0] : a.tokens;
   fa::split_unit<D, NREP, LMAX, 8, false>(a, blockIdx.x, blockIdx.y, blockIdx.z, T, threadIdx.x, s_p, s_red, fa::CtaSync{});
 }
 
@@ -78,7 +78,14 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, Act
       return;
     }
   }
-  a.dst[(size_t)h0 * D + threadIdx.x] = o;
+  if (a.dst_seqs > 1) {
+    // several sequences: head h of sequence i is global head i * heads_per_seq + h; dst keeps the sequence index fastest
+    const int hps = a.heads / a.dst_seqs, hg = h0 + hl;
+    const int seq = hg / hps, hloc = hg - seq * hps;
+    a.dst[((size_t)hloc * D + d) * a.dst_seqs + seq] = o;
+  } else {
+    a.dst[(size_t)h0 * D + threadIdx.x] = o;
+  }
   if constexpr (FAMILY != 0) {
     s_out[threadIdx.x] = o;
     __syncthreads();

@@ -319,6 +319,110 @@ __global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, c
   }
 }
 
+// one decode step of several sequences: column j is sequence j at its own position
+__global__ void rope_store_seqs_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                       const int* __restrict__ positions, int B, int n_head, int n_head_kv, int head_dim,
+                                       int rot_dim, int neox, float* __restrict__ q_out, __half* kcache, __half* vcache,
+                                       int64_t seq_stride, int64_t cache_head_stride) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= B) return;
+  const int head = blockIdx.y, pos = positions[j], pairs = rot_dim / 2;
+  const float* ct = cos_t + (int64_t)pos * pairs;
+  const float* st = sin_t + (int64_t)pos * pairs;
+  const int x1_base = neox ? pairs : 1, stride = neox ? 1 : 2;
+  if (head < n_head) {
+    const float* h = q + (int64_t)head * head_dim * B + j;
+    float* o = q_out + ((int64_t)j * n_head + head) * head_dim;
+    for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
+      const int d0 = p * stride, d1 = p * stride + x1_base;
+      const float x0 = h[(int64_t)d0 * B], x1 = h[(int64_t)d1 * B], c = ct[p], s = st[p];
+      o[d0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+      o[d1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    }
+    for (int d = rot_dim + threadIdx.y; d < head_dim; d += blockDim.y) o[d] = h[(int64_t)d * B];
+  } else {
+    const int kh = head - n_head;
+    const float* h = k + (int64_t)kh * head_dim * B + j;
+    const float* vv = v + (int64_t)kh * head_dim * B + j;
+    __half* kd = kcache + (int64_t)j * seq_stride + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+    __half* vd = vcache + (int64_t)j * seq_stride + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+    for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
+      const int d0 = p * stride, d1 = p * stride + x1_base;
+      const float x0 = h[(int64_t)d0 * B], x1 = h[(int64_t)d1 * B], c = ct[p], s = st[p];
+      kd[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+      kd[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
+    }
+    for (int d = rot_dim + threadIdx.y; d < head_dim; d += blockDim.y) kd[d] = __float2half_rn(h[(int64_t)d * B]);
+    for (int d = threadIdx.y; d < head_dim; d += blockDim.y) vd[d] = __float2half_rn(vv[(int64_t)d * B]);
+  }
+}
+
+__global__ void batch_begin_kernel(int* state, int stride, int B) {
+  const int j = threadIdx.x;
+  if (j < B) state[2 * stride + j] = state[stride + j] + 1;
+  if (j == 0) state[3 * stride] = 0;
+}
+
+__global__ void batch_advance_kernel(int* state, int stride, int B, const int* __restrict__ idx, int* out) {
+  const int j = threadIdx.x;
+  const int step = state[3 * stride];
+  __syncthreads();
+  if (j < B) {
+    state[j] = idx[j];
+    state[stride + j] += 1;
+    state[2 * stride + j] += 1;
+    out[(int64_t)step * B + j] = idx[j];
+  }
+  if (j == 0) state[3 * stride] = step + 1;
+}
+
+// argmax per column of x {rows, B} (column index fastest): CTA b scans a row range for every column, thread t
+// column t % B; then one CTA per launch folds the candidates.  Highest value, lowest row on ties; a NaN never
+// replaces a candidate (the reference's `>` comparison)
+__device__ __forceinline__ bool argmax_better(float v, int r, float bv, int br) { return br < 0 || v > bv || (v == bv && r < br); }
+
+__global__ void __launch_bounds__(256) argmax_columns_part_kernel(const float* __restrict__ x, int rows, int B, float* part_val, int* part_idx) {
+  __shared__ float s_v[256];
+  __shared__ int s_i[256];
+  const int lanes = 256 / B;            // row lanes per column
+  const int col = threadIdx.x % B, rl = threadIdx.x / B;
+  const int per = (rows + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * per, r1 = min(rows, r0 + per);
+  float bv = 0.0f;
+  int bi = -1;
+  if (rl < lanes)
+    for (int r = r0 + rl; r < r1; r += lanes) {
+      const float v = x[(int64_t)r * B + col];
+      if (argmax_better(v, r, bv, bi)) { bv = v; bi = r; }
+    }
+  s_v[threadIdx.x] = bv;
+  s_i[threadIdx.x] = bi;
+  __syncthreads();
+  if (threadIdx.x < B) {
+    for (int l = 1; l < lanes; ++l) {
+      const float v = s_v[l * B + col];
+      const int r = s_i[l * B + col];
+      if (r >= 0 && argmax_better(v, r, bv, bi)) { bv = v; bi = r; }
+    }
+    part_val[blockIdx.x * B + col] = bv;
+    part_idx[blockIdx.x * B + col] = bi;
+  }
+}
+
+__global__ void argmax_columns_finish_kernel(const float* part_val, const int* part_idx, int parts, int B, int* out_idx) {
+  const int col = threadIdx.x;
+  if (col >= B) return;
+  float bv = 0.0f;
+  int bi = -1;
+  for (int p = 0; p < parts; ++p) {
+    const float v = part_val[p * B + col];
+    const int r = part_idx[p * B + col];
+    if (r >= 0 && argmax_better(v, r, bv, bi)) { bv = v; bi = r; }
+  }
+  out_idx[col] = bi < 0 ? 0 : bi;
+}
+
 __global__ void add_inplace_kernel(float* __restrict__ acc, const float* __restrict__ y, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) acc[i] = __fadd_rn(acc[i], y[i]);
@@ -497,6 +601,36 @@ cudaError_t launch_rope_store_batch(float* q, const float* k, const float* v, co
                                     __half* vcache, int64_t cache_head_stride, cudaStream_t st) {
   rope_store_batch_kernel<<<dim3((B + 31) / 32, n_head + n_head_kv), dim3(32, 8), 0, st>>>(
       q, k, v, cos_t, sin_t, pos0, B, n_head, n_head_kv, head_dim, rot_dim, neox, kcache, vcache, cache_head_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope_store_seqs(const float* q, const float* k, const float* v, const float* cos_t, const float* sin_t,
+                                   const int* positions, int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
+                                   float* q_out, __half* kcache, __half* vcache, int64_t seq_stride, int64_t cache_head_stride,
+                                   cudaStream_t st) {
+  rope_store_seqs_kernel<<<dim3((B + 31) / 32, n_head + n_head_kv), dim3(32, 8), 0, st>>>(
+      q, k, v, cos_t, sin_t, positions, B, n_head, n_head_kv, head_dim, rot_dim, neox, q_out, kcache, vcache, seq_stride,
+      cache_head_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_batch_begin(int* state, int stride, int B, cudaStream_t st) {
+  if (B < 1 || B > 256) return cudaErrorInvalidValue;
+  batch_begin_kernel<<<1, 256, 0, st>>>(state, stride, B);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_batch_advance(int* state, int stride, int B, const int* idx, int* out, cudaStream_t st) {
+  if (B < 1 || B > 256) return cudaErrorInvalidValue;
+  batch_advance_kernel<<<1, 256, 0, st>>>(state, stride, B, idx, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_columns(const float* x, int rows, int B, float* part_val, int* part_idx, int* out_idx, cudaStream_t st) {
+  if (B < 1 || B > 256 || rows < 1) return cudaErrorInvalidValue;
+  const int parts = rows < kArgmaxColumnParts ? rows : kArgmaxColumnParts;
+  argmax_columns_part_kernel<<<parts, 256, 0, st>>>(x, rows, B, part_val, part_idx);
+  argmax_columns_finish_kernel<<<1, 256, 0, st>>>(part_val, part_idx, parts, B, out_idx);
   return cudaGetLastError();
 }
 

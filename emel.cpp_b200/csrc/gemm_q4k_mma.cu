@@ -1,0 +1,247 @@
+// 9 to 31 columns of Q4_K weights x Q8_K activations (a decode step of several sequences): too many columns for
+// the CUDA-core mat-vec kernels, whose integer dot products per weight byte grow with the column count, and too
+// few to fill the 128-token tile of the tcgen05 kernel.  The integer part runs on the legacy tensor path,
+// mma.sync.m16n8k32 (s8 x s8 -> s32): one instruction = one 32-weight sub-block of 16 rows against 8 columns.
+//
+// Per 256-weight super-block and (row, column) the value is the reference's
+//   fma(d*dx, isum, -(dmin*dx)*msum),  isum = sum_j sc_j * dot_j(q, x),  msum = sum_j m_j * bsum_j
+// (src/emel/kernel/x86_64/actions.hpp:859-866) added to the row sum in ascending block order: dot_j comes out of
+// the MMA as an exact int32, the 6-bit scale multiplies it on the CUDA cores, the mins meet the activations'
+// 32-element sums in four dp2a, and the float chain is the mat-vec kernels' — same bits.
+//
+// CTA = 64 weight rows (4 warps x 16) x NT*8 columns; K is walked two super-blocks at a time through a three-stage
+// cp.async ring that holds the weight rows as they lie in memory (2 x 144 bytes per row and stage), the
+// activation bytes, their 16-element sums and scales.  Row strides are padded by 16 bytes so that the 8 rows x 4
+// lanes of a fragment load fall on 32 different banks.
+// Fragments (PTX ISA, m16n8k32, lane = 4g + t):
+//   A: a0 (row g, k 4t..4t+3)  a1 (row g+8, same k)  a2 (row g, k 16+4t..)  a3 (row g+8, k 16+4t..)
+//   B: b0 (k 4t..4t+3, col g)  b1 (k 16+4t.., col g)
+//   C: c0,c1 (row g, cols 2t, 2t+1)  c2,c3 (row g+8, same cols)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace emelb {
+
+namespace {
+
+constexpr int kWarpsM = 4, kTM = 16 * kWarpsM, kSbPerStage = 2, kStageK = kSbPerStage * QK_K, kStagesM = 3;
+constexpr int kWRow = kSbPerStage * Q4_K_BYTES + 16;   // 304 bytes = 76 words: 76 g + t covers 32 banks
+constexpr int kXRow = kStageK + 16;                    // 528 bytes = 132 words: 4 g + t
+constexpr int kBsRow = kStageK / 16 * 2 + 16;          // 32 int16 sums of 16 elements, padded
+constexpr int kThreadsM = 32 * kWarpsM;
+
+template <int NT>
+struct Q4Stage {
+  uint8_t w[kTM][kWRow];
+  int8_t x[NT * 8][kXRow];
+  uint8_t bs[NT * 8][kBsRow];
+  float dx[NT * 8][kSbPerStage];
+};
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ int dp2a_lo_su(uint32_t pair, uint32_t bytes, int c) {
+  int d;
+  asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(pair), "r"(bytes), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp2a_hi_su(uint32_t pair, uint32_t bytes, int c) {
+  int d;
+  asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(pair), "r"(bytes), "r"(c));
+  return d;
+}
+
+__device__ __forceinline__ void cp_async8(void* smem, const void* gmem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+
+// the 6-bit scales and mins of a super-block as four words of four bytes: scales 0-3, 4-7, mins 0-3, 4-7
+// (get_scale_min_k4, src/emel/kernel/detail.hpp:1066-1076)
+struct ScaleWords { uint32_t sc_lo, sc_hi, mn_lo, mn_hi; };
+__device__ __forceinline__ ScaleWords unpack_scales(const uint4& h) {
+  ScaleWords s;
+  s.sc_lo = h.y & 0x3f3f3f3fu;
+  s.mn_lo = h.z & 0x3f3f3f3fu;
+  s.sc_hi = (h.w & 0x0f0f0f0fu) | (((h.y >> 6) & 0x03030303u) << 4);
+  s.mn_hi = ((h.w >> 4) & 0x0f0f0f0fu) | (((h.z >> 6) & 0x03030303u) << 4);
+  return s;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreadsM, 2) gemm_q4k_mma_kernel(const GemvArgs p, int ncols) {
+  using Stage = Q4Stage<NT>;
+  extern __shared__ __align__(16) unsigned char smem_q4m[];
+  Stage* stages = reinterpret_cast<Stage*>(smem_q4m);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * kTM;
+  const int nstages = p.K / kStageK;
+
+  // rows and columns past the edge are read from the last valid one (their results are never stored)
+  auto issue = [&](int ks, Stage& st) {
+    constexpr int kWPieces = kSbPerStage * Q4_K_BYTES / 16;   // 18
+    for (int idx = tid; idx < kTM * kWPieces; idx += kThreadsM) {
+      const int r = idx / kWPieces, piece = idx - r * kWPieces;
+      const int row = min(row0 + r, p.M - 1);
+      cp_async16(&st.w[r][16 * piece], p.W + (int64_t)row * p.row_bytes + (int64_t)ks * (kSbPerStage * Q4_K_BYTES) + 16 * piece);
+    }
+    constexpr int kXPieces = kStageK / 16;                    // 32
+    for (int idx = tid; idx < NT * 8 * kXPieces; idx += kThreadsM) {
+      const int c = idx / kXPieces, piece = idx - c * kXPieces;
+      const int col = p.col0 + min(c, ncols - 1);
+      cp_async16(&st.x[c][16 * piece], p.act.qs + (int64_t)col * p.act.col_stride_qs + (int64_t)ks * kStageK + 16 * piece);
+    }
+    constexpr int kBPieces = kStageK / 16 * 2 / 16;           // 4
+    for (int idx = tid; idx < NT * 8 * kBPieces; idx += kThreadsM) {
+      const int c = idx / kBPieces, piece = idx - c * kBPieces;
+      const int col = p.col0 + min(c, ncols - 1);
+      cp_async16(&st.bs[c][16 * piece], reinterpret_cast<const uint8_t*>(p.act.bsums + (int64_t)col * p.act.col_stride_bs + (int64_t)ks * (kStageK / 16)) + 16 * piece);
+    }
+    for (int c = tid; c < NT * 8; c += kThreadsM) {
+      const int col = p.col0 + min(c, ncols - 1);
+      cp_async8(&st.dx[c][0], p.act.d + (int64_t)col * p.act.col_stride_d + (int64_t)ks * kSbPerStage);
+    }
+    cp_async_commit();
+  };
+
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+
+#pragma unroll
+  for (int s = 0; s < kStagesM - 1; ++s) {
+    if (s < nstages) issue(s, stages[s]);
+    else cp_async_commit();
+  }
+  const int ra = warp * 16 + g, rb = ra + 8;
+  for (int ks = 0; ks < nstages; ++ks) {
+    // the ring slot refilled here was read two turns ago; every warp has passed the barrier that ended that turn
+    if (ks + kStagesM - 1 < nstages) issue(ks + kStagesM - 1, stages[(ks + kStagesM - 1) % kStagesM]);
+    else cp_async_commit();
+    cp_async_wait<kStagesM - 1>();
+    __syncthreads();
+    const Stage& st = stages[ks % kStagesM];
+#pragma unroll
+    for (int sb = 0; sb < kSbPerStage; ++sb) {
+      const uint8_t* ba = &st.w[ra][sb * Q4_K_BYTES];
+      const uint8_t* bb = &st.w[rb][sb * Q4_K_BYTES];
+      const uint4 ha = *reinterpret_cast<const uint4*>(ba), hb = *reinterpret_cast<const uint4*>(bb);
+      const ScaleWords sa = unpack_scales(ha), sw = unpack_scales(hb);
+      int isum[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) isum[nt][i] = 0;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        // bytes 32r .. 32r+31 of the quants: low nibbles = sub-block 2r, high nibbles = sub-block 2r+1
+        const uint32_t wa0 = *reinterpret_cast<const uint32_t*>(ba + 16 + 32 * r + 4 * t);
+        const uint32_t wa1 = *reinterpret_cast<const uint32_t*>(ba + 32 + 32 * r + 4 * t);
+        const uint32_t wb0 = *reinterpret_cast<const uint32_t*>(bb + 16 + 32 * r + 4 * t);
+        const uint32_t wb1 = *reinterpret_cast<const uint32_t*>(bb + 32 + 32 * r + 4 * t);
+        const uint32_t scw_a = r < 2 ? sa.sc_lo : sa.sc_hi, scw_b = r < 2 ? sw.sc_lo : sw.sc_hi;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int j = 2 * r + half, sh = 16 * (r & 1) + 8 * half;
+          const int sca = (int)((scw_a >> sh) & 0xffu), scb = (int)((scw_b >> sh) & 0xffu);
+          const uint32_t af[4] = {(wa0 >> (4 * half)) & 0x0f0f0f0fu, (wb0 >> (4 * half)) & 0x0f0f0f0fu,
+                                  (wa1 >> (4 * half)) & 0x0f0f0f0fu, (wb1 >> (4 * half)) & 0x0f0f0f0fu};
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const int8_t* xr = &st.x[nt * 8 + g][sb * QK_K + j * 32 + 4 * t];
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xr), b1 = *reinterpret_cast<const uint32_t*>(xr + 16);
+            int c[4] = {0, 0, 0, 0};
+            mma_s8(c, af, b0, b1);
+            isum[nt][0] += sca * c[0];
+            isum[nt][1] += sca * c[1];
+            isum[nt][2] += scb * c[2];
+            isum[nt][3] += scb * c[3];
+          }
+        }
+      }
+      const float da = h2f((uint16_t)(ha.x & 0xffffu)), dmin_a = h2f((uint16_t)(ha.x >> 16));
+      const float db = h2f((uint16_t)(hb.x & 0xffffu)), dmin_b = h2f((uint16_t)(hb.x >> 16));
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int col = nt * 8 + 2 * t + i;
+          // the column's sixteen 16-element sums of this super-block -> eight 32-element sums, two per word
+          const int4 s0 = *reinterpret_cast<const int4*>(&st.bs[col][sb * 32]);
+          const int4 s1 = *reinterpret_cast<const int4*>(&st.bs[col][sb * 32 + 16]);
+          const int w[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          uint32_t pw[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int p0 = (int)(short)(w[2 * k] & 0xffff) + (w[2 * k] >> 16);
+            const int p1 = (int)(short)(w[2 * k + 1] & 0xffff) + (w[2 * k + 1] >> 16);
+            pw[k] = ((uint32_t)p0 & 0xffffu) | ((uint32_t)p1 << 16);
+          }
+          int ma = dp2a_lo_su(pw[0], sa.mn_lo, 0);
+          ma = dp2a_hi_su(pw[1], sa.mn_lo, ma);
+          ma = dp2a_lo_su(pw[2], sa.mn_hi, ma);
+          ma = dp2a_hi_su(pw[3], sa.mn_hi, ma);
+          int mb = dp2a_lo_su(pw[0], sw.mn_lo, 0);
+          mb = dp2a_hi_su(pw[1], sw.mn_lo, mb);
+          mb = dp2a_lo_su(pw[2], sw.mn_hi, mb);
+          mb = dp2a_hi_su(pw[3], sw.mn_hi, mb);
+          const float dx = st.dx[col][sb];
+          const float va = __fmaf_rn(__fmul_rn(dx, da), (float)isum[nt][i], -__fmul_rn(__fmul_rn(dx, dmin_a), (float)ma));
+          const float vb = __fmaf_rn(__fmul_rn(dx, db), (float)isum[nt][2 + i], -__fmul_rn(__fmul_rn(dx, dmin_b), (float)mb));
+          acc[nt][i] = __fadd_rn(acc[nt][i], va);
+          acc[nt][2 + i] = __fadd_rn(acc[nt][2 + i], vb);
+        }
+      }
+    }
+    __syncthreads();  // this slot is free for the copy issued at the top of the next turn but one
+  }
+
+  const int ya = row0 + ra, yb = row0 + rb;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = nt * 8 + 2 * t + i;
+      if (c >= ncols) continue;
+      if (ya < p.M) p.y[(int64_t)ya * p.ldy + p.col0 + c] = acc[nt][i];
+      if (yb < p.M) p.y[(int64_t)yb * p.ldy + p.col0 + c] = acc[nt][2 + i];
+    }
+  }
+}
+
+template <int NT>
+cudaError_t launch_nt(const GemvArgs& a, int ncols, cudaStream_t st) {
+  const int smem = (int)(kStagesM * sizeof(Q4Stage<NT>));
+  static thread_local unsigned configured = 0;  // one bit per device (one context, one lane per host thread)
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(configured & (1u << (dev & 31)))) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm_q4k_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured |= 1u << (dev & 31);
+  }
+  gemm_q4k_mma_kernel<NT><<<(a.M + kTM - 1) / kTM, kThreadsM, smem, st>>>(a, ncols);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_q4k_mma_supported(int type, const GemvArgs& a, int ncols) {
+  if (type != T_Q4_K || ncols < kGemmMmaMinCols || ncols >= kGemmTcMinCols) return false;
+  if (a.K % kStageK != 0 || a.residual || a.W2 || a.W3 || a.pro_x || a.rope_cos || !a.act.bsums) return false;
+  return reinterpret_cast<uintptr_t>(a.W) % 16 == 0 && a.row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.qs) % 16 == 0 &&
+         a.act.col_stride_qs % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.bsums) % 16 == 0 && a.act.col_stride_bs % 8 == 0 &&
+         reinterpret_cast<uintptr_t>(a.act.d) % 8 == 0 && a.act.col_stride_d % 2 == 0;
+}
+
+cudaError_t launch_gemm_q4k_mma(const GemvArgs& a, int ncols, cudaStream_t st) {
+  return ncols <= 16 ? launch_nt<2>(a, ncols, st) : launch_nt<4>(a, ncols, st);
+}
+
+}  // namespace emelb

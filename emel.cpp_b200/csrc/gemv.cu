@@ -220,6 +220,11 @@ cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int
     ++*launches;
     return launch_gemm_q8_mma(type, a, ncols, sm_count, st);
   }
+  // a handful of columns of Q4_K (several sequences decoding together): mma.sync per sub-block (gemm_q4k_mma.cu)
+  if (!argmax && gemm_q4k_mma_supported(type, a, ncols)) {
+    ++*launches;
+    return launch_gemm_q4k_mma(a, ncols, st);
+  }
   // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
   if (!argmax && gemv_takes_tensor_core(type, a, ncols)) {
     *launches += a.tc_ws_reuse ? 1 : 2;

@@ -122,6 +122,10 @@ bool gemv_takes_tensor_core(int type, const GemvArgs& a, int ncols);
 bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols);
 cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, int sm_count, cudaStream_t st);
 
+// gemm_q4k_mma.cu: 9 to 31 columns of Q4_K weights (mma.sync int8, one sub-block per instruction)
+bool gemm_q4k_mma_supported(int type, const GemvArgs& a, int ncols);
+cudaError_t launch_gemm_q4k_mma(const GemvArgs& a, int ncols, cudaStream_t st);
+
 // gemv2.cu
 cudaError_t launch_gemv_stream2(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
                                 int* launches, int* grid_out);
@@ -170,6 +174,20 @@ cudaError_t launch_rope_store_batch(float* q, const float* k, const float* v, co
                                     int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,
                                     __half* vcache, int64_t cache_head_stride, cudaStream_t st);
 cudaError_t launch_add_inplace(float* acc, const float* y, int64_t n, cudaStream_t st);
+// ---- one decode step of B sequences together (activations {features, B}, sequence index fastest)
+// state: three rows of `stride` ints {token, position, kv token count} per sequence, then {step}
+cudaError_t launch_batch_begin(int* state, int stride, int B, cudaStream_t st);
+// rotates q column j at positions[j] into q_out [B][n_head * head_dim] and writes k, v column j as f16 rows of
+// sequence j's cache (cache planes of consecutive sequences lie seq_stride halves apart)
+cudaError_t launch_rope_store_seqs(const float* q, const float* k, const float* v, const float* cos_t, const float* sin_t,
+                                   const int* positions, int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
+                                   float* q_out, __half* kcache, __half* vcache, int64_t seq_stride, int64_t cache_head_stride,
+                                   cudaStream_t st);
+// per column of x {rows, B}: the highest value and, on ties, the lowest row (src/emel/kernel/detail.hpp:3720-3723)
+constexpr int kArgmaxColumnParts = 256;
+cudaError_t launch_argmax_columns(const float* x, int rows, int B, float* part_val, int* part_idx, int* out_idx, cudaStream_t st);
+// token <- idx, position and token count + 1, idx appended to out[step * B + j]
+cudaError_t launch_batch_advance(int* state, int stride, int B, const int* idx, int* out, cudaStream_t st);
 // causal attention of a batch of B query tokens at positions pos0 .. pos0 + B - 1 over the f16 KV cache
 // (q, dst feature-major {heads * head_dim, B}; f32 online softmax); false from the predicate: not taken
 struct PrefillAttnArgs {
@@ -200,6 +218,7 @@ cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out
 // gemm_tc.cu — Q4_K x Q8_K for many columns on the tensor cores (tcgen05, TMEM accumulators);
 // same numbers as the mat-vec kernels.  a.col0/a.y/a.ldy address the output as for launch_gemv.
 constexpr int kGemmTcMinCols = 32;
+constexpr int kGemmMmaMinCols = 9;   // fewer columns: the CUDA-core mat-vec kernels
 bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act);
 // true when launch_gemv would run the kernel that honours GemvArgs::pro_x for this matrix
 bool gemv_prologue_supported(int type, const void* w, int64_t row_bytes, int K);
@@ -278,6 +297,10 @@ struct FlashArgs {
   int splits;            // KV splits per kv head
   float* part_acc;       // [H][splits][d]
   float* part_ml;        // [H][splits][2]  (running max, running sum)
+  // several sequences at once (one query token each): sequence i owns kv heads [i * kv_heads_per_seq, ...) of the
+  // cache planes and the matching query heads, and tokens_dev[i] is its token count; 0: one sequence
+  int kv_heads_per_seq;
+  int dst_seqs;          // > 1: dst is {heads_per_seq * d, dst_seqs} with the sequence index fastest (a product's activation layout)
   JoinOut join_out;      // split-KV merge step (world > 1): this rank's heads, quantized to Q8_K, go into every rank's planes
 };
 // out_family 1 / 2: the merge step also writes the result quantized (Q8_K / Q8_0 planes, one column) for the

@@ -75,6 +75,17 @@ struct emelb_llama {
   float *b_gate = nullptr, *b_up = nullptr, *b_ffn = nullptr, *b_y = nullptr;
   double* b_partial = nullptr;
   int fa_splits = 1;
+  // sequences decoded together (emelb_llama_set_sequences): the cache planes are [layer][sequence][kv head][capacity][d];
+  // the one-sequence entry points work on sequence cur_seq
+  int n_seq = 1, cur_seq = 0;
+  int* bstate = nullptr;      // rows of kMaxSeqs ints: token, position, kv token count; then {step}
+  int* b_idx = nullptr;       // next token per sequence
+  int* b_out = nullptr;       // generated ids, [step][sequence]
+  float *b_qs = nullptr, *b_logits = nullptr, *b_part_acc = nullptr, *b_part_ml = nullptr, *b_amax_val = nullptr;
+  int* b_amax_idx = nullptr;
+  int seq_cap = 0;            // sequences the batch-step buffers were sized for
+  cudaGraphExec_t batch_graph = nullptr;
+  int batch_graph_B = 0, batch_graph_mode = -1, batch_launches = 0;
   int G = 1, rank = 0;        // row sharding
   int* pair_buf = nullptr;    // G x 16-byte records {value bits, global row, -, -}: argmax candidates
   // sharded sessions keep the vectors that are joined across ranks in one allocation (the exchange arena) so
@@ -106,6 +117,13 @@ struct emelb_llama {
 };
 
 namespace {
+
+constexpr int kMaxSeqs = 64;
+
+// offset (halves) of sequence seq's planes of layer l inside the K or V cache
+int64_t cache_off(const emelb_llama* s, int l, int seq) {
+  return ((int64_t)l * s->n_seq + seq) * (s->cfg.n_head_kv / s->G) * s->capacity * s->cfg.head_dim;
+}
 
 bool dev_alloc(emelb_llama* s, void** p, size_t bytes) {
   if (cudaMalloc(p, (bytes + 255) & ~size_t(255)) != cudaSuccess) {
@@ -385,7 +403,7 @@ struct Enqueue {
     a.pro_eps = s->cfg.rms_eps;
     a.join_in = join_in(in_join);
     if (rope) {
-      const int64_t layer_off = (int64_t)rope_layer * (cfg.n_head_kv / s->G) * s->capacity * cfg.head_dim;
+      const int64_t layer_off = cache_off(s, rope_layer, s->cur_seq);
       a.rope_cos = s->rope_cos;
       a.rope_sin = s->rope_sin;
       a.rope_pos = s->state + 1;
@@ -411,7 +429,7 @@ struct Enqueue {
   // context quantized for the output projection (family of wo's type)
   FlashArgs flash_args(int layer) const {
     const emelb_llama_config& c = s->cfg;
-    const int64_t layer_off = (int64_t)layer * (c.n_head_kv / s->G) * s->capacity * c.head_dim;
+    const int64_t layer_off = cache_off(s, layer, s->cur_seq);
     FlashArgs a{};
     a.q = s->q;
     a.k = s->kcache + layer_off;
@@ -531,7 +549,7 @@ struct Enqueue {
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
       const Layer& w = s->layers[l];
-      const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
+      const int64_t layer_off = cache_off(s, l, s->cur_seq);
       check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       ++launches;
       batch_matmul(w.wq, s->b_norm, s->b_q, B);
@@ -560,6 +578,74 @@ struct Enqueue {
     }
   }
 
+  // One decode step of sequences 0 .. B-1 together: column j of every activation tensor {features, B} is sequence
+  // j's token (ids, positions and token counts in s->bstate).  Per column the arithmetic is token_step's: the
+  // same products, the same rotation, the split-KV attention with the session's split count, so a sequence
+  // decodes to the tokens it decodes to alone.  Ends with the per-column argmax (and the logits left in
+  // s->b_logits, {n_vocab, B}).
+  void batch_step(int B) {
+    const emelb_llama_config& c = s->cfg;
+    const int G = s->G, r = s->rank;
+    const int heads_l = c.n_head / G, kv_l = c.n_head_kv / G;
+    const size_t q_l = (size_t)heads_l * c.head_dim, embd_l = (size_t)c.n_embd / G, ff_l = (size_t)c.n_ff / G, b = (size_t)B;
+    const size_t vocab_l = (size_t)c.n_vocab / G;
+    const int rot = c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim;
+    float* attn_mine = s->b_attn + r * q_l * b;
+    float* y_mine = s->b_y + r * embd_l * b;
+    float* ffn_mine = s->b_ffn + r * ff_l * b;
+    const int* tok = s->bstate;
+    const int* pos = s->bstate + kMaxSeqs;
+    const int* kvn = s->bstate + 2 * kMaxSeqs;
+    s->planes_src = nullptr;
+    check(launch_embed_rows(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, tok, B, s->b_hidden, c.n_embd, st));
+    ++launches;
+    for (int l = 0; l < c.n_layer; ++l) {
+      const Layer& w = s->layers[l];
+      const int64_t layer_off = cache_off(s, l, 0);
+      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
+      ++launches;
+      batch_matmul(w.wq, s->b_norm, s->b_q, B);
+      batch_matmul(w.wk, s->b_norm, s->b_k, B, true);
+      batch_matmul(w.wv, s->b_norm, s->b_v, B, true);
+      check(launch_rope_store_seqs(s->b_q, s->b_k, s->b_v, s->rope_cos, s->rope_sin, pos, B, heads_l, kv_l, c.head_dim, rot,
+                                   c.rope_neox, s->b_qs, s->kcache + layer_off, s->vcache + layer_off,
+                                   (int64_t)kv_l * s->capacity * c.head_dim, s->capacity * c.head_dim, st));
+      ++launches;
+      // every (sequence, head) is one head of a wider attention problem over the sequences' cache planes
+      FlashArgs a = flash_args(l);
+      a.q = s->b_qs;
+      a.k = s->kcache + layer_off;
+      a.v = s->vcache + layer_off;
+      a.dst = attn_mine;
+      a.heads = heads_l * B;
+      a.kv_heads = kv_l * B;
+      a.tokens_dev = kvn;
+      a.kv_heads_per_seq = kv_l;
+      a.dst_seqs = B;
+      a.part_acc = s->b_part_acc;
+      a.part_ml = s->b_part_ml;
+      check(launch_flash_decode(a, s->c->sm_count, st, &launches, 0, planes()));
+      batch_gather(s->b_attn, q_l, B);
+      batch_matmul(w.wo, s->b_attn, y_mine, B);
+      batch_gather(s->b_y, embd_l, B);
+      check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
+      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.ffn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
+      batch_matmul(w.gate, s->b_norm, s->b_gate, B);
+      batch_matmul(w.up, s->b_norm, s->b_up, B, true);
+      check(launch_swiglu(s->b_gate, s->b_up, (int)(ff_l * b), ffn_mine, 0, planes(), st));
+      batch_gather(s->b_ffn, ff_l, B);
+      batch_matmul(w.down, s->b_ffn, y_mine, B);
+      batch_gather(s->b_y, embd_l, B);
+      check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
+      launches += 4;
+    }
+    check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(s->out_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
+    batch_matmul(s->output, s->b_norm, s->b_logits + r * vocab_l * b, B);
+    batch_gather(s->b_logits, vocab_l, B);
+    check(launch_argmax_columns(s->b_logits, c.n_vocab, B, s->b_amax_val, s->b_amax_idx, s->b_idx, st));
+    launches += 3;
+  }
+
   void token_step(Mode mode) {
     const emelb_llama_config& c = s->cfg;
     // which launches of the step carry the programmatic-serialization attribute (bit mask: 1 mat-vecs,
@@ -577,7 +663,7 @@ struct Enqueue {
     s->planes_src = nullptr;
     check(launch_embed_row(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->state, s->hidden, c.n_embd, st));
     ++launches;
-    const bool one_kernel = s->token_usable && s->step_mode == 1 && s->c->attention_mode == 0 && G == 1;
+    const bool one_kernel = s->token_usable && s->step_mode == 1 && s->c->attention_mode == 0 && G == 1 && s->n_seq == 1;
     if (one_kernel) {
       // every layer inside one persistent kernel (token_kernel.cu)
       check(launch_llama_token(token_args(s), s->c->sm_count, &s->token_launch, st));
@@ -593,7 +679,7 @@ struct Enqueue {
         roped = normed_matvec_group(s->hidden, w.attn_norm, ws, ys, 3, false, l, hidden_joined_in_next ? J_HIDDEN_B : J_NONE);
       }
       if (!roped) {
-        const int64_t layer_off = (int64_t)l * kv_l * s->capacity * c.head_dim;
+        const int64_t layer_off = cache_off(s, l, s->cur_seq);
         g_pdl_launch = (pm & 2) != 0;
         check(launch_rope_store(s->q, s->k, s->v, s->rope_cos, s->rope_sin, s->state + 1, heads_l, kv_l, c.head_dim,
                                 c.rope_dim < c.head_dim ? c.rope_dim : c.head_dim, c.rope_neox, s->kcache + layer_off,
@@ -800,7 +886,7 @@ uint32_t emelb_llama_create(emelb_ctx* c, const emelb_llama_config* cfg, emelb_l
   ok = ok && dev_alloc(s, (void**)&s->state, 4 * sizeof(int));
   if (G == 1) ok = ok && dev_alloc(s, (void**)&s->pair_buf, 4 * sizeof(int));
   ok = ok && dev_alloc(s, (void**)&s->tokens_dev, sizeof(int) * (size_t)(g.n_ctx + 8));
-  ok = ok && cudaMallocHost((void**)&s->host_pinned, sizeof(int) * (size_t)(g.n_ctx + 4)) == cudaSuccess;
+  ok = ok && cudaMallocHost((void**)&s->host_pinned, sizeof(int) * (size_t)(g.n_ctx + 4 + 2 * kMaxSeqs)) == cudaSuccess;
   if (ok) {
     ok = cudaMemsetAsync(s->kcache, 0, 2 * cache_halves, c->stream) == cudaSuccess &&
          cudaMemsetAsync(s->vcache, 0, 2 * cache_halves, c->stream) == cudaSuccess &&
@@ -845,6 +931,7 @@ uint32_t emelb_llama_destroy(emelb_llama* s) {
   cudaStreamSynchronize(s->c->stream);
   for (auto& g : s->graphs)
     if (g) cudaGraphExecDestroy(g);
+  if (s->batch_graph) cudaGraphExecDestroy(s->batch_graph);
   for (int g = 0; g < kMaxPeers; ++g)
     if (s->peer_base[g] && g != s->rank) cudaIpcCloseMemHandle(s->peer_base[g]);
   for (void* p : s->owned) cudaFree(p);
@@ -1018,6 +1105,209 @@ uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n, i
   }
   ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
   return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+namespace {
+
+// buffers of the batch step, sized for the session's sequence count
+bool reserve_sequences(emelb_llama* s) {
+  if (s->seq_cap >= s->n_seq) return true;
+  const emelb_llama_config& c = s->cfg;
+  const size_t b = (size_t)s->n_seq, q_dim = (size_t)c.n_head * c.head_dim;
+  bool ok = true;
+  if (!s->bstate) {
+    ok = dev_alloc(s, (void**)&s->bstate, sizeof(int) * (3 * kMaxSeqs + 4)) && dev_alloc(s, (void**)&s->b_idx, sizeof(int) * kMaxSeqs);
+    ok = ok && dev_alloc(s, (void**)&s->b_amax_val, 4 * (size_t)kArgmaxColumnParts * kMaxSeqs) &&
+         dev_alloc(s, (void**)&s->b_amax_idx, 4 * (size_t)kArgmaxColumnParts * kMaxSeqs);
+  }
+  ok = ok && dev_alloc(s, (void**)&s->b_qs, 4 * b * q_dim) && dev_alloc(s, (void**)&s->b_logits, 4 * b * c.n_vocab);
+  ok = ok && dev_alloc(s, (void**)&s->b_part_acc, 4 * b * (q_dim / s->G) * s->fa_splits) &&
+       dev_alloc(s, (void**)&s->b_part_ml, 4 * b * (c.n_head / s->G) * s->fa_splits * 2);
+  ok = ok && dev_alloc(s, (void**)&s->b_out, sizeof(int) * b * (size_t)(c.n_ctx + 8));
+  if (ok) s->seq_cap = s->n_seq;
+  return ok;
+}
+
+// columns of the batch buffers when the batch step is what allocates them: room for the prompt path's batches too
+int batch_buffer_columns(const emelb_llama* s) {
+  int cols = s->prefill_batch < s->cfg.n_ctx ? s->prefill_batch : s->cfg.n_ctx;
+  if (cols < s->n_seq) cols = s->n_seq;
+  return cols < 2 ? 2 : cols;
+}
+
+void drop_graphs(emelb_llama* s) {
+  for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;
+  s->batch_graph_mode = -1;
+}
+
+bool free_owned(emelb_llama* s, void* p) {
+  for (size_t i = 0; i < s->owned.size(); ++i)
+    if (s->owned[i] == p) {
+      s->owned.erase(s->owned.begin() + (long)i);
+      return cudaFree(p) == cudaSuccess;
+    }
+  return false;
+}
+
+// the batch step needs the batch attention path's preconditions: split-KV attention, room for B columns of the
+// widest activation in the context's planes, the communicator in a sharded session
+bool batch_step_ok(emelb_llama* s, int B) {
+  const emelb_llama_config& c = s->cfg;
+  if (s->c->attention_mode != 0 || B < 1 || B > s->n_seq) return false;
+  if (s->G > 1 && (!s->c->comm || s->c->comm_world != s->G)) return false;
+  int widest = c.n_ff > c.n_embd ? c.n_ff : c.n_embd;
+  if (c.n_head * c.head_dim > widest) widest = c.n_head * c.head_dim;
+  if ((uint64_t)widest * (uint64_t)B > s->c->act_capacity) return false;
+  if (((int64_t)(c.n_head / s->G) * c.head_dim * B) % 256 != 0) return false;   // the merge step works on 256-value groups
+  Enqueue probe{s, s->c->stream};
+  FlashArgs a = probe.flash_args(0);
+  a.heads *= B;
+  a.kv_heads *= B;
+  return flash_split_supported(a);
+}
+
+cudaGraphExec_t batch_step_graph(emelb_llama* s, int B) {
+  if (s->batch_graph && s->batch_graph_B == B && s->batch_graph_mode == s->c->attention_mode) return s->batch_graph;
+  emelb_ctx* c = s->c;
+  if (s->batch_graph) {
+    cudaStreamSynchronize(c->stream);
+    cudaGraphExecDestroy(s->batch_graph);
+    s->batch_graph = nullptr;
+  }
+  // one eager pass first (sets per-kernel attributes outside the capture); it is a real step for the state the
+  // caller has just written, so the KV rows it writes are the rows the replay writes again
+  Enqueue warm{s, c->stream};
+  warm.batch_step(B);
+  if (!warm.ok || !ctx_cuda_ok(c, cudaStreamSynchronize(c->stream))) return nullptr;
+  if (!ctx_cuda_ok(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal))) return nullptr;
+  Enqueue e{s, c->stream};
+  e.batch_step(B);
+  cudaGraph_t g = nullptr;
+  const bool ended = ctx_cuda_ok(c, cudaStreamEndCapture(c->stream, &g));
+  if (!ended || !e.ok || !g) {
+    if (g) cudaGraphDestroy(g);
+    return nullptr;
+  }
+  cudaGraphExec_t ex = nullptr;
+  const bool inst = ctx_cuda_ok(c, cudaGraphInstantiate(&ex, g, 0));
+  cudaGraphDestroy(g);
+  if (!inst) return nullptr;
+  s->batch_graph = ex;
+  s->batch_graph_B = B;
+  s->batch_graph_mode = c->attention_mode;
+  s->batch_launches = e.launches;
+  return ex;
+}
+
+bool write_batch_state(emelb_llama* s, const int32_t* tokens, const int32_t* positions, int B) {
+  emelb_ctx* c = s->c;
+  std::memcpy(s->host_pinned, tokens, sizeof(int) * (size_t)B);
+  std::memcpy(s->host_pinned + kMaxSeqs, positions, sizeof(int) * (size_t)B);
+  bool ok = ctx_cuda_ok(c, cudaMemcpyAsync(s->bstate, s->host_pinned, sizeof(int) * (size_t)(kMaxSeqs + B), cudaMemcpyHostToDevice, c->stream));
+  c->diag.h2d_bytes += sizeof(int) * 2 * (uint64_t)B;
+  ok = ok && ctx_cuda_ok(c, launch_batch_begin(s->bstate, kMaxSeqs, B, c->stream));
+  c->diag.kernel_launches += 1;
+  return ok;
+}
+
+bool valid_batch(const emelb_llama* s, const int32_t* tokens, const int32_t* positions, int B, int steps) {
+  if (!tokens || !positions || B < 1 || B > s->n_seq || B > kMaxSeqs) return false;
+  for (int j = 0; j < B; ++j)
+    if (!valid_step(s, tokens[j], positions[j]) || positions[j] + steps > s->cfg.n_ctx) return false;
+  return true;
+}
+
+}  // namespace
+
+uint32_t emelb_llama_set_sequences(emelb_llama* s, int32_t n_seq) {
+  if (!s || n_seq < 1 || n_seq > kMaxSeqs) return EMELB_INVALID_REQUEST;
+  emelb_ctx* c = s->c;
+  cudaSetDevice(c->device);
+  if (!ctx_cuda_ok(c, cudaStreamSynchronize(c->stream))) return EMELB_INTERNAL_ERROR;
+  if (n_seq == s->n_seq) return EMELB_OK;
+  const emelb_llama_config& g = s->cfg;
+  const size_t halves = (size_t)g.n_layer * (size_t)n_seq * (g.n_head_kv / s->G) * s->capacity * g.head_dim;
+  __half *k = nullptr, *v = nullptr;
+  if (!dev_alloc(s, (void**)&k, 2 * halves)) return EMELB_INTERNAL_ERROR;
+  if (!dev_alloc(s, (void**)&v, 2 * halves)) {
+    free_owned(s, k);
+    return EMELB_INTERNAL_ERROR;
+  }
+  free_owned(s, s->kcache);
+  free_owned(s, s->vcache);
+  s->kcache = k;
+  s->vcache = v;
+  s->n_seq = n_seq;
+  s->cur_seq = 0;
+  s->token_layers_valid = false;
+  drop_graphs(s);
+  const bool ok = ctx_cuda_ok(c, cudaMemsetAsync(k, 0, 2 * halves, c->stream)) && ctx_cuda_ok(c, cudaMemsetAsync(v, 0, 2 * halves, c->stream)) &&
+                  ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_llama_select_sequence(emelb_llama* s, int32_t seq) {
+  if (!s || seq < 0 || seq >= s->n_seq) return EMELB_INVALID_REQUEST;
+  if (seq != s->cur_seq) {
+    s->cur_seq = seq;
+    for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;   // captured steps hold the other sequence's planes
+  }
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_decode_batch(emelb_llama* s, const int32_t* tokens, const int32_t* positions, int32_t n_seq,
+                                  float* logits_out, int32_t* tokens_out) {
+  if (!s || !all_bound(s) || !valid_batch(s, tokens, positions, n_seq, 1)) return EMELB_INVALID_REQUEST;
+  emelb_ctx* c = s->c;
+  cudaSetDevice(c->device);
+  if (!batch_step_ok(s, n_seq)) return EMELB_UNSUPPORTED_OP;
+  if (!reserve_sequences(s) || !reserve_batch(s, batch_buffer_columns(s)) || s->batch_cap < n_seq) return EMELB_INTERNAL_ERROR;
+  bool ok = write_batch_state(s, tokens, positions, n_seq);
+  Enqueue e{s, c->stream};
+  if (ok) e.batch_step(n_seq);
+  ok = ok && e.ok;
+  c->diag.kernel_launches += e.launches;
+  const size_t lbytes = sizeof(float) * (size_t)s->cfg.n_vocab * (size_t)n_seq;
+  if (ok && logits_out) {
+    ok = ctx_cuda_ok(c, cudaMemcpyAsync(logits_out, s->b_logits, lbytes, cudaMemcpyDeviceToHost, c->stream));
+    c->diag.d2h_bytes += lbytes;
+  }
+  if (ok && tokens_out) {
+    ok = ctx_cuda_ok(c, cudaMemcpyAsync(s->host_pinned, s->b_idx, sizeof(int) * (size_t)n_seq, cudaMemcpyDeviceToHost, c->stream));
+    c->diag.d2h_bytes += sizeof(int) * (uint64_t)n_seq;
+  }
+  ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
+  if (ok && tokens_out) std::memcpy(tokens_out, s->host_pinned, sizeof(int) * (size_t)n_seq);
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_llama_generate_batch(emelb_llama* s, const int32_t* first_tokens, const int32_t* start_positions, int32_t n_seq,
+                                    int32_t n_steps, int32_t* tokens_out) {
+  if (!s || !tokens_out || n_steps <= 0 || !all_bound(s) || !valid_batch(s, first_tokens, start_positions, n_seq, n_steps))
+    return EMELB_INVALID_REQUEST;
+  emelb_ctx* c = s->c;
+  cudaSetDevice(c->device);
+  if (!batch_step_ok(s, n_seq)) return EMELB_UNSUPPORTED_OP;
+  if (!reserve_sequences(s) || !reserve_batch(s, batch_buffer_columns(s)) || s->batch_cap < n_seq) return EMELB_INTERNAL_ERROR;
+  bool ok = write_batch_state(s, first_tokens, start_positions, n_seq);
+  cudaGraphExec_t g = ok ? batch_step_graph(s, n_seq) : nullptr;
+  if (!g) return EMELB_INTERNAL_ERROR;
+  for (int i = 0; ok && i < n_steps; ++i) {
+    ok = ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+    ok = ok && ctx_cuda_ok(c, launch_batch_advance(s->bstate, kMaxSeqs, n_seq, s->b_idx, s->b_out, c->stream));
+  }
+  c->diag.kernel_launches += (uint64_t)n_steps * (uint64_t)(s->batch_launches + 1);
+  const size_t bytes = sizeof(int) * (size_t)n_steps * (size_t)n_seq;
+  ok = ok && ctx_cuda_ok(c, cudaMemcpyAsync(tokens_out, s->b_out, bytes, cudaMemcpyDeviceToHost, c->stream));
+  ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
+  c->diag.d2h_bytes += bytes;
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
+uint32_t emelb_llama_batch_launches_per_step(const emelb_llama* s, int32_t* out) {
+  if (!s || !out) return EMELB_INVALID_REQUEST;
+  *out = s->batch_launches + 1;
+  return EMELB_OK;
 }
 
 uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token, int32_t start_pos, int32_t n, int32_t* tokens_out) {

@@ -35,6 +35,11 @@ SIGNATURES = {
     "emelb_llama_set_step_mode": [_P, C.c_int32],
     "emelb_llama_set_prefill_batch": [_P, C.c_int32],
     "emelb_llama_set_join_fusion": [_P, C.c_int32],
+    "emelb_llama_set_sequences": [_P, C.c_int32],
+    "emelb_llama_select_sequence": [_P, C.c_int32],
+    "emelb_llama_decode_batch": [_P, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32, _P, C.POINTER(C.c_int32)],
+    "emelb_llama_generate_batch": [_P, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.POINTER(C.c_int32)],
+    "emelb_llama_batch_launches_per_step": [_P, C.POINTER(C.c_int32)],
     "emelb_llama_decode_profile": [_P, C.c_int32, C.c_int32, _P, C.c_uint64],
     "emelb_llama_exchange_export": [_P, _P, C.c_uint64],
     "emelb_llama_exchange_attach": [_P, _P, C.c_uint64],
@@ -170,6 +175,42 @@ class Session:
     def set_prefill_batch(self, max_tokens: int) -> bool:
         """Prompt tokens per batch of prefill(): 0 walks the prompt token by token."""
         return self._ret(eb.lib().emelb_llama_set_prefill_batch(self._h, max_tokens))
+
+    def set_sequences(self, n_seq: int) -> bool:
+        """Hold n_seq KV caches (reallocated and cleared); decode_batch / generate_batch step sequences 0..n-1 together."""
+        return self._ret(eb.lib().emelb_llama_set_sequences(self._h, n_seq))
+
+    def select_sequence(self, seq: int) -> bool:
+        """The sequence prefill / decode / generate work on."""
+        return self._ret(eb.lib().emelb_llama_select_sequence(self._h, seq))
+
+    def decode_batch(self, tokens, positions, want_logits: bool = False):
+        """One step of len(tokens) sequences -> next ids, or with want_logits (ids, logits [n_seq, n_vocab])."""
+        t = np.ascontiguousarray(tokens, np.int32)
+        p = np.ascontiguousarray(positions, np.int32)
+        out = np.zeros(t.size, np.int32)
+        logits = np.zeros((self.cfg.n_vocab, t.size), np.float32) if want_logits else None
+        ip = C.POINTER(C.c_int32)
+        if not self._ret(eb.lib().emelb_llama_decode_batch(self._h, t.ctypes.data_as(ip), p.ctypes.data_as(ip), t.size,
+                                                           logits.ctypes.data if want_logits else None, out.ctypes.data_as(ip))):
+            raise eb.BackendError(f"decode_batch failed with error mask {self.last_error}")
+        return (out, logits.T.copy()) if want_logits else out
+
+    def generate_batch(self, first_tokens, start_positions, n_steps: int):
+        """n_steps greedy steps of len(first_tokens) sequences fed back on the device -> ids [n_steps, n_seq]."""
+        t = np.ascontiguousarray(first_tokens, np.int32)
+        p = np.ascontiguousarray(start_positions, np.int32)
+        out = np.zeros((n_steps, t.size), np.int32)
+        ip = C.POINTER(C.c_int32)
+        if not self._ret(eb.lib().emelb_llama_generate_batch(self._h, t.ctypes.data_as(ip), p.ctypes.data_as(ip), t.size, n_steps,
+                                                             out.ctypes.data_as(ip))):
+            raise eb.BackendError(f"generate_batch failed with error mask {self.last_error}")
+        return out
+
+    def batch_launches_per_step(self) -> int:
+        v = C.c_int32(0)
+        eb.lib().emelb_llama_batch_launches_per_step(self._h, C.byref(v))
+        return v.value
 
     def set_join_fusion(self, on: bool) -> bool:
         """Sharded sessions with peers attached: joins inside the neighbouring kernels (default) or one join kernel each."""

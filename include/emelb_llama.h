@@ -141,6 +141,28 @@ EMELB_API uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* ha
  * sessions are destroyed — no arena is freed while a peer still maps it. */
 EMELB_API uint32_t emelb_llama_exchange_detach(emelb_llama* s);
 
+/* ---- several sequences decoded together (batch decode).  A session holds n_seq KV caches (default 1;
+ * emelb_llama_set_sequences reallocates and clears them).  The one-sequence entry points above (prefill, decode,
+ * generate) work on the sequence chosen by emelb_llama_select_sequence (default 0), so a caller fills each
+ * sequence's cache with its prompt and then steps all of them together:
+ *   decode_batch   one step: sequence j (0 <= j < n_seq) takes tokens[j] at positions[j]; logits_out (optional,
+ *                  host, {n_vocab, n_seq} with the sequence index fastest -- op_mul_mat's result layout) and
+ *                  tokens_out (optional, host, the greedy next id per sequence);
+ *   generate_batch n_steps greedy steps fed back on the device, one CUDA-graph replay per step;
+ *                  tokens_out[step * n_seq + j].
+ * Column j of every product is computed with the arithmetic of the one-sequence step (same block order, same
+ * rotation, split-KV attention with the same split count), so each sequence gets exactly the tokens and logits
+ * it gets when decoded alone.  Needs attention mode 0; EMELB_UNSUPPORTED_OP otherwise.  The reference's generator
+ * decodes one sequence per session (src/emel/text/generator/detail.hpp:4860-4914); this is that loop over
+ * several sessions' worth of state with the weights streamed once per step. */
+EMELB_API uint32_t emelb_llama_set_sequences(emelb_llama* s, int32_t n_seq);
+EMELB_API uint32_t emelb_llama_select_sequence(emelb_llama* s, int32_t seq);
+EMELB_API uint32_t emelb_llama_decode_batch(emelb_llama* s, const int32_t* tokens, const int32_t* positions, int32_t n_seq,
+                                            float* logits_out, int32_t* tokens_out);
+EMELB_API uint32_t emelb_llama_generate_batch(emelb_llama* s, const int32_t* first_tokens, const int32_t* start_positions,
+                                              int32_t n_seq, int32_t n_steps, int32_t* tokens_out);
+EMELB_API uint32_t emelb_llama_batch_launches_per_step(const emelb_llama* s, int32_t* out);
+
 /* Row-sharded sessions with every peer attached: where a layer's products all take the streaming kernel, its four
  * joins run inside the kernels either side of them -- the producing kernel (attention merge, output projection,
  * SwiGLU, down projection) stores its rows into every rank's copy of the vector and raises a flag, the consuming

@@ -125,6 +125,7 @@ def test_reference_block_fixtures(be, checker, t, salt):
     (4096, 64, 2), (2048, 129, 3), (4096, 40, 8), (2048, 31, 13),
     (14336, 24, 2), (14336, 24, 4), (8192, 19, 7),    # long rows: column copies that fit / do not fit in shared memory
     (2048, 2048, 12), (2048, 4096, 20), (4096, 2048, 16), (2048, 512, 20),   # column groups after the first, many CTAs
+    (1024, 70, 9), (4096, 130, 31), (8192, 64, 16), (512, 5, 17), (14336, 100, 16),   # 9..31 columns: Q4_K takes the mma.sync kernel
 ])
 def test_mul_mat_parity(be, checker, port, t, k, m, n):
     w = synth.encoded_weights(port, t, 100 + t, m, k)
@@ -166,9 +167,11 @@ def test_mul_mat_many_columns_tensor_core_kernel(be, checker, port, k, m, n):
     assert be.sync()       # a bounded wait that ran out would surface here
 
 
-def test_mul_mat_many_columns_random_block_bytes(be, checker):
-    """Arbitrary scale/min bits (all 6-bit values, extreme nibbles) through the tensor-core kernel."""
-    k, m, n = 1024, 192, 96
+@pytest.mark.parametrize("n", [96, 16, 23])
+def test_mul_mat_many_columns_random_block_bytes(be, checker, n):
+    """Arbitrary scale/min bits (all 6-bit values, extreme nibbles) through the tcgen05 kernel (96 columns) and
+    the mma.sync kernel (16 and 23 columns)."""
+    k, m = 1024, 192
     rng = synth.rng(77)
     w = rng.integers(0, 256, size=m * eb.row_bytes(eb.Q4_K, k), dtype=np.uint8)
     blocks = w.reshape(-1, eb.BLOCK_BYTES[eb.Q4_K])
