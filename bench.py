@@ -810,6 +810,108 @@ def time_cfg1_matvec(be, timed_region, copies=68):
     return ms * 1e3 / (5 * copies), wbytes + 4672 + 4 * m
 
 
+def run_decode_batch(args):
+    """--batch B > 1: B sequences decoded together (BASELINE configuration 5's batch-16 decode, or the 8B shape).
+    Every sequence gets its own random prompt of the configured length; a step = one token for each sequence."""
+    import torch
+    import emel_cpp_b200 as eb
+    from emel_cpp_b200 import llama as el
+
+    rank, world, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    sh = DECODE_SHAPES[args.workload]
+    out_type = eb.Q6_K if args.workload == "decode_8b" else eb.Q4_K
+    steps, warmup, B = args.steps, args.warmup, args.batch
+    prompt_len = sh["prompt"] if args.prompt is None else args.prompt
+    n_ctx = ((prompt_len + warmup + steps + 15) // 16) * 16
+    be = eb.Backend(local)
+    stream = torch.cuda.ExternalStream(be.stream(), device=dev)
+    shard = world > 1
+    dist = None
+    if shard:
+        import torch.distributed as dist
+        box = [eb.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        assert be.comm_init(rank, world, box[0]), be.last_error
+    G, r = (world, rank) if shard else (1, 0)
+    sess, info = build_decode_session(be, sh, out_type, n_ctx, r, G, dist, peer=False)
+    assert sess.set_sequences(B), sess.last_error
+    rng = np.random.Generator(np.random.PCG64(42))
+    t0 = time.perf_counter()
+    first, pos = [], []
+    for j in range(B):
+        prompt = rng.integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32)
+        assert sess.select_sequence(j)
+        assert sess.prefill(prompt[:-1], 0), sess.last_error
+        first.append(int(prompt[-1]))
+        pos.append(prompt_len - 1)
+    prefill_s = time.perf_counter() - t0
+
+    def timed_region(fn):
+        be.sync()
+        barrier(world)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = fn()
+        e1.record(stream)
+        be.sync()
+        torch.cuda.synchronize()
+        barrier(world)
+        return max_over_ranks(e0.elapsed_time(e1), world, dev), out
+
+    with ClockSampler(local) as clk:
+        w_ids = sess.generate_batch(first, pos, warmup)
+        ms, ids = timed_region(lambda: sess.generate_batch(w_ids[-1], [p + warmup for p in pos], steps))
+        launches = sess.batch_launches_per_step()
+        # end to end: one C-ABI call per step, B token ids in, B next ids out (host round trip every step)
+        d0 = be.diagnostics()
+
+        def loop():
+            t, o = list(w_ids[-1]), []
+            for i in range(steps):
+                t = list(sess.decode_batch(t, [p + warmup + i for p in pos]))
+                o.append(t)
+            return o
+        ms_e, ids_e = timed_region(loop)
+        d1 = be.diagnostics()
+        assert [list(x) for x in ids] == ids_e, "device-fed and host-fed batch loops disagree"
+        # the same sequences one at a time, for the ratio
+        assert sess.select_sequence(0)
+        w1 = sess.generate(first[0], pos[0], warmup)
+        ms1, ids1 = timed_region(lambda: sess.generate(int(w1[-1]), pos[0] + warmup, min(steps, 32)))
+        assert list(ids1) == [int(x[0]) for x in ids[:len(ids1)]], "sequence 0 decodes differently alone"
+    clocks = clk.summary()
+    tok_s = steps * B / (ms * 1e-3)
+    kv_bytes_per_pos = sh["n_layer"] * 2 * sh["n_head_kv"] * sh["head_dim"] * 2
+    ctx_mid = prompt_len + warmup + steps // 2
+    bytes_per_step = info["weight_bytes"] * (world if shard else 1) + kv_bytes_per_pos * ctx_mid * B
+    peaks, peak_kind = measured_peaks()
+    gbs = bytes_per_step / (ms / steps * 1e-3) / 1e9 / (world if shard else 1)
+    line = {
+        "metric": "decode tok/s", "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "strong" if shard else "weak", "vs_baseline": None,
+        "dtype": "int8 dot (mma.sync / dp4a) + f32 scales; f16 KV", "data": "synthetic",
+        "config": {"workload": sh["name"].replace("batch-1", f"batch-{B}"), "batch": B, "prompt_tokens": prompt_len, "decoded_tokens_per_sequence": steps,
+                   "n_ctx": n_ctx, "launch": "one CUDA-graph replay per step; the next token ids are fed back on the device",
+                   "l2_policy": f"inputs larger than L2: {bytes_per_step / 1e9:.2f} GB of weights and KV rows read per step",
+                   "parallelism": "single GPU" if world == 1 else f"matrices row-sharded over {world} GPUs, NCCL all-gather joins of the batch tensors",
+                   "kernel_launches_per_step": launches, "prefill_s": round(prefill_s, 2)},
+        "hbm_gbs_effective": round(gbs, 1),
+        "e2e": {"value": round(steps * B / (ms_e * 1e-3), 2), "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
+                "d2h_bytes_per_step": (d1["d2h_bytes"] - d0["d2h_bytes"]) // steps},
+        "gpu_launches": launches * steps,
+        "roofline": {"bound": "hbm", "kernel": "whole step (weights once + every sequence's KV rows)", "achieved": round(gbs, 2),
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": f"of {peak_kind}",
+                     "algorithmic_bytes_per_step": int(bytes_per_step), "traffic": None},
+        "one_sequence_alone": {"tok_s": round(len(ids1) / (ms1 * 1e-3), 2), "same_tokens": True},
+        "cpu_baseline": None, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    release_decode_session(be, sess, info, world)
+
+
 def run_decode(args):
     import torch
     import emel_cpp_b200 as eb
@@ -1160,6 +1262,7 @@ def main():
     ap.add_argument("--shard", action="store_true", help="accepted for compatibility: sharding is what --gpus N > 1 does")
     ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
                     help="sharded decode: join the ranks' row intervals by peer stores over NVLink (default) or by NCCL all-gathers")
+    ap.add_argument("--batch", type=int, default=1, help="decode workloads: sequences decoded together (one token each per step)")
     ap.add_argument("--one-kernel", action="store_true",
                     help="decode workloads: run the headline through the one-kernel step (every layer of a token in one "
                          "persistent kernel) instead of the launch chain")
@@ -1173,7 +1276,7 @@ def main():
     elif args.impl == "reference":
         (run_reference_decode if decode else run_reference_gemv)(args)
     else:
-        (run_decode if decode else run_gemv)(args)
+        (run_decode_batch if decode and args.batch > 1 else run_decode if decode else run_gemv)(args)
 
 
 if __name__ == "__main__":

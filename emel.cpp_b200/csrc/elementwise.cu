@@ -283,6 +283,47 @@ rms_apply_batch_kernel(const float* __restrict__ x, const float* __restrict__ w,
     out[(int64_t)e * B + j] = __fmul_rn(__fmul_rn(x[(int64_t)e * B + j], scale), w[e]);
 }
 
+// A few columns (a decode step of several sequences): one launch normalises and quantizes.  CTA = one column, 1024
+// threads; the squares are summed in f64 (thread partial sums over features t, t + 1024, ..., then warps, then one
+// thread in a fixed order), and then warp w takes 256-feature blocks w, w + 32, ...: the lane's 8 elements are
+// scaled, multiplied by the weight and quantized to Q8_K like every other activation vector.
+__global__ void __launch_bounds__(1024)
+rms_norm_quant_cols_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int K, int B, ActPlanesMut planes) {
+  __shared__ double s_part[32];
+  __shared__ float s_scale;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, col = blockIdx.x;
+  double ss = 0.0;
+#pragma unroll 4
+  for (int e = threadIdx.x; e < K; e += 1024) {
+    const float v = x[(int64_t)e * B + col];
+    ss += (double)__fmul_rn(v, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) s_part[warp] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t += s_part[i];
+    const float mean = (float)(t / (double)K);
+    s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  for (int blk = warp; blk < K / QK_K; blk += 32) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = blk * QK_K + 8 * lane + i;
+      v[i] = __fmul_rn(__fmul_rn(x[(int64_t)e * B + col], scale), w[e]);
+    }
+    uint32_t lo, hi; int bs; float dq;
+    q8_k_block_warp(v, lane, lo, hi, bs, dq);
+    q8_k_store_planes(planes, col, K, blk, lane, lo, hi, bs, dq);
+  }
+}
+
 // thread = (token j fastest, rotation pair or copied element, head)
 __global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, const float* __restrict__ v,
                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pos0, int B,
@@ -319,42 +360,55 @@ __global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, c
   }
 }
 
-// one decode step of several sequences: column j is sequence j at its own position
-__global__ void rope_store_seqs_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                       const int* __restrict__ positions, int B, int n_head, int n_head_kv, int head_dim,
-                                       int rot_dim, int neox, float* __restrict__ q_out, __half* kcache, __half* vcache,
-                                       int64_t seq_stride, int64_t cache_head_stride) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= B) return;
-  const int head = blockIdx.y, pos = positions[j], pairs = rot_dim / 2;
-  const float* ct = cos_t + (int64_t)pos * pairs;
-  const float* st = sin_t + (int64_t)pos * pairs;
-  const int x1_base = neox ? pairs : 1, stride = neox ? 1 : 2;
-  if (head < n_head) {
-    const float* h = q + (int64_t)head * head_dim * B + j;
-    float* o = q_out + ((int64_t)j * n_head + head) * head_dim;
-    for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
-      const int d0 = p * stride, d1 = p * stride + x1_base;
-      const float x0 = h[(int64_t)d0 * B], x1 = h[(int64_t)d1 * B], c = ct[p], s = st[p];
-      o[d0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-      o[d1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
-    }
-    for (int d = rot_dim + threadIdx.y; d < head_dim; d += blockDim.y) o[d] = h[(int64_t)d * B];
+// one decode step of several sequences: column j is sequence j at its own position.  Thread = (sequence j fastest,
+// slot, head): a slot is one rotation pair or, past the rotated dimensions, two copied elements; heads are the
+// query heads, then the K heads, then the V heads (two elements per slot, no rotation)
+__global__ void __launch_bounds__(256)
+rope_store_seqs_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ positions, int B,
+                       int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, float* __restrict__ q_out, __half* kcache,
+                       __half* vcache, int64_t seq_stride, int64_t cache_head_stride) {
+  const int half = head_dim / 2, pairs = rot_dim / 2;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)(n_head + 2 * n_head_kv) * half * B;
+  if (idx >= total) return;
+  const int j = (int)(idx % B);
+  const int slot = (int)((idx / B) % half);
+  const int head = (int)(idx / ((int64_t)B * half));
+  const int pos = positions[j];
+  int d0, d1;
+  float c = 1.0f, sn = 0.0f;
+  const bool is_v = head >= n_head + n_head_kv;
+  const bool rotate = !is_v && slot < pairs;
+  if (rotate) {
+    d0 = neox ? slot : 2 * slot;
+    d1 = neox ? slot + pairs : 2 * slot + 1;
+    c = cos_t[(int64_t)pos * pairs + slot];
+    sn = sin_t[(int64_t)pos * pairs + slot];
+  } else if (is_v) {
+    d0 = 2 * slot;
+    d1 = 2 * slot + 1;
   } else {
-    const int kh = head - n_head;
-    const float* h = k + (int64_t)kh * head_dim * B + j;
-    const float* vv = v + (int64_t)kh * head_dim * B + j;
-    __half* kd = kcache + (int64_t)j * seq_stride + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
-    __half* vd = vcache + (int64_t)j * seq_stride + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
-    for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
-      const int d0 = p * stride, d1 = p * stride + x1_base;
-      const float x0 = h[(int64_t)d0 * B], x1 = h[(int64_t)d1 * B], c = ct[p], s = st[p];
-      kd[d0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
-      kd[d1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
-    }
-    for (int d = rot_dim + threadIdx.y; d < head_dim; d += blockDim.y) kd[d] = __float2half_rn(h[(int64_t)d * B]);
-    for (int d = threadIdx.y; d < head_dim; d += blockDim.y) vd[d] = __float2half_rn(vv[(int64_t)d * B]);
+    d0 = rot_dim + 2 * (slot - pairs);
+    d1 = d0 + 1;
+  }
+  const float* src = head < n_head ? q + (int64_t)head * head_dim * B
+                                   : (is_v ? v + (int64_t)(head - n_head - n_head_kv) * head_dim * B : k + (int64_t)(head - n_head) * head_dim * B);
+  const float x0 = src[(int64_t)d0 * B + j], x1 = src[(int64_t)d1 * B + j];
+  float o0 = x0, o1 = x1;
+  if (rotate) {
+    o0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+    o1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+  }
+  if (head < n_head) {
+    float* o = q_out + ((int64_t)j * n_head + head) * head_dim;
+    o[d0] = o0;
+    o[d1] = o1;
+  } else {
+    const int kh = is_v ? head - n_head - n_head_kv : head - n_head;
+    __half* dst = (is_v ? vcache : kcache) + (int64_t)j * seq_stride + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+    dst[d0] = __float2half_rn(o0);
+    dst[d1] = __float2half_rn(o1);
   }
 }
 
@@ -608,9 +662,17 @@ cudaError_t launch_rope_store_seqs(const float* q, const float* k, const float* 
                                    const int* positions, int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
                                    float* q_out, __half* kcache, __half* vcache, int64_t seq_stride, int64_t cache_head_stride,
                                    cudaStream_t st) {
-  rope_store_seqs_kernel<<<dim3((B + 31) / 32, n_head + n_head_kv), dim3(32, 8), 0, st>>>(
-      q, k, v, cos_t, sin_t, positions, B, n_head, n_head_kv, head_dim, rot_dim, neox, q_out, kcache, vcache, seq_stride,
-      cache_head_stride);
+  if (head_dim % 2 != 0 || rot_dim % 2 != 0) return cudaErrorInvalidValue;
+  const int64_t total = (int64_t)(n_head + 2 * n_head_kv) * (head_dim / 2) * B;
+  rope_store_seqs_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(q, k, v, cos_t, sin_t, positions, B, n_head, n_head_kv,
+                                                                         head_dim, rot_dim, neox, q_out, kcache, vcache, seq_stride,
+                                                                         cache_head_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rms_norm_quant_cols(const float* x, const float* w, float eps, int K, int B, ActPlanesMut planes, cudaStream_t st) {
+  if (K % QK_K != 0 || B < 1) return cudaErrorInvalidValue;
+  rms_norm_quant_cols_kernel<<<B, 1024, 0, st>>>(x, w, eps, K, B, planes);
   return cudaGetLastError();
 }
 

@@ -223,7 +223,7 @@ cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int
   // a handful of columns of Q4_K (several sequences decoding together): mma.sync per sub-block (gemm_q4k_mma.cu)
   if (!argmax && gemm_q4k_mma_supported(type, a, ncols)) {
     ++*launches;
-    return launch_gemm_q4k_mma(a, ncols, st);
+    return launch_gemm_q4k_mma(a, ncols, sm_count, st);
   }
   // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
   if (!argmax && gemv_takes_tensor_core(type, a, ncols)) {

@@ -124,7 +124,7 @@ cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, int sm_co
 
 // gemm_q4k_mma.cu: 9 to 31 columns of Q4_K weights (mma.sync int8, one sub-block per instruction)
 bool gemm_q4k_mma_supported(int type, const GemvArgs& a, int ncols);
-cudaError_t launch_gemm_q4k_mma(const GemvArgs& a, int ncols, cudaStream_t st);
+cudaError_t launch_gemm_q4k_mma(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st);
 
 // gemv2.cu
 cudaError_t launch_gemv_stream2(int type, const GemvArgs& a, int ncols, bool argmax, int sm_count, cudaStream_t st,
@@ -183,6 +183,8 @@ cudaError_t launch_rope_store_seqs(const float* q, const float* k, const float* 
                                    const int* positions, int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
                                    float* q_out, __half* kcache, __half* vcache, int64_t seq_stride, int64_t cache_head_stride,
                                    cudaStream_t st);
+// rms_norm of every column of x {K, B} and its Q8_K planes in one launch (a few columns: one CTA each)
+cudaError_t launch_rms_norm_quant_cols(const float* x, const float* w, float eps, int K, int B, ActPlanesMut planes, cudaStream_t st);
 // per column of x {rows, B}: the highest value and, on ties, the lowest row (src/emel/kernel/detail.hpp:3720-3723)
 constexpr int kArgmaxColumnParts = 256;
 cudaError_t launch_argmax_columns(const float* x, int rows, int B, float* part_val, int* part_idx, int* out_idx, cudaStream_t st);

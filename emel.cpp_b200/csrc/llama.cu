@@ -523,6 +523,39 @@ struct Enqueue {
     check(launch_gemv(w.type, a, B, false, s->c->sm_count, st, &launches));
   }
 
+  // up to three matrices of one type and K against the same batch (Q, K, V or gate, up): one launch where the
+  // 16-column tensor-core kernel takes the group, else one product each
+  void batch_matmul_group(const Tensor* const* w, float* const* y, int n, const float* x, int B, bool quantized = false) {
+    bool same = n >= 2 && n <= 3;
+    for (int i = 1; same && i < n; ++i) same = w[i]->type == w[0]->type && w[i]->K == w[0]->K && w[i]->row_bytes == w[0]->row_bytes;
+    GemvArgs a{};
+    if (same) {
+      a.W = w[0]->dev;
+      a.row_bytes = w[0]->row_bytes;
+      a.M = w[0]->M;
+      a.K = w[0]->K;
+      a.act = planes_view(planes(), w[0]->type, w[0]->K);
+      a.y = y[0];
+      a.ldy = B;
+      a.W2 = w[1]->dev; a.M2 = w[1]->M; a.y2 = y[1];
+      if (n == 3) { a.W3 = w[2]->dev; a.M3 = w[2]->M; a.y3 = y[2]; }
+      same = gemm_q4k_mma_supported(w[0]->type, a, B);
+    }
+    if (!same) {
+      for (int i = 0; i < n; ++i) batch_matmul(*w[i], x, y[i], B, quantized || i > 0);
+      return;
+    }
+    if (!quantized) {
+      check(quantize_into_planes(w[0]->type, x, B, B, w[0]->K, planes(), st));
+      ++launches;
+      batch_family = family_of(w[0]->type);
+      batch_tc_tiled = false;
+    }
+    a.sched = s->c->next_sched();
+    a.status = s->c->status_word();
+    check(launch_gemv(w[0]->type, a, B, false, s->c->sm_count, st, &launches));
+  }
+
   // B prompt tokens (ids in s->batch_tokens) at positions pos0 .. pos0 + B - 1 through every layer: fills the
   // KV cache rows of those positions.  Same arithmetic per token as token_step except the attention, which
   // is the f32 online-softmax kernel for token batches (attention mode 0 only).
@@ -597,16 +630,32 @@ struct Enqueue {
     const int* pos = s->bstate + kMaxSeqs;
     const int* kvn = s->bstate + 2 * kMaxSeqs;
     s->planes_src = nullptr;
+    // rms_norm of the batch for a product of weight type `type`: with K-quant weights one launch leaves the Q8_K
+    // planes (true: the product need not quantize), else the f32 result goes to b_norm
+    auto norm = [&](const Tensor& nw, int type) {
+      if (family_of(type) == 1 && B <= 64) {
+        check(launch_rms_norm_quant_cols(s->b_hidden, reinterpret_cast<const float*>(nw.dev), c.rms_eps, c.n_embd, B, planes(), st));
+        ++launches;
+        batch_family = 1;
+        batch_tc_tiled = false;
+        return true;
+      }
+      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(nw.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
+      launches += 2;
+      return false;
+    };
     check(launch_embed_rows(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, tok, B, s->b_hidden, c.n_embd, st));
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
       const Layer& w = s->layers[l];
       const int64_t layer_off = cache_off(s, l, 0);
-      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
-      ++launches;
-      batch_matmul(w.wq, s->b_norm, s->b_q, B);
-      batch_matmul(w.wk, s->b_norm, s->b_k, B, true);
-      batch_matmul(w.wv, s->b_norm, s->b_v, B, true);
+      {
+        const bool same_type = w.wk.type == w.wq.type && w.wv.type == w.wq.type;
+        const bool quantized = same_type ? norm(w.attn_norm, w.wq.type) : (norm(w.attn_norm, T_F32), false);
+        const Tensor* ws[3] = {&w.wq, &w.wk, &w.wv};
+        float* ys[3] = {s->b_q, s->b_k, s->b_v};
+        batch_matmul_group(ws, ys, 3, s->b_norm, B, quantized);
+      }
       check(launch_rope_store_seqs(s->b_q, s->b_k, s->b_v, s->rope_cos, s->rope_sin, pos, B, heads_l, kv_l, c.head_dim, rot,
                                    c.rope_neox, s->b_qs, s->kcache + layer_off, s->vcache + layer_off,
                                    (int64_t)kv_l * s->capacity * c.head_dim, s->capacity * c.head_dim, st));
@@ -629,21 +678,26 @@ struct Enqueue {
       batch_matmul(w.wo, s->b_attn, y_mine, B);
       batch_gather(s->b_y, embd_l, B);
       check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
-      check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.ffn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
-      batch_matmul(w.gate, s->b_norm, s->b_gate, B);
-      batch_matmul(w.up, s->b_norm, s->b_up, B, true);
+      ++launches;
+      {
+        const bool quantized = w.up.type == w.gate.type ? norm(w.ffn_norm, w.gate.type) : (norm(w.ffn_norm, T_F32), false);
+        const Tensor* ws[2] = {&w.gate, &w.up};
+        float* ys[2] = {s->b_gate, s->b_up};
+        batch_matmul_group(ws, ys, 2, s->b_norm, B, quantized);
+      }
       check(launch_swiglu(s->b_gate, s->b_up, (int)(ff_l * b), ffn_mine, 0, planes(), st));
+      ++launches;
       batch_gather(s->b_ffn, ff_l, B);
       batch_matmul(w.down, s->b_ffn, y_mine, B);
       batch_gather(s->b_y, embd_l, B);
       check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
-      launches += 4;
+      ++launches;
     }
-    check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(s->out_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
-    batch_matmul(s->output, s->b_norm, s->b_logits + r * vocab_l * b, B);
+    const bool quantized = norm(s->out_norm, s->output.type);
+    batch_matmul(s->output, s->b_norm, s->b_logits + r * vocab_l * b, B, quantized);
     batch_gather(s->b_logits, vocab_l, B);
     check(launch_argmax_columns(s->b_logits, c.n_vocab, B, s->b_amax_val, s->b_amax_idx, s->b_idx, st));
-    launches += 3;
+    launches += 2;
   }
 
   void token_step(Mode mode) {
