@@ -149,6 +149,27 @@ def main():
     assert np.array_equal(batched["full"].view(np.uint32), batched["shard"].view(np.uint32)), \
         float(np.abs(batched["full"] - batched["shard"]).max())
 
+    # several sequences stepped together in a sharded session (joins of the batch tensors by NCCL): every sequence
+    # gets the ids it gets alone in the same session
+    be_shard.set_attention_mode(0)
+    sess = build(be_shard, be_full, CFG, rank, world, buffers)
+    assert sess.set_sequences(3), sess.last_error
+    firsts, poss, alone = [], [], []
+    for j in range(3):
+        pj = np.random.Generator(np.random.PCG64(30 + j)).integers(0, CFG["n_vocab"], size=7 + 2 * j).tolist()
+        assert sess.select_sequence(j) and sess.prefill(pj[:-1], 0), sess.last_error
+        firsts.append(pj[-1])
+        poss.append(len(pj) - 1)
+    for j in range(3):
+        assert sess.select_sequence(j)
+        alone.append(list(sess.generate(firsts[j], poss[j], 6)))
+    together = sess.generate_batch(firsts, poss, 6)
+    for j in range(3):
+        assert list(together[:, j]) == alone[j], (j, list(together[:, j]), alone[j])
+    assert be_shard.sync()
+    dist.barrier()
+    sess.close()
+
     # op level: each rank runs its row slice of one op_mul_mat, then the join
     k, m, n = 2048, 4096, 3
     w = be_full.alloc(m * eb.row_bytes(eb.Q4_K, k))
