@@ -50,6 +50,10 @@ using fa::kMergeMaxSplits;
 template <int FAMILY>
 __global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, ActPlanesMut planes) {
   pdl_trigger();
+  JoinOut jo{};   // a constant of the session: fetched before the wait for the preceding kernel
+  if constexpr (FAMILY == 1) {
+    if (a.join_out) jo = *a.join_out;
+  }
   pdl_wait();
   __shared__ float s_w[4][kMergeMaxSplits];
   __shared__ float s_inv[4];
@@ -62,7 +66,7 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, Act
   const int hl = threadIdx.x / D, d = threadIdx.x - hl * D;
   const float o = fa::merge_output(a, h0 + hl, d, s_w[hl], s_inv[hl]);
   if constexpr (FAMILY == 1) {
-    if (a.join_out.world > 1) {
+    if (a.join_out) {
       // these are this rank's heads of a joined vector: the block goes, quantized, into every rank's planes
       s_out[threadIdx.x] = o;
       __syncthreads();
@@ -72,9 +76,9 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, Act
         for (int i = 0; i < 8; ++i) v[i] = s_out[8 * lane + i];
         uint32_t lo, hi; int bs; float dq;
         q8_k_block_warp(v, lane, lo, hi, bs, dq);
-        join_store_q8_k_block(a.join_out, a.join_out.first_block + blockIdx.x, lane, lo, hi, bs, dq);
+        join_store_q8_k_block(jo, jo.first_block + blockIdx.x, lane, lo, hi, bs, dq);
       }
-      join_publish(a.join_out, gridDim.x);
+      join_publish(jo, gridDim.x);
       return;
     }
   }
@@ -265,13 +269,13 @@ bool flash_merge_can_quantize(const FlashArgs& a) { return (a.heads * a.head_dim
 cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches, int out_family,
                                 ActPlanesMut out_planes) {
   (void)sm_count;
-  if (a.join_out.world > 1 && (a.heads * a.head_dim) % 256 != 0) return cudaErrorInvalidValue;
+  if (a.join_out && (a.heads * a.head_dim) % 256 != 0) return cudaErrorInvalidValue;
   const int n_rep = a.heads / a.kv_heads;
   cudaError_t e = a.head_dim == 64 ? launch_split<64>(a, n_rep, st) : launch_split<128>(a, n_rep, st);
   if (e != cudaSuccess) return e;
   const int total = a.heads * a.head_dim;
   if (total % 256 == 0) {
-    if (a.join_out.world > 1) out_family = 1;
+    if (a.join_out) out_family = 1;
     if (out_family == 1) EMELB_LAUNCH(flash_merge_kernel<1>, total / 256, 256, 0, st, a, out_planes);
     else if (out_family == 2) EMELB_LAUNCH(flash_merge_kernel<2>, total / 256, 256, 0, st, a, out_planes);
     else EMELB_LAUNCH(flash_merge_kernel<0>, total / 256, 256, 0, st, a, out_planes);

@@ -592,8 +592,9 @@ cudaError_t launch_rope_rows(const StridedF32& src, const StridedF32& dst, const
 
 // the SwiGLU of this rank's interval of the ffn vector: one 256-block per CTA, quantized to Q8_K once and written
 // into every rank's planes of the joined vector
-__global__ void __launch_bounds__(256) swiglu_join_kernel(const float* __restrict__ gate, const float* __restrict__ up, JoinOut join) {
+__global__ void __launch_bounds__(256) swiglu_join_kernel(const float* __restrict__ gate, const float* __restrict__ up, const JoinOut* __restrict__ join_dev) {
   pdl_trigger();
+  const JoinOut jo = *join_dev;   // a constant of the session: fetched before the wait for the preceding kernel
   pdl_wait();
   __shared__ float s_v[QK_K];
   const int lane = threadIdx.x & 31;
@@ -607,14 +608,14 @@ __global__ void __launch_bounds__(256) swiglu_join_kernel(const float* __restric
     for (int i = 0; i < 8; ++i) v[i] = s_v[8 * lane + i];
     uint32_t lo, hi; int bs; float d;
     q8_k_block_warp(v, lane, lo, hi, bs, d);
-    join_store_q8_k_block(join, join.first_block + blockIdx.x, lane, lo, hi, bs, d);
+    join_store_q8_k_block(jo, jo.first_block + blockIdx.x, lane, lo, hi, bs, d);
   }
-  join_publish(join, gridDim.x);
+  join_publish(jo, gridDim.x);
 }
 
-cudaError_t launch_swiglu_join(const float* gate, const float* up, int n, const JoinOut& join, cudaStream_t st) {
-  if (n % QK_K != 0) return cudaErrorInvalidValue;
-  EMELB_LAUNCH(swiglu_join_kernel, n / QK_K, 256, 0, st, gate, up, join);
+cudaError_t launch_swiglu_join(const float* gate, const float* up, int n, const JoinOut* join_dev, cudaStream_t st) {
+  if (n % QK_K != 0 || !join_dev) return cudaErrorInvalidValue;
+  EMELB_LAUNCH(swiglu_join_kernel, n / QK_K, 256, 0, st, gate, up, join_dev);
   return cudaGetLastError();
 }
 

@@ -556,7 +556,9 @@ __host__ __device__ constexpr int warp_bytes3() {
 
 // NCOLS > 1: the same rows against NCOLS activation columns (plain outputs only): the weights of a stage
 // are decoded once per column from shared memory, every column keeps its own f32 chain
-template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX, int NCOLS = 1>
+// JOIN: the launch waits for / raises a join by peer stores (row-sharded sessions); compiled apart so that the
+// one-GPU kernels carry none of it
+template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX, int NCOLS = 1, bool JOIN = false>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 gemv3_kernel(const GemvArgs p) {
   static_assert(NCOLS == 1 || !ARGMAX, "the fused argmax is a one-column path");
@@ -577,6 +579,17 @@ gemv3_kernel(const GemvArgs p) {
   const int ntasks = nt0 + nt1 + nt2;
 
   pdl_trigger();
+  // the join descriptors are constants of the session: fetched now, while the first weight copies start
+  JoinIn ji{};
+  char* jo_base = nullptr;
+  int64_t jo_offset = 0;
+  if constexpr (JOIN) {
+    if (p.join_in) ji = *p.join_in;
+    if (p.join_out) {
+      jo_offset = p.join_out->out_offset;
+      if (lane < p.join_out->world) jo_base = p.join_out->base[lane];
+    }
+  }
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(bars + s, 1);
@@ -622,10 +635,10 @@ gemv3_kernel(const GemvArgs p) {
   pdl_wait();
   // a joined input vector: every peer's rows must have landed before the first read
   bool joined_in = false;
-  if constexpr (KQ && NCOLS == 1) {
-    if (p.join_in.flags) {
+  if constexpr (JOIN) {
+    if (p.join_in) {
       joined_in = true;
-      join_wait(p.join_in, p.status);
+      join_wait(ji, p.status);
     }
   }
 
@@ -643,8 +656,8 @@ gemv3_kernel(const GemvArgs p) {
       if (p.pro_x) {
         fused = true;
         // rows written by peers are read past the L1 (ld.cg): a line of an earlier read may still sit there
-        auto ldx = [&](const float* a) { return joined_in ? __ldcg(a) : __ldg(a); };
-        auto ldx4 = [&](const float* a) { return joined_in ? __ldcg(reinterpret_cast<const float4*>(a)) : __ldg(reinterpret_cast<const float4*>(a)); };
+        auto ldx = [&](const float* a) { return JOIN && joined_in ? __ldcg(a) : __ldg(a); };
+        auto ldx4 = [&](const float* a) { return JOIN && joined_in ? __ldcg(reinterpret_cast<const float4*>(a)) : __ldg(reinterpret_cast<const float4*>(a)); };
         float scale = 1.0f;
         if (p.pro_w) {
           // rms_norm (src/emel/text/generator/detail.hpp:2735-2756): f64 sum of the f32 squares
@@ -692,14 +705,14 @@ gemv3_kernel(const GemvArgs p) {
       const int4* gq = reinterpret_cast<const int4*>(p.act.qs + gcol * p.act.col_stride_qs);
       // planes written by peers are read past the L1 (ld.cg): a line of an earlier read may still sit there
       for (int i = threadIdx.x; i < p.K / 16; i += WARPS * 32)
-        reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = joined_in ? __ldcg(gq + i) : __ldg(gq + i);
+        reinterpret_cast<int4*>(sq)[i ^ ((i >> 4) & 7)] = JOIN && joined_in ? __ldcg(gq + i) : __ldg(gq + i);
       if constexpr (KQ) {
         const int4* gb = reinterpret_cast<const int4*>(p.act.bsums + gcol * p.act.col_stride_bs);
-        for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = joined_in ? __ldcg(gb + i) : __ldg(gb + i);
+        for (int i = threadIdx.x; i < p.K / 128; i += WARPS * 32) reinterpret_cast<int4*>(sb)[i] = JOIN && joined_in ? __ldcg(gb + i) : __ldg(gb + i);
       }
       const float* gd = p.act.d + gcol * p.act.col_stride_d;
       const int nd = KQ ? p.K / QK_K : p.K / 32;
-      for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = joined_in ? __ldcg(gd + i) : __ldg(gd + i);
+      for (int i = threadIdx.x; i < nd; i += WARPS * 32) sd[i] = JOIN && joined_in ? __ldcg(gd + i) : __ldg(gd + i);
     }
     if (col == 0) {
       x.qs = sq;
@@ -803,8 +816,8 @@ gemv3_kernel(const GemvArgs p) {
           }
         }
       }
-      if constexpr (KQ && !ARGMAX && NCOLS == 1) {
-        if (p.join_out.world > 1) {
+      if constexpr (JOIN) {
+        if (p.join_out) {
           // this rank's rows go to every rank's copy of the vector: the four rows of the task are collected and
           // lanes 0 .. world-1 store them to one rank each (row counts are multiples of four in a sharded session)
           plain = false;
@@ -812,10 +825,9 @@ gemv3_kernel(const GemvArgs p) {
           if (b == 0 && row < mseg && p.residual) o = __fadd_rn(p.residual[row], acc);
           const float4 o4 = make_float4(__shfl_sync(0xffffffffu, o, 0), __shfl_sync(0xffffffffu, o, 8),
                                         __shfl_sync(0xffffffffu, o, 16), __shfl_sync(0xffffffffu, o, 24));
-          char* base = lane < p.join_out.world ? join_base(p.join_out, lane) : nullptr;
           const int row0 = lt * ROWS_PER_STAGE;
-          if (base && row0 + ROWS_PER_STAGE <= mseg)
-            *reinterpret_cast<float4*>(base + p.join_out.out_offset + (int64_t)row0 * 4) = o4;
+          if (jo_base && row0 + ROWS_PER_STAGE <= mseg)
+            *reinterpret_cast<float4*>(jo_base + jo_offset + (int64_t)row0 * 4) = o4;
         }
       }
       if (plain && row < mseg) {
@@ -837,8 +849,8 @@ gemv3_kernel(const GemvArgs p) {
   }
   if (failed && lane == 0 && p.status) atomicExch(p.status, 1);
 
-  constexpr bool kJoins = KQ && !ARGMAX && NCOLS == 1;
-  if (kJoins && p.join_out.world > 1) __threadfence_system();   // this thread's stores to the peers, before the block is counted
+  constexpr bool kJoins = JOIN;
+  if (kJoins && p.join_out) __threadfence_system();   // this thread's stores to the peers, before the block is counted
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -846,7 +858,7 @@ gemv3_kernel(const GemvArgs p) {
       p.sched[0] = 0;
       p.sched[1] = 0;
       __threadfence();
-      if (kJoins && p.join_out.world > 1) join_raise(p.join_out);
+      if (kJoins && p.join_out) join_raise(*p.join_out);
     }
   }
 
@@ -904,9 +916,9 @@ cudaError_t launch2(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_
 }
 
 // third generation: one column (or the argmax head), activations in shared memory
-template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX, int NCOLS = 1>
+template <int T, int STAGES, int WARPS, int MINB, bool ARGMAX, int NCOLS = 1, bool JOIN = false>
 cudaError_t launch3(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
-  auto kern = gemv3_kernel<T, STAGES, WARPS, MINB, ARGMAX, NCOLS>;
+  auto kern = gemv3_kernel<T, STAGES, WARPS, MINB, ARGMAX, NCOLS, JOIN>;
   const size_t smem = (size_t)NCOLS * act_smem_bytes(is_k_type(T), a.K) + (size_t)WARPS * warp_bytes3<T, STAGES>();
   // Per instantiation, host thread (one context, one lane per thread) and device: the attribute is set once,
   // and the CTAs per SM are remembered for the last few shared-memory sizes (matrices of different K alternate
@@ -946,18 +958,18 @@ cudaError_t launch3(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_
   return launch_kernel(kern, dim3(grid), dim3(WARPS * 32), smem, st, a.pdl != 0, a);
 }
 
-template <int T, bool ARGMAX>
+template <int T, bool ARGMAX, bool JOIN = false>
 cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* grid_out) {
   constexpr bool kLight = T == T_Q4_K || T == T_Q4_0;  // 64 registers: 32 warps per SM; the others 16
   constexpr int kWarpsPerSm = kLight ? 32 : 16;
   // few rows: smaller CTAs, so that every SM gets about the same number of 4-row tasks
   const int ntasks = (a.M + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE + (a.M2 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE +
                      (a.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
-  if (ntasks >= 8 * 3 * sm_count || ARGMAX) return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX>(a, sm_count, st, grid_out);
-  if (ntasks >= 4 * 3 * sm_count) return launch3<T, 1, 4, kWarpsPerSm / 4, ARGMAX>(a, sm_count, st, grid_out);
+  if (ntasks >= 8 * 3 * sm_count || ARGMAX) return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
+  if (ntasks >= 4 * 3 * sm_count) return launch3<T, 1, 4, kWarpsPerSm / 4, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
   // about one task per warp: keep the whole row group of a warp in flight (2 chunks), or a deeper ring for long rows
-  if (a.K / CHUNK >= 4) return launch3<T, 4, 2, kLight ? 4 : 3, ARGMAX>(a, sm_count, st, grid_out);
-  return launch3<T, 2, 2, kLight ? 8 : 4, ARGMAX>(a, sm_count, st, grid_out);
+  if (a.K / CHUNK >= 4) return launch3<T, 4, 2, kLight ? 4 : 3, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
+  return launch3<T, 2, 2, kLight ? 8 : 4, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
 }
 
 template <int T>
@@ -982,7 +994,9 @@ cudaError_t launch_type2(GemvArgs a, int ncols, bool argmax, int sm_count, cudaS
     else if (left >= 4) { e = launch2<T, 4, 1, false>(b, sm_count, st, grid_out); done += 4; }
     else if (left >= 2) { e = launch2<T, 2, 1, false>(b, sm_count, st, grid_out); done += 2; }
     else {
-      e = launch3_cfg<T, false>(b, sm_count, st, grid_out);
+      const bool join = b.join_in != nullptr || b.join_out != nullptr;
+      if constexpr (is_k_type(T)) e = join ? launch3_cfg<T, false, true>(b, sm_count, st, grid_out) : launch3_cfg<T, false>(b, sm_count, st, grid_out);
+      else e = join ? cudaErrorInvalidValue : launch3_cfg<T, false>(b, sm_count, st, grid_out);
       done += 1;
     }
     ++*launches;

@@ -40,7 +40,8 @@ constexpr int kSchedSlots = 64;   // task-counter slots rotated over consecutive
 // rank per GPU).  The producing kernel writes its output rows into every rank's copy of the vector (the
 // exchange arenas hold it at the same offset) and its last block raises this rank's flag on every peer with the
 // join's new sequence number; the consuming kernel waits, bounded, until every peer's flag has reached this
-// rank's own sequence number before it reads the vector.  Plain peer stores and loads only.
+// rank's own sequence number before it reads the vector.  Plain peer stores and loads only.  The descriptors live
+// in device memory (a session writes them once when its peers are attached); kernels take pointers to them.
 constexpr int kMaxPeers = 8;
 struct JoinOut {
   char* base[kMaxPeers];   // every rank's exchange arena as mapped here (base[rank] is this rank's own)
@@ -97,8 +98,8 @@ struct GemvArgs {
   float pro_eps;
   // one-column plain products of a row-sharded session: wait for join_in before reading pro_x or the planes,
   // and / or write the f32 rows (ldy == 1, first matrix only) to every rank and raise join_out
-  JoinIn join_in;
-  JoinOut join_out;
+  const JoinIn* join_in;     // device memory; null: none
+  const JoinOut* join_out;   // device memory; null: none
   uint8_t* tc_ws;        // workspace of the many-column tensor-core kernel (null: that kernel is not used)
   size_t tc_ws_bytes;
   int tc_ws_reuse;       // the previous many-column Q4_K product of this stream used the same planes, K, columns and col0
@@ -158,7 +159,7 @@ cudaError_t launch_rope_store(float* q, const float* k, const float* v, const fl
                               const int* pos_dev, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox,
                               __half* kcache, __half* vcache, int64_t cache_head_stride, cudaStream_t st);
 // join: the product of this rank's n elements (a multiple of 256) goes, quantized to Q8_K, into every rank's planes
-cudaError_t launch_swiglu_join(const float* gate, const float* up, int n, const JoinOut& join, cudaStream_t st);
+cudaError_t launch_swiglu_join(const float* gate, const float* up, int n, const JoinOut* join_dev, cudaStream_t st);
 cudaError_t launch_swiglu(const float* gate, const float* up, int n, float* out, int family, ActPlanesMut planes,
                           cudaStream_t st);
 cudaError_t launch_embed_row(int type, const uint8_t* table, int64_t row_bytes, const int* token_dev, float* dst, int K,
@@ -303,7 +304,7 @@ struct FlashArgs {
   // cache planes and the matching query heads, and tokens_dev[i] is its token count; 0: one sequence
   int kv_heads_per_seq;
   int dst_seqs;          // > 1: dst is {heads_per_seq * d, dst_seqs} with the sequence index fastest (a product's activation layout)
-  JoinOut join_out;      // split-KV merge step (world > 1): this rank's heads, quantized to Q8_K, go into every rank's planes
+  const JoinOut* join_out;   // device memory or null; split-KV merge step: this rank's heads, quantized to Q8_K, go into every rank's planes
 };
 // out_family 1 / 2: the merge step also writes the result quantized (Q8_K / Q8_0 planes, one column) for the
 // matrix product that consumes it; only when flash_merge_can_quantize(a)

@@ -95,7 +95,10 @@ struct emelb_llama {
   ActPlanesMut attn_planes{}, ffn_planes{};   // Q8_K planes of the joined attention context / SwiGLU product (in the arena)
   char* peer_base[kMaxPeers] = {};
   bool peers_attached = false;
-  bool fused_joins = true;    // peers attached: joins inside the producing / consuming kernels where a layer qualifies
+  bool fused_joins = true;
+  // descriptors of the fused joins in device memory, written when the peers are attached: [join id] (0 unused)
+  JoinOut* join_out_dev = nullptr;
+  JoinIn* join_in_dev = nullptr;    // peers attached: joins inside the producing / consuming kernels where a layer qualifies
   cudaGraphExec_t graphs[MODE_COUNT] = {nullptr, nullptr, nullptr};
   int graph_attention_mode[MODE_COUNT] = {-1, -1, -1};
   int launches_per_token = 0;          // of the argmax step
@@ -310,41 +313,12 @@ struct Enqueue {
   // ---- joins fused into the kernels either side of them (peers attached).  One flag row, sequence counter and
   // block counter per join of a layer; row 0 belongs to the stand-alone join kernel.
   enum JoinId { J_NONE = 0, J_ATTN = 1, J_HIDDEN_A = 2, J_FFN = 3, J_HIDDEN_B = 4 };
-  JoinOut join_out(int id, const void* first) const {
-    JoinOut j{};
-    if (id == J_NONE) return j;
-    for (int g = 0; g < s->G; ++g) j.base[g] = s->peer_base[g];
-    j.out_offset = first ? static_cast<const char*>(first) - s->arena : 0;
-    j.flag_offset = (unsigned)(s->flags_off + 32 * (size_t)id);
-    j.seq = reinterpret_cast<unsigned*>(s->arena + s->seq_off) + id;
-    j.done = reinterpret_cast<int*>(s->arena + s->seq_off + 64) + id;
-    j.world = s->G;
-    j.rank = s->rank;
-    return j;
-  }
-  // the producer quantizes its interval (elems_per_rank, a multiple of 256) into every rank's planes
-  JoinOut join_out_planes(int id, const ActPlanesMut& pl, size_t elems_per_rank) const {
-    JoinOut j = join_out(id, nullptr);
-    j.qs_offset = reinterpret_cast<const char*>(pl.qs) - s->arena;
-    j.bsums_offset = reinterpret_cast<const char*>(pl.bsums) - s->arena;
-    j.d_offset = reinterpret_cast<const char*>(pl.d) - s->arena;
-    j.first_block = (int)((size_t)s->rank * elems_per_rank / QK_K);
-    return j;
-  }
-  JoinIn join_in(int id) const {
-    JoinIn j{};
-    if (id == J_NONE) return j;
-    j.flags = reinterpret_cast<const unsigned*>(s->arena + s->flags_off + 32 * (size_t)id);
-    j.seq = reinterpret_cast<const unsigned*>(s->arena + s->seq_off) + id;
-    j.world = s->G;
-    j.rank = s->rank;
-    j.wait_ns = s->c->peer_wait_ns;
-    return j;
-  }
+  const JoinOut* join_out(int id) const { return id == J_NONE || !s->join_out_dev ? nullptr : s->join_out_dev + id; }
+  const JoinIn* join_in(int id) const { return id == J_NONE || !s->join_in_dev ? nullptr : s->join_in_dev + id; }
   // whether every join of layer l can run inside its neighbours: the split-KV merge step produces the attention
   // context, and every product of the layer takes the streaming kernel with the quantization in its prologue
   bool layer_joins_fusable(int l) const {
-    if (s->G <= 1 || !s->peers_attached || !s->fused_joins || s->c->attention_mode != 0) return false;
+    if (s->G <= 1 || !s->peers_attached || !s->join_out_dev || !s->fused_joins || s->c->attention_mode != 0) return false;
     const emelb_llama_config& c = s->cfg;
     const Layer& w = s->layers[l];
     const int64_t q_l = (int64_t)(c.n_head / s->G) * c.head_dim;
@@ -370,7 +344,7 @@ struct Enqueue {
     a.ldy = 1;
     a.residual = residual;
     a.join_in = join_in(in);
-    a.join_out = join_out(out, y);
+    a.join_out = join_out(out);   // the descriptor's offset is this rank's interval of the hidden vector (== y)
     a.sched = s->c->next_sched();
     a.status = s->c->status_word();
     a.pdl = s->c->pdl & 1;
@@ -451,7 +425,7 @@ struct Enqueue {
   void attention(int layer, int out_family, int out_join = 0) {
     const emelb_llama_config& c = s->cfg;
     FlashArgs a = flash_args(layer);
-    if (out_join) a.join_out = join_out_planes(out_join, s->attn_planes, (size_t)a.heads * a.head_dim);
+    a.join_out = join_out(out_join);
     if (s->c->attention_mode == 0 && flash_split_supported(a)) {
       const bool fuse = s->G == 1 && flash_merge_can_quantize(a);
       check(launch_flash_decode(a, s->c->sm_count, st, &launches, fuse ? out_family : 0, planes()));
@@ -766,7 +740,7 @@ struct Enqueue {
         s->planes_src = s->ffn;
         s->planes_family = family_of(w.down.type);
       } else if (fj) {
-        check(launch_swiglu_join(s->gate, s->up, (int)ff_l, join_out_planes(J_FFN, s->ffn_planes, ff_l), st));
+        check(launch_swiglu_join(s->gate, s->up, (int)ff_l, join_out(J_FFN), st));
         s->planes_src = nullptr;
       } else {
         // the product is quantized after the join, over the full vector
@@ -1406,6 +1380,40 @@ uint32_t emelb_llama_exchange_attach(emelb_llama* s, const uint8_t* handles, uin
     void* p = nullptr;
     if (!ctx_cuda_ok(s->c, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess))) return EMELB_INTERNAL_ERROR;
     s->peer_base[g] = static_cast<char*>(p);
+  }
+  // descriptors of the joins that run inside kernels: one flag row, sequence counter and block counter per join of
+  // a layer (row 0 belongs to the stand-alone join kernel)
+  {
+    const emelb_llama_config& c = s->cfg;
+    const size_t q_l = (size_t)(c.n_head / s->G) * c.head_dim, embd_l = (size_t)c.n_embd / s->G, ff_l = (size_t)c.n_ff / s->G;
+    JoinOut jo[5] = {};
+    JoinIn ji[5] = {};
+    for (int id = 1; id <= 4; ++id) {
+      for (int g = 0; g < s->G; ++g) jo[id].base[g] = s->peer_base[g];
+      jo[id].flag_offset = (unsigned)(s->flags_off + 32 * (size_t)id);
+      jo[id].seq = reinterpret_cast<unsigned*>(s->arena + s->seq_off) + id;
+      jo[id].done = reinterpret_cast<int*>(s->arena + s->seq_off + 64) + id;
+      jo[id].world = s->G;
+      jo[id].rank = s->rank;
+      ji[id].flags = reinterpret_cast<const unsigned*>(s->arena + s->flags_off + 32 * (size_t)id);
+      ji[id].seq = jo[id].seq;
+      ji[id].world = s->G;
+      ji[id].rank = s->rank;
+      ji[id].wait_ns = s->c->peer_wait_ns;
+    }
+    auto planes_of = [&](JoinOut& j, const ActPlanesMut& pl, size_t per_rank) {
+      j.qs_offset = reinterpret_cast<const char*>(pl.qs) - s->arena;
+      j.bsums_offset = reinterpret_cast<const char*>(pl.bsums) - s->arena;
+      j.d_offset = reinterpret_cast<const char*>(pl.d) - s->arena;
+      j.first_block = (int)((size_t)s->rank * per_rank / QK_K);
+    };
+    planes_of(jo[1], s->attn_planes, q_l);                                        // J_ATTN
+    planes_of(jo[3], s->ffn_planes, ff_l);                                        // J_FFN
+    jo[2].out_offset = jo[4].out_offset = (int64_t)(reinterpret_cast<char*>(s->hidden + s->rank * embd_l) - s->arena);   // J_HIDDEN_A / _B
+    bool ok = s->join_out_dev || (dev_alloc(s, (void**)&s->join_out_dev, sizeof jo) && dev_alloc(s, (void**)&s->join_in_dev, sizeof ji));
+    ok = ok && ctx_cuda_ok(s->c, cudaMemcpy(s->join_out_dev, jo, sizeof jo, cudaMemcpyHostToDevice)) &&
+         ctx_cuda_ok(s->c, cudaMemcpy(s->join_in_dev, ji, sizeof ji, cudaMemcpyHostToDevice));
+    if (!ok) return EMELB_INTERNAL_ERROR;
   }
   s->peers_attached = true;
   for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;   // captured steps hold the NCCL joins

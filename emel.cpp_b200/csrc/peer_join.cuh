@@ -5,15 +5,6 @@
 
 namespace emelb {
 
-// base[g] for a runtime g without indexing the kernel parameter dynamically
-__device__ __forceinline__ char* join_base(const JoinOut& j, int g) {
-  char* b = nullptr;
-#pragma unroll
-  for (int i = 0; i < kMaxPeers; ++i)
-    if (g == i) b = j.base[i];
-  return b;
-}
-
 // One warp: the Q8_K block it has just quantized (q8_k_block_warp's outputs) goes into every rank's planes of the
 // joined vector, at 256-block `blk` of that vector.
 __device__ __forceinline__ void join_store_q8_k_block(const JoinOut& j, int blk, int lane, uint32_t lo, uint32_t hi, int bsum16,
