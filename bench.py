@@ -139,8 +139,8 @@ def max_over_ranks(x, world, device):
 def gemv_spec(args):
     import emel_cpp_b200 as eb
     if args.workload == "gemv_q4_k":
-        t, k, m, n = eb.Q4_K, args.cols or 4096, args.rows or 4096, 1
-        name = f"cfg1: Q4_K {m}x{k} mat-vec, x~N(0,1) -> Q8_K"
+        t, k, m, n = eb.Q4_K, args.cols or 4096, args.rows or 4096, args.ncols
+        name = f"cfg1: Q4_K {m}x{k} mat-vec, x~N(0,1) -> Q8_K" + (f", token batch {n}" if n > 1 else "")
     else:
         t, k, m, n = eb.Q8_0, 4096, 14336, args.ncols
         name = f"cfg2: Q8_0 14336x4096, token batch {n}"
@@ -1048,14 +1048,14 @@ def run_decode(args):
                                              "same_tokens_as_launch_chain": list(ids1) == res["ids"]}
             assert sess.set_step_mode(0)
         if world > 1 and shard and peer_joins:
-            # the same session with one join kernel per join instead of the joins inside the neighbouring kernels
-            assert sess.set_join_fusion(False)
+            # the same session with the joins inside the neighbouring kernels instead of one join kernel each
+            assert sess.set_join_fusion(True)
             w_ids = sess.generate(int(prompt[-1]), prompt_len - 1, warmup)
             ms_j, ids_j = timed_region(lambda: sess.generate(int(w_ids[-1]), prompt_len - 1 + warmup, steps))
-            extras["join_kernels"] = {"tok_s": round(steps / (ms_j * 1e-3), 2), "kernel_launches_per_token": sess.launches_per_token(),
-                                      "same_tokens": list(ids_j) == res["ids"],
-                                      "note": "one peer-store join kernel per join, products quantize after the join"}
-            assert sess.set_join_fusion(True)
+            extras["joins_in_kernels"] = {"tok_s": round(steps / (ms_j * 1e-3), 2), "kernel_launches_per_token": sess.launches_per_token(),
+                                          "same_tokens": list(ids_j) == res["ids"],
+                                          "note": "producers push their interval (f32 rows or Q8_K planes) and raise a flag, consumers wait in their prologue"}
+            assert sess.set_join_fusion(False)
         if world > 1 and shard:
             # beside the headline: N independent replicas of the same model (no collective), and configuration 5
             # (70B shape) row-sharded over the same N GPUs with a shortened prompt
@@ -1097,7 +1097,7 @@ def run_decode(args):
                    "l2_policy": f"inputs larger than L2: {weight_bytes * (world if shard else 1) / 1e9:.2f} GB of weights streamed per token",
                    "parallelism": "single GPU" if world == 1 else (
                        f"one sequence, matrices row-sharded over {world} GPUs, 4 joins of f32 row intervals per layer "
-                       f"({'peer stores over NVLink from inside the producing kernels, the consuming product waits on flags' if peer_joins else 'NCCL all-gather'}; "
+                       f"({'peer stores over NVLink, one kernel per join' if peer_joins else 'NCCL all-gather'}; "
                        "the prompt's batch joins are NCCL all-gathers)" if shard
                        else f"{world} independent replicas (one sequence per GPU), no collective"),
                    "kernel_launches_per_token": res["launches"],

@@ -95,7 +95,9 @@ struct emelb_llama {
   ActPlanesMut attn_planes{}, ffn_planes{};   // Q8_K planes of the joined attention context / SwiGLU product (in the arena)
   char* peer_base[kMaxPeers] = {};
   bool peers_attached = false;
-  bool fused_joins = true;
+  // peers attached: joins inside the producing / consuming kernels where a layer qualifies.  Opt-in: measured equal to
+  // one join kernel each on 2 GPUs and 10 % slower on 4
+  bool fused_joins = false;
   // descriptors of the fused joins in device memory, written when the peers are attached: [join id] (0 unused)
   JoinOut* join_out_dev = nullptr;
   JoinIn* join_in_dev = nullptr;    // peers attached: joins inside the producing / consuming kernels where a layer qualifies
