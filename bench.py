@@ -1205,7 +1205,18 @@ def cpu_baseline_decode(sh, out_type, budget_s=8.0):
     assert dec.lib.mul_mat(dec.head_op, **dec.kw)
     t_head = time.perf_counter() - t0
     sec = sh["n_layer"] * t_layer + t_head
+    # the serial route beside it: one kernel actor, one core (two layers and the head's share, scaled)
+    one_core = None
+    if dec.kind == "reference" and lanes > 1:
+        d1 = CpuDecoder(sh, out_type, 1, sh["prompt"])
+        d1.layer()
+        t0 = time.perf_counter()
+        d1.layer()
+        t1 = time.perf_counter() - t0
+        one_core = {"value": round(1.0 / (sh["n_layer"] * t1 + t_head * lanes), 4), "unit": "tok/s", "cores": 1,
+                    "sample": "one layer on one thread x the layer count + the output projection's 8-lane time x 8"}
     return {"value": round(1.0 / sec, 4), "unit": "tok/s", "cores": lanes if dec.kind == "reference" else 1, "kind": dec.kind,
+            "one_core": one_core,
             "sample": f"mean of {reps} layers (7 mat-vecs + attention over {sh['prompt']} tokens each) x {sh['n_layer']} layers + one "
                       f"output projection; AVX2/FMA route, mat-vecs row-sliced over {lanes} threads, attention single-threaded "
                       "as in the reference"}
