@@ -965,8 +965,14 @@ cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* g
   // few rows: smaller CTAs, so that every SM gets about the same number of 4-row tasks
   const int ntasks = (a.M + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE + (a.M2 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE +
                      (a.M3 + ROWS_PER_STAGE - 1) / ROWS_PER_STAGE;
-  if (ntasks >= 8 * 3 * sm_count || ARGMAX) return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
+  // With the normalisation in the prologue every CTA normalises and quantizes the whole vector before its first
+  // product: eight warps share that work, whatever the task count (with two-warp CTAs the grouped Q/K/V launch of
+  // the 8B shape spent half its time there: the decode step went from 441 to 468 tok/s with this rule)
+  const bool norm_prologue = a.pro_x && a.pro_w;
+  if (ntasks >= 8 * 3 * sm_count || ARGMAX || (norm_prologue && ntasks >= 4 * 3 * sm_count))
+    return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
   if (ntasks >= 4 * 3 * sm_count) return launch3<T, 1, 4, kWarpsPerSm / 4, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
+  if (norm_prologue) return launch3<T, 2, 8, kLight ? 2 : 1, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
   // about one task per warp: keep the whole row group of a warp in flight (2 chunks), or a deeper ring for long rows
   if (a.K / CHUNK >= 4) return launch3<T, 4, 2, kLight ? 4 : 3, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
   return launch3<T, 2, 2, kLight ? 8 : 4, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
