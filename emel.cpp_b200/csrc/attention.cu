@@ -87,6 +87,21 @@ __global__ void __launch_bounds__(256) flash_merge_kernel(const FlashArgs a, Act
     const int hps = a.heads / a.dst_seqs, hg = h0 + hl;
     const int seq = hg / hps, hloc = hg - seq * hps;
     a.dst[((size_t)hloc * D + d) * a.dst_seqs + seq] = o;
+    if constexpr (FAMILY == 1) {
+      // the CTA's 256 values are one Q8_K block of that sequence's column (heads_per_seq * D is a multiple of 256)
+      s_out[threadIdx.x] = o;
+      __syncthreads();
+      if (warp == 0) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = s_out[8 * lane + i];
+        uint32_t lo, hi; int bs; float dq;
+        q8_k_block_warp(v, lane, lo, hi, bs, dq);
+        const int col = (h0 / hps), blk = (h0 - col * hps) * D / QK_K;
+        q8_k_store_planes(planes, col, hps * D, blk, lane, lo, hi, bs, dq);
+      }
+    }
+    return;
   } else {
     a.dst[(size_t)h0 * D + threadIdx.x] = o;
   }

@@ -324,6 +324,27 @@ rms_norm_quant_cols_kernel(const float* __restrict__ x, const float* __restrict_
   }
 }
 
+// SwiGLU of a few columns, quantized for the down projection in the same launch: one warp per (256-feature block,
+// column), the lane's 8 elements computed from gate and up and quantized to Q8_K
+__global__ void __launch_bounds__(256)
+swiglu_quant_cols_kernel(const float* __restrict__ gate, const float* __restrict__ up, int K, int B, ActPlanesMut planes) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int nblk = K / QK_K;
+  if (item >= nblk * B) return;
+  const int col = item % B, blk = item / B;
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t o = (int64_t)(blk * QK_K + 8 * lane + i) * B + col;
+    const float g = gate[o];
+    v[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf_exact(-g))), up[o]);
+  }
+  uint32_t lo, hi; int bs; float dq;
+  q8_k_block_warp(v, lane, lo, hi, bs, dq);
+  q8_k_store_planes(planes, col, K, blk, lane, lo, hi, bs, dq);
+}
+
 // thread = (token j fastest, rotation pair or copied element, head)
 __global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, const float* __restrict__ v,
                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pos0, int B,
@@ -668,6 +689,13 @@ cudaError_t launch_rope_store_seqs(const float* q, const float* k, const float* 
   rope_store_seqs_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(q, k, v, cos_t, sin_t, positions, B, n_head, n_head_kv,
                                                                          head_dim, rot_dim, neox, q_out, kcache, vcache, seq_stride,
                                                                          cache_head_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_quant_cols(const float* gate, const float* up, int K, int B, ActPlanesMut planes, cudaStream_t st) {
+  if (K % QK_K != 0 || B < 1) return cudaErrorInvalidValue;
+  const int items = K / QK_K * B;
+  swiglu_quant_cols_kernel<<<(items + 7) / 8, 256, 0, st>>>(gate, up, K, B, planes);
   return cudaGetLastError();
 }
 

@@ -446,7 +446,10 @@ __global__ void __launch_bounds__(kThreads16, 1) gemm_q4k_mma16_kernel(const Gem
       for (int e = 0; e < 2; ++e) {
         const int o = tid + e * kThreads16;
         const int row = ctile.row0 + (o >> 4), col = o & 15;
-        if (row < ctile.M && col < ncols) ctile.y[(int64_t)row * p.ldy + p.col0 + col] = acc[e];
+        if (row < ctile.M && col < ncols) {
+          const int64_t o16 = (int64_t)row * p.ldy + p.col0 + col;
+          ctile.y[o16] = p.residual ? __fadd_rn(p.residual[o16], acc[e]) : acc[e];   // the residual belongs to the first matrix
+        }
       }
     }
   }
@@ -488,8 +491,9 @@ cudaError_t launch_nt(const GemvArgs& a, int ncols, cudaStream_t st) {
 
 bool gemm_q4k_mma_supported(int type, const GemvArgs& a, int ncols) {
   if (type != T_Q4_K || ncols < kGemmMmaMinCols || ncols >= kGemmTcMinCols) return false;
-  if (a.K % kStageK != 0 || a.residual || a.pro_x || a.rope_cos || !a.act.bsums) return false;
+  if (a.K % kStageK != 0 || a.pro_x || a.rope_cos || !a.act.bsums) return false;
   const bool grouped = a.W2 || a.W3;
+  if (a.residual && (grouped || ncols > 16 || a.K % kStageK16 != 0)) return false;        // the 16-column kernel adds it on store
   if (grouped && (ncols > 16 || a.K % kStageK16 != 0)) return false;   // several matrices: the 16-column kernel only
   for (const uint8_t* w : {a.W, a.W2, a.W3})
     if (reinterpret_cast<uintptr_t>(w) % 16 != 0) return false;

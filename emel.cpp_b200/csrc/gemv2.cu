@@ -969,6 +969,11 @@ cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* g
   // product: eight warps share that work, whatever the task count (with two-warp CTAs the grouped Q/K/V launch of
   // the 8B shape spent half its time there: the decode step went from 441 to 468 tok/s with this rule)
   const bool norm_prologue = a.pro_x && a.pro_w;
+  if constexpr (kLight && !ARGMAX) {
+    // many tasks and a long vector: one CTA of 32 warps per SM normalises once where four CTAs of eight warps did it
+    // four times (70B shape, K = 8192: 84.8 -> 86.0 tok/s; at K = 4096 the eight-warp CTAs are faster, 469 against 458)
+    if (norm_prologue && ntasks >= 32 * sm_count && a.K >= 8192) return launch3<T, 1, 32, 1, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
+  }
   if (ntasks >= 8 * 3 * sm_count || ARGMAX || (norm_prologue && ntasks >= 4 * 3 * sm_count))
     return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
   if (ntasks >= 4 * 3 * sm_count) return launch3<T, 1, 4, kWarpsPerSm / 4, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);

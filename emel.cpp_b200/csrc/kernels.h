@@ -186,6 +186,8 @@ cudaError_t launch_rope_store_seqs(const float* q, const float* k, const float* 
                                    cudaStream_t st);
 // rms_norm of every column of x {K, B} and its Q8_K planes in one launch (a few columns: one CTA each)
 cudaError_t launch_rms_norm_quant_cols(const float* x, const float* w, float eps, int K, int B, ActPlanesMut planes, cudaStream_t st);
+// SwiGLU of gate, up {K, B} quantized to Q8_K planes in one launch (a few columns)
+cudaError_t launch_swiglu_quant_cols(const float* gate, const float* up, int K, int B, ActPlanesMut planes, cudaStream_t st);
 // per column of x {rows, B}: the highest value and, on ties, the lowest row (src/emel/kernel/detail.hpp:3720-3723)
 constexpr int kArgmaxColumnParts = 256;
 cudaError_t launch_argmax_columns(const float* x, int rows, int B, float* part_val, int* part_idx, int* out_idx, cudaStream_t st);

@@ -464,7 +464,9 @@ struct Enqueue {
   void gather(float* full, size_t count_per_rank) { gather_bytes(full, count_per_rank * sizeof(float)); }
 
   // y {w.M, B} = w x quantized(x {w.K, B}); the Q4_K products of 32 and more tokens run on the tensor cores
-  void batch_matmul(const Tensor& w, const float* x, float* y, int B, bool same_input = false) {
+  // residual_inplace: y += w x where the product's kernel can add on store (y is then both addend and result);
+  // returns whether it did -- otherwise y holds the bare product and the caller adds
+  bool batch_matmul(const Tensor& w, const float* x, float* y, int B, bool same_input = false, bool residual_inplace = false) {
     // same_input: the planes still hold x quantized for this family (the previous product read the same x)
     bool requantized = false;
     if (!same_input || batch_family != family_of(w.type)) {
@@ -496,7 +498,14 @@ struct Enqueue {
     a.part_idx = s->c->part_idx;
     a.best_val = s->c->best_val;
     a.best_idx = s->c->best_idx;
+    bool added = false;
+    if (residual_inplace) {
+      a.residual = y;
+      added = gemm_q4k_mma_supported(w.type, a, B);
+      if (!added) a.residual = nullptr;
+    }
     check(launch_gemv(w.type, a, B, false, s->c->sm_count, st, &launches));
+    return added;
   }
 
   // up to three matrices of one type and K against the same batch (Q, K, V or gate, up): one launch where the
@@ -620,6 +629,27 @@ struct Enqueue {
       launches += 2;
       return false;
     };
+    // b_hidden += w x: unsharded, the product's kernel adds on store where it can; else the product goes to this
+    // rank's rows of b_y, the rows are joined, and one kernel adds
+    auto residual_product = [&](const Tensor& w, const float* x, float* y_rows, int cols, bool quantized) {
+      if (G == 1) {
+        GemvArgs probe{};
+        probe.W = w.dev;
+        probe.row_bytes = w.row_bytes;
+        probe.M = w.M;
+        probe.K = w.K;
+        probe.act = planes_view(planes(), w.type, w.K);
+        probe.residual = s->b_hidden;
+        if (gemm_q4k_mma_supported(w.type, probe, cols)) {
+          batch_matmul(w, x, s->b_hidden, cols, quantized, true);
+          return;
+        }
+      }
+      batch_matmul(w, x, y_rows, cols, quantized);
+      batch_gather(s->b_y, embd_l, cols);
+      check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * cols, st));
+      ++launches;
+    };
     check(launch_embed_rows(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, tok, B, s->b_hidden, c.n_embd, st));
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
@@ -649,25 +679,33 @@ struct Enqueue {
       a.dst_seqs = B;
       a.part_acc = s->b_part_acc;
       a.part_ml = s->b_part_ml;
-      check(launch_flash_decode(a, s->c->sm_count, st, &launches, 0, planes()));
+      // unsharded with K-quant weights: the merge step leaves each sequence's context quantized for Wo, and the
+      // products add the residual on store
+      const bool attn_q = G == 1 && family_of(w.wo.type) == 1 && q_l % 256 == 0;
+      check(launch_flash_decode(a, s->c->sm_count, st, &launches, attn_q ? 1 : 0, planes()));
+      if (attn_q) {
+        batch_family = 1;
+        batch_tc_tiled = false;
+      }
       batch_gather(s->b_attn, q_l, B);
-      batch_matmul(w.wo, s->b_attn, y_mine, B);
-      batch_gather(s->b_y, embd_l, B);
-      check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
-      ++launches;
+      residual_product(w.wo, s->b_attn, y_mine, B, attn_q);
       {
         const bool quantized = w.up.type == w.gate.type ? norm(w.ffn_norm, w.gate.type) : (norm(w.ffn_norm, T_F32), false);
         const Tensor* ws[2] = {&w.gate, &w.up};
         float* ys[2] = {s->b_gate, s->b_up};
         batch_matmul_group(ws, ys, 2, s->b_norm, B, quantized);
       }
-      check(launch_swiglu(s->b_gate, s->b_up, (int)(ff_l * b), ffn_mine, 0, planes(), st));
+      const bool ffn_q = G == 1 && family_of(w.down.type) == 1 && B <= 64;
+      if (ffn_q) {
+        check(launch_swiglu_quant_cols(s->b_gate, s->b_up, c.n_ff, B, planes(), st));
+        batch_family = 1;
+        batch_tc_tiled = false;
+      } else {
+        check(launch_swiglu(s->b_gate, s->b_up, (int)(ff_l * b), ffn_mine, 0, planes(), st));
+      }
       ++launches;
       batch_gather(s->b_ffn, ff_l, B);
-      batch_matmul(w.down, s->b_ffn, y_mine, B);
-      batch_gather(s->b_y, embd_l, B);
-      check(launch_add_inplace(s->b_hidden, s->b_y, (int64_t)c.n_embd * B, st));
-      ++launches;
+      residual_product(w.down, s->b_ffn, y_mine, B, ffn_q);
     }
     const bool quantized = norm(s->out_norm, s->output.type);
     batch_matmul(s->output, s->b_norm, s->b_logits + r * vocab_l * b, B, quantized);
