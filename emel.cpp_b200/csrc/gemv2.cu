@@ -973,6 +973,7 @@ cudaError_t launch3_cfg(const GemvArgs& a, int sm_count, cudaStream_t st, int* g
     // many tasks and a long vector: one CTA of 32 warps per SM normalises once where four CTAs of eight warps did it
     // four times (70B shape, K = 8192: 84.8 -> 86.0 tok/s; at K = 4096 the eight-warp CTAs are faster, 469 against 458)
     if (norm_prologue && ntasks >= 32 * sm_count && a.K >= 8192) return launch3<T, 1, 32, 1, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
+    if (norm_prologue && ntasks >= 32 * sm_count) return launch3<T, 1, 16, 2, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
   }
   if (ntasks >= 8 * 3 * sm_count || ARGMAX || (norm_prologue && ntasks >= 4 * 3 * sm_count))
     return launch3<T, 1, 8, kWarpsPerSm / 8, ARGMAX, 1, JOIN>(a, sm_count, st, grid_out);
