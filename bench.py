@@ -1047,8 +1047,9 @@ def run_decode(args):
                                              "kernel_launches_per_token": sess.launches_per_token(),
                                              "same_tokens_as_launch_chain": list(ids1) == res["ids"]}
             assert sess.set_step_mode(0)
-        if world > 1 and shard and peer_joins:
-            # the same session with the joins inside the neighbouring kernels instead of one join kernel each
+        if world > 1 and world <= 4 and shard and peer_joins:
+            # the same session with the joins inside the neighbouring kernels instead of one join kernel each (run on
+            # the rank counts this form has been validated on: 2 and 4)
             assert sess.set_join_fusion(True)
             w_ids = sess.generate(int(prompt[-1]), prompt_len - 1, warmup)
             ms_j, ids_j = timed_region(lambda: sess.generate(int(w_ids[-1]), prompt_len - 1 + warmup, steps))
