@@ -1178,8 +1178,16 @@ uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n, i
 namespace {
 
 // buffers of the batch step, sized for the session's sequence count
+bool free_owned(emelb_llama* s, void* p);
+
 bool reserve_sequences(emelb_llama* s) {
   if (s->seq_cap >= s->n_seq) return true;
+  // sized for fewer sequences before: release those buffers first
+  for (void* p : {(void*)s->b_qs, (void*)s->b_logits, (void*)s->b_part_acc, (void*)s->b_part_ml, (void*)s->b_out})
+    if (p) free_owned(s, p);
+  s->b_qs = s->b_logits = s->b_part_acc = s->b_part_ml = nullptr;
+  s->b_out = nullptr;
+  s->seq_cap = 0;
   const emelb_llama_config& c = s->cfg;
   const size_t b = (size_t)s->n_seq, q_dim = (size_t)c.n_head * c.head_dim;
   bool ok = true;
@@ -1285,6 +1293,23 @@ bool valid_batch(const emelb_llama* s, const int32_t* tokens, const int32_t* pos
   return true;
 }
 
+// the token-batch buffers were sized by an earlier, smaller batch: release them so that reserve_batch sizes them again
+void release_small_batch(emelb_llama* s, int need) {
+  if (s->batch_cap <= 0 || s->batch_cap >= need) return;
+  cudaStreamSynchronize(s->c->stream);
+  for (void* p : {(void*)s->batch_tokens, (void*)s->b_hidden, (void*)s->b_norm, (void*)s->b_y, (void*)s->b_q, (void*)s->b_attn,
+                  (void*)s->b_k, (void*)s->b_v, (void*)s->b_gate, (void*)s->b_up, (void*)s->b_ffn, (void*)s->b_partial})
+    if (p) free_owned(s, p);
+  s->batch_tokens = nullptr;
+  s->b_hidden = s->b_norm = s->b_y = s->b_q = s->b_attn = s->b_k = s->b_v = s->b_gate = s->b_up = s->b_ffn = nullptr;
+  s->b_partial = nullptr;
+  s->batch_cap = 0;
+  if (s->batch_graph) {
+    cudaGraphExecDestroy(s->batch_graph);
+    s->batch_graph = nullptr;
+  }
+}
+
 }  // namespace
 
 uint32_t emelb_llama_set_sequences(emelb_llama* s, int32_t n_seq) {
@@ -1329,6 +1354,7 @@ uint32_t emelb_llama_decode_batch(emelb_llama* s, const int32_t* tokens, const i
   emelb_ctx* c = s->c;
   cudaSetDevice(c->device);
   if (!batch_step_ok(s, n_seq)) return EMELB_UNSUPPORTED_OP;
+  release_small_batch(s, n_seq);
   if (!reserve_sequences(s) || !reserve_batch(s, batch_buffer_columns(s)) || s->batch_cap < n_seq) return EMELB_INTERNAL_ERROR;
   bool ok = write_batch_state(s, tokens, positions, n_seq);
   Enqueue e{s, c->stream};
@@ -1356,6 +1382,7 @@ uint32_t emelb_llama_generate_batch(emelb_llama* s, const int32_t* first_tokens,
   emelb_ctx* c = s->c;
   cudaSetDevice(c->device);
   if (!batch_step_ok(s, n_seq)) return EMELB_UNSUPPORTED_OP;
+  release_small_batch(s, n_seq);
   if (!reserve_sequences(s) || !reserve_batch(s, batch_buffer_columns(s)) || s->batch_cap < n_seq) return EMELB_INTERNAL_ERROR;
   bool ok = write_batch_state(s, first_tokens, start_positions, n_seq);
   cudaGraphExec_t g = ok ? batch_step_graph(s, n_seq) : nullptr;

@@ -94,3 +94,22 @@ def test_batch_requests_are_checked(be, port):
         assert list(sess.decode_batch([1, 2], [0, 0])) == [sess.decode_batch([1], [0])[0], sess.decode_batch([2], [0])[0]]
     finally:
         sess.close()
+
+
+def test_buffers_grow_with_the_sequence_count(be, port):
+    """Batch buffers sized by an earlier, smaller prompt batch or sequence count are sized again."""
+    sess, cpu = build_model(be, port, TINY, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K}, seed=3)
+    cpu.close()
+    try:
+        assert sess.set_prefill_batch(4)
+        assert sess.prefill([5, 6, 7, 8, 9, 10], 0)          # sizes the prompt path's buffers for 4 columns
+        assert sess.set_sequences(2)
+        first, pos = fill_sequences(sess, TINY, 2, seed=8)
+        two = sess.generate_batch(first, pos, 3)
+        assert sess.set_sequences(9)                          # clears the caches: fill again, now 9 sequences
+        first9, pos9 = fill_sequences(sess, TINY, 9, seed=8)
+        assert first9[:2] == first and pos9[:2] == pos
+        nine = sess.generate_batch(first9, pos9, 3)
+        assert np.array_equal(nine[:, :2], two)
+    finally:
+        sess.close()
