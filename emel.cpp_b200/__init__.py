@@ -38,6 +38,15 @@ class Op(C.Structure):
                 ("index_out", C.POINTER(C.c_int32))]
 
 
+class HeadRangeRequest(C.Structure):
+    """emelb_head_range_request: kernel::attention's head-range event (src/emel/kernel/attention/events.hpp:18-31)."""
+    _fields_ = [("query", C.c_void_p), ("query_count", C.c_uint64), ("key_cache", C.c_void_p), ("key_count", C.c_uint64),
+                ("value_cache", C.c_void_p), ("value_count", C.c_uint64), ("output", C.c_void_p), ("output_count", C.c_uint64),
+                ("layer_offset", C.c_uint64), ("hidden_dim", C.c_int32), ("head_dim", C.c_int32), ("head_begin", C.c_int32),
+                ("head_end", C.c_int32), ("position_capacity", C.c_int32), ("physical_begin", C.c_int32),
+                ("valid_positions", C.c_int32)]
+
+
 class TensorState(C.Structure):
     _fields_ = [("lifecycle_state", C.c_uint8), ("buffer", C.c_void_p), ("buffer_bytes", C.c_uint64),
                 ("host", C.c_void_p), ("tensor_type", C.c_int32)]
@@ -88,6 +97,8 @@ _SIGNATURES = {
     "emelb_rms_norm": [_P, C.POINTER(Op)],
     "emelb_rope": [_P, C.POINTER(Op)],
     "emelb_glu": [_P, C.POINTER(Op)],
+    "emelb_attention_head_range_can_run": [C.POINTER(HeadRangeRequest)],
+    "emelb_attention_head_range": [_P, C.POINTER(HeadRangeRequest)],
     "emelb_quantize": [_P, C.POINTER(View), C.POINTER(View)],
     "emelb_dequantize": [_P, C.POINTER(View), C.POINTER(View)],
     "emelb_graph_begin": [_P],
@@ -206,6 +217,20 @@ def flash_op(q, kc, vc, dst, head_dim, heads, kv_heads, tokens, capacity, scale=
     return op
 
 
+def head_range_request(query, key_cache, value_cache, output, layer_offset, hidden_dim, head_dim, head_begin, head_end,
+                       position_capacity, physical_begin, valid_positions, counts=None) -> "HeadRangeRequest":
+    """kernel::attention's head_range_request (src/emel/kernel/attention/events.hpp:18-31); counts default to the
+    arrays' element counts."""
+    r = HeadRangeRequest()
+    sizes = counts or [getattr(a, "size", 0) for a in (query, key_cache, value_cache, output)]
+    r.query, r.key_cache, r.value_cache, r.output = ptr(query), ptr(key_cache), ptr(value_cache), ptr(output)
+    r.query_count, r.key_count, r.value_count, r.output_count = sizes
+    r.layer_offset, r.hidden_dim, r.head_dim = layer_offset, hidden_dim, head_dim
+    r.head_begin, r.head_end, r.position_capacity = head_begin, head_end, position_capacity
+    r.physical_begin, r.valid_positions = physical_begin, valid_positions
+    return r
+
+
 def strided_view(data, t: int, ne, nb) -> View:
     """A view with explicit byte strides (any valid layout)."""
     v = View()
@@ -292,6 +317,9 @@ class Backend:
 
     def rope(self, op: Op) -> bool:
         return self._ret(lib().emelb_rope(self._h, C.byref(op)))
+
+    def attention_head_range(self, request: "HeadRangeRequest") -> bool:
+        return self._ret(lib().emelb_attention_head_range(self._h, C.byref(request)))
 
     def glu(self, op: Op) -> bool:
         return self._ret(lib().emelb_glu(self._h, C.byref(op)))

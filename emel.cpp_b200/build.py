@@ -23,6 +23,7 @@ SOURCES = {
     "token_kernel.cu": ["-fmad=false"],
     "synth.cu": [],
     "attention.cu": ["-fmad=false"],
+    "attention_bf16.cu": ["-fmad=false"],
     "prefill_attention.cu": [],
     "gemm_tc.cu": [],
     "gemm_q8_mma.cu": [],

@@ -917,6 +917,76 @@ uint32_t emelb_glu(emelb_ctx* c, const emelb_op* op) {
   return reject(c);
 }
 
+// ------------------------------------------------------------------ kernel::attention head-range event
+namespace {
+bool ranges_disjoint(const void* a, uint64_t a_bytes, const void* b, uint64_t b_bytes) {
+  const uintptr_t ab = reinterpret_cast<uintptr_t>(a), bb = reinterpret_cast<uintptr_t>(b);
+  if (ab > UINTPTR_MAX - a_bytes || bb > UINTPTR_MAX - b_bytes) return false;
+  return ab + a_bytes <= bb || bb + b_bytes <= ab;
+}
+// guard_request_shape_supported (src/emel/kernel/attention/guards.hpp:28-90)
+bool head_range_ok(const emelb_head_range_request& r) {
+  if (r.hidden_dim <= 0 || r.head_dim <= 0 || r.head_begin < 0 || r.head_end <= r.head_begin || r.position_capacity <= 0 ||
+      r.physical_begin < 0 || r.physical_begin >= r.position_capacity || r.valid_positions <= 0 ||
+      r.valid_positions > r.position_capacity)
+    return false;
+  const uint64_t hidden = (uint64_t)r.hidden_dim, hd = (uint64_t)r.head_dim, cap = (uint64_t)r.position_capacity;
+  const uint64_t heads = (uint64_t)(r.head_end - r.head_begin), mx = UINT64_MAX;
+  if (cap > (mx - r.layer_offset) / hidden || heads > mx / hd || (uint64_t)r.head_end > hidden / hd) return false;
+  const uint64_t cache_required = r.layer_offset + cap * hidden, output_required = heads * hd;
+  if (hd > 8192 || cap > 8192 || !r.query || !r.key_cache || !r.value_cache || !r.output || r.query_count < hidden ||
+      r.key_count < cache_required || r.value_count < cache_required || r.output_count < output_required ||
+      reinterpret_cast<uintptr_t>(r.query) % alignof(float) != 0 || reinterpret_cast<uintptr_t>(r.key_cache) % alignof(uint16_t) != 0 ||
+      reinterpret_cast<uintptr_t>(r.value_cache) % alignof(uint16_t) != 0 || reinterpret_cast<uintptr_t>(r.output) % alignof(float) != 0 ||
+      hidden > mx / sizeof(float) || cache_required > mx / sizeof(uint16_t) || output_required > mx / sizeof(float))
+    return false;
+  const uint64_t qb = hidden * sizeof(float), cb = cache_required * sizeof(uint16_t), ob = output_required * sizeof(float);
+  return ranges_disjoint(r.output, ob, r.query, qb) && ranges_disjoint(r.output, ob, r.key_cache, cb) &&
+         ranges_disjoint(r.output, ob, r.value_cache, cb);
+}
+}  // namespace
+
+uint32_t emelb_attention_head_range_can_run(const emelb_head_range_request* r) {
+  return r && head_range_ok(*r) ? EMELB_OK : EMELB_INVALID_REQUEST;
+}
+
+uint32_t emelb_attention_head_range(emelb_ctx* c, const emelb_head_range_request* r) {
+  if (!c || !r) return EMELB_INVALID_REQUEST;
+  if (!head_range_ok(*r)) return reject(c);
+  cudaSetDevice(c->device);
+  const uint64_t hidden = (uint64_t)r->hidden_dim, cache_elems = r->layer_offset + (uint64_t)r->position_capacity * hidden;
+  const uint64_t qb = hidden * 4, cb = cache_elems * 2, ob = (uint64_t)(r->head_end - r->head_begin) * r->head_dim * 4;
+  auto up = [](uint64_t b) { return (b + 255) & ~uint64_t(255); };
+  const void* q = stage_in(c, r->query, qb, 0);
+  const void* k = stage_in(c, r->key_cache, cb, up(qb));
+  const void* v = stage_in(c, r->value_cache, cb, up(qb) + up(cb));
+  OutBinding out{};
+  if (!q || !k || !v || !bind_out(c, r->output, ob, 0, &out)) {
+    c->diag.rejected_dispatch_calls += 1;
+    return EMELB_UNSUPPORTED_OP;   // host caches larger than the staging area
+  }
+  HeadRangeArgs a{};
+  a.query = static_cast<const float*>(q);
+  a.key = static_cast<const uint16_t*>(k);
+  a.value = static_cast<const uint16_t*>(v);
+  a.output = static_cast<float*>(out.dev);
+  a.layer_offset = (size_t)r->layer_offset;
+  a.hidden_dim = r->hidden_dim;
+  a.head_dim = r->head_dim;
+  a.head_begin = r->head_begin;
+  a.head_end = r->head_end;
+  a.capacity = r->position_capacity;
+  a.physical_begin = r->physical_begin;
+  a.valid = r->valid_positions;
+  a.scale = 1.0f / std::sqrt((float)r->head_dim);
+  bool ok = cuda_ok(c, launch_head_range_attention(a, c->stream));
+  c->diag.kernel_launches += 1;
+  bool need_sync = false;
+  ok = ok && finish_out(c, out, &need_sync);
+  if (ok && need_sync) ok = cuda_ok(c, cudaStreamSynchronize(c->stream));
+  return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
+}
+
 // ------------------------------------------------------------------ quantize / dequantize
 uint32_t emelb_quantize(emelb_ctx* c, const emelb_view* src, const emelb_view* dst) {
   if (!c || !src || !dst || !src->data || !dst->data) return EMELB_INVALID_REQUEST;

@@ -313,6 +313,17 @@ struct FlashArgs {
 cudaError_t launch_flash_decode(const FlashArgs& a, int sm_count, cudaStream_t st, int* launches, int out_family,
                                 ActPlanesMut out_planes);
 bool flash_merge_can_quantize(const FlashArgs& a);
+// attention_bf16.cu: kernel::attention's head-range event (bf16 KV ring buffer, reference scalar arithmetic)
+struct HeadRangeArgs {
+  const float* query;
+  const uint16_t* key;
+  const uint16_t* value;
+  float* output;
+  size_t layer_offset;
+  int hidden_dim, head_dim, head_begin, head_end, capacity, physical_begin, valid;
+  float scale;   // 1 / sqrt(head_dim), computed on the host as the reference does
+};
+cudaError_t launch_head_range_attention(const HeadRangeArgs& a, cudaStream_t st);
 // score_ws: [heads][t_stride] f32 scratch; order 1 = scalar route, 2 = x86 AVX2 route
 cudaError_t launch_flash_reference_order(const FlashArgs& a, float* score_ws, int t_stride, int order, cudaStream_t st,
                                          int* launches);

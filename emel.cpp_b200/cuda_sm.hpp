@@ -17,6 +17,7 @@
 #include <cstdint>
 #include <cstring>
 
+#include "emel/kernel/attention/events.hpp"
 #include "emel/kernel/errors.hpp"
 #include "emel/kernel/events.hpp"
 
@@ -110,6 +111,31 @@ class sm {
   bool process_event(const ::emel::kernel::event::op_glu& ev) noexcept {
     const emelb_op op = detail::to_op(ev);
     return finish(emelb_glu(ctx_, &op));
+  }
+
+  // kernel::attention's head-range event (src/emel/kernel/attention/events.hpp:33-43): the result's `accepted`
+  // is what effect_execute_head_range / effect_reject_execute leave there
+  bool process_event(const ::emel::kernel::attention::event::execute& ev) noexcept {
+    const auto& r = ev.request;
+    emelb_head_range_request q{};
+    q.query = r.query.data();
+    q.query_count = r.query.size();
+    q.key_cache = r.key_cache.data();
+    q.key_count = r.key_cache.size();
+    q.value_cache = r.value_cache.data();
+    q.value_count = r.value_cache.size();
+    q.output = r.output.data();
+    q.output_count = r.output.size();
+    q.layer_offset = r.layer_offset;
+    q.hidden_dim = r.hidden_dim;
+    q.head_dim = r.head_dim;
+    q.head_begin = r.head_begin;
+    q.head_end = r.head_end;
+    q.position_capacity = r.position_capacity;
+    q.physical_begin = r.physical_begin;
+    q.valid_positions = r.valid_positions;
+    ev.result.accepted = finish(emelb_attention_head_range(ctx_, &q));
+    return ev.result.accepted;
   }
 
   // every other op event: no row in this backend

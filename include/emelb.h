@@ -253,6 +253,35 @@ EMELB_API uint32_t emelb_rope(emelb_ctx* ctx, const emelb_op* op);
  * EMELB_INVALID_REQUEST.  The decoder layer's SwiGLU lives in emelb_llama. ---- */
 EMELB_API uint32_t emelb_glu(emelb_ctx* ctx, const emelb_op* op);
 
+/* ---- kernel::attention's head-range event (src/emel/kernel/attention/events.hpp:18-31; the work is
+ * effect_execute_head_range, src/emel/kernel/attention/actions.hpp:15-96): attention of one query token over a
+ * bf16 KV ring buffer laid out [position][hidden_dim] per layer, for heads head_begin .. head_end-1 (no grouped
+ * heads: head h reads columns h*head_dim.. of both caches).  Per head: the query is rounded to bf16; the score of
+ * logical position p (physical row (physical_begin + p) mod position_capacity) is the f64 sum, in element order, of
+ * the f32 products k*q, rounded to f32 and multiplied by 1/sqrt(head_dim); rows outside the valid positions score
+ * -inf; a softmax over all position_capacity rows (max, expf, f64 sum in row order, weights times (float)(1/sum));
+ * the weights are rounded to bf16; and the output is the f64 sum over the valid positions, in logical order, of the
+ * f32 products v*weight, rounded to f32.  The arithmetic follows the reference's scalar route (its build without a
+ * global -mavx2: the oracle's build definition) bit for bit.
+ * Counts are element counts of the spans (request validation mirrors guard_request_shape_supported,
+ * src/emel/kernel/attention/guards.hpp:28-90, including the limits head_dim, position_capacity <= 8192 and the
+ * requirement that the output span overlaps none of the inputs).  Pointers may be host or device memory. ---- */
+typedef struct emelb_head_range_request {
+  const float* query;            /* hidden_dim floats */
+  uint64_t query_count;
+  const uint16_t* key_cache;     /* bf16 bits */
+  uint64_t key_count;
+  const uint16_t* value_cache;
+  uint64_t value_count;
+  float* output;                 /* (head_end - head_begin) * head_dim floats */
+  uint64_t output_count;
+  uint64_t layer_offset;         /* elements before this layer's rows in both caches */
+  int32_t hidden_dim, head_dim, head_begin, head_end, position_capacity, physical_begin, valid_positions;
+} emelb_head_range_request;
+/* pure guard: EMELB_OK or EMELB_INVALID_REQUEST */
+EMELB_API uint32_t emelb_attention_head_range_can_run(const emelb_head_range_request* request);
+EMELB_API uint32_t emelb_attention_head_range(emelb_ctx* ctx, const emelb_head_range_request* request);
+
 /* ---- the same attention for a batch of prompt tokens: query token j (of `batch`)
  * sits at position pos0 + j and attends to cache positions 0 .. pos0 + j.  The
  * reference walks a prompt through op_flash_attn_ext one token at a time

@@ -247,6 +247,16 @@ class Ref(_Lib):
     def can_run(self, code, op):
         return bool(self.f("can_run")(code, C.byref(op)))
 
+    def head_range_can_run(self, request):
+        fn = self.f("head_range_can_run")
+        fn.restype, fn.argtypes = C.c_int, [C.c_void_p]
+        return bool(fn(C.addressof(request)))
+
+    def head_range(self, request):
+        fn = self.f("head_range")
+        fn.restype, fn.argtypes = C.c_int, [C.c_void_p]
+        return bool(fn(C.addressof(request)))
+
     def rms_norm(self, op):
         return bool(self.f("rms_norm")(C.byref(op)))
 

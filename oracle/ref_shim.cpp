@@ -17,6 +17,8 @@
 #include <vector>
 
 #include "emel/gguf/loader/detail.hpp"
+#include "emel/kernel/attention/actions.hpp"
+#include "emel/kernel/attention/guards.hpp"
 #include "emel/kernel/x86_64/actions.hpp"
 
 #include "../include/emelb.h"
@@ -151,6 +153,42 @@ int ref_rope(const emelb_op* op) {
   if (p.mode == kd::rope_mode_norm) return kd::run_rope_as<false>(r) ? 1 : 0;
   if (p.mode == kd::rope_mode_neox) return kd::run_rope_as<true>(r) ? 1 : 0;
   return 0;
+}
+
+// ---- kernel::attention head-range event: the guard (src/emel/kernel/attention/guards.hpp:28-90) and the work
+//      (src/emel/kernel/attention/actions.hpp:15-96) on the actor's own context type
+namespace {
+static emel::kernel::attention::event::head_range_request to_head_range(const emelb_head_range_request& r) {
+  emel::kernel::attention::event::head_range_request q{};
+  q.query = std::span<const float>(r.query, r.query_count);
+  q.key_cache = std::span<const uint16_t>(r.key_cache, r.key_count);
+  q.value_cache = std::span<const uint16_t>(r.value_cache, r.value_count);
+  q.output = std::span<float>(r.output, r.output_count);
+  q.layer_offset = r.layer_offset;
+  q.hidden_dim = r.hidden_dim;
+  q.head_dim = r.head_dim;
+  q.head_begin = r.head_begin;
+  q.head_end = r.head_end;
+  q.position_capacity = r.position_capacity;
+  q.physical_begin = r.physical_begin;
+  q.valid_positions = r.valid_positions;
+  return q;
+}
+}  // namespace
+
+int ref_head_range_can_run(const emelb_head_range_request* r) {
+  return emel::kernel::attention::guard::guard_request_shape_supported(to_head_range(*r)) ? 1 : 0;
+}
+
+int ref_head_range(const emelb_head_range_request* r) {
+  namespace ka = emel::kernel::attention;
+  const auto q = to_head_range(*r);
+  if (!ka::guard::guard_request_shape_supported(q)) return 0;
+  static thread_local ka::action::context ctx;
+  ka::event::dispatch_result result{};
+  ka::event::execute ev(q, result);
+  ka::action::effect_execute_head_range{}(ev, ctx);
+  return result.accepted ? 1 : 0;
 }
 
 // ---- op_mul_mat, scalar shared route (src/emel/kernel/detail.hpp:3356-3571)

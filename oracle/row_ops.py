@@ -169,3 +169,61 @@ def rope(op) -> bool:
                     theta = f32(theta * theta_scale)
                 y[i3, i2, i1] = out
     return True
+
+
+# ---- kernel::attention's head-range event (src/emel/kernel/attention/actions.hpp:15-96), scalar route
+def f32_to_bf16_bits(x):
+    """ggml's round-to-nearest-even with NaN quieting (src/emel/kernel/detail.hpp:3944-3952), vectorised."""
+    u = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    nan = (u & 0x7fffffff) > 0x7f800000
+    r = ((u + (0x7fff + ((u >> 16) & 1))) >> 16) & 0xffff
+    return np.where(nan, ((u >> 16) | 64) & 0xffff, r).astype(np.uint16)
+
+
+def bf16_bits_to_f32(b):
+    return (np.asarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def head_range_can_run(query, key, value, output, layer_offset, hidden_dim, head_dim, head_begin, head_end, capacity,
+                       physical_begin, valid):
+    """guard_request_shape_supported (src/emel/kernel/attention/guards.hpp:28-90) for numpy arrays (which are aligned
+    and cannot overlap unless they share memory)."""
+    if (hidden_dim <= 0 or head_dim <= 0 or head_begin < 0 or head_end <= head_begin or capacity <= 0 or physical_begin < 0 or
+            physical_begin >= capacity or valid <= 0 or valid > capacity):
+        return False
+    if head_end > hidden_dim // head_dim or head_dim > 8192 or capacity > 8192:
+        return False
+    need = layer_offset + capacity * hidden_dim
+    if query.size < hidden_dim or key.size < need or value.size < need or output.size < (head_end - head_begin) * head_dim:
+        return False
+    return not (np.shares_memory(output, query) or np.shares_memory(output, key) or np.shares_memory(output, value))
+
+
+def head_range_attention(query, key, value, output, layer_offset, hidden_dim, head_dim, head_begin, head_end, capacity,
+                         physical_begin, valid):
+    """effect_execute_head_range.  Sums whose order the reference fixes are taken with cumsum (sequential); the
+    exponentials go through f64 exp rounded to f32, which is not glibc's expf to the last bit, so against the compiled
+    reference the result agrees to about 1e-6 relative only."""
+    if not head_range_can_run(query, key, value, output, layer_offset, hidden_dim, head_dim, head_begin, head_end, capacity,
+                              physical_begin, valid):
+        return False
+    f32 = np.float32
+    scale = f32(1.0) / np.sqrt(f32(head_dim), dtype=np.float32)
+    phys = (physical_begin + np.arange(valid)) % capacity
+    for head in range(head_begin, head_end):
+        ho = head * head_dim
+        q = bf16_bits_to_f32(f32_to_bf16_bits(query[ho:ho + head_dim]))
+        scores = np.full(capacity, -np.inf, np.float32)
+        rows = layer_offset + phys[:, None] * hidden_dim + ho + np.arange(head_dim)[None, :]
+        k = bf16_bits_to_f32(key[rows])
+        prod = (k * q[None, :]).astype(np.float32).astype(np.float64)
+        scores[phys] = np.cumsum(prod, axis=1)[:, -1].astype(np.float32) * scale
+        mx = scores.max()
+        with np.errstate(over="ignore", under="ignore"):
+            e = np.exp((scores - mx).astype(np.float64)).astype(np.float32)
+        total = np.cumsum(e.astype(np.float64))[-1]
+        w = bf16_bits_to_f32(f32_to_bf16_bits(e * f32(1.0 / total)))
+        v = bf16_bits_to_f32(value[rows])
+        acc = np.cumsum((v * w[phys][:, None]).astype(np.float32).astype(np.float64), axis=0)[-1]
+        output[(head - head_begin) * head_dim:(head - head_begin + 1) * head_dim] = acc.astype(np.float32)
+    return True

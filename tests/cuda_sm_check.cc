@@ -26,6 +26,12 @@ int main() {
   mm.dst.ne = {1, 1, 1, 1};
   mm.dst.nb = {4, 4, 4, 4};
   const bool accepted = machine.process_event(mm);
+  // the other attention actor's event type is accepted as it is too (rejected here: no device)
+  emel::kernel::attention::event::head_range_request hr{};
+  emel::kernel::attention::event::dispatch_result hr_result{};
+  emel::kernel::attention::event::execute hr_event(hr, hr_result);
+  const bool hr_accepted = machine.process_event(hr_event);
+  if (hr_accepted || hr_result.accepted) return 1;
   ev::op_add other{};
   const bool other_accepted = machine.process_event(other);
   std::printf("engaged=%d accepted=%d error=%u other=%d other_error=%u\n", machine.engaged() ? 1 : 0, accepted ? 1 : 0,
