@@ -746,7 +746,7 @@ def build_decode_session(be, sh, out_type, n_ctx, rank, G, dist=None, seed0=5000
         assert sess.exchange_attach(handles), sess.last_error
         dist.barrier()          # every rank has mapped its peers before anybody's first join
         peer_joins = True
-    info = dict(weight_bytes=0, q4k_bytes=0, q4k_ops=[], peer_joins=peer_joins, allocs=[])
+    info = dict(weight_bytes=0, q4k_bytes=0, q4k_ops=[], peer_joins=peer_joins, allocs=[], tensors=[], norm_ones=None)
     r = rank if G > 1 else 0
     for i, (layer, role, k, m, t) in enumerate(decode_tensors(sh, out_type)):
         row0 = 0
@@ -757,6 +757,7 @@ def build_decode_session(be, sh, out_type, n_ctx, rank, G, dist=None, seed0=5000
         info["allocs"].append(d)
         assert be.synth_fill(d, t, m * k, seed0 + i, 0.02, row0 * k), be.last_error
         assert sess.bind_matrix(layer, role, d, t), sess.last_error
+        info["tensors"].append((layer, role, d, t, nbytes))
         if role != el.TOKEN_EMBD:
             info["weight_bytes"] += nbytes
             if t == eb.Q4_K and layer >= 0:
@@ -764,6 +765,7 @@ def build_decode_session(be, sh, out_type, n_ctx, rank, G, dist=None, seed0=5000
                 info["q4k_ops"].append((layer, role, d, t, k, m))
     ones = be.alloc(4 * sh["n_embd"])
     info["allocs"].append(ones)
+    info["norm_ones"] = ones
     assert be.to_device(ones, np.ones(sh["n_embd"], np.float32))
     assert sess.bind_norm(-1, el.OUTPUT_NORM, ones)
     for l in range(sh["n_layer"]):
@@ -910,6 +912,129 @@ def run_decode_batch(args):
     }
     print(json.dumps(line), flush=True)
     release_decode_session(be, sess, info, world)
+
+
+def run_decode_streamed(args):
+    """--layer-window S: the decode workload with the layers' matrices kept in page-locked host memory and streamed
+    through a window of S layer slots in HBM (include/emelb_window.h) -- the arrangement for a model whose layers do
+    not fit the HBM left for weights.  The resident session runs first on the same weights; the streamed session
+    must produce the same tokens.  The bound is the host-to-device copy rate, measured here with one plain copy
+    of 1 GB from the same page-locked buffer."""
+    import torch
+    import emel_cpp_b200 as eb
+    from emel_cpp_b200 import llama as el
+    from emel_cpp_b200 import window as ew
+
+    assert args.gpus == 1, "the layer window is a one-GPU arrangement"
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    sh = DECODE_SHAPES[args.workload]
+    out_type = eb.Q6_K if args.workload == "decode_8b" else eb.Q4_K
+    slots, depth = args.layer_window, max(1, args.layer_window // 2)
+    steps, warmup, B = min(args.steps, 16), 1, max(1, args.batch)
+    prompt_len = 512 if args.prompt is None else args.prompt
+    n_ctx = ((prompt_len + warmup + steps + 15) // 16) * 16
+    be = eb.Backend(0)
+    stream = torch.cuda.ExternalStream(be.stream(), device=dev)
+
+    def timed_region(fn):
+        be.sync()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = fn()
+        e1.record(stream)
+        be.sync()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), out
+
+    rng = np.random.Generator(np.random.PCG64(42))
+    prompts = [rng.integers(0, sh["n_vocab"], size=prompt_len, dtype=np.int32) for _ in range(B)]
+
+    def run(sess):
+        """-> prefill ms (sequence 0), decode ms, ids"""
+        assert sess.set_sequences(B), sess.last_error
+        pre_ms = None
+        for j in range(B):
+            assert sess.select_sequence(j)
+            ms, ok = timed_region(lambda: sess.prefill(prompts[j][:-1], 0))
+            assert ok, sess.last_error
+            pre_ms = ms if pre_ms is None else pre_ms
+        first, pos = [int(p[-1]) for p in prompts], [prompt_len - 1] * B
+        if B == 1:
+            w = sess.generate(first[0], pos[0], warmup)
+            ms, ids = timed_region(lambda: sess.generate(int(w[-1]), pos[0] + warmup, steps))
+            return pre_ms, ms, [int(x) for x in w] + [int(x) for x in ids]
+        w = sess.generate_batch(first, pos, warmup)
+        ms, ids = timed_region(lambda: sess.generate_batch(w[-1], [p + warmup for p in pos], steps))
+        return pre_ms, ms, [list(map(int, x)) for x in w] + [list(map(int, x)) for x in ids]
+
+    sess, info = build_decode_session(be, sh, out_type, n_ctx, 0, 1)
+    res_pre, res_ms, res_ids = run(sess)
+    sess.close()
+    # the layers' matrices -> one page-locked host image, packed like a file; their device copies are freed
+    layer_tensors = [t for t in info["tensors"] if t[0] >= 0]
+    offs, at = {}, 4096
+    for layer, role, d, t, nbytes in layer_tensors:
+        offs[(layer, role)] = at
+        at += (nbytes + 4095) // 4096 * 4096
+    image = torch.empty(at, dtype=torch.uint8, pin_memory=True)
+    for layer, role, d, t, nbytes in layer_tensors:
+        o = offs[(layer, role)]
+        assert be.to_host(image[o:o + nbytes].numpy(), d, nbytes)
+        be.free(d)
+        info["allocs"].remove(d)
+    layer_bytes = sum(t[4] for t in layer_tensors)
+    layers = [[(l * 16 + role, offs[(l, role)], nbytes) for (layer, role, d, t, nbytes) in layer_tensors if layer == l] for l in range(sh["n_layer"])]
+    _o, sizes, cap = ew.plan_layers(layers)
+    win = ew.LayerWindow(be)
+    assert win.bind(image, layers, slots * cap, slots, depth), win.last_error
+    assert win.bound["streaming_active"], "the layers fit the budget: nothing to stream"
+    sess = el.Session(be, el.config(sh["n_layer"], sh["n_embd"], sh["n_head"], sh["n_head_kv"], sh["head_dim"], sh["n_ff"], sh["n_vocab"], n_ctx))
+    assert sess.set_window(win), sess.last_error
+    base = image.data_ptr()
+    for layer, role, d, t, nbytes in info["tensors"]:
+        assert sess.bind_matrix(layer, role, d if layer < 0 else base + offs[(layer, role)], t), sess.last_error
+    assert sess.bind_norm(-1, el.OUTPUT_NORM, info["norm_ones"])
+    for l in range(sh["n_layer"]):
+        assert sess.bind_norm(l, el.ATTN_NORM, info["norm_ones"]) and sess.bind_norm(l, el.FFN_NORM, info["norm_ones"])
+    # the copy rate the stream is bounded by: 1 GB of the same buffer in one copy
+    probe_bytes = min(1 << 30, at)
+    probe = be.alloc(probe_bytes)
+    host_view = image[:probe_bytes].numpy()
+    assert be.to_device(probe, host_view)
+    copy_ms, ok = timed_region(lambda: be.to_device(probe, host_view))
+    assert ok
+    be.free(probe)
+    h2d_peak = probe_bytes / (copy_ms * 1e-3) / 1e9
+    with ClockSampler(0) as clk:
+        win_pre, win_ms, win_ids = run(sess)
+    assert win_ids == res_ids, "the streamed session decodes differently from the resident one"
+    st = win.stats()
+    tok_s = steps * B / (win_ms * 1e-3)
+    gbs = layer_bytes * steps / (win_ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s, layers streamed from host memory", "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(win_ms / steps, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 dot + f32 scales; f16 KV", "data": "synthetic",
+        "config": {"workload": sh["name"].replace("batch-1", f"batch-{B}") + f", layers streamed through {slots} slots", "batch": B,
+                   "window_slots": slots, "prefetch_depth": depth, "prompt_tokens": prompt_len, "decoded_tokens_per_sequence": steps,
+                   "slot_bytes": cap, "layer_bytes_per_step": layer_bytes, "hbm_for_layers": slots * cap,
+                   "source_page_locked": win.bound["source_page_locked"], "launch": "plain launches; copies ordered by events",
+                   "l2_policy": f"inputs larger than L2: {layer_bytes / 1e9:.2f} GB cross PCIe and are read per step"},
+        "same_tokens_as_resident": True,
+        "resident": {"tok_s": round(steps * B / (res_ms * 1e-3), 2), "prefill_tok_s": round((prompt_len - 1) / (res_pre * 1e-3), 1)},
+        "prefill_tok_s": round((prompt_len - 1) / (win_pre * 1e-3), 1),
+        "roofline": {"bound": "pcie", "kernel": "slot loads (one copy per matrix)", "achieved": round(gbs, 2), "peak": round(h2d_peak, 2),
+                     "unit": "GB/s", "frac": round(gbs / h2d_peak, 4), "peak_source": "one 1 GB page-locked copy timed in this run", "traffic": None},
+        "window": st, "gpu_launches": sess.launches_per_token() * steps if B == 1 else sess.batch_launches_per_step() * steps,
+        "e2e": None, "cpu_baseline": None, "clocks": clk.summary(),
+    }
+    print(json.dumps(line), flush=True)
+    sess.close()
+    win.close()
+    for d in info["allocs"]:
+        be.free(d)
 
 
 def run_decode(args):
@@ -1275,6 +1400,9 @@ def main():
     ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
                     help="sharded decode: join the ranks' row intervals by peer stores over NVLink (default) or by NCCL all-gathers")
     ap.add_argument("--batch", type=int, default=1, help="decode workloads: sequences decoded together (one token each per step)")
+    ap.add_argument("--layer-window", type=int, default=0,
+                    help="decode workloads, one GPU: keep the layers' matrices in page-locked host memory and stream them "
+                         "through a window of this many layer slots in HBM (2-8); prints its own line")
     ap.add_argument("--one-kernel", action="store_true",
                     help="decode workloads: run the headline through the one-kernel step (every layer of a token in one "
                          "persistent kernel) instead of the launch chain")
@@ -1287,6 +1415,8 @@ def main():
         (run_reference_load if args.impl == "reference" else run_load)(args)
     elif args.impl == "reference":
         (run_reference_decode if decode else run_reference_gemv)(args)
+    elif decode and args.layer_window > 0:
+        run_decode_streamed(args)
     else:
         (run_decode_batch if decode and args.batch > 1 else run_decode if decode else run_gemv)(args)
 

@@ -118,8 +118,8 @@ _SIGNATURES = {
 
 
 def declared_symbols():
-    from . import gguf as _gguf, llama as _llama
-    return sorted(list(_SIGNATURES) + list(_llama.SIGNATURES) + list(_gguf.SIGNATURES))
+    from . import gguf as _gguf, llama as _llama, window as _window
+    return sorted(list(_SIGNATURES) + list(_llama.SIGNATURES) + list(_gguf.SIGNATURES) + list(_window.SIGNATURES))
 
 
 def lib():
@@ -134,9 +134,10 @@ def lib():
             fn = getattr(_lib, name)
             fn.restype = C.c_uint32
             fn.argtypes = args
-        from . import gguf as _gguf, llama as _llama
+        from . import gguf as _gguf, llama as _llama, window as _window
         _llama.register(_lib)
         _gguf.register(_lib)
+        _window.register(_lib)
     return _lib
 
 

@@ -33,6 +33,7 @@ SOURCES = {
     "noalloc.cu": [],
     "gguf.cu": [],
     "upload.cu": [],
+    "window.cu": [],
     "api.cu": [],
 }
 
@@ -62,6 +63,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     headers.append(os.path.join(os.path.dirname(HERE), "include", "emelb.h"))
     headers.append(os.path.join(os.path.dirname(HERE), "include", "emelb_llama.h"))
     headers.append(os.path.join(os.path.dirname(HERE), "include", "emelb_gguf.h"))
+    headers.append(os.path.join(os.path.dirname(HERE), "include", "emelb_window.h"))
     headers = [h for h in headers if os.path.exists(h)]
     nccl_inc, nccl_lib = _nccl_paths()
     objs = []

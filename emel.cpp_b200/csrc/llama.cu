@@ -25,7 +25,9 @@
 #include <vector>
 
 #include "../../include/emelb_llama.h"
+#include "../../include/emelb_window.h"
 #include "ctx.h"
+#include "window.h"
 
 using namespace emelb;
 
@@ -39,6 +41,7 @@ namespace {
 
 struct Tensor {
   const uint8_t* dev = nullptr;
+  int64_t win_off = -1;   // >= 0: the tensor is streamed; its offset inside the layer's slot of the session's window
   int type = EMELB_UNKNOWN;
   int64_t row_bytes = 0;
   int K = 0, M = 0;
@@ -118,6 +121,10 @@ struct emelb_llama {
   int step_mode = 0;             // 0: the chain of per-operation launches, 1: one kernel per token where it applies
   TokenLaunchState token_launch;
   unsigned long long* token_trace = nullptr;   // device stamps of emelb_llama_decode_profile
+  // a streaming layer window (emelb_llama_set_window): layer tensors bound to addresses inside its source are read
+  // from the slot the window hands out for the layer; steps then run as plain launches, not as replayed graphs
+  emelb_window* window = nullptr;
+  bool streamed = false;
   std::vector<void*> owned;
 };
 
@@ -139,7 +146,15 @@ bool dev_alloc(emelb_llama* s, void** p, size_t bytes) {
   return true;
 }
 
-bool bound(const Tensor& t) { return t.dev != nullptr; }
+bool bound(const Tensor& t) { return t.dev != nullptr || t.win_off >= 0; }
+
+// layer tensors that are streamed through the session's window instead of being resident
+int streamed_tensors(const emelb_llama* s) {
+  int n = 0;
+  for (const Layer& l : s->layers)
+    for (const Tensor* t : {&l.attn_norm, &l.wq, &l.wk, &l.wv, &l.wo, &l.ffn_norm, &l.gate, &l.up, &l.down}) n += t->win_off >= 0;
+  return n;
+}
 
 bool all_bound(const emelb_llama* s) {
   if (!bound(s->tok_embd) || !bound(s->out_norm) || !bound(s->output)) return false;
@@ -194,7 +209,7 @@ void prepare_token_kernel(emelb_llama* s) {
   s->token_layers_valid = true;
   s->token_usable = false;
   const emelb_llama_config& c = s->cfg;
-  if (s->G != 1 || c.rope_neox || (c.head_dim & 1) || !all_bound(s)) return;
+  if (s->G != 1 || c.rope_neox || (c.head_dim & 1) || !all_bound(s) || s->streamed) return;
   std::vector<TokenLayerW> host(c.n_layer);
   for (int l = 0; l < c.n_layer; ++l) {
     const Layer& w = s->layers[l];
@@ -228,7 +243,26 @@ struct Enqueue {
   int batch_family = 0;  // family the planes were last quantized for by batch_matmul
   bool batch_tc_tiled = false;  // the tensor-core workspace holds the current planes in operand order
 
+  Layer slot_view;       // the current layer's tensors when they are read from a window slot
+
   void check(cudaError_t e) { ok = ok && ctx_cuda_ok(s->c, e); }
+
+  // Layer l's tensors for the launches that follow.  A streamed layer is asked of the window here: the view holds
+  // until the next call, and the window orders its copies against this stream.  On a failed acquire `ok` drops and
+  // the caller must launch nothing for the layer
+  const Layer& layer_weights(int l) {
+    if (!s->streamed) return s->layers[l];
+    const uint8_t* base = nullptr;
+    if (emelb_window_acquire(s->window, l, &base, nullptr) != EMELB_WINDOW_OK || !base) {
+      ok = false;
+      return s->layers[l];
+    }
+    slot_view = s->layers[l];
+    for (Tensor* t : {&slot_view.attn_norm, &slot_view.wq, &slot_view.wk, &slot_view.wv, &slot_view.wo, &slot_view.ffn_norm,
+                      &slot_view.gate, &slot_view.up, &slot_view.down})
+      if (t->win_off >= 0) t->dev = base + t->win_off;
+    return slot_view;
+  }
 
   ActPlanesMut planes() const { return ActPlanesMut{s->c->act_qs, s->c->act_d, s->c->act_bsums}; }
 
@@ -566,7 +600,8 @@ struct Enqueue {
     check(launch_embed_rows(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, s->batch_tokens, B, s->b_hidden, c.n_embd, st));
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
-      const Layer& w = s->layers[l];
+      const Layer& w = layer_weights(l);
+      if (!ok) break;
       const int64_t layer_off = cache_off(s, l, s->cur_seq);
       check(launch_rms_norm_batch(s->b_hidden, reinterpret_cast<const float*>(w.attn_norm.dev), c.rms_eps, c.n_embd, B, s->b_norm, s->b_partial, st));
       ++launches;
@@ -653,7 +688,8 @@ struct Enqueue {
     check(launch_embed_rows(s->tok_embd.type, s->tok_embd.dev, s->tok_embd.row_bytes, tok, B, s->b_hidden, c.n_embd, st));
     ++launches;
     for (int l = 0; l < c.n_layer; ++l) {
-      const Layer& w = s->layers[l];
+      const Layer& w = layer_weights(l);
+      if (!ok) break;
       const int64_t layer_off = cache_off(s, l, 0);
       {
         const bool same_type = w.wk.type == w.wq.type && w.wv.type == w.wq.type;
@@ -739,7 +775,8 @@ struct Enqueue {
     }
     bool hidden_joined_in_next = false;   // the previous layer left the join of the hidden vector to this layer's first launch
     for (int l = 0; l < c.n_layer && !one_kernel; ++l) {
-      const Layer& w = s->layers[l];
+      const Layer& w = layer_weights(l);
+      if (!ok) break;
       bool roped = false;
       {
         const Tensor* ws[3] = {&w.wq, &w.wk, &w.wv};
@@ -855,6 +892,28 @@ cudaGraphExec_t step_graph(emelb_llama* s, Mode mode, int token, int position) {
   s->launches_mode[mode] = e.launches;
   if (mode == MODE_ARGMAX) s->launches_per_token = e.launches;
   return ex;
+}
+
+// make mode's step launchable for the device-side state: the replayable graph, or nothing when layers are streamed
+// (a window acquire orders copies against the stream with events, which a replayed graph could not re-issue)
+bool step_ready(emelb_llama* s, Mode mode, int token, int position) {
+  if (s->streamed) return true;
+  return step_graph(s, mode, token, position) != nullptr;
+}
+
+// enqueue one step of `mode`
+bool step_launch(emelb_llama* s, Mode mode) {
+  emelb_ctx* c = s->c;
+  if (!s->streamed) {
+    c->diag.kernel_launches += s->launches_mode[mode];
+    return ctx_cuda_ok(c, cudaGraphLaunch(s->graphs[mode], c->stream));
+  }
+  Enqueue e{s, c->stream};
+  e.token_step(mode);
+  c->diag.kernel_launches += e.launches;
+  s->launches_mode[mode] = e.launches;
+  if (mode == MODE_ARGMAX) s->launches_per_token = e.launches;
+  return e.ok;
 }
 
 bool valid_step(const emelb_llama* s, int token, int position) {
@@ -1050,7 +1109,13 @@ uint32_t emelb_llama_bind(emelb_llama* s, int32_t layer, int32_t role, const eme
     if ((int64_t)t->nb[1] != x.row_bytes || t->nb[0] != 1) return EMELB_INVALID_REQUEST;
   }
   x.dev = static_cast<const uint8_t*>(ctx_resolve_weights(s->c, t->data));
-  if (!x.dev) return EMELB_INVALID_REQUEST;
+  if (!x.dev) {
+    // not resident: a layer tensor may lie in the source of the session's streaming window
+    uint64_t off = 0;
+    if (model_level || !window_find_extent(s->window, layer, t->data, (uint64_t)x.row_bytes * (uint64_t)M, &off) || off % 16 != 0)
+      return EMELB_INVALID_REQUEST;
+    x.win_off = (int64_t)off;
+  }
   Tensor* slot = nullptr;
   if (model_level) slot = role == EMELB_T_TOKEN_EMBD ? &s->tok_embd : (role == EMELB_T_OUTPUT_NORM ? &s->out_norm : &s->output);
   else {
@@ -1061,7 +1126,21 @@ uint32_t emelb_llama_bind(emelb_llama* s, int32_t layer, int32_t role, const eme
   *slot = x;
   // bindings changed: captured steps hold stale pointers
   for (int m = 0; m < MODE_COUNT; ++m) s->graph_attention_mode[m] = -1;
+  s->batch_graph_mode = -1;
   s->token_layers_valid = false;
+  s->streamed = streamed_tensors(s) > 0;
+  return EMELB_OK;
+}
+
+uint32_t emelb_llama_set_window(emelb_llama* s, emelb_window* w) {
+  if (!s) return EMELB_INVALID_REQUEST;
+  // tensors bound through the previous window keep offsets into its slots: they must be bound again first
+  if (streamed_tensors(s) > 0) return EMELB_INVALID_REQUEST;
+  if (w) {
+    // one window per unsharded session, on the session's context, with one descriptor per layer
+    if (s->G != 1 || window_ctx(w) != s->c || !window_streaming(w) || window_layer_count(w) != s->cfg.n_layer) return EMELB_INVALID_REQUEST;
+  }
+  s->window = w;
   return EMELB_OK;
 }
 
@@ -1070,11 +1149,10 @@ uint32_t emelb_llama_decode(emelb_llama* s, int32_t token, int32_t position, flo
   emelb_ctx* c = s->c;
   cudaSetDevice(c->device);
   const Mode mode = logits_out ? MODE_LOGITS : MODE_ARGMAX;
-  cudaGraphExec_t g = step_graph(s, mode, token, position);
-  if (!g) return EMELB_INTERNAL_ERROR;
+  if (!step_ready(s, mode, token, position)) return EMELB_INTERNAL_ERROR;
   bool ok = ctx_cuda_ok(c, launch_step_begin(s->state, token, position, c->stream));
-  ok = ok && ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
-  c->diag.kernel_launches += 1 + s->launches_mode[mode];
+  ok = ok && step_launch(s, mode);
+  c->diag.kernel_launches += 1;
   if (ok && logits_out) {
     cudaPointerAttributes at{};
     const bool dev = cudaPointerGetAttributes(&at, logits_out) == cudaSuccess && at.type == cudaMemoryTypeDevice;
@@ -1163,13 +1241,12 @@ uint32_t emelb_llama_prefill(emelb_llama* s, const int32_t* tokens, int32_t n, i
     if (!ok) return EMELB_INTERNAL_ERROR;
   }
   if (done < n) {
-    cudaGraphExec_t g = step_graph(s, MODE_PREFILL, tokens[done], start_pos + done);
-    if (!g) return EMELB_INTERNAL_ERROR;
+    if (!step_ready(s, MODE_PREFILL, tokens[done], start_pos + done)) return EMELB_INTERNAL_ERROR;
     for (int i = done; ok && i < n; ++i) {
       ok = ctx_cuda_ok(c, launch_step_begin(s->state, tokens[i], start_pos + i, c->stream));
-      ok = ok && ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+      ok = ok && step_launch(s, MODE_PREFILL);
     }
-    c->diag.kernel_launches += (uint64_t)(n - done) * (1 + s->launches_mode[MODE_PREFILL]);
+    c->diag.kernel_launches += (uint64_t)(n - done);
   }
   ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
   return ok ? EMELB_OK : EMELB_INTERNAL_ERROR;
@@ -1385,10 +1462,18 @@ uint32_t emelb_llama_generate_batch(emelb_llama* s, const int32_t* first_tokens,
   release_small_batch(s, n_seq);
   if (!reserve_sequences(s) || !reserve_batch(s, batch_buffer_columns(s)) || s->batch_cap < n_seq) return EMELB_INTERNAL_ERROR;
   bool ok = write_batch_state(s, first_tokens, start_positions, n_seq);
-  cudaGraphExec_t g = ok ? batch_step_graph(s, n_seq) : nullptr;
-  if (!g) return EMELB_INTERNAL_ERROR;
+  cudaGraphExec_t g = ok && !s->streamed ? batch_step_graph(s, n_seq) : nullptr;
+  if (!g && !(ok && s->streamed)) return EMELB_INTERNAL_ERROR;
   for (int i = 0; ok && i < n_steps; ++i) {
-    ok = ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+    if (g) {
+      ok = ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
+    } else {
+      // streamed layers: plain launches, the window's events order the slot copies
+      Enqueue e{s, c->stream};
+      e.batch_step(n_seq);
+      ok = e.ok;
+      s->batch_launches = e.launches;
+    }
     ok = ok && ctx_cuda_ok(c, launch_batch_advance(s->bstate, kMaxSeqs, n_seq, s->b_idx, s->b_out, c->stream));
   }
   c->diag.kernel_launches += (uint64_t)n_steps * (uint64_t)(s->batch_launches + 1);
@@ -1410,11 +1495,10 @@ uint32_t emelb_llama_generate(emelb_llama* s, int32_t first_token, int32_t start
     return EMELB_INVALID_REQUEST;
   emelb_ctx* c = s->c;
   cudaSetDevice(c->device);
-  cudaGraphExec_t g = step_graph(s, MODE_ARGMAX, first_token, start_pos);
-  if (!g) return EMELB_INTERNAL_ERROR;
+  if (!step_ready(s, MODE_ARGMAX, first_token, start_pos)) return EMELB_INTERNAL_ERROR;
   bool ok = ctx_cuda_ok(c, launch_step_begin(s->state, first_token, start_pos, c->stream));
-  for (int i = 0; ok && i < n; ++i) ok = ctx_cuda_ok(c, cudaGraphLaunch(g, c->stream));
-  c->diag.kernel_launches += 1 + (uint64_t)n * s->launches_per_token;
+  for (int i = 0; ok && i < n; ++i) ok = step_launch(s, MODE_ARGMAX);
+  c->diag.kernel_launches += 1;
   ok = ok && ctx_cuda_ok(c, cudaMemcpyAsync(s->host_pinned, s->tokens_dev, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, c->stream));
   ok = ok && ctx_cuda_ok(c, cudaStreamSynchronize(c->stream));
   if (!ok) return EMELB_INTERNAL_ERROR;

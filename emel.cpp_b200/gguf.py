@@ -245,6 +245,72 @@ def llama_config(f: File, n_ctx: int | None = None, kv_block: int = 16, shard_ra
                      shard_rank=shard_rank, shard_count=shard_count)
 
 
+def layer_extents(f: File, n_layer: int):
+    """One list of (tensor_id, file_offset, byte_size) per layer: the nine `blk.<layer>.*` tensors of the decoder, in
+    role order -- the extents a streaming window is bound with.  tensor_id is the tensor's index in the file."""
+    layers = []
+    for layer in range(n_layer):
+        weights = []
+        for stem in _LAYER_TENSORS.values():
+            t = f.find_tensor(f"blk.{layer}.{stem}.weight")
+            if t is None:
+                raise GgufError(f"gguf tensor blk.{layer}.{stem}.weight", MODEL_INVALID)
+            weights.append((t["index"], t["file_offset"], t["data_size"]))
+        layers.append(weights)
+    return layers
+
+
+def load_llama_streamed(backend: eb.Backend, f: File, budget_bytes: int, window_slots: int = 4, prefetch_depth: int = 2,
+                        n_ctx: int | None = None, first_tensor_id: int = 0, staged_only: bool = False):
+    """A decoder whose layers stay in the file mapping and cross to HBM through a streaming window of
+    `window_slots` layer slots (budget_bytes is the HBM the layers may take; a model that fits it is loaded
+    whole by load_llama instead).  The embedding table, the output norm and the output projection are uploaded
+    as usual.  Returns (session, window); close the session before the window."""
+    from . import window as ew
+    cfg = llama_config(f, n_ctx)
+    layers = layer_extents(f, cfg.n_layer)
+    first = f.tensor(0)
+    base = first["data"] - first["file_offset"]
+    size = max(t["file_offset"] + t["data_size"] for t in f.tensors())
+    win = ew.LayerWindow(backend)
+    if staged_only:
+        win.set_staged_only(True)
+    if not win.bind(base, layers, budget_bytes, window_slots, prefetch_depth, source_bytes=size):
+        err = win.last_error
+        win.close()
+        raise GgufError("layer window bind", err)
+    if not win.bound["streaming_active"]:
+        win.close()
+        return load_llama(backend, f, n_ctx, first_tensor_id), None
+    sess = el.Session(backend, cfg)
+    shapes = el.matrix_shapes(cfg)
+    try:
+        if not sess.set_window(win):
+            raise GgufError("layer window attach", MODEL_INVALID)
+        for role, name in _GLOBAL_TENSORS.items():
+            t = f.find_tensor(name)
+            if t is None:
+                raise GgufError(f"gguf tensor {name}", MODEL_INVALID)
+            f.upload(backend, t["index"], first_tensor_id + t["index"])
+            ok = sess.bind_norm(-1, role, t["data"]) if role in _NORMS else sess.bind_matrix(-1, role, t["data"], t["type"])
+            if not ok:
+                raise GgufError(f"gguf bind {name}", MODEL_INVALID)
+        for layer in range(cfg.n_layer):
+            for role, stem in _LAYER_TENSORS.items():
+                t = f.find_tensor(f"blk.{layer}.{stem}.weight")
+                if role in _NORMS:
+                    ok = t["type"] == eb.F32 and sess.bind_norm(layer, role, t["data"])
+                else:
+                    ok = (t["dims"][0], t["dims"][1]) == shapes[role] and sess.bind_matrix(layer, role, t["data"], t["type"])
+                if not ok:
+                    raise GgufError(f"gguf bind blk.{layer}.{stem}.weight", MODEL_INVALID)
+    except Exception:
+        sess.close()
+        win.close()
+        raise
+    return sess, win
+
+
 def load_llama(backend: eb.Backend, f: File, n_ctx: int | None = None, first_tensor_id: int = 0,
                shard_rank: int = 0, shard_count: int = 1) -> el.Session:
     """Uploads every tensor the decoder needs from the mapping to HBM and binds it by its

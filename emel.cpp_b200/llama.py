@@ -216,6 +216,12 @@ class Session:
         """Sharded sessions with peers attached: joins inside the neighbouring kernels (default) or one join kernel each."""
         return self._ret(eb.lib().emelb_llama_set_join_fusion(self._h, 1 if on else 0))
 
+    def set_window(self, window) -> bool:
+        """Attach a bound, streaming LayerWindow (or None to detach): layer tensors bound afterwards by an address
+        inside its source are read from the window's slots (emelb_llama_set_window)."""
+        self._window = window   # kept alive with the session
+        return self._ret(eb.lib().emelb_llama_set_window(self._h, window.handle if window is not None else None))
+
     def set_step_mode(self, mode: int) -> bool:
         """0: the chain of per-operation launches (default); 1: one persistent kernel per token where the session qualifies."""
         return self._ret(eb.lib().emelb_llama_set_step_mode(self._h, mode))

@@ -18,6 +18,7 @@
 #define EMELB_LLAMA_H
 
 #include "emelb.h"
+#include "emelb_window.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -171,6 +172,17 @@ EMELB_API uint32_t emelb_llama_batch_launches_per_step(const emelb_llama* s, int
  * launches per token at the 8B shape; measured no faster on 2 GPUs and slower on 4, hence not the default).  Same
  * result bit for bit either way. */
 EMELB_API uint32_t emelb_llama_set_join_fusion(emelb_llama* s, int32_t on);
+
+/* Layers streamed from host memory (models whose layers do not fit the HBM left for weights).  `w` is a bound,
+ * streaming emelb_window on the session's context with one layer descriptor per model layer.  After this call
+ * emelb_llama_bind accepts, for a layer tensor, a view whose `data` is not resident but is the address of one of that
+ * layer's extents inside the window's source (same byte size): the tensor is then read from the slot the window
+ * hands out for the layer.  Resident and streamed tensors may be mixed.  Each layer pass of a step, of a prompt batch
+ * and of a batch step acquires its layer once, so the next layers cross PCIe while the current one computes; steps
+ * run as plain launches instead of replayed graphs.  Same results bit for bit as the resident session.  Unsharded
+ * sessions only.  The window must stay bound while tensors of the session are bound through it; w = null detaches
+ * (refused while streamed tensors are bound). */
+EMELB_API uint32_t emelb_llama_set_window(emelb_llama* s, emelb_window* w);
 
 /* How a decode step is enqueued.  0 (default): the chain of per-operation
  * launches.  1: where the session qualifies (unsharded, Q4_K layer matrices with
