@@ -19,7 +19,7 @@ ROLE_NAMES = {el.ATTN_Q: "attn_q", el.ATTN_K: "attn_k", el.ATTN_V: "attn_v", el.
 NORM_NAMES = {el.ATTN_NORM: "attn_norm", el.FFN_NORM: "ffn_norm"}
 
 
-def model_file(port, seed, types):
+def model_file(port, seed, types, CFG=CFG):
     shapes = el.matrix_shapes(el.config(**CFG))
     matrices, norms, plan = {}, {}, []
 
@@ -100,6 +100,59 @@ def test_decode_from_gguf_file_matches_reference_loop(be, port, tmp_path, types)
             cpu.close()
             for t in f.tensors():
                 be.evict(5000 + 100 * len(types) + t["index"])
+
+
+def test_layers_streamed_from_a_gguf_file(be, port, tmp_path):
+    """The same file decoded with its layers resident and with its layers left in the mapping and streamed through
+    a two-slot window: identical logits and ids."""
+    from emel_cpp_b200 import window as ew
+    cfg4 = dict(CFG, n_layer=4)
+    types = {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K, el.FFN_DOWN: eb.Q6_K}
+    image, _plan = model_file(port, 33, types, cfg4)
+    path = tmp_path / "tiny-llama-4.gguf"
+    path.write_bytes(image)
+    prompt = synth.rng(6).integers(0, CFG["n_vocab"], size=12).tolist()
+    with gguf.File(str(path)) as f:
+        resident = gguf.load_llama(be, f, first_tensor_id=7000)
+        try:
+            assert resident.prefill(prompt[:-1], 0)
+            want_logits = resident.decode(prompt[-1], len(prompt) - 1, want_logits=True)
+            want_ids = list(resident.generate(prompt[-1], len(prompt) - 1, 12))
+        finally:
+            resident.close()
+            for t in f.tensors():
+                be.evict(7000 + t["index"])
+        layers = gguf.layer_extents(f, 4)
+        assert [len(w) for w in layers] == [9] * 4
+        _offs, sizes, cap = ew.plan_layers(layers)
+        # a budget that holds every layer: nothing is streamed, the plain loader's session comes back
+        sess, win = gguf.load_llama_streamed(be, f, sum(sizes), 2, 1, first_tensor_id=7000)
+        try:
+            assert win is None and list(sess.generate(prompt[-1], len(prompt) - 1, 1)) is not None
+        finally:
+            sess.close()
+            for t in f.tensors():
+                be.evict(7000 + t["index"])
+        for staged in (False, True):
+            sess, win = gguf.load_llama_streamed(be, f, 2 * cap, 2, 1, first_tensor_id=7200, staged_only=staged)
+            try:
+                assert win is not None and win.bound["streaming_active"] and win.bound["window_slots"] == 2
+                assert sess.prefill(prompt[:-1], 0), sess.last_error
+                got = sess.decode(prompt[-1], len(prompt) - 1, want_logits=True)
+                assert np.array_equal(got.view(np.uint32), want_logits.view(np.uint32))
+                assert list(sess.generate(prompt[-1], len(prompt) - 1, 12)) == want_ids
+                # only the three model-level tensors are resident
+                assert eb.LIFECYCLE[be.state(7200 + f.find_tensor("blk.0.attn_q.weight")["index"]).lifecycle_state] != "resident"
+                assert eb.LIFECYCLE[be.state(7200 + f.find_tensor("output.weight")["index"]).lifecycle_state] == "resident"
+                assert win.stats()["loads_failed"] == 0
+            finally:
+                sess.close()
+                win.close()
+                for t in f.tensors():
+                    be.evict(7200 + t["index"])
+        # a window that cannot hold two layers
+        with pytest.raises(gguf.GgufError):
+            gguf.load_llama_streamed(be, f, cap, 2, 1, first_tensor_id=7400)
 
 
 def test_upload_rows_feeds_a_row_sharded_product(be, port, tmp_path):
