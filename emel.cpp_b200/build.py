@@ -28,6 +28,7 @@ SOURCES = {
     "gemm_tc.cu": [],
     "gemm_q8_mma.cu": [],
     "gemm_q4k_mma.cu": [],
+    "gemm_q6k_mma.cu": [],
     "llama.cu": [],
     "comm.cu": [],
     "noalloc.cu": [],

@@ -225,6 +225,11 @@ cudaError_t launch_gemv(int type, const GemvArgs& a, int ncols, bool argmax, int
     ++*launches;
     return launch_gemm_q4k_mma(a, ncols, sm_count, st);
   }
+  // nine or more columns of Q6_K: mma.sync per 16-weight scale group (gemm_q6k_mma.cu)
+  if (!argmax && gemm_q6k_mma_supported(type, a, ncols)) {
+    ++*launches;
+    return launch_gemm_q6k_mma(a, ncols, sm_count, st);
+  }
   // many columns of Q4_K: the tensor-core kernel (same numbers, see gemm_tc.cu)
   if (!argmax && gemv_takes_tensor_core(type, a, ncols)) {
     *launches += a.tc_ws_reuse ? 1 : 2;

@@ -167,6 +167,32 @@ def test_mul_mat_many_columns_tensor_core_kernel(be, checker, port, k, m, n):
     assert be.sync()       # a bounded wait that ran out would surface here
 
 
+@pytest.mark.parametrize("k,m,n", [
+    (2048, 128, 32), (2048, 5, 33), (4096, 300, 130), (2048, 129, 257), (4096, 260, 64), (14336, 150, 70), (6144, 70, 9),
+    (4096, 64, 17), (2048, 1000, 40),
+])
+def test_mul_mat_many_columns_q6_k(be, checker, port, k, m, n):
+    """Nine or more columns of Q6_K (K a multiple of 2048) take the mma.sync kernel, one instruction per 16-weight
+    scale group: ragged tiles in both directions, every column tile width, the same bits as the mat-vec route."""
+    w = synth.encoded_weights(port, eb.Q6_K, 700 + m, m, k)
+    x = synth.activations_f32(800 + n, k, n)
+    got, want = gpu_mul_mat(be, eb.Q6_K, w, k, m, x, n), cpu_mul_mat(checker, eb.Q6_K, w, k, m, x, n)
+    assert_mul_mat_parity(got, want, checker, eb.Q6_K)
+    x8 = np.ascontiguousarray(x.reshape(k, n)[:, :8])
+    got8 = gpu_mul_mat(be, eb.Q6_K, w, k, m, x8, 8)
+    assert np.array_equal(got.reshape(m, n)[:, :8].view(np.uint32), got8.view(np.uint32))
+
+
+@pytest.mark.parametrize("n", [48, 12])
+def test_mul_mat_many_columns_q6_k_random_block_bytes(be, checker, n):
+    """Arbitrary block bytes: every 6-bit code and every int8 scale, -128 included."""
+    k, m = 4096, 96
+    w = synth.random_blocks(eb.Q6_K, 910, m, k)
+    x = synth.activations_f32(911, k, n)
+    got, want = gpu_mul_mat(be, eb.Q6_K, w, k, m, x, n), cpu_mul_mat(checker, eb.Q6_K, w, k, m, x, n)
+    assert_mul_mat_parity(got, want, checker, eb.Q6_K)
+
+
 @pytest.mark.parametrize("n", [96, 16, 23])
 def test_mul_mat_many_columns_random_block_bytes(be, checker, n):
     """Arbitrary scale/min bits (all 6-bit values, extreme nibbles) through the tcgen05 kernel (96 columns) and
