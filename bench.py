@@ -717,6 +717,9 @@ DECODE_SHAPES = {
 }
 
 
+MIX_Q6_K = False   # set by --mix
+
+
 def decode_tensors(sh, out_type):
     """(layer, role, K, M, type) of every matrix, in the roles of include/emelb_llama.h."""
     import emel_cpp_b200 as eb
@@ -727,7 +730,10 @@ def decode_tensors(sh, out_type):
                  (el.FFN_DOWN, sh["n_ff"], sh["n_embd"])]
     out = [(-1, el.TOKEN_EMBD, sh["n_embd"], sh["n_vocab"], eb.Q4_K), (-1, el.OUTPUT, sh["n_embd"], sh["n_vocab"], out_type)]
     for l in range(sh["n_layer"]):
-        out += [(l, role, k, m, eb.Q4_K) for role, k, m in per_layer]
+        # --mix: the value and down projections of every other layer are Q6_K, as quantization mixes of the Q4_K_M
+        # kind have them
+        out += [(l, role, k, m, eb.Q6_K if MIX_Q6_K and l % 2 == 0 and role in (el.ATTN_V, el.FFN_DOWN) else eb.Q4_K)
+                for role, k, m in per_layer]
     return out
 
 
@@ -1131,6 +1137,8 @@ def run_decode(args):
         for layer in sorted(per_layer):
             roles = per_layer[layer]
             for group in ((el.ATTN_Q, el.ATTN_K, el.ATTN_V), (el.ATTN_OUT,), (el.FFN_GATE, el.FFN_UP), (el.FFN_DOWN,)):
+                if any(role not in roles for role in group):
+                    continue            # --mix: a Q6_K matrix in the group
                 ops, off = [], 0
                 for role in group:
                     d, t, k, m = roles[role]
@@ -1217,7 +1225,8 @@ def run_decode(args):
         "metric": "decode tok/s", "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms / steps, 5), "higher_is_better": True, "scaling": "strong" if shard else "weak", "vs_baseline": None,
         "dtype": "int8 dot (dp4a) + f32 scales; f16 KV", "data": "synthetic",
-        "config": {"workload": sh["name"], "prompt_tokens": prompt_len, "decoded_tokens": steps, "n_ctx": n_ctx,
+        "config": {"workload": sh["name"] + (" (--mix: attn_v and ffn_down of every other layer Q6_K)" if MIX_Q6_K else ""),
+                   "prompt_tokens": prompt_len, "decoded_tokens": steps, "n_ctx": n_ctx,
                    "launch": ("one persistent kernel per token plus the output head" if args.one_kernel else "one CUDA-graph replay per token")
                              + "; the next token id is fed back on the device",
                    "l2_policy": f"inputs larger than L2: {weight_bytes * (world if shard else 1) / 1e9:.2f} GB of weights streamed per token",
@@ -1406,7 +1415,11 @@ def main():
     ap.add_argument("--one-kernel", action="store_true",
                     help="decode workloads: run the headline through the one-kernel step (every layer of a token in one "
                          "persistent kernel) instead of the launch chain")
+    ap.add_argument("--mix", action="store_true",
+                    help="decode workloads: attn_v and ffn_down of every other layer as Q6_K instead of Q4_K")
     args = ap.parse_args()
+    global MIX_Q6_K
+    MIX_Q6_K = args.mix
     args.warmup = max(3, args.warmup)
     decode = args.workload.startswith("decode")
     if args.workload == "prefill_q4_k":

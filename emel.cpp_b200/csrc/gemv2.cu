@@ -802,15 +802,16 @@ gemv3_kernel(const GemvArgs p) {
           const float other = __shfl_sync(0xffffffffu, acc, ((r4 ^ 1) << 3));
           if (b == 0 && row < mseg) {
             const int hd = p.rope_head_dim, head = row / hd, d = row - head * hd;
+            const int rseg = seg + p.rope_seg0;    // 0: query rows, 1: key rows, 2: value rows
             float out = acc;
-            if (seg < 2 && d < p.rope_rot_dim) {
+            if (rseg < 2 && d < p.rope_rot_dim) {
               const int pos = *p.rope_pos, pairs = p.rope_rot_dim >> 1;
               const float cs = p.rope_cos[(int64_t)pos * pairs + (d >> 1)], sn = p.rope_sin[(int64_t)pos * pairs + (d >> 1)];
               out = (d & 1) ? __fadd_rn(__fmul_rn(other, sn), __fmul_rn(acc, cs)) : __fsub_rn(__fmul_rn(acc, cs), __fmul_rn(other, sn));
             }
-            if (seg == 0) yseg[row] = out;
+            if (rseg == 0) yseg[row] = out;
             else {
-              __half* cache = seg == 1 ? p.rope_kcache : p.rope_vcache;
+              __half* cache = rseg == 1 ? p.rope_kcache : p.rope_vcache;
               cache[(int64_t)head * p.rope_cache_head_stride + (int64_t)(*p.rope_pos) * hd + d] = __float2half_rn(out);
             }
           }

@@ -86,6 +86,7 @@ struct GemvArgs {
   const float* rope_sin;
   const int* rope_pos;
   int rope_head_dim, rope_rot_dim;
+  int rope_seg0;           // which of Q / K / V the launch's first matrix is (a group split by weight type)
   __half* rope_kcache;     // this layer's cache planes, [kv head][capacity][head_dim]
   __half* rope_vcache;
   int64_t rope_cache_head_stride;

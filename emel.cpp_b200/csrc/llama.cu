@@ -390,6 +390,23 @@ struct Enqueue {
   bool normed_matvec_group(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax = false,
                            int rope_layer = -1, int in_join = 0) {
     const bool fuse = group_fusable(x, nw, w, n);
+    if (!fuse && n == 3 && rope_layer >= 0 && !argmax && in_join == 0 && s->G == 1) {
+      // Q / K / V of different weight types (a Q6_K value projection beside Q4_K ones): one launch per run of equal
+      // types, each with the normalisation in its prologue and its part of the RoPE / KV-store epilogue
+      const emelb_llama_config& cfg = s->cfg;
+      int first[4] = {0, 0, 0, 0}, runs = 0;
+      for (int i = 0; i < 3; ++i)
+        if (i == 0 || w[i]->type != w[i - 1]->type) first[runs++] = i;
+      first[runs] = 3;
+      bool all = !cfg.rope_neox && cfg.head_dim % 2 == 0;
+      for (int r = 0; all && r < runs; ++r) all = group_fusable(x, nw, w + first[r], first[r + 1] - first[r]);
+      for (int i = 0; all && i < 3; ++i) all = w[i]->M % cfg.head_dim == 0;
+      if (all) {
+        for (int r = 0; r < runs; ++r) fused_group_launch(x, nw, w + first[r], y + first[r], first[r + 1] - first[r], false, rope_layer, 0, first[r]);
+        s->planes_src = nullptr;
+        return true;
+      }
+    }
     if (!fuse) {
       rms_norm(x, nw, family_of(w[0]->type));
       if (n == 1) matvec(*w[0], s->norm, y ? y[0] : nullptr, nullptr, argmax);
@@ -398,6 +415,17 @@ struct Enqueue {
     }
     const emelb_llama_config& cfg = s->cfg;
     const bool rope = rope_layer >= 0 && n == 3 && !cfg.rope_neox && cfg.head_dim % 2 == 0 && w[0]->M % cfg.head_dim == 0;
+    fused_group_launch(x, nw, w, y, n, argmax, rope ? rope_layer : -1, in_join, 0);
+    s->planes_src = nullptr;
+    return rope;
+  }
+
+  // one launch of the streaming kernel for 1-3 matrices of one type with the rms_norm prologue; rope_layer >= 0 adds the
+  // RoPE / KV-store epilogue, seg0 saying which of Q / K / V the first matrix is
+  void fused_group_launch(const float* x, const Tensor& nw, const Tensor* const* w, float* const* y, int n, bool argmax,
+                          int rope_layer, int in_join, int seg0) {
+    const emelb_llama_config& cfg = s->cfg;
+    const bool rope = rope_layer >= 0;
     GemvArgs a{};
     a.W = w[0]->dev;
     a.row_bytes = w[0]->row_bytes;
@@ -419,6 +447,7 @@ struct Enqueue {
       a.rope_pos = s->state + 1;
       a.rope_head_dim = cfg.head_dim;
       a.rope_rot_dim = cfg.rope_dim < cfg.head_dim ? cfg.rope_dim : cfg.head_dim;
+      a.rope_seg0 = seg0;
       a.rope_kcache = s->kcache + layer_off;
       a.rope_vcache = s->vcache + layer_off;
       a.rope_cache_head_stride = s->capacity * cfg.head_dim;
@@ -431,8 +460,6 @@ struct Enqueue {
     a.best_val = s->c->best_val;
     a.best_idx = s->c->best_idx;
     check(launch_gemv(w[0]->type, a, 1, argmax, s->c->sm_count, st, &launches));
-    s->planes_src = nullptr;
-    return rope;
   }
 
   // attention of one layer; when the split-KV kernels run unsharded, their merge step also leaves the

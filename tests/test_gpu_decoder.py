@@ -71,6 +71,10 @@ def be():
 @pytest.mark.parametrize("cfg,types", [
     (TINY, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K}),
     (MIXED, {"embd": eb.Q8_0, "output": eb.Q8_0, "default": eb.Q8_0, el.ATTN_K: eb.Q4_K, el.FFN_DOWN: eb.Q4_0}),
+    # Q6_K value and down projections beside Q4_K: Q/K and V run as two fused launches, each with its share of the
+    # RoPE / KV-store epilogue; and a Q6_K query projection (three runs of one matrix each)
+    (MIXED, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K, el.ATTN_V: eb.Q6_K, el.FFN_DOWN: eb.Q6_K}),
+    (MIXED, {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K, el.ATTN_K: eb.Q6_K}),
 ])
 def test_greedy_decode_matches_reference_loop(be, port, cfg, types):
     sess, cpu = build_model(be, port, cfg, types, seed=5)
