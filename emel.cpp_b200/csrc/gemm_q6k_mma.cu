@@ -10,7 +10,7 @@
 // multiplies the MMA's exact int32 result on the CUDA cores and the float chain is the mat-vec kernels': same bits.
 //
 // CTA = WARPS x 16 weight rows x NT x 8 columns, one super-block of K per turn.  Q6_K blocks are 210 bytes, so a
-// block starts at any even offset: the ring (two stages, cp.async) holds for every row the 224-byte, 16-byte
+// block starts at any even offset: cp.async brings for every row the 224-byte, 16-byte
 // aligned window that covers the block (rows are 16-byte multiples -- K is a multiple of 2048 -- so the window
 // never leaves the row), and a cooperative pass expands ql / qh from there into one int8 value per weight, K-major,
 // which the A fragments are read from with ldmatrix.  Scales and d are read from the raw window.
@@ -26,11 +26,10 @@ namespace {
 
 constexpr int kRawWin = 224, kRawRow = kRawWin + 16;   // 240 bytes per row and stage
 constexpr int kERow6 = QK_K + 16;                      // 272 bytes = 68 words: 8 rows x 16 bytes fall on 32 banks
-constexpr int kStages6 = 2;
 
-template <int NT, int WARPS>
-struct Q6Stage {
-  uint8_t w[16 * WARPS][kRawRow];
+// the activation side of a turn: NT x 8 columns of one super-block and their scales (double buffered)
+template <int NT>
+struct Q6XStage {
   int8_t x[NT * 8][kERow6];
   float dx[NT * 8];
 };
@@ -61,26 +60,31 @@ __device__ __forceinline__ uint32_t lds32_even(const uint8_t* p) {
 // per byte: value (0..63) - 32 as int8
 __device__ __forceinline__ uint32_t minus_32(uint32_t v) { return ((v | 0x80808080u) - 0x20202020u) ^ 0x80808080u; }
 
-template <int NT, int WARPS>
+// Shared memory: a ring of RS raw windows per row (a window is refilled as soon as it has been expanded, so the copies
+// run under the MMA loops), the expanded block, RS + 1 activation stages.  64 columns: RS = 1, 67 KB, three CTAs per
+// SM, the MMA loop is long enough to cover one copy; 16 and 32 columns: short loops, deeper rings.
+template <int NT, int WARPS, int RS>
 __global__ void __launch_bounds__(32 * WARPS) gemm_q6k_mma_kernel(const GemvArgs p, int ncols) {
-  using Stage = Q6Stage<NT, WARPS>;
+  using XStage = Q6XStage<NT>;
   constexpr int kRows = 16 * WARPS, kThreads = 32 * WARPS, kCols = NT * 8;
   extern __shared__ __align__(16) unsigned char smem_q6m[];
-  Stage* stages = reinterpret_cast<Stage*>(smem_q6m);
-  int8_t (*e)[kERow6] = reinterpret_cast<int8_t (*)[kERow6]>(smem_q6m + kStages6 * sizeof(Stage));
+  uint8_t (*raws)[kRows][kRawRow] = reinterpret_cast<uint8_t (*)[kRows][kRawRow]>(smem_q6m);
+  int8_t (*e)[kERow6] = reinterpret_cast<int8_t (*)[kERow6]>(smem_q6m + RS * kRows * kRawRow);
+  XStage* xs = reinterpret_cast<XStage*>(smem_q6m + RS * kRows * kRawRow + kRows * kERow6);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * kRows, c0 = blockIdx.y * kCols;
   const int nsb = p.K / QK_K;
 
   // rows and columns past the edge are read from the last valid one (their results are never stored)
-  auto issue = [&](int sb, Stage& st) {
+  auto issue = [&](int sb) {
     const int64_t win = ((int64_t)sb * Q6_K_BYTES) & ~(int64_t)15;   // the same for every row: rows are 16-byte multiples
     constexpr int kWPieces = kRawWin / 16;                            // 14
     for (int idx = tid; idx < kRows * kWPieces; idx += kThreads) {
       const int r = idx / kWPieces, piece = idx - r * kWPieces;
       const int row = min(row0 + r, p.M - 1);
-      cp_async16(&st.w[r][16 * piece], p.W + (int64_t)row * p.row_bytes + win + 16 * piece);
+      cp_async16(&raws[sb % RS][r][16 * piece], p.W + (int64_t)row * p.row_bytes + win + 16 * piece);
     }
+    XStage& st = xs[sb % (RS + 1)];
     constexpr int kXPieces = QK_K / 16;                               // 16
     for (int idx = tid; idx < kCols * kXPieces; idx += kThreads) {
       const int c = idx / kXPieces, piece = idx - c * kXPieces;
@@ -100,25 +104,27 @@ __global__ void __launch_bounds__(32 * WARPS) gemm_q6k_mma_kernel(const GemvArgs
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
 
-  issue(0, stages[0]);
+#pragma unroll
+  for (int s0 = 0; s0 < RS; ++s0) {
+    if (s0 < nsb) issue(s0);
+    else cp_async_commit();
+  }
   const int ra = warp * 16 + g, rb = ra + 8;
   // ldmatrix row addresses: A -- matrices (rows 0-7, group j), (rows 8-15, j), (rows 0-7, j+1), (rows 8-15, j+1);
   // B -- matrix m = group 4jj + m of the n-tile's eight columns
   const uint32_t a_lane = smem6(&e[warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][16 * (lane >> 4)]);
   for (int sb = 0; sb < nsb; ++sb) {
-    if (sb + 1 < nsb) {
-      issue(sb + 1, stages[(sb + 1) % kStages6]);   // that stage's readers finished before the barrier that ended the last turn
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    cp_async_wait<RS - 1>();
     __syncthreads();
-    const Stage& st = stages[sb % kStages6];
+    const XStage& st = xs[sb % (RS + 1)];
+    uint8_t (*raw)[kRawRow] = raws[sb % RS];
     const int off = (sb * Q6_K_BYTES) & 15;         // of the block inside its window (even)
-    // expand: item = (row, half n of the block, word i of that half's 32 byte positions) -> four words of q - 32
-    for (int idx = tid; idx < kRows * 16; idx += kThreads) {
-      const int r = idx >> 4, n = (idx >> 3) & 1, i = idx & 7;
-      const uint8_t* blk = &st.w[r][off];
+    // expand: item = (row, half n of the block, word i of that half's 32 byte positions) -> four words of q - 32.
+    // A warp's 32 items are word i of rows R, R+2, R+4, R+6 for one n: 32 different banks for every load and store
+    // (row strides of 60 and 68 words)
+    for (int grp = warp; grp < kRows / 2; grp += WARPS) {
+      const int n = grp & 1, r = 8 * (grp >> 2) + ((grp >> 1) & 1) + 2 * (lane >> 3), i = lane & 7;
+      const uint8_t* blk = &raw[r][off];
       const uint32_t qa = lds32_even(blk + 64 * n + 4 * i), qb = lds32_even(blk + 64 * n + 32 + 4 * i);
       const uint32_t qh = lds32_even(blk + 128 + 32 * n + 4 * i);
       uint32_t* out = reinterpret_cast<uint32_t*>(&e[r][128 * n + 4 * i]);
@@ -127,14 +133,20 @@ __global__ void __launch_bounds__(32 * WARPS) gemm_q6k_mma_kernel(const GemvArgs
       out[16] = minus_32(((qa >> 4) & 0x0f0f0f0fu) | (((qh >> 4) & 0x03030303u) << 4));
       out[24] = minus_32(((qb >> 4) & 0x0f0f0f0fu) | (((qh >> 6) & 0x03030303u) << 4));
     }
-    __syncthreads();
-    // the sixteen int8 scales of the two rows this thread holds results for
+    // the sixteen int8 scales and d of the two rows this thread holds results for
     uint32_t sa[4], sw[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      sa[k] = lds32_even(&st.w[ra][off + 192 + 4 * k]);
-      sw[k] = lds32_even(&st.w[rb][off + 192 + 4 * k]);
+      sa[k] = lds32_even(&raw[ra][off + 192 + 4 * k]);
+      sw[k] = lds32_even(&raw[rb][off + 192 + 4 * k]);
     }
+    const float da = h2f(*reinterpret_cast<const uint16_t*>(&raw[ra][off + 208]));
+    const float db = h2f(*reinterpret_cast<const uint16_t*>(&raw[rb][off + 208]));
+    __syncthreads();
+    // this raw window is free, and so is the activation stage of the turn before: the copies for RS turns ahead
+    // run under the MMA loops
+    if (sb + RS < nsb) issue(sb + RS);
+    else cp_async_commit();
     int isum[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -166,8 +178,6 @@ __global__ void __launch_bounds__(32 * WARPS) gemm_q6k_mma_kernel(const GemvArgs
         }
       }
     }
-    const float da = h2f(*reinterpret_cast<const uint16_t*>(&st.w[ra][off + 208]));
-    const float db = h2f(*reinterpret_cast<const uint16_t*>(&st.w[rb][off + 208]));
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -177,7 +187,8 @@ __global__ void __launch_bounds__(32 * WARPS) gemm_q6k_mma_kernel(const GemvArgs
         acc[nt][2 + i] = __fadd_rn(acc[nt][2 + i], __fmul_rn(__fmul_rn(dx, db), (float)isum[nt][2 + i]));
       }
     }
-    __syncthreads();  // the expanded block and this stage are free for the next turn
+    // no barrier here: the one at the top of the next turn separates this turn's reads of the expanded block and of
+    // this activation stage from their next writers (the expansion of turn sb+1, the copies issued in turn sb+1)
   }
 
   const int ya = row0 + ra, yb = row0 + rb;
@@ -193,13 +204,13 @@ __global__ void __launch_bounds__(32 * WARPS) gemm_q6k_mma_kernel(const GemvArgs
   }
 }
 
-template <int NT, int WARPS>
+template <int NT, int WARPS, int RS>
 cudaError_t launch_q6(const GemvArgs& a, int ncols, cudaStream_t st) {
   constexpr int kRows = 16 * WARPS;
-  const int smem = (int)(kStages6 * sizeof(Q6Stage<NT, WARPS>) + (size_t)kRows * kERow6);
-  cudaError_t e = cudaFuncSetAttribute(gemm_q6k_mma_kernel<NT, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  const int smem = (int)((RS + 1) * sizeof(Q6XStage<NT>) + (size_t)kRows * (RS * kRawRow + kERow6));
+  cudaError_t e = cudaFuncSetAttribute(gemm_q6k_mma_kernel<NT, WARPS, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  gemm_q6k_mma_kernel<NT, WARPS><<<dim3((a.M + kRows - 1) / kRows, (ncols + NT * 8 - 1) / (NT * 8)), 32 * WARPS, smem, st>>>(a, ncols);
+  gemm_q6k_mma_kernel<NT, WARPS, RS><<<dim3((a.M + kRows - 1) / kRows, (ncols + NT * 8 - 1) / (NT * 8)), 32 * WARPS, smem, st>>>(a, ncols);
   return cudaGetLastError();
 }
 
@@ -214,10 +225,11 @@ bool gemm_q6k_mma_supported(int type, const GemvArgs& a, int ncols) {
 
 cudaError_t launch_gemm_q6k_mma(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
   (void)sm_count;
-  // column tile by column count: 16, 32 or 64 columns per CTA; 64-row tiles keep two CTAs on an SM
-  if (ncols <= 16) return launch_q6<2, 4>(a, ncols, st);
-  if (ncols <= 32) return launch_q6<4, 4>(a, ncols, st);
-  return launch_q6<8, 4>(a, ncols, st);
+  // column tile by column count: 16, 32 or 64 columns per CTA, 64 rows (32-row tiles for small grids measured no
+  // faster: a CTA's walk along K is what takes the time there, and K cannot be split -- the sums are ordered)
+  if (ncols <= 16) return launch_q6<2, 4, 3>(a, ncols, st);
+  if (ncols <= 32) return launch_q6<4, 4, 2>(a, ncols, st);
+  return launch_q6<8, 4, 1>(a, ncols, st);
 }
 
 }  // namespace emelb
