@@ -4,7 +4,7 @@
 // sumf += (float)sumi * (d_w * d_x), block after block), so a tensor-core instruction can cover exactly one block:
 // mma.sync.m16n8k32 (s8 x s8 -> s32) gives the 32-term integer sums of 16 rows x 8 columns, and the CUDA
 // cores apply the two scales and add the blocks up in ascending order with the reference's roundings — the
-// same bits as the mat-vec kernels.  The scaling, 4 float operations per product and block, bounds the
+// same bits as the mat-vec kernels — two columns per instruction on the packed f32x2 pipe.  The scaling, 4 float operations per product and block, bounds the
 // kernel, not the MMAs; a tcgen05 tile would only move the same scaling work behind a TMEM load.
 //
 // One CTA = 128 (or, for small grids, 64) weight rows x 64 activation columns, one warp per 16 rows; K is walked in chunks of 8
@@ -38,13 +38,49 @@ struct Q8Stage {
   static constexpr int kRaw = kChunkBlocks * kBB;
   uint8_t a[kTM][kRaw];
   int8_t b[kTN][kRowStride];
-  float dx[kTN][kChunkBlocks];
+  float dx[kChunkBlocks][kTN];   // block-major: the scales of two neighbouring columns are one 8-byte load
 };
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void cp_async4_q8(void* smem, const void* gmem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+
+// Two IEEE round-to-nearest f32 operations per instruction (sm_100 packed arithmetic), lane for lane the scalar
+// result.  One trap, measured: a mul.rn.f32x2 whose only use is an add.rn.f32x2 comes out of ptxas (12.9) as one
+// fused multiply-add -- a single rounding -- in spite of the .rn modifiers and of -fmad=false.  The sum is therefore
+// written as fma(prod, 1.0, acc) with a 1.0 the assembler cannot see through: prod * 1 + acc rounds once, exactly as
+// prod + acc does, and the product keeps its own rounding
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ float2 unpack_f32x2(unsigned long long v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
 }
 
 // 4 bytes at a 2-byte aligned shared-memory address
@@ -78,22 +114,25 @@ __global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_ke
       const int col = p.col0 + min(c0 + c, ncols - 1);
       cp_async16(&st.b[c][16 * piece], p.act.qs + (int64_t)col * p.act.col_stride_qs + (int64_t)kc * kChunk + 16 * piece);
     }
-    for (int idx = tid; idx < kTN * 2; idx += kThreadsQ8) {
-      const int c = idx >> 1, half = idx & 1;
+    for (int idx = tid; idx < kTN * kChunkBlocks; idx += kThreadsQ8) {
+      const int c = idx / kChunkBlocks, b = idx - c * kChunkBlocks;
       const int col = p.col0 + min(c0 + c, ncols - 1);
-      cp_async16(&st.dx[c][4 * half], p.act.d + (int64_t)col * p.act.col_stride_d + kc * kChunkBlocks + 4 * half);
+      cp_async4_q8(&st.dx[b][c], p.act.d + (int64_t)col * p.act.col_stride_d + kc * kChunkBlocks + b);
     }
     cp_async_commit();
   };
 
-  float acc[kTN / 8][4];
+  // results as pairs of neighbouring columns: [0] row g, [1] row g+8.  The scaling runs on the packed f32x2
+  // instructions (two IEEE-rounded operations per instruction: the same bits as the scalar chain)
+  unsigned long long acc[kTN / 8][2];
 #pragma unroll
-  for (int nt = 0; nt < kTN / 8; ++nt)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+  for (int nt = 0; nt < kTN / 8; ++nt) acc[nt][0] = acc[nt][1] = 0ull;
 
   issue(0, stages[0]);
   const int ra = warp * 16 + g, rb = ra + 8;
+  // 1.0 in both lanes, as a value the assembler cannot know: prod * 1 + acc rounds once, exactly as prod + acc does
+  const float one = p.K > 0 ? 1.0f : 2.0f;
+  const unsigned long long one2 = pack_f32x2(one, one);
   for (int kc = 0; kc < chunks; ++kc) {
     if (kc + 1 < chunks) {
       issue(kc + 1, stages[(kc + 1) % kStagesQ8]);   // that buffer's readers finished before the barrier below (last turn)
@@ -108,6 +147,7 @@ __global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_ke
       const uint8_t* ba = &st.a[ra][b * Stage::kBB];
       const uint8_t* bb = &st.a[rb][b * Stage::kBB];
       const float dwa = h2f(*reinterpret_cast<const uint16_t*>(ba)), dwb = h2f(*reinterpret_cast<const uint16_t*>(bb));
+      const unsigned long long dwa2 = pack_f32x2(dwa, dwa), dwb2 = pack_f32x2(dwb, dwb);
       uint32_t af[4];
       if constexpr (T == T_Q8_0) {
         af[0] = lds32_h(ba + 2 + 4 * t);
@@ -128,11 +168,9 @@ __global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_ke
         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&st.b[nt * 8 + g][b * QK32 + 16 + 4 * t]);
         int c[4] = {0, 0, 0, 0};
         mma_s8(c, af, b0, b1);
-        const float dx0 = st.dx[nt * 8 + 2 * t][b], dx1 = st.dx[nt * 8 + 2 * t + 1][b];
-        acc[nt][0] = __fadd_rn(acc[nt][0], __fmul_rn((float)c[0], __fmul_rn(dwa, dx0)));
-        acc[nt][1] = __fadd_rn(acc[nt][1], __fmul_rn((float)c[1], __fmul_rn(dwa, dx1)));
-        acc[nt][2] = __fadd_rn(acc[nt][2], __fmul_rn((float)c[2], __fmul_rn(dwb, dx0)));
-        acc[nt][3] = __fadd_rn(acc[nt][3], __fmul_rn((float)c[3], __fmul_rn(dwb, dx1)));
+        const unsigned long long dx = *reinterpret_cast<const unsigned long long*>(&st.dx[b][nt * 8 + 2 * t]);
+        acc[nt][0] = fma_f32x2(mul_f32x2(pack_f32x2((float)c[0], (float)c[1]), mul_f32x2(dwa2, dx)), one2, acc[nt][0]);
+        acc[nt][1] = fma_f32x2(mul_f32x2(pack_f32x2((float)c[2], (float)c[3]), mul_f32x2(dwb2, dx)), one2, acc[nt][1]);
       }
     }
     __syncthreads();  // this stage is free for the copy issued two turns from now
@@ -145,8 +183,9 @@ __global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_ke
     for (int i = 0; i < 2; ++i) {
       const int c = c0 + nt * 8 + 2 * t + i;
       if (c >= ncols) continue;
-      if (ya < p.M) p.y[(int64_t)ya * p.ldy + p.col0 + c] = acc[nt][i];
-      if (yb < p.M) p.y[(int64_t)yb * p.ldy + p.col0 + c] = acc[nt][2 + i];
+      const float2 va = unpack_f32x2(acc[nt][0]), vb = unpack_f32x2(acc[nt][1]);
+      if (ya < p.M) p.y[(int64_t)ya * p.ldy + p.col0 + c] = i ? va.y : va.x;
+      if (yb < p.M) p.y[(int64_t)yb * p.ldy + p.col0 + c] = i ? vb.y : vb.x;
     }
   }
 }
