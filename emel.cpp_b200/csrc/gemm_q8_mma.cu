@@ -24,15 +24,15 @@ namespace emelb {
 
 namespace {
 
-constexpr int kTN = 64, kChunkBlocks = 8, kChunk = kChunkBlocks * QK32;
+constexpr int kChunkBlocks = 8, kChunk = kChunkBlocks * QK32;
 constexpr int kRowStride = kChunk + 16;  // bytes: fragment loads of 8 rows x 4 lanes hit 32 distinct banks
-constexpr int kStagesQ8 = 2;
 
 // One stage of the ring: the weight rows as they lie in memory (8 blocks = 272 B of Q8_0 or 144 B of Q4_0 per
 // row, copied 16 bytes at a time by cp.async; both row strides put 8 rows x 4 lanes on distinct banks), the
 // activation rows and their block scales.
-template <int T, int WARPS>
+template <int T, int WARPS, int NT>
 struct Q8Stage {
+  static constexpr int kTN = NT * 8;
   static constexpr int kTM = 16 * WARPS;
   static constexpr int kBB = T == T_Q8_0 ? Q8_0_BYTES : Q4_0_BYTES;
   static constexpr int kRaw = kChunkBlocks * kBB;
@@ -91,13 +91,17 @@ __device__ __forceinline__ uint32_t lds32_h(const uint8_t* p) {
 // per byte: nibble value (0..15) - 8 as int8
 __device__ __forceinline__ uint32_t nibbles_minus_8(uint32_t v) { return ((v | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
-template <int T, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_kernel(const GemvArgs p, int ncols) {
-  using Stage = Q8Stage<T, WARPS>;
-  constexpr int kTM = Stage::kTM, kThreadsQ8 = 32 * WARPS;
+// NT x 8 columns per CTA (8 .. 64: few columns are a memory-bound walk over the weights, so narrow tiles with a deeper
+// ring and more CTAs per SM), STAGES ring slots.  WARPS x CW warps: warp (r, c) holds rows 16r.. of column group c
+// (NT / CW n-tiles), so that a tile of a few dozen columns still puts enough warps on an SM to cover its latencies
+template <int T, int WARPS, int NT, int STAGES, int CW>
+__global__ void __launch_bounds__(32 * WARPS * CW) gemm_q8_mma_kernel(const GemvArgs p, int ncols) {
+  using Stage = Q8Stage<T, WARPS, NT>;
+  constexpr int kTM = Stage::kTM, kThreadsQ8 = 32 * WARPS * CW, kTN = NT * 8, NTW = NT / CW;
+  static_assert(NT % CW == 0, "column groups must divide the tile");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Stage* stages = reinterpret_cast<Stage*>(smem_raw);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) % WARPS, cgrp = (tid >> 5) / WARPS, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * kTM, c0 = blockIdx.y * kTN;
   const int chunks = p.K / kChunk;
 
@@ -124,24 +128,26 @@ __global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_ke
 
   // results as pairs of neighbouring columns: [0] row g, [1] row g+8.  The scaling runs on the packed f32x2
   // instructions (two IEEE-rounded operations per instruction: the same bits as the scalar chain)
-  unsigned long long acc[kTN / 8][2];
+  unsigned long long acc[NTW][2];
 #pragma unroll
-  for (int nt = 0; nt < kTN / 8; ++nt) acc[nt][0] = acc[nt][1] = 0ull;
+  for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = 0ull;
 
-  issue(0, stages[0]);
+#pragma unroll
+  for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+    if (s0 < chunks) issue(s0, stages[s0]);
+    else cp_async_commit();
+  }
   const int ra = warp * 16 + g, rb = ra + 8;
   // 1.0 in both lanes, as a value the assembler cannot know: prod * 1 + acc rounds once, exactly as prod + acc does
   const float one = p.K > 0 ? 1.0f : 2.0f;
   const unsigned long long one2 = pack_f32x2(one, one);
   for (int kc = 0; kc < chunks; ++kc) {
-    if (kc + 1 < chunks) {
-      issue(kc + 1, stages[(kc + 1) % kStagesQ8]);   // that buffer's readers finished before the barrier below (last turn)
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    // the slot refilled here was read in the turn before; every warp has passed the barrier that ended it
+    if (kc + STAGES - 1 < chunks) issue(kc + STAGES - 1, stages[(kc + STAGES - 1) % STAGES]);
+    else cp_async_commit();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
-    const Stage& st = stages[kc % kStagesQ8];
+    const Stage& st = stages[kc % STAGES];
 #pragma unroll
     for (int b = 0; b < kChunkBlocks; ++b) {
       const uint8_t* ba = &st.a[ra][b * Stage::kBB];
@@ -163,25 +169,26 @@ __global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_ke
         af[3] = nibbles_minus_8((qb >> 4) & 0x0f0f0f0fu);
       }
 #pragma unroll
-      for (int nt = 0; nt < kTN / 8; ++nt) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&st.b[nt * 8 + g][b * QK32 + 4 * t]);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&st.b[nt * 8 + g][b * QK32 + 16 + 4 * t]);
+      for (int nt = 0; nt < NTW; ++nt) {
+        const int cb = (cgrp * NTW + nt) * 8;   // first column of this n-tile inside the CTA's tile
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&st.b[cb + g][b * QK32 + 4 * t]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&st.b[cb + g][b * QK32 + 16 + 4 * t]);
         int c[4] = {0, 0, 0, 0};
         mma_s8(c, af, b0, b1);
-        const unsigned long long dx = *reinterpret_cast<const unsigned long long*>(&st.dx[b][nt * 8 + 2 * t]);
+        const unsigned long long dx = *reinterpret_cast<const unsigned long long*>(&st.dx[b][cb + 2 * t]);
         acc[nt][0] = fma_f32x2(mul_f32x2(pack_f32x2((float)c[0], (float)c[1]), mul_f32x2(dwa2, dx)), one2, acc[nt][0]);
         acc[nt][1] = fma_f32x2(mul_f32x2(pack_f32x2((float)c[2], (float)c[3]), mul_f32x2(dwb2, dx)), one2, acc[nt][1]);
       }
     }
-    __syncthreads();  // this stage is free for the copy issued two turns from now
+    __syncthreads();  // this stage is free for the copy issued at the top of the next turn
   }
 
   const int ya = row0 + ra, yb = row0 + rb;
 #pragma unroll
-  for (int nt = 0; nt < kTN / 8; ++nt) {
+  for (int nt = 0; nt < NTW; ++nt) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const int c = c0 + nt * 8 + 2 * t + i;
+      const int c = c0 + (cgrp * NTW + nt) * 8 + 2 * t + i;
       if (c >= ncols) continue;
       const float2 va = unpack_f32x2(acc[nt][0]), vb = unpack_f32x2(acc[nt][1]);
       if (ya < p.M) p.y[(int64_t)ya * p.ldy + p.col0 + c] = i ? va.y : va.x;
@@ -190,28 +197,34 @@ __global__ void __launch_bounds__(32 * WARPS, 512 / (32 * WARPS)) gemm_q8_mma_ke
   }
 }
 
-template <int T, int WARPS>
+template <int T, int WARPS, int NT, int STAGES, int CW>
 cudaError_t launch_w(const GemvArgs& a, int ncols, cudaStream_t st) {
-  constexpr int kTM = 16 * WARPS;
-  const int smem = (int)(kStagesQ8 * sizeof(Q8Stage<T, WARPS>));
-  cudaError_t e = cudaFuncSetAttribute(gemm_q8_mma_kernel<T, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  constexpr int kTM = 16 * WARPS, kTN = NT * 8;
+  const int smem = (int)(STAGES * sizeof(Q8Stage<T, WARPS, NT>));
+  cudaError_t e = cudaFuncSetAttribute(gemm_q8_mma_kernel<T, WARPS, NT, STAGES, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  gemm_q8_mma_kernel<T, WARPS><<<dim3((a.M + kTM - 1) / kTM, (ncols + kTN - 1) / kTN), 32 * WARPS, smem, st>>>(a, ncols);
+  gemm_q8_mma_kernel<T, WARPS, NT, STAGES, CW><<<dim3((a.M + kTM - 1) / kTM, (ncols + kTN - 1) / kTN), 32 * WARPS * CW, smem, st>>>(a, ncols);
   return cudaGetLastError();
 }
 
-// 128-row tiles; 64-row tiles (4 warps) while the 128-row grid would leave SMs without a CTA pair
+// Many columns: 64-column tiles, 128 rows (64 while the 128-row grid would leave SMs without a CTA pair), two stages.
+// Few columns: 8 / 16 / 32 / 64-column tiles of 64 rows with a deeper ring.  (Spreading a tile's columns over two or
+// four warps per row group, CW > 1, measured slower at 32 and 64 columns: 45.8 against 35.8 us and 62.0 against 56.2
+// us for 14336 x 4096 -- the kernel is bound by instructions per MMA, not by warps in flight)
 template <int T>
 cudaError_t launch_t(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
-  const int64_t big = (int64_t)((a.M + 127) / 128) * ((ncols + kTN - 1) / kTN);
-  return big >= 2 * (int64_t)sm_count ? launch_w<T, 8>(a, ncols, st) : launch_w<T, 4>(a, ncols, st);
+  if (ncols <= 8) return launch_w<T, 4, 1, 4, 1>(a, ncols, st);
+  if (ncols <= 16) return launch_w<T, 4, 2, 4, 1>(a, ncols, st);
+  if (ncols <= 32) return launch_w<T, 4, 4, 3, 1>(a, ncols, st);
+  const int64_t big = (int64_t)((a.M + 127) / 128) * ((ncols + 63) / 64);
+  return big >= 2 * (int64_t)sm_count ? launch_w<T, 8, 8, 2, 1>(a, ncols, st) : launch_w<T, 4, 8, 3, 1>(a, ncols, st);
 }
 
 }  // namespace
 
 bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols) {
   if (type != T_Q8_0 && type != T_Q4_0) return false;
-  if (ncols < kGemmTcMinCols || a.K % kChunk != 0 || a.residual || a.W2 || a.W3 || a.pro_x || a.rope_cos) return false;
+  if (ncols < kGemmQ8MmaMinCols || a.K % kChunk != 0 || a.residual || a.W2 || a.W3 || a.pro_x || a.rope_cos || a.join_in || a.join_out) return false;
   return reinterpret_cast<uintptr_t>(a.W) % 16 == 0 && a.row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.qs) % 16 == 0 &&
          a.act.col_stride_qs % 16 == 0 && reinterpret_cast<uintptr_t>(a.act.d) % 16 == 0;
 }

@@ -227,6 +227,7 @@ cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out
 // same numbers as the mat-vec kernels.  a.col0/a.y/a.ldy address the output as for launch_gemv.
 constexpr int kGemmTcMinCols = 32;
 constexpr int kGemmMmaMinCols = 9;   // fewer columns: the CUDA-core mat-vec kernels
+constexpr int kGemmQ8MmaMinCols = 5; // Q8_0 / Q4_0: from five columns on the mma.sync kernel beats the mat-vec kernels' column loop
 bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act);
 // true when launch_gemv would run the kernel that honours GemvArgs::pro_x for this matrix
 bool gemv_prologue_supported(int type, const void* w, int64_t row_bytes, int K);
