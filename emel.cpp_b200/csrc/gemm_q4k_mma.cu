@@ -490,7 +490,7 @@ cudaError_t launch_nt(const GemvArgs& a, int ncols, cudaStream_t st) {
 }  // namespace
 
 bool gemm_q4k_mma_supported(int type, const GemvArgs& a, int ncols) {
-  if (type != T_Q4_K || ncols < kGemmMmaMinCols || ncols >= kGemmTcMinCols) return false;
+  if (type != T_Q4_K || ncols < kGemmQ4kMmaMinCols || ncols >= kGemmTcMinCols) return false;
   if (a.K % kStageK != 0 || a.pro_x || a.rope_cos || !a.act.bsums) return false;
   const bool grouped = a.W2 || a.W3;
   if (a.residual && (grouped || ncols > 16 || a.K % kStageK16 != 0)) return false;        // the 16-column kernel adds it on store

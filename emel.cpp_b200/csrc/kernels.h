@@ -226,7 +226,8 @@ cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out
 // gemm_tc.cu — Q4_K x Q8_K for many columns on the tensor cores (tcgen05, TMEM accumulators);
 // same numbers as the mat-vec kernels.  a.col0/a.y/a.ldy address the output as for launch_gemv.
 constexpr int kGemmTcMinCols = 32;
-constexpr int kGemmMmaMinCols = 9;   // fewer columns: the CUDA-core mat-vec kernels
+constexpr int kGemmMmaMinCols = 9;   // Q6_K: fewer columns run the CUDA-core mat-vec kernels
+constexpr int kGemmQ4kMmaMinCols = 5; // Q4_K: 8 columns take 39 / 63 us through the mat-vec kernel, 23-28 / 35 us through the mma.sync one (4096x14336 / 14336x4096)
 constexpr int kGemmQ8MmaMinCols = 5; // Q8_0 / Q4_0: from five columns on the mma.sync kernel beats the mat-vec kernels' column loop
 bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act);
 // true when launch_gemv would run the kernel that honours GemvArgs::pro_x for this matrix
