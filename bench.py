@@ -264,7 +264,7 @@ def run_gemv(args):
                             "unit": "TFLOP/s", "frac": round(tf / peaks["bf16_tflops"], 4),
                             "peak_source": f"of {peak_kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms_k * 1e3 / launches, 3),
                             "flops_per_launch": flops, "traffic": None}
-    elif n >= 5 and t == eb.Q8_0:   # the library's threshold for the mma.sync kernel (kGemmQ8MmaMinCols)
+    elif n >= 3 and t == eb.Q8_0:   # the library's threshold for the mma.sync kernel (kGemmQ8MmaMinCols)
         line["dtype"] = "int8 mma.sync (one 32-weight block per instruction) + f32 scales"
         line["roofline"]["kernel"] = f"gemm_q8_mma_n{n}"
     if rank == 0:

@@ -345,18 +345,24 @@ swiglu_quant_cols_kernel(const float* __restrict__ gate, const float* __restrict
   q8_k_store_planes(planes, col, K, blk, lane, lo, hi, bs, dq);
 }
 
-// thread = (token j fastest, rotation pair or copied element, head)
-__global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, const float* __restrict__ v,
-                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pos0, int B,
-                                        int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,
-                                        __half* vcache, int64_t cache_head_stride) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= B) return;
-  const int head = blockIdx.y, pos = pos0 + j, pairs = rot_dim / 2;
+// thread = (token j fastest, rotation pair or copied element, head).  Query heads are rotated in place.  K / V heads
+// go to the f16 cache: the inputs are feature-major (tokens along the lanes) and a cache row is one token's head_dim
+// halves, so storing straight from the registers would put 2 bytes per lane into 32 different rows; with `rows`
+// a 32-token tile of the rotated K head and of the V head is put together in shared memory (2 x 32 x (head_dim + 8)
+// halves) and each warp then writes whole rows, 8 bytes per lane.
+__global__ void __launch_bounds__(256)
+rope_store_batch_kernel(float* q, const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t, int pos0, int B, int n_head, int n_head_kv, int head_dim, int rot_dim,
+                        int neox, __half* kcache, __half* vcache, int64_t cache_head_stride, int rows) {
+  extern __shared__ __align__(16) __half kv_tile[];
+  const int j0 = blockIdx.x * 32, j = j0 + threadIdx.x;
+  const bool live = j < B;
+  const int head = blockIdx.y, pos = pos0 + (live ? j : 0), pairs = rot_dim / 2;
   const float* ct = cos_t + (int64_t)pos * pairs;
   const float* st = sin_t + (int64_t)pos * pairs;
   const int x1_base = neox ? pairs : 1, stride = neox ? 1 : 2;
   if (head < n_head) {
+    if (!live) return;
     float* h = q + (int64_t)head * head_dim * B + j;
     for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
       const int64_t d0 = (int64_t)(p * stride) * B, d1 = (int64_t)(p * stride + x1_base) * B;
@@ -364,12 +370,16 @@ __global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, c
       h[d0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
       h[d1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
     }
-  } else {
-    const int kh = head - n_head;
+    return;
+  }
+  const int kh = head - n_head;
+  const int row = head_dim + 8;
+  // destination of this thread's values: its token's cache rows, or its token's rows of the tile
+  __half* kd = rows ? kv_tile + threadIdx.x * row : kcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+  __half* vd = rows ? kv_tile + (32 + threadIdx.x) * row : vcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
+  if (live) {
     const float* h = k + (int64_t)kh * head_dim * B + j;
     const float* vv = v + (int64_t)kh * head_dim * B + j;
-    __half* kd = kcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
-    __half* vd = vcache + (int64_t)kh * cache_head_stride + (int64_t)pos * head_dim;
     for (int p = threadIdx.y; p < pairs; p += blockDim.y) {
       const int d0 = p * stride, d1 = p * stride + x1_base;
       const float x0 = h[(int64_t)d0 * B], x1 = h[(int64_t)d1 * B], c = ct[p], s = st[p];
@@ -378,6 +388,15 @@ __global__ void rope_store_batch_kernel(float* q, const float* __restrict__ k, c
     }
     for (int d = rot_dim + threadIdx.y; d < head_dim; d += blockDim.y) kd[d] = __float2half_rn(h[(int64_t)d * B]);
     for (int d = threadIdx.y; d < head_dim; d += blockDim.y) vd[d] = __float2half_rn(vv[(int64_t)d * B]);
+  }
+  if (!rows) return;
+  __syncthreads();
+  for (int t = threadIdx.y; t < 32 && j0 + t < B; t += blockDim.y) {
+    const int64_t off = (int64_t)kh * cache_head_stride + (int64_t)(pos0 + j0 + t) * head_dim;
+    for (int d = 4 * threadIdx.x; d < head_dim; d += 128) {
+      *reinterpret_cast<uint2*>(kcache + off + d) = *reinterpret_cast<const uint2*>(kv_tile + t * row + d);
+      *reinterpret_cast<uint2*>(vcache + off + d) = *reinterpret_cast<const uint2*>(kv_tile + (32 + t) * row + d);
+    }
   }
 }
 
@@ -675,8 +694,12 @@ int rms_norm_batch_partials(int B) { return kNormSlices * B; }
 cudaError_t launch_rope_store_batch(float* q, const float* k, const float* v, const float* cos_t, const float* sin_t, int pos0,
                                     int B, int n_head, int n_head_kv, int head_dim, int rot_dim, int neox, __half* kcache,
                                     __half* vcache, int64_t cache_head_stride, cudaStream_t st) {
-  rope_store_batch_kernel<<<dim3((B + 31) / 32, n_head + n_head_kv), dim3(32, 8), 0, st>>>(
-      q, k, v, cos_t, sin_t, pos0, B, n_head, n_head_kv, head_dim, rot_dim, neox, kcache, vcache, cache_head_stride);
+  // cache rows written as rows where the layout allows 8-byte stores
+  const size_t tile_bytes = 2 * 32 * (size_t)(head_dim + 8) * sizeof(__half);
+  const bool rows = head_dim % 4 == 0 && cache_head_stride % 4 == 0 && tile_bytes <= 48 * 1024 &&
+                    reinterpret_cast<uintptr_t>(kcache) % 8 == 0 && reinterpret_cast<uintptr_t>(vcache) % 8 == 0;
+  rope_store_batch_kernel<<<dim3((B + 31) / 32, n_head + n_head_kv), dim3(32, 8), rows ? tile_bytes : 0, st>>>(
+      q, k, v, cos_t, sin_t, pos0, B, n_head, n_head_kv, head_dim, rot_dim, neox, kcache, vcache, cache_head_stride, rows ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -228,7 +228,7 @@ cudaError_t launch_step_advance(int* state, const int* best_idx, int* tokens_out
 constexpr int kGemmTcMinCols = 32;
 constexpr int kGemmMmaMinCols = 9;   // Q6_K: fewer columns run the CUDA-core mat-vec kernels
 constexpr int kGemmQ4kMmaMinCols = 5; // Q4_K: 8 columns take 39 / 63 us through the mat-vec kernel, 23-28 / 35 us through the mma.sync one (4096x14336 / 14336x4096)
-constexpr int kGemmQ8MmaMinCols = 5; // Q8_0 / Q4_0: from five columns on the mma.sync kernel beats the mat-vec kernels' column loop
+constexpr int kGemmQ8MmaMinCols = 3; // Q8_0 / Q4_0: from three columns on the mma.sync kernel (21-24 us for up to 8 columns of 14336x4096) beats the mat-vec kernels (29 us at 4 columns)
 bool gemm_tc_supported(int type, int K, int ncols, const void* W, int64_t row_bytes, const ActPlanes& act);
 // true when launch_gemv would run the kernel that honours GemvArgs::pro_x for this matrix
 bool gemv_prologue_supported(int type, const void* w, int64_t row_bytes, int K);

@@ -41,6 +41,39 @@ quantize_q8_k_kernel(const float* __restrict__ x, int n, int K, ActPlanesMut pla
   }
 }
 
+// Many columns (a prompt batch): one CTA per (256-block, 32 columns).  The input is feature-major, {K, n}: the 256
+// elements of a column's block lie n floats apart, so the kernel above fetches a 32-byte sector for every float.  Here
+// the f32 tile is read with the columns along the lanes (every load a full line), transposed through shared memory, and
+// the warps then quantize one column each exactly as above.
+constexpr int kQTileCols = 32, kQTileRow = QK_K + 4;   // rows stay 16-byte aligned for the float4 reads
+
+__global__ void __launch_bounds__(256)
+quantize_q8_k_cols_kernel(const float* __restrict__ x, int n, int ncols, int K, ActPlanesMut planes) {
+  __shared__ __align__(16) float tile[kQTileCols][kQTileRow];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int blk = blockIdx.x, c0 = blockIdx.y * kQTileCols;
+  const int col = min(c0 + lane, ncols - 1);                // lanes past the edge repeat the last column; never stored
+  const float* src = x + (int64_t)blk * QK_K * n + col;
+#pragma unroll 8
+  for (int j = 0; j < QK_K / 8; ++j) {
+    const int k = warp + 8 * j;
+    tile[lane][k] = src[(int64_t)k * n];
+  }
+  __syncthreads();
+  for (int c = warp; c < kQTileCols && c0 + c < ncols; c += 8) {
+    const float4 a = *reinterpret_cast<const float4*>(&tile[c][8 * lane]);
+    const float4 b = *reinterpret_cast<const float4*>(&tile[c][8 * lane + 4]);
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t lo, hi;
+    int s;
+    float d;
+    q8_k_block_warp(v, lane, lo, hi, s, d);
+    q8_k_store_planes(planes, c0 + c, K, blk, lane, lo, hi, s, d);
+  }
+}
+
 // Eight lanes per 32-block, four elements per lane
 template <bool BLOCKS>
 __global__ void __launch_bounds__(128)
@@ -141,6 +174,11 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ src, int64_t src_r
 }  // namespace
 
 cudaError_t launch_quantize_q8_k_planes(const float* x, int n, int ncols, int K, ActPlanesMut out, cudaStream_t st) {
+  if (ncols >= 16) {
+    const dim3 tiles(K / QK_K, (ncols + kQTileCols - 1) / kQTileCols);
+    EMELB_LAUNCH(quantize_q8_k_cols_kernel, tiles, 256, 0, st, x, n, ncols, K, out);
+    return cudaGetLastError();
+  }
   const dim3 grid((K / QK_K + 3) / 4, ncols);
   EMELB_LAUNCH(quantize_q8_k_kernel<false>, grid, 128, 0, st, x, n, K, out, nullptr, 0);
   return cudaGetLastError();
