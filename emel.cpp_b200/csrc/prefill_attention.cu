@@ -37,10 +37,19 @@ constexpr int kMmaThreads = 128;
 template <int D>
 struct PrefillMmaSmem {
   static constexpr int kRowStride = D + 8;     // halves; rows 16 bytes x 17 apart: 8 rows of a fragment load cover all banks
-  __half q[kRows][kRowStride];
-  __half k[kKT][kRowStride];
-  __half v[kKT][kRowStride];                   // row-major like K; ldmatrix.trans hands out the V fragments
+  // Two K / V stages.  The query tile is needed only until the warps have taken their fragments into registers;
+  // its memory then serves as the second K stage (kRows == kKT), so the double buffering costs one tile, not two
+  __half q_k1[kRows][kRowStride];              // query tile, later K stage 1
+  __half k0[kKT][kRowStride];
+  __half v[2][kKT][kRowStride];                // row-major like K; ldmatrix.trans hands out the V fragments
 };
+static_assert(kRows == kKT, "the query tile doubles as a K stage");
+
+// 16 bytes global -> shared without passing through registers; src_bytes = 0 fills the 16 bytes with zeros
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, int src_bytes) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
+}
 
 // four 8x8 b16 matrices; lane l supplies the address of row l % 8 of matrix l / 8
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row) {
@@ -78,7 +87,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
     const int j = j0 + jt;
     float val = 0.0f;
     if (j < B) val = a.q[((int64_t)(kh * n_rep + rep) * D + d) * B + j];
-    sm.q[rep * QT + jt][d] = __float2half_rn(val);
+    sm.q_k1[rep * QT + jt][d] = __float2half_rn(val);
   }
   __syncthreads();
 
@@ -87,10 +96,10 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
   uint32_t qf[D / 16][4];
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
-    qf[kk][0] = *reinterpret_cast<const uint32_t*>(&sm.q[r0][kk * 16 + 2 * t]);
-    qf[kk][1] = *reinterpret_cast<const uint32_t*>(&sm.q[r1][kk * 16 + 2 * t]);
-    qf[kk][2] = *reinterpret_cast<const uint32_t*>(&sm.q[r0][kk * 16 + 2 * t + 8]);
-    qf[kk][3] = *reinterpret_cast<const uint32_t*>(&sm.q[r1][kk * 16 + 2 * t + 8]);
+    qf[kk][0] = *reinterpret_cast<const uint32_t*>(&sm.q_k1[r0][kk * 16 + 2 * t]);
+    qf[kk][1] = *reinterpret_cast<const uint32_t*>(&sm.q_k1[r1][kk * 16 + 2 * t]);
+    qf[kk][2] = *reinterpret_cast<const uint32_t*>(&sm.q_k1[r0][kk * 16 + 2 * t + 8]);
+    qf[kk][3] = *reinterpret_cast<const uint32_t*>(&sm.q_k1[r1][kk * 16 + 2 * t + 8]);
   }
   int t_row[2];
   {
@@ -111,19 +120,32 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
   const __half* kbase = a.k + (int64_t)kh * a.cache_head_stride;
   const __half* vbase = a.v + (int64_t)kh * a.cache_head_stride;
 
-  for (int t0 = 0; t0 < t_cta; t0 += kKT) {
-    __syncthreads();  // the previous tile's readers are done
+  // cache tile t0 .. t0+63 -> stage `buf`, asynchronously; rows the batch has not written yet are zero-filled
+  auto issue = [&](int t0, int buf) {
+    __half (*kdst)[PrefillMmaSmem<D>::kRowStride] = buf ? sm.q_k1 : sm.k0;
     for (int idx = tid; idx < kKT * (D / 8); idx += kMmaThreads) {
       const int tt = idx / (D / 8), c = idx % (D / 8);
-      uint4 kk = make_uint4(0u, 0u, 0u, 0u), vv = kk;
-      if (t0 + tt < t_written) {
-        kk = *reinterpret_cast<const uint4*>(kbase + (int64_t)(t0 + tt) * D + 8 * c);
-        vv = *reinterpret_cast<const uint4*>(vbase + (int64_t)(t0 + tt) * D + 8 * c);
-      }
-      *reinterpret_cast<uint4*>(&sm.k[tt][8 * c]) = kk;
-      *reinterpret_cast<uint4*>(&sm.v[tt][8 * c]) = vv;
+      const bool live = t0 + tt < t_written;
+      const int64_t off = (int64_t)(live ? t0 + tt : 0) * D + 8 * c;
+      cp_async16_zfill(&kdst[tt][8 * c], kbase + off, live ? 16 : 0);
+      cp_async16_zfill(&sm.v[buf][tt][8 * c], vbase + off, live ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  __syncthreads();   // every warp holds its query fragments: the query tile's memory may become K stage 1
+  if (t_cta > 0) issue(0, 0);
+  int buf = 0;
+  for (int t0 = 0; t0 < t_cta; t0 += kKT, buf ^= 1) {
+    // the other stage was read in the turn before; every warp has passed the barrier that ended that turn
+    if (t0 + kKT < t_cta) {
+      issue(t0 + kKT, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
+    const __half (*ktile)[PrefillMmaSmem<D>::kRowStride] = buf ? sm.q_k1 : sm.k0;
+    const __half (*vtile)[PrefillMmaSmem<D>::kRowStride] = sm.v[buf];
 
     // scores of 16 rows x 64 positions
     float s[kKT / 8][4];
@@ -135,7 +157,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
 #pragma unroll
       for (int kk = 0; kk < D / 16; kk += 2) {
         uint32_t kb[4];
-        ldmatrix_x4(kb, &sm.k[nt * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8 + (lane >> 4) * 16]);
+        ldmatrix_x4(kb, &ktile[nt * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8 + (lane >> 4) * 16]);
         mma_f16(s[nt], qf[kk], kb[0], kb[1]);
         mma_f16(s[nt], qf[kk + 1], kb[2], kb[3]);
       }
@@ -201,13 +223,14 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
 #pragma unroll
       for (int dn = 0; dn < D / 8; dn += 2) {
         uint32_t vb[4];
-        ldmatrix_x4_trans(vb, &sm.v[jj * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][(dn + (lane >> 4)) * 8]);
+        ldmatrix_x4_trans(vb, &vtile[jj * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][(dn + (lane >> 4)) * 8]);
         mma_f16(o[dn], hi, vb[0], vb[1]);
         mma_f16(o[dn], lo, vb[0], vb[1]);
         mma_f16(o[dn + 1], hi, vb[2], vb[3]);
         mma_f16(o[dn + 1], lo, vb[2], vb[3]);
       }
     }
+    __syncthreads();   // this stage is free for the copy issued at the top of the next turn
   }
 
 #pragma unroll
