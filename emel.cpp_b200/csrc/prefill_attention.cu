@@ -80,7 +80,8 @@ __global__ void __launch_bounds__(kMmaThreads, 3) prefill_attention_mma_kernel(c
   PrefillMmaSmem<D>& sm = *reinterpret_cast<PrefillMmaSmem<D>*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int n_rep = a.heads / a.kv_heads, QT = kRows / n_rep;
-  const int kh = blockIdx.y, j0 = blockIdx.x * QT, B = a.B;
+  // token tiles in descending order: a later tile walks more of the cache, and the long walks should start first
+  const int kh = blockIdx.y, j0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * QT, B = a.B;
 
   for (int idx = tid; idx < kRows * D; idx += kMmaThreads) {
     const int jt = idx % QT, d = (idx / QT) % D, rep = idx / (QT * D);
