@@ -243,23 +243,28 @@ __global__ void __launch_bounds__(kThreadsM, 2) gemm_q4k_mma_kernel(const GemvAr
 // V or gate, up) run in one launch: tiles are counted through the segments.
 // The columns' 32-element activation sums (two 16-element sums each) are packed once per stage by the threads that
 // copied them, two per word, as dp2a wants them.
-constexpr int kRows16 = 64, kWarps16 = 16, kThreads16 = 32 * kWarps16, kSbPerStage16 = 4, kStageK16 = kSbPerStage16 * QK_K;
-constexpr int kStages16 = 3;
+// Two shapes of the kernel: RG = 4 row groups (64-row tiles, 16 warps, three stages, one CTA per SM) and RG = 2
+// (32-row tiles, 8 warps, two stages, two CTAs per SM) for matrices whose 64-row tiles would not fill the GPU -- a
+// CTA's walk along K is a chain of dependent turns, so more and smaller CTAs that interleave on an SM finish sooner.
+constexpr int kSbPerStage16 = 4, kStageK16 = kSbPerStage16 * QK_K;
 constexpr int kWPieces16 = kSbPerStage16 * Q4_K_BYTES / 16;                               // 36 per row
-constexpr int kWSlots16 = (kRows16 * kWPieces16 + kThreads16 - 1) / kThreads16;           // 5 copies per thread (the last one half used)
+constexpr int kWSlots16 = 5;   // ceil(16 RG rows x 36 pieces / (128 RG threads)) = ceil(4.5): copies per thread, the last one half used
+constexpr int kSmall16Factor = 8;   // fewer 64-row tiles than this many per SM: the 32-row shape
 constexpr int kWRow16 = kSbPerStage16 * Q4_K_BYTES + 16;   // 592 bytes = 148 words: 20 g + t covers 32 banks
 constexpr int kXRow16 = kStageK16 + 16;                    // 1040 bytes = 260 words: 4 g + t
 
+template <int RG>
 struct Q4Stage16 {
-  uint8_t w[kRows16][kWRow16];
+  uint8_t w[16 * RG][kWRow16];
   int8_t x[16][kXRow16];
   uint8_t bs[16][kSbPerStage16][32];     // raw 16-element sums: 16 int16 per column and super-block
   uint4 pw[16][kSbPerStage16 + 1];       // the same as eight 32-element sums, two per word (80-byte rows: 4 columns on 16 banks)
   float dx[16][kSbPerStage16];
 };
+template <int RG, int STAGES>
 struct Q4Smem16 {
-  Q4Stage16 stage[kStages16];
-  float table[2][4][kSbPerStage16][256];   // [stage parity][row group][super-block of the stage][row * 16 + column]
+  Q4Stage16<RG> stage[STAGES];
+  float table[2][RG][kSbPerStage16][256];   // [stage parity][row group][super-block of the stage][row * 16 + column]
 };
 
 struct Tile16 {
@@ -268,9 +273,12 @@ struct Tile16 {
   int M, row0;
 };
 
-__global__ void __launch_bounds__(kThreads16, 1) gemm_q4k_mma16_kernel(const GemvArgs p, int ncols) {
+template <int RG, int STAGES>
+__global__ void __launch_bounds__(128 * RG, RG == 4 ? 1 : 2) gemm_q4k_mma16_kernel(const GemvArgs p, int ncols) {
+  constexpr int kRows16 = 16 * RG, kThreads16 = 128 * RG, kStages16 = STAGES, kXPer = 1024 / kThreads16;
+  using Q4Stage16 = Q4Stage16<RG>;
   extern __shared__ __align__(16) unsigned char smem_q4m16[];
-  Q4Smem16& sm = *reinterpret_cast<Q4Smem16*>(smem_q4m16);
+  Q4Smem16<RG, STAGES>& sm = *reinterpret_cast<Q4Smem16<RG, STAGES>*>(smem_q4m16);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int rg = warp >> 2, kq = warp & 3;
   const int nstages = p.K / kStageK16;
@@ -294,9 +302,15 @@ __global__ void __launch_bounds__(kThreads16, 1) gemm_q4k_mma16_kernel(const Gem
   // this thread's copies of a stage (16-byte cp.async): tile-independent parts once, the weight rows per tile.
   // Bulk copies (cp.async.bulk, one per 576-byte row piece) were tried instead and ran at half the speed: 112 small
   // copies per stage and SM are more than the copy engine takes without stalling.
-  const int xc0 = tid >> 6, xp = tid & 63;                                   // activation pieces tid and tid + 512
-  const int8_t* xsrc0 = p.act.qs + (int64_t)(p.col0 + min(xc0, ncols - 1)) * p.act.col_stride_qs + 16 * xp;
-  const int8_t* xsrc1 = p.act.qs + (int64_t)(p.col0 + min(xc0 + 8, ncols - 1)) * p.act.col_stride_qs + 16 * xp;
+  // activation pieces tid, tid + threads, ...: 16 columns x 64 pieces of 16 bytes per stage
+  const int8_t* xsrc[kXPer];
+  int xdst[kXPer];
+#pragma unroll
+  for (int q = 0; q < kXPer; ++q) {
+    const int idx = tid + q * kThreads16, xc = idx >> 6, xp = idx & 63;
+    xsrc[q] = p.act.qs + (int64_t)(p.col0 + min(xc, ncols - 1)) * p.act.col_stride_qs + 16 * xp;
+    xdst[q] = xc * kXRow16 + 16 * xp;
+  }
   const int bcol = tid >> 2, bsb = tid & 3;                                   // tid < 64: 32 bytes of sums; 64 <= tid < 80: scales
   const uint8_t* bsrc = reinterpret_cast<const uint8_t*>(p.act.bsums + (int64_t)(p.col0 + min(bcol & 15, ncols - 1)) * p.act.col_stride_bs) + 32 * bsb;
   const float* dsrc = p.act.d + (int64_t)(p.col0 + min(tid & 15, ncols - 1)) * p.act.col_stride_d;
@@ -324,8 +338,8 @@ __global__ void __launch_bounds__(kThreads16, 1) gemm_q4k_mma16_kernel(const Gem
     for (int sl = 0; sl < kWSlots16; ++sl)
       if (sl < kWSlots16 - 1 || tid < kRows16 * kWPieces16 - (kWSlots16 - 1) * kThreads16)
         cp_async16(&st.w[0][0] + wdst[sl], wbase + wsrc[sl]);
-    cp_async16(&st.x[xc0][16 * xp], xsrc0 + (int64_t)ks * kStageK16);
-    cp_async16(&st.x[xc0 + 8][16 * xp], xsrc1 + (int64_t)ks * kStageK16);
+#pragma unroll
+    for (int q = 0; q < kXPer; ++q) cp_async16(&st.x[0][0] + xdst[q], xsrc[q] + (int64_t)ks * kStageK16);
     if (tid < 64) {
       cp_async16(&st.bs[bcol][bsb][0], bsrc + (int64_t)ks * (kStageK16 / 8));
       cp_async16(&st.bs[bcol][bsb][16], bsrc + (int64_t)ks * (kStageK16 / 8) + 16);
@@ -335,7 +349,7 @@ __global__ void __launch_bounds__(kThreads16, 1) gemm_q4k_mma16_kernel(const Gem
     cp_async_commit();
   };
 
-  float acc[2] = {0.0f, 0.0f};   // elements tid and tid + 512 of the tile's 64 x 16 outputs
+  float acc[2] = {0.0f, 0.0f};   // elements tid and tid + threads of the tile's rows x 16 outputs
 #pragma unroll
   for (int s = 0; s < kStages16 - 1; ++s) {
     if (s < total) issue(s);
@@ -456,20 +470,27 @@ __global__ void __launch_bounds__(kThreads16, 1) gemm_q4k_mma16_kernel(const Gem
   cp_async_wait<0>();
 }
 
-cudaError_t launch_16(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
-  const int smem = (int)sizeof(Q4Smem16);
+template <int RG, int STAGES>
+cudaError_t launch_16_rg(const GemvArgs& a, int ncols, cudaStream_t st) {
+  constexpr int kRows16 = 16 * RG;
+  const int smem = (int)sizeof(Q4Smem16<RG, STAGES>);
   static thread_local unsigned configured = 0;  // one bit per device (one context, one lane per host thread)
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(configured & (1u << (dev & 31)))) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_q4k_mma16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const cudaError_t e = cudaFuncSetAttribute(gemm_q4k_mma16_kernel<RG, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured |= 1u << (dev & 31);
   }
   const int tiles = (a.M + kRows16 - 1) / kRows16 + (a.M2 + kRows16 - 1) / kRows16 + (a.M3 + kRows16 - 1) / kRows16;
-  (void)sm_count;   // one CTA per tile measured faster than one CTA per SM walking its tiles (36.8 against 41.1 us for 448 tiles)
-  gemm_q4k_mma16_kernel<<<tiles, kThreads16, smem, st>>>(a, ncols);
+  // one CTA per tile measured faster than one CTA per SM walking its tiles (36.8 against 41.1 us for 448 tiles)
+  gemm_q4k_mma16_kernel<RG, STAGES><<<tiles, 128 * RG, smem, st>>>(a, ncols);
   return cudaGetLastError();
+}
+
+cudaError_t launch_16(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
+  const int tiles64 = (a.M + 63) / 64 + (a.M2 + 63) / 64 + (a.M3 + 63) / 64;
+  return tiles64 < kSmall16Factor * sm_count ? launch_16_rg<2, 2>(a, ncols, st) : launch_16_rg<4, 3>(a, ncols, st);
 }
 
 template <int NT>
