@@ -67,11 +67,6 @@ __device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, un
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
 __device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
   unsigned long long r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
@@ -92,16 +87,14 @@ __device__ __forceinline__ uint32_t lds32_h(const uint8_t* p) {
 __device__ __forceinline__ uint32_t nibbles_minus_8(uint32_t v) { return ((v | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
 // NT x 8 columns per CTA (8 .. 64: few columns are a memory-bound walk over the weights, so narrow tiles with a deeper
-// ring and more CTAs per SM), STAGES ring slots.  WARPS x CW warps: warp (r, c) holds rows 16r.. of column group c
-// (NT / CW n-tiles), so that a tile of a few dozen columns still puts enough warps on an SM to cover its latencies
-template <int T, int WARPS, int NT, int STAGES, int CW>
-__global__ void __launch_bounds__(32 * WARPS * CW) gemm_q8_mma_kernel(const GemvArgs p, int ncols) {
+// ring and more CTAs per SM), STAGES ring slots; one warp per 16 rows
+template <int T, int WARPS, int NT, int STAGES>
+__global__ void __launch_bounds__(32 * WARPS) gemm_q8_mma_kernel(const GemvArgs p, int ncols) {
   using Stage = Q8Stage<T, WARPS, NT>;
-  constexpr int kTM = Stage::kTM, kThreadsQ8 = 32 * WARPS * CW, kTN = NT * 8, NTW = NT / CW;
-  static_assert(NT % CW == 0, "column groups must divide the tile");
+  constexpr int kTM = Stage::kTM, kThreadsQ8 = 32 * WARPS, kTN = NT * 8, NTW = NT, cgrp = 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Stage* stages = reinterpret_cast<Stage*>(smem_raw);
-  const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) % WARPS, cgrp = (tid >> 5) / WARPS, g = lane >> 2, t = lane & 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * kTM, c0 = blockIdx.y * kTN;
   const int chunks = p.K / kChunk;
 
@@ -197,27 +190,27 @@ __global__ void __launch_bounds__(32 * WARPS * CW) gemm_q8_mma_kernel(const Gemv
   }
 }
 
-template <int T, int WARPS, int NT, int STAGES, int CW>
+template <int T, int WARPS, int NT, int STAGES>
 cudaError_t launch_w(const GemvArgs& a, int ncols, cudaStream_t st) {
   constexpr int kTM = 16 * WARPS, kTN = NT * 8;
   const int smem = (int)(STAGES * sizeof(Q8Stage<T, WARPS, NT>));
-  cudaError_t e = cudaFuncSetAttribute(gemm_q8_mma_kernel<T, WARPS, NT, STAGES, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = cudaFuncSetAttribute(gemm_q8_mma_kernel<T, WARPS, NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  gemm_q8_mma_kernel<T, WARPS, NT, STAGES, CW><<<dim3((a.M + kTM - 1) / kTM, (ncols + kTN - 1) / kTN), 32 * WARPS * CW, smem, st>>>(a, ncols);
+  gemm_q8_mma_kernel<T, WARPS, NT, STAGES><<<dim3((a.M + kTM - 1) / kTM, (ncols + kTN - 1) / kTN), 32 * WARPS, smem, st>>>(a, ncols);
   return cudaGetLastError();
 }
 
 // Many columns: 64-column tiles, 128 rows (64 while the 128-row grid would leave SMs without a CTA pair), two stages.
 // Few columns: 8 / 16 / 32 / 64-column tiles of 64 rows with a deeper ring.  (Spreading a tile's columns over two or
-// four warps per row group, CW > 1, measured slower at 32 and 64 columns: 45.8 against 35.8 us and 62.0 against 56.2
-// us for 14336 x 4096 -- the kernel is bound by instructions per MMA, not by warps in flight)
+// four warps per row group measured slower at 32 and 64 columns: 45.8 against 35.8 us and 62.0 against 56.2 us for
+// 14336 x 4096 -- the kernel is bound by instructions per MMA, not by warps in flight)
 template <int T>
 cudaError_t launch_t(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st) {
-  if (ncols <= 8) return launch_w<T, 4, 1, 4, 1>(a, ncols, st);
-  if (ncols <= 16) return launch_w<T, 4, 2, 4, 1>(a, ncols, st);
-  if (ncols <= 32) return launch_w<T, 4, 4, 3, 1>(a, ncols, st);
+  if (ncols <= 8) return launch_w<T, 4, 1, 4>(a, ncols, st);
+  if (ncols <= 16) return launch_w<T, 4, 2, 4>(a, ncols, st);
+  if (ncols <= 32) return launch_w<T, 4, 4, 3>(a, ncols, st);
   const int64_t big = (int64_t)((a.M + 127) / 128) * ((ncols + 63) / 64);
-  return big >= 2 * (int64_t)sm_count ? launch_w<T, 8, 8, 2, 1>(a, ncols, st) : launch_w<T, 4, 8, 3, 1>(a, ncols, st);
+  return big >= 2 * (int64_t)sm_count ? launch_w<T, 8, 8, 2>(a, ncols, st) : launch_w<T, 4, 8, 3>(a, ncols, st);
 }
 
 }  // namespace
