@@ -333,6 +333,24 @@ bool device_pointer(const void* p, int device) {
   return at.type == cudaMemoryTypeDevice && at.device == device;
 }
 
+// The decisions of a bind once the plan is known (guards.hpp:83-186): a zero budget or a model that fits binds as
+// passthrough; else slot / prefetch sizing, then the slots against the budget, then the storage.  device < 0: the
+// storage is not asked of the CUDA runtime (a request checked on a host without a GPU)
+uint32_t budget_decision(const emelb_window_request& r, uint64_t slot_capacity, uint64_t total, int device, bool* fits) {
+  *fits = r.budget_bytes == 0 || total <= r.budget_bytes;
+  if (*fits) return EMELB_WINDOW_OK;
+  const bool config = r.window_slots >= 2 && r.window_slots <= EMELB_WINDOW_MAX_SLOTS && r.prefetch_depth > 0 &&
+                      r.prefetch_depth < r.window_slots;
+  const uint64_t need = uint64_t(r.window_slots) * slot_capacity;
+  if (!config) return EMELB_WINDOW_INVALID_REQUEST;
+  if (need > r.budget_bytes) return EMELB_WINDOW_BUDGET_TOO_SMALL;
+  if (!r.slot_storage || r.slot_storage_bytes < need ||
+      (reinterpret_cast<uintptr_t>(r.slot_storage) % EMELB_WINDOW_SLOT_ALIGNMENT) != 0 ||
+      (device >= 0 && !device_pointer(r.slot_storage, device)))
+    return EMELB_WINDOW_SLOT_STORAGE_TOO_SMALL;
+  return EMELB_WINDOW_OK;
+}
+
 uint32_t do_unbind(emelb_window* w) {
   if (!w->bound) return EMELB_WINDOW_NOT_BOUND;
   cudaSetDevice(w->c->device);
@@ -417,20 +435,8 @@ uint32_t emelb_window_bind(emelb_window* w, const emelb_window_request* request,
   scan_layers(w, r);
   uint64_t total = 0;
   for (const emelb_window_layer& d : w->plan) total += d.slot_bytes;
-  uint32_t err = EMELB_WINDOW_OK;
-  const bool fits = r.budget_bytes == 0 || total <= r.budget_bytes;
-  if (!fits) {
-    // guards.hpp:92-186: slot / prefetch sizing, then the budget, then the storage
-    const bool config = r.window_slots >= 2 && r.window_slots <= EMELB_WINDOW_MAX_SLOTS && r.prefetch_depth > 0 &&
-                        r.prefetch_depth < r.window_slots;
-    const uint64_t need = uint64_t(r.window_slots) * w->slot_capacity;
-    if (!config) err = EMELB_WINDOW_INVALID_REQUEST;
-    else if (need > r.budget_bytes) err = EMELB_WINDOW_BUDGET_TOO_SMALL;
-    else if (!r.slot_storage || r.slot_storage_bytes < need ||
-             (reinterpret_cast<uintptr_t>(r.slot_storage) % EMELB_WINDOW_SLOT_ALIGNMENT) != 0 ||
-             !device_pointer(r.slot_storage, w->c->device))
-      err = EMELB_WINDOW_SLOT_STORAGE_TOO_SMALL;
-  }
+  bool fits = false;
+  const uint32_t err = budget_decision(r, w->slot_capacity, total, w->c->device, &fits);
   if (err != EMELB_WINDOW_OK) {
     release_source(w);
     reset_window(w);
@@ -477,6 +483,24 @@ uint32_t emelb_window_bind(emelb_window* w, const emelb_window_request* request,
     out->source_page_locked = w->page_locked ? 1 : 0;
   }
   return EMELB_WINDOW_OK;
+}
+
+uint32_t emelb_window_check(const emelb_window_request* request, int32_t* streaming_active, uint64_t* slot_capacity_bytes,
+                            uint64_t* total_bytes) {
+  if (!request) return EMELB_WINDOW_INVALID_REQUEST;
+  if (streaming_active) *streaming_active = 0;
+  if (!request_valid(*request)) return EMELB_WINDOW_INVALID_REQUEST;
+  if (request->file_size_bytes > kMaxMappingBytes) return EMELB_WINDOW_SOURCE_MAP_FAILED;
+  emelb_window plan;   // holds the scanned plan only; no device object is touched
+  scan_layers(&plan, *request);
+  uint64_t total = 0;
+  for (const emelb_window_layer& d : plan.plan) total += d.slot_bytes;
+  if (slot_capacity_bytes) *slot_capacity_bytes = plan.slot_capacity;
+  if (total_bytes) *total_bytes = total;
+  bool fits = false;
+  const uint32_t err = budget_decision(*request, plan.slot_capacity, total, -1, &fits);
+  if (err == EMELB_WINDOW_OK && streaming_active) *streaming_active = fits ? 0 : 1;
+  return err;
 }
 
 uint32_t emelb_window_acquire(emelb_window* w, int32_t layer_index, const uint8_t** slot_base, const emelb_window_layer** layout) {

@@ -53,6 +53,7 @@ SIGNATURES = {
     "emelb_window_create": [_P, C.POINTER(_P)],
     "emelb_window_destroy": [_P],
     "emelb_window_bind": [_P, C.POINTER(Request), C.POINTER(Bound)],
+    "emelb_window_check": [C.POINTER(Request), C.POINTER(C.c_int32), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)],
     "emelb_window_acquire": [_P, C.c_int32, C.POINTER(_P), C.POINTER(C.POINTER(Layer))],
     "emelb_window_unbind": [_P],
     "emelb_window_get_stats": [_P, C.POINTER(Stats)],
@@ -87,6 +88,28 @@ def plan_layers(layers):
         offsets.append(offs)
         sizes.append(at)
     return offsets, sizes, max(sizes, default=0)
+
+
+def check_request(file_size: int, layers, budget_bytes: int, window_slots: int = 0, prefetch_depth: int = 0,
+                  stage_chunk_bytes: int = DEFAULT_CHUNK_BYTES, slot_storage: int = 0, slot_storage_bytes: int = 0,
+                  file_path: bytes = b"model.gguf"):
+    """emelb_window_check: the bind decisions for a request, without a GPU.
+    -> (error bits, streaming_active, slot capacity, packed bytes of all layers)"""
+    req = Request()
+    req.file_path, req.file_size_bytes = file_path, file_size
+    flat = [w for weights in layers for w in weights]
+    ext = (Extent * max(1, len(flat)))()
+    for i, (tid, off, size) in enumerate(flat):
+        ext[i].tensor_id, ext[i].file_offset, ext[i].byte_size = tid, off, size
+    counts = (C.c_uint16 * max(1, len(layers)))(*[len(w) for w in layers])
+    req.extents, req.extent_count = ext, len(flat)
+    req.layer_weight_counts, req.layer_count = counts, len(layers)
+    req.budget_bytes, req.window_slots, req.prefetch_depth = budget_bytes, window_slots, prefetch_depth
+    req.stage_chunk_bytes = stage_chunk_bytes
+    req.slot_storage, req.slot_storage_bytes = slot_storage, slot_storage_bytes
+    streaming, cap, total = C.c_int32(0), C.c_uint64(0), C.c_uint64(0)
+    err = eb.lib().emelb_window_check(C.byref(req), C.byref(streaming), C.byref(cap), C.byref(total))
+    return int(err), bool(streaming.value), int(cap.value), int(total.value)
 
 
 def slot_of(layer: int, window_slots: int) -> int:

@@ -138,6 +138,13 @@ EMELB_API uint32_t emelb_window_destroy(emelb_window* w);
  * prefetch_depth layers before it returns. */
 EMELB_API uint32_t emelb_window_bind(emelb_window* w, const emelb_window_request* request, emelb_window_bound* out);
 
+/* The request checks and decisions of emelb_window_bind without binding anything (no GPU needed): the same error
+ * bits in the same order, except that the source is not opened (a missing file is only found by bind) and that
+ * slot_storage is checked for presence, size and alignment only.  Also reports the slot capacity (the largest packed
+ * layer) and the packed size of all layers, which is what a caller sizes slot_storage and the budget from. */
+EMELB_API uint32_t emelb_window_check(const emelb_window_request* request, int32_t* streaming_active,
+                                      uint64_t* slot_capacity_bytes, uint64_t* total_bytes);
+
 /* event::acquire_layer_window: make layer `layer_index`'s weights readable by
  * work enqueued on the context's stream after this call, and advance the ring
  * (submit the load of layer (layer_index + prefetch_depth) % layer_count unless

@@ -109,3 +109,66 @@ def test_package_plan_matches_oracle():
     # the error bits are the reference's (src/emel/model/tensor/window/errors.hpp:9-21)
     assert (ew.INVALID_REQUEST, ew.NOT_BOUND, ew.ALREADY_BOUND, ew.SOURCE_MAP_FAILED, ew.BUDGET_TOO_SMALL, ew.LAYER_OUT_OF_RANGE,
             ew.SLOT_COPY_FAILED, ew.NOT_STREAMING, ew.INTERNAL_ERROR, ew.SLOT_STORAGE_TOO_SMALL) == tuple(1 << i for i in range(10))
+
+
+def test_library_request_check_matches_oracle():
+    """emelb_window_check (no GPU): the reference test cases and random requests, every decision and the plan
+    sizes against the oracle."""
+    layers, size = fixture_layers()
+    aligned_addr = 1 << 20          # any non-null, 64-byte aligned address: the check never touches it
+    cases = [
+        dict(budget=STREAMING_BUDGET, slots=4, depth=2, storage=ARENA),
+        dict(budget=0, slots=4, depth=2, storage=ARENA),
+        dict(budget=0, slots=0, depth=0, storage=0),
+        dict(budget=0, slots=4, depth=2, storage=ARENA, chunk=64 * 1024),
+        dict(budget=STREAMING_BUDGET, slots=1, depth=0, storage=ARENA),
+        dict(budget=STREAMING_BUDGET, slots=4, depth=4, storage=ARENA),
+        dict(budget=STREAMING_BUDGET, slots=9, depth=2, storage=ARENA),
+        dict(budget=STREAMING_BUDGET, slots=4, depth=2, storage=64),
+        dict(budget=STREAMING_BUDGET, slots=4, depth=2, storage=0),
+        dict(budget=3 * 2 * WEIGHT_BYTES, slots=4, depth=2, storage=ARENA),
+        dict(budget=LAYERS * WEIGHTS * WEIGHT_BYTES, slots=4, depth=2, storage=ARENA),
+    ]
+    for c in cases:
+        chunk = c.get("chunk", wo.DEFAULT_CHUNK)
+        err, streaming, cap, total = ew.check_request(size, layers, c["budget"], c["slots"], c["depth"], chunk,
+                                                      aligned_addr if c["storage"] else 0, c["storage"])
+        want = wo.bind_decision(size, layers, c["budget"], c["slots"], c["depth"], c["storage"],
+                                storage_null=c["storage"] == 0, chunk=chunk)
+        assert (err, streaming) == want, (c, err, streaming, want)
+    # an extent past the end; a misaligned arena; a source past the mapping cap
+    bad = [list(ws) for ws in layers]
+    bad[-1][-1] = (bad[-1][-1][0], size - 16, 64)
+    assert ew.check_request(size, bad, 0, 4, 2)[0] == ew.INVALID_REQUEST
+    assert ew.check_request(size, layers, STREAMING_BUDGET, 4, 2, slot_storage=aligned_addr + 8,
+                            slot_storage_bytes=ARENA)[0] == ew.SLOT_STORAGE_TOO_SMALL
+    huge = 1 << 62
+    assert ew.check_request(huge, [[(0, 0, huge)], [(1, 0, huge)]], 64 * 1024, 8, 2, slot_storage=aligned_addr,
+                            slot_storage_bytes=ARENA)[0] == ew.SOURCE_MAP_FAILED
+    assert ew.check_request(size, [], 0)[0] == ew.INVALID_REQUEST
+    assert ew.check_request(size, [[]], 0)[0] == ew.INVALID_REQUEST
+    assert ew.check_request(size, [[(i, HEADER, 16) for i in range(13)]], 0)[0] == ew.INVALID_REQUEST   # 13 weights in a layer
+    assert ew.check_request(0, layers, 0)[0] == ew.INVALID_REQUEST
+    assert ew.check_request(size, layers, 0, file_path=b"")[0] == ew.INVALID_REQUEST
+    # random requests
+    rng = random.Random(11)
+    for _ in range(300):
+        lay, off = [], rng.randrange(0, 4096)
+        for _l in range(rng.randrange(1, 10)):
+            ws = []
+            for _w in range(rng.randrange(1, 10)):
+                n = rng.randrange(1, 50000)
+                ws.append((len(ws), off, n))
+                off += n + rng.randrange(0, 64)
+            lay.append(ws)
+        fsize = off + rng.randrange(0, 100)
+        plan, cap = wo.scan_layers(lay)
+        total = sum(d["slot_bytes"] for d in plan)
+        budget = rng.choice([0, total, total - 1, cap, 2 * cap, 3 * cap, 8 * cap, rng.randrange(1, 2 * total + 2)])
+        slots, depth = rng.randrange(0, 11), rng.randrange(0, 11)
+        storage = rng.choice([0, 64, cap, slots * cap, 8 * cap])
+        err, streaming, cap_got, total_got = ew.check_request(fsize, lay, budget, slots, depth, wo.DEFAULT_CHUNK,
+                                                              aligned_addr if storage else 0, storage)
+        want = wo.bind_decision(fsize, lay, budget, slots, depth, storage, storage_null=storage == 0)
+        assert (err, streaming) == want, (budget, slots, depth, storage, cap, total, err, streaming, want)
+        assert (cap_got, total_got) == (cap, total)
