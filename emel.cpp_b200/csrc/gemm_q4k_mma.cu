@@ -1,4 +1,4 @@
-// 9 to 31 columns of Q4_K weights x Q8_K activations (a decode step of several sequences): too many columns for
+// 5 to 31 columns of Q4_K weights x Q8_K activations (a decode step of several sequences): too many columns for
 // the CUDA-core mat-vec kernels, whose integer dot products per weight byte grow with the column count, and too
 // few to fill the 128-token tile of the tcgen05 kernel.  The integer part runs on the legacy tensor path,
 // mma.sync.m16n8k32 (s8 x s8 -> s32): one instruction = one 32-weight sub-block of 16 rows against 8 columns.

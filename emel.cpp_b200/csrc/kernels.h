@@ -124,7 +124,7 @@ bool gemv_takes_tensor_core(int type, const GemvArgs& a, int ncols);
 bool gemm_q8_mma_supported(int type, const GemvArgs& a, int ncols);
 cudaError_t launch_gemm_q8_mma(int type, const GemvArgs& a, int ncols, int sm_count, cudaStream_t st);
 
-// gemm_q4k_mma.cu: 9 to 31 columns of Q4_K weights (mma.sync int8, one sub-block per instruction)
+// gemm_q4k_mma.cu: 5 to 31 columns of Q4_K weights (mma.sync int8, one sub-block per instruction)
 bool gemm_q6k_mma_supported(int type, const GemvArgs& a, int ncols);
 cudaError_t launch_gemm_q6k_mma(const GemvArgs& a, int ncols, int sm_count, cudaStream_t st);
 bool gemm_q4k_mma_supported(int type, const GemvArgs& a, int ncols);
