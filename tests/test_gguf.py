@@ -240,3 +240,34 @@ def test_file_mapping_and_lookups(tmp_path):
     bad.write_bytes(image[:100])
     assert eb.lib().emelb_gguf_open_file(str(bad).encode(), C.byref(h)) == gguf.PARSE_FAILED and not h.value
     assert eb.lib().emelb_gguf_close(None) == gguf.INVALID_REQUEST
+
+
+def test_layer_extents_feed_a_window_request(tmp_path, port):
+    """The extents a streaming window is bound with, taken from a parsed Llama file: nine tensors per layer in role
+    order, each inside the file and disjoint, and the window's request check accepts them (no GPU involved)."""
+    from emel_cpp_b200 import llama as el, window as ew
+    from tests.test_gpu_gguf import CFG, model_file
+    cfg = dict(CFG, n_layer=3)
+    types = {"embd": eb.Q4_K, "output": eb.Q6_K, "default": eb.Q4_K, el.FFN_DOWN: eb.Q6_K}
+    image, _plan = model_file(port, 5, types, cfg)
+    path = tmp_path / "llama3.gguf"
+    path.write_bytes(image)
+    with gguf.File(str(path)) as f:
+        layers = gguf.layer_extents(f, 3)
+        assert [len(ws) for ws in layers] == [9, 9, 9]
+        spans = sorted((off, off + size) for ws in layers for _tid, off, size in ws)
+        assert all(a1 <= b0 for (_a0, a1), (b0, _b1) in zip(spans, spans[1:]))          # disjoint
+        assert spans[0][0] >= f.data_section_offset and spans[-1][1] <= len(image)
+        for l, ws in enumerate(layers):
+            for (tid, off, size), stem in zip(ws, ("attn_norm", "attn_q", "attn_k", "attn_v", "attn_output", "ffn_norm",
+                                                    "ffn_gate", "ffn_up", "ffn_down")):
+                t = f.find_tensor(f"blk.{l}.{stem}.weight")
+                assert (tid, off, size) == (t["index"], t["file_offset"], t["data_size"])
+        _offs, sizes, cap = ew.plan_layers(layers)
+        err, streaming, cap_lib, total_lib = ew.check_request(len(image), layers, 2 * cap, 2, 1, slot_storage=1 << 20,
+                                                              slot_storage_bytes=2 * cap)
+        assert (err, streaming, cap_lib, total_lib) == (ew.OK, True, cap, sum(sizes))
+        assert ew.check_request(len(image), layers, sum(sizes), 2, 1)[:2] == (ew.OK, False)     # fits: passthrough
+        assert ew.check_request(len(image), layers, cap, 2, 1, slot_storage=1 << 20, slot_storage_bytes=2 * cap)[0] == ew.BUDGET_TOO_SMALL
+        with pytest.raises(gguf.GgufError):
+            gguf.layer_extents(f, 4)       # the file has three layers
