@@ -62,7 +62,8 @@ __device__ __forceinline__ uint32_t minus_32(uint32_t v) { return ((v | 0x808080
 
 // Shared memory: a ring of RS raw windows per row (a window is refilled as soon as it has been expanded, so the copies
 // run under the MMA loops), the expanded block, RS + 1 activation stages.  64 columns: RS = 1, 67 KB, three CTAs per
-// SM, the MMA loop is long enough to cover one copy; 16 and 32 columns: short loops, deeper rings.
+// SM, the MMA loop is long enough to cover one copy; 32 columns: RS = 2; 16 columns: RS = 1 again -- 42 KB, five CTAs
+// per SM, which covers the copy better than a deeper ring in fewer CTAs did (6.73 against 6.76 ms for a batch-16 step).
 template <int NT, int WARPS, int RS>
 __global__ void __launch_bounds__(32 * WARPS) gemm_q6k_mma_kernel(const GemvArgs p, int ncols) {
   using XStage = Q6XStage<NT>;
@@ -227,7 +228,7 @@ cudaError_t launch_gemm_q6k_mma(const GemvArgs& a, int ncols, int sm_count, cuda
   (void)sm_count;
   // column tile by column count: 16, 32 or 64 columns per CTA, 64 rows (32-row tiles for small grids measured no
   // faster: a CTA's walk along K is what takes the time there, and K cannot be split -- the sums are ordered)
-  if (ncols <= 16) return launch_q6<2, 4, 3>(a, ncols, st);
+  if (ncols <= 16) return launch_q6<2, 4, 1>(a, ncols, st);
   if (ncols <= 32) return launch_q6<4, 4, 2>(a, ncols, st);
   return launch_q6<8, 4, 1>(a, ncols, st);
 }
